@@ -1,0 +1,147 @@
+/* mfqb200 -- C ABI of the B200-native MFQ packed-weight execution path.
+ *
+ * Every function returns an int status (MFQB_OK == 0).  On failure a thread-local
+ * message is available from mfqb_last_error().  No exception crosses this boundary.
+ * Device work is enqueued on the caller's stream (a cudaStream_t passed as
+ * mfqb_stream_t; NULL = the legacy default stream) and is asynchronous unless a
+ * function says otherwise.  Handles are opaque and owned by the library until the
+ * matching *_free / *_close call.  There is no CPU execution path: a call that needs
+ * a GPU fails with MFQB_ERR_CUDA when none is usable.
+ *
+ * The comments cite the interface of the reference runtime that each entry point
+ * stands in for (paths inside the reference project).
+ */
+#ifndef MFQB200_H
+#define MFQB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* mfqb_stream_t; /* == cudaStream_t */
+
+enum {
+    MFQB_OK = 0,
+    MFQB_ERR_ARG = 1,         /* bad argument (null pointer, size out of range, wrong handle) */
+    MFQB_ERR_FORMAT = 2,      /* malformed or truncated file / blob */
+    MFQB_ERR_UNSUPPORTED = 3, /* well-formed, but a dtype / profile outside this path */
+    MFQB_ERR_CUDA = 4,        /* CUDA runtime error (message holds the CUDA error string) */
+    MFQB_ERR_IO = 5,          /* file system error */
+    MFQB_ERR_TIMEOUT = 6      /* a bounded device-side wait ran out (multi-GPU paths) */
+};
+
+enum { MFQB_F32 = 0, MFQB_BF16 = 1 }; /* element types of activations / outputs */
+
+enum { MFQB_FAMILY_NINT = 1, MFQB_FAMILY_NVQ = 2 };
+
+const char* mfqb_last_error(void);
+int mfqb_version(void);
+
+/* ---------------------------------------------------------------------------------
+ * MFQ container.  Replaces MfqFile (cpp_runtime/mfq_decode.cpp:1294-1527) and the
+ * Python reader (mfq/formats/io.py:782-831): "MFQ1", version, arch, optional extra
+ * metadata, record table {name, dtype, nbytes}, blobs back to back.  A file whose
+ * length differs from the end of the last blob is rejected.  Shards named
+ * "<stem>-%05d-of-%05d.mfq" are opened together when the first shard is given
+ * (cpp_runtime/mfq_decode.cpp:1359-1427).
+ * --------------------------------------------------------------------------------- */
+typedef struct mfqb_file mfqb_file;
+
+int mfqb_file_open(const char* path, mfqb_file** out);
+int mfqb_file_open_memory(const void* image, uint64_t nbytes, mfqb_file** out); /* copies */
+int mfqb_file_close(mfqb_file* f);
+int mfqb_file_header(const mfqb_file* f, uint32_t* version, const char** arch, int* n_extra,
+                     int* n_records);
+int mfqb_file_extra(const mfqb_file* f, int i, const char** key, const char** json);
+int mfqb_file_record(const mfqb_file* f, int i, const char** name, const char** dtype,
+                     uint64_t* nbytes);
+int mfqb_file_find(const mfqb_file* f, const char* name, int* index); /* -1 if absent */
+/* Pointer to the record's blob inside the mapping (valid until mfqb_file_close). */
+int mfqb_file_blob(const mfqb_file* f, int i, const void** data, uint64_t* nbytes);
+
+/* ---------------------------------------------------------------------------------
+ * Dense quantized weights.  Replaces unpack_nint / unpack_nvq + the to-device copies
+ * (cpp_runtime/mfq_decode.cpp:1546-1589, 2268-2293, 3756-4013, 4121-4139) and the
+ * packed-domain tensor-parallel slicers slice_nint_cpu_output / _input_groups /
+ * slice_nvq_cpu (cpp_runtime/mfq_decode.cpp:1663-1744, 3579-3677).
+ *
+ * dtype is the record's label ("NINT2".."NINT8", "NVQ3", "NVQ3J-512", "NVQ3J",
+ * "NIQ3").  The blob is decoded on the host, re-laid into the device format and
+ * uploaded to `device`; the call returns after the upload has completed.
+ *
+ * axis: 0 = output rows [begin,end), 1 = input columns [begin,end).  Input slices must
+ * start on a group boundary (NINT) / a multiple of 24 (NVQ); begin=0,end=-1 = whole.
+ * --------------------------------------------------------------------------------- */
+typedef struct mfqb_weight mfqb_weight;
+
+typedef struct mfqb_weight_info {
+    int family;          /* MFQB_FAMILY_* */
+    int bits;            /* NINT code width / NVQ index width */
+    int groupsize;
+    int sub_bits;
+    int64_t n;           /* output rows held by this handle */
+    int64_t k;           /* input columns held by this handle */
+    int device;
+    int jsc_banks;       /* NVQ-JSC codebook banks, 0 otherwise */
+    uint64_t payload_bytes; /* algorithmic bytes: the file streams of this (slice of the)
+                               tensor, header excluded -- the roofline numerator */
+    uint64_t device_bytes;  /* bytes this handle actually holds in HBM */
+} mfqb_weight_info;
+
+int mfqb_weight_from_blob(const char* dtype, const void* blob, uint64_t nbytes, int device,
+                          mfqb_weight** out);
+int mfqb_weight_from_blob_slice(const char* dtype, const void* blob, uint64_t nbytes, int axis,
+                                int64_t begin, int64_t end, int device, mfqb_weight** out);
+int mfqb_weight_info_get(const mfqb_weight* w, mfqb_weight_info* info);
+int mfqb_weight_free(mfqb_weight* w);
+
+/* Reference decoder on the GPU: writes the [n, k] row-major dequantized tensor.
+ * out_dtype MFQB_F32 is bit-identical to nint_quant.dequantize / nvq_quant.dequantize /
+ * dequantize_nvq_jsc (mfq/quantize/nint_quant.py:896-908, nvq_quant.py:612-626,
+ * nvq_jsc.py:1053-1079); MFQB_BF16 is the nearest-even rounding of that.
+ * Stands in for dequant_full_packed_* / nvq_dequant_kernel
+ * (mfq/kernels/cuda/nint_matmul.cu:136-161,442-481, nvq_matmul.cu:421-471). */
+int mfqb_dequant(const mfqb_weight* w, void* out, int out_dtype, mfqb_stream_t stream);
+
+/* y[m, n] = x[m, k] . W^T with float32 accumulation.  x is row-major bf16 with exactly
+ * k columns; y is row-major [m, n] in y_dtype.  Any m >= 1 is accepted: m <= 16 runs the
+ * weight-streaming kernel, larger m the tensor-core tile kernel.
+ * Stands in for nint_matmul / nvq_matmul / QuantLinear::forward
+ * (cpp_runtime/mfq_decode.cpp:8130-8315, 7884-7932, 9209). */
+int mfqb_mul_mat(const mfqb_weight* w, const void* x_bf16, int m, void* y, int y_dtype,
+                 mfqb_stream_t stream);
+
+/* Same product with host buffers: copies x to the device, runs, copies y back and
+ * waits.  (The reference runtime keeps activations on the device; this entry point is
+ * what a host-side caller such as the numpy runtime mfq/runtime/linear.py:37-42 uses.) */
+int mfqb_mul_mat_host(const mfqb_weight* w, const void* x_bf16_host, int m, void* y_host,
+                      int y_dtype);
+
+/* ---------------------------------------------------------------------------------
+ * Tensor-parallel slice planner.  Same results and the same rejections as
+ * plan_tensor_parallel_slices / validate_tensor_parallel_slices
+ * (cpp_runtime/tensor_parallel.h:23-118) and tensor_parallel_granularity
+ * (cpp_runtime/mfq_decode.cpp:9445-9461).  weights may be NULL (equal split).
+ * begins/ends receive n_devices entries each.
+ * --------------------------------------------------------------------------------- */
+int mfqb_tp_plan(int64_t extent, int64_t granularity, int n_devices, const double* weights,
+                 int64_t* begins, int64_t* ends);
+int mfqb_tp_validate(int64_t extent, int64_t granularity, int n_slices, const int64_t* begins,
+                     const int64_t* ends);
+int mfqb_tp_granularity(int64_t extent, int64_t preferred, int n_devices, int64_t* out);
+
+/* ---------------------------------------------------------------------------------
+ * Host-side self-check of the device layout (no GPU): packs the blob into the device
+ * format, reads every code and scale field back through the same accessors the kernels
+ * use, and reports the number of mismatches against the file streams.
+ * --------------------------------------------------------------------------------- */
+int mfqb_selfcheck_layout(const char* dtype, const void* blob, uint64_t nbytes,
+                          uint64_t* mismatches);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MFQB200_H */

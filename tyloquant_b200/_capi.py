@@ -1,0 +1,87 @@
+"""ctypes binding of ``libmfqb200.so`` (the C ABI declared in ``include/mfqb200.h``).
+
+The library is built in-tree by :mod:`tyloquant_b200.build`.  There is no fallback: if the
+shared library is missing, importing this module raises.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libmfqb200.so")
+
+OK, ERR_ARG, ERR_FORMAT, ERR_UNSUPPORTED, ERR_CUDA, ERR_IO, ERR_TIMEOUT = range(7)
+F32, BF16 = 0, 1
+FAMILY_NINT, FAMILY_NVQ = 1, 2
+
+
+class MfqbError(RuntimeError):
+    """Raised when a library call returns a non-zero status."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"[mfqb status {code}] {message}")
+        self.code = code
+        self.message = message
+
+
+class WeightInfo(C.Structure):
+    _fields_ = [("family", C.c_int), ("bits", C.c_int), ("groupsize", C.c_int), ("sub_bits", C.c_int),
+                ("n", C.c_int64), ("k", C.c_int64), ("device", C.c_int), ("jsc_banks", C.c_int),
+                ("payload_bytes", C.c_uint64), ("device_bytes", C.c_uint64)]
+
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it with `python -m tyloquant_b200.build` "
+        "(there is no CPU or pure-Python execution path)")
+
+lib = C.CDLL(LIB_PATH)
+
+_vp, _i, _i64, _u64, _cp = C.c_void_p, C.c_int, C.c_int64, C.c_uint64, C.c_char_p
+_P = C.POINTER
+
+_SIGNATURES = {
+    "mfqb_last_error": (_cp, []),
+    "mfqb_version": (_i, []),
+    "mfqb_file_open": (_i, [_cp, _P(_vp)]),
+    "mfqb_file_open_memory": (_i, [_vp, _u64, _P(_vp)]),
+    "mfqb_file_close": (_i, [_vp]),
+    "mfqb_file_header": (_i, [_vp, _P(C.c_uint32), _P(_cp), _P(_i), _P(_i)]),
+    "mfqb_file_extra": (_i, [_vp, _i, _P(_cp), _P(_cp)]),
+    "mfqb_file_record": (_i, [_vp, _i, _P(_cp), _P(_cp), _P(_u64)]),
+    "mfqb_file_find": (_i, [_vp, _cp, _P(_i)]),
+    "mfqb_file_blob": (_i, [_vp, _i, _P(_vp), _P(_u64)]),
+    "mfqb_weight_from_blob": (_i, [_cp, _vp, _u64, _i, _P(_vp)]),
+    "mfqb_weight_from_blob_slice": (_i, [_cp, _vp, _u64, _i, _i64, _i64, _i, _P(_vp)]),
+    "mfqb_weight_info_get": (_i, [_vp, _P(WeightInfo)]),
+    "mfqb_weight_free": (_i, [_vp]),
+    "mfqb_dequant": (_i, [_vp, _vp, _i, _vp]),
+    "mfqb_mul_mat": (_i, [_vp, _vp, _i, _vp, _i, _vp]),
+    "mfqb_mul_mat_host": (_i, [_vp, _vp, _i, _vp, _i]),
+    "mfqb_tp_plan": (_i, [_i64, _i64, _i, _P(C.c_double), _P(_i64), _P(_i64)]),
+    "mfqb_tp_validate": (_i, [_i64, _i64, _i, _P(_i64), _P(_i64)]),
+    "mfqb_tp_granularity": (_i, [_i64, _i64, _i, _P(_i64)]),
+    "mfqb_selfcheck_layout": (_i, [_cp, _vp, _u64, _P(_u64)]),
+}
+
+for _name, (_res, _args) in _SIGNATURES.items():
+    _fn = getattr(lib, _name)
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+def check(status: int) -> None:
+    if status != OK:
+        raise MfqbError(status, lib.mfqb_last_error().decode("utf-8", "replace"))
+
+
+def buffer_address(data) -> tuple[int, int, object]:
+    """(address, nbytes, keepalive) of a bytes-like object, without copying when possible."""
+    mv = memoryview(data)
+    if mv.readonly:
+        keep = (C.c_char * mv.nbytes).from_buffer_copy(mv)
+    else:
+        keep = (C.c_char * mv.nbytes).from_buffer(mv)
+    return C.addressof(keep), mv.nbytes, keep

@@ -1,0 +1,264 @@
+// Weight-streaming GEMV for NINT weights on mma.sync tensor-core tiles.
+//
+//   y[m, n] = sum_k x[m, k] * W[n, k],   W[n, k] = (ns[n]*ss[n,g]) * q[n,k] - (nm[n]*sm[n,g])
+//
+// is evaluated as   ns[n] * sum_g ss[n,g] * (sum_{k in g} q x)  -  nm[n] * sum_g sm[n,g] * xsum[g]
+// with every inner sum in float32:
+//   * the integer codes q go to the tensor cores as exact bf16 values (128 + q, built with one
+//     logic op per code pair; the accumulator starts at -128 * xsum[g]), x as bf16, one
+//     m16n8k16 / m16n8k8 chain per group of a 16-row block, batch rows (m <= 8) in the n8 slot;
+//   * each group accumulator is scaled by its integer sub-scale on the CUDA cores;
+//   * the sub-min term is a second small tensor-core product over the groups of a chunk, with
+//     xsum split into three bf16 pieces (24 significant bits).
+// A warp owns one chunk of 8 groups (its x fragments live in registers) and walks the CTA's
+// row-blocks; partial sums of the chunks meet in shared memory.
+// Replaces gemv_packed_* / gemv_packed_bits_* (mfq/kernels/cuda/nint_matmul.cu:1317-1383,
+// 2598-2872) without their int8 activation quantization.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "nint_layout.h"
+#include "pair_unit.h"
+
+namespace mfqb {
+
+__device__ __forceinline__ void mma_k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                        uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_k8(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(b0));
+}
+
+constexpr uint32_t kBf16x2_128 = 0x43004300u;  // (128.0, 128.0)
+
+__device__ __forceinline__ uint32_t bf162_sub128(uint32_t v) {
+    __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162*>(&v);
+    uint32_t c = kBf16x2_128;
+    __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162*>(&c);
+    __nv_bfloat162 r = __hsub2(a, b);
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+
+// Pair of small unsigned integers (low / high half) -> exact bf16x2.
+template <int W>
+__device__ __forceinline__ uint32_t pair_to_bf162(uint32_t raw) {
+    if constexpr (W <= 7) {
+        return bf162_sub128(raw | kBf16x2_128);
+    } else {
+        __nv_bfloat162 r = __floats2bfloat162_rn((float)(raw & 0xFFFFu), (float)(raw >> 16));
+        return *reinterpret_cast<uint32_t*>(&r);
+    }
+}
+template <int W>
+__device__ __forceinline__ void pair_to_floats(uint32_t raw, float& lo, float& hi) {
+    if constexpr (W <= 7) {
+        const uint32_t u = bf162_sub128(raw | kBf16x2_128);
+        lo = __uint_as_float(u << 16);
+        hi = __uint_as_float(u & 0xFFFF0000u);
+    } else {
+        lo = (float)(raw & 0xFFFFu);
+        hi = (float)(raw >> 16);
+    }
+}
+
+__device__ __forceinline__ uint32_t pack_bf162(float lo, float hi) {
+    __nv_bfloat162 r = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+
+struct GemvArgs {
+    NintDev w;
+    const __nv_bfloat16* x;  // [m, k]
+    void* y;                 // [m, ldy]
+    int m, ldy, y_dtype;
+    int rb_per_cta;          // row-blocks per CTA
+    int xstride;             // shared-memory row stride of x in elements (even)
+};
+
+constexpr int kGemvThreads = 256;
+
+template <int BITS, int PER, int SW>
+__global__ void __launch_bounds__(kGemvThreads, 2) nint_gemv_kernel(const GemvArgs a) {
+    constexpr int G = kChunkGroups, HALF = PER / 2, P = G * PER;
+    constexpr int WC = PairUnit<BITS>::words_for(P), SWC = PairUnit<SW>::words_for(16);
+    constexpr int NPL = BITS == 8 ? 2 : 1;  // 8-bit codes go through as two 4-bit planes
+    using QU = PairUnit<BITS>;
+    using SU = PairUnit<SW>;
+    const NintDev& w = a.w;
+
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int ngp = w.nchunks * G;
+    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem);
+    float* xsum = reinterpret_cast<float*>(smem + (((size_t)a.m * a.xstride * 2 + 15) & ~(size_t)15));
+    float* ypart = xsum + (size_t)ngp * 8;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int q = lane >> 2, c = lane & 3;
+    const int rb0 = blockIdx.x * a.rb_per_cta;
+    const int rb1 = min(rb0 + a.rb_per_cta, w.nrb);
+    const int nrb = rb1 - rb0;
+
+    // ---- stage x (zero beyond k), group sums, clear partials ---------------------------
+    for (int m = 0; m < a.m; ++m) {
+        const __nv_bfloat16* src = a.x + (size_t)m * w.k;
+        __nv_bfloat16* dst = xs + (size_t)m * a.xstride;
+        for (int i = tid; i < a.xstride; i += kGemvThreads) dst[i] = i < w.k ? src[i] : __float2bfloat16(0.f);
+    }
+    for (int i = tid; i < nrb * 128; i += kGemvThreads) ypart[i] = 0.f;
+    __syncthreads();
+    for (int i = tid; i < ngp * 8; i += kGemvThreads) {
+        const int grp = i >> 3, n = i & 7;
+        float s = 0.f;
+        if (n < a.m) {
+            const __nv_bfloat16* p = xs + (size_t)n * a.xstride + (size_t)grp * w.gs;
+            for (int e = 0; e < w.gs; ++e) s += __bfloat162float(p[e]);
+        }
+        xsum[i] = s;
+    }
+    __syncthreads();
+
+    const uint32_t* xrow = reinterpret_cast<const uint32_t*>(xs + (size_t)q * a.xstride);
+    const bool has_col = q < a.m;
+
+    for (int seg = warp; seg < w.nchunks; seg += kGemvThreads / 32) {
+        // x fragments of this chunk (batch column q), accumulator seeds, sub-min operand
+        uint32_t xf[G][HALF];
+        float ci[G][2];
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const int grp = seg * G + g;
+#pragma unroll
+            for (int j = 0; j < HALF; ++j) {
+                const bool ok = has_col && (c * PER + 2 * j < w.gs);
+                xf[g][j] = ok ? xrow[(grp * w.gs + c * PER) / 2 + j] : 0u;
+            }
+            const float2 s = *reinterpret_cast<const float2*>(&xsum[grp * 8 + 2 * c]);
+            ci[g][0] = -128.f * s.x;
+            ci[g][1] = -128.f * s.y;
+        }
+        uint32_t bmin[3];
+        {
+            float v0 = xsum[(seg * G + 2 * c) * 8 + q], v1 = xsum[(seg * G + 2 * c + 1) * 8 + q];
+#pragma unroll
+            for (int s = 0; s < 3; ++s) {
+                const __nv_bfloat16 h0 = __float2bfloat16_rn(v0), h1 = __float2bfloat16_rn(v1);
+                v0 -= __bfloat162float(h0);
+                v1 -= __bfloat162float(h1);
+                __nv_bfloat162 pr;
+                pr.x = h0;
+                pr.y = h1;
+                bmin[s] = *reinterpret_cast<uint32_t*>(&pr);
+            }
+        }
+
+        for (int rb = rb0; rb < rb1; ++rb) {
+            const size_t item = (size_t)rb * w.nchunks + seg;
+            uint32_t qw[WC], sw[SWC];
+#pragma unroll
+            for (int j = 0; j < WC; ++j) qw[j] = __ldg(w.qwords + (item * WC + j) * 32 + lane);
+#pragma unroll
+            for (int j = 0; j < SWC; ++j) sw[j] = __ldg(w.swords + (item * SWC + j) * 8 + q);
+            const uint32_t an_lo = __ldg(w.anchors + rb * 16 + q), an_hi = __ldg(w.anchors + rb * 16 + 8 + q);
+
+            float tot[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float acc[NPL][4];
+#pragma unroll
+                for (int pl = 0; pl < NPL; ++pl) {
+                    acc[pl][0] = ci[g][0];
+                    acc[pl][1] = ci[g][1];
+                    acc[pl][2] = ci[g][0];
+                    acc[pl][3] = ci[g][1];
+                }
+#pragma unroll
+                for (int j = 0; j + 1 < HALF; j += 2) {
+                    const uint32_t r0 = QU::at(qw, (g * 2 + 0) * HALF + j), r1 = QU::at(qw, (g * 2 + 1) * HALF + j);
+                    const uint32_t r2 = QU::at(qw, (g * 2 + 0) * HALF + j + 1), r3 = QU::at(qw, (g * 2 + 1) * HALF + j + 1);
+                    if constexpr (NPL == 1) {
+                        mma_k16(acc[0], r0 | kBf16x2_128, r1 | kBf16x2_128, r2 | kBf16x2_128, r3 | kBf16x2_128, xf[g][j],
+                                xf[g][j + 1]);
+                    } else {
+                        constexpr uint32_t NIB = 0x000F000Fu;
+                        mma_k16(acc[0], (r0 & NIB) | kBf16x2_128, (r1 & NIB) | kBf16x2_128, (r2 & NIB) | kBf16x2_128,
+                                (r3 & NIB) | kBf16x2_128, xf[g][j], xf[g][j + 1]);
+                        mma_k16(acc[1], ((r0 >> 4) & NIB) | kBf16x2_128, ((r1 >> 4) & NIB) | kBf16x2_128,
+                                ((r2 >> 4) & NIB) | kBf16x2_128, ((r3 >> 4) & NIB) | kBf16x2_128, xf[g][j], xf[g][j + 1]);
+                    }
+                }
+                if constexpr (HALF & 1) {
+                    constexpr int j = HALF - 1;
+                    const uint32_t r0 = QU::at(qw, (g * 2 + 0) * HALF + j), r1 = QU::at(qw, (g * 2 + 1) * HALF + j);
+                    if constexpr (NPL == 1) {
+                        mma_k8(acc[0], r0 | kBf16x2_128, r1 | kBf16x2_128, xf[g][j]);
+                    } else {
+                        constexpr uint32_t NIB = 0x000F000Fu;
+                        mma_k8(acc[0], (r0 & NIB) | kBf16x2_128, (r1 & NIB) | kBf16x2_128, xf[g][j]);
+                        mma_k8(acc[1], ((r0 >> 4) & NIB) | kBf16x2_128, ((r1 >> 4) & NIB) | kBf16x2_128, xf[g][j]);
+                    }
+                }
+                float s_lo, s_hi;
+                pair_to_floats<SW>(SU::at(sw, g), s_lo, s_hi);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float v = acc[0][e];
+                    if constexpr (NPL == 2) v = fmaf(16.f, acc[1][e], v);
+                    tot[e] = fmaf(e < 2 ? s_lo : s_hi, v, tot[e]);
+                }
+            }
+            // sub-min term: rows (lo, hi) x groups (2c, 2c+1) of this chunk against xsum
+            uint32_t m_lo, m_hi;
+            switch (c) {
+                case 0: m_lo = SU::at(sw, 8); m_hi = SU::at(sw, 12); break;
+                case 1: m_lo = SU::at(sw, 9); m_hi = SU::at(sw, 13); break;
+                case 2: m_lo = SU::at(sw, 10); m_hi = SU::at(sw, 14); break;
+                default: m_lo = SU::at(sw, 11); m_hi = SU::at(sw, 15); break;
+            }
+            m_lo = pair_to_bf162<SW>(m_lo);
+            m_hi = pair_to_bf162<SW>(m_hi);
+            float mt[4] = {0.f, 0.f, 0.f, 0.f};
+            mma_k8(mt, m_lo, m_hi, bmin[2]);
+            mma_k8(mt, m_lo, m_hi, bmin[1]);
+            mma_k8(mt, m_lo, m_hi, bmin[0]);
+
+            const __half2 h_lo = *reinterpret_cast<const __half2*>(&an_lo), h_hi = *reinterpret_cast<const __half2*>(&an_hi);
+            const float2 f_lo = __half22float2(h_lo), f_hi = __half22float2(h_hi);  // (ns, nm)
+            float* yp = ypart + (size_t)(rb - rb0) * 128;
+            atomicAdd(yp + q * 8 + 2 * c, f_lo.x * tot[0] - f_lo.y * mt[0]);
+            atomicAdd(yp + q * 8 + 2 * c + 1, f_lo.x * tot[1] - f_lo.y * mt[1]);
+            atomicAdd(yp + (q + 8) * 8 + 2 * c, f_hi.x * tot[2] - f_hi.y * mt[2]);
+            atomicAdd(yp + (q + 8) * 8 + 2 * c + 1, f_hi.x * tot[3] - f_hi.y * mt[3]);
+        }
+    }
+    __syncthreads();
+    const int rows = nrb * 16;
+    for (int i = tid; i < rows * a.m; i += kGemvThreads) {
+        const int n = i / rows, rr = i % rows, row = rb0 * 16 + rr;
+        if (row < w.n) {
+            const float v = ypart[rr * 8 + n];
+            if (a.y_dtype == 0 /* MFQB_F32 */) reinterpret_cast<float*>(a.y)[(size_t)n * a.ldy + row] = v;
+            else reinterpret_cast<__nv_bfloat16*>(a.y)[(size_t)n * a.ldy + row] = __float2bfloat16_rn(v);
+        }
+    }
+}
+
+// Shared-memory footprint and launch geometry, computed on the host.
+struct GemvPlan {
+    int xstride, rb_per_cta, grid;
+    size_t smem;
+};
+GemvPlan plan_nint_gemv(const NintDev& w, int m, int num_sms);
+
+template <int BITS>
+cudaError_t launch_nint_gemv_bits(const GemvArgs& a, const GemvPlan& p, cudaStream_t stream);
+
+}  // namespace mfqb

@@ -1,0 +1,35 @@
+// NINT5 instantiations of the weight-streaming GEMV (one translation unit per code width
+// so the widths compile in parallel).
+#include "nint_gemv.cuh"
+
+namespace mfqb {
+
+template <int BITS, int PER, int SW>
+static cudaError_t launch_one(const GemvArgs& a, const GemvPlan& p, cudaStream_t stream) {
+    auto kern = nint_gemv_kernel<BITS, PER, SW>;
+    if (p.smem > 48 * 1024) {
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem);
+        if (e != cudaSuccess) return e;
+    }
+    kern<<<p.grid, kGemvThreads, p.smem, stream>>>(a);
+    return cudaGetLastError();
+}
+
+template <>
+cudaError_t launch_nint_gemv_bits<5>(const GemvArgs& a, const GemvPlan& p, cudaStream_t stream) {
+    switch (a.w.per * 16 + a.w.sw) {
+        case 71: return launch_one<5, 4, 7>(a, p, stream);
+        case 72: return launch_one<5, 4, 8>(a, p, stream);
+        case 103: return launch_one<5, 6, 7>(a, p, stream);
+        case 104: return launch_one<5, 6, 8>(a, p, stream);
+        case 135: return launch_one<5, 8, 7>(a, p, stream);
+        case 136: return launch_one<5, 8, 8>(a, p, stream);
+        case 199: return launch_one<5, 12, 7>(a, p, stream);
+        case 200: return launch_one<5, 12, 8>(a, p, stream);
+        case 263: return launch_one<5, 16, 7>(a, p, stream);
+        case 264: return launch_one<5, 16, 8>(a, p, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace mfqb

@@ -1,0 +1,319 @@
+// Dense weight handles: blob -> device layout -> decode / multiply entry points.
+#include <cuda_bf16.h>
+
+#include <memory>
+#include <mutex>
+
+#include "cuda_util.h"
+#include "nint_gemv.cuh"
+#include "nvq.h"
+
+namespace mfqb {
+
+int device_sm_count(int device) {
+    static std::mutex mu;
+    static int cache[64] = {0};
+    std::lock_guard<std::mutex> lock(mu);
+    if (device < 0 || device >= 64) fail(MFQB_ERR_ARG, "device index %d out of range", device);
+    if (!cache[device]) {
+        int v = 0;
+        MFQB_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, device));
+        cache[device] = v;
+    }
+    return cache[device];
+}
+
+GemvPlan plan_nint_gemv(const NintDev& w, int m, int num_sms) {
+    GemvPlan p;
+    const int kp = w.nchunks * kChunkGroups * w.gs;      // zero-padded columns
+    int words = (kp + 1) / 2;
+    // Row stride (in 32-bit words) congruent to 2*PER mod 32: the eight batch rows a warp reads
+    // together then fall into distinct shared-memory banks.
+    words += (((2 * w.per - words) % 32) + 32) % 32;
+    p.xstride = words * 2;
+    const int target = 2 * num_sms;
+    p.rb_per_cta = (w.nrb + target - 1) / target;
+    p.grid = (w.nrb + p.rb_per_cta - 1) / p.rb_per_cta;
+    p.smem = (((size_t)m * p.xstride * 2 + 15) & ~(size_t)15) + (size_t)w.nchunks * kChunkGroups * 8 * 4 +
+             (size_t)p.rb_per_cta * 128 * 4;
+    return p;
+}
+
+// ---- reference decoder on the GPU -----------------------------------------------------------
+// One thread per (row, group, lane-of-quad): reads its code pairs and the two scale fields
+// through the same accessors as the GEMV and writes w = fl(fl(d*q) - m), d = fl(ns*ss),
+// m = fl(nm*sm): three separately rounded float32 operations, as the reference decoder does
+// (mfq/quantize/nint_quant.py:896-908).
+template <int SW>
+__device__ __forceinline__ void read_scales(const NintDev& w, size_t item, int q, int r, int g, float& ss, float& sm) {
+    constexpr int SWC = PairUnit<SW>::words_for(16);
+    uint32_t sq[SWC];
+#pragma unroll
+    for (int i = 0; i < SWC; ++i) sq[i] = w.swords[(item * SWC + i) * 8 + q];
+    const uint32_t sp = PairUnit<SW>::get_rt(sq + (g / PairUnit<SW>::NP) * PairUnit<SW>::U, g % PairUnit<SW>::NP);
+    const int mt = 8 + 4 * r + g / 2;
+    const uint32_t mp = PairUnit<SW>::get_rt(sq + (mt / PairUnit<SW>::NP) * PairUnit<SW>::U, mt % PairUnit<SW>::NP);
+    ss = (float)(r ? (sp >> 16) : (sp & 0xFFFFu));
+    sm = (float)((g & 1) ? (mp >> 16) : (mp & 0xFFFFu));
+}
+
+template <int BITS>
+__global__ void nint_dequant_kernel(const NintDev w, void* out, int out_dtype) {
+    using QU = PairUnit<BITS>;
+    const size_t total = (size_t)w.n * w.ng * 4;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const int c = (int)(idx & 3);
+        const size_t rg = idx >> 2;
+        const int grp = (int)(rg % w.ng), row = (int)(rg / w.ng);
+        const int rb = row >> 4, q = row & 7, r = (row >> 3) & 1, ch = grp / kChunkGroups, g = grp % kChunkGroups;
+        const int lane = 4 * q + c, half = w.per / 2;
+        const size_t item = (size_t)rb * w.nchunks + ch;
+        float ss, sm;
+        switch (w.sw) {
+            case 5: read_scales<5>(w, item, q, r, g, ss, sm); break;
+            case 6: read_scales<6>(w, item, q, r, g, ss, sm); break;
+            case 7: read_scales<7>(w, item, q, r, g, ss, sm); break;
+            default: read_scales<8>(w, item, q, r, g, ss, sm); break;
+        }
+        const uint32_t an = w.anchors[row];
+        const float2 nsm = __half22float2(*reinterpret_cast<const __half2*>(&an));
+        const float d = __fmul_rn(nsm.x, ss), m = __fmul_rn(nsm.y, sm);
+        for (int j = 0; j < half; ++j) {
+            const int t = (g * 2 + r) * half + j, unit = t / QU::NP;
+            uint32_t uw[QU::U];
+#pragma unroll
+            for (int u = 0; u < QU::U; ++u) uw[u] = w.qwords[(item * w.wc + unit * QU::U + u) * 32 + lane];
+            const uint32_t pr = QU::get_rt(uw, t % QU::NP);
+            const int i0 = c * w.per + 2 * j, k0 = grp * w.gs + i0;
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                if (i0 + e < w.gs && k0 + e < w.k) {
+                    const float code = (float)(e ? (pr >> 16) : (pr & 0xFFFFu));
+                    const float v = __fsub_rn(__fmul_rn(d, code), m);
+                    const size_t o = (size_t)row * w.k + k0 + e;
+                    if (out_dtype == MFQB_F32) reinterpret_cast<float*>(out)[o] = v;
+                    else reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(v);
+                }
+            }
+        }
+    }
+}
+
+static void launch_nint_dequant(const NintDev& w, void* out, int out_dtype, cudaStream_t s) {
+    const size_t total = (size_t)w.n * w.ng * 4;
+    const int block = 256;
+    const int grid = (int)std::min<size_t>((total + block - 1) / block, 148 * 32);
+    switch (w.bits) {
+        case 2: nint_dequant_kernel<2><<<grid, block, 0, s>>>(w, out, out_dtype); break;
+        case 3: nint_dequant_kernel<3><<<grid, block, 0, s>>>(w, out, out_dtype); break;
+        case 4: nint_dequant_kernel<4><<<grid, block, 0, s>>>(w, out, out_dtype); break;
+        case 5: nint_dequant_kernel<5><<<grid, block, 0, s>>>(w, out, out_dtype); break;
+        case 6: nint_dequant_kernel<6><<<grid, block, 0, s>>>(w, out, out_dtype); break;
+        case 8: nint_dequant_kernel<8><<<grid, block, 0, s>>>(w, out, out_dtype); break;
+        default: fail(MFQB_ERR_UNSUPPORTED, "NINT%d has no kernel", w.bits);
+    }
+    MFQB_CUDA(cudaGetLastError());
+}
+
+static void launch_nint_gemv(const NintDev& w, const void* x, int m, void* y, int y_dtype, int ldy, int device,
+                             cudaStream_t s) {
+    GemvArgs a;
+    a.w = w;
+    a.x = static_cast<const __nv_bfloat16*>(x);
+    a.y = y;
+    a.m = m;
+    a.ldy = ldy;
+    a.y_dtype = y_dtype;
+    const GemvPlan p = plan_nint_gemv(w, m, device_sm_count(device));
+    a.rb_per_cta = p.rb_per_cta;
+    a.xstride = p.xstride;
+    cudaError_t e;
+    switch (w.bits) {
+        case 2: e = launch_nint_gemv_bits<2>(a, p, s); break;
+        case 3: e = launch_nint_gemv_bits<3>(a, p, s); break;
+        case 4: e = launch_nint_gemv_bits<4>(a, p, s); break;
+        case 5: e = launch_nint_gemv_bits<5>(a, p, s); break;
+        case 6: e = launch_nint_gemv_bits<6>(a, p, s); break;
+        case 8: e = launch_nint_gemv_bits<8>(a, p, s); break;
+        default: fail(MFQB_ERR_UNSUPPORTED, "NINT%d has no kernel", w.bits);
+    }
+    if (e != cudaSuccess) fail(MFQB_ERR_CUDA, "NINT%d gs=%d GEMV launch: %s", w.bits, w.gs, cudaGetErrorString(e));
+}
+
+}  // namespace mfqb
+
+using namespace mfqb;
+
+struct mfqb_weight {
+    int family = 0, device = 0;
+    mfqb_weight_info info{};
+    NintDev nint{};
+    DevBuf qwords, swords, anchors;
+    NvqDevicePtr nvq;
+};
+
+namespace mfqb {
+
+// Largest batch the GEMV can stage in shared memory for this weight.
+static int nint_gemv_max_batch(const NintDev& w, int device) {
+    for (int m = 8; m >= 1; --m)
+        if (plan_nint_gemv(w, m, device_sm_count(device)).smem <= 200 * 1024) return m;
+    return 0;
+}
+
+static void check_nint_supported(const HostNint& t) {
+    const int b = t.bits;
+    if (!(b == 2 || b == 3 || b == 4 || b == 5 || b == 6 || b == 8))
+        fail(MFQB_ERR_UNSUPPORTED, "NINT%d is not an executable code width (2,3,4,5,6,8)", b);
+    if (t.gs % 2 || t.gs < 8 || t.gs > 64) fail(MFQB_ERR_UNSUPPORTED, "NINT groupsize %d is outside the runtime catalog", t.gs);
+    const int per = nint_per(t.gs);
+    const bool ok = (b == 2 && per == 4) || (b == 3 && per == 6) || (b == 4 && (per == 4 || per == 6 || per == 8 || per == 12)) ||
+                    ((b == 5 || b == 8) && (per == 4 || per == 6 || per == 8 || per == 12 || per == 16)) ||
+                    (b == 6 && (per == 6 || per == 8 || per == 10 || per == 12 || per == 16));
+    if (!ok) fail(MFQB_ERR_UNSUPPORTED, "NINT%d with groupsize %d is outside the runtime catalog", b, t.gs);
+}
+
+static mfqb_weight* make_nint_weight(const HostNint& t, int device) {
+    check_nint_supported(t);
+    NintPacked p = pack_nint_device(t);
+    auto w = std::make_unique<mfqb_weight>();
+    DeviceGuard guard(device);
+    w->family = MFQB_FAMILY_NINT;
+    w->device = device;
+    w->qwords.upload(p.qwords.data(), p.qwords.size() * 4);
+    w->swords.upload(p.swords.data(), p.swords.size() * 4);
+    w->anchors.upload(p.anchors.data(), p.anchors.size() * 4);
+    w->nint = p.d;
+    w->nint.qwords = static_cast<const uint32_t*>(w->qwords.p);
+    w->nint.swords = static_cast<const uint32_t*>(w->swords.p);
+    w->nint.anchors = static_cast<const uint32_t*>(w->anchors.p);
+    mfqb_weight_info& i = w->info;
+    i.family = MFQB_FAMILY_NINT;
+    i.bits = t.bits;
+    i.groupsize = t.gs;
+    i.sub_bits = t.sub_bits;
+    i.n = t.n;
+    i.k = t.k;
+    i.device = device;
+    i.jsc_banks = 0;
+    i.payload_bytes = nint_payload_bytes(t);
+    i.device_bytes = w->qwords.bytes + w->swords.bytes + w->anchors.bytes;
+    return w.release();
+}
+
+}  // namespace mfqb
+
+extern "C" {
+#pragma GCC visibility push(default)
+
+int mfqb_weight_from_blob_slice(const char* dtype, const void* blob, uint64_t nbytes, int axis, int64_t begin,
+                                int64_t end, int device, mfqb_weight** out) {
+    return guarded([&] {
+        if (!dtype || !blob || !out) fail(MFQB_ERR_ARG, "mfqb_weight_from_blob: null argument");
+        const std::string d(dtype);
+        const bool whole = begin == 0 && end < 0;
+        if (dtype_is_nint(d)) {
+            HostNint t = parse_nint(blob, nbytes);
+            if (d[4] - '0' != t.bits) fail(MFQB_ERR_FORMAT, "MFQ dtype/blob mismatch: %s contains NINT%d", dtype, t.bits);
+            *out = whole ? make_nint_weight(t, device) : make_nint_weight(slice_nint(t, axis, begin, end), device);
+        } else if (dtype_is_nvq(d)) {
+            HostNvq t = parse_nvq(blob, nbytes);
+            check_nvq_dtype(d, t);
+            auto w = std::make_unique<mfqb_weight>();
+            w->family = MFQB_FAMILY_NVQ;
+            w->device = device;
+            w->nvq = make_nvq_device(whole ? t : slice_nvq(t, axis, begin, end), device, &w->info);
+            *out = w.release();
+        } else {
+            fail(MFQB_ERR_UNSUPPORTED, "dtype '%s' is outside the packed-weight execution path", dtype);
+        }
+    });
+}
+
+int mfqb_weight_from_blob(const char* dtype, const void* blob, uint64_t nbytes, int device, mfqb_weight** out) {
+    return mfqb_weight_from_blob_slice(dtype, blob, nbytes, 0, 0, -1, device, out);
+}
+
+int mfqb_weight_info_get(const mfqb_weight* w, mfqb_weight_info* info) {
+    return guarded([&] {
+        if (!w || !info) fail(MFQB_ERR_ARG, "mfqb_weight_info_get: null argument");
+        *info = w->info;
+    });
+}
+
+int mfqb_weight_free(mfqb_weight* w) {
+    return guarded([&] {
+        if (!w) return;
+        DeviceGuard guard(w->device);
+        delete w;
+    });
+}
+
+int mfqb_dequant(const mfqb_weight* w, void* out, int out_dtype, mfqb_stream_t stream) {
+    return guarded([&] {
+        if (!w || !out) fail(MFQB_ERR_ARG, "mfqb_dequant: null argument");
+        if (out_dtype != MFQB_F32 && out_dtype != MFQB_BF16) fail(MFQB_ERR_ARG, "mfqb_dequant: bad output dtype");
+        DeviceGuard guard(w->device);
+        if (w->family == MFQB_FAMILY_NINT) launch_nint_dequant(w->nint, out, out_dtype, stream);
+        else nvq_dequant(*w->nvq, out, out_dtype, stream);
+    });
+}
+
+int mfqb_mul_mat(const mfqb_weight* w, const void* x, int m, void* y, int y_dtype, mfqb_stream_t stream) {
+    return guarded([&] {
+        if (!w || !x || !y) fail(MFQB_ERR_ARG, "mfqb_mul_mat: null argument");
+        if (m < 1) fail(MFQB_ERR_ARG, "mfqb_mul_mat: m must be >= 1, got %d", m);
+        if (y_dtype != MFQB_F32 && y_dtype != MFQB_BF16) fail(MFQB_ERR_ARG, "mfqb_mul_mat: bad output dtype");
+        DeviceGuard guard(w->device);
+        const int64_t n = w->info.n, k = w->info.k;
+        const size_t ysz = y_dtype == MFQB_F32 ? 4 : 2;
+        if (w->family == MFQB_FAMILY_NINT) {
+            const int mb = nint_gemv_max_batch(w->nint, w->device);
+            if (mb == 0) fail(MFQB_ERR_UNSUPPORTED, "k=%lld is too long for the shared-memory staging of the GEMV", (long long)k);
+            for (int m0 = 0; m0 < m; m0 += mb) {
+                const int mm = std::min(mb, m - m0);
+                launch_nint_gemv(w->nint, static_cast<const char*>(x) + (size_t)m0 * k * 2, mm,
+                                 static_cast<char*>(y) + (size_t)m0 * n * ysz, y_dtype, (int)n, w->device, stream);
+            }
+        } else {
+            nvq_mul_mat(*w->nvq, x, m, y, y_dtype, stream);
+        }
+    });
+}
+
+int mfqb_mul_mat_host(const mfqb_weight* w, const void* x_host, int m, void* y_host, int y_dtype) {
+    return guarded([&] {
+        if (!w || !x_host || !y_host) fail(MFQB_ERR_ARG, "mfqb_mul_mat_host: null argument");
+        if (m < 1) fail(MFQB_ERR_ARG, "mfqb_mul_mat_host: m must be >= 1");
+        DeviceGuard guard(w->device);
+        const size_t xb = (size_t)m * w->info.k * 2, yb = (size_t)m * w->info.n * (y_dtype == MFQB_F32 ? 4 : 2);
+        DevBuf dx, dy;
+        dx.alloc(xb);
+        dy.alloc(yb);
+        cudaStream_t s = nullptr;
+        MFQB_CUDA(cudaMemcpyAsync(dx.p, x_host, xb, cudaMemcpyHostToDevice, s));
+        const int rc = mfqb_mul_mat(w, dx.p, m, dy.p, y_dtype, s);
+        if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
+        MFQB_CUDA(cudaMemcpyAsync(y_host, dy.p, yb, cudaMemcpyDeviceToHost, s));
+        MFQB_CUDA(cudaStreamSynchronize(s));
+    });
+}
+
+int mfqb_selfcheck_layout(const char* dtype, const void* blob, uint64_t nbytes, uint64_t* mismatches) {
+    return guarded([&] {
+        if (!dtype || !blob || !mismatches) fail(MFQB_ERR_ARG, "mfqb_selfcheck_layout: null argument");
+        const std::string d(dtype);
+        if (dtype_is_nint(d)) {
+            HostNint t = parse_nint(blob, nbytes);
+            check_nint_supported(t);
+            *mismatches = selfcheck_nint_layout(t);
+        } else if (dtype_is_nvq(d)) {
+            *mismatches = selfcheck_nvq_layout(parse_nvq(blob, nbytes));
+        } else {
+            fail(MFQB_ERR_UNSUPPORTED, "dtype '%s' is outside the packed-weight execution path", dtype);
+        }
+    });
+}
+
+#pragma GCC visibility pop
+}  // extern "C"

@@ -1,0 +1,93 @@
+"""Dense quantized weights on a GPU (mirrors ``NintWeight`` / ``NvqWeight`` with
+``nint_matmul`` / ``nvq_matmul`` / ``QuantLinear::forward`` of the reference runtime,
+cpp_runtime/mfq_decode.cpp:2102-2165, 4027-4055, 8130-8315, 7884-7932, 9209).
+
+torch is used only for device memory and streams; all arithmetic runs in the library."""
+
+from __future__ import annotations
+
+import ctypes as C
+
+from . import _capi
+from ._capi import BF16, F32, WeightInfo, check, lib
+
+
+def _torch():
+    import torch
+    return torch
+
+
+def _stream_ptr(device_index: int) -> int:
+    return _torch().cuda.current_stream(device_index).cuda_stream
+
+
+class QuantWeight:
+    """One NINT or NVQ3 tensor, decoded from its MFQ blob into the device layout."""
+
+    def __init__(self, handle: C.c_void_p):
+        self._h = handle
+        info = WeightInfo()
+        check(lib.mfqb_weight_info_get(self._h, C.byref(info)))
+        self.info = info
+        self.n, self.k, self.device = info.n, info.k, info.device
+
+    @classmethod
+    def from_blob(cls, dtype: str, blob, device: int = 0, *, axis: int = 0, begin: int = 0, end: int = -1):
+        addr, n, keep = _capi.buffer_address(blob)
+        h = C.c_void_p()
+        check(lib.mfqb_weight_from_blob_slice(dtype.encode(), addr, n, axis, begin, end, device, C.byref(h)))
+        del keep
+        return cls(h)
+
+    @property
+    def payload_bytes(self) -> int:
+        return self.info.payload_bytes
+
+    @property
+    def device_bytes(self) -> int:
+        return self.info.device_bytes
+
+    def dequantize(self, dtype="float32"):
+        """[n, k] tensor: float32 is bit-identical to the reference decoder."""
+        torch = _torch()
+        tdt = torch.float32 if str(dtype).endswith("float32") else torch.bfloat16
+        out = torch.empty((self.n, self.k), dtype=tdt, device=f"cuda:{self.device}")
+        check(lib.mfqb_dequant(self._h, out.data_ptr(), F32 if tdt == torch.float32 else BF16, _stream_ptr(self.device)))
+        return out
+
+    def matmul(self, x, out_dtype=None):
+        """``y = x @ W.T`` for a bf16 CUDA tensor ``x`` of shape [m, k] (or [k])."""
+        torch = _torch()
+        squeeze = x.dim() == 1
+        x2 = x.reshape(1, -1) if squeeze else x
+        if x2.dtype != torch.bfloat16 or not x2.is_cuda or x2.device.index != self.device:
+            raise ValueError(f"x must be a bfloat16 tensor on cuda:{self.device}")
+        if x2.shape[-1] != self.k:
+            raise ValueError(f"x has {x2.shape[-1]} columns, the weight has k={self.k}")
+        x2 = x2.contiguous()
+        tdt = out_dtype or torch.bfloat16
+        y = torch.empty((x2.shape[0], self.n), dtype=tdt, device=x2.device)
+        check(lib.mfqb_mul_mat(self._h, x2.data_ptr(), x2.shape[0], y.data_ptr(),
+                               F32 if tdt == torch.float32 else BF16, _stream_ptr(self.device)))
+        return y[0] if squeeze else y
+
+    def matmul_host(self, x_bits, out_f32: bool = False):
+        """Host-buffer product: ``x_bits`` is a uint16 numpy array of bf16 bit patterns [m, k];
+        returns a numpy array (uint16 bf16 bits, or float32)."""
+        import numpy as np
+        x_bits = np.ascontiguousarray(x_bits, dtype=np.uint16).reshape(-1, self.k)
+        m = x_bits.shape[0]
+        y = np.empty((m, self.n), dtype=np.float32 if out_f32 else np.uint16)
+        check(lib.mfqb_mul_mat_host(self._h, x_bits.ctypes.data, m, y.ctypes.data, F32 if out_f32 else BF16))
+        return y
+
+    def free(self) -> None:
+        if self._h:
+            lib.mfqb_weight_free(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
