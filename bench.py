@@ -1,0 +1,370 @@
+"""Benchmark of the packed-weight GEMV (the headline metric: packed GEMV HBM GB/s).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (``config.workload``): BASELINE config 1 -- one 4096 x 4096 NINT3 (3, 24, 5) weight,
+x = 1 x 4096 bf16, y = x W^T with float32 accumulation.  One weight is 7.2 MB and would sit in
+the 126 MB L2, so a *step* is one GEMV over each of ``pool`` distinct seeded weights (pool x 7.2 MB
+> 2.5 x L2): every launch streams its weight from HBM.  The step is captured once in a CUDA
+graph and replayed.  ``value`` = algorithmic bytes of the step / device time, inputs resident
+in HBM.  ``e2e`` = the same step through the host-buffer entry point (x copied in from pinned
+memory and y copied back inside the timed region, every launch).
+
+With N > 1 (torchrun, one rank per GPU) every rank runs the same step on its own replica of
+the pool -- the GEMV microbenchmark does not shard, so this is "replicas only" weak scaling with
+no collective on the data path; the time is the max over ranks.
+
+``--impl reference`` times the reference CPU path (dequantize once, then float32
+``x @ W.T`` per call, mfq/runtime/linear.py:17-46) restated in the oracle, on the host cores.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_ROWS, N_COLS = 4096, 4096
+PROFILE = (3, 24, 5)
+POOL = 48
+WORKLOAD = "cfg1: NINT3 (bits=3, gs=24, sub_bits=5) 4096x4096 GEMV, x 1x4096 bf16, pool of 48 distinct weights per step"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def algorithmic_bytes(payload: int, m: int, n: int, k: int) -> int:
+    """Packed payload of the weight record (file streams) + x (bf16) + y (bf16)."""
+    return payload + m * k * 2 + m * n * 2
+
+
+def cpu_reference_arm(steps: int, warmup: int, budget_s: float = 20.0):
+    """Reference CPU path (oracle port): dequantize once, then float32 x @ W.T per call."""
+    from oracle import mfq_oracle as O
+    from tyloquant_b200 import encode
+
+    bits, gs, sb = PROFILE
+    blob = encode.random_nint_blob(N_ROWS, N_COLS, bits, gs, sb, seed=1001)
+    t0 = time.perf_counter()
+    w = O.dequant_nint(O.unpack_nint(blob))
+    t_cold = time.perf_counter() - t0
+    x = encode.bf16_round(np.random.default_rng(1002).standard_normal((1, N_COLS), dtype=np.float32))
+    payload = O.nint_payload_nbytes(N_ROWS, N_COLS, bits, gs, sb)
+    nbytes = algorithmic_bytes(payload, 1, N_ROWS, N_COLS)
+    for _ in range(max(warmup, 3)):
+        O.linear(x, w)
+    # one "step" of the reference arm = a bounded sample: `calls` cached products
+    t0 = time.perf_counter()
+    O.linear(x, w)
+    one = max(time.perf_counter() - t0, 1e-6)
+    calls = int(max(1, min(POOL, budget_s / max(steps, 1) / one)))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        for _ in range(calls):
+            O.linear(x, w)
+    dt = time.perf_counter() - t0
+    try:
+        from threadpoolctl import threadpool_info
+        cores = max([p.get("num_threads", 1) for p in threadpool_info()] or [1])
+    except Exception:
+        cores = os.cpu_count() or 1
+    gbs = nbytes * calls * steps / dt / 1e9
+    return {"value": gbs, "unit": "GB/s", "cores": int(cores), "kind": "port",
+            "sample": f"{calls} cached float32 x@W.T calls per step on one dequantized 4096x4096 NINT3 weight "
+                      f"(numpy/BLAS); cold unpack+dequantize of that weight took {t_cold * 1e3:.0f} ms "
+                      f"({payload / t_cold / 1e9:.3f} GB/s)",
+            "ms_per_call": dt / (calls * steps) * 1e3, "cold_dequant_ms": t_cold * 1e3}, dt / steps * 1e3
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-sweep", action="store_true", help="skip the per-profile sweep")
+    ap.add_argument("--only", default=None, help="run one sweep case by name with a few plain launches "
+                    "(small, for profilers) and print its line")
+    ap.add_argument("--reps", type=int, default=3, help="launch rounds for --only")
+    args = ap.parse_args()
+    steps, warmup = max(args.steps, 1), max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    base = {"metric": "packed GEMV HBM GB/s", "unit": "GB/s", "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 x, u3 codes, f32 accumulate",
+            "data": "synthetic", "config": {"workload": WORKLOAD, "pool": POOL, "l2_policy": "inputs larger than L2 "
+                                            f"({POOL} x 7.2 MB weights per step)", "parallelism": f"replicas x{args.gpus}"}}
+
+    if args.only:
+        print(json.dumps(sweep(local_rank, measured_peaks()[0]["hbm_gbs"], only=args.only, reps=args.reps)))
+        return
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        cb, ms = cpu_reference_arm(steps, warmup)
+        line = dict(base)
+        line.update({"impl": "reference", "value": cb["value"], "ms_per_step": ms, "n_gpus": args.gpus,
+                     "cpu_baseline": cb, "gpu_launches": 0,
+                     "e2e": {"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
+        print(json.dumps(line))
+        return
+
+    import torch
+
+    from tyloquant_b200 import QuantWeight, encode
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU execution path)")
+    torch.cuda.set_device(local_rank)
+    dev = local_rank
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{dev}"))
+
+    bits, gs, sb = PROFILE
+    weights = []
+    for i in range(POOL):
+        blob = encode.random_nint_blob(N_ROWS, N_COLS, bits, gs, sb, seed=1001 + i, device=f"cuda:{dev}")
+        weights.append(QuantWeight.from_blob(f"NINT{bits}", blob, device=dev))
+    payload = weights[0].payload_bytes
+    step_bytes = POOL * algorithmic_bytes(payload, 1, N_ROWS, N_COLS)
+    x = torch.from_numpy(encode.bf16_round(np.random.default_rng(1002).standard_normal((1, N_COLS), dtype=np.float32)))
+    x = x.to(f"cuda:{dev}").to(torch.bfloat16)
+    ys = [torch.empty((1, N_ROWS), dtype=torch.bfloat16, device=f"cuda:{dev}") for _ in range(POOL)]
+
+    from tyloquant_b200._capi import BF16, check, lib
+
+    stream = torch.cuda.Stream(device=dev)
+
+    def run_step_direct():
+        sp = torch.cuda.current_stream(dev).cuda_stream
+        for w, y in zip(weights, ys):
+            check(lib.mfqb_mul_mat(w._h, x.data_ptr(), 1, y.data_ptr(), BF16, sp))
+
+    graph = None
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            run_step_direct()
+        stream.synchronize()
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                run_step_direct()
+            graph = g
+        except Exception as exc:  # capture refused: fall back to direct launches
+            sys.stderr.write(f"graph capture failed, timing direct launches: {exc}\n")
+            graph = None
+
+    def run_step():
+        if graph is not None:
+            graph.replay()
+        else:
+            run_step_direct()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    with torch.cuda.stream(stream):
+        for _ in range(warmup):
+            run_step()
+        barrier()
+        sampler = ClockSampler(dev)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            run_step()
+        e1.record(stream)
+        barrier()
+        clocks = sampler.stop()
+        ms = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([ms], device=f"cuda:{dev}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / steps
+    value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end through the host-buffer entry point ---------------------------------
+    xh = torch.from_numpy(encode.bf16_bits(x.float().cpu().numpy()).astype(np.int16)).pin_memory()
+    yh = torch.empty((1, N_ROWS), dtype=torch.int16).pin_memory()
+    e2e_steps = max(3, min(steps, 10))
+
+    def e2e_step():
+        for w in weights:
+            check(lib.mfqb_mul_mat_host(w._h, xh.data_ptr(), 1, yh.data_ptr(), BF16))
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    torch.cuda.synchronize(dev)
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    if dist is not None:
+        t = torch.tensor([e2e_ms], device=f"cuda:{dev}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = world * step_bytes / (e2e_ms * 1e-3) / 1e9
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peaks, peak_kind = measured_peaks()
+    launch_us = ms_per_step * 1e3 / POOL
+    achieved = algorithmic_bytes(payload, 1, N_ROWS, N_COLS) / (launch_us * 1e-6) / 1e9
+    line = dict(base)
+    line.update({
+        "value": value, "ms_per_step": ms_per_step, "clocks": clocks, "gpu_launches": POOL * steps,
+        "graph_replay": graph is not None,
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": POOL * N_COLS * 2,
+                "d2h_bytes_per_step": POOL * N_ROWS * 2, "ms_per_step": e2e_ms,
+                "api": "mfqb_mul_mat_host (pinned host x and y, weights resident)"},
+        "roofline": {"bound": "hbm", "kernel": "nint_gemv_kernel<3,6,5>", "achieved": achieved, "peak": peaks["hbm_gbs"],
+                     "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": f"{peak_kind} copy bandwidth",
+                     "us_per_launch": launch_us, "algorithmic_bytes_per_launch": algorithmic_bytes(payload, 1, N_ROWS, N_COLS),
+                     "device_bytes_per_launch": weights[0].device_bytes, "traffic": None},
+    })
+    if args.gpus == 1:
+        cb, _ = cpu_reference_arm(3, 3, budget_s=12.0)
+        line["cpu_baseline"] = cb
+        if not args.no_sweep:
+            line["sweep"] = sweep(dev, peaks["hbm_gbs"])
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def sweep(dev: int, peak: float, only: str | None = None, reps: int = 10) -> dict:
+    """GB/s of one GEMV launch per profile and shape (pool of distinct weights > L2, graph replay).
+
+    With ``only`` a single case runs, without a graph and with a pool just above L2, so that a
+    profiler sees a handful of plain launches."""
+    import torch
+
+    from tyloquant_b200 import QuantWeight, encode
+    from tyloquant_b200._capi import BF16, check, lib
+
+    out = {}
+    cases = [(f"NINT{b}_4096x4096_m1", (b, gs, sb), 4096, 4096, 1) for b, (_, gs, sb) in encode.CANONICAL_NINT.items()]
+    cases += [("NINT4_14336x4096_m1", (4, 24, 6), 14336, 4096, 1), ("NINT6_14336x4096_m1", (6, 24, 7), 14336, 4096, 1),
+              ("NINT3_4096x4096_m8", (3, 24, 5), 4096, 4096, 8), ("NINT4_4096x14336_m1", (4, 24, 6), 4096, 14336, 1)]
+    for name, (b, gs, sb), n, k, m in cases:
+        if only and name != only:
+            continue
+        blob = encode.random_nint_blob(n, k, b, gs, sb, seed=77, device=f"cuda:{dev}")
+        probe = QuantWeight.from_blob(f"NINT{b}", blob, device=dev)
+        pool = int(max(4, min(64, (1.2 if only else 2.5) * 126e6 / probe.device_bytes + 1)))
+        ws = [probe] + [QuantWeight.from_blob(f"NINT{b}", blob, device=dev) for _ in range(pool - 1)]
+        x = torch.randn((m, k), device=f"cuda:{dev}").to(torch.bfloat16)
+        y = torch.empty((m, n), dtype=torch.bfloat16, device=f"cuda:{dev}")
+        stream = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(stream):
+            def step():
+                sp = torch.cuda.current_stream(dev).cuda_stream
+                for w in ws:
+                    check(lib.mfqb_mul_mat(w._h, x.data_ptr(), m, y.data_ptr(), BF16, sp))
+            step()
+            stream.synchronize()
+            if only:
+                class _Direct:
+                    replay = staticmethod(step)
+                g = _Direct()
+            else:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    step()
+                for _ in range(3):
+                    g.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(reps):
+                g.replay()
+            e1.record(stream)
+            stream.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (reps * pool)
+        nbytes = algorithmic_bytes(probe.payload_bytes, m, n, k)
+        out[name] = {"us_per_launch": us, "GBps": nbytes / us / 1e3, "frac_of_peak": nbytes / us / 1e3 / peak,
+                     "pool": pool, "device_over_payload": probe.device_bytes / probe.payload_bytes}
+        for w in ws:
+            w.free()
+    return out
+
+
+if __name__ == "__main__":
+    main()

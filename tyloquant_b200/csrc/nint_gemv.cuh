@@ -81,167 +81,240 @@ struct GemvArgs {
     void* y;                 // [m, ldy]
     int m, ldy, y_dtype;
     int rb_per_cta;          // row-blocks per CTA
-    int xstride;             // shared-memory row stride of x in elements (even)
+    int xstride;             // row stride (elements, multiple of 8) of x staged in shared memory; 0 = read x from global
 };
 
-constexpr int kGemvThreads = 256;
+constexpr uint32_t kBf16x2_one = 0x3F803F80u;  // (1.0, 1.0)
+
+// Programmatic dependent launch: let the next kernel of the stream start early, and wait for
+// the previous one before touching anything it may have produced.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 template <int BITS, int PER, int SW>
-__global__ void __launch_bounds__(kGemvThreads, 2) nint_gemv_kernel(const GemvArgs a) {
-    constexpr int G = kChunkGroups, HALF = PER / 2, P = G * PER;
-    constexpr int WC = PairUnit<BITS>::words_for(P), SWC = PairUnit<SW>::words_for(16);
+struct GemvItem {   // packed words of one (row-block, chunk) item, as loaded by one lane
+    static constexpr int WC = PairUnit<BITS>::words_for(kChunkGroups * PER), SWC = PairUnit<SW>::words_for(16);
+    uint32_t qw[WC], sw[SWC], an_lo, an_hi;
+    __device__ __forceinline__ void load(const NintDev& w, int rb, int seg, int lane) {
+        const size_t item = (size_t)rb * w.nchunks + seg;
+        const int q = lane >> 2;
+#pragma unroll
+        for (int j = 0; j < WC; ++j) qw[j] = __ldg(w.qwords + (item * WC + j) * 32 + lane);
+#pragma unroll
+        for (int j = 0; j < SWC; ++j) sw[j] = __ldg(w.swords + (item * SWC + j) * 8 + q);
+        an_lo = __ldg(w.anchors + rb * 16 + q);
+        an_hi = __ldg(w.anchors + rb * 16 + 8 + q);
+    }
+};
+
+// One CTA owns rb_per_cta row-blocks and all chunks of K.  Warp i takes chunks i, i + nwarps,
+// ... and, for each, every row-block of the CTA (so its x fragments are built once per chunk).
+// Each warp keeps two (chunk, row-block) items of packed words in flight in registers; the first
+// two are requested before the kernel waits for its predecessor, since weights are constants.
+// Shared memory: partial sums [rb_per_cta][16][8] float32, one 8x8 float32 tile per warp, and
+// (when it fits) x staged as bf16 [m][xstride].
+template <int BITS, int PER, int SW>
+__global__ void __launch_bounds__(256, 2) nint_gemv_kernel(const GemvArgs a) {
+    constexpr int G = kChunkGroups, HALF = PER / 2;
     constexpr int NPL = BITS == 8 ? 2 : 1;  // 8-bit codes go through as two 4-bit planes
+    using Item = GemvItem<BITS, PER, SW>;
     using QU = PairUnit<BITS>;
     using SU = PairUnit<SW>;
     const NintDev& w = a.w;
 
     extern __shared__ __align__(16) unsigned char smem[];
-    const int ngp = w.nchunks * G;
-    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem);
-    float* xsum = reinterpret_cast<float*>(smem + (((size_t)a.m * a.xstride * 2 + 15) & ~(size_t)15));
-    float* ypart = xsum + (size_t)ngp * 8;
-
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float* ypart = reinterpret_cast<float*>(smem);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const int q = lane >> 2, c = lane & 3;
     const int rb0 = blockIdx.x * a.rb_per_cta;
-    const int rb1 = min(rb0 + a.rb_per_cta, w.nrb);
-    const int nrb = rb1 - rb0;
+    const int nrb = min(a.rb_per_cta, w.nrb - rb0);
+    float* xt = ypart + (size_t)a.rb_per_cta * 128 + warp * 64;
+    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(ypart + (size_t)a.rb_per_cta * 128 + nwarps * 64);
 
-    // ---- stage x (zero beyond k), group sums, clear partials ---------------------------
-    for (int m = 0; m < a.m; ++m) {
-        const __nv_bfloat16* src = a.x + (size_t)m * w.k;
-        __nv_bfloat16* dst = xs + (size_t)m * a.xstride;
-        for (int i = tid; i < a.xstride; i += kGemvThreads) dst[i] = i < w.k ? src[i] : __float2bfloat16(0.f);
-    }
-    for (int i = tid; i < nrb * 128; i += kGemvThreads) ypart[i] = 0.f;
-    __syncthreads();
-    for (int i = tid; i < ngp * 8; i += kGemvThreads) {
-        const int grp = i >> 3, n = i & 7;
-        float s = 0.f;
-        if (n < a.m) {
-            const __nv_bfloat16* p = xs + (size_t)n * a.xstride + (size_t)grp * w.gs;
-            for (int e = 0; e < w.gs; ++e) s += __bfloat162float(p[e]);
+    // items of this warp: i -> chunk warp + (i / nrb) * nwarps, row-block rb0 + i % nrb
+    const int my_segs = warp < w.nchunks ? (w.nchunks - warp + nwarps - 1) / nwarps : 0;
+    const int n_mine = my_segs * nrb;
+    auto item_seg = [&](int i) { return warp + (i / nrb) * nwarps; };
+    auto item_rb = [&](int i) { return rb0 + i % nrb; };
+
+    pdl_launch_dependents();
+    Item it0, it1;
+    if (0 < n_mine) it0.load(w, item_rb(0), item_seg(0), lane);
+    if (1 < n_mine) it1.load(w, item_rb(1), item_seg(1), lane);
+    for (int i = tid; i < nrb * 128; i += blockDim.x) ypart[i] = 0.f;
+    pdl_wait();
+    if (a.xstride > 0) {
+        // stage x: 16-byte copies when rows are 16-byte aligned, zero beyond k
+        const int kp = a.xstride;
+        if ((w.k & 7) == 0 && (reinterpret_cast<uintptr_t>(a.x) & 15) == 0) {
+            const int vec_per_row = kp / 8;
+            for (int i = tid; i < a.m * vec_per_row; i += blockDim.x) {
+                const int m = i / vec_per_row, v = i % vec_per_row;
+                uint4 val = make_uint4(0u, 0u, 0u, 0u);
+                if (v * 8 < w.k) val = __ldg(reinterpret_cast<const uint4*>(a.x + (size_t)m * w.k) + v);
+                *reinterpret_cast<uint4*>(xs + (size_t)m * kp + v * 8) = val;
+            }
+        } else {
+            for (int i = tid; i < a.m * kp; i += blockDim.x) {
+                const int m = i / kp, k = i % kp;
+                xs[i] = k < w.k ? a.x[(size_t)m * w.k + k] : __float2bfloat16(0.f);
+            }
         }
-        xsum[i] = s;
     }
     __syncthreads();
 
-    const uint32_t* xrow = reinterpret_cast<const uint32_t*>(xs + (size_t)q * a.xstride);
     const bool has_col = q < a.m;
+    const bool even_k = (w.k & 1) == 0;
+    const __nv_bfloat16* xcol = a.x + (size_t)q * w.k;
+    const uint32_t* xrow = reinterpret_cast<const uint32_t*>(xs + (size_t)q * a.xstride);
+    int cur_seg = -1;
+    uint32_t xf[G][HALF];
+    float ci[G][2];
+    uint32_t bmin[3];
 
-    for (int seg = warp; seg < w.nchunks; seg += kGemvThreads / 32) {
-        // x fragments of this chunk (batch column q), accumulator seeds, sub-min operand
-        uint32_t xf[G][HALF];
-        float ci[G][2];
+    auto prepare_chunk = [&](int seg) {
+        // x fragments of the chunk for batch column q
 #pragma unroll
         for (int g = 0; g < G; ++g) {
-            const int grp = seg * G + g;
+            const int kbase = (seg * G + g) * w.gs + c * PER;
 #pragma unroll
             for (int j = 0; j < HALF; ++j) {
-                const bool ok = has_col && (c * PER + 2 * j < w.gs);
-                xf[g][j] = ok ? xrow[(grp * w.gs + c * PER) / 2 + j] : 0u;
-            }
-            const float2 s = *reinterpret_cast<const float2*>(&xsum[grp * 8 + 2 * c]);
-            ci[g][0] = -128.f * s.x;
-            ci[g][1] = -128.f * s.y;
-        }
-        uint32_t bmin[3];
-        {
-            float v0 = xsum[(seg * G + 2 * c) * 8 + q], v1 = xsum[(seg * G + 2 * c + 1) * 8 + q];
-#pragma unroll
-            for (int s = 0; s < 3; ++s) {
-                const __nv_bfloat16 h0 = __float2bfloat16_rn(v0), h1 = __float2bfloat16_rn(v1);
-                v0 -= __bfloat162float(h0);
-                v1 -= __bfloat162float(h1);
-                __nv_bfloat162 pr;
-                pr.x = h0;
-                pr.y = h1;
-                bmin[s] = *reinterpret_cast<uint32_t*>(&pr);
-            }
-        }
-
-        for (int rb = rb0; rb < rb1; ++rb) {
-            const size_t item = (size_t)rb * w.nchunks + seg;
-            uint32_t qw[WC], sw[SWC];
-#pragma unroll
-            for (int j = 0; j < WC; ++j) qw[j] = __ldg(w.qwords + (item * WC + j) * 32 + lane);
-#pragma unroll
-            for (int j = 0; j < SWC; ++j) sw[j] = __ldg(w.swords + (item * SWC + j) * 8 + q);
-            const uint32_t an_lo = __ldg(w.anchors + rb * 16 + q), an_hi = __ldg(w.anchors + rb * 16 + 8 + q);
-
-            float tot[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-                float acc[NPL][4];
-#pragma unroll
-                for (int pl = 0; pl < NPL; ++pl) {
-                    acc[pl][0] = ci[g][0];
-                    acc[pl][1] = ci[g][1];
-                    acc[pl][2] = ci[g][0];
-                    acc[pl][3] = ci[g][1];
-                }
-#pragma unroll
-                for (int j = 0; j + 1 < HALF; j += 2) {
-                    const uint32_t r0 = QU::at(qw, (g * 2 + 0) * HALF + j), r1 = QU::at(qw, (g * 2 + 1) * HALF + j);
-                    const uint32_t r2 = QU::at(qw, (g * 2 + 0) * HALF + j + 1), r3 = QU::at(qw, (g * 2 + 1) * HALF + j + 1);
-                    if constexpr (NPL == 1) {
-                        mma_k16(acc[0], r0 | kBf16x2_128, r1 | kBf16x2_128, r2 | kBf16x2_128, r3 | kBf16x2_128, xf[g][j],
-                                xf[g][j + 1]);
-                    } else {
-                        constexpr uint32_t NIB = 0x000F000Fu;
-                        mma_k16(acc[0], (r0 & NIB) | kBf16x2_128, (r1 & NIB) | kBf16x2_128, (r2 & NIB) | kBf16x2_128,
-                                (r3 & NIB) | kBf16x2_128, xf[g][j], xf[g][j + 1]);
-                        mma_k16(acc[1], ((r0 >> 4) & NIB) | kBf16x2_128, ((r1 >> 4) & NIB) | kBf16x2_128,
-                                ((r2 >> 4) & NIB) | kBf16x2_128, ((r3 >> 4) & NIB) | kBf16x2_128, xf[g][j], xf[g][j + 1]);
+                const int k0 = kbase + 2 * j;
+                uint32_t v = 0u;
+                if (has_col && (c * PER + 2 * j < w.gs)) {
+                    if (a.xstride > 0) {
+                        v = xrow[k0 >> 1];
+                    } else if (k0 < w.k) {
+                        if (even_k) {
+                            v = __ldg(reinterpret_cast<const uint32_t*>(xcol + k0));
+                        } else {
+                            v = __ldg(reinterpret_cast<const unsigned short*>(xcol + k0));
+                            if (k0 + 1 < w.k) v |= (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(xcol + k0 + 1)) << 16;
+                        }
                     }
                 }
-                if constexpr (HALF & 1) {
-                    constexpr int j = HALF - 1;
-                    const uint32_t r0 = QU::at(qw, (g * 2 + 0) * HALF + j), r1 = QU::at(qw, (g * 2 + 1) * HALF + j);
-                    if constexpr (NPL == 1) {
-                        mma_k8(acc[0], r0 | kBf16x2_128, r1 | kBf16x2_128, xf[g][j]);
-                    } else {
-                        constexpr uint32_t NIB = 0x000F000Fu;
-                        mma_k8(acc[0], (r0 & NIB) | kBf16x2_128, (r1 & NIB) | kBf16x2_128, xf[g][j]);
-                        mma_k8(acc[1], ((r0 >> 4) & NIB) | kBf16x2_128, ((r1 >> 4) & NIB) | kBf16x2_128, xf[g][j]);
-                    }
-                }
-                float s_lo, s_hi;
-                pair_to_floats<SW>(SU::at(sw, g), s_lo, s_hi);
+                xf[g][j] = v;
+            }
+        }
+        // group sums of x through the tensor cores (A = ones): seeds of the accumulators
+        __syncwarp();
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    float v = acc[0][e];
-                    if constexpr (NPL == 2) v = fmaf(16.f, acc[1][e], v);
-                    tot[e] = fmaf(e < 2 ? s_lo : s_hi, v, tot[e]);
+        for (int g = 0; g < G; ++g) {
+            float s[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int j = 0; j + 1 < HALF; j += 2)
+                mma_k16(s, kBf16x2_one, kBf16x2_one, kBf16x2_one, kBf16x2_one, xf[g][j], xf[g][j + 1]);
+            if constexpr (HALF & 1) mma_k8(s, kBf16x2_one, kBf16x2_one, xf[g][HALF - 1]);
+            ci[g][0] = -128.f * s[0];
+            ci[g][1] = -128.f * s[1];
+            if (q == 0) *reinterpret_cast<float2*>(xt + g * 8 + 2 * c) = make_float2(s[0], s[1]);
+        }
+        __syncwarp();
+        // sub-min operand: xsum of groups (2c, 2c+1) for column q, split in three bf16 pieces
+        float v0 = xt[(2 * c) * 8 + q], v1 = xt[(2 * c + 1) * 8 + q];
+#pragma unroll
+        for (int s = 0; s < 3; ++s) {
+            const __nv_bfloat16 h0 = __float2bfloat16_rn(v0), h1 = __float2bfloat16_rn(v1);
+            v0 -= __bfloat162float(h0);
+            v1 -= __bfloat162float(h1);
+            __nv_bfloat162 pr;
+            pr.x = h0;
+            pr.y = h1;
+            bmin[s] = *reinterpret_cast<uint32_t*>(&pr);
+        }
+    };
+
+    auto compute_item = [&](const Item& it, int rbl) {
+        float tot[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float acc[NPL][4];
+#pragma unroll
+            for (int pl = 0; pl < NPL; ++pl) {
+                acc[pl][0] = ci[g][0];
+                acc[pl][1] = ci[g][1];
+                acc[pl][2] = ci[g][0];
+                acc[pl][3] = ci[g][1];
+            }
+#pragma unroll
+            for (int j = 0; j + 1 < HALF; j += 2) {
+                const uint32_t r0 = QU::at(it.qw, (g * 2 + 0) * HALF + j), r1 = QU::at(it.qw, (g * 2 + 1) * HALF + j);
+                const uint32_t r2 = QU::at(it.qw, (g * 2 + 0) * HALF + j + 1), r3 = QU::at(it.qw, (g * 2 + 1) * HALF + j + 1);
+                if constexpr (NPL == 1) {
+                    mma_k16(acc[0], r0 | kBf16x2_128, r1 | kBf16x2_128, r2 | kBf16x2_128, r3 | kBf16x2_128, xf[g][j], xf[g][j + 1]);
+                } else {
+                    constexpr uint32_t NIB = 0x000F000Fu;
+                    mma_k16(acc[0], (r0 & NIB) | kBf16x2_128, (r1 & NIB) | kBf16x2_128, (r2 & NIB) | kBf16x2_128,
+                            (r3 & NIB) | kBf16x2_128, xf[g][j], xf[g][j + 1]);
+                    mma_k16(acc[1], ((r0 >> 4) & NIB) | kBf16x2_128, ((r1 >> 4) & NIB) | kBf16x2_128,
+                            ((r2 >> 4) & NIB) | kBf16x2_128, ((r3 >> 4) & NIB) | kBf16x2_128, xf[g][j], xf[g][j + 1]);
                 }
             }
-            // sub-min term: rows (lo, hi) x groups (2c, 2c+1) of this chunk against xsum
-            uint32_t m_lo, m_hi;
-            switch (c) {
-                case 0: m_lo = SU::at(sw, 8); m_hi = SU::at(sw, 12); break;
-                case 1: m_lo = SU::at(sw, 9); m_hi = SU::at(sw, 13); break;
-                case 2: m_lo = SU::at(sw, 10); m_hi = SU::at(sw, 14); break;
-                default: m_lo = SU::at(sw, 11); m_hi = SU::at(sw, 15); break;
+            if constexpr (HALF & 1) {
+                constexpr int j = HALF - 1;
+                const uint32_t r0 = QU::at(it.qw, (g * 2 + 0) * HALF + j), r1 = QU::at(it.qw, (g * 2 + 1) * HALF + j);
+                if constexpr (NPL == 1) {
+                    mma_k8(acc[0], r0 | kBf16x2_128, r1 | kBf16x2_128, xf[g][j]);
+                } else {
+                    constexpr uint32_t NIB = 0x000F000Fu;
+                    mma_k8(acc[0], (r0 & NIB) | kBf16x2_128, (r1 & NIB) | kBf16x2_128, xf[g][j]);
+                    mma_k8(acc[1], ((r0 >> 4) & NIB) | kBf16x2_128, ((r1 >> 4) & NIB) | kBf16x2_128, xf[g][j]);
+                }
             }
-            m_lo = pair_to_bf162<SW>(m_lo);
-            m_hi = pair_to_bf162<SW>(m_hi);
-            float mt[4] = {0.f, 0.f, 0.f, 0.f};
-            mma_k8(mt, m_lo, m_hi, bmin[2]);
-            mma_k8(mt, m_lo, m_hi, bmin[1]);
-            mma_k8(mt, m_lo, m_hi, bmin[0]);
+            float s_lo, s_hi;
+            pair_to_floats<SW>(SU::at(it.sw, g), s_lo, s_hi);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float v = acc[0][e];
+                if constexpr (NPL == 2) v = fmaf(16.f, acc[1][e], v);
+                tot[e] = fmaf(e < 2 ? s_lo : s_hi, v, tot[e]);
+            }
+        }
+        // sub-min term: rows (lo, hi) x groups (2c, 2c+1) of this chunk against xsum
+        uint32_t m_lo, m_hi;
+        switch (c) {
+            case 0: m_lo = SU::at(it.sw, 8); m_hi = SU::at(it.sw, 12); break;
+            case 1: m_lo = SU::at(it.sw, 9); m_hi = SU::at(it.sw, 13); break;
+            case 2: m_lo = SU::at(it.sw, 10); m_hi = SU::at(it.sw, 14); break;
+            default: m_lo = SU::at(it.sw, 11); m_hi = SU::at(it.sw, 15); break;
+        }
+        m_lo = pair_to_bf162<SW>(m_lo);
+        m_hi = pair_to_bf162<SW>(m_hi);
+        float mt[4] = {0.f, 0.f, 0.f, 0.f};
+        mma_k8(mt, m_lo, m_hi, bmin[2]);
+        mma_k8(mt, m_lo, m_hi, bmin[1]);
+        mma_k8(mt, m_lo, m_hi, bmin[0]);
 
-            const __half2 h_lo = *reinterpret_cast<const __half2*>(&an_lo), h_hi = *reinterpret_cast<const __half2*>(&an_hi);
-            const float2 f_lo = __half22float2(h_lo), f_hi = __half22float2(h_hi);  // (ns, nm)
-            float* yp = ypart + (size_t)(rb - rb0) * 128;
+        const __half2 h_lo = *reinterpret_cast<const __half2*>(&it.an_lo), h_hi = *reinterpret_cast<const __half2*>(&it.an_hi);
+        const float2 f_lo = __half22float2(h_lo), f_hi = __half22float2(h_hi);  // (ns, nm)
+        float* yp = ypart + (size_t)rbl * 128;
+        if (2 * c < a.m) {
             atomicAdd(yp + q * 8 + 2 * c, f_lo.x * tot[0] - f_lo.y * mt[0]);
-            atomicAdd(yp + q * 8 + 2 * c + 1, f_lo.x * tot[1] - f_lo.y * mt[1]);
             atomicAdd(yp + (q + 8) * 8 + 2 * c, f_hi.x * tot[2] - f_hi.y * mt[2]);
+        }
+        if (2 * c + 1 < a.m) {
+            atomicAdd(yp + q * 8 + 2 * c + 1, f_lo.x * tot[1] - f_lo.y * mt[1]);
             atomicAdd(yp + (q + 8) * 8 + 2 * c + 1, f_hi.x * tot[3] - f_hi.y * mt[3]);
+        }
+    };
+
+    for (int i = 0; i < n_mine; i += 2) {
+        {
+            const int seg = item_seg(i);
+            if (seg != cur_seg) { cur_seg = seg; prepare_chunk(seg); }
+            compute_item(it0, i % nrb);
+            if (i + 2 < n_mine) it0.load(w, item_rb(i + 2), item_seg(i + 2), lane);
+        }
+        if (i + 1 < n_mine) {
+            const int seg = item_seg(i + 1);
+            if (seg != cur_seg) { cur_seg = seg; prepare_chunk(seg); }
+            compute_item(it1, (i + 1) % nrb);
+            if (i + 3 < n_mine) it1.load(w, item_rb(i + 3), item_seg(i + 3), lane);
         }
     }
     __syncthreads();
     const int rows = nrb * 16;
-    for (int i = tid; i < rows * a.m; i += kGemvThreads) {
+    for (int i = tid; i < rows * a.m; i += blockDim.x) {
         const int n = i / rows, rr = i % rows, row = rb0 * 16 + rr;
         if (row < w.n) {
             const float v = ypart[rr * 8 + n];
@@ -253,7 +326,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) nint_gemv_kernel(const GemvAr
 
 // Shared-memory footprint and launch geometry, computed on the host.
 struct GemvPlan {
-    int xstride, rb_per_cta, grid;
+    int rb_per_cta, grid, threads, xstride;
     size_t smem;
 };
 GemvPlan plan_nint_gemv(const NintDev& w, int m, int num_sms);

@@ -1,6 +1,7 @@
 // Dense weight handles: blob -> device layout -> decode / multiply entry points.
 #include <cuda_bf16.h>
 
+#include <algorithm>
 #include <memory>
 #include <mutex>
 
@@ -25,17 +26,28 @@ int device_sm_count(int device) {
 
 GemvPlan plan_nint_gemv(const NintDev& w, int m, int num_sms) {
     GemvPlan p;
-    const int kp = w.nchunks * kChunkGroups * w.gs;      // zero-padded columns
-    int words = (kp + 1) / 2;
-    // Row stride (in 32-bit words) congruent to 2*PER mod 32: the eight batch rows a warp reads
-    // together then fall into distinct shared-memory banks.
-    words += (((2 * w.per - words) % 32) + 32) % 32;
-    p.xstride = words * 2;
+    // Two 8-warp CTAs per SM; each CTA owns whole row-blocks (all chunks of K), so partial sums
+    // stay in its shared memory.
     const int target = 2 * num_sms;
-    p.rb_per_cta = (w.nrb + target - 1) / target;
+    p.rb_per_cta = std::max(1, (w.nrb + target - 1) / target);
     p.grid = (w.nrb + p.rb_per_cta - 1) / p.rb_per_cta;
-    p.smem = (((size_t)m * p.xstride * 2 + 15) & ~(size_t)15) + (size_t)w.nchunks * kChunkGroups * 8 * 4 +
-             (size_t)p.rb_per_cta * 128 * 4;
+    const int warps = 8;
+    p.threads = warps * 32;
+    // x in shared memory: rows padded to whole chunks, stride chosen so that the eight batch rows a
+    // warp reads together fall into distinct banks (stride in words = 2*PER mod 32), kept a
+    // multiple of 8 elements for the 16-byte staging copies.
+    const int kp = w.nchunks * kChunkGroups * w.gs;
+    int words = (kp + 1) / 2;
+    if (m > 1) words += (((2 * w.per - words) % 32) + 32) % 32;
+    p.xstride = ((words * 2 + 7) / 8) * 8;
+    if (m == 1) {   // single-row kernel: partial sums [rb][16] and x, always staged
+        p.smem = (size_t)p.rb_per_cta * 16 * 4 + (size_t)p.xstride * 2;
+        return p;
+    }
+    const size_t fixed = (size_t)p.rb_per_cta * 128 * 4 + (size_t)warps * 64 * 4;
+    const size_t xbytes = (size_t)m * p.xstride * 2;
+    if (fixed + xbytes > 100 * 1024) p.xstride = 0;   // too long to stage twice per SM: read x from global
+    p.smem = fixed + (p.xstride ? xbytes : 0);
     return p;
 }
 
@@ -154,12 +166,8 @@ struct mfqb_weight {
 
 namespace mfqb {
 
-// Largest batch the GEMV can stage in shared memory for this weight.
-static int nint_gemv_max_batch(const NintDev& w, int device) {
-    for (int m = 8; m >= 1; --m)
-        if (plan_nint_gemv(w, m, device_sm_count(device)).smem <= 200 * 1024) return m;
-    return 0;
-}
+// Batch rows one GEMV launch covers (the n8 slot of the tensor-core tile).
+static int nint_gemv_max_batch(const NintDev&, int) { return 8; }
 
 static void check_nint_supported(const HostNint& t) {
     const int b = t.bits;
