@@ -82,6 +82,7 @@ struct GemvArgs {
     int m, ldy, y_dtype;
     int rb_per_cta;          // row-blocks per CTA
     int xstride;             // row stride (elements, multiple of 8) of x staged in shared memory; 0 = read x from global
+    int stages;              // records per warp ring (single-row kernel)
 };
 
 constexpr uint32_t kBf16x2_one = 0x3F803F80u;  // (1.0, 1.0)
@@ -96,12 +97,12 @@ struct GemvItem {   // packed words of one (row-block, chunk) item, as loaded by
     static constexpr int WC = PairUnit<BITS>::words_for(kChunkGroups * PER), SWC = PairUnit<SW>::words_for(16);
     uint32_t qw[WC], sw[SWC], an_lo, an_hi;
     __device__ __forceinline__ void load(const NintDev& w, int rb, int seg, int lane) {
-        const size_t item = (size_t)rb * w.nchunks + seg;
+        const uint32_t* rec = w.items + ((size_t)rb * w.nchunks + seg) * (WC * 32 + SWC * 8);
         const int q = lane >> 2;
 #pragma unroll
-        for (int j = 0; j < WC; ++j) qw[j] = __ldg(w.qwords + (item * WC + j) * 32 + lane);
+        for (int j = 0; j < WC; ++j) qw[j] = __ldg(rec + j * 32 + lane);
 #pragma unroll
-        for (int j = 0; j < SWC; ++j) sw[j] = __ldg(w.swords + (item * SWC + j) * 8 + q);
+        for (int j = 0; j < SWC; ++j) sw[j] = __ldg(rec + WC * 32 + j * 8 + q);
         an_lo = __ldg(w.anchors + rb * 16 + q);
         an_hi = __ldg(w.anchors + rb * 16 + 8 + q);
     }
@@ -326,7 +327,7 @@ __global__ void __launch_bounds__(256, 2) nint_gemv_kernel(const GemvArgs a) {
 
 // Shared-memory footprint and launch geometry, computed on the host.
 struct GemvPlan {
-    int rb_per_cta, grid, threads, xstride;
+    int rb_per_cta, grid, threads, xstride, stages;
     size_t smem;
 };
 GemvPlan plan_nint_gemv(const NintDev& w, int m, int num_sms);

@@ -15,34 +15,72 @@
 
 namespace mfqb {
 
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+// Records per warp ring: about 6 KB of ring per warp (three 8-warp CTAs per SM then keep well
+// over 100 KB of weight bytes requested per SM), between 2 and 6 stages.
+__host__ __device__ constexpr int gemv_m1_stages(int rec_words) {
+    return 6144 / (rec_words * 4) < 2 ? 2 : (6144 / (rec_words * 4) > 6 ? 6 : 6144 / (rec_words * 4));
+}
+
+// Shared memory: partial sums [rb_per_cta][16] f32 | anchors [rb_per_cta][16] u32 | x bf16
+// [xstride] | per warp a ring of `stages` item records.  Every warp streams its own items
+// (chunk-major, as in the batched kernel) through its ring with 16-byte asynchronous copies:
+// nothing a copy in flight occupies is a register, so a CTA keeps tens of kilobytes requested
+// at all times; the first `stages` items are requested before the kernel waits for its
+// predecessor in the stream, since weights are constants.
 template <int BITS, int PER, int SW>
-__global__ void __launch_bounds__(256, 2) nint_gemv_m1_kernel(const GemvArgs a) {
+__global__ void __launch_bounds__(256, 3) nint_gemv_m1_kernel(const GemvArgs a) {
     constexpr int G = kChunkGroups, HALF = PER / 2;
     constexpr int NPL = BITS == 8 ? 2 : 1;
     static_assert(G == 8, "eight groups per chunk map onto the eight mma columns");
-    using Item = GemvItem<BITS, PER, SW>;
     using QU = PairUnit<BITS>;
     using SU = PairUnit<SW>;
+    constexpr int WC = QU::words_for(G * PER), SWC = SU::words_for(16), REC = WC * 32 + SWC * 8;
+    constexpr int S = gemv_m1_stages(REC);
     const NintDev& w = a.w;
 
     extern __shared__ __align__(16) unsigned char smem[];
-    float* ypart = reinterpret_cast<float*>(smem);                       // [rb_per_cta][16]
-    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(ypart + (size_t)a.rb_per_cta * 16);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const int q = lane >> 2, c = lane & 3;
-    const int rb0 = blockIdx.x * a.rb_per_cta;
-    const int nrb = min(a.rb_per_cta, w.nrb - rb0);
+    float* ypart = reinterpret_cast<float*>(smem);
+    uint32_t* anch = reinterpret_cast<uint32_t*>(ypart + (size_t)a.rb_per_cta * 16);
+    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(anch + (size_t)a.rb_per_cta * 16);
+    uint32_t* ring = reinterpret_cast<uint32_t*>(xs + a.xstride) + (size_t)warp * S * REC;
+    // balanced split of the row-blocks over the grid: CTA b owns [b*nrb/grid, (b+1)*nrb/grid)
+    const int rb0 = (int)(((long long)blockIdx.x * w.nrb) / gridDim.x);
+    const int nrb = (int)(((long long)(blockIdx.x + 1) * w.nrb) / gridDim.x) - rb0;
 
+    // items of this warp, chunk-major: chunk = warp, warp + nwarps, ...; inside a chunk every
+    // row-block of the CTA.  Two cursors walk that sequence (issue runs S items ahead); they are
+    // advanced incrementally -- no division in the loop.
     const int my_segs = warp < w.nchunks ? (w.nchunks - warp + nwarps - 1) / nwarps : 0;
     const int n_mine = my_segs * nrb;
-    auto item_seg = [&](int i) { return warp + (i / nrb) * nwarps; };
-    auto item_rb = [&](int i) { return rb0 + i % nrb; };
+    int iss_i = 0, iss_seg = warp, iss_rbl = 0, iss_stage = 0;
+    auto issue = [&]() {
+        if (iss_i < n_mine) {
+            const uint32_t* src = w.items + ((size_t)(rb0 + iss_rbl) * w.nchunks + iss_seg) * REC;
+            uint32_t* dst = ring + iss_stage * REC;
+#pragma unroll
+            for (int off = 0; off < REC; off += 128)
+                if (off + 128 <= REC || lane * 4 < REC - off) cp_async16(dst + off + lane * 4, src + off + lane * 4);
+        }
+        cp_async_commit();   // one group per item slot, empty past the end: keeps the wait count uniform
+        ++iss_i;
+        if (++iss_rbl == nrb) { iss_rbl = 0; iss_seg += nwarps; }
+        if (++iss_stage == S) iss_stage = 0;
+    };
 
     pdl_launch_dependents();
-    Item it0, it1;
-    if (0 < n_mine) it0.load(w, item_rb(0), item_seg(0), lane);
-    if (1 < n_mine) it1.load(w, item_rb(1), item_seg(1), lane);
-    for (int i = tid; i < nrb * 16; i += blockDim.x) ypart[i] = 0.f;
+#pragma unroll
+    for (int i = 0; i < S; ++i) issue();
+    for (int i = tid; i < nrb * 16; i += blockDim.x) {
+        ypart[i] = 0.f;
+        anch[i] = __ldg(w.anchors + rb0 * 16 + i);
+    }
     pdl_wait();
     {   // stage x (zero beyond k): 16-byte copies when the row is 16-byte aligned
         const int kp = a.xstride;
@@ -86,24 +124,36 @@ __global__ void __launch_bounds__(256, 2) nint_gemv_m1_kernel(const GemvArgs a) 
         xs1 = s[1];
     };
 
-    auto compute_item = [&](const Item& it, int rbl) {
+    int seg = warp, rbl = 0, stage = 0;
+    for (int i = 0; i < n_mine; ++i) {
+        if (seg != cur_seg) { cur_seg = seg; prepare_chunk(seg); }
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(S - 1) : "memory");
+        __syncwarp();
+        const uint32_t* rec = ring + stage * REC;
+        uint32_t qw[WC], sw[SWC];
+#pragma unroll
+        for (int j = 0; j < WC; ++j) qw[j] = rec[j * 32 + lane];
+#pragma unroll
+        for (int j = 0; j < SWC; ++j) sw[j] = rec[WC * 32 + j * 8 + q];
+        __syncwarp();          // every lane has read the stage before it is refilled
+        issue();
+
         const float seed0 = (NPL == 2 ? -128.f * 17.f : -128.f) * xs0, seed1 = (NPL == 2 ? -128.f * 17.f : -128.f) * xs1;
-        float acc_a[4] = {seed0, seed1, seed0, seed1}, acc_b[4] = {0.f, 0.f, 0.f, 0.f};
-        float acc_c[4] = {0.f, 0.f, 0.f, 0.f}, acc_d[4] = {0.f, 0.f, 0.f, 0.f};   // high nibbles (8-bit codes)
+        float ch[4][4] = {{seed0, seed1, seed0, seed1}, {0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        float hi[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};   // high nibbles (8-bit codes)
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
 #pragma unroll
             for (int j = 0; j < HALF; ++j) {
-                const uint32_t r0 = QU::at(it.qw, (g * 2 + 0) * HALF + j), r1 = QU::at(it.qw, (g * 2 + 1) * HALF + j);
-                const uint32_t r2 = QU::at(it.qw, ((g + 4) * 2 + 0) * HALF + j), r3 = QU::at(it.qw, ((g + 4) * 2 + 1) * HALF + j);
+                const uint32_t r0 = QU::at(qw, (g * 2 + 0) * HALF + j), r1 = QU::at(qw, (g * 2 + 1) * HALF + j);
+                const uint32_t r2 = QU::at(qw, ((g + 4) * 2 + 0) * HALF + j), r3 = QU::at(qw, ((g + 4) * 2 + 1) * HALF + j);
                 if constexpr (NPL == 1) {
-                    mma_k16(g < 2 ? acc_a : acc_b, r0 | kBf16x2_128, r1 | kBf16x2_128, r2 | kBf16x2_128, r3 | kBf16x2_128,
-                            b0[g][j], b1[g][j]);
+                    mma_k16(ch[g], r0 | kBf16x2_128, r1 | kBf16x2_128, r2 | kBf16x2_128, r3 | kBf16x2_128, b0[g][j], b1[g][j]);
                 } else {
                     constexpr uint32_t NIB = 0x000F000Fu;
-                    mma_k16(g < 2 ? acc_a : acc_b, (r0 & NIB) | kBf16x2_128, (r1 & NIB) | kBf16x2_128, (r2 & NIB) | kBf16x2_128,
+                    mma_k16(ch[g & 1], (r0 & NIB) | kBf16x2_128, (r1 & NIB) | kBf16x2_128, (r2 & NIB) | kBf16x2_128,
                             (r3 & NIB) | kBf16x2_128, b0[g][j], b1[g][j]);
-                    mma_k16(g < 2 ? acc_c : acc_d, ((r0 >> 4) & NIB) | kBf16x2_128, ((r1 >> 4) & NIB) | kBf16x2_128,
+                    mma_k16(hi[g & 1], ((r0 >> 4) & NIB) | kBf16x2_128, ((r1 >> 4) & NIB) | kBf16x2_128,
                             ((r2 >> 4) & NIB) | kBf16x2_128, ((r3 >> 4) & NIB) | kBf16x2_128, b0[g][j], b1[g][j]);
                 }
             }
@@ -111,26 +161,28 @@ __global__ void __launch_bounds__(256, 2) nint_gemv_m1_kernel(const GemvArgs a) 
         float acc[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            acc[e] = acc_a[e] + acc_b[e];
-            if constexpr (NPL == 2) acc[e] = fmaf(16.f, acc_c[e] + acc_d[e], acc[e]);
+            if constexpr (NPL == 1) acc[e] = (ch[0][e] + ch[1][e]) + (ch[2][e] + ch[3][e]);
+            else acc[e] = fmaf(16.f, hi[0][e] + hi[1][e], ch[0][e] + ch[1][e]);
         }
         // sub-scales / sub-mins of rows (q, q+8) x groups (2c, 2c+1)
         uint32_t sp0, sp1, mp_lo, mp_hi;
         switch (c) {
-            case 0: sp0 = SU::at(it.sw, 0); sp1 = SU::at(it.sw, 1); mp_lo = SU::at(it.sw, 8); mp_hi = SU::at(it.sw, 12); break;
-            case 1: sp0 = SU::at(it.sw, 2); sp1 = SU::at(it.sw, 3); mp_lo = SU::at(it.sw, 9); mp_hi = SU::at(it.sw, 13); break;
-            case 2: sp0 = SU::at(it.sw, 4); sp1 = SU::at(it.sw, 5); mp_lo = SU::at(it.sw, 10); mp_hi = SU::at(it.sw, 14); break;
-            default: sp0 = SU::at(it.sw, 6); sp1 = SU::at(it.sw, 7); mp_lo = SU::at(it.sw, 11); mp_hi = SU::at(it.sw, 15); break;
+            case 0: sp0 = SU::at(sw, 0); sp1 = SU::at(sw, 1); mp_lo = SU::at(sw, 8); mp_hi = SU::at(sw, 12); break;
+            case 1: sp0 = SU::at(sw, 2); sp1 = SU::at(sw, 3); mp_lo = SU::at(sw, 9); mp_hi = SU::at(sw, 13); break;
+            case 2: sp0 = SU::at(sw, 4); sp1 = SU::at(sw, 5); mp_lo = SU::at(sw, 10); mp_hi = SU::at(sw, 14); break;
+            default: sp0 = SU::at(sw, 6); sp1 = SU::at(sw, 7); mp_lo = SU::at(sw, 11); mp_hi = SU::at(sw, 15); break;
         }
         float s0_lo, s0_hi, s1_lo, s1_hi, m0_lo, m1_lo, m0_hi, m1_hi;
         pair_to_floats<SW>(sp0, s0_lo, s0_hi);
         pair_to_floats<SW>(sp1, s1_lo, s1_hi);
         pair_to_floats<SW>(mp_lo, m0_lo, m1_lo);
         pair_to_floats<SW>(mp_hi, m0_hi, m1_hi);
-        const __half2 h_lo = *reinterpret_cast<const __half2*>(&it.an_lo), h_hi = *reinterpret_cast<const __half2*>(&it.an_hi);
-        const float2 f_lo = __half22float2(h_lo), f_hi = __half22float2(h_hi);  // (ns, nm)
+        const uint32_t an_lo = anch[rbl * 16 + q], an_hi = anch[rbl * 16 + q + 8];
+        const float2 f_lo = __half22float2(*reinterpret_cast<const __half2*>(&an_lo));   // (ns, nm)
+        const float2 f_hi = __half22float2(*reinterpret_cast<const __half2*>(&an_hi));
         float v_lo = f_lo.x * fmaf(s1_lo, acc[1], s0_lo * acc[0]) - f_lo.y * fmaf(m1_lo, xs1, m0_lo * xs0);
         float v_hi = f_hi.x * fmaf(s1_hi, acc[3], s0_hi * acc[2]) - f_hi.y * fmaf(m1_hi, xs1, m0_hi * xs0);
+        // the four lanes of a quad hold different groups of the same two rows
         v_lo += __shfl_xor_sync(0xffffffffu, v_lo, 1);
         v_hi += __shfl_xor_sync(0xffffffffu, v_hi, 1);
         v_lo += __shfl_xor_sync(0xffffffffu, v_lo, 2);
@@ -139,22 +191,10 @@ __global__ void __launch_bounds__(256, 2) nint_gemv_m1_kernel(const GemvArgs a) 
             atomicAdd(ypart + rbl * 16 + q, v_lo);
             atomicAdd(ypart + rbl * 16 + q + 8, v_hi);
         }
-    };
-
-    for (int i = 0; i < n_mine; i += 2) {
-        {
-            const int seg = item_seg(i);
-            if (seg != cur_seg) { cur_seg = seg; prepare_chunk(seg); }
-            compute_item(it0, i % nrb);
-            if (i + 2 < n_mine) it0.load(w, item_rb(i + 2), item_seg(i + 2), lane);
-        }
-        if (i + 1 < n_mine) {
-            const int seg = item_seg(i + 1);
-            if (seg != cur_seg) { cur_seg = seg; prepare_chunk(seg); }
-            compute_item(it1, (i + 1) % nrb);
-            if (i + 3 < n_mine) it1.load(w, item_rb(i + 3), item_seg(i + 3), lane);
-        }
+        if (++rbl == nrb) { rbl = 0; seg += nwarps; }
+        if (++stage == S) stage = 0;
     }
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     __syncthreads();
     for (int i = tid; i < nrb * 16; i += blockDim.x) {
         const int row = rb0 * 16 + i;

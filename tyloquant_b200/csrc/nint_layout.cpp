@@ -21,8 +21,9 @@ NintPacked pack_nint_device(const HostNint& t) {
     const int half = d.per / 2, npairs = kChunkGroups * d.per;
     d.wc = pair_unit_words(d.bits, npairs);
     const int swords_per = pair_unit_words(d.sw, 16);
-    p.qwords.assign((size_t)d.nrb * d.nchunks * d.wc * 32, 0u);
-    p.swords.assign((size_t)d.nrb * d.nchunks * swords_per * 8, 0u);
+    d.swc = swords_per;
+    d.rec_words = d.wc * 32 + d.swc * 8;
+    p.items.assign((size_t)d.nrb * d.nchunks * d.rec_words, 0u);
     p.anchors.assign((size_t)d.nrb * 16, 0u);
     for (int64_t r = 0; r < t.n; ++r) p.anchors[r] = (uint32_t)t.ns[r] | ((uint32_t)t.nm[r] << 16);
 
@@ -48,7 +49,7 @@ NintPacked pack_nint_device(const HostNint& t) {
                         }
                     }
                 }
-                for (int w = 0; w < d.wc; ++w) p.qwords[(item * d.wc + w) * 32 + lane] = lane_words[w];
+                for (int w = 0; w < d.wc; ++w) p.items[item * d.rec_words + (size_t)w * 32 + lane] = lane_words[w];
             }
             for (int q = 0; q < 8; ++q) {
                 std::fill(quad_words.begin(), quad_words.end(), 0u);
@@ -61,7 +62,7 @@ NintPacked pack_nint_device(const HostNint& t) {
                 for (int r = 0; r < 2; ++r)
                     for (int j = 0; j < 4; ++j)
                         pair_put(d.sw, quad_words.data(), 8 + 4 * r + j, sub(t.sm, r, 2 * j), sub(t.sm, r, 2 * j + 1));
-                for (int w = 0; w < swords_per; ++w) p.swords[(item * swords_per + w) * 8 + q] = quad_words[w];
+                for (int w = 0; w < swords_per; ++w) p.items[item * d.rec_words + (size_t)d.wc * 32 + (size_t)w * 8 + q] = quad_words[w];
             }
         }
     }
@@ -81,7 +82,7 @@ uint64_t selfcheck_nint_layout(const HostNint& t) {
         for (int64_t grp = 0; grp < t.ng; ++grp) {
             const int ch = (int)(grp / kChunkGroups), g = (int)(grp % kChunkGroups);
             const size_t item = (size_t)rb * d.nchunks + ch;
-            for (int w = 0; w < swords_per; ++w) quad_words[w] = p.swords[(item * swords_per + w) * 8 + q];
+            for (int w = 0; w < swords_per; ++w) quad_words[w] = p.items[item * d.rec_words + (size_t)d.wc * 32 + (size_t)w * 8 + q];
             const uint32_t sp = pair_get(d.sw, quad_words.data(), g);
             const uint32_t ssv = r ? (sp >> 16) : (sp & 0xFFFF);
             const uint32_t mp = pair_get(d.sw, quad_words.data(), 8 + 4 * r + g / 2);
@@ -90,7 +91,7 @@ uint64_t selfcheck_nint_layout(const HostNint& t) {
             if (smv != t.sm[row * t.ng + grp]) ++bad;
             for (int c = 0; c < 4; ++c) {
                 const int lane = 4 * q + c;
-                for (int w = 0; w < d.wc; ++w) lane_words[w] = p.qwords[(item * d.wc + w) * 32 + lane];
+                for (int w = 0; w < d.wc; ++w) lane_words[w] = p.items[item * d.rec_words + (size_t)w * 32 + lane];
                 for (int j = 0; j < half; ++j) {
                     const uint32_t pr = pair_get(d.bits, lane_words.data(), (g * 2 + r) * half + j);
                     const int i0 = c * d.per + 2 * j;

@@ -10,14 +10,18 @@
 //          = codes (c*PER + 2j, c*PER + 2j + 1) of row r, group g   (0 beyond the group)
 //
 // PER = groupsize/4 rounded up to an even number.  The pairs of a lane are packed with
-// PairUnit<bits>; word w of the 32 lanes is stored contiguously ([row-block][chunk][w][lane])
-// so one warp load instruction reads 128 consecutive bytes.
+// PairUnit<bits>; word w of the 32 lanes is stored contiguously ([w][lane]) so one warp load
+// instruction reads 128 consecutive bytes.
 //
 // Scales: per (row-block, chunk, quad q) 16 pairs of width SW (the stored sub-scale width,
 // >= the tensor's sub_bits), packed with PairUnit<SW>:
 //   pair g      (g = 0..7)        = (sub_scale[lo][g], sub_scale[hi][g])
 //   pair 8+4r+j (r = 0..1, j<4)   = (sub_min[r][2j],   sub_min[r][2j+1])
-// stored as [row-block][chunk][word][quad].
+// stored as [word][quad].
+//
+// One (row-block, chunk) item is one contiguous record of rec_words 32-bit words,
+//   [wc x 32 code words][swc x 8 scale words],   a multiple of 32 bytes,
+// records ordered [row-block][chunk]; a kernel moves a record with a few 16-byte async copies.
 // Anchors: one 32-bit word per row: f16 neuron_scale | f16 neuron_min << 16.
 #pragma once
 #include <cstdint>
@@ -26,8 +30,7 @@
 namespace mfqb {
 
 struct NintDev {
-    const uint32_t* qwords;
-    const uint32_t* swords;
+    const uint32_t* items;    // [nrb * nchunks][rec_words]
     const uint32_t* anchors;
     int n, k, ng;        // rows, columns, groups per row
     int nrb, nchunks;    // row-blocks of 16, chunks of 8 groups
@@ -35,6 +38,8 @@ struct NintDev {
     int per;             // codes per lane per row per group (even)
     int sw;              // stored scale width
     int wc;              // code words per lane per chunk
+    int swc;             // scale words per quad per chunk
+    int rec_words;       // wc * 32 + swc * 8
 };
 
 constexpr int kChunkGroups = 8;
@@ -49,7 +54,7 @@ inline int nint_stored_sub_width(int bits, int sub_bits) {
 
 struct HostNint;
 struct NintPacked {
-    std::vector<uint32_t> qwords, swords, anchors;
+    std::vector<uint32_t> items, anchors;
     NintDev d{};   // pointers unset; geometry filled
 };
 NintPacked pack_nint_device(const HostNint& t);

@@ -6,7 +6,7 @@
 #include <mutex>
 
 #include "cuda_util.h"
-#include "nint_gemv.cuh"
+#include "nint_gemv_m1.cuh"
 #include "nvq.h"
 
 namespace mfqb {
@@ -40,8 +40,14 @@ GemvPlan plan_nint_gemv(const NintDev& w, int m, int num_sms) {
     int words = (kp + 1) / 2;
     if (m > 1) words += (((2 * w.per - words) % 32) + 32) % 32;
     p.xstride = ((words * 2 + 7) / 8) * 8;
-    if (m == 1) {   // single-row kernel: partial sums [rb][16] and x, always staged
-        p.smem = (size_t)p.rb_per_cta * 16 * 4 + (size_t)p.xstride * 2;
+    p.stages = 0;
+    if (m == 1) {   // single-row kernel: partial sums and anchors [rb][16], x, and a record ring per warp
+        const size_t rec_bytes = (size_t)w.rec_words * 4;
+        p.stages = gemv_m1_stages(w.rec_words);
+        // three CTAs per SM, all resident at once; row-blocks are split evenly inside the kernel
+        p.grid = std::min(w.nrb, 3 * num_sms);
+        p.rb_per_cta = (w.nrb + p.grid - 1) / p.grid;
+        p.smem = (size_t)p.rb_per_cta * 16 * 8 + (size_t)p.xstride * 2 + (size_t)warps * p.stages * rec_bytes;
         return p;
     }
     const size_t fixed = (size_t)p.rb_per_cta * 128 * 4 + (size_t)warps * 64 * 4;
@@ -61,7 +67,7 @@ __device__ __forceinline__ void read_scales(const NintDev& w, size_t item, int q
     constexpr int SWC = PairUnit<SW>::words_for(16);
     uint32_t sq[SWC];
 #pragma unroll
-    for (int i = 0; i < SWC; ++i) sq[i] = w.swords[(item * SWC + i) * 8 + q];
+    for (int i = 0; i < SWC; ++i) sq[i] = w.items[item * w.rec_words + w.wc * 32 + i * 8 + q];
     const uint32_t sp = PairUnit<SW>::get_rt(sq + (g / PairUnit<SW>::NP) * PairUnit<SW>::U, g % PairUnit<SW>::NP);
     const int mt = 8 + 4 * r + g / 2;
     const uint32_t mp = PairUnit<SW>::get_rt(sq + (mt / PairUnit<SW>::NP) * PairUnit<SW>::U, mt % PairUnit<SW>::NP);
@@ -94,7 +100,7 @@ __global__ void nint_dequant_kernel(const NintDev w, void* out, int out_dtype) {
             const int t = (g * 2 + r) * half + j, unit = t / QU::NP;
             uint32_t uw[QU::U];
 #pragma unroll
-            for (int u = 0; u < QU::U; ++u) uw[u] = w.qwords[(item * w.wc + unit * QU::U + u) * 32 + lane];
+            for (int u = 0; u < QU::U; ++u) uw[u] = w.items[item * w.rec_words + (unit * QU::U + u) * 32 + lane];
             const uint32_t pr = QU::get_rt(uw, t % QU::NP);
             const int i0 = c * w.per + 2 * j, k0 = grp * w.gs + i0;
 #pragma unroll
@@ -139,6 +145,7 @@ static void launch_nint_gemv(const NintDev& w, const void* x, int m, void* y, in
     const GemvPlan p = plan_nint_gemv(w, m, device_sm_count(device));
     a.rb_per_cta = p.rb_per_cta;
     a.xstride = p.xstride;
+    a.stages = p.stages;
     cudaError_t e;
     switch (w.bits) {
         case 2: e = launch_nint_gemv_bits<2>(a, p, s); break;
@@ -160,7 +167,7 @@ struct mfqb_weight {
     int family = 0, device = 0;
     mfqb_weight_info info{};
     NintDev nint{};
-    DevBuf qwords, swords, anchors;
+    DevBuf items, anchors;
     NvqDevicePtr nvq;
 };
 
@@ -188,12 +195,10 @@ static mfqb_weight* make_nint_weight(const HostNint& t, int device) {
     DeviceGuard guard(device);
     w->family = MFQB_FAMILY_NINT;
     w->device = device;
-    w->qwords.upload(p.qwords.data(), p.qwords.size() * 4);
-    w->swords.upload(p.swords.data(), p.swords.size() * 4);
+    w->items.upload(p.items.data(), p.items.size() * 4);
     w->anchors.upload(p.anchors.data(), p.anchors.size() * 4);
     w->nint = p.d;
-    w->nint.qwords = static_cast<const uint32_t*>(w->qwords.p);
-    w->nint.swords = static_cast<const uint32_t*>(w->swords.p);
+    w->nint.items = static_cast<const uint32_t*>(w->items.p);
     w->nint.anchors = static_cast<const uint32_t*>(w->anchors.p);
     mfqb_weight_info& i = w->info;
     i.family = MFQB_FAMILY_NINT;
@@ -205,7 +210,7 @@ static mfqb_weight* make_nint_weight(const HostNint& t, int device) {
     i.device = device;
     i.jsc_banks = 0;
     i.payload_bytes = nint_payload_bytes(t);
-    i.device_bytes = w->qwords.bytes + w->swords.bytes + w->anchors.bytes;
+    i.device_bytes = w->items.bytes + w->anchors.bytes;
     return w.release();
 }
 
