@@ -72,6 +72,16 @@ def test_device_layout_round_trips_every_golden_nint_profile(golden):
         assert _selfcheck(dtype, blob) == 0, key
 
 
+def test_device_layout_round_trips_every_golden_nvq_profile(golden):
+    for key, dtype in [("nvq3_a", "NVQ3"), ("nvq3_b", "NVQ3"), ("nvq3_custom", "NVQ3"), ("nvq3j512_a", "NVQ3J-512"),
+                       ("nvq3j512_b", "NVQ3J-512")]:
+        assert _selfcheck(dtype, golden[key + "__blob"].tobytes()) == 0, key
+    banks = encode.synthetic_d4_banks(512, 2, seed=1)
+    w = encode.bf16_round(np.random.default_rng(0).standard_normal((21, 250), dtype=np.float32) * np.float32(0.02))
+    assert _selfcheck("NVQ3J-512", encode.nvq_blob(encode.quantize_nvq3(w, banks, jsc=True))) == 0
+    assert _selfcheck("NVQ3", encode.nvq_blob(encode.quantize_nvq3(w, O.d4_256_codebook()[None]))) == 0
+
+
 def test_device_layout_round_trips_ragged_shapes():
     for (n, k, bits, gs, sb) in [(1, 24, 3, 24, 5), (17, 25, 4, 24, 6), (33, 4096, 2, 16, 5), (16, 769, 5, 28, 7),
                                  (5, 100, 8, 48, 7), (40, 500, 6, 30, 7), (9, 64, 4, 32, 4), (9, 64, 4, 32, 8)]:
