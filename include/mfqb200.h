@@ -134,6 +134,93 @@ int mfqb_tp_validate(int64_t extent, int64_t granularity, int n_slices, const in
 int mfqb_tp_granularity(int64_t extent, int64_t preferred, int n_devices, int64_t* out);
 
 /* ---------------------------------------------------------------------------------
+ * Mixture-of-experts routing.
+ *
+ * mfqb_moe_topk replaces moe_topk_cuda (mfq/kernels/cuda/moe.cu:124-263, 3552-3637):
+ * per token, the k experts with the highest score, in descending score order, ties to the
+ * smaller expert id, NaN logits ranking last.  mode: 0 softmax over all experts, 1 sigmoid,
+ * 2 sqrt(softplus), 3 "delayed softmax" (select on raw logits, softmax over the selected k --
+ * the default of the reference FFN, cpp_runtime/mfq_decode.cpp:10483).  bias (may be NULL)
+ * is added to the score used for selection only.  With modes 0-2 `normalize` divides the k
+ * weights by max(sum, norm_floor).  Weights are finally multiplied by `scale`.
+ * logits: device float32 [tokens, experts]; ids: device int32 [tokens, k]; weights: device
+ * float32 [tokens, k].  k <= 16, experts <= 4096.
+ *
+ * mfqb_moe_route_plan replaces build_moe_route_plan / moe_build_expert_map_cuda
+ * (cpp_runtime/mfq_decode.cpp:2681-2708, mfq/kernels/cuda/moe.cu:472-542, 3676-3697):
+ * expert_bounds[e] .. expert_bounds[e+1] delimit, in pair_order, the (token*k + route) pair
+ * indices routed to expert e (ascending -- the reference fills them in arbitrary order);
+ * tile_bounds counts tiles of tile_m pairs per expert.  All arrays are device int32:
+ * expert_bounds and tile_bounds [experts+1], pair_order [tokens*k].
+ * --------------------------------------------------------------------------------- */
+enum { MFQB_ROUTER_SOFTMAX = 0, MFQB_ROUTER_SIGMOID = 1, MFQB_ROUTER_SQRT_SOFTPLUS = 2,
+       MFQB_ROUTER_DELAYED_SOFTMAX = 3 };
+
+int mfqb_moe_topk(const float* logits, int tokens, int experts, int k, int mode, const float* bias,
+                  int normalize, float norm_floor, float scale, int32_t* ids, float* weights,
+                  mfqb_stream_t stream);
+int mfqb_moe_route_plan(const int32_t* ids, int tokens, int k, int experts, int tile_m,
+                        int32_t* expert_bounds, int32_t* tile_bounds, int32_t* pair_order,
+                        mfqb_stream_t stream);
+
+/* ---------------------------------------------------------------------------------
+ * Expert-wise mixed-precision weights ("NINTM" records) and the routed expert matmul.
+ *
+ * mfqb_nintm_from_blob replaces unpack_nint_moe + initialize_nint_moe_dispatch +
+ * to_gpu_nint_moe (cpp_runtime/mfq_decode.cpp:2367-2478, 3249-3381); with an expert range
+ * [begin, end) it is the expert-parallel shard of to_cuda_device_moe_expert_slice
+ * (cpp_runtime/mfq_decode.cpp:5479-5590): only cohort rows of experts in the range are
+ * uploaded; the others are "not held" and their routes produce zeros.
+ *
+ * mfqb_mul_mat_id replaces NintMoeWeight::forward (cpp_runtime/mfq_decode.cpp:2908-3071):
+ *   out[t, r, :] = W[ids[t, r]] . x[src],   src = t (x_per_pair = 0, x is [tokens, k])
+ *                                            or the pair t*routes + r (x_per_pair = 1).
+ * x bf16, ids device int32 [tokens, routes], out [tokens, routes, out_per_expert] in out_dtype.
+ * --------------------------------------------------------------------------------- */
+typedef struct mfqb_moe_weight mfqb_moe_weight;
+
+typedef struct mfqb_moe_info {
+    int n_experts, out_per_expert, k;
+    int expert_begin, expert_end;  /* experts held by this handle */
+    int n_pools;
+    int device;
+    uint64_t payload_bytes;        /* file streams of the held experts */
+    uint64_t device_bytes;
+} mfqb_moe_info;
+
+int mfqb_nintm_from_blob(const void* blob, uint64_t nbytes, int expert_begin, int expert_end,
+                         int device, mfqb_moe_weight** out); /* end < 0: all experts */
+int mfqb_moe_info_get(const mfqb_moe_weight* w, mfqb_moe_info* info);
+/* bytes of the file streams of one expert (0 if not held): the roofline numerator of a step
+ * is the sum over the distinct experts it touches */
+int mfqb_moe_expert_bytes(const mfqb_moe_weight* w, int expert, uint64_t* payload_bytes);
+int mfqb_moe_weight_free(mfqb_moe_weight* w);
+/* [out_per_expert, k] float32/bf16 decode of one held expert (bit-identical to
+ * dequantize_expertwise, mfq/quantize/expert_nint.py:597-607) */
+int mfqb_moe_dequant_expert(const mfqb_moe_weight* w, int expert, void* out, int out_dtype,
+                            mfqb_stream_t stream);
+int mfqb_mul_mat_id(const mfqb_moe_weight* w, const void* x_bf16, int x_per_pair, const int32_t* ids,
+                    int tokens, int routes, void* out, int out_dtype, mfqb_stream_t stream);
+
+/* SwiGLU split (moe_swiglu_split_cuda, mfq/kernels/cuda/moe.cu:2979-2996; glu.cuh:6-17):
+ * rows of gate_up are [gate(F) | up(F)]; hidden = up * gate / (1 + exp(-gate)) in float32,
+ * stored as bf16.  Weighted reduce (moe_weighted_reduce_cuda, moe.cu:2957-2977):
+ * y[t, :] = sum_r weights[t, r] * expert_out[t, r, :] in float32, routes in order. */
+int mfqb_moe_swiglu(const void* gate_up, int in_dtype, int rows, int f, void* hidden_bf16,
+                    mfqb_stream_t stream);
+int mfqb_moe_weighted_reduce(const void* expert_out, int in_dtype, const float* weights, int tokens,
+                             int routes, int h, void* y, int y_dtype, mfqb_stream_t stream);
+
+/* Whole expert FFN (nint_moe_ffn_forward, cpp_runtime/mfq_decode.cpp:3394-3416):
+ *   y[t] = sum_r weights[t, r] * down_e( silu(gate_e x[t]) * up_e x[t] ),  e = ids[t, r].
+ * gate_up holds [E, 2F, H] (gate rows first), down [E, H, F].  The intermediates live in a
+ * scratch buffer the library keeps per device (grown on demand with cudaMalloc, so the first
+ * call for a given size must not be inside a stream capture). */
+int mfqb_moe_ffn(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* down, const void* x_bf16,
+                 const int32_t* ids, const float* weights, int tokens, int routes, void* y, int y_dtype,
+                 mfqb_stream_t stream);
+
+/* ---------------------------------------------------------------------------------
  * Host-side self-check of the device layout (no GPU): packs the blob into the device
  * format, reads every code and scale field back through the same accessors the kernels
  * use, and reports the number of mismatches against the file streams.

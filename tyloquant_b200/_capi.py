@@ -32,9 +32,15 @@ class WeightInfo(C.Structure):
                 ("payload_bytes", C.c_uint64), ("device_bytes", C.c_uint64)]
 
 
+class MoeInfo(C.Structure):
+    _fields_ = [("n_experts", C.c_int), ("out_per_expert", C.c_int), ("k", C.c_int), ("expert_begin", C.c_int),
+                ("expert_end", C.c_int), ("n_pools", C.c_int), ("device", C.c_int), ("payload_bytes", C.c_uint64),
+                ("device_bytes", C.c_uint64)]
+
+
 if not os.path.exists(LIB_PATH):
     raise ImportError(
-        f"{LIB_PATH} is missing: build it with `python -m tyloquant_b200.build` "
+        f"{LIB_PATH} is missing: build it with `python tyloquant_b200/build.py` "
         "(there is no CPU or pure-Python execution path)")
 
 lib = C.CDLL(LIB_PATH)
@@ -64,6 +70,17 @@ _SIGNATURES = {
     "mfqb_tp_validate": (_i, [_i64, _i64, _i, _P(_i64), _P(_i64)]),
     "mfqb_tp_granularity": (_i, [_i64, _i64, _i, _P(_i64)]),
     "mfqb_selfcheck_layout": (_i, [_cp, _vp, _u64, _P(_u64)]),
+    "mfqb_moe_topk": (_i, [_vp, _i, _i, _i, _i, _vp, _i, C.c_float, C.c_float, _vp, _vp, _vp]),
+    "mfqb_moe_route_plan": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "mfqb_nintm_from_blob": (_i, [_vp, _u64, _i, _i, _i, _P(_vp)]),
+    "mfqb_moe_info_get": (_i, [_vp, _P(MoeInfo)]),
+    "mfqb_moe_expert_bytes": (_i, [_vp, _i, _P(_u64)]),
+    "mfqb_moe_weight_free": (_i, [_vp]),
+    "mfqb_moe_dequant_expert": (_i, [_vp, _i, _vp, _i, _vp]),
+    "mfqb_mul_mat_id": (_i, [_vp, _vp, _i, _vp, _i, _i, _vp, _i, _vp]),
+    "mfqb_moe_swiglu": (_i, [_vp, _i, _i, _i, _vp, _vp]),
+    "mfqb_moe_weighted_reduce": (_i, [_vp, _i, _vp, _i, _i, _i, _vp, _i, _vp]),
+    "mfqb_moe_ffn": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _i, _vp]),
 }
 
 for _name, (_res, _args) in _SIGNATURES.items():

@@ -1,6 +1,6 @@
 """Build ``libmfqb200.so`` in-tree with nvcc for sm_100a.
 
-``python -m tyloquant_b200.build`` (or ``build()``) compiles every source under
+``python tyloquant_b200/build.py`` (or ``build()``) compiles every source under
 ``csrc/`` into ``tyloquant_b200/lib/`` and links the shared library.  Objects are cached
 by a hash of the source text, its headers and the flags, and translation units compile in
 parallel.  nvcc cross-compiles without a GPU.

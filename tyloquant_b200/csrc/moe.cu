@@ -1,0 +1,256 @@
+// Expert-wise mixed-precision weights (NINTM) on the device and the routed expert matmul.
+//
+// Every precision cohort of the record becomes one NINT device tensor whose rows are the held
+// experts of the cohort, each padded to whole 16-row blocks.  A routed matmul launches the
+// single-row kernel once per cohort over (row splits, pairs) CTAs; a CTA looks its pair's expert
+// up in two small tables (cohort of the expert, position inside the cohort) and returns when
+// the expert belongs to another cohort or is not held by this handle (expert-parallel shard).
+#include <cuda_bf16.h>
+
+#include <algorithm>
+#include <memory>
+#include <mutex>
+
+#include "cuda_util.h"
+#include "nint_gemv.cuh"
+
+namespace mfqb {
+void launch_swiglu(const void* gate_up, int in_dtype, int rows, int f, void* hidden, cudaStream_t s);
+void launch_weighted_reduce(const void* src, int in_dtype, const float* weights, int tokens, int routes, int h, void* y, int y_dtype,
+                            cudaStream_t s);
+
+struct MoePool {
+    NintDev d{};
+    DevBuf items, anchors;
+    int held = 0;   // experts of this cohort held here
+};
+
+// Rows of the listed experts (positions inside the cohort tensor), each padded with all-zero
+// rows to `padded` rows.
+static HostNint gather_experts(const HostNint& t, const std::vector<int>& local, int64_t ope, int64_t padded) {
+    HostNint r;
+    r.bits = t.bits;
+    r.sub_bits = t.sub_bits;
+    r.gs = t.gs;
+    r.k = t.k;
+    r.ng = t.ng;
+    r.n = (int64_t)local.size() * padded;
+    r.ns.assign(r.n, 0);
+    r.nm.assign(r.n, 0);
+    r.ss.assign((size_t)r.n * t.ng, 0);
+    r.sm.assign((size_t)r.n * t.ng, 0);
+    r.q.assign((size_t)r.n * t.ng * t.gs, 0);
+    for (size_t i = 0; i < local.size(); ++i) {
+        const int64_t src = (int64_t)local[i] * ope, dst = (int64_t)i * padded;
+        std::copy(t.ns.begin() + src, t.ns.begin() + src + ope, r.ns.begin() + dst);
+        std::copy(t.nm.begin() + src, t.nm.begin() + src + ope, r.nm.begin() + dst);
+        std::copy(t.ss.begin() + src * t.ng, t.ss.begin() + (src + ope) * t.ng, r.ss.begin() + dst * t.ng);
+        std::copy(t.sm.begin() + src * t.ng, t.sm.begin() + (src + ope) * t.ng, r.sm.begin() + dst * t.ng);
+        std::copy(t.q.begin() + src * t.ng * t.gs, t.q.begin() + (src + ope) * t.ng * t.gs, r.q.begin() + dst * t.ng * t.gs);
+    }
+    return r;
+}
+
+// Per-device scratch for the FFN intermediates; grown on demand.
+struct Scratch {
+    std::mutex mu;
+    DevBuf buf[64];
+};
+static Scratch g_scratch;
+static void* scratch_get(int device, size_t bytes) {
+    std::lock_guard<std::mutex> lock(g_scratch.mu);
+    DevBuf& b = g_scratch.buf[device];
+    if (b.bytes < bytes) b.alloc(bytes + bytes / 4);
+    return b.p;
+}
+
+}  // namespace mfqb
+
+using namespace mfqb;
+
+struct mfqb_moe_weight {
+    mfqb_moe_info info{};
+    std::vector<std::unique_ptr<MoePool>> pools;
+    std::vector<int> expert_pool, expert_local;          // host copies
+    std::vector<uint64_t> expert_bytes;
+    DevBuf d_expert_pool, d_expert_local;
+    int padded = 0;                                       // rows per expert on the device (multiple of 16)
+};
+
+static uint64_t expert_payload_bytes(const HostNint& t, int64_t ope) {
+    // share of the cohort's file streams: anchors + sub-scales + sub-mins + codes of `ope` rows
+    const uint64_t per_row_bits = 32ull + 2ull * t.ng * t.sub_bits + (uint64_t)t.ng * t.gs * t.bits;
+    return (per_row_bits * (uint64_t)ope + 7) / 8;
+}
+
+extern "C" {
+#pragma GCC visibility push(default)
+
+int mfqb_nintm_from_blob(const void* blob, uint64_t nbytes, int expert_begin, int expert_end, int device, mfqb_moe_weight** out) {
+    return guarded([&] {
+        if (!blob || !out) fail(MFQB_ERR_ARG, "mfqb_nintm_from_blob: null argument");
+        HostNintm t = parse_nintm(blob, nbytes);
+        if (expert_end < 0) expert_end = (int)t.n_experts;
+        if (expert_begin < 0 || expert_begin >= expert_end || expert_end > t.n_experts)
+            fail(MFQB_ERR_ARG, "expert range [%d, %d) is outside [0, %lld)", expert_begin, expert_end, (long long)t.n_experts);
+        if (t.pools.size() > 16) fail(MFQB_ERR_UNSUPPORTED, "more than 16 precision cohorts in one NINTM record");
+        auto w = std::make_unique<mfqb_moe_weight>();
+        DeviceGuard guard(device);
+        const int64_t ope = t.out_per_expert;
+        w->padded = (int)((ope + 15) / 16 * 16);
+        w->expert_pool.assign((size_t)t.n_experts, -1);
+        w->expert_local.assign((size_t)t.n_experts, 0);
+        w->expert_bytes.assign((size_t)t.n_experts, 0);
+        uint64_t payload = 0, dev_bytes = 0;
+        for (auto& hp : t.pools) {
+            check_nint_supported(hp.tensor);
+            std::vector<int> local;
+            const int pool_index = (int)w->pools.size();
+            for (size_t i = 0; i < hp.expert_ids.size(); ++i) {
+                const int e = hp.expert_ids[i];
+                if (e < expert_begin || e >= expert_end) continue;
+                w->expert_pool[e] = pool_index;
+                w->expert_local[e] = (int)local.size();
+                w->expert_bytes[e] = expert_payload_bytes(hp.tensor, ope);
+                payload += w->expert_bytes[e];
+                local.push_back((int)i);
+            }
+            auto pool = std::make_unique<MoePool>();
+            pool->held = (int)local.size();
+            if (!local.empty()) {
+                NintPacked p = pack_nint_device(gather_experts(hp.tensor, local, ope, w->padded));
+                pool->items.upload(p.items.data(), p.items.size() * 4);
+                pool->anchors.upload(p.anchors.data(), p.anchors.size() * 4);
+                pool->d = p.d;
+                pool->d.items = static_cast<const uint32_t*>(pool->items.p);
+                pool->d.anchors = static_cast<const uint32_t*>(pool->anchors.p);
+                dev_bytes += pool->items.bytes + pool->anchors.bytes;
+            }
+            w->pools.push_back(std::move(pool));
+        }
+        w->d_expert_pool.upload(w->expert_pool.data(), w->expert_pool.size() * 4);
+        w->d_expert_local.upload(w->expert_local.data(), w->expert_local.size() * 4);
+        mfqb_moe_info& i = w->info;
+        i.n_experts = (int)t.n_experts;
+        i.out_per_expert = (int)ope;
+        i.k = (int)t.k;
+        i.expert_begin = expert_begin;
+        i.expert_end = expert_end;
+        i.n_pools = (int)w->pools.size();
+        i.device = device;
+        i.payload_bytes = payload;
+        i.device_bytes = dev_bytes + w->d_expert_pool.bytes + w->d_expert_local.bytes;
+        *out = w.release();
+    });
+}
+
+int mfqb_moe_info_get(const mfqb_moe_weight* w, mfqb_moe_info* info) {
+    return guarded([&] {
+        if (!w || !info) fail(MFQB_ERR_ARG, "mfqb_moe_info_get: null argument");
+        *info = w->info;
+    });
+}
+
+int mfqb_moe_expert_bytes(const mfqb_moe_weight* w, int expert, uint64_t* payload_bytes) {
+    return guarded([&] {
+        if (!w || !payload_bytes || expert < 0 || expert >= w->info.n_experts) fail(MFQB_ERR_ARG, "mfqb_moe_expert_bytes: bad argument");
+        *payload_bytes = w->expert_bytes[expert];
+    });
+}
+
+int mfqb_moe_weight_free(mfqb_moe_weight* w) {
+    return guarded([&] {
+        if (!w) return;
+        DeviceGuard guard(w->info.device);
+        delete w;
+    });
+}
+
+int mfqb_moe_dequant_expert(const mfqb_moe_weight* w, int expert, void* out, int out_dtype, mfqb_stream_t stream) {
+    return guarded([&] {
+        if (!w || !out) fail(MFQB_ERR_ARG, "mfqb_moe_dequant_expert: null argument");
+        if (out_dtype != MFQB_F32 && out_dtype != MFQB_BF16) fail(MFQB_ERR_ARG, "mfqb_moe_dequant_expert: bad output dtype");
+        if (expert < 0 || expert >= w->info.n_experts || w->expert_pool[expert] < 0)
+            fail(MFQB_ERR_ARG, "expert %d is not held by this handle", expert);
+        DeviceGuard guard(w->info.device);
+        const MoePool& pool = *w->pools[w->expert_pool[expert]];
+        NintDev view = pool.d;   // the expert's row-blocks as a tensor of its own
+        const int rb0 = w->expert_local[expert] * (w->padded / 16);
+        view.items += (size_t)rb0 * view.nchunks * view.rec_words;
+        view.anchors += (size_t)rb0 * 16;
+        view.n = w->info.out_per_expert;
+        view.nrb = w->padded / 16;
+        launch_nint_dequant_view(view, out, out_dtype, stream);
+    });
+}
+
+int mfqb_mul_mat_id(const mfqb_moe_weight* w, const void* x, int x_per_pair, const int32_t* ids, int tokens, int routes, void* out,
+                    int out_dtype, mfqb_stream_t stream) {
+    return guarded([&] {
+        if (!w || !x || !ids || !out) fail(MFQB_ERR_ARG, "mfqb_mul_mat_id: null argument");
+        if (tokens < 0 || routes < 1) fail(MFQB_ERR_ARG, "mfqb_mul_mat_id: bad sizes");
+        if (out_dtype != MFQB_F32 && out_dtype != MFQB_BF16) fail(MFQB_ERR_ARG, "mfqb_mul_mat_id: bad output dtype");
+        if (tokens == 0) return;
+        DeviceGuard guard(w->info.device);
+        const int pairs = tokens * routes, ope = w->info.out_per_expert;
+        // Routes to experts this handle does not hold produce zeros (expert-parallel shards are
+        // summed afterwards), so clear the output when the handle is partial.
+        if (w->info.expert_end - w->info.expert_begin != w->info.n_experts)
+            MFQB_CUDA(cudaMemsetAsync(out, 0, (size_t)pairs * ope * (out_dtype == MFQB_F32 ? 4 : 2), stream));
+        for (size_t pi = 0; pi < w->pools.size(); ++pi) {
+            const MoePool& pool = *w->pools[pi];
+            if (!pool.held) continue;
+            GemvArgs a{};
+            a.w = pool.d;
+            a.x = static_cast<const __nv_bfloat16*>(x);
+            a.y = out;
+            a.ldy = ope;
+            a.y_dtype = out_dtype;
+            a.route_ids = ids;
+            a.expert_pool = static_cast<const int*>(w->d_expert_pool.p);
+            a.expert_local = static_cast<const int*>(w->d_expert_local.p);
+            a.pool = (int)pi;
+            a.rb_per_expert = w->padded / 16;
+            a.routes = routes;
+            a.x_per_pair = x_per_pair ? 1 : 0;
+            for (int p0 = 0; p0 < pairs; p0 += 32768) {   // gridDim.y limit
+                GemvArgs b = a;
+                const int np = std::min(32768, pairs - p0);
+                b.route_ids = ids + p0;
+                b.y = static_cast<char*>(out) + (size_t)p0 * ope * (out_dtype == MFQB_F32 ? 4 : 2);
+                // x: pair p0 is token p0 / routes when x is shared; chunks start on token boundaries
+                if (p0 % routes) fail(MFQB_ERR_ARG, "mfqb_mul_mat_id: routes must divide 32768 for more than 32768 pairs");
+                b.x = a.x + (size_t)(x_per_pair ? p0 : p0 / routes) * w->info.k;
+                launch_nint_gemv_routed(b, np, w->info.device, stream);
+            }
+        }
+    });
+}
+
+int mfqb_moe_ffn(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* down, const void* x, const int32_t* ids, const float* weights,
+                 int tokens, int routes, void* y, int y_dtype, mfqb_stream_t stream) {
+    return guarded([&] {
+        if (!gate_up || !down || !x || !ids || !weights || !y) fail(MFQB_ERR_ARG, "mfqb_moe_ffn: null argument");
+        const int h = gate_up->info.k, f2 = gate_up->info.out_per_expert, f = f2 / 2;
+        if (f2 % 2 || down->info.k != f || down->info.out_per_expert != h || down->info.n_experts != gate_up->info.n_experts)
+            fail(MFQB_ERR_ARG, "mfqb_moe_ffn: gate_up [E, 2F, H] and down [E, H, F] shapes do not match");
+        if (gate_up->info.device != down->info.device) fail(MFQB_ERR_ARG, "mfqb_moe_ffn: weights live on different devices");
+        if (tokens <= 0) return;
+        DeviceGuard guard(gate_up->info.device);
+        const size_t pairs = (size_t)tokens * routes;
+        const size_t b_gu = pairs * f2 * 4, b_hid = (pairs * f * 2 + 255) / 256 * 256, b_dn = pairs * h * 4;
+        char* s = static_cast<char*>(scratch_get(gate_up->info.device, b_gu + b_hid + b_dn));
+        float* gu = reinterpret_cast<float*>(s);
+        void* hid = s + b_gu;
+        float* dn = reinterpret_cast<float*>(s + b_gu + b_hid);
+        int rc = mfqb_mul_mat_id(gate_up, x, 0, ids, tokens, routes, gu, MFQB_F32, stream);
+        if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
+        launch_swiglu(gu, MFQB_F32, (int)pairs, f, hid, stream);
+        rc = mfqb_mul_mat_id(down, hid, 1, ids, tokens, routes, dn, MFQB_F32, stream);
+        if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
+        launch_weighted_reduce(dn, MFQB_F32, weights, tokens, routes, h, y, y_dtype, stream);
+    });
+}
+
+#pragma GCC visibility pop
+}  // extern "C"

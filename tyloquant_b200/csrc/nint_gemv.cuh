@@ -19,6 +19,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include "common.h"
 #include "nint_layout.h"
 #include "pair_unit.h"
 
@@ -83,6 +84,16 @@ struct GemvArgs {
     int rb_per_cta;          // row-blocks per CTA
     int xstride;             // row stride (elements, multiple of 8) of x staged in shared memory; 0 = read x from global
     int stages;              // records per warp ring (single-row kernel)
+    // Routed mode of the single-row kernel (expert matmul, "mul_mat_id"): blockIdx.y is a
+    // (token, route) pair; the pair's expert selects a block of rows_per_expert rows of w.
+    // A CTA whose expert does not live in this cohort (pool) returns at once.
+    const int* route_ids;    // [pairs] expert of each pair; nullptr = plain GEMV
+    const int* expert_pool;  // [experts] cohort index of each expert (-1: not held here)
+    const int* expert_local; // [experts] position of the expert inside its cohort
+    int pool;                // cohort this launch covers
+    int rb_per_expert;       // rows_per_expert / 16
+    int routes;              // routes per token (R)
+    int x_per_pair;          // 1: x is [pairs, k]; 0: x is [tokens, k], shared by the token's routes
 };
 
 constexpr uint32_t kBf16x2_one = 0x3F803F80u;  // (1.0, 1.0)
@@ -327,12 +338,16 @@ __global__ void __launch_bounds__(256, 2) nint_gemv_kernel(const GemvArgs a) {
 
 // Shared-memory footprint and launch geometry, computed on the host.
 struct GemvPlan {
-    int rb_per_cta, grid, threads, xstride, stages;
+    int rb_per_cta, grid, grid_y, threads, xstride, stages;
     size_t smem;
 };
 GemvPlan plan_nint_gemv(const NintDev& w, int m, int num_sms);
 
 template <int BITS>
 cudaError_t launch_nint_gemv_bits(const GemvArgs& a, const GemvPlan& p, cudaStream_t stream);
+
+void launch_nint_gemv_routed(GemvArgs a, int pairs, int device, cudaStream_t s);
+void launch_nint_dequant_view(const NintDev& w, void* out, int out_dtype, cudaStream_t s);
+void check_nint_supported(const HostNint& t);
 
 }  // namespace mfqb

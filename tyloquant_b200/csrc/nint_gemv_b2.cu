@@ -12,7 +12,7 @@ static cudaError_t launch_one(const GemvArgs& a, const GemvPlan& p, cudaStream_t
         if (e != cudaSuccess) return e;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)p.grid);
+    cfg.gridDim = dim3((unsigned)p.grid, (unsigned)p.grid_y);
     cfg.blockDim = dim3((unsigned)p.threads);
     cfg.dynamicSmemBytes = p.smem;
     cfg.stream = stream;

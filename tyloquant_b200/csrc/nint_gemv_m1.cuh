@@ -50,9 +50,24 @@ __global__ void __launch_bounds__(256, 3) nint_gemv_m1_kernel(const GemvArgs a) 
     uint32_t* anch = reinterpret_cast<uint32_t*>(ypart + (size_t)a.rb_per_cta * 16);
     __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(anch + (size_t)a.rb_per_cta * 16);
     uint32_t* ring = reinterpret_cast<uint32_t*>(xs + a.xstride) + (size_t)warp * S * REC;
-    // balanced split of the row-blocks over the grid: CTA b owns [b*nrb/grid, (b+1)*nrb/grid)
-    const int rb0 = (int)(((long long)blockIdx.x * w.nrb) / gridDim.x);
-    const int nrb = (int)(((long long)(blockIdx.x + 1) * w.nrb) / gridDim.x) - rb0;
+    // balanced split of the row-blocks over gridDim.x: CTA b owns [b*R/grid, (b+1)*R/grid) of the
+    // R row-blocks of the whole matrix, or of its pair's expert in routed mode
+    int rb_base = 0, rb_total = w.nrb;
+    const __nv_bfloat16* xrow = a.x;
+    size_t y_off = 0;
+    if (a.route_ids != nullptr) {
+        pdl_wait();   // the routing table comes from the previous kernel
+        const int pair = blockIdx.y, e = a.route_ids[pair];
+        if (e < 0 || a.expert_pool[e] != a.pool) return;
+        rb_total = a.rb_per_expert;
+        rb_base = a.expert_local[e] * a.rb_per_expert;
+        xrow += (size_t)(a.x_per_pair ? pair : pair / a.routes) * w.k;
+        y_off = (size_t)pair * a.ldy;
+    }
+    const int rbl0 = (int)(((long long)blockIdx.x * rb_total) / gridDim.x);
+    const int nrb = (int)(((long long)(blockIdx.x + 1) * rb_total) / gridDim.x) - rbl0;
+    const int rb0 = rb_base + rbl0;
+    const int row_limit = a.route_ids != nullptr ? a.ldy : w.n;   // rows this problem has (an expert's rows are padded to whole blocks)
 
     // items of this warp, chunk-major: chunk = warp, warp + nwarps, ...; inside a chunk every
     // row-block of the CTA.  Two cursors walk that sequence (issue runs S items ahead); they are
@@ -84,14 +99,14 @@ __global__ void __launch_bounds__(256, 3) nint_gemv_m1_kernel(const GemvArgs a) 
     pdl_wait();
     {   // stage x (zero beyond k): 16-byte copies when the row is 16-byte aligned
         const int kp = a.xstride;
-        if ((w.k & 7) == 0 && (reinterpret_cast<uintptr_t>(a.x) & 15) == 0) {
+        if ((w.k & 7) == 0 && (reinterpret_cast<uintptr_t>(xrow) & 15) == 0) {
             for (int v = tid; v < kp / 8; v += blockDim.x) {
                 uint4 val = make_uint4(0u, 0u, 0u, 0u);
-                if (v * 8 < w.k) val = __ldg(reinterpret_cast<const uint4*>(a.x) + v);
+                if (v * 8 < w.k) val = __ldg(reinterpret_cast<const uint4*>(xrow) + v);
                 *reinterpret_cast<uint4*>(xs + v * 8) = val;
             }
         } else {
-            for (int k = tid; k < kp; k += blockDim.x) xs[k] = k < w.k ? a.x[k] : __float2bfloat16(0.f);
+            for (int k = tid; k < kp; k += blockDim.x) xs[k] = k < w.k ? xrow[k] : __float2bfloat16(0.f);
         }
     }
     __syncthreads();
@@ -197,11 +212,11 @@ __global__ void __launch_bounds__(256, 3) nint_gemv_m1_kernel(const GemvArgs a) 
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     __syncthreads();
     for (int i = tid; i < nrb * 16; i += blockDim.x) {
-        const int row = rb0 * 16 + i;
-        if (row < w.n) {
+        const int row = rbl0 * 16 + i;   // row inside the problem (matrix, or the pair's expert)
+        if (row < row_limit) {
             const float v = ypart[i];
-            if (a.y_dtype == 0 /* MFQB_F32 */) reinterpret_cast<float*>(a.y)[row] = v;
-            else reinterpret_cast<__nv_bfloat16*>(a.y)[row] = __float2bfloat16_rn(v);
+            if (a.y_dtype == 0 /* MFQB_F32 */) reinterpret_cast<float*>(a.y)[y_off + row] = v;
+            else reinterpret_cast<__nv_bfloat16*>(a.y)[y_off + row] = __float2bfloat16_rn(v);
         }
     }
 }

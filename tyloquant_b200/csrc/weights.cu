@@ -26,6 +26,7 @@ int device_sm_count(int device) {
 
 GemvPlan plan_nint_gemv(const NintDev& w, int m, int num_sms) {
     GemvPlan p;
+    p.grid_y = 1;
     // Two 8-warp CTAs per SM; each CTA owns whole row-blocks (all chunks of K), so partial sums
     // stay in its shared memory.
     const int target = 2 * num_sms;
@@ -142,6 +143,9 @@ static void launch_nint_gemv(const NintDev& w, const void* x, int m, void* y, in
     a.m = m;
     a.ldy = ldy;
     a.y_dtype = y_dtype;
+    a.route_ids = nullptr;
+    a.expert_pool = a.expert_local = nullptr;
+    a.pool = a.rb_per_expert = a.routes = a.x_per_pair = 0;
     const GemvPlan p = plan_nint_gemv(w, m, device_sm_count(device));
     a.rb_per_cta = p.rb_per_cta;
     a.xstride = p.xstride;
@@ -158,6 +162,35 @@ static void launch_nint_gemv(const NintDev& w, const void* x, int m, void* y, in
     }
     if (e != cudaSuccess) fail(MFQB_ERR_CUDA, "NINT%d gs=%d GEMV launch: %s", w.bits, w.gs, cudaGetErrorString(e));
 }
+
+// Routed single-row launch over (splits, pairs) CTAs for one cohort; see GemvArgs.
+void launch_nint_gemv_routed(GemvArgs a, int pairs, int device, cudaStream_t s) {
+    const NintDev& w = a.w;
+    a.m = 1;
+    GemvPlan p = plan_nint_gemv(w, 1, device_sm_count(device));
+    const int want = (3 * device_sm_count(device) + pairs - 1) / std::max(pairs, 1);
+    const int splits = std::max(1, std::min(a.rb_per_expert, want));
+    p.rb_per_cta = (a.rb_per_expert + splits - 1) / splits;
+    p.smem = (size_t)p.rb_per_cta * 16 * 8 + (size_t)p.xstride * 2 + (size_t)8 * p.stages * w.rec_words * 4;
+    a.rb_per_cta = p.rb_per_cta;
+    a.xstride = p.xstride;
+    a.stages = p.stages;
+    p.grid = splits;
+    p.grid_y = pairs;
+    cudaError_t e;
+    switch (w.bits) {
+        case 2: e = launch_nint_gemv_bits<2>(a, p, s); break;
+        case 3: e = launch_nint_gemv_bits<3>(a, p, s); break;
+        case 4: e = launch_nint_gemv_bits<4>(a, p, s); break;
+        case 5: e = launch_nint_gemv_bits<5>(a, p, s); break;
+        case 6: e = launch_nint_gemv_bits<6>(a, p, s); break;
+        case 8: e = launch_nint_gemv_bits<8>(a, p, s); break;
+        default: fail(MFQB_ERR_UNSUPPORTED, "NINT%d has no kernel", w.bits);
+    }
+    if (e != cudaSuccess) fail(MFQB_ERR_CUDA, "NINT%d routed GEMV launch: %s", w.bits, cudaGetErrorString(e));
+}
+
+void launch_nint_dequant_view(const NintDev& w, void* out, int out_dtype, cudaStream_t s) { launch_nint_dequant(w, out, out_dtype, s); }
 
 }  // namespace mfqb
 
@@ -176,7 +209,7 @@ namespace mfqb {
 // Batch rows one GEMV launch covers (the n8 slot of the tensor-core tile).
 static int nint_gemv_max_batch(const NintDev&, int) { return 8; }
 
-static void check_nint_supported(const HostNint& t) {
+void check_nint_supported(const HostNint& t) {
     const int b = t.bits;
     if (!(b == 2 || b == 3 || b == 4 || b == 5 || b == 6 || b == 8))
         fail(MFQB_ERR_UNSUPPORTED, "NINT%d is not an executable code width (2,3,4,5,6,8)", b);
