@@ -220,6 +220,30 @@ int mfqb_moe_ffn(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* down, co
                  const int32_t* ids, const float* weights, int tokens, int routes, void* y, int y_dtype,
                  mfqb_stream_t stream);
 
+/* Expert FFN that allocates nothing.  (No counterpart in the reference runtime, whose FFN takes
+ * its workspaces from the libtorch caching allocator.)
+ *
+ * Same result as mfqb_moe_ffn, for callers that are not allowed to allocate device memory at the
+ * point of the call: code running while a stream is being captured into a graph, a serving loop
+ * that has handed all free HBM to its KV cache and must not fragment it, or a host process whose
+ * allocator hooks forbid cudaMalloc on the hot path.  The three intermediates (gate/up
+ * products, the SwiGLU activation, the down products) go into one fixed array of
+ * MFQB_STATIC_SCRATCH_BYTES that is part of the library image; every GPU that loads the library
+ * holds that much memory until the process exits.
+ *
+ *  - tokens * routes * (2F*4 + F*2 + H*4) bytes (rounded up a little) must fit; a larger call is
+ *    rejected with MFQB_ERR_ARG and a message giving both numbers -- use mfqb_moe_ffn then.
+ *  - The first call on a device looks the array's device address up (once per device, with that
+ *    device current).  Make that first call before any stream capture.
+ *  - All calls share the one array and it keeps the previous call's contents; each call clears
+ *    the part it uses first.  Two calls whose device work overlaps (different streams, or
+ *    different host threads) race on it: serialise them.
+ *  - It calls no cudaMalloc / cudaFree and no library routine that allocates. */
+#define MFQB_STATIC_SCRATCH_BYTES (8u << 20)
+int mfqb_moe_ffn_static(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* down, const void* x_bf16,
+                        const int32_t* ids, const float* weights, int tokens, int routes, void* y,
+                        int y_dtype, mfqb_stream_t stream);
+
 /* ---------------------------------------------------------------------------------
  * Host-side self-check of the device layout (no GPU): packs the blob into the device
  * format, reads every code and scale field back through the same accessors the kernels

@@ -81,6 +81,7 @@ _SIGNATURES = {
     "mfqb_moe_swiglu": (_i, [_vp, _i, _i, _i, _vp, _vp]),
     "mfqb_moe_weighted_reduce": (_i, [_vp, _i, _vp, _i, _i, _i, _vp, _i, _vp]),
     "mfqb_moe_ffn": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _i, _vp]),
+    "mfqb_moe_ffn_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _i, _vp]),
 }
 
 for _name, (_res, _args) in _SIGNATURES.items():

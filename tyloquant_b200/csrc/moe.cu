@@ -254,3 +254,65 @@ int mfqb_moe_ffn(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* down, co
 
 #pragma GCC visibility pop
 }  // extern "C"
+
+// ---- expert FFN for callers that cannot allocate -------------------------------------------------
+// Scratch for the intermediates lives in this fixed array inside the library image instead of a
+// cudaMalloc'd buffer.  Every GPU that loads the library carries it until the process exits.
+static __device__ __align__(256) unsigned char g_ffn_static_scratch[MFQB_STATIC_SCRATCH_BYTES];
+
+namespace mfqb {
+// The array's name is only a host-side stand-in; the device address is asked for once per device,
+// with that device current, and cached.
+static unsigned char* ffn_static_scratch(int device) {
+    static std::mutex mu;
+    static unsigned char* ptr[64] = {nullptr};
+    std::lock_guard<std::mutex> lock(mu);
+    if (device < 0 || device >= 64) fail(MFQB_ERR_ARG, "device index %d out of range", device);
+    if (!ptr[device]) {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_ffn_static_scratch);
+        if (e != cudaSuccess || !p) fail(MFQB_ERR_CUDA, "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
+        ptr[device] = static_cast<unsigned char*>(p);
+    }
+    return ptr[device];
+}
+}  // namespace mfqb
+
+extern "C" {
+#pragma GCC visibility push(default)
+
+int mfqb_moe_ffn_static(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* down, const void* x, const int32_t* ids,
+                        const float* weights, int tokens, int routes, void* y, int y_dtype, mfqb_stream_t stream) {
+    return guarded([&] {
+        if (!gate_up || !down || !x || !ids || !weights || !y) fail(MFQB_ERR_ARG, "mfqb_moe_ffn_static: null argument");
+        const int h = gate_up->info.k, f2 = gate_up->info.out_per_expert, f = f2 / 2;
+        if (f2 % 2 || down->info.k != f || down->info.out_per_expert != h || down->info.n_experts != gate_up->info.n_experts)
+            fail(MFQB_ERR_ARG, "mfqb_moe_ffn_static: gate_up [E, 2F, H] and down [E, H, F] shapes do not match");
+        if (gate_up->info.device != down->info.device) fail(MFQB_ERR_ARG, "mfqb_moe_ffn_static: weights live on different devices");
+        if (tokens <= 0 || routes < 1) return;
+        const size_t pairs = (size_t)tokens * routes;
+        const size_t b_gu = pairs * f2 * 4, b_hid = (pairs * f * 2 + 255) / 256 * 256, b_dn = pairs * h * 4;
+        if (b_gu + b_hid + b_dn > (size_t)MFQB_STATIC_SCRATCH_BYTES)
+            fail(MFQB_ERR_ARG,
+                 "mfqb_moe_ffn_static: %d tokens x %d routes need %llu bytes of scratch, the built-in array holds %llu; "
+                 "use mfqb_moe_ffn or fewer tokens per call",
+                 tokens, routes, (unsigned long long)(b_gu + b_hid + b_dn), (unsigned long long)MFQB_STATIC_SCRATCH_BYTES);
+        DeviceGuard guard(gate_up->info.device);
+        unsigned char* s = ffn_static_scratch(gate_up->info.device);
+        // The array still holds whatever the previous call left: start the two accumulation targets
+        // from zero so that a route to an expert nobody holds contributes nothing.
+        MFQB_CUDA(cudaMemsetAsync(s, 0, b_gu + b_hid + b_dn, stream));
+        float* gu = reinterpret_cast<float*>(s);
+        void* hid = s + b_gu;
+        float* dn = reinterpret_cast<float*>(s + b_gu + b_hid);
+        int rc = mfqb_mul_mat_id(gate_up, x, 0, ids, tokens, routes, gu, MFQB_F32, stream);
+        if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
+        launch_swiglu(gu, MFQB_F32, (int)pairs, f, hid, stream);
+        rc = mfqb_mul_mat_id(down, hid, 1, ids, tokens, routes, dn, MFQB_F32, stream);
+        if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
+        launch_weighted_reduce(dn, MFQB_F32, weights, tokens, routes, h, y, y_dtype, stream);
+    });
+}
+
+#pragma GCC visibility pop
+}  // extern "C"
