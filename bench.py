@@ -305,6 +305,7 @@ def main() -> None:
         line["cpu_baseline"] = cb
         if not args.no_sweep:
             line["sweep"] = sweep(dev, peaks["hbm_gbs"])
+            line["moe_layer_cfg4"] = moe_layer_bench(dev, peaks["hbm_gbs"])
     print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
@@ -321,16 +322,41 @@ def sweep(dev: int, peak: float, only: str | None = None, reps: int = 10) -> dic
     from tyloquant_b200._capi import BF16, check, lib
 
     out = {}
-    cases = [(f"NINT{b}_4096x4096_m1", (b, gs, sb), 4096, 4096, 1) for b, (_, gs, sb) in encode.CANONICAL_NINT.items()]
-    cases += [("NINT4_14336x4096_m1", (4, 24, 6), 14336, 4096, 1), ("NINT6_14336x4096_m1", (6, 24, 7), 14336, 4096, 1),
-              ("NINT3_4096x4096_m8", (3, 24, 5), 4096, 4096, 8), ("NINT4_4096x14336_m1", (4, 24, 6), 4096, 14336, 1)]
-    for name, (b, gs, sb), n, k, m in cases:
+    d = f"cuda:{dev}"
+
+    def nint_case(b, gs, sb, n, k):
+        return (f"NINT{b}", lambda: encode.random_nint_blob(n, k, b, gs, sb, seed=77, device=d))
+
+    def nvq_case(jsc, n, k):
+        def make():
+            rng = np.random.default_rng(3001)
+            w = encode.bf16_round(rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02))
+            banks = encode.synthetic_d4_banks(512, 2, seed=9) if jsc else encode.d4_256_codebook()[None]
+            return encode.nvq_blob(encode.quantize_nvq3(w, banks, jsc=jsc, device=d))
+        return ("NVQ3J-512" if jsc else "NVQ3", make)
+
+    cases = [(f"NINT{b}_4096x4096_m1", nint_case(b, gs, sb, 4096, 4096), 4096, 4096, 1)
+             for b, (_, gs, sb) in encode.CANONICAL_NINT.items()]
+    cases += [("NINT4_14336x4096_m1", nint_case(4, 24, 6, 14336, 4096), 14336, 4096, 1),
+              ("NINT6_14336x4096_m1", nint_case(6, 24, 7, 14336, 4096), 14336, 4096, 1),
+              ("NINT3_4096x4096_m8", nint_case(3, 24, 5, 4096, 4096), 4096, 4096, 8),
+              ("NINT4_4096x14336_m1", nint_case(4, 24, 6, 4096, 14336), 4096, 14336, 1),
+              ("NVQ3_17408x5120_m1", nvq_case(False, 17408, 5120), 17408, 5120, 1),
+              ("NVQ3_17408x5120_m4", nvq_case(False, 17408, 5120), 17408, 5120, 4),
+              ("NVQ3_17408x5120_m8", nvq_case(False, 17408, 5120), 17408, 5120, 8),
+              ("NVQ3J-512_17408x5120_m1", nvq_case(True, 17408, 5120), 17408, 5120, 1)]
+    blob_cache = {}
+    for name, (dtype, make_blob), n, k, m in cases:
         if only and name != only:
             continue
-        blob = encode.random_nint_blob(n, k, b, gs, sb, seed=77, device=f"cuda:{dev}")
-        probe = QuantWeight.from_blob(f"NINT{b}", blob, device=dev)
+        key = name.rsplit("_m", 1)[0]
+        if key not in blob_cache:
+            blob_cache.clear()
+            blob_cache[key] = make_blob()
+        blob = blob_cache[key]
+        probe = QuantWeight.from_blob(dtype, blob, device=dev)
         pool = int(max(4, min(64, (1.2 if only else 2.5) * 126e6 / probe.device_bytes + 1)))
-        ws = [probe] + [QuantWeight.from_blob(f"NINT{b}", blob, device=dev) for _ in range(pool - 1)]
+        ws = [probe] + [QuantWeight.from_blob(dtype, blob, device=dev) for _ in range(pool - 1)]
         x = torch.randn((m, k), device=f"cuda:{dev}").to(torch.bfloat16)
         y = torch.empty((m, n), dtype=torch.bfloat16, device=f"cuda:{dev}")
         stream = torch.cuda.Stream(device=dev)
@@ -363,6 +389,60 @@ def sweep(dev: int, peak: float, only: str | None = None, reps: int = 10) -> dic
                      "pool": pool, "device_over_payload": probe.device_bytes / probe.payload_bytes}
         for w in ws:
             w.free()
+    return out
+
+
+def moe_layer_bench(dev: int, peak: float, token_counts=(1, 32, 256), reps: int = 5) -> dict:
+    """BASELINE config 4 on one GPU: hidden 2048, 128 experts, top-8, expert FFN width 768 (SwiGLU),
+    per-expert NINT bits drawn from {2,3,4,6} with seed 4003.  A step = router + expert FFN for T
+    tokens; 16 different (x, logits) inputs are cycled inside one CUDA graph so that successive steps
+    touch different experts (all experts together are ~330 MB, more than L2)."""
+    import torch
+
+    from tyloquant_b200 import encode, moe
+
+    d = f"cuda:{dev}"
+    h, e_count, f, k = 2048, 128, 768, 8
+    bits = np.random.default_rng(4003).choice([2, 3, 4, 6], e_count)
+    gen = torch.Generator(d).manual_seed(4001)
+    wgu = (torch.randn((e_count, 2 * f, h), device=d, generator=gen) * 0.02).to(torch.bfloat16).float()
+    wdn = (torch.randn((e_count, h, f), device=d, generator=gen) * 0.02).to(torch.bfloat16).float()
+    gu = moe.MoeWeight(encode.quantize_expertwise(wgu, bits, device=d), device=dev)
+    dn = moe.MoeWeight(encode.quantize_expertwise(wdn, bits, device=d), device=dev)
+    del wgu, wdn
+    out = {"expert_payload_MB": (gu.info.payload_bytes + dn.info.payload_bytes) / 1e6}
+    nsets = 16
+    for t in token_counts:
+        xs = [torch.randn((t, h), device=d, generator=gen).to(torch.bfloat16) for _ in range(nsets)]
+        zs = [torch.randn((t, e_count), device=d, generator=gen) for _ in range(nsets)]
+        touched = 0
+        for z in zs:
+            ids = torch.topk(z, k, dim=1).indices.unique().tolist()
+            touched += sum(gu.expert_bytes(i) + dn.expert_bytes(i) for i in ids)
+        stream = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(stream):
+            def step():
+                for x, z in zip(xs, zs):
+                    ids, wts = moe.moe_topk(z, k)
+                    moe.moe_ffn(gu, dn, x, ids, wts, out_dtype=torch.bfloat16)
+            step()
+            stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                step()
+            for _ in range(2):
+                g.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(reps):
+                g.replay()
+            e1.record(stream)
+            stream.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (reps * nsets)
+        out[f"T{t}"] = {"us_per_layer_step": us, "tokens_per_s": t / us * 1e6, "distinct_expert_MB_per_step": touched / nsets / 1e6,
+                        "GBps": touched / nsets / us / 1e3, "frac_of_peak": touched / nsets / us / 1e3 / peak}
+    gu.free()
+    dn.free()
     return out
 
 

@@ -41,17 +41,19 @@ def pack_bits(values: np.ndarray, bits: int) -> bytes:
     v = np.ascontiguousarray(values).reshape(-1)
     if bits == 8:
         return v.astype(np.uint8).tobytes()
-    if bits in (1, 2, 4):
-        per = 8 // bits
-        u = v.astype(np.uint8)
-        pad = (-u.size) % per
+    nbytes = (v.size * bits + 7) // 8
+    if bits < 8:
+        # eight values fill exactly `bits` bytes: build them as one little-endian uint64 per octet
+        pad = (-v.size) % 8
+        u = v.astype(np.uint64)
         if pad:
-            u = np.concatenate([u, np.zeros(pad, dtype=np.uint8)])
-        u = u.reshape(-1, per)
-        out = np.zeros(u.shape[0], dtype=np.uint8)
-        for i in range(per):
-            out |= u[:, i] << (bits * i)
-        return out.tobytes()
+            u = np.concatenate([u, np.zeros(pad, dtype=np.uint64)])
+        u = u.reshape(-1, 8)
+        word = np.zeros(u.shape[0], dtype=np.uint64)
+        for i in range(8):
+            word |= u[:, i] << np.uint64(bits * i)
+        out = word.view(np.uint8).reshape(-1, 8)[:, :bits]
+        return np.ascontiguousarray(out).tobytes()[:nbytes]
     out = bytearray()
     step = 1 << 20  # multiple of 8 values, so every chunk ends on a byte boundary
     for s in range(0, v.size, step):
@@ -66,6 +68,24 @@ def _torch():
     return torch
 
 
+def _pack_any(values, bits: int) -> bytes:
+    """pack_bits for numpy arrays or torch tensors (the latter packed on their own device)."""
+    if isinstance(values, np.ndarray) or bits >= 8:
+        return pack_bits(np.asarray(values.cpu()) if not isinstance(values, np.ndarray) else values, bits)
+    torch = _torch()
+    v = values.reshape(-1).to(torch.int64)
+    nbytes = (v.numel() * bits + 7) // 8
+    pad = (-v.numel()) % 8
+    if pad:
+        v = torch.cat([v, torch.zeros(pad, dtype=torch.int64, device=v.device)])
+    v = v.reshape(-1, 8)
+    word = torch.zeros(v.shape[0], dtype=torch.int64, device=v.device)
+    for i in range(8):
+        word |= v[:, i] << (bits * i)
+    out = word.view(torch.uint8).reshape(-1, 8)[:, :bits].contiguous()
+    return out.cpu().numpy().tobytes()[:nbytes]
+
+
 # ---------------------------------------------------------------------------------------
 # NINT
 # ---------------------------------------------------------------------------------------
@@ -73,7 +93,10 @@ def _torch():
 def quantize_nint(weight: np.ndarray, bits: int, gs: int, sub_bits: int, device: str = "cpu") -> dict:
     """Min/max affine groups anchored on per-row f16 scale / min.  ``weight`` is [n, k]."""
     torch = _torch()
-    w = torch.as_tensor(np.ascontiguousarray(weight, dtype=np.float32), device=device)
+    if isinstance(weight, torch.Tensor):
+        w = weight.to(device=device, dtype=torch.float32)
+    else:
+        w = torch.as_tensor(np.ascontiguousarray(weight, dtype=np.float32), device=device)
     n, k = w.shape
     ng = -(-k // gs)
     pad = ng * gs - k
@@ -97,8 +120,7 @@ def quantize_nint(weight: np.ndarray, bits: int, gs: int, sub_bits: int, device:
     return dict(bits=bits, gs=gs, sub_bits=sub_bits, n=n, k=k, ng=ng,
                 neuron_scale=neu_d.cpu().numpy().astype(np.float16),
                 neuron_min=neu_dm.cpu().numpy().astype(np.float16),
-                sub_scale=ss.to(torch.uint8).cpu().numpy(), sub_min=sm.to(torch.uint8).cpu().numpy(),
-                q=q.to(torch.uint8).cpu().numpy())
+                sub_scale=ss.to(torch.uint8), sub_min=sm.to(torch.uint8), q=q.to(torch.uint8))
 
 
 def nint_blob(t: dict) -> bytes:
@@ -107,8 +129,8 @@ def nint_blob(t: dict) -> bytes:
              struct.pack("<I", 2), struct.pack("<2q", t["n"], t["k"]), struct.pack("<II", t["n"], t["ng"]),
              np.ascontiguousarray(t["neuron_scale"], dtype="<f2").tobytes(),
              np.ascontiguousarray(t["neuron_min"], dtype="<f2").tobytes(),
-             pack_bits(t["sub_scale"], t["sub_bits"]), pack_bits(t["sub_min"], t["sub_bits"]),
-             pack_bits(t["q"], t["bits"])]
+             _pack_any(t["sub_scale"], t["sub_bits"]), _pack_any(t["sub_min"], t["sub_bits"]),
+             _pack_any(t["q"], t["bits"])]
     return b"".join(parts)
 
 
@@ -202,6 +224,27 @@ def nvq_blob(t: dict) -> bytes:
     return b"".join(parts)
 
 
+# Packed 256-entry D4 magnitude grid of plain NVQ3 (format constant, see csrc/nvq_d4_256.h):
+# 256 little-endian uint16, four 3-bit digits each, magnitude = 2*digit + 1.
+_D4_256_HEX = (
+    "00000200040009000b000f0010001200190022003b003d004100430048004a005100550058005a0061006c00780080008200840089009000920099009b009f00"
+    "a900af00bd00c100c700c800ca00d500f8000b011f0124012f013b013d01410147015a016a019d01b401c801cc01ce01e301f1010102030208020a0211021302"
+    "18021a021c0227022802400242024902500252028102830288028a0291029802ba02c002c202d002d902e602f60201030503280350035403660379038503d203"
+    "e0030004020409040b041004120416041904220441044304450448044a04510458047304770478048004820489048f04900492049f04a004ad04c104c804cc04"
+    "f804fc041d052b054305570561057c05c105c305ce05e505010608060a0611061306280635063a064006420650065906640666068106830688069506aa06ba06"
+    "c906db06180727073a074007460752076d078c079e07b307db07f00704080f081d081f082b082f087c0890089f08a008b008b608c708e5080409290934095509"
+    "63097809c509c809ca09d8090a0a210a380a400a460a560a6d0a8c0a9a0aba0ac20aeb0a080b130b170b3a0b420b590ba80bd40be20b140c240c260c340c510c"
+    "710c8f0cb40cd80cde0c240d450d6a0d9b0dc30dd10d030e050e070e080e1a0e2a0e560e600e8a0ea50eaa0ec00ecd0edb0ef00e110f210f400f420f540f980f"
+)
+
+
+def d4_256_codebook() -> np.ndarray:
+    """The built-in 256-entry D4 grid of plain NVQ3 as int8 [256, 4] (odd magnitudes 1..15)."""
+    enc = np.frombuffer(bytes.fromhex(_D4_256_HEX), dtype="<u2")
+    digits = (enc[:, None] >> (3 * np.arange(4, dtype=np.uint16))[None, :]) & 7
+    return np.ascontiguousarray(2 * digits + 1, dtype=np.int8)
+
+
 def synthetic_d4_banks(entries: int, banks: int, seed: int) -> np.ndarray:
     """Seeded stand-in for the learned NVQ-JSC banks: ``entries`` distinct rows of odd
     magnitudes 1..15 per bank.  (Real files carry their banks inside the blob.)"""
@@ -237,7 +280,7 @@ def quantize_expertwise(weight: np.ndarray, bits_per_expert, device: str = "cpu"
     pools = []
     for b, ids in cohorts.items():
         bits, gs, sb = CANONICAL_NINT[b]
-        rows = np.ascontiguousarray(weight[ids]).reshape(len(ids) * out, k)
+        rows = weight[ids].reshape(len(ids) * out, k)   # numpy array or torch tensor
         pools.append((ids, f"NINT{bits}", nint_blob(quantize_nint(rows, bits, gs, sb, device=device))))
     return nintm_blob(e_count, out, k, pools)
 
