@@ -220,6 +220,30 @@ int mfqb_moe_ffn(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* down, co
                  const int32_t* ids, const float* weights, int tokens, int routes, void* y, int y_dtype,
                  mfqb_stream_t stream);
 
+/* ---------------------------------------------------------------------------------
+ * Tensor- / expert-parallel reduction.  Replaces reduce_tensor_parallel_outputs
+ * (cpp_runtime/mfq_decode.cpp:9009-9114: float32 ncclAllReduce, or copy-to-primary and add)
+ * for the decode-sized vectors of row-parallel linears and expert-parallel FFN partials:
+ * a one-shot all-reduce over NVLink peer memory -- every rank stores its vector into every
+ * peer, raises a flag, waits (bounded) for the peers' flags and adds the slots in rank order,
+ * so all ranks end with bit-identical sums.  One process per GPU; the per-rank buffers are
+ * shared with CUDA IPC handles that the caller exchanges (64 bytes each).
+ *
+ *   create -> handle (send to every peer) -> attach(peer, its handle) for every other rank
+ *   -> allreduce ... -> destroy.   All ranks must issue the same sequence of allreduce calls
+ * with the same n.  A wait that passes its deadline (default 2 s) sets the status word to
+ * MFQB_ERR_TIMEOUT and lets the kernel return; mfqb_comm_status reads it without
+ * synchronising.  max_elems <= 262144 floats, world <= 8.
+ * --------------------------------------------------------------------------------- */
+typedef struct mfqb_comm mfqb_comm;
+int mfqb_comm_create(int rank, int world, uint64_t max_elems, int device, mfqb_comm** out);
+int mfqb_comm_handle(const mfqb_comm* c, void* handle64);
+int mfqb_comm_attach(mfqb_comm* c, int peer, const void* handle64);
+int mfqb_comm_set_timeout_ms(mfqb_comm* c, int ms);
+int mfqb_allreduce_f32(mfqb_comm* c, const float* in, float* out, uint64_t n, mfqb_stream_t stream);
+int mfqb_comm_status(const mfqb_comm* c, int* status);
+int mfqb_comm_destroy(mfqb_comm* c);
+
 /* Expert FFN that allocates nothing.  (No counterpart in the reference runtime, whose FFN takes
  * its workspaces from the libtorch caching allocator.)
  *

@@ -1,0 +1,107 @@
+"""Multi-GPU: one-shot NVLink all-reduce and the expert-parallel FFN, as child processes on two
+GPUs (skipped on a single-GPU box).  Failures are made on the host: a rank that does not join
+makes the peer's bounded wait run out, which must surface as a status, not a hang."""
+
+import os
+import socket
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, q):
+    import torch
+    import torch.distributed as dist
+
+    from oracle import mfq_oracle as O
+    from tyloquant_b200 import _capi, comm, encode, moe
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    res = {}
+    try:
+        c = comm.Communicator(rank, world, 1 << 16, rank).connect()
+        # 1. sums, identical on every rank, several sizes back to back
+        for n in (1, 2048, 5000, 1 << 16):
+            g = torch.Generator("cuda").manual_seed(100 + rank)
+            x = torch.randn(n, device="cuda", generator=g)
+            y = c.allreduce(x)
+            xs = [torch.empty(n) for _ in range(world)]
+            dist.all_gather(xs, x.cpu())
+            want = sum(xs[1:], xs[0].clone())          # rank order, like the kernel
+            res[f"sum{n}"] = bool(torch.equal(y.cpu(), want))
+            ys = [torch.empty(n) for _ in range(world)]
+            dist.all_gather(ys, y.cpu())
+            res[f"same{n}"] = all(torch.equal(ys[0], t) for t in ys)
+        torch.cuda.synchronize()
+        res["status_ok"] = c.status() == 0
+
+        # 2. expert-parallel FFN: each rank holds an expert range, partial outputs are all-reduced
+        e_count, h, f, k, tokens = 16, 256, 96, 4, 5
+        bits = np.random.default_rng(1).choice([2, 3, 4, 6], e_count)
+        rng = np.random.default_rng(2)
+        wgu = encode.bf16_round(rng.standard_normal((e_count, 2 * f, h), dtype=np.float32) * np.float32(0.02))
+        wdn = encode.bf16_round(rng.standard_normal((e_count, h, f), dtype=np.float32) * np.float32(0.02))
+        gu_blob, dn_blob = encode.quantize_expertwise(wgu, bits), encode.quantize_expertwise(wdn, bits)
+        b, e = comm.shard_range(e_count, rank, world, 128)
+        gu, dn = moe.MoeWeight(gu_blob, rank, b, e), moe.MoeWeight(dn_blob, rank, b, e)
+        x = encode.bf16_round(rng.standard_normal((tokens, h), dtype=np.float32))
+        z = rng.standard_normal((tokens, e_count)).astype(np.float32)
+        ids, wts = moe.moe_topk(torch.from_numpy(z).cuda(), k)
+        part = moe.moe_ffn(gu, dn, torch.from_numpy(x).cuda().to(torch.bfloat16), ids, wts)
+        y = c.allreduce(part.reshape(-1)).reshape(tokens, h).cpu().numpy()
+        rid, rw = O.moe_topk(z, k)
+        y_ref = O.moe_ffn(x, O.dequant_nintm(O.unpack_nintm(gu_blob)), O.dequant_nintm(O.unpack_nintm(dn_blob)), rid, rw)
+        res["ep_err"] = float(np.linalg.norm(y - y_ref) / np.linalg.norm(y_ref))
+
+        # 3. a rank that does not join: the other rank's wait runs out and reports it
+        dist.barrier()
+        c.set_timeout_ms(200)
+        if rank == 0:
+            c.allreduce(torch.ones(64, device="cuda"))
+            torch.cuda.synchronize()
+            res["timeout_status"] = c.status()
+            res["context_alive"] = bool((torch.ones(4, device="cuda") * 2).sum().item() == 8.0)
+        dist.barrier()
+        c.close()
+    finally:
+        q.put((rank, res))
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_allreduce_expert_parallel_and_timeout_on_two_gpus():
+    import torch.multiprocessing as mp
+    from tyloquant_b200 import _capi
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=300) for _ in range(world))
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for rank in range(world):
+        r = results[rank]
+        for n in (1, 2048, 5000, 1 << 16):
+            assert r[f"sum{n}"] and r[f"same{n}"], (rank, n)
+        assert r["status_ok"]
+        assert r["ep_err"] <= 4e-3
+    assert results[0]["timeout_status"] == _capi.ERR_TIMEOUT
+    assert results[0]["context_alive"]

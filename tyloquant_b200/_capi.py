@@ -81,6 +81,13 @@ _SIGNATURES = {
     "mfqb_moe_swiglu": (_i, [_vp, _i, _i, _i, _vp, _vp]),
     "mfqb_moe_weighted_reduce": (_i, [_vp, _i, _vp, _i, _i, _i, _vp, _i, _vp]),
     "mfqb_moe_ffn": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _i, _vp]),
+    "mfqb_comm_create": (_i, [_i, _i, _u64, _i, _P(_vp)]),
+    "mfqb_comm_handle": (_i, [_vp, _vp]),
+    "mfqb_comm_attach": (_i, [_vp, _i, _vp]),
+    "mfqb_comm_set_timeout_ms": (_i, [_vp, _i]),
+    "mfqb_allreduce_f32": (_i, [_vp, _vp, _vp, _u64, _vp]),
+    "mfqb_comm_status": (_i, [_vp, _P(_i)]),
+    "mfqb_comm_destroy": (_i, [_vp]),
     "mfqb_moe_ffn_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _i, _vp]),
 }
 

@@ -39,6 +39,15 @@ __device__ __forceinline__ void mma_k8(float (&d)[4], uint32_t a0, uint32_t a1, 
         : "r"(a0), "r"(a1), "r"(b0));
 }
 
+// First step of an accumulation chain: D = A*B + 0 (no accumulator registers to clear).
+__device__ __forceinline__ void mma_k16_first(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+
 constexpr uint32_t kBf16x2_128 = 0x43004300u;  // (128.0, 128.0)
 
 __device__ __forceinline__ uint32_t bf162_sub128(uint32_t v) {

@@ -8,8 +8,8 @@
 // owns groups 2c, 2c+1 of rows q, q+8, so nothing is decoded twice -- and a quad reduction
 // adds the eight groups.  Every mma handles pair j of group g (slots 2c, 2c+1) and of group
 // g+4 (slots 2c+8, 2c+9), which the lane-stream layout already provides.
-// The group sums of x (for the -128 seed and the sub-min term) come out of the same
-// tensor-core pattern with A = 1.
+// The group sums of x (for the -128 seed and the sub-min term) are computed once per CTA into a
+// shared-memory table while x is staged.
 #pragma once
 #include "nint_gemv.cuh"
 
@@ -49,7 +49,8 @@ __global__ void __launch_bounds__(256, 3) nint_gemv_m1_kernel(const GemvArgs a) 
     float* ypart = reinterpret_cast<float*>(smem);
     uint32_t* anch = reinterpret_cast<uint32_t*>(ypart + (size_t)a.rb_per_cta * 16);
     __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(anch + (size_t)a.rb_per_cta * 16);
-    uint32_t* ring = reinterpret_cast<uint32_t*>(xs + a.xstride) + (size_t)warp * S * REC;
+    float* xsum_tab = reinterpret_cast<float*>(xs + a.xstride);            // [nchunks * 8] group sums of x
+    uint32_t* ring = reinterpret_cast<uint32_t*>(xsum_tab + w.nchunks * G) + (size_t)warp * S * REC;
     // balanced split of the row-blocks over gridDim.x: CTA b owns [b*R/grid, (b+1)*R/grid) of the
     // R row-blocks of the whole matrix, or of its pair's expert in routed mode
     int rb_base = 0, rb_total = w.nrb;
@@ -110,8 +111,18 @@ __global__ void __launch_bounds__(256, 3) nint_gemv_m1_kernel(const GemvArgs a) 
         }
     }
     __syncthreads();
-
     const uint32_t* xw = reinterpret_cast<const uint32_t*>(xs);
+    // group sums of x, once per CTA: seed of the accumulators (-128 * sum) and the sub-min term
+    for (int g = tid; g < w.nchunks * G; g += blockDim.x) {
+        float s = 0.f;
+        const uint32_t* p = xw + (g * w.gs) / 2;
+        for (int e = 0; e < w.gs / 2; ++e) {
+            const uint32_t v = p[e];
+            s += __uint_as_float(v << 16) + __uint_as_float(v & 0xFFFF0000u);
+        }
+        xsum_tab[g] = s;
+    }
+    __syncthreads();
     int cur_seg = -1;
     uint32_t b0[4][HALF], b1[4][HALF];   // block-diagonal B: non-zero only where the lane's column is the mma's group
     float xs0 = 0.f, xs1 = 0.f;          // group sums of x for groups 2c, 2c+1 of the chunk
@@ -125,18 +136,17 @@ __global__ void __launch_bounds__(256, 3) nint_gemv_m1_kernel(const GemvArgs a) 
             xq[j] = 0u;
             if (c * PER + 2 * j < w.gs) xq[j] = xw[((seg * G + q) * w.gs + c * PER) / 2 + j];
         }
-        float s[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
 #pragma unroll
             for (int j = 0; j < HALF; ++j) {
                 b0[g][j] = q == g ? xq[j] : 0u;
                 b1[g][j] = q == g + 4 ? xq[j] : 0u;
-                mma_k16(s, kBf16x2_one, kBf16x2_one, kBf16x2_one, kBf16x2_one, b0[g][j], b1[g][j]);
             }
         }
-        xs0 = s[0];
-        xs1 = s[1];
+        const float2 sums = *reinterpret_cast<const float2*>(xsum_tab + seg * G + 2 * c);
+        xs0 = sums.x;
+        xs1 = sums.y;
     };
 
     int seg = warp, rbl = 0, stage = 0;
@@ -154,8 +164,7 @@ __global__ void __launch_bounds__(256, 3) nint_gemv_m1_kernel(const GemvArgs a) 
         issue();
 
         const float seed0 = (NPL == 2 ? -128.f * 17.f : -128.f) * xs0, seed1 = (NPL == 2 ? -128.f * 17.f : -128.f) * xs1;
-        float ch[4][4] = {{seed0, seed1, seed0, seed1}, {0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-        float hi[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};   // high nibbles (8-bit codes)
+        float ch[4][4], hi[2][4];   // chains; hi = high nibbles (8-bit codes); seeds are added at the end
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
 #pragma unroll
@@ -163,7 +172,14 @@ __global__ void __launch_bounds__(256, 3) nint_gemv_m1_kernel(const GemvArgs a) 
                 const uint32_t r0 = QU::at(qw, (g * 2 + 0) * HALF + j), r1 = QU::at(qw, (g * 2 + 1) * HALF + j);
                 const uint32_t r2 = QU::at(qw, ((g + 4) * 2 + 0) * HALF + j), r3 = QU::at(qw, ((g + 4) * 2 + 1) * HALF + j);
                 if constexpr (NPL == 1) {
-                    mma_k16(ch[g], r0 | kBf16x2_128, r1 | kBf16x2_128, r2 | kBf16x2_128, r3 | kBf16x2_128, b0[g][j], b1[g][j]);
+                    if (j == 0) mma_k16_first(ch[g], r0 | kBf16x2_128, r1 | kBf16x2_128, r2 | kBf16x2_128, r3 | kBf16x2_128, b0[g][j], b1[g][j]);
+                    else mma_k16(ch[g], r0 | kBf16x2_128, r1 | kBf16x2_128, r2 | kBf16x2_128, r3 | kBf16x2_128, b0[g][j], b1[g][j]);
+                } else if (g < 2 && j == 0) {
+                    constexpr uint32_t NIB = 0x000F000Fu;
+                    mma_k16_first(ch[g & 1], (r0 & NIB) | kBf16x2_128, (r1 & NIB) | kBf16x2_128, (r2 & NIB) | kBf16x2_128,
+                                  (r3 & NIB) | kBf16x2_128, b0[g][j], b1[g][j]);
+                    mma_k16_first(hi[g & 1], ((r0 >> 4) & NIB) | kBf16x2_128, ((r1 >> 4) & NIB) | kBf16x2_128,
+                                  ((r2 >> 4) & NIB) | kBf16x2_128, ((r3 >> 4) & NIB) | kBf16x2_128, b0[g][j], b1[g][j]);
                 } else {
                     constexpr uint32_t NIB = 0x000F000Fu;
                     mma_k16(ch[g & 1], (r0 & NIB) | kBf16x2_128, (r1 & NIB) | kBf16x2_128, (r2 & NIB) | kBf16x2_128,
@@ -176,8 +192,9 @@ __global__ void __launch_bounds__(256, 3) nint_gemv_m1_kernel(const GemvArgs a) 
         float acc[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            if constexpr (NPL == 1) acc[e] = (ch[0][e] + ch[1][e]) + (ch[2][e] + ch[3][e]);
-            else acc[e] = fmaf(16.f, hi[0][e] + hi[1][e], ch[0][e] + ch[1][e]);
+            const float seed = (e & 1) ? seed1 : seed0;
+            if constexpr (NPL == 1) acc[e] = ((ch[0][e] + ch[1][e]) + (ch[2][e] + ch[3][e])) + seed;
+            else acc[e] = fmaf(16.f, hi[0][e] + hi[1][e], ch[0][e] + ch[1][e]) + seed;
         }
         // sub-scales / sub-mins of rows (q, q+8) x groups (2c, 2c+1)
         uint32_t sp0, sp1, mp_lo, mp_hi;

@@ -48,7 +48,8 @@ GemvPlan plan_nint_gemv(const NintDev& w, int m, int num_sms) {
         // three CTAs per SM, all resident at once; row-blocks are split evenly inside the kernel
         p.grid = std::min(w.nrb, 3 * num_sms);
         p.rb_per_cta = (w.nrb + p.grid - 1) / p.grid;
-        p.smem = (size_t)p.rb_per_cta * 16 * 8 + (size_t)p.xstride * 2 + (size_t)warps * p.stages * rec_bytes;
+        p.smem = (size_t)p.rb_per_cta * 16 * 8 + (size_t)p.xstride * 2 + (size_t)w.nchunks * kChunkGroups * 4 +
+                 (size_t)warps * p.stages * rec_bytes;
         return p;
     }
     const size_t fixed = (size_t)p.rb_per_cta * 128 * 4 + (size_t)warps * 64 * 4;
@@ -171,7 +172,8 @@ void launch_nint_gemv_routed(GemvArgs a, int pairs, int device, cudaStream_t s) 
     const int want = (3 * device_sm_count(device) + pairs - 1) / std::max(pairs, 1);
     const int splits = std::max(1, std::min(a.rb_per_expert, want));
     p.rb_per_cta = (a.rb_per_expert + splits - 1) / splits;
-    p.smem = (size_t)p.rb_per_cta * 16 * 8 + (size_t)p.xstride * 2 + (size_t)8 * p.stages * w.rec_words * 4;
+    p.smem = (size_t)p.rb_per_cta * 16 * 8 + (size_t)p.xstride * 2 + (size_t)w.nchunks * kChunkGroups * 4 +
+             (size_t)8 * p.stages * w.rec_words * 4;
     a.rb_per_cta = p.rb_per_cta;
     a.xstride = p.xstride;
     a.stages = p.stages;
