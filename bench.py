@@ -298,7 +298,10 @@ def main() -> None:
         "roofline": {"bound": "hbm", "kernel": "nint_gemv_kernel<3,6,5>", "achieved": achieved, "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": f"{peak_kind} copy bandwidth",
                      "us_per_launch": launch_us, "algorithmic_bytes_per_launch": algorithmic_bytes(payload, 1, N_ROWS, N_COLS),
-                     "device_bytes_per_launch": weights[0].device_bytes, "traffic": None},
+                     "device_bytes_per_launch": weights[0].device_bytes,
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch, ncu --set full capture
+                     # summarised in profiles/nint_gemv_m1_nint3_4096x4096.md
+                     "traffic": 7434496},
     })
     if args.gpus == 1:
         cb, _ = cpu_reference_arm(3, 3, budget_s=12.0)
