@@ -114,6 +114,11 @@ int mfqb_dequant(const mfqb_weight* w, void* out, int out_dtype, mfqb_stream_t s
 int mfqb_mul_mat(const mfqb_weight* w, const void* x_bf16, int m, void* y, int y_dtype,
                  mfqb_stream_t stream);
 
+/* Status word of the device-side bounded waits of the tile kernel on `device`: 0, or
+ * MFQB_ERR_TIMEOUT when a wait inside a kernel ran out (the kernel then returned early and
+ * its output is not valid).  Reads a host-mapped word; does not synchronise. */
+int mfqb_device_status(int device, int* status);
+
 /* Same product with host buffers: copies x to the device, runs, copies y back and
  * waits.  (The reference runtime keeps activations on the device; this entry point is
  * what a host-side caller such as the numpy runtime mfq/runtime/linear.py:37-42 uses.) */

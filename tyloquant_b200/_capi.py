@@ -65,6 +65,7 @@ _SIGNATURES = {
     "mfqb_weight_free": (_i, [_vp]),
     "mfqb_dequant": (_i, [_vp, _vp, _i, _vp]),
     "mfqb_mul_mat": (_i, [_vp, _vp, _i, _vp, _i, _vp]),
+    "mfqb_device_status": (_i, [_i, _P(_i)]),
     "mfqb_mul_mat_host": (_i, [_vp, _vp, _i, _vp, _i]),
     "mfqb_tp_plan": (_i, [_i64, _i64, _i, _P(C.c_double), _P(_i64), _P(_i64)]),
     "mfqb_tp_validate": (_i, [_i64, _i64, _i, _P(_i64), _P(_i64)]),

@@ -6,6 +6,7 @@
 #include <mutex>
 
 #include "cuda_util.h"
+#include "nint_gemm_tc.cuh"
 #include "nint_gemv_m1.cuh"
 #include "nvq.h"
 
@@ -192,6 +193,76 @@ void launch_nint_gemv_routed(GemvArgs a, int pairs, int device, cudaStream_t s) 
     if (e != cudaSuccess) fail(MFQB_ERR_CUDA, "NINT%d routed GEMV launch: %s", w.bits, cudaGetErrorString(e));
 }
 
+// ---- tcgen05 prefill GEMM: x conversion pre-pass, per-device scratch and status word -----------
+__global__ void x_to_f16_kernel(const __nv_bfloat16* __restrict__ x, int m, int k, int kx, __half* __restrict__ out) {
+    const size_t total = (size_t)m * kx;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / kx, c = i % kx;
+        // bf16 -> f16: exact for |x| in [2^-14, 65504]; larger magnitudes saturate to +-65504
+        float v = c < (size_t)k ? __bfloat162float(x[r * k + c]) : 0.f;
+        v = fminf(fmaxf(v, -65504.f), 65504.f);
+        out[i] = __float2half_rn(v);
+    }
+}
+
+struct GemmDeviceState {
+    std::mutex mu;
+    DevBuf x16[64];
+    int* status_host[64] = {nullptr};
+    int* status_dev[64] = {nullptr};
+};
+static GemmDeviceState g_gemm;
+
+static int* gemm_status_word(int device) {   // pinned, mapped: the host can read it without a sync
+    if (!g_gemm.status_host[device]) {
+        MFQB_CUDA(cudaHostAlloc((void**)&g_gemm.status_host[device], sizeof(int), cudaHostAllocMapped));
+        *g_gemm.status_host[device] = 0;
+        MFQB_CUDA(cudaHostGetDevicePointer((void**)&g_gemm.status_dev[device], g_gemm.status_host[device], 0));
+    }
+    return g_gemm.status_dev[device];
+}
+
+// Returns false when this weight has no tensor-core tile kernel (the caller falls back to GEMV passes).
+static bool launch_nint_gemm(const NintDev& w, const void* x, int m, void* y, int y_dtype, int device, cudaStream_t s) {
+    const GemmPlan p = plan_nint_gemm(w, m);
+    if (p.bn == 0 || w.sw == 8) return false;
+    std::lock_guard<std::mutex> lock(g_gemm.mu);
+    GemmArgs a{};
+    a.w = w;
+    a.m = m;
+    a.kx = (w.k + 7) / 8 * 8;
+    a.y = y;
+    a.y_dtype = y_dtype;
+    a.bn = p.bn;
+    a.error = gemm_status_word(device);
+    DevBuf& xb = g_gemm.x16[device];
+    const size_t need = (size_t)m * a.kx * sizeof(__half);
+    if (xb.bytes < need) xb.alloc(need + need / 2);
+    a.x16 = static_cast<const __half*>(xb.p);
+    const size_t total = (size_t)m * a.kx;
+    x_to_f16_kernel<<<(int)std::min<size_t>((total + 255) / 256, 148 * 8), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), m, w.k,
+                                                                                      a.kx, static_cast<__half*>(xb.p));
+    MFQB_CUDA(cudaGetLastError());
+    cudaError_t e;
+    switch (w.bits) {
+        case 2: e = launch_nint_gemm_bits<2>(a, p, s); break;
+        case 3: e = launch_nint_gemm_bits<3>(a, p, s); break;
+        case 4: e = launch_nint_gemm_bits<4>(a, p, s); break;
+        case 5: e = launch_nint_gemm_bits<5>(a, p, s); break;
+        case 6: e = launch_nint_gemm_bits<6>(a, p, s); break;
+        case 8: e = launch_nint_gemm_bits<8>(a, p, s); break;
+        default: return false;
+    }
+    if (e == cudaErrorNotSupported) return false;
+    if (e != cudaSuccess) fail(MFQB_ERR_CUDA, "NINT%d gs=%d GEMM launch: %s", w.bits, w.gs, cudaGetErrorString(e));
+    return true;
+}
+
+int gemm_device_status(int device) {
+    std::lock_guard<std::mutex> lock(g_gemm.mu);
+    return g_gemm.status_host[device] ? *static_cast<volatile int*>(g_gemm.status_host[device]) : 0;
+}
+
 void launch_nint_dequant_view(const NintDev& w, void* out, int out_dtype, cudaStream_t s) { launch_nint_dequant(w, out, out_dtype, s); }
 
 }  // namespace mfqb
@@ -316,6 +387,8 @@ int mfqb_mul_mat(const mfqb_weight* w, const void* x, int m, void* y, int y_dtyp
         const int64_t n = w->info.n, k = w->info.k;
         const size_t ysz = y_dtype == MFQB_F32 ? 4 : 2;
         if (w->family == MFQB_FAMILY_NINT) {
+            // more than 16 rows: tensor-core tile kernel (x conversion buffer is library scratch)
+            if (m > 16 && launch_nint_gemm(w->nint, x, m, y, y_dtype, w->device, stream)) return;
             const int mb = nint_gemv_max_batch(w->nint, w->device);
             if (mb == 0) fail(MFQB_ERR_UNSUPPORTED, "k=%lld is too long for the shared-memory staging of the GEMV", (long long)k);
             for (int m0 = 0; m0 < m; m0 += mb) {
@@ -344,6 +417,13 @@ int mfqb_mul_mat_host(const mfqb_weight* w, const void* x_host, int m, void* y_h
         if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
         MFQB_CUDA(cudaMemcpyAsync(y_host, dy.p, yb, cudaMemcpyDeviceToHost, s));
         MFQB_CUDA(cudaStreamSynchronize(s));
+    });
+}
+
+int mfqb_device_status(int device, int* status) {
+    return guarded([&] {
+        if (!status || device < 0 || device >= 64) fail(MFQB_ERR_ARG, "mfqb_device_status: bad argument");
+        *status = gemm_device_status(device);
     });
 }
 
