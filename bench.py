@@ -163,6 +163,10 @@ def main() -> None:
             "data": "synthetic", "config": {"workload": WORKLOAD, "pool": POOL, "l2_policy": "inputs larger than L2 "
                                             f"({POOL} x 7.2 MB weights per step)", "parallelism": f"replicas x{args.gpus}"}}
 
+    if args.only == "gemm":
+        pk = measured_peaks()[0]
+        print(json.dumps(gemm_bench(local_rank, pk.get("bf16_tflops_sustained", pk["bf16_tflops"]))))
+        return
     if args.only:
         print(json.dumps(sweep(local_rank, measured_peaks()[0]["hbm_gbs"], only=args.only, reps=args.reps)))
         return
@@ -309,6 +313,7 @@ def main() -> None:
         if not args.no_sweep:
             line["sweep"] = sweep(dev, peaks["hbm_gbs"])
             line["moe_layer_cfg4"] = moe_layer_bench(dev, peaks["hbm_gbs"])
+            line["gemm_cfg2"] = gemm_bench(dev, peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]))
     print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
@@ -392,6 +397,34 @@ def sweep(dev: int, peak: float, only: str | None = None, reps: int = 10) -> dic
                      "pool": pool, "device_over_payload": probe.device_bytes / probe.payload_bytes}
         for w in ws:
             w.free()
+    return out
+
+
+def gemm_bench(dev: int, peak_tflops: float, reps: int = 5) -> dict:
+    """BASELINE config 2: M = 512 tokens, N = 14336, K = 4096, NINT4 (4,32,6) and NINT8 (8,32,7):
+    TFLOP/s of mfqb_mul_mat (x conversion pre-pass + tcgen05 tile kernel) against the dense bf16 peak."""
+    import torch
+
+    from tyloquant_b200 import QuantWeight, encode
+
+    d = f"cuda:{dev}"
+    m, n, k = 512, 14336, 4096
+    out = {}
+    for name, (b, gs, sb) in (("NINT4_gs32", (4, 32, 6)), ("NINT8_gs32", (8, 32, 7)), ("NINT4_gs24", (4, 24, 6))):
+        w = QuantWeight.from_blob(f"NINT{b}", encode.random_nint_blob(n, k, b, gs, sb, seed=2001, device=d), device=dev)
+        x = torch.randn((m, k), device=d).to(torch.bfloat16)
+        for _ in range(3):
+            y = w.matmul(x)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            y = w.matmul(x)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        ms = e0.elapsed_time(e1) / reps
+        tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+        out[name] = {"ms": ms, "TFLOPs": tf, "frac_of_bf16_peak": tf / peak_tflops, "weight_payload_MB": w.payload_bytes / 1e6}
+        w.free()
     return out
 
 
