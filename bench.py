@@ -109,6 +109,13 @@ def cpu_reference_arm(steps: int, warmup: int, budget_s: float = 20.0):
     from oracle import mfq_oracle as O
     from tyloquant_b200 import encode
 
+    try:   # torchrun exports OMP_NUM_THREADS=1: the reference arm may use every host core
+        import torch
+        torch.set_num_threads(os.cpu_count() or 1)
+        from threadpoolctl import threadpool_limits
+        threadpool_limits(limits=os.cpu_count() or 1)
+    except Exception:
+        pass
     bits, gs, sb = PROFILE
     blob = encode.random_nint_blob(N_ROWS, N_COLS, bits, gs, sb, seed=1001)
     t0 = time.perf_counter()

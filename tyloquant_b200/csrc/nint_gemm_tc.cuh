@@ -17,7 +17,11 @@
 // Replaces mmq_f16_packed_kernel and the dequantise-then-cuBLAS path
 // (mfq/kernels/cuda/nint_matmul.cu:8138-8372, 303-333).
 #pragma once
+#include <cuda.h>
 #include <cuda_fp16.h>
+
+#include <algorithm>
+#include <type_traits>
 
 #include "nint_gemv_m1.cuh"
 #include "tc05.cuh"
@@ -31,28 +35,31 @@ struct GemmArgs {
     void* y;             // [m, n]
     int y_dtype;
     int bn;              // tokens per tile: 64, 128 or 256
+    int stages;          // ring depth in 64-column atoms
     int* error;          // device word: set to MFQB_ERR_TIMEOUT when a wait expires
 };
 
-constexpr int kGemmThreads = 288;   // 8 producer warps + 1 mma warp
+constexpr int kGemmProducerWarps = 16;
+constexpr int kGemmThreads = (kGemmProducerWarps + 2) * 32;   // + mma warp + x loader warp
 
+// The ring is counted in atoms: one stage = 64 columns of K = a 128 x 64 f16 slab of W (16 KB) and
+// a BN x 64 f16 slab of x, each a K-major tile with the 128-byte swizzle.  A chunk of 8 groups is
+// ATOMS consecutive stages.  Two producer warps share one row-block record (groups 0-3 / 4-7).
 template <int BITS, int PER, int SW>
-__global__ void __launch_bounds__(kGemmThreads, 1) nint_gemm_tc_kernel(const GemmArgs a) {
+__global__ void __launch_bounds__(kGemmThreads, 1) nint_gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x_map) {
     constexpr int G = kChunkGroups, HALF = PER / 2, GS = 4 * PER, KST = G * GS, ATOMS = KST / 64;
     static_assert(KST % 64 == 0, "a chunk must be whole 64-element swizzle atoms");
     using QU = PairUnit<BITS>;
     using SU = PairUnit<SW>;
     constexpr int WC = QU::words_for(G * PER), SWC = SU::words_for(16), REC = WC * 32 + SWC * 8;
+    constexpr int NPROD = kGemmProducerWarps * 32;
     const NintDev& w = a.w;
-    const int BN = a.bn;
+    const int BN = a.bn, NS = a.stages;
 
     extern __shared__ unsigned char smem_raw[];
-    // 1024-byte aligned tile area
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    const int a_stage_bytes = ATOMS * 128 * 128, b_stage_bytes = ATOMS * BN * 128;
-    unsigned char* a_tile[2] = {tiles, tiles + a_stage_bytes};
-    unsigned char* b_tile[2] = {tiles + 2 * a_stage_bytes, tiles + 2 * a_stage_bytes + b_stage_bytes};
-    __shared__ __align__(8) uint64_t full_bar[2], empty_bar[2], done_bar;
+    const int stage_bytes = 128 * 128 + BN * 128;   // A atom then B atom
+    __shared__ __align__(8) uint64_t full_bar[8], empty_bar[8], done_bar;
     __shared__ uint32_t tmem_base_slot;
     __shared__ int failed;
 
@@ -61,116 +68,151 @@ __global__ void __launch_bounds__(kGemmThreads, 1) nint_gemm_tc_kernel(const Gem
     const int row0 = blockIdx.x * 128, tok0 = blockIdx.y * BN;
 
     if (tid == 0) {
-        mbar_init(&full_bar[0], 256);
-        mbar_init(&full_bar[1], 256);
-        mbar_init(&empty_bar[0], 1);
-        mbar_init(&empty_bar[1], 1);
+        for (int i = 0; i < 8; ++i) {
+            mbar_init(&full_bar[i], NPROD + 1);   // producers + the x loader's expect_tx arrival
+            mbar_init(&empty_bar[i], 1);
+        }
         mbar_init(&done_bar, 1);
         failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 8) tmem_alloc(&tmem_base_slot, (uint32_t)BN);
+    if (warp == kGemmProducerWarps) tmem_alloc(&tmem_base_slot, (uint32_t)BN);
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_d = tmem_base_slot;
 
-    if (warp < 8) {
+    if (warp < kGemmProducerWarps) {
         // ------------------------------ producers ------------------------------
-        const int rb = blockIdx.x * 8 + warp;            // row-block of w this warp dequantises
+        const int rbl = warp >> 1, half = warp & 1;      // row-block of the tile, group half of the chunk
+        const int rb = blockIdx.x * 8 + rbl;
         const bool rb_valid = rb < w.nrb;
-        for (int ch = 0; ch < w.nchunks; ++ch) {
-            const int st = ch & 1, use = ch >> 1;
-            if (use > 0 && !mbar_wait(&empty_bar[st], (use - 1) & 1)) { failed = 1; break; }
-            // x slice: BN rows x KST columns, 16-byte chunks, swizzled
-            unsigned char* bt = b_tile[st];
-            const int chunks_per_row = KST / 8;
-            for (int i = tid; i < BN * chunks_per_row; i += 256) {
-                const int t = i / chunks_per_row, c16 = i % chunks_per_row;
-                const int atom = c16 >> 3, in_atom = c16 & 7;
-                unsigned char* dst = bt + atom * (BN * 128) + t * 128 + ((in_atom ^ (t & 7)) << 4);
-                const int k0 = ch * KST + c16 * 8, tok = tok0 + t;
-                if (tok < a.m && k0 < a.kx) cp_async16(dst, a.x16 + (size_t)tok * a.kx + k0);
-                else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+        bool alive = true;
+        uint32_t nq[WC], ns_[SWC];
+        if (rb_valid) {
+            const uint32_t* rec = w.items + (size_t)rb * w.nchunks * REC;
+#pragma unroll
+            for (int j = 0; j < WC; ++j) nq[j] = __ldg(rec + j * 32 + lane);
+#pragma unroll
+            for (int j = 0; j < SWC; ++j) ns_[j] = __ldg(rec + WC * 32 + j * 8 + q);
+        }
+        for (int ch = 0; ch < w.nchunks && alive; ++ch) {
+            // acquire the chunk's stages
+#pragma unroll
+            for (int j = 0; j < ATOMS; ++j) {
+                const int ai = ch * ATOMS + j, st = ai % NS, use = ai / NS;
+                if (use > 0 && !mbar_wait(&empty_bar[st], (use - 1) & 1)) { failed = 1; alive = false; }
             }
-            cp_async_commit();
-            // weight record -> f16 rows of the A tile
-            unsigned char* at = a_tile[st];
+            if (!alive) break;
+            // weight record -> f16 rows of the A atoms (this warp: 16 rows x 4 groups)
             if (rb_valid) {
-                const uint32_t* rec = w.items + ((size_t)rb * w.nchunks + ch) * REC;
                 uint32_t qw[WC], sw[SWC];
 #pragma unroll
-                for (int j = 0; j < WC; ++j) qw[j] = __ldg(rec + j * 32 + lane);
+                for (int j = 0; j < WC; ++j) qw[j] = nq[j];
 #pragma unroll
-                for (int j = 0; j < SWC; ++j) sw[j] = __ldg(rec + WC * 32 + j * 8 + q);
+                for (int j = 0; j < SWC; ++j) sw[j] = ns_[j];
+                if (ch + 1 < w.nchunks) {   // next record's words are requested before this one is decoded
+                    const uint32_t* rec = w.items + ((size_t)rb * w.nchunks + ch + 1) * REC;
+#pragma unroll
+                    for (int j = 0; j < WC; ++j) nq[j] = __ldg(rec + j * 32 + lane);
+#pragma unroll
+                    for (int j = 0; j < SWC; ++j) ns_[j] = __ldg(rec + WC * 32 + j * 8 + q);
+                }
                 const uint32_t an_lo = __ldg(w.anchors + rb * 16 + q), an_hi = __ldg(w.anchors + rb * 16 + 8 + q);
                 const float2 f_lo = __half22float2(*reinterpret_cast<const __half2*>(&an_lo));   // (ns, nm)
                 const float2 f_hi = __half22float2(*reinterpret_cast<const __half2*>(&an_hi));
-                float smin[2][G];
+                auto do_half = [&](auto half_tag) {
+                    constexpr int H = decltype(half_tag)::value;
 #pragma unroll
-                for (int r = 0; r < 2; ++r)
+                    for (int gg = 0; gg < 4; ++gg) {
+                        constexpr int dummy = 0;
+                        (void)dummy;
+                        const int g = H * 4 + gg;
+                        float s_lo, s_hi, m_lo[2], m_hi[2];
+                        pair_to_floats<SW>(SU::at(sw, g), s_lo, s_hi);
+                        pair_to_floats<SW>(SU::at(sw, 8 + g / 2), m_lo[0], m_lo[1]);       // sub-mins of row lo, groups 2*(g/2), +1
+                        pair_to_floats<SW>(SU::at(sw, 12 + g / 2), m_hi[0], m_hi[1]);      // row hi
+                        const float d[2] = {f_lo.x * s_lo, f_hi.x * s_hi};
+                        // codes enter as 128 + q (bf16 trick), so the constant term absorbs 128 * d
+                        const float off = (BITS <= 6) ? 128.f : 0.f;
+                        const float mn[2] = {fmaf(off, d[0], f_lo.y * m_lo[g & 1]), fmaf(off, d[1], f_hi.y * m_hi[g & 1])};
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) pair_to_floats<SW>(SU::at(sw, 8 + 4 * r + j), smin[r][2 * j], smin[r][2 * j + 1]);
+                        for (int r = 0; r < 2; ++r) {
+                            const int row = rbl * 16 + q + 8 * r;
 #pragma unroll
-                for (int g = 0; g < G; ++g) {
-                    float s_lo, s_hi;
-                    pair_to_floats<SW>(SU::at(sw, g), s_lo, s_hi);
-                    const float d[2] = {f_lo.x * s_lo, f_hi.x * s_hi};
-                    const float mn[2] = {f_lo.y * smin[0][g], f_hi.y * smin[1][g]};
-#pragma unroll
-                    for (int r = 0; r < 2; ++r) {
-                        const int row = warp * 16 + q + 8 * r;
-#pragma unroll
-                        for (int j = 0; j < HALF; ++j) {
-                            const uint32_t raw = QU::at(qw, (g * 2 + r) * HALF + j);
-                            const float v0 = fmaf(d[r], (float)(raw & 0xFFFFu), -mn[r]);
-                            const float v1 = fmaf(d[r], (float)(raw >> 16), -mn[r]);
-                            const __half2 h = __floats2half2_rn(v0, v1);
-                            const int k = g * GS + c * PER + 2 * j, atom = k >> 6, kk = k & 63;
-                            *reinterpret_cast<__half2*>(at + atom * (128 * 128) + row * 128 + (((kk >> 3) ^ q) << 4) + (kk & 7) * 2) = h;
+                            for (int j = 0; j < HALF; ++j) {
+                                const uint32_t raw = QU::at(qw, (g * 2 + r) * HALF + j);
+                                float c0, c1;
+                                if constexpr (BITS <= 6) {
+                                    const uint32_t v = raw | kBf16x2_128;
+                                    c0 = __uint_as_float(v << 16);
+                                    c1 = __uint_as_float(v & 0xFFFF0000u);
+                                } else {
+                                    c0 = (float)(raw & 0xFFFFu);
+                                    c1 = (float)(raw >> 16);
+                                }
+                                const __half2 h = __floats2half2_rn(fmaf(d[r], c0, -mn[r]), fmaf(d[r], c1, -mn[r]));
+                                const int k = g * GS + c * PER + 2 * j, atom = k >> 6, kk = k & 63;
+                                unsigned char* at = tiles + ((ch * ATOMS + atom) % NS) * stage_bytes;
+                                *reinterpret_cast<__half2*>(at + row * 128 + (((kk >> 3) ^ q) << 4) + (kk & 7) * 2) = h;
+                            }
                         }
                     }
-                }
-            } else {
-                // rows past the end of w: zero the warp's 16 rows
+                };
+                if (half == 0) do_half(std::integral_constant<int, 0>{});
+                else do_half(std::integral_constant<int, 1>{});
+            } else if (half == 0) {
+                // rows past the end of w: zero the row-block's 16 rows in every atom of the chunk
                 for (int i = lane; i < 16 * ATOMS * 8; i += 32) {
                     const int r = i / (ATOMS * 8), rest = i % (ATOMS * 8), atom = rest >> 3, c16 = rest & 7;
-                    *reinterpret_cast<uint4*>(at + atom * (128 * 128) + (warp * 16 + r) * 128 + (c16 << 4)) = make_uint4(0u, 0u, 0u, 0u);
+                    unsigned char* at = tiles + ((ch * ATOMS + atom) % NS) * stage_bytes;
+                    *reinterpret_cast<uint4*>(at + (rbl * 16 + r) * 128 + (c16 << 4)) = make_uint4(0u, 0u, 0u, 0u);
                 }
             }
-            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
             fence_proxy_async_smem();
-            mbar_arrive(&full_bar[st]);
+#pragma unroll
+            for (int j = 0; j < ATOMS; ++j) mbar_arrive(&full_bar[(ch * ATOMS + j) % NS]);
+        }
+    } else if (warp == kGemmProducerWarps + 1) {
+        // ------------------------------ x loader (TMA) ------------------------------
+        if (lane == 0) {
+            const int natoms = w.nchunks * ATOMS;
+            for (int ai = 0; ai < natoms; ++ai) {
+                const int st = ai % NS, use = ai / NS;
+                if (use > 0 && !mbar_wait(&empty_bar[st], (use - 1) & 1)) { failed = 1; break; }
+                mbar_arrive_expect_tx(&full_bar[st], (uint32_t)(BN * 128));
+                tma_load_2d(tiles + st * stage_bytes + 128 * 128, &x_map, ai * 64, tok0, &full_bar[st]);
+            }
         }
     } else if (lane == 0) {
         // ------------------------------ mma issuer ------------------------------
         const uint32_t idesc = instr_desc_f16(128, BN);
-        for (int ch = 0; ch < w.nchunks; ++ch) {
-            const int st = ch & 1, use = ch >> 1;
+        const int natoms = w.nchunks * ATOMS;
+        for (int ai = 0; ai < natoms; ++ai) {
+            const int st = ai % NS, use = ai / NS;
             if (!mbar_wait(&full_bar[st], use & 1)) { failed = 1; break; }
             tc_fence_after_sync();
-            const uint32_t a_base = smem_u32(a_tile[st]), b_base = smem_u32(b_tile[st]);
-#pragma unroll 1
-            for (int j = 0; j < KST / 16; ++j) {
-                const uint64_t ad = smem_desc_sw128(a_base + (j >> 2) * (128 * 128) + (j & 3) * 32);
-                const uint64_t bd = smem_desc_sw128(b_base + (j >> 2) * (BN * 128) + (j & 3) * 32);
-                tc_mma_f16(tmem_d, ad, bd, idesc, ch > 0 || j > 0);
-            }
+            const uint32_t a_base = smem_u32(tiles + st * stage_bytes), b_base = a_base + 128 * 128;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                tc_mma_f16(tmem_d, smem_desc_sw128(a_base + j * 32), smem_desc_sw128(b_base + j * 32), idesc, ai > 0 || j > 0);
             tc_commit(&empty_bar[st]);
         }
         tc_commit(&done_bar);
     }
 
     // ------------------------------ epilogue ------------------------------
-    if (warp < 8) {
+    if (warp < kGemmProducerWarps) {
         bool ok = !failed && mbar_wait(&done_bar, 0);
         ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld is warp-wide: take the decision together
         if (!ok) failed = 1;
         tc_fence_after_sync();
-        if (ok) {
-            const int lane_quarter = warp & 3, col_half = warp >> 2;
+        const int lane_quarter = warp & 3, part = warp >> 2;          // 4 column parts
+        const int cols_per_part = BN / 4 < 32 ? 32 : BN / 4;
+        const int c_begin = part * cols_per_part, c_end = min(BN, c_begin + cols_per_part);
+        if (ok && c_begin < BN) {
             const int n = row0 + lane_quarter * 32 + lane;
-            for (int cb = col_half * (BN / 2); cb < (col_half + 1) * (BN / 2); cb += 32) {
+            for (int cb = c_begin; cb < c_end; cb += 32) {
                 uint32_t r[32];
                 tmem_ld32(tmem_d + ((uint32_t)(lane_quarter * 32) << 16) + (uint32_t)cb, r);
                 if (n < w.n) {
@@ -189,31 +231,36 @@ __global__ void __launch_bounds__(kGemmThreads, 1) nint_gemm_tc_kernel(const Gem
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 8) {
+    if (warp == kGemmProducerWarps) {
         tmem_free(tmem_d, (uint32_t)BN);
         if (lane == 0 && failed) atomicExch(a.error, MFQB_ERR_TIMEOUT);
     }
 }
 
 struct GemmPlan {
-    int bn, grid_x, grid_y;
+    int bn, stages, grid_x, grid_y;
     size_t smem;
 };
 // gs must be 16, 24 or 32 (a chunk is then whole swizzle atoms); returns bn = 0 otherwise.
 inline GemmPlan plan_nint_gemm(const NintDev& w, int m) {
     GemmPlan p{};
     if (!(w.gs == 16 || w.gs == 24 || w.gs == 32) || w.per * 4 != w.gs) return p;
-    const int kst = kChunkGroups * w.gs, atoms = kst / 64;
-    int bn = w.gs == 16 ? 256 : (w.gs == 24 ? 128 : 64);
+    const int atoms = kChunkGroups * w.gs / 64;
+    // wide token tiles amortise the dequantisation; 32-wide groups (4 atoms per chunk) take the
+    // narrower tile so that the ring holds more than one chunk
+    int bn = (w.gs == 32) ? 128 : 256;
     while (bn > 64 && bn / 2 >= m) bn /= 2;
     p.bn = bn;
+    const int stage_bytes = 128 * 128 + bn * 128;
+    p.stages = std::min(8, (int)((220 * 1024) / stage_bytes));
+    if (p.stages < atoms) { p.bn = 0; return p; }
     p.grid_x = (w.n + 127) / 128;
     p.grid_y = (m + bn - 1) / bn;
-    p.smem = (size_t)2 * atoms * (128 + bn) * 128 + 1024;
+    p.smem = (size_t)p.stages * stage_bytes + 1024;
     return p;
 }
 
 template <int BITS>
-cudaError_t launch_nint_gemm_bits(const GemmArgs& a, const GemmPlan& p, cudaStream_t stream);
+cudaError_t launch_nint_gemm_bits(const GemmArgs& a, const GemmPlan& p, const CUtensorMap& x_map, cudaStream_t stream);
 
 }  // namespace mfqb

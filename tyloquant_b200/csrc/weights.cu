@@ -222,6 +222,32 @@ static int* gemm_status_word(int device) {   // pinned, mapped: the host can rea
     return g_gemm.status_dev[device];
 }
 
+// Tensor map of the f16 activations [m, kx] for 64-column x bn-row boxes with the 128-byte swizzle.
+// cuTensorMapEncodeTiled is looked up through the runtime, so the library links only libcudart.
+static CUtensorMap make_x_map(const void* x16, int m, int kx, int bn) {
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        MFQB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+        if (!fn || qres != cudaDriverEntryPointSuccess) fail(MFQB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+        encode = reinterpret_cast<EncodeFn>(fn);
+    }
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)kx, (cuuint64_t)m};
+    const cuuint64_t strides[1] = {(cuuint64_t)kx * sizeof(__half)};
+    const cuuint32_t box[2] = {64u, (cuuint32_t)bn};
+    const cuuint32_t elem[2] = {1u, 1u};
+    const CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x16), dims, strides, box, elem,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) fail(MFQB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return map;
+}
+
 // Returns false when this weight has no tensor-core tile kernel (the caller falls back to GEMV passes).
 static bool launch_nint_gemm(const NintDev& w, const void* x, int m, void* y, int y_dtype, int device, cudaStream_t s) {
     const GemmPlan p = plan_nint_gemm(w, m);
@@ -234,6 +260,7 @@ static bool launch_nint_gemm(const NintDev& w, const void* x, int m, void* y, in
     a.y = y;
     a.y_dtype = y_dtype;
     a.bn = p.bn;
+    a.stages = p.stages;
     a.error = gemm_status_word(device);
     DevBuf& xb = g_gemm.x16[device];
     const size_t need = (size_t)m * a.kx * sizeof(__half);
@@ -243,14 +270,15 @@ static bool launch_nint_gemm(const NintDev& w, const void* x, int m, void* y, in
     x_to_f16_kernel<<<(int)std::min<size_t>((total + 255) / 256, 148 * 8), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), m, w.k,
                                                                                       a.kx, static_cast<__half*>(xb.p));
     MFQB_CUDA(cudaGetLastError());
+    const CUtensorMap x_map = make_x_map(xb.p, m, a.kx, p.bn);
     cudaError_t e;
     switch (w.bits) {
-        case 2: e = launch_nint_gemm_bits<2>(a, p, s); break;
-        case 3: e = launch_nint_gemm_bits<3>(a, p, s); break;
-        case 4: e = launch_nint_gemm_bits<4>(a, p, s); break;
-        case 5: e = launch_nint_gemm_bits<5>(a, p, s); break;
-        case 6: e = launch_nint_gemm_bits<6>(a, p, s); break;
-        case 8: e = launch_nint_gemm_bits<8>(a, p, s); break;
+        case 2: e = launch_nint_gemm_bits<2>(a, p, x_map, s); break;
+        case 3: e = launch_nint_gemm_bits<3>(a, p, x_map, s); break;
+        case 4: e = launch_nint_gemm_bits<4>(a, p, x_map, s); break;
+        case 5: e = launch_nint_gemm_bits<5>(a, p, x_map, s); break;
+        case 6: e = launch_nint_gemm_bits<6>(a, p, x_map, s); break;
+        case 8: e = launch_nint_gemm_bits<8>(a, p, x_map, s); break;
         default: return false;
     }
     if (e == cudaErrorNotSupported) return false;
