@@ -159,6 +159,7 @@ def main() -> None:
     ap.add_argument("--only", default=None, help="run one sweep case by name with a few plain launches "
                     "(small, for profilers) and print its line")
     ap.add_argument("--reps", type=int, default=3, help="launch rounds for --only")
+    ap.add_argument("--tokens", type=int, nargs="*", default=None, help="token counts for --only moe")
     args = ap.parse_args()
     steps, warmup = max(args.steps, 1), max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -173,6 +174,9 @@ def main() -> None:
     if args.only == "gemm":
         pk = measured_peaks()[0]
         print(json.dumps(gemm_bench(local_rank, pk.get("bf16_tflops_sustained", pk["bf16_tflops"]))))
+        return
+    if args.only == "moe":
+        print(json.dumps(moe_layer_bench(local_rank, measured_peaks()[0]["hbm_gbs"], token_counts=tuple(args.tokens or (1, 8, 32, 64, 128, 256, 1024)))))
         return
     if args.only:
         print(json.dumps(sweep(local_rank, measured_peaks()[0]["hbm_gbs"], only=args.only, reps=args.reps)))

@@ -111,7 +111,7 @@ def test_golden_nintm_ffn_matches_oracle(golden):
     dn.free()
 
 
-@pytest.mark.parametrize("tokens", [1, 32])
+@pytest.mark.parametrize("tokens", [1, 32, 101])
 def test_mixed_precision_layer_and_expert_shards(tokens):
     """A scaled-down config-4 layer: 16 experts, bits drawn from {2,3,4,6}, top-4."""
     e_count, h, f, k = 16, 256, 96, 4

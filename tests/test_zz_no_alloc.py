@@ -37,7 +37,7 @@ def test_static_scratch_ffn_matches_allocating_ffn_twice_in_a_row():
     wdn = encode.bf16_round(rng.standard_normal((e_count, h, f), dtype=np.float32) * np.float32(0.02))
     gu = moe.MoeWeight(encode.quantize_expertwise(wgu, bits, device="cuda"))
     dn = moe.MoeWeight(encode.quantize_expertwise(wdn, bits, device="cuda"))
-    for tokens in (9, 2):   # the second, smaller call runs over the first call's leftovers
+    for tokens in (9, 40, 2):   # later calls run over the earlier calls' leftovers; 40 tokens take the tiled path
         x = torch.from_numpy(encode.bf16_round(rng.standard_normal((tokens, h), dtype=np.float32))).cuda().to(torch.bfloat16)
         z = torch.from_numpy(rng.standard_normal((tokens, e_count)).astype(np.float32)).cuda()
         ids, wts = moe.moe_topk(z, k)

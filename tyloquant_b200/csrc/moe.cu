@@ -19,6 +19,19 @@ void launch_swiglu(const void* gate_up, int in_dtype, int rows, int f, void* hid
 void launch_weighted_reduce(const void* src, int in_dtype, const float* weights, int tokens, int routes, int h, void* y, int y_dtype,
                             cudaStream_t s);
 
+void launch_route_plan(const int32_t* ids, int pairs, int experts, int tile_m, int32_t* expert_bounds, int32_t* tile_bounds,
+                       int32_t* pair_order, cudaStream_t stream);
+
+// Device buffers of a route plan: expert_bounds [E+1], tile_bounds [E+1], pair_order [pairs].
+struct PlanBufs {
+    int32_t *expert_bounds, *tile_bounds, *pair_order;
+    static size_t bytes(int experts, size_t pairs) { return ((2 * ((size_t)experts + 1) + pairs) * 4 + 255) / 256 * 256; }
+    static PlanBufs carve(void* p, int experts) {
+        int32_t* b = static_cast<int32_t*>(p);
+        return PlanBufs{b, b + experts + 1, b + 2 * (experts + 1)};
+    }
+};
+
 struct MoePool {
     NintDev d{};
     DevBuf items, anchors;
@@ -54,12 +67,12 @@ static HostNint gather_experts(const HostNint& t, const std::vector<int>& local,
 // Per-device scratch for the FFN intermediates; grown on demand.
 struct Scratch {
     std::mutex mu;
-    DevBuf buf[64];
+    DevBuf buf[64], plan[64];
 };
 static Scratch g_scratch;
-static void* scratch_get(int device, size_t bytes) {
+static void* scratch_get(int device, size_t bytes, int slot = 0) {
     std::lock_guard<std::mutex> lock(g_scratch.mu);
-    DevBuf& b = g_scratch.buf[device];
+    DevBuf& b = slot ? g_scratch.plan[device] : g_scratch.buf[device];
     if (b.bytes < bytes) b.alloc(bytes + bytes / 4);
     return b.p;
 }
@@ -184,6 +197,56 @@ int mfqb_moe_dequant_expert(const mfqb_moe_weight* w, int expert, void* out, int
     });
 }
 
+// Tiles of 8 pairs per expert pay off once an expert sees several pairs on average.
+static bool moe_use_tiles(const mfqb_moe_weight* w, int pairs) { return pairs >= 4 * w->info.n_experts; }
+
+// plan == nullptr: one single-row problem per pair.  Otherwise the batched kernel runs over the
+// plan's tiles (the plan must have been built for these ids with tile_m = 8).
+static void mul_mat_id_impl(const mfqb_moe_weight* w, const void* x, int x_per_pair, const int32_t* ids, int tokens, int routes,
+                            void* out, int out_dtype, const PlanBufs* plan, cudaStream_t stream) {
+    const int pairs = tokens * routes, ope = w->info.out_per_expert;
+    // Routes to experts this handle does not hold produce zeros (expert-parallel shards are
+    // summed afterwards), so clear the output when the handle is partial.
+    if (w->info.expert_end - w->info.expert_begin != w->info.n_experts)
+        MFQB_CUDA(cudaMemsetAsync(out, 0, (size_t)pairs * ope * (out_dtype == MFQB_F32 ? 4 : 2), stream));
+    for (size_t pi = 0; pi < w->pools.size(); ++pi) {
+        const MoePool& pool = *w->pools[pi];
+        if (!pool.held) continue;
+        GemvArgs a{};
+        a.w = pool.d;
+        a.x = static_cast<const __nv_bfloat16*>(x);
+        a.y = out;
+        a.ldy = ope;
+        a.y_dtype = out_dtype;
+        a.expert_pool = static_cast<const int*>(w->d_expert_pool.p);
+        a.expert_local = static_cast<const int*>(w->d_expert_local.p);
+        a.pool = (int)pi;
+        a.rb_per_expert = w->padded / 16;
+        a.routes = routes;
+        a.x_per_pair = x_per_pair ? 1 : 0;
+        if (plan) {
+            a.expert_bounds = plan->expert_bounds;
+            a.tile_bounds = plan->tile_bounds;
+            a.pair_order = plan->pair_order;
+            a.n_experts = w->info.n_experts;
+            const int max_tiles = pairs / 8 + std::min(pairs, w->info.n_experts);
+            if (max_tiles > 65535) fail(MFQB_ERR_ARG, "mfqb_mul_mat_id: too many route tiles (%d)", max_tiles);
+            launch_nint_gemv_routed_tiles(a, max_tiles, w->info.device, stream);
+            continue;
+        }
+        a.route_ids = ids;
+        for (int p0 = 0; p0 < pairs; p0 += 32768) {   // gridDim.y limit
+            GemvArgs b = a;
+            const int np = std::min(32768, pairs - p0);
+            b.route_ids = ids + p0;
+            b.y = static_cast<char*>(out) + (size_t)p0 * ope * (out_dtype == MFQB_F32 ? 4 : 2);
+            if (p0 % routes) fail(MFQB_ERR_ARG, "mfqb_mul_mat_id: routes must divide 32768 for more than 32768 pairs");
+            b.x = a.x + (size_t)(x_per_pair ? p0 : p0 / routes) * w->info.k;
+            launch_nint_gemv_routed(b, np, w->info.device, stream);
+        }
+    }
+}
+
 int mfqb_mul_mat_id(const mfqb_moe_weight* w, const void* x, int x_per_pair, const int32_t* ids, int tokens, int routes, void* out,
                     int out_dtype, mfqb_stream_t stream) {
     return guarded([&] {
@@ -192,37 +255,13 @@ int mfqb_mul_mat_id(const mfqb_moe_weight* w, const void* x, int x_per_pair, con
         if (out_dtype != MFQB_F32 && out_dtype != MFQB_BF16) fail(MFQB_ERR_ARG, "mfqb_mul_mat_id: bad output dtype");
         if (tokens == 0) return;
         DeviceGuard guard(w->info.device);
-        const int pairs = tokens * routes, ope = w->info.out_per_expert;
-        // Routes to experts this handle does not hold produce zeros (expert-parallel shards are
-        // summed afterwards), so clear the output when the handle is partial.
-        if (w->info.expert_end - w->info.expert_begin != w->info.n_experts)
-            MFQB_CUDA(cudaMemsetAsync(out, 0, (size_t)pairs * ope * (out_dtype == MFQB_F32 ? 4 : 2), stream));
-        for (size_t pi = 0; pi < w->pools.size(); ++pi) {
-            const MoePool& pool = *w->pools[pi];
-            if (!pool.held) continue;
-            GemvArgs a{};
-            a.w = pool.d;
-            a.x = static_cast<const __nv_bfloat16*>(x);
-            a.y = out;
-            a.ldy = ope;
-            a.y_dtype = out_dtype;
-            a.route_ids = ids;
-            a.expert_pool = static_cast<const int*>(w->d_expert_pool.p);
-            a.expert_local = static_cast<const int*>(w->d_expert_local.p);
-            a.pool = (int)pi;
-            a.rb_per_expert = w->padded / 16;
-            a.routes = routes;
-            a.x_per_pair = x_per_pair ? 1 : 0;
-            for (int p0 = 0; p0 < pairs; p0 += 32768) {   // gridDim.y limit
-                GemvArgs b = a;
-                const int np = std::min(32768, pairs - p0);
-                b.route_ids = ids + p0;
-                b.y = static_cast<char*>(out) + (size_t)p0 * ope * (out_dtype == MFQB_F32 ? 4 : 2);
-                // x: pair p0 is token p0 / routes when x is shared; chunks start on token boundaries
-                if (p0 % routes) fail(MFQB_ERR_ARG, "mfqb_mul_mat_id: routes must divide 32768 for more than 32768 pairs");
-                b.x = a.x + (size_t)(x_per_pair ? p0 : p0 / routes) * w->info.k;
-                launch_nint_gemv_routed(b, np, w->info.device, stream);
-            }
+        const int pairs = tokens * routes;
+        if (moe_use_tiles(w, pairs)) {   // larger batches: route plan in library scratch, batched kernel over its tiles
+            PlanBufs plan = PlanBufs::carve(scratch_get(w->info.device, PlanBufs::bytes(w->info.n_experts, pairs), 1), w->info.n_experts);
+            launch_route_plan(ids, pairs, w->info.n_experts, 8, plan.expert_bounds, plan.tile_bounds, plan.pair_order, stream);
+            mul_mat_id_impl(w, x, x_per_pair, ids, tokens, routes, out, out_dtype, &plan, stream);
+        } else {
+            mul_mat_id_impl(w, x, x_per_pair, ids, tokens, routes, out, out_dtype, nullptr, stream);
         }
     });
 }
@@ -239,15 +278,20 @@ int mfqb_moe_ffn(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* down, co
         DeviceGuard guard(gate_up->info.device);
         const size_t pairs = (size_t)tokens * routes;
         const size_t b_gu = pairs * f2 * 4, b_hid = (pairs * f * 2 + 255) / 256 * 256, b_dn = pairs * h * 4;
-        char* s = static_cast<char*>(scratch_get(gate_up->info.device, b_gu + b_hid + b_dn));
+        const bool tiles = moe_use_tiles(gate_up, (int)pairs);
+        const size_t b_plan = tiles ? PlanBufs::bytes(gate_up->info.n_experts, pairs) : 0;
+        char* s = static_cast<char*>(scratch_get(gate_up->info.device, b_gu + b_hid + b_dn + b_plan));
         float* gu = reinterpret_cast<float*>(s);
         void* hid = s + b_gu;
         float* dn = reinterpret_cast<float*>(s + b_gu + b_hid);
-        int rc = mfqb_mul_mat_id(gate_up, x, 0, ids, tokens, routes, gu, MFQB_F32, stream);
-        if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
+        PlanBufs plan{};
+        if (tiles) {   // one route plan serves both matmuls
+            plan = PlanBufs::carve(s + b_gu + b_hid + b_dn, gate_up->info.n_experts);
+            launch_route_plan(ids, (int)pairs, gate_up->info.n_experts, 8, plan.expert_bounds, plan.tile_bounds, plan.pair_order, stream);
+        }
+        mul_mat_id_impl(gate_up, x, 0, ids, tokens, routes, gu, MFQB_F32, tiles ? &plan : nullptr, stream);
         launch_swiglu(gu, MFQB_F32, (int)pairs, f, hid, stream);
-        rc = mfqb_mul_mat_id(down, hid, 1, ids, tokens, routes, dn, MFQB_F32, stream);
-        if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
+        mul_mat_id_impl(down, hid, 1, ids, tokens, routes, dn, MFQB_F32, tiles ? &plan : nullptr, stream);
         launch_weighted_reduce(dn, MFQB_F32, weights, tokens, routes, h, y, y_dtype, stream);
     });
 }
@@ -292,24 +336,29 @@ int mfqb_moe_ffn_static(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* d
         if (tokens <= 0 || routes < 1) return;
         const size_t pairs = (size_t)tokens * routes;
         const size_t b_gu = pairs * f2 * 4, b_hid = (pairs * f * 2 + 255) / 256 * 256, b_dn = pairs * h * 4;
-        if (b_gu + b_hid + b_dn > (size_t)MFQB_STATIC_SCRATCH_BYTES)
+        const bool tiles = moe_use_tiles(gate_up, (int)pairs);
+        const size_t b_plan = tiles ? PlanBufs::bytes(gate_up->info.n_experts, pairs) : 0;
+        if (b_gu + b_hid + b_dn + b_plan > (size_t)MFQB_STATIC_SCRATCH_BYTES)
             fail(MFQB_ERR_ARG,
                  "mfqb_moe_ffn_static: %d tokens x %d routes need %llu bytes of scratch, the built-in array holds %llu; "
                  "use mfqb_moe_ffn or fewer tokens per call",
-                 tokens, routes, (unsigned long long)(b_gu + b_hid + b_dn), (unsigned long long)MFQB_STATIC_SCRATCH_BYTES);
+                 tokens, routes, (unsigned long long)(b_gu + b_hid + b_dn + b_plan), (unsigned long long)MFQB_STATIC_SCRATCH_BYTES);
         DeviceGuard guard(gate_up->info.device);
         unsigned char* s = ffn_static_scratch(gate_up->info.device);
         // The array still holds whatever the previous call left: start the two accumulation targets
         // from zero so that a route to an expert nobody holds contributes nothing.
-        MFQB_CUDA(cudaMemsetAsync(s, 0, b_gu + b_hid + b_dn, stream));
+        MFQB_CUDA(cudaMemsetAsync(s, 0, b_gu + b_hid + b_dn + b_plan, stream));
         float* gu = reinterpret_cast<float*>(s);
         void* hid = s + b_gu;
         float* dn = reinterpret_cast<float*>(s + b_gu + b_hid);
-        int rc = mfqb_mul_mat_id(gate_up, x, 0, ids, tokens, routes, gu, MFQB_F32, stream);
-        if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
+        PlanBufs plan{};
+        if (tiles) {   // the route plan lives in the same fixed array
+            plan = PlanBufs::carve(s + b_gu + b_hid + b_dn, gate_up->info.n_experts);
+            launch_route_plan(ids, (int)pairs, gate_up->info.n_experts, 8, plan.expert_bounds, plan.tile_bounds, plan.pair_order, stream);
+        }
+        mul_mat_id_impl(gate_up, x, 0, ids, tokens, routes, gu, MFQB_F32, tiles ? &plan : nullptr, stream);
         launch_swiglu(gu, MFQB_F32, (int)pairs, f, hid, stream);
-        rc = mfqb_mul_mat_id(down, hid, 1, ids, tokens, routes, dn, MFQB_F32, stream);
-        if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
+        mul_mat_id_impl(down, hid, 1, ids, tokens, routes, dn, MFQB_F32, tiles ? &plan : nullptr, stream);
         launch_weighted_reduce(dn, MFQB_F32, weights, tokens, routes, h, y, y_dtype, stream);
     });
 }

@@ -174,6 +174,15 @@ void launch_weighted_reduce(const void* src, int in_dtype, const float* weights,
     MFQB_CUDA(cudaGetLastError());
 }
 
+void launch_route_plan(const int32_t* ids, int pairs, int experts, int tile_m, int32_t* expert_bounds, int32_t* tile_bounds,
+                       int32_t* pair_order, cudaStream_t stream) {
+    const int blocks = (experts + 3) / 4;
+    route_count_kernel<<<blocks, 128, 0, stream>>>(ids, pairs, experts, expert_bounds + 1);
+    route_scan_kernel<<<1, 32, 0, stream>>>(experts, tile_m, expert_bounds, tile_bounds);
+    route_place_kernel<<<blocks, 128, 0, stream>>>(ids, pairs, experts, expert_bounds, pair_order);
+    MFQB_CUDA(cudaGetLastError());
+}
+
 }  // namespace mfqb
 
 using namespace mfqb;
@@ -200,11 +209,7 @@ int mfqb_moe_route_plan(const int32_t* ids, int tokens, int k, int experts, int 
     return guarded([&] {
         if (!ids || !expert_bounds || !tile_bounds || !pair_order) fail(MFQB_ERR_ARG, "mfqb_moe_route_plan: null argument");
         if (tokens < 0 || k < 1 || experts < 1 || tile_m < 1) fail(MFQB_ERR_ARG, "mfqb_moe_route_plan: bad sizes");
-        const int pairs = tokens * k, blocks = (experts + 3) / 4;
-        route_count_kernel<<<blocks, 128, 0, stream>>>(ids, pairs, experts, expert_bounds + 1);
-        route_scan_kernel<<<1, 32, 0, stream>>>(experts, tile_m, expert_bounds, tile_bounds);
-        route_place_kernel<<<blocks, 128, 0, stream>>>(ids, pairs, experts, expert_bounds, pair_order);
-        MFQB_CUDA(cudaGetLastError());
+        launch_route_plan(ids, tokens * k, experts, tile_m, expert_bounds, tile_bounds, pair_order, stream);
     });
 }
 

@@ -103,6 +103,12 @@ struct GemvArgs {
     int rb_per_expert;       // rows_per_expert / 16
     int routes;              // routes per token (R)
     int x_per_pair;          // 1: x is [pairs, k]; 0: x is [tokens, k], shared by the token's routes
+    // Routed tile mode of the batched kernel: blockIdx.y is a tile of up to 8 pairs of one expert,
+    // taken from a route plan (expert_bounds / tile_bounds / pair_order of mfqb_moe_route_plan).
+    const int* expert_bounds;
+    const int* tile_bounds;
+    const int* pair_order;
+    int n_experts;
 };
 
 constexpr uint32_t kBf16x2_one = 0x3F803F80u;  // (1.0, 1.0)
@@ -147,8 +153,37 @@ __global__ void __launch_bounds__(256, 2) nint_gemv_kernel(const GemvArgs a) {
     float* ypart = reinterpret_cast<float*>(smem);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const int q = lane >> 2, c = lane & 3;
-    const int rb0 = blockIdx.x * a.rb_per_cta;
-    const int nrb = min(a.rb_per_cta, w.nrb - rb0);
+    __shared__ int row_src[8], row_dst[8];   // x row read / y row written by batch column i
+    int rb0 = blockIdx.x * a.rb_per_cta, rb_limit = w.nrb, m_cur = a.m, row_bias = 0, row_limit = w.n;
+    if (a.tile_bounds != nullptr) {
+        pdl_wait();   // the route plan comes from earlier kernels of the stream
+        const int t = blockIdx.y;
+        if (t >= a.tile_bounds[a.n_experts]) return;
+        int lo = 0, hi = a.n_experts - 1;   // expert e with tile_bounds[e] <= t < tile_bounds[e + 1]
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (a.tile_bounds[mid] <= t) lo = mid; else hi = mid - 1;
+        }
+        const int e = lo;
+        if (a.expert_pool[e] != a.pool) return;
+        const int p0 = a.expert_bounds[e] + (t - a.tile_bounds[e]) * 8;
+        m_cur = min(8, a.expert_bounds[e + 1] - p0);
+        if (tid < 8) {
+            const int pair = tid < m_cur ? a.pair_order[p0 + tid] : 0;
+            row_src[tid] = a.x_per_pair ? pair : pair / a.routes;
+            row_dst[tid] = pair;
+        }
+        const int base = a.expert_local[e] * a.rb_per_expert;
+        rb0 = base + blockIdx.x * a.rb_per_cta;
+        rb_limit = base + a.rb_per_expert;
+        row_bias = base * 16;        // y rows are counted inside the expert
+        row_limit = a.ldy;
+    } else if (tid < 8) {
+        row_src[tid] = tid;
+        row_dst[tid] = tid;
+    }
+    const int nrb = min(a.rb_per_cta, rb_limit - rb0);
+    if (nrb <= 0) return;
     float* xt = ypart + (size_t)a.rb_per_cta * 128 + warp * 64;
     __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(ypart + (size_t)a.rb_per_cta * 128 + nwarps * 64);
 
@@ -164,29 +199,30 @@ __global__ void __launch_bounds__(256, 2) nint_gemv_kernel(const GemvArgs a) {
     if (1 < n_mine) it1.load(w, item_rb(1), item_seg(1), lane);
     for (int i = tid; i < nrb * 128; i += blockDim.x) ypart[i] = 0.f;
     pdl_wait();
+    __syncthreads();   // row_src / row_dst
     if (a.xstride > 0) {
         // stage x: 16-byte copies when rows are 16-byte aligned, zero beyond k
         const int kp = a.xstride;
         if ((w.k & 7) == 0 && (reinterpret_cast<uintptr_t>(a.x) & 15) == 0) {
             const int vec_per_row = kp / 8;
-            for (int i = tid; i < a.m * vec_per_row; i += blockDim.x) {
+            for (int i = tid; i < m_cur * vec_per_row; i += blockDim.x) {
                 const int m = i / vec_per_row, v = i % vec_per_row;
                 uint4 val = make_uint4(0u, 0u, 0u, 0u);
-                if (v * 8 < w.k) val = __ldg(reinterpret_cast<const uint4*>(a.x + (size_t)m * w.k) + v);
+                if (v * 8 < w.k) val = __ldg(reinterpret_cast<const uint4*>(a.x + (size_t)row_src[m] * w.k) + v);
                 *reinterpret_cast<uint4*>(xs + (size_t)m * kp + v * 8) = val;
             }
         } else {
-            for (int i = tid; i < a.m * kp; i += blockDim.x) {
+            for (int i = tid; i < m_cur * kp; i += blockDim.x) {
                 const int m = i / kp, k = i % kp;
-                xs[i] = k < w.k ? a.x[(size_t)m * w.k + k] : __float2bfloat16(0.f);
+                xs[i] = k < w.k ? a.x[(size_t)row_src[m] * w.k + k] : __float2bfloat16(0.f);
             }
         }
     }
     __syncthreads();
 
-    const bool has_col = q < a.m;
+    const bool has_col = q < m_cur;
     const bool even_k = (w.k & 1) == 0;
-    const __nv_bfloat16* xcol = a.x + (size_t)q * w.k;
+    const __nv_bfloat16* xcol = a.x + (size_t)row_src[q] * w.k;
     const uint32_t* xrow = reinterpret_cast<const uint32_t*>(xs + (size_t)q * a.xstride);
     int cur_seg = -1;
     uint32_t xf[G][HALF];
@@ -309,11 +345,11 @@ __global__ void __launch_bounds__(256, 2) nint_gemv_kernel(const GemvArgs a) {
         const __half2 h_lo = *reinterpret_cast<const __half2*>(&it.an_lo), h_hi = *reinterpret_cast<const __half2*>(&it.an_hi);
         const float2 f_lo = __half22float2(h_lo), f_hi = __half22float2(h_hi);  // (ns, nm)
         float* yp = ypart + (size_t)rbl * 128;
-        if (2 * c < a.m) {
+        if (2 * c < m_cur) {
             atomicAdd(yp + q * 8 + 2 * c, f_lo.x * tot[0] - f_lo.y * mt[0]);
             atomicAdd(yp + (q + 8) * 8 + 2 * c, f_hi.x * tot[2] - f_hi.y * mt[2]);
         }
-        if (2 * c + 1 < a.m) {
+        if (2 * c + 1 < m_cur) {
             atomicAdd(yp + q * 8 + 2 * c + 1, f_lo.x * tot[1] - f_lo.y * mt[1]);
             atomicAdd(yp + (q + 8) * 8 + 2 * c + 1, f_hi.x * tot[3] - f_hi.y * mt[3]);
         }
@@ -335,12 +371,12 @@ __global__ void __launch_bounds__(256, 2) nint_gemv_kernel(const GemvArgs a) {
     }
     __syncthreads();
     const int rows = nrb * 16;
-    for (int i = tid; i < rows * a.m; i += blockDim.x) {
-        const int n = i / rows, rr = i % rows, row = rb0 * 16 + rr;
-        if (row < w.n) {
+    for (int i = tid; i < rows * m_cur; i += blockDim.x) {
+        const int n = i / rows, rr = i % rows, row = rb0 * 16 + rr - row_bias;
+        if (row < row_limit) {
             const float v = ypart[rr * 8 + n];
-            if (a.y_dtype == 0 /* MFQB_F32 */) reinterpret_cast<float*>(a.y)[(size_t)n * a.ldy + row] = v;
-            else reinterpret_cast<__nv_bfloat16*>(a.y)[(size_t)n * a.ldy + row] = __float2bfloat16_rn(v);
+            if (a.y_dtype == 0 /* MFQB_F32 */) reinterpret_cast<float*>(a.y)[(size_t)row_dst[n] * a.ldy + row] = v;
+            else reinterpret_cast<__nv_bfloat16*>(a.y)[(size_t)row_dst[n] * a.ldy + row] = __float2bfloat16_rn(v);
         }
     }
 }
@@ -356,6 +392,7 @@ template <int BITS>
 cudaError_t launch_nint_gemv_bits(const GemvArgs& a, const GemvPlan& p, cudaStream_t stream);
 
 void launch_nint_gemv_routed(GemvArgs a, int pairs, int device, cudaStream_t s);
+void launch_nint_gemv_routed_tiles(GemvArgs a, int max_tiles, int device, cudaStream_t s);
 void launch_nint_dequant_view(const NintDev& w, void* out, int out_dtype, cudaStream_t s);
 void check_nint_supported(const HostNint& t);
 

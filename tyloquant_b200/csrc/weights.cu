@@ -148,6 +148,8 @@ static void launch_nint_gemv(const NintDev& w, const void* x, int m, void* y, in
     a.route_ids = nullptr;
     a.expert_pool = a.expert_local = nullptr;
     a.pool = a.rb_per_expert = a.routes = a.x_per_pair = 0;
+    a.expert_bounds = a.tile_bounds = a.pair_order = nullptr;
+    a.n_experts = 0;
     const GemvPlan p = plan_nint_gemv(w, m, device_sm_count(device));
     a.rb_per_cta = p.rb_per_cta;
     a.xstride = p.xstride;
@@ -289,6 +291,36 @@ static bool launch_nint_gemm(const NintDev& w, const void* x, int m, void* y, in
 int gemm_device_status(int device) {
     std::lock_guard<std::mutex> lock(g_gemm.mu);
     return g_gemm.status_host[device] ? *static_cast<volatile int*>(g_gemm.status_host[device]) : 0;
+}
+
+// Batched kernel over route-plan tiles (up to 8 pairs of one expert each) for one cohort.
+void launch_nint_gemv_routed_tiles(GemvArgs a, int max_tiles, int device, cudaStream_t s) {
+    const NintDev& w = a.w;
+    a.m = 8;
+    GemvPlan p = plan_nint_gemv(w, 8, device_sm_count(device));
+    p.rb_per_cta = std::min(a.rb_per_expert, 48);
+    const int splits = (a.rb_per_expert + p.rb_per_cta - 1) / p.rb_per_cta;
+    const size_t fixed = (size_t)p.rb_per_cta * 128 * 4 + (size_t)8 * 64 * 4;
+    const size_t xbytes = (size_t)8 * p.xstride * 2;
+    if (fixed + xbytes > 100 * 1024) p.xstride = 0;
+    p.smem = fixed + (p.xstride ? xbytes : 0);
+    a.rb_per_cta = p.rb_per_cta;
+    a.xstride = p.xstride;
+    a.stages = 0;
+    p.grid = splits;
+    p.grid_y = max_tiles;
+    p.threads = 256;
+    cudaError_t e;
+    switch (w.bits) {
+        case 2: e = launch_nint_gemv_bits<2>(a, p, s); break;
+        case 3: e = launch_nint_gemv_bits<3>(a, p, s); break;
+        case 4: e = launch_nint_gemv_bits<4>(a, p, s); break;
+        case 5: e = launch_nint_gemv_bits<5>(a, p, s); break;
+        case 6: e = launch_nint_gemv_bits<6>(a, p, s); break;
+        case 8: e = launch_nint_gemv_bits<8>(a, p, s); break;
+        default: fail(MFQB_ERR_UNSUPPORTED, "NINT%d has no kernel", w.bits);
+    }
+    if (e != cudaSuccess) fail(MFQB_ERR_CUDA, "NINT%d routed tile launch: %s", w.bits, cudaGetErrorString(e));
 }
 
 void launch_nint_dequant_view(const NintDev& w, void* out, int out_dtype, cudaStream_t s) { launch_nint_dequant(w, out, out_dtype, s); }
