@@ -37,7 +37,12 @@ def check_products(w: QuantWeight, w_ref: np.ndarray, m: int, seed: int):
     y32 = w.matmul(bf16_tensor(x), out_dtype=torch.float32).cpu().numpy()
     assert rel_l2(y32, y_ref) <= REL_L2
     y16 = w.matmul(bf16_tensor(x)).float().cpu().numpy()
-    assert rel_l2(y16, O.bf16_round(y_ref)) <= REL_L2
+    # The bf16 output must be a correct rounding of an accurate result: within half a bf16 step of
+    # the oracle plus the accuracy bound itself.  Equality with the rounded oracle is not required:
+    # short rows of low-precision factors put the exact sum on rounding ties, where a difference of
+    # one float32 unit decides the direction.
+    assert np.all(np.abs(y16 - y_ref) <= np.abs(y_ref) * (2.0 ** -8 * 1.02) + REL_L2 * np.abs(y_ref).max())
+    assert rel_l2(y16, y_ref) <= 3e-3   # rounding an exact result to bf16 alone is up to 2.3e-3
     assert np.abs(y16 - y_ref).max() <= MAX_ABS_BF16
     return rel_l2(y32, y_ref)
 

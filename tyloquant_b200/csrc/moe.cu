@@ -2,7 +2,8 @@
 //
 // Every precision cohort of the record becomes one NINT device tensor whose rows are the held
 // experts of the cohort, each padded to whole 16-row blocks.  A routed matmul launches the
-// single-row kernel once per cohort over (row splits, pairs) CTAs; a CTA looks its pair's expert
+// single-row kernel once per cohort over (row splits, pairs) CTAs (larger batches: the batched
+// kernel over route-plan tiles of 8 pairs of one expert); a CTA looks its pair's expert
 // up in two small tables (cohort of the expert, position inside the cohort) and returns when
 // the expert belongs to another cohort or is not held by this handle (expert-parallel shard).
 #include <cuda_bf16.h>
@@ -12,7 +13,7 @@
 #include <mutex>
 
 #include "cuda_util.h"
-#include "nint_gemv.cuh"
+#include "nint_gemv1_bl.cuh"
 
 namespace mfqb {
 void launch_swiglu(const void* gate_up, int in_dtype, int rows, int f, void* hidden, cudaStream_t s);
@@ -32,8 +33,15 @@ struct PlanBufs {
     }
 };
 
+void launch_nint_bl_dequant(const NintDevB& w, void* out, int out_dtype, cudaStream_t s);
+void launch_nint_bl_gemv_routed(GemvArgsB a, int pairs, int device, cudaStream_t s);
+void launch_nint_bl_gemv_tiles(GemvArgsB a, int max_tiles, int device, cudaStream_t s);
+void check_nint_supported(const HostNint& t);
+size_t nint_bl_planes_bytes(const NintDevB& w, int rows);
+void launch_x_planes(const NintDevB& w, const void* x, int rows, void* planes, const uint2** xq_g, const float2** gtab_g, cudaStream_t s);
+
 struct MoePool {
-    NintDev d{};
+    NintDevB d{};
     DevBuf items, anchors;
     int held = 0;   // experts of this cohort held here
 };
@@ -131,7 +139,7 @@ int mfqb_nintm_from_blob(const void* blob, uint64_t nbytes, int expert_begin, in
             auto pool = std::make_unique<MoePool>();
             pool->held = (int)local.size();
             if (!local.empty()) {
-                NintPacked p = pack_nint_device(gather_experts(hp.tensor, local, ope, w->padded));
+                NintPackedB p = pack_nint_bytes(gather_experts(hp.tensor, local, ope, w->padded));
                 pool->items.upload(p.items.data(), p.items.size() * 4);
                 pool->anchors.upload(p.anchors.data(), p.anchors.size() * 4);
                 pool->d = p.d;
@@ -187,24 +195,42 @@ int mfqb_moe_dequant_expert(const mfqb_moe_weight* w, int expert, void* out, int
             fail(MFQB_ERR_ARG, "expert %d is not held by this handle", expert);
         DeviceGuard guard(w->info.device);
         const MoePool& pool = *w->pools[w->expert_pool[expert]];
-        NintDev view = pool.d;   // the expert's row-blocks as a tensor of its own
+        NintDevB view = pool.d;   // the expert's row-blocks as a tensor of its own
         const int rb0 = w->expert_local[expert] * (w->padded / 16);
         view.items += (size_t)rb0 * view.nchunks * view.rec_words;
         view.anchors += (size_t)rb0 * 16;
         view.n = w->info.out_per_expert;
         view.nrb = w->padded / 16;
-        launch_nint_dequant_view(view, out, out_dtype, stream);
+        launch_nint_bl_dequant(view, out, out_dtype, stream);
     });
 }
 
 // Tiles of 8 pairs per expert pay off once an expert sees several pairs on average.
 static bool moe_use_tiles(const mfqb_moe_weight* w, int pairs) { return pairs >= 4 * w->info.n_experts; }
 
+// Bytes of quantised activation planes the tile path needs for `rows` input rows: one set per
+// distinct group size among the held cohorts (cohorts of equal group size share theirs).
+static size_t moe_planes_bytes(const mfqb_moe_weight* w, int rows) {
+    size_t total = 0;
+    for (size_t pi = 0; pi < w->pools.size(); ++pi) {
+        if (!w->pools[pi]->held) continue;
+        bool seen = false;
+        for (size_t pj = 0; pj < pi; ++pj) seen = seen || (w->pools[pj]->held && w->pools[pj]->d.gs == w->pools[pi]->d.gs);
+        if (!seen) total += (nint_bl_planes_bytes(w->pools[pi]->d, rows) + 255) / 256 * 256;
+    }
+    return total;
+}
+
 // plan == nullptr: one single-row problem per pair.  Otherwise the batched kernel runs over the
-// plan's tiles (the plan must have been built for these ids with tile_m = 8).
+// plan's tiles (the plan must have been built for these ids with tile_m = 8) and `planes` is
+// moe_planes_bytes() of device memory for the quantised input rows.
 static void mul_mat_id_impl(const mfqb_moe_weight* w, const void* x, int x_per_pair, const int32_t* ids, int tokens, int routes,
-                            void* out, int out_dtype, const PlanBufs* plan, cudaStream_t stream) {
+                            void* out, int out_dtype, const PlanBufs* plan, void* planes, cudaStream_t stream) {
     const int pairs = tokens * routes, ope = w->info.out_per_expert;
+    const int in_rows = x_per_pair ? pairs : tokens;
+    struct PlaneSet { int gs; const uint2* xq; const float2* gtab; };
+    std::vector<PlaneSet> sets;
+    char* planes_next = static_cast<char*>(planes);
     // Routes to experts this handle does not hold produce zeros (expert-parallel shards are
     // summed afterwards), so clear the output when the handle is partial.
     if (w->info.expert_end - w->info.expert_begin != w->info.n_experts)
@@ -212,7 +238,7 @@ static void mul_mat_id_impl(const mfqb_moe_weight* w, const void* x, int x_per_p
     for (size_t pi = 0; pi < w->pools.size(); ++pi) {
         const MoePool& pool = *w->pools[pi];
         if (!pool.held) continue;
-        GemvArgs a{};
+        GemvArgsB a{};
         a.w = pool.d;
         a.x = static_cast<const __nv_bfloat16*>(x);
         a.y = out;
@@ -231,18 +257,30 @@ static void mul_mat_id_impl(const mfqb_moe_weight* w, const void* x, int x_per_p
             a.n_experts = w->info.n_experts;
             const int max_tiles = pairs / 8 + std::min(pairs, w->info.n_experts);
             if (max_tiles > 65535) fail(MFQB_ERR_ARG, "mfqb_mul_mat_id: too many route tiles (%d)", max_tiles);
-            launch_nint_gemv_routed_tiles(a, max_tiles, w->info.device, stream);
+            const PlaneSet* ps = nullptr;
+            for (const PlaneSet& c : sets)
+                if (c.gs == pool.d.gs) ps = &c;
+            if (!ps) {   // first cohort of this group size: quantise the input rows once
+                PlaneSet n{pool.d.gs, nullptr, nullptr};
+                launch_x_planes(pool.d, x, in_rows, planes_next, &n.xq, &n.gtab, stream);
+                planes_next += (nint_bl_planes_bytes(pool.d, in_rows) + 255) / 256 * 256;
+                sets.push_back(n);
+                ps = &sets.back();
+            }
+            a.xq_g = ps->xq;
+            a.gtab_g = ps->gtab;
+            launch_nint_bl_gemv_tiles(a, max_tiles, w->info.device, stream);
             continue;
         }
         a.route_ids = ids;
         for (int p0 = 0; p0 < pairs; p0 += 32768) {   // gridDim.y limit
-            GemvArgs b = a;
+            GemvArgsB b = a;
             const int np = std::min(32768, pairs - p0);
             b.route_ids = ids + p0;
             b.y = static_cast<char*>(out) + (size_t)p0 * ope * (out_dtype == MFQB_F32 ? 4 : 2);
             if (p0 % routes) fail(MFQB_ERR_ARG, "mfqb_mul_mat_id: routes must divide 32768 for more than 32768 pairs");
             b.x = a.x + (size_t)(x_per_pair ? p0 : p0 / routes) * w->info.k;
-            launch_nint_gemv_routed(b, np, w->info.device, stream);
+            launch_nint_bl_gemv_routed(b, np, w->info.device, stream);
         }
     }
 }
@@ -257,11 +295,13 @@ int mfqb_mul_mat_id(const mfqb_moe_weight* w, const void* x, int x_per_pair, con
         DeviceGuard guard(w->info.device);
         const int pairs = tokens * routes;
         if (moe_use_tiles(w, pairs)) {   // larger batches: route plan in library scratch, batched kernel over its tiles
-            PlanBufs plan = PlanBufs::carve(scratch_get(w->info.device, PlanBufs::bytes(w->info.n_experts, pairs), 1), w->info.n_experts);
+            const size_t b_plan = PlanBufs::bytes(w->info.n_experts, pairs);
+            char* s = static_cast<char*>(scratch_get(w->info.device, b_plan + moe_planes_bytes(w, x_per_pair ? pairs : tokens), 1));
+            PlanBufs plan = PlanBufs::carve(s, w->info.n_experts);
             launch_route_plan(ids, pairs, w->info.n_experts, 8, plan.expert_bounds, plan.tile_bounds, plan.pair_order, stream);
-            mul_mat_id_impl(w, x, x_per_pair, ids, tokens, routes, out, out_dtype, &plan, stream);
+            mul_mat_id_impl(w, x, x_per_pair, ids, tokens, routes, out, out_dtype, &plan, s + b_plan, stream);
         } else {
-            mul_mat_id_impl(w, x, x_per_pair, ids, tokens, routes, out, out_dtype, nullptr, stream);
+            mul_mat_id_impl(w, x, x_per_pair, ids, tokens, routes, out, out_dtype, nullptr, nullptr, stream);
         }
     });
 }
@@ -280,7 +320,8 @@ int mfqb_moe_ffn(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* down, co
         const size_t b_gu = pairs * f2 * 4, b_hid = (pairs * f * 2 + 255) / 256 * 256, b_dn = pairs * h * 4;
         const bool tiles = moe_use_tiles(gate_up, (int)pairs);
         const size_t b_plan = tiles ? PlanBufs::bytes(gate_up->info.n_experts, pairs) : 0;
-        char* s = static_cast<char*>(scratch_get(gate_up->info.device, b_gu + b_hid + b_dn + b_plan));
+        const size_t b_pgu = tiles ? moe_planes_bytes(gate_up, tokens) : 0, b_pdn = tiles ? moe_planes_bytes(down, (int)pairs) : 0;
+        char* s = static_cast<char*>(scratch_get(gate_up->info.device, b_gu + b_hid + b_dn + b_plan + b_pgu + b_pdn));
         float* gu = reinterpret_cast<float*>(s);
         void* hid = s + b_gu;
         float* dn = reinterpret_cast<float*>(s + b_gu + b_hid);
@@ -289,9 +330,10 @@ int mfqb_moe_ffn(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* down, co
             plan = PlanBufs::carve(s + b_gu + b_hid + b_dn, gate_up->info.n_experts);
             launch_route_plan(ids, (int)pairs, gate_up->info.n_experts, 8, plan.expert_bounds, plan.tile_bounds, plan.pair_order, stream);
         }
-        mul_mat_id_impl(gate_up, x, 0, ids, tokens, routes, gu, MFQB_F32, tiles ? &plan : nullptr, stream);
+        char* planes = s + b_gu + b_hid + b_dn + b_plan;
+        mul_mat_id_impl(gate_up, x, 0, ids, tokens, routes, gu, MFQB_F32, tiles ? &plan : nullptr, planes, stream);
         launch_swiglu(gu, MFQB_F32, (int)pairs, f, hid, stream);
-        mul_mat_id_impl(down, hid, 1, ids, tokens, routes, dn, MFQB_F32, tiles ? &plan : nullptr, stream);
+        mul_mat_id_impl(down, hid, 1, ids, tokens, routes, dn, MFQB_F32, tiles ? &plan : nullptr, planes + b_pgu, stream);
         launch_weighted_reduce(dn, MFQB_F32, weights, tokens, routes, h, y, y_dtype, stream);
     });
 }
@@ -337,7 +379,10 @@ int mfqb_moe_ffn_static(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* d
         const size_t pairs = (size_t)tokens * routes;
         const size_t b_gu = pairs * f2 * 4, b_hid = (pairs * f * 2 + 255) / 256 * 256, b_dn = pairs * h * 4;
         const bool tiles = moe_use_tiles(gate_up, (int)pairs);
-        const size_t b_plan = tiles ? PlanBufs::bytes(gate_up->info.n_experts, pairs) : 0;
+        const size_t b_plan = tiles ? PlanBufs::bytes(gate_up->info.n_experts, pairs) + moe_planes_bytes(gate_up, tokens) +
+                                          moe_planes_bytes(down, (int)pairs)
+                                    : 0;
+        const size_t b_pgu = tiles ? moe_planes_bytes(gate_up, tokens) : 0;
         if (b_gu + b_hid + b_dn + b_plan > (size_t)MFQB_STATIC_SCRATCH_BYTES)
             fail(MFQB_ERR_ARG,
                  "mfqb_moe_ffn_static: %d tokens x %d routes need %llu bytes of scratch, the built-in array holds %llu; "
@@ -356,9 +401,10 @@ int mfqb_moe_ffn_static(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* d
             plan = PlanBufs::carve(s + b_gu + b_hid + b_dn, gate_up->info.n_experts);
             launch_route_plan(ids, (int)pairs, gate_up->info.n_experts, 8, plan.expert_bounds, plan.tile_bounds, plan.pair_order, stream);
         }
-        mul_mat_id_impl(gate_up, x, 0, ids, tokens, routes, gu, MFQB_F32, tiles ? &plan : nullptr, stream);
+        char* planes = reinterpret_cast<char*>(s) + b_gu + b_hid + b_dn + (tiles ? PlanBufs::bytes(gate_up->info.n_experts, pairs) : 0);   // inside the fixed array, after the plan
+        mul_mat_id_impl(gate_up, x, 0, ids, tokens, routes, gu, MFQB_F32, tiles ? &plan : nullptr, planes, stream);
         launch_swiglu(gu, MFQB_F32, (int)pairs, f, hid, stream);
-        mul_mat_id_impl(down, hid, 1, ids, tokens, routes, dn, MFQB_F32, tiles ? &plan : nullptr, stream);
+        mul_mat_id_impl(down, hid, 1, ids, tokens, routes, dn, MFQB_F32, tiles ? &plan : nullptr, planes + b_pgu, stream);
         launch_weighted_reduce(dn, MFQB_F32, weights, tokens, routes, h, y, y_dtype, stream);
     });
 }

@@ -1,0 +1,204 @@
+// Byte-lane NINT: decoder kernel and the launch planning of the GEMV kernels.
+#include <algorithm>
+#include <mutex>
+
+#include "common.h"
+#include "cuda_util.h"
+#include "nint_gemv_bl_launch.cuh"
+
+namespace mfqb {
+
+// ---- reference decoder on the GPU -----------------------------------------------------------
+// One thread per (row, group, quad of four slots): reads its codes and the two scale bytes
+// through the same accessors as the GEMV and writes w = fl(fl(d*q) - m), d = fl(ns*ss),
+// m = fl(nm*sm): three separately rounded float32 operations, as the reference decoder does
+// (mfq/quantize/nint_quant.py:896-908).
+template <int BITS>
+__global__ void nint_bl_dequant_kernel(const NintDevB w, void* out, int out_dtype) {
+    using BU = ByteUnit<BITS>;
+    const int quads = 2 * w.t8;
+    const size_t total = (size_t)w.n * w.ng * quads;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const int j = (int)(idx % quads);
+        const size_t rg = idx / quads;
+        const int grp = (int)(rg % w.ng), row = (int)(rg / w.ng);
+        if (4 * j >= w.gs) continue;
+        const int rb = row >> 4, q = row & 7, hi = (row >> 3) & 1, ch = grp / kChunkGroupsB, g = grp % kChunkGroupsB;
+        const int f = g >> 2, o = g & 3;
+        const int lane = 4 * q + 2 * (o & 1) + (j & 1);
+        const int reg = (f * w.t8 + (j >> 1)) * 4 + 2 * (o >> 1) + hi;
+        const uint32_t* rec = w.items + ((size_t)rb * w.nchunks + ch) * w.rec_words;
+        uint32_t uw[BU::U];
+#pragma unroll
+        for (int u = 0; u < BU::U; ++u) uw[u] = rec[((reg / BU::NP) * BU::U + u) * 32 + lane];
+        const uint32_t codes = BU::at(uw, reg % BU::NP);
+        const int slane = 4 * q + (g >> 1), sbyte = 8 * (2 * hi + (g & 1));
+        const float ss = (float)((rec[w.wc * 32 + slane] >> sbyte) & 0xFF), sm = (float)((rec[(w.wc + 1) * 32 + slane] >> sbyte) & 0xFF);
+        const uint32_t an = w.anchors[row];
+        const float2 nsm = __half22float2(*reinterpret_cast<const __half2*>(&an));
+        const float d = __fmul_rn(nsm.x, ss), m = __fmul_rn(nsm.y, sm);
+        const int k0 = grp * w.gs + 4 * j;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            if (4 * j + e < w.gs && k0 + e < w.k) {
+                const float v = __fsub_rn(__fmul_rn(d, (float)((codes >> (8 * e)) & 0xFF)), m);
+                const size_t off = (size_t)row * w.k + k0 + e;
+                if (out_dtype == MFQB_F32) reinterpret_cast<float*>(out)[off] = v;
+                else reinterpret_cast<__nv_bfloat16*>(out)[off] = __float2bfloat16_rn(v);
+            }
+        }
+    }
+}
+
+void launch_nint_bl_dequant(const NintDevB& w, void* out, int out_dtype, cudaStream_t s) {
+    const size_t total = (size_t)w.n * w.ng * 2 * w.t8;
+    const int block = 256;
+    const int grid = (int)std::min<size_t>((total + block - 1) / block, 148 * 32);
+    switch (w.bits) {
+        case 2: nint_bl_dequant_kernel<2><<<grid, block, 0, s>>>(w, out, out_dtype); break;
+        case 3: nint_bl_dequant_kernel<3><<<grid, block, 0, s>>>(w, out, out_dtype); break;
+        case 4: nint_bl_dequant_kernel<4><<<grid, block, 0, s>>>(w, out, out_dtype); break;
+        case 5: nint_bl_dequant_kernel<5><<<grid, block, 0, s>>>(w, out, out_dtype); break;
+        case 6: nint_bl_dequant_kernel<6><<<grid, block, 0, s>>>(w, out, out_dtype); break;
+        case 8: nint_bl_dequant_kernel<8><<<grid, block, 0, s>>>(w, out, out_dtype); break;
+        default: fail(MFQB_ERR_UNSUPPORTED, "NINT%d has no kernel", w.bits);
+    }
+    MFQB_CUDA(cudaGetLastError());
+}
+
+bool nint_bl_supported(int bits, int gs) {
+    const int t8 = (gs + 7) / 8;
+    return gs >= 8 && gs <= 64 && nint_bl_in_catalog(bits, t8);
+}
+
+// ---- GEMV launch planning ---------------------------------------------------------------------
+static void dispatch(const GemvArgsB& a, const GemvPlanB& p, cudaStream_t s, const char* what) {
+    cudaError_t e;
+    switch (a.w.bits) {
+        case 2: e = launch_gemv_bl_bits<2>(a, p, s); break;
+        case 3: e = launch_gemv_bl_bits<3>(a, p, s); break;
+        case 4: e = launch_gemv_bl_bits<4>(a, p, s); break;
+        case 5: e = launch_gemv_bl_bits<5>(a, p, s); break;
+        case 6: e = launch_gemv_bl_bits<6>(a, p, s); break;
+        case 8: e = launch_gemv_bl_bits<8>(a, p, s); break;
+        default: fail(MFQB_ERR_UNSUPPORTED, "NINT%d has no kernel", a.w.bits);
+    }
+    if (e != cudaSuccess) fail(MFQB_ERR_CUDA, "NINT%d gs=%d %s launch: %s", a.w.bits, a.w.gs, what, cudaGetErrorString(e));
+}
+
+constexpr size_t kGemvSmemLimit = 200 * 1024;
+
+static size_t gemv1_smem(const NintDevB& w, int rb_per_cta) {
+    return (size_t)rb_per_cta * 16 * 8 + (size_t)8 * gemv1_bl_stages(w.rec_words) * w.rec_words * 4;
+}
+static size_t gemvn_smem(const NintDevB& w, int rb_per_cta, int passes, int kt) {
+    const int mb = 2 * passes, tg = kt * kChunkGroupsB;
+    return (size_t)(mb + 1) * rb_per_cta * 16 * 4 + (size_t)mb * tg * 8 + (size_t)mb * tg * gemv1_bl_qstride(w.t8) * 8 +
+           (size_t)8 * gemv1_bl_stages(w.rec_words) * w.rec_words * 4;
+}
+// Bytes of the quantised planes of `rows` activation rows for this weight.
+size_t nint_bl_planes_bytes(const NintDevB& w, int rows) {
+    return (size_t)rows * w.nchunks * kChunkGroupsB * (gemv1_bl_qstride(w.t8) + 1) * 8;
+}
+
+// Quantises x [rows, k] into `planes` (nint_bl_planes_bytes): xq for all rows, then gtab.
+void launch_x_planes(const NintDevB& w, const void* x, int rows, void* planes, const uint2** xq_g, const float2** gtab_g, cudaStream_t s) {
+    const int ngp = w.nchunks * kChunkGroupsB, qs = gemv1_bl_qstride(w.t8);
+    uint2* xq = static_cast<uint2*>(planes);
+    float2* gtab = reinterpret_cast<float2*>(xq + (size_t)rows * ngp * qs);
+    *xq_g = xq;
+    *gtab_g = gtab;
+    // 64 groups per CTA: one pass of its 256 threads (four threads per group)
+    const dim3 grid((unsigned)((ngp + 63) / 64), (unsigned)rows);
+    const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
+    switch (w.t8) {
+        case 2: x_planes_kernel<2><<<grid, 256, 0, s>>>(xb, w.k, w.gs, ngp, 64, xq, gtab); break;
+        case 3: x_planes_kernel<3><<<grid, 256, 0, s>>>(xb, w.k, w.gs, ngp, 64, xq, gtab); break;
+        case 4: x_planes_kernel<4><<<grid, 256, 0, s>>>(xb, w.k, w.gs, ngp, 64, xq, gtab); break;
+        case 5: x_planes_kernel<5><<<grid, 256, 0, s>>>(xb, w.k, w.gs, ngp, 64, xq, gtab); break;
+        case 6: x_planes_kernel<6><<<grid, 256, 0, s>>>(xb, w.k, w.gs, ngp, 64, xq, gtab); break;
+        case 8: x_planes_kernel<8><<<grid, 256, 0, s>>>(xb, w.k, w.gs, ngp, 64, xq, gtab); break;
+        default: fail(MFQB_ERR_UNSUPPORTED, "group size %d has no kernel", w.gs);
+    }
+    MFQB_CUDA(cudaGetLastError());
+}
+
+// Library scratch for the planes of a plain batched product (grows on demand, per device).
+static void* planes_scratch(int device, size_t bytes) {
+    static std::mutex mu;
+    static DevBuf buf[64];
+    std::lock_guard<std::mutex> lock(mu);
+    if (device < 0 || device >= 64) fail(MFQB_ERR_ARG, "device index %d out of range", device);
+    if (buf[device].bytes < bytes) buf[device].alloc(bytes + bytes / 2);
+    return buf[device].p;
+}
+
+static int passes_for(int m) { return m <= 2 ? 1 : (m <= 4 ? 2 : 4); }
+
+// K tile of the batched kernel: whole K when its planes fit in about 48 KB, else a multiple of the
+// eight warps that does.
+static int gemvn_kt(const NintDevB& w, int passes) {
+    const size_t per_chunk = (size_t)2 * passes * kChunkGroupsB * 8 * (1 + gemv1_bl_qstride(w.t8));
+    int kt = (w.nchunks + 7) / 8 * 8;
+    while (kt > 8 && kt * per_chunk > 48 * 1024) kt -= 8;
+    return kt;
+}
+
+// y[m, n] = x[m, k] * W^T for m <= 8 (the caller loops larger batches)
+void launch_nint_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtype, int ldy, int device, cudaStream_t s) {
+    GemvArgsB a{};
+    a.w = w;
+    a.x = static_cast<const __nv_bfloat16*>(x);
+    a.y = y;
+    a.m = m;
+    a.ldy = ldy;
+    a.y_dtype = y_dtype;
+    GemvPlanB p;
+    const int sms = device_sm_count(device);
+    if (m == 1) {
+        // three CTAs per SM, all resident at once; row-blocks are split evenly inside the kernel
+        p.grid = std::min(w.nrb, 3 * sms);
+        a.rb_per_cta = (w.nrb + p.grid - 1) / p.grid;
+        p.smem = gemv1_smem(w, a.rb_per_cta);
+    } else {
+        launch_x_planes(w, x, m, planes_scratch(device, nint_bl_planes_bytes(w, m)), &a.xq_g, &a.gtab_g, s);
+        p.passes = passes_for(m);
+        a.kt_chunks = gemvn_kt(w, p.passes);
+        p.grid = std::min(w.nrb, (p.passes == 4 ? 2 : 3) * sms);
+        a.rb_per_cta = (w.nrb + p.grid - 1) / p.grid;
+        p.smem = gemvn_smem(w, a.rb_per_cta, p.passes, a.kt_chunks);
+    }
+    dispatch(a, p, s, "GEMV");
+}
+
+// Routed single-row launch over (splits, pairs) CTAs for one cohort; see GemvArgsB.
+void launch_nint_bl_gemv_routed(GemvArgsB a, int pairs, int device, cudaStream_t s) {
+    const NintDevB& w = a.w;
+    a.m = 1;
+    GemvPlanB p;
+    const int want = (3 * device_sm_count(device) + pairs - 1) / std::max(pairs, 1);
+    const int splits = std::max(1, std::min(a.rb_per_expert, want));
+    a.rb_per_cta = (a.rb_per_expert + splits - 1) / splits;
+    p.smem = gemv1_smem(w, a.rb_per_cta);
+    p.grid = splits;
+    p.grid_y = pairs;
+    dispatch(a, p, s, "routed GEMV");
+}
+
+// Batched kernel over route-plan tiles (up to 8 pairs of one expert each) for one cohort.
+void launch_nint_bl_gemv_tiles(GemvArgsB a, int max_tiles, int device, cudaStream_t s) {
+    const NintDevB& w = a.w;
+    a.m = 8;
+    GemvPlanB p;
+    p.passes = 4;
+    a.kt_chunks = gemvn_kt(w, p.passes);
+    const int want = (2 * device_sm_count(device) + max_tiles - 1) / std::max(max_tiles, 1);
+    const int splits = std::max(std::max(1, (a.rb_per_expert + 47) / 48), std::min(a.rb_per_expert, want));
+    a.rb_per_cta = (a.rb_per_expert + splits - 1) / splits;
+    p.smem = gemvn_smem(w, a.rb_per_cta, p.passes, a.kt_chunks);
+    p.grid = splits;
+    p.grid_y = max_tiles;
+    dispatch(a, p, s, "routed tile GEMV");
+}
+
+}  // namespace mfqb

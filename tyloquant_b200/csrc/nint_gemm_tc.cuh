@@ -4,13 +4,13 @@
 //
 // One CTA owns a tile of 128 weight rows x BN tokens and walks K one chunk (8 groups) at a time
 // through a two-stage shared-memory ring:
-//   * warps 0-7 (producers): warp r dequantises the chunk's record of row-block r of the tile
-//     (w = d*q - m in float32, rounded once to f16) into the A tile, and all eight warps copy the
-//     BN x chunk slice of x (f16) into the B tile with 16-byte cp.async; both tiles are K-major rows
-//     of 128 bytes with the 128-byte swizzle the tensor core expects;
-//   * warp 8: one thread issues tcgen05.mma (M = 128, N = BN, K = 16 per instruction) for the
+//   * 16 producer warps: a pair of warps dequantises the chunk's record of one row-block of the
+//     tile (w = d*q - m in float32, rounded once to f16) into the A atoms; one more warp feeds the
+//     BN x 64 slices of x (f16) into the B atoms with TMA; both are K-major rows of 128 bytes with
+//     the 128-byte swizzle the tensor core expects;
+//   * one warp: one thread issues tcgen05.mma (M = 128, N = BN, K = 16 per instruction) for the
 //     chunk, D accumulating in tensor memory, and tcgen05.commit hands the stage back;
-//   * epilogue: warps 0-7 read the accumulator with tcgen05.ld (lane = weight row) and store y.
+//   * epilogue: the producer warps read the accumulator with tcgen05.ld (lane = weight row) and store y.
 // f16 (not bf16) operands keep the dequantised weights within 2^-11 relative; x arrives as f16 from
 // a conversion pre-pass.  Every mbarrier wait is bounded: on expiry the kernel records an error
 // word and every role leaves through the common exit, which frees the tensor memory.
@@ -23,13 +23,13 @@
 #include <algorithm>
 #include <type_traits>
 
-#include "nint_gemv_m1.cuh"
+#include "nint_gemv1_bl.cuh"
 #include "tc05.cuh"
 
 namespace mfqb {
 
 struct GemmArgs {
-    NintDev w;
+    NintDevB w;
     const __half* x16;   // [m, kx] f16, kx = k rounded up to 8, zero padded
     int m, kx;
     void* y;             // [m, n]
@@ -44,16 +44,20 @@ constexpr int kGemmThreads = (kGemmProducerWarps + 2) * 32;   // + mma warp + x 
 
 // The ring is counted in atoms: one stage = 64 columns of K = a 128 x 64 f16 slab of W (16 KB) and
 // a BN x 64 f16 slab of x, each a K-major tile with the 128-byte swizzle.  A chunk of 8 groups is
-// ATOMS consecutive stages.  Two producer warps share one row-block record (groups 0-3 / 4-7).
-template <int BITS, int PER, int SW>
+// ATOMS consecutive stages.  Two producer warps share one row-block record: warp half f decodes
+// the registers of family f (groups 4f .. 4f+3) of the byte-lane layout.
+template <int BITS, int T>
 __global__ void __launch_bounds__(kGemmThreads, 1) nint_gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x_map) {
-    constexpr int G = kChunkGroups, HALF = PER / 2, GS = 4 * PER, KST = G * GS, ATOMS = KST / 64;
+    constexpr int G = kChunkGroupsB, GS = 8 * T, KST = G * GS, ATOMS = KST / 64;
     static_assert(KST % 64 == 0, "a chunk must be whole 64-element swizzle atoms");
-    using QU = PairUnit<BITS>;
-    using SU = PairUnit<SW>;
-    constexpr int WC = QU::words_for(G * PER), SWC = SU::words_for(16), REC = WC * 32 + SWC * 8;
+    using BU = ByteUnit<BITS>;
+    constexpr int WC = BU::words_for(8 * T), REC = (WC + 2) * 32;
+    // words of one family: registers [f * 4T, (f + 1) * 4T) start on a unit boundary when 4T is a
+    // multiple of the unit's register count; otherwise the warp reads the whole stream
+    constexpr bool SPLIT = (4 * T) % BU::NP == 0;
+    constexpr int FW = SPLIT ? (4 * T) / BU::NP * BU::U : WC;
     constexpr int NPROD = kGemmProducerWarps * 32;
-    const NintDev& w = a.w;
+    const NintDevB& w = a.w;
     const int BN = a.bn, NS = a.stages;
 
     extern __shared__ unsigned char smem_raw[];
@@ -84,18 +88,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1) nint_gemm_tc_kernel(const Gem
 
     if (warp < kGemmProducerWarps) {
         // ------------------------------ producers ------------------------------
-        const int rbl = warp >> 1, half = warp & 1;      // row-block of the tile, group half of the chunk
+        const int rbl = warp >> 1, f = warp & 1;         // row-block of the tile, family of the chunk
         const int rb = blockIdx.x * 8 + rbl;
         const bool rb_valid = rb < w.nrb;
         bool alive = true;
-        uint32_t nq[WC], ns_[SWC];
-        if (rb_valid) {
-            const uint32_t* rec = w.items + (size_t)rb * w.nchunks * REC;
+        const int w0 = SPLIT ? f * FW : 0;               // first code word of this warp's registers
+        const int r0 = SPLIT ? 0 : f * 4 * T;            // register index of (t = 0, a = 0) inside those words
+        uint32_t nq[FW], nsc[4];
+        auto fetch = [&](int ch) {
+            const uint32_t* rec = w.items + ((size_t)rb * w.nchunks + ch) * REC;
 #pragma unroll
-            for (int j = 0; j < WC; ++j) nq[j] = __ldg(rec + j * 32 + lane);
+            for (int j = 0; j < FW; ++j) nq[j] = __ldg(rec + (w0 + j) * 32 + lane);
+            // scale words of the lanes that own (rows q, q+8) x groups 4f + {0,1} and 4f + {2,3}
 #pragma unroll
-            for (int j = 0; j < SWC; ++j) ns_[j] = __ldg(rec + WC * 32 + j * 8 + q);
-        }
+            for (int j = 0; j < 4; ++j) nsc[j] = __ldg(rec + (WC + (j >> 1)) * 32 + 4 * q + 2 * f + (j & 1));
+        };
+        if (rb_valid) fetch(0);
         for (int ch = 0; ch < w.nchunks && alive; ++ch) {
             // acquire the chunk's stages
 #pragma unroll
@@ -106,62 +114,42 @@ __global__ void __launch_bounds__(kGemmThreads, 1) nint_gemm_tc_kernel(const Gem
             if (!alive) break;
             // weight record -> f16 rows of the A atoms (this warp: 16 rows x 4 groups)
             if (rb_valid) {
-                uint32_t qw[WC], sw[SWC];
+                uint32_t qw[FW], sc[4];
 #pragma unroll
-                for (int j = 0; j < WC; ++j) qw[j] = nq[j];
+                for (int j = 0; j < FW; ++j) qw[j] = nq[j];
 #pragma unroll
-                for (int j = 0; j < SWC; ++j) sw[j] = ns_[j];
-                if (ch + 1 < w.nchunks) {   // next record's words are requested before this one is decoded
-                    const uint32_t* rec = w.items + ((size_t)rb * w.nchunks + ch + 1) * REC;
-#pragma unroll
-                    for (int j = 0; j < WC; ++j) nq[j] = __ldg(rec + j * 32 + lane);
-#pragma unroll
-                    for (int j = 0; j < SWC; ++j) ns_[j] = __ldg(rec + WC * 32 + j * 8 + q);
-                }
+                for (int j = 0; j < 4; ++j) sc[j] = nsc[j];
+                if (ch + 1 < w.nchunks) fetch(ch + 1);   // next record's words are requested before this one is decoded
                 const uint32_t an_lo = __ldg(w.anchors + rb * 16 + q), an_hi = __ldg(w.anchors + rb * 16 + 8 + q);
                 const float2 f_lo = __half22float2(*reinterpret_cast<const __half2*>(&an_lo));   // (ns, nm)
                 const float2 f_hi = __half22float2(*reinterpret_cast<const __half2*>(&an_hi));
-                auto do_half = [&](auto half_tag) {
-                    constexpr int H = decltype(half_tag)::value;
+                // register a of a step: row q + 8(a&1), group 4f + 2(a>>1) + (c>>1); its scale bytes sit in
+                // word (a>>1) of the pair fetched above, byte 2(a&1) + (c>>1)
+                float d[4], mn[4];
 #pragma unroll
-                    for (int gg = 0; gg < 4; ++gg) {
-                        constexpr int dummy = 0;
-                        (void)dummy;
-                        const int g = H * 4 + gg;
-                        float s_lo, s_hi, m_lo[2], m_hi[2];
-                        pair_to_floats<SW>(SU::at(sw, g), s_lo, s_hi);
-                        pair_to_floats<SW>(SU::at(sw, 8 + g / 2), m_lo[0], m_lo[1]);       // sub-mins of row lo, groups 2*(g/2), +1
-                        pair_to_floats<SW>(SU::at(sw, 12 + g / 2), m_hi[0], m_hi[1]);      // row hi
-                        const float d[2] = {f_lo.x * s_lo, f_hi.x * s_hi};
-                        // codes enter as 128 + q (bf16 trick), so the constant term absorbs 128 * d
-                        const float off = (BITS <= 6) ? 128.f : 0.f;
-                        const float mn[2] = {fmaf(off, d[0], f_lo.y * m_lo[g & 1]), fmaf(off, d[1], f_hi.y * m_hi[g & 1])};
+                for (int aa = 0; aa < 4; ++aa) {
+                    const int sh = 8 * (2 * (aa & 1) + (c >> 1));
+                    const float ss = (float)((sc[aa >> 1] >> sh) & 0xFF), sm = (float)((sc[2 + (aa >> 1)] >> sh) & 0xFF);
+                    d[aa] = ((aa & 1) ? f_hi.x : f_lo.x) * ss;
+                    mn[aa] = ((aa & 1) ? f_hi.y : f_lo.y) * sm;
+                }
 #pragma unroll
-                        for (int r = 0; r < 2; ++r) {
-                            const int row = rbl * 16 + q + 8 * r;
+                for (int t = 0; t < T; ++t) {
 #pragma unroll
-                            for (int j = 0; j < HALF; ++j) {
-                                const uint32_t raw = QU::at(qw, (g * 2 + r) * HALF + j);
-                                float c0, c1;
-                                if constexpr (BITS <= 6) {
-                                    const uint32_t v = raw | kBf16x2_128;
-                                    c0 = __uint_as_float(v << 16);
-                                    c1 = __uint_as_float(v & 0xFFFF0000u);
-                                } else {
-                                    c0 = (float)(raw & 0xFFFFu);
-                                    c1 = (float)(raw >> 16);
-                                }
-                                const __half2 h = __floats2half2_rn(fmaf(d[r], c0, -mn[r]), fmaf(d[r], c1, -mn[r]));
-                                const int k = g * GS + c * PER + 2 * j, atom = k >> 6, kk = k & 63;
-                                unsigned char* at = tiles + ((ch * ATOMS + atom) % NS) * stage_bytes;
-                                *reinterpret_cast<__half2*>(at + row * 128 + (((kk >> 3) ^ q) << 4) + (kk & 7) * 2) = h;
-                            }
-                        }
+                    for (int aa = 0; aa < 4; ++aa) {
+                        const uint32_t v = BU::at(qw, r0 + t * 4 + aa);
+                        const int row = rbl * 16 + q + 8 * (aa & 1);
+                        const __half2 h01 = __floats2half2_rn(fmaf(d[aa], (float)(v & 0xFF), -mn[aa]), fmaf(d[aa], (float)((v >> 8) & 0xFF), -mn[aa]));
+                        const __half2 h23 = __floats2half2_rn(fmaf(d[aa], (float)((v >> 16) & 0xFF), -mn[aa]), fmaf(d[aa], (float)(v >> 24), -mn[aa]));
+                        const int k = (4 * f + 2 * (aa >> 1) + (c >> 1)) * GS + 8 * t + 4 * (c & 1), atom = k >> 6, kk = k & 63;
+                        unsigned char* at = tiles + ((ch * ATOMS + atom) % NS) * stage_bytes;
+                        uint2 pk;
+                        pk.x = *reinterpret_cast<const uint32_t*>(&h01);
+                        pk.y = *reinterpret_cast<const uint32_t*>(&h23);
+                        *reinterpret_cast<uint2*>(at + row * 128 + (((kk >> 3) ^ q) << 4) + (kk & 7) * 2) = pk;
                     }
-                };
-                if (half == 0) do_half(std::integral_constant<int, 0>{});
-                else do_half(std::integral_constant<int, 1>{});
-            } else if (half == 0) {
+                }
+            } else if (f == 0) {
                 // rows past the end of w: zero the row-block's 16 rows in every atom of the chunk
                 for (int i = lane; i < 16 * ATOMS * 8; i += 32) {
                     const int r = i / (ATOMS * 8), rest = i % (ATOMS * 8), atom = rest >> 3, c16 = rest & 7;
@@ -241,14 +229,14 @@ struct GemmPlan {
     int bn, stages, grid_x, grid_y;
     size_t smem;
 };
-// gs must be 16, 24 or 32 (a chunk is then whole swizzle atoms); returns bn = 0 otherwise.
-inline GemmPlan plan_nint_gemm(const NintDev& w, int m) {
+// The group size must be a multiple of 8 (a chunk is then whole swizzle atoms); returns bn = 0 otherwise.
+inline GemmPlan plan_nint_gemm(const NintDevB& w, int m) {
     GemmPlan p{};
-    if (!(w.gs == 16 || w.gs == 24 || w.gs == 32) || w.per * 4 != w.gs) return p;
-    const int atoms = kChunkGroups * w.gs / 64;
-    // wide token tiles amortise the dequantisation; 32-wide groups (4 atoms per chunk) take the
+    if (w.gs % 8 != 0 || w.t8 * 8 != w.gs) return p;
+    const int atoms = kChunkGroupsB * w.gs / 64;
+    // wide token tiles amortise the dequantisation; wide groups (4 or more atoms per chunk) take the
     // narrower tile so that the ring holds more than one chunk
-    int bn = (w.gs == 32) ? 128 : 256;
+    int bn = (w.gs >= 32) ? 128 : 256;
     while (bn > 64 && bn / 2 >= m) bn /= 2;
     p.bn = bn;
     const int stage_bytes = 128 * 128 + bn * 128;
@@ -262,5 +250,33 @@ inline GemmPlan plan_nint_gemm(const NintDev& w, int m) {
 
 template <int BITS>
 cudaError_t launch_nint_gemm_bits(const GemmArgs& a, const GemmPlan& p, const CUtensorMap& x_map, cudaStream_t stream);
+
+template <int BITS, int T>
+static cudaError_t launch_nint_gemm_one(const GemmArgs& a, const GemmPlan& p, const CUtensorMap& x_map, cudaStream_t stream) {
+    if constexpr (nint_bl_in_catalog(BITS, T)) {
+        auto kern = nint_gemm_tc_kernel<BITS, T>;
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem);
+        if (e != cudaSuccess) return e;
+        kern<<<dim3((unsigned)p.grid_x, (unsigned)p.grid_y), kGemmThreads, p.smem, stream>>>(a, x_map);
+        return cudaGetLastError();
+    } else {
+        return cudaErrorNotSupported;
+    }
+}
+
+// One translation unit per code width (nint_gemm_b*.cu) instantiates the launch table.
+#define MFQB_GEMM_INSTANTIATE(BITS)                                                                                                     \
+    template <>                                                                                                                         \
+    cudaError_t launch_nint_gemm_bits<BITS>(const GemmArgs& a, const GemmPlan& p, const CUtensorMap& x_map, cudaStream_t stream) {      \
+        switch (a.w.t8) {                                                                                                               \
+            case 2: return launch_nint_gemm_one<BITS, 2>(a, p, x_map, stream);                                                          \
+            case 3: return launch_nint_gemm_one<BITS, 3>(a, p, x_map, stream);                                                          \
+            case 4: return launch_nint_gemm_one<BITS, 4>(a, p, x_map, stream);                                                          \
+            case 5: return launch_nint_gemm_one<BITS, 5>(a, p, x_map, stream);                                                          \
+            case 6: return launch_nint_gemm_one<BITS, 6>(a, p, x_map, stream);                                                          \
+            case 8: return launch_nint_gemm_one<BITS, 8>(a, p, x_map, stream);                                                          \
+            default: return cudaErrorNotSupported;                                                                                      \
+        }                                                                                                                               \
+    }
 
 }  // namespace mfqb

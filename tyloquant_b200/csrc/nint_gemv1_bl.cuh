@@ -1,0 +1,378 @@
+// Single-row (m = 1) GEMV for NINT weights in the byte-lane layout: the decode hot path.
+//
+// The weights never leave the integer domain.  The activation row is quantised once per CTA,
+// group by group, to 16-bit integers  x_k ~ sx_g * xi_k  (sx_g a power of two chosen from the
+// group's largest magnitude, so a bf16 input is reproduced exactly unless it is more than 2^7
+// below that magnitude) and split into a low unsigned and a high signed byte plane.  The int8
+// tensor-core instruction mma.m16n8k32 then forms  D[row][g] = sum_k q[row][k] * xi[k]  exactly:
+// with one activation row the n8 slot of the tile is free, so the eight columns carry the eight
+// *groups* of a chunk.  The B operand is block-diagonal (column g holds x only at the k-slots of
+// group g), and one accumulator tile per byte plane collects all groups of the chunk.  The
+// per-group integer sub-scales and sub-mins and the row anchors are applied once per chunk in
+// float32 -- lane (q, c) owns groups 2c, 2c+1 of rows q, q+8, exactly the scale bytes its two
+// private scale words hold -- and a quad reduction adds the eight groups:
+//
+//   y[row] = sum_g sx_g * ( ns*ss_g * D[row][g]  -  nm*sm_g * X_g ),     X_g = sum_k xi_k.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "common.h"
+#include "lane_unit.h"
+#include "nint_blayout.h"
+
+namespace mfqb {
+
+struct GemvArgsB {
+    NintDevB w;
+    const __nv_bfloat16* x;  // [m, k]
+    void* y;                 // [m, ldy]
+    int m, ldy, y_dtype;
+    int rb_per_cta;          // row-blocks per CTA (upper bound; the kernel splits evenly)
+    // Routed mode (expert matmul, "mul_mat_id"): blockIdx.y is a (token, route) pair; the pair's
+    // expert selects a block of rb_per_expert row-blocks of w.  A CTA whose expert does not
+    // live in this cohort (pool) returns at once.
+    const int* route_ids;    // [pairs] expert of each pair; nullptr = plain GEMV
+    const int* expert_pool;  // [experts] cohort index of each expert (-1: not held here)
+    const int* expert_local; // [experts] position of the expert inside its cohort
+    int pool;                // cohort this launch covers
+    int rb_per_expert;       // rows_per_expert / 16
+    int routes;              // routes per token (R)
+    int x_per_pair;          // 1: x is [pairs, k]; 0: x is [tokens, k], shared by the token's routes
+    // Tile mode of the batched kernel: blockIdx.y is a tile of pairs of one expert, taken from a
+    // route plan (expert_bounds / tile_bounds / pair_order of mfqb_moe_route_plan).
+    const int* expert_bounds;
+    const int* tile_bounds;
+    const int* pair_order;
+    int n_experts;
+    int kt_chunks;           // batched kernel: chunks of K staged per tile (a multiple of the warps per CTA)
+    // Batched kernel: the activation rows already quantised by x_planes_kernel, row r at
+    // xq_g + r * ngp * QS and gtab_g + r * ngp (ngp = nchunks * 8 groups, QS quads per group).
+    const uint2* xq_g;
+    const float2* gtab_g;
+};
+
+__device__ __forceinline__ void pdl_launch_dependents_b() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait_b() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+__device__ __forceinline__ void cp_async16_b(void* smem_dst, const void* gsrc) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit_b() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+
+// D (s32) += A (u8, 16x32) * B (u8 or s8, 32x8)
+__device__ __forceinline__ void imma_u8u8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void imma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Records per warp ring: about 6 KB of ring per warp, between 2 and 6 stages.
+__host__ __device__ constexpr int gemv1_bl_stages(int rec_words) {
+    return 6144 / (rec_words * 4) < 2 ? 2 : (6144 / (rec_words * 4) > 6 ? 6 : 6144 / (rec_words * 4));
+}
+// Quads (uint2: low-plane word, high-plane word) per group in the staged activation row: 2T
+// quads, padded so that the eight groups a warp reads together start in distinct banks.
+__host__ __device__ constexpr int gemv1_bl_qstride(int t8) { return (2 * t8) % 8 == 0 ? 2 * t8 + 1 : 2 * t8; }
+
+// Quantises groups [g0, g0 + ngroups) of one activation row into shared memory (ngroups a multiple
+// of 8): xq[gl * QS + j] = (low bytes, high bytes) of the four slots 4j..4j+3 of group g0 + gl,
+// gtab[gl] = (sx_g, sx_g * X_g).  Four threads per group; every thread of the CTA must call it.
+template <int T>
+__device__ __forceinline__ void stage_x_planes(const __nv_bfloat16* __restrict__ xrow, int k, int gs, int g0, int ngroups, uint2* xq,
+                                               float2* gtab) {
+    constexpr int QS = gemv1_bl_qstride(T);
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(xrow) & 7) == 0;
+    for (int u = threadIdx.x; u < ngroups * 4; u += blockDim.x) {
+        const int gl = u >> 2, g = g0 + gl, c = u & 3;
+        float v[(2 * T + 3) / 4][4];
+        uint32_t ab = 0u;   // largest magnitude of the group as float bits (orders like the value; NaN is largest)
+#pragma unroll
+        for (int jj = 0; jj < (2 * T + 3) / 4; ++jj) {
+            const int j = c + 4 * jj, k0 = g * gs + 4 * j;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[jj][i] = 0.f;
+            if (j < 2 * T && 4 * j < gs) {
+                if (vec_ok && (k0 & 3) == 0 && k0 + 3 < k && 4 * j + 3 < gs) {
+                    const uint2 raw = __ldg(reinterpret_cast<const uint2*>(xrow + k0));
+                    v[jj][0] = __uint_as_float(raw.x << 16);
+                    v[jj][1] = __uint_as_float(raw.x & 0xFFFF0000u);
+                    v[jj][2] = __uint_as_float(raw.y << 16);
+                    v[jj][3] = __uint_as_float(raw.y & 0xFFFF0000u);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (4 * j + i < gs && k0 + i < k) v[jj][i] = __bfloat162float(xrow[k0 + i]);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) ab = max(ab, __float_as_uint(v[jj][i]) & 0x7FFFFFFFu);
+        }
+        ab = max(ab, __shfl_xor_sync(0xffffffffu, ab, 1));
+        ab = max(ab, __shfl_xor_sync(0xffffffffu, ab, 2));
+        const uint32_t eb = max(ab >> 23, 15u);
+        // eb = 255: an infinity or NaN in the group; its scale becomes NaN and so does every output
+        const float sx = __uint_as_float(eb >= 255u ? 0x7FC00000u : (eb - 14u) << 23);
+        const float inv = __uint_as_float((268u - min(eb, 254u)) << 23);
+        constexpr float kMagic = 12582912.f;   // 1.5 * 2^23: the low 16 mantissa bits hold round(x * inv) in two's complement
+        float xs = 0.f;
+#pragma unroll
+        for (int jj = 0; jj < (2 * T + 3) / 4; ++jj) {
+            const int j = c + 4 * jj;
+            uint32_t f[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float r = fmaf(v[jj][i], inv, kMagic);
+                xs += r - kMagic;
+                f[i] = __float_as_uint(r);
+            }
+            const uint32_t t01 = __byte_perm(f[0], f[1], 0x5140), t23 = __byte_perm(f[2], f[3], 0x5140);
+            if (j < 2 * T) xq[gl * QS + j] = make_uint2(__byte_perm(t01, t23, 0x5410), __byte_perm(t01, t23, 0x7632));
+        }
+        xs += __shfl_xor_sync(0xffffffffu, xs, 1);
+        xs += __shfl_xor_sync(0xffffffffu, xs, 2);
+        if (c == 0) gtab[gl] = make_float2(sx, sx * xs);
+    }
+}
+
+// Per-warp form for the single-row kernel: the warp quantises the eight groups of one chunk in
+// registers.  Lane 4g + c loads quads c, c + 4, ... of group g (x_chunk_load), then x_chunk_quant
+// returns what the lane feeds to the tensor core for its column (= group g): the byte planes of
+// quads 2t + (c & 1), t = 0..T-1 -- its own quads and those of lane c ^ 2 -- and the (scale,
+// scaled sum) pairs of groups 2c and 2c + 1.
+template <int T>
+struct XChunkRaw {
+    static constexpr int JJ = (2 * T + 3) / 4;
+    uint2 v[JJ];   // four bf16 each
+};
+template <int T>
+__device__ __forceinline__ void x_chunk_load(const __nv_bfloat16* __restrict__ xrow, bool vec_ok, int k, int gs, int g, int c,
+                                             XChunkRaw<T>& raw) {
+#pragma unroll
+    for (int jj = 0; jj < XChunkRaw<T>::JJ; ++jj) {
+        const int j = c + 4 * jj, k0 = g * gs + 4 * j;
+        raw.v[jj] = make_uint2(0u, 0u);
+        if (j < 2 * T && 4 * j < gs) {
+            if (vec_ok && (k0 & 3) == 0 && k0 + 3 < k && 4 * j + 3 < gs) {
+                raw.v[jj] = __ldg(reinterpret_cast<const uint2*>(xrow + k0));
+            } else {
+                const unsigned short* xb = reinterpret_cast<const unsigned short*>(xrow);
+                uint32_t e[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (4 * j + i < gs && k0 + i < k) e[i] = __ldg(xb + k0 + i);
+                raw.v[jj] = make_uint2(e[0] | (e[1] << 16), e[2] | (e[3] << 16));
+            }
+        }
+    }
+}
+template <int T>
+__device__ __forceinline__ void x_chunk_quant(const XChunkRaw<T>& raw, int c, uint32_t (&xlo)[T], uint32_t (&xhi)[T], float4& gt) {
+    constexpr int JJ = XChunkRaw<T>::JJ;
+    float v[JJ][4];
+    uint32_t ab = 0u;   // largest magnitude of the group as float bits (orders like the value; NaN is largest)
+#pragma unroll
+    for (int jj = 0; jj < JJ; ++jj) {
+        v[jj][0] = __uint_as_float(raw.v[jj].x << 16);
+        v[jj][1] = __uint_as_float(raw.v[jj].x & 0xFFFF0000u);
+        v[jj][2] = __uint_as_float(raw.v[jj].y << 16);
+        v[jj][3] = __uint_as_float(raw.v[jj].y & 0xFFFF0000u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) ab = max(ab, __float_as_uint(v[jj][i]) & 0x7FFFFFFFu);
+    }
+    ab = max(ab, __shfl_xor_sync(0xffffffffu, ab, 1));
+    ab = max(ab, __shfl_xor_sync(0xffffffffu, ab, 2));
+    const uint32_t eb = max(ab >> 23, 15u);
+    const float sx = __uint_as_float(eb >= 255u ? 0x7FC00000u : (eb - 14u) << 23);   // NaN for a group holding inf or NaN
+    const float inv = __uint_as_float((268u - min(eb, 254u)) << 23);
+    constexpr float kMagic = 12582912.f;   // 1.5 * 2^23
+    float xs = 0.f;
+    uint32_t mine_lo[JJ], mine_hi[JJ];
+#pragma unroll
+    for (int jj = 0; jj < JJ; ++jj) {
+        uint32_t f[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float r = fmaf(v[jj][i], inv, kMagic);
+            xs += r - kMagic;
+            f[i] = __float_as_uint(r);
+        }
+        const uint32_t t01 = __byte_perm(f[0], f[1], 0x5140), t23 = __byte_perm(f[2], f[3], 0x5140);
+        mine_lo[jj] = __byte_perm(t01, t23, 0x5410);
+        mine_hi[jj] = __byte_perm(t01, t23, 0x7632);
+    }
+    xs += __shfl_xor_sync(0xffffffffu, xs, 1);
+    xs += __shfl_xor_sync(0xffffffffu, xs, 2);
+    const float sxx = sx * xs;
+    // quad 2t + (c&1) belongs to this lane when (t & 1) == (c >> 1), else to lane c ^ 2; either way slot t >> 1
+    const bool own_even = (c >> 1) == 0;
+#pragma unroll
+    for (int jj = 0; jj < JJ; ++jj) {
+        const uint32_t other_lo = __shfl_xor_sync(0xffffffffu, mine_lo[jj], 2), other_hi = __shfl_xor_sync(0xffffffffu, mine_hi[jj], 2);
+        if (2 * jj < T) {
+            xlo[2 * jj] = own_even ? mine_lo[jj] : other_lo;
+            xhi[2 * jj] = own_even ? mine_hi[jj] : other_hi;
+        }
+        if (2 * jj + 1 < T) {
+            xlo[2 * jj + 1] = own_even ? other_lo : mine_lo[jj];
+            xhi[2 * jj + 1] = own_even ? other_hi : mine_hi[jj];
+        }
+    }
+    gt.x = __shfl_sync(0xffffffffu, sx, 8 * c);
+    gt.y = __shfl_sync(0xffffffffu, sxx, 8 * c);
+    gt.z = __shfl_sync(0xffffffffu, sx, 8 * c + 4);
+    gt.w = __shfl_sync(0xffffffffu, sxx, 8 * c + 4);
+}
+
+// Shared memory: partial sums [rb_per_cta][16] f32 | anchors [rb_per_cta][16] u32 | per warp a
+// ring of S item records.  Every warp streams its own items (chunk-major) through its ring with
+// 16-byte asynchronous copies; the first S items are requested before the kernel waits for its
+// predecessor in the stream, since weights are constants.  The activation row is read straight
+// from global memory, one chunk ahead, and quantised in registers by the warp that needs it.
+template <int BITS, int T>
+__global__ void __launch_bounds__(256, (ByteUnit<BITS>::words_for(8 * T) > 48 ? 1 : (ByteUnit<BITS>::words_for(8 * T) > 24 ? 2 : 3))) nint_gemv1_bl_kernel(const GemvArgsB a) {
+    constexpr int G = kChunkGroupsB;
+    using BU = ByteUnit<BITS>;
+    constexpr int WC = BU::words_for(8 * T), REC = (WC + 2) * 32;
+    constexpr int S = gemv1_bl_stages(REC);
+    const NintDevB& w = a.w;
+
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    const int q = lane >> 2, c = lane & 3;
+    float* ypart = reinterpret_cast<float*>(smem);
+    uint32_t* anch = reinterpret_cast<uint32_t*>(ypart + (size_t)a.rb_per_cta * 16);
+    uint32_t* ring = anch + (size_t)a.rb_per_cta * 16 + (size_t)warp * S * REC;
+
+    // balanced split of the row-blocks over gridDim.x: CTA b owns [b*R/grid, (b+1)*R/grid) of the
+    // R row-blocks of the whole matrix, or of its pair's expert in routed mode
+    int rb_base = 0, rb_total = w.nrb;
+    const __nv_bfloat16* xrow = a.x;
+    size_t y_off = 0;
+    if (a.route_ids != nullptr) {
+        pdl_wait_b();   // the routing table comes from the previous kernel
+        const int pair = blockIdx.y, e = a.route_ids[pair];
+        if (e < 0 || a.expert_pool[e] != a.pool) return;
+        rb_total = a.rb_per_expert;
+        rb_base = a.expert_local[e] * a.rb_per_expert;
+        xrow += (size_t)(a.x_per_pair ? pair : pair / a.routes) * w.k;
+        y_off = (size_t)pair * a.ldy;
+    }
+    const int rbl0 = (int)(((long long)blockIdx.x * rb_total) / gridDim.x);
+    const int nrb = (int)(((long long)(blockIdx.x + 1) * rb_total) / gridDim.x) - rbl0;
+    const int rb0 = rb_base + rbl0;
+    const int row_limit = a.route_ids != nullptr ? a.ldy : w.n;   // rows this problem has (an expert's rows are padded to whole blocks)
+
+    // items of this warp, chunk-major: chunk = warp, warp + nwarps, ...; inside a chunk every
+    // row-block of the CTA.  Two cursors walk that sequence (issue runs S items ahead).
+    const int my_segs = warp < w.nchunks ? (w.nchunks - warp + nwarps - 1) / nwarps : 0;
+    const int n_mine = my_segs * nrb;
+    int iss_i = 0, iss_seg = warp, iss_rbl = 0, iss_stage = 0;
+    auto issue = [&]() {
+        if (iss_i < n_mine) {
+            const uint32_t* src = w.items + ((size_t)(rb0 + iss_rbl) * w.nchunks + iss_seg) * REC;
+            uint32_t* dst = ring + iss_stage * REC;
+#pragma unroll
+            for (int off = 0; off < REC; off += 128)
+                if (off + 128 <= REC || lane * 4 < REC - off) cp_async16_b(dst + off + lane * 4, src + off + lane * 4);
+        }
+        cp_async_commit_b();   // one group per item slot, empty past the end: keeps the wait count uniform
+        ++iss_i;
+        if (++iss_rbl == nrb) { iss_rbl = 0; iss_seg += nwarps; }
+        if (++iss_stage == S) iss_stage = 0;
+    };
+
+    pdl_launch_dependents_b();
+#pragma unroll
+    for (int i = 0; i < S; ++i) issue();
+    for (int i = tid; i < nrb * 16; i += blockDim.x) {
+        ypart[i] = 0.f;
+        anch[i] = __ldg(w.anchors + rb0 * 16 + i);
+    }
+    __syncthreads();
+    pdl_wait_b();
+
+    // Block-diagonal B: lane (q, c) feeds column q = group q of the chunk, which is octet q&3 of
+    // the steps of family q>>2; its bytes are live only where the fragment's k-range (octet c>>1
+    // of b0, octet 2 + (c>>1) of b1) is that octet.
+    const bool live = (c >> 1) == (q & 1);
+    const uint32_t m00 = (live && (q >> 1) == 0) ? 0xFFFFFFFFu : 0u, m01 = (live && (q >> 1) == 1) ? 0xFFFFFFFFu : 0u;
+    const uint32_t m10 = (live && (q >> 1) == 2) ? 0xFFFFFFFFu : 0u, m11 = (live && (q >> 1) == 3) ? 0xFFFFFFFFu : 0u;
+
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(xrow) & 7) == 0;
+    int cur_seg = -1;
+    uint32_t xlo[T], xhi[T];
+    float4 gt = make_float4(0.f, 0.f, 0.f, 0.f);   // (sx, sx*X) of groups 2c, 2c+1 of the chunk
+    XChunkRaw<T> raw;                              // the activations of the warp's next chunk, requested one chunk ahead
+    if (n_mine > 0) x_chunk_load<T>(xrow, vec_ok, w.k, w.gs, warp * G + q, c, raw);
+
+    int seg = warp, rbl = 0, stage = 0;
+    for (int i = 0; i < n_mine; ++i) {
+        if (seg != cur_seg) {
+            cur_seg = seg;
+            x_chunk_quant<T>(raw, c, xlo, xhi, gt);
+            if (seg + nwarps < w.nchunks) x_chunk_load<T>(xrow, vec_ok, w.k, w.gs, (seg + nwarps) * G + q, c, raw);
+        }
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(S - 1) : "memory");
+        __syncwarp();
+        const uint32_t* rec = ring + stage * REC;
+        uint32_t qw[WC];
+#pragma unroll
+        for (int j = 0; j < WC; ++j) qw[j] = rec[j * 32 + lane];
+        const uint32_t s0 = rec[WC * 32 + lane], s1 = rec[(WC + 1) * 32 + lane];
+        __syncwarp();          // every lane has read the stage before it is refilled
+        issue();
+        int dlo[4] = {0, 0, 0, 0}, dhi[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int f = 0; f < 2; ++f) {
+#pragma unroll
+            for (int t = 0; t < T; ++t) {
+                const int r = (f * T + t) * 4;
+                const uint32_t a0 = BU::at(qw, r), a1 = BU::at(qw, r + 1), a2 = BU::at(qw, r + 2), a3 = BU::at(qw, r + 3);
+                const uint32_t mb0 = f ? m10 : m00, mb1 = f ? m11 : m01;
+                imma_u8u8(dlo, a0, a1, a2, a3, xlo[t] & mb0, xlo[t] & mb1);
+                imma_u8s8(dhi, a0, a1, a2, a3, xhi[t] & mb0, xhi[t] & mb1);
+            }
+        }
+        // D = 256 * high + low: sums of q * xi for rows (q, q+8) x groups (2c, 2c+1)
+        const float d0 = (float)(dhi[0] * 256 + dlo[0]) * gt.x, d1 = (float)(dhi[1] * 256 + dlo[1]) * gt.z;
+        const float d2 = (float)(dhi[2] * 256 + dlo[2]) * gt.x, d3 = (float)(dhi[3] * 256 + dlo[3]) * gt.z;
+        const uint32_t an_lo = anch[rbl * 16 + q], an_hi = anch[rbl * 16 + q + 8];
+        const float2 f_lo = __half22float2(*reinterpret_cast<const __half2*>(&an_lo));   // (ns, nm)
+        const float2 f_hi = __half22float2(*reinterpret_cast<const __half2*>(&an_hi));
+        const float ss0 = (float)(s0 & 0xFF), ss1 = (float)((s0 >> 8) & 0xFF), ss2 = (float)((s0 >> 16) & 0xFF), ss3 = (float)(s0 >> 24);
+        const float sm0 = (float)(s1 & 0xFF), sm1 = (float)((s1 >> 8) & 0xFF), sm2 = (float)((s1 >> 16) & 0xFF), sm3 = (float)(s1 >> 24);
+        float v_lo = f_lo.x * fmaf(ss1, d1, ss0 * d0) - f_lo.y * fmaf(sm1, gt.w, sm0 * gt.y);
+        float v_hi = f_hi.x * fmaf(ss3, d3, ss2 * d2) - f_hi.y * fmaf(sm3, gt.w, sm2 * gt.y);
+        // the four lanes of a quad hold different groups of the same two rows
+        v_lo += __shfl_xor_sync(0xffffffffu, v_lo, 1);
+        v_hi += __shfl_xor_sync(0xffffffffu, v_hi, 1);
+        v_lo += __shfl_xor_sync(0xffffffffu, v_lo, 2);
+        v_hi += __shfl_xor_sync(0xffffffffu, v_hi, 2);
+        if (c == 0) {
+            atomicAdd(ypart + rbl * 16 + q, v_lo);
+            atomicAdd(ypart + rbl * 16 + q + 8, v_hi);
+        }
+        if (++rbl == nrb) { rbl = 0; seg += nwarps; }
+        if (++stage == S) stage = 0;
+    }
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();
+    for (int i = tid; i < nrb * 16; i += blockDim.x) {
+        const int row = rbl0 * 16 + i;   // row inside the problem (matrix, or the pair's expert)
+        if (row < row_limit) {
+            const float v = ypart[i];
+            if (a.y_dtype == 0 /* MFQB_F32 */) reinterpret_cast<float*>(a.y)[y_off + row] = v;
+            else reinterpret_cast<__nv_bfloat16*>(a.y)[y_off + row] = __float2bfloat16_rn(v);
+        }
+    }
+}
+
+}  // namespace mfqb

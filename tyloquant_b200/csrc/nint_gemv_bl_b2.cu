@@ -1,0 +1,6 @@
+// NINT2 instantiations of the byte-lane GEMV kernels.
+#include "nint_gemv_bl_launch.cuh"
+
+namespace mfqb {
+MFQB_GEMV_BL_INSTANTIATE(2)
+}  // namespace mfqb

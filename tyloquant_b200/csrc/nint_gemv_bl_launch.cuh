@@ -1,0 +1,66 @@
+// Per-code-width launch tables of the byte-lane GEMV kernels; one translation unit per width
+// (nint_gemv_bl_b*.cu) instantiates launch_gemv_bl_bits<BITS> so the widths compile in parallel.
+#pragma once
+#include "nint_gemvn_bl.cuh"
+
+namespace mfqb {
+
+struct GemvPlanB {
+    int grid = 1, grid_y = 1, threads = 256;
+    int passes = 0;      // 0: single-row kernel; 1, 2, 4: batched kernel with that many two-row passes
+    size_t smem = 0;
+};
+
+template <int BITS>
+cudaError_t launch_gemv_bl_bits(const GemvArgsB& a, const GemvPlanB& p, cudaStream_t stream);
+
+template <typename Kernel>
+static cudaError_t launch_kernel_pdl(Kernel kernel, const GemvArgsB& a, const GemvPlanB& p, cudaStream_t stream) {
+    if (p.smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem);
+        if (e != cudaSuccess) return e;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)p.grid, (unsigned)p.grid_y);
+    cfg.blockDim = dim3((unsigned)p.threads);
+    cfg.dynamicSmemBytes = p.smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, a);
+}
+
+template <int BITS, int T>
+static cudaError_t launch_gemv_bl_one(const GemvArgsB& a, const GemvPlanB& p, cudaStream_t stream) {
+    switch (p.passes) {
+        case 0: return launch_kernel_pdl(nint_gemv1_bl_kernel<BITS, T>, a, p, stream);
+        case 1: return launch_kernel_pdl(nint_gemvn_bl_kernel<BITS, T, 1>, a, p, stream);
+        case 2: return launch_kernel_pdl(nint_gemvn_bl_kernel<BITS, T, 2>, a, p, stream);
+        case 4: return launch_kernel_pdl(nint_gemvn_bl_kernel<BITS, T, 4>, a, p, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+#define MFQB_GEMV_BL_INSTANTIATE(BITS)                                                                              \
+    template <int T>                                                                                                \
+    static cudaError_t launch_if_catalog(const GemvArgsB& a, const GemvPlanB& p, cudaStream_t stream) {             \
+        if constexpr (nint_bl_in_catalog(BITS, T)) return launch_gemv_bl_one<BITS, T>(a, p, stream);                \
+        else return cudaErrorInvalidValue;                                                                          \
+    }                                                                                                               \
+    template <>                                                                                                     \
+    cudaError_t launch_gemv_bl_bits<BITS>(const GemvArgsB& a, const GemvPlanB& p, cudaStream_t stream) {            \
+        switch (a.w.t8) {                                                                                           \
+            case 2: return launch_if_catalog<2>(a, p, stream);                                                      \
+            case 3: return launch_if_catalog<3>(a, p, stream);                                                      \
+            case 4: return launch_if_catalog<4>(a, p, stream);                                                      \
+            case 5: return launch_if_catalog<5>(a, p, stream);                                                      \
+            case 6: return launch_if_catalog<6>(a, p, stream);                                                      \
+            case 8: return launch_if_catalog<8>(a, p, stream);                                                      \
+            default: return cudaErrorInvalidValue;                                                                  \
+        }                                                                                                           \
+    }
+
+}  // namespace mfqb

@@ -74,7 +74,7 @@ __global__ void __launch_bounds__(256, 3) nint_gemv_m1_kernel(const GemvArgs a) 
     // row-block of the CTA.  Two cursors walk that sequence (issue runs S items ahead); they are
     // advanced incrementally -- no division in the loop.
     const int my_segs = warp < w.nchunks ? (w.nchunks - warp + nwarps - 1) / nwarps : 0;
-    const int n_mine = my_segs * nrb;
+    const int n_mine = a.stages == -1 ? 0 : my_segs * nrb;
     int iss_i = 0, iss_seg = warp, iss_rbl = 0, iss_stage = 0;
     auto issue = [&]() {
         if (iss_i < n_mine) {
@@ -162,6 +162,17 @@ __global__ void __launch_bounds__(256, 3) nint_gemv_m1_kernel(const GemvArgs a) 
         for (int j = 0; j < SWC; ++j) sw[j] = rec[WC * 32 + j * 8 + q];
         __syncwarp();          // every lane has read the stage before it is refilled
         issue();
+        if (a.stages == -2) {   // DBG: memory pipeline only
+            uint32_t v = 0;
+#pragma unroll
+            for (int j = 0; j < WC; ++j) v ^= qw[j];
+#pragma unroll
+            for (int j = 0; j < SWC; ++j) v ^= sw[j];
+            if (v == 0x12345678u) atomicAdd(ypart + rbl * 16 + q, 1.f);
+            if (++rbl == nrb) { rbl = 0; seg += nwarps; }
+            if (++stage == S) stage = 0;
+            continue;
+        }
 
         const float seed0 = (NPL == 2 ? -128.f * 17.f : -128.f) * xs0, seed1 = (NPL == 2 ? -128.f * 17.f : -128.f) * xs1;
         float ch[4][4], hi[2][4];   // chains; hi = high nibbles (8-bit codes); seeds are added at the end

@@ -1,0 +1,233 @@
+// Batched GEMV (2 to 8 activation rows per pass) for NINT weights in the byte-lane layout.
+//
+// Same integer pipeline as the single-row kernel (activation rows quantised per group to 16-bit
+// integers, two byte planes, int8 tensor-core mma with a block-diagonal B), but the eight
+// columns of a step (f, t) now carry two batch rows x the four groups of the family:
+//
+//   column n  ->  batch row 2p + (n >> 2),  group 4f + (n & 3)          (pass p = 0..P-1)
+//
+// so a pass of two rows costs as many mma as the single-row kernel and a batch of 2P rows
+// decodes every weight once.  The accumulator fragment gives lane (q, c) the sums of weight
+// rows q, q+8 for batch row 2p + (c>>1) and groups 4f + 2(c&1) + {0, 1}; the scale bytes of
+// those (rows, groups) are the scale words of lane 4q + 2f + (c&1) of the record.  Lanes c and
+// c^1 together hold the four groups of the family, so one shuffle finishes the sum over groups.
+//
+// The activation rows arrive already quantised (x_planes_kernel runs once per call, so a row
+// shared by many CTAs is quantised once).  K is processed in tiles of kt_chunks chunks: the planes
+// of all batch rows for one tile are copied into shared memory ([row][group][quad] of (low, high)
+// words plus a (scale, scaled sum) table); the weight records stream through per-warp rings that
+// run ahead across tiles.
+//
+// Tile mode (expert matmul with a route plan): blockIdx.y is a tile of up to 2P (token, route)
+// pairs of one expert; x rows are gathered through pair_order and results scatter back to pair
+// order.  The route plan's tile size must equal 2P.
+#pragma once
+#include "nint_gemv1_bl.cuh"
+
+namespace mfqb {
+
+// Quantises rows of x into the global plane buffers the batched kernel reads: grid = (K splits,
+// rows), every CTA a range of whole chunks.
+template <int T>
+__global__ void __launch_bounds__(256) x_planes_kernel(const __nv_bfloat16* __restrict__ x, int k, int gs, int ngp, int groups_per_cta,
+                                                       uint2* __restrict__ xq_g, float2* __restrict__ gtab_g) {
+    constexpr int QS = gemv1_bl_qstride(T);
+    const int row = blockIdx.y, g0 = blockIdx.x * groups_per_cta;
+    if (g0 >= ngp) return;
+    stage_x_planes<T>(x + (size_t)row * k, k, gs, g0, min(groups_per_cta, ngp - g0), xq_g + ((size_t)row * ngp + g0) * QS,
+                      gtab_g + (size_t)row * ngp + g0);
+}
+
+template <int BITS, int T, int P>
+__global__ void __launch_bounds__(256, (P >= 4 || ByteUnit<BITS>::words_for(8 * T) > 24) ? 2 : 3) nint_gemvn_bl_kernel(const GemvArgsB a) {
+    constexpr int G = kChunkGroupsB, MB = 2 * P;
+    using BU = ByteUnit<BITS>;
+    constexpr int WC = BU::words_for(8 * T), REC = (WC + 2) * 32;
+    constexpr int S = gemv1_bl_stages(REC), QS = gemv1_bl_qstride(T);
+    const NintDevB& w = a.w;
+
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ int row_src[MB], row_dst[MB];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    const int q = lane >> 2, c = lane & 3;
+    const int KT = a.kt_chunks, tile_groups = KT * G;
+    const int ystride = a.rb_per_cta * 16;
+    float* ypart = reinterpret_cast<float*>(smem);                                  // [MB][rb_per_cta * 16]
+    uint32_t* anch = reinterpret_cast<uint32_t*>(ypart + (size_t)MB * ystride);     // [rb_per_cta * 16]
+    float2* gtab = reinterpret_cast<float2*>(anch + ystride);                       // [MB][tile_groups]
+    uint2* xq = reinterpret_cast<uint2*>(gtab + (size_t)MB * tile_groups);          // [MB][tile_groups * QS]
+    uint32_t* ring = reinterpret_cast<uint32_t*>(xq + (size_t)MB * tile_groups * QS) + (size_t)warp * S * REC;
+
+    int m_cur = a.m, rb0, nrb, rbl0 = 0, row_limit = w.n;
+    if (a.tile_bounds != nullptr) {
+        pdl_wait_b();   // the route plan comes from the previous kernels
+        const int t = blockIdx.y;
+        if (t >= a.tile_bounds[a.n_experts]) return;
+        int lo = 0, hi = a.n_experts - 1;   // expert e with tile_bounds[e] <= t < tile_bounds[e + 1]
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (a.tile_bounds[mid] <= t) lo = mid;
+            else hi = mid - 1;
+        }
+        const int e = lo;
+        if (a.expert_pool[e] != a.pool) return;
+        const int p0 = a.expert_bounds[e] + (t - a.tile_bounds[e]) * MB;
+        m_cur = min(MB, a.expert_bounds[e + 1] - p0);
+        if (tid < MB) {
+            const int pair = tid < m_cur ? a.pair_order[p0 + tid] : 0;
+            row_src[tid] = a.x_per_pair ? pair : pair / a.routes;
+            row_dst[tid] = pair;
+        }
+        rbl0 = (int)(((long long)blockIdx.x * a.rb_per_expert) / gridDim.x);
+        nrb = (int)(((long long)(blockIdx.x + 1) * a.rb_per_expert) / gridDim.x) - rbl0;
+        rb0 = a.expert_local[e] * a.rb_per_expert + rbl0;
+        row_limit = a.ldy;
+    } else {
+        if (tid < MB) row_src[tid] = row_dst[tid] = tid;
+        rbl0 = (int)(((long long)blockIdx.x * w.nrb) / gridDim.x);
+        nrb = (int)(((long long)(blockIdx.x + 1) * w.nrb) / gridDim.x) - rbl0;
+        rb0 = rbl0;
+    }
+
+    // items of this warp: K tile by K tile; inside a tile its chunks (warp, warp + nwarps, ...),
+    // inside a chunk every row-block of the CTA.  KT is a multiple of nwarps, so the chunks of a
+    // warp are simply warp, warp + nwarps, ... over the whole of K.
+    const int my_segs = warp < w.nchunks ? (w.nchunks - warp + nwarps - 1) / nwarps : 0;
+    const int n_mine = my_segs * nrb;
+    int iss_i = 0, iss_seg = warp, iss_rbl = 0, iss_stage = 0;
+    auto issue = [&]() {
+        if (iss_i < n_mine) {
+            const uint32_t* src = w.items + ((size_t)(rb0 + iss_rbl) * w.nchunks + iss_seg) * REC;
+            uint32_t* dst = ring + iss_stage * REC;
+#pragma unroll
+            for (int off = 0; off < REC; off += 128)
+                if (off + 128 <= REC || lane * 4 < REC - off) cp_async16_b(dst + off + lane * 4, src + off + lane * 4);
+        }
+        cp_async_commit_b();
+        ++iss_i;
+        if (++iss_rbl == nrb) { iss_rbl = 0; iss_seg += nwarps; }
+        if (++iss_stage == S) iss_stage = 0;
+    };
+
+    pdl_launch_dependents_b();
+#pragma unroll
+    for (int i = 0; i < S; ++i) issue();
+    for (int i = tid; i < MB * ystride; i += blockDim.x) ypart[i] = 0.f;
+    for (int i = tid; i < nrb * 16; i += blockDim.x) anch[i] = __ldg(w.anchors + rb0 * 16 + i);
+    // rows past the batch contribute nothing: their planes and tables stay zero
+    for (int i = tid; i < (MB - m_cur) * tile_groups; i += blockDim.x) gtab[(size_t)m_cur * tile_groups + i] = make_float2(0.f, 0.f);
+    for (int i = tid; i < (MB - m_cur) * tile_groups * QS; i += blockDim.x) xq[(size_t)m_cur * tile_groups * QS + i] = make_uint2(0u, 0u);
+    pdl_wait_b();
+    __syncthreads();   // row_src / row_dst
+
+    // B masks: lane (q, c) feeds column q = (batch row q>>2 of the pass, octet o = q&3); its bytes
+    // are live in b0 where the fragment's octet c>>1 is o (o < 2), in b1 where 2 + (c>>1) is o
+    const int o = q & 3;
+    const bool live = (o & 1) == (c >> 1);
+    const uint32_t mA = (live && o < 2) ? 0xFFFFFFFFu : 0u, mB = (live && o >= 2) ? 0xFFFFFFFFu : 0u;
+
+    int seg = warp, rbl = 0, stage = 0, done = 0;
+    const int ntiles = (w.nchunks + KT - 1) / KT;
+    for (int tile = 0; tile < ntiles; ++tile) {
+        if (tile > 0) __syncthreads();   // every warp is done with the previous tile's planes
+        const int ch0 = tile * KT, nch = min(KT, w.nchunks - ch0);
+        const int ngp = w.nchunks * G;
+        for (int m = 0; m < m_cur; ++m) {
+            const uint4* src = reinterpret_cast<const uint4*>(a.xq_g + ((size_t)row_src[m] * ngp + ch0 * G) * QS);
+            uint4* dst = reinterpret_cast<uint4*>(xq + (size_t)m * tile_groups * QS);
+            for (int i = tid; i < nch * G * QS / 2; i += blockDim.x) dst[i] = __ldg(src + i);
+            const uint4* gsrc = reinterpret_cast<const uint4*>(a.gtab_g + (size_t)row_src[m] * ngp + ch0 * G);
+            uint4* gdst = reinterpret_cast<uint4*>(gtab + (size_t)m * tile_groups);
+            for (int i = tid; i < nch * G / 2; i += blockDim.x) gdst[i] = __ldg(gsrc + i);
+        }
+        __syncthreads();
+        const int tile_end = ch0 + nch;
+        while (done < n_mine && seg < tile_end) {
+            const int segl = seg - ch0;
+            asm volatile("cp.async.wait_group %0;\n" ::"n"(S - 1) : "memory");
+            __syncwarp();
+            const uint32_t* rec = ring + stage * REC;
+            uint32_t qw[WC];
+#pragma unroll
+            for (int j = 0; j < WC; ++j) qw[j] = rec[j * 32 + lane];
+            uint32_t sc[2][2];   // scale words of the lanes that own (rows q, q+8) x groups 4f + 2(c&1) + {0,1}
+#pragma unroll
+            for (int f = 0; f < 2; ++f) {
+                sc[f][0] = rec[WC * 32 + 4 * q + 2 * f + (c & 1)];
+                sc[f][1] = rec[(WC + 1) * 32 + 4 * q + 2 * f + (c & 1)];
+            }
+            __syncwarp();          // every lane has read the stage before it is refilled
+            issue();
+
+            float A_lo[P], A_hi[P], M_lo[P], M_hi[P];
+#pragma unroll
+            for (int p = 0; p < P; ++p) A_lo[p] = A_hi[p] = M_lo[p] = M_hi[p] = 0.f;
+#pragma unroll
+            for (int f = 0; f < 2; ++f) {
+                int dlo[P][4], dhi[P][4];
+#pragma unroll
+                for (int p = 0; p < P; ++p)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) dlo[p][e] = dhi[p][e] = 0;
+#pragma unroll
+                for (int t = 0; t < T; ++t) {
+                    const int r = (f * T + t) * 4;
+                    const uint32_t a0 = BU::at(qw, r), a1 = BU::at(qw, r + 1), a2 = BU::at(qw, r + 2), a3 = BU::at(qw, r + 3);
+#pragma unroll
+                    for (int p = 0; p < P; ++p) {
+                        const uint2 v = xq[((size_t)(2 * p + (q >> 2)) * tile_groups + segl * G + 4 * f + o) * QS + 2 * t + (c & 1)];
+                        imma_u8u8(dlo[p], a0, a1, a2, a3, v.x & mA, v.x & mB);
+                        imma_u8s8(dhi[p], a0, a1, a2, a3, v.y & mA, v.y & mB);
+                    }
+                }
+                const float ss0 = (float)(sc[f][0] & 0xFF), ss1 = (float)((sc[f][0] >> 8) & 0xFF);
+                const float ss2 = (float)((sc[f][0] >> 16) & 0xFF), ss3 = (float)(sc[f][0] >> 24);
+                const float sm0 = (float)(sc[f][1] & 0xFF), sm1 = (float)((sc[f][1] >> 8) & 0xFF);
+                const float sm2 = (float)((sc[f][1] >> 16) & 0xFF), sm3 = (float)(sc[f][1] >> 24);
+#pragma unroll
+                for (int p = 0; p < P; ++p) {
+                    // (sx, sx*X) of groups 4f + 2(c&1) + {0,1} for batch row 2p + (c>>1)
+                    const float4 gt = *reinterpret_cast<const float4*>(gtab + (size_t)(2 * p + (c >> 1)) * tile_groups + segl * G + 4 * f + 2 * (c & 1));
+                    const float d0 = (float)(dhi[p][0] * 256 + dlo[p][0]) * gt.x, d1 = (float)(dhi[p][1] * 256 + dlo[p][1]) * gt.z;
+                    const float d2 = (float)(dhi[p][2] * 256 + dlo[p][2]) * gt.x, d3 = (float)(dhi[p][3] * 256 + dlo[p][3]) * gt.z;
+                    A_lo[p] = fmaf(ss1, d1, fmaf(ss0, d0, A_lo[p]));
+                    A_hi[p] = fmaf(ss3, d3, fmaf(ss2, d2, A_hi[p]));
+                    M_lo[p] = fmaf(sm1, gt.w, fmaf(sm0, gt.y, M_lo[p]));
+                    M_hi[p] = fmaf(sm3, gt.w, fmaf(sm2, gt.y, M_hi[p]));
+                }
+            }
+            const uint32_t an_lo = anch[rbl * 16 + q], an_hi = anch[rbl * 16 + q + 8];
+            const float2 f_lo = __half22float2(*reinterpret_cast<const __half2*>(&an_lo));   // (ns, nm)
+            const float2 f_hi = __half22float2(*reinterpret_cast<const __half2*>(&an_hi));
+#pragma unroll
+            for (int p = 0; p < P; ++p) {
+                float v_lo = f_lo.x * A_lo[p] - f_lo.y * M_lo[p];
+                float v_hi = f_hi.x * A_hi[p] - f_hi.y * M_hi[p];
+                v_lo += __shfl_xor_sync(0xffffffffu, v_lo, 1);   // lanes c, c^1: the other two groups of each family
+                v_hi += __shfl_xor_sync(0xffffffffu, v_hi, 1);
+                const int m = 2 * p + (c >> 1);
+                if ((c & 1) == 0 && m < m_cur) {
+                    atomicAdd(ypart + (size_t)m * ystride + rbl * 16 + q, v_lo);
+                    atomicAdd(ypart + (size_t)m * ystride + rbl * 16 + q + 8, v_hi);
+                }
+            }
+            ++done;
+            if (++rbl == nrb) { rbl = 0; seg += nwarps; }
+            if (++stage == S) stage = 0;
+        }
+    }
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();
+    for (int i = tid; i < m_cur * nrb * 16; i += blockDim.x) {
+        const int m = i / (nrb * 16), j = i % (nrb * 16);
+        const int row = rbl0 * 16 + j;   // row inside the problem (matrix, or the tile's expert)
+        if (row < row_limit) {
+            const float v = ypart[(size_t)m * ystride + j];
+            const size_t off = (size_t)row_dst[m] * a.ldy + row;
+            if (a.y_dtype == 0 /* MFQB_F32 */) reinterpret_cast<float*>(a.y)[off] = v;
+            else reinterpret_cast<__nv_bfloat16*>(a.y)[off] = __float2bfloat16_rn(v);
+        }
+    }
+}
+
+}  // namespace mfqb
