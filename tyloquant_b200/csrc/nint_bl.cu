@@ -72,9 +72,12 @@ bool nint_bl_supported(int bits, int gs) {
 }
 
 // ---- GEMV launch planning ---------------------------------------------------------------------
+cudaError_t launch_gemv_bl_nvq(const GemvArgsB& a, const GemvPlanB& p, cudaStream_t stream);
+
 static void dispatch(const GemvArgsB& a, const GemvPlanB& p, cudaStream_t s, const char* what) {
     cudaError_t e;
     switch (a.w.bits) {
+        case 0: e = launch_gemv_bl_nvq(a, p, s); break;   // lattice records
         case 2: e = launch_gemv_bl_bits<2>(a, p, s); break;
         case 3: e = launch_gemv_bl_bits<3>(a, p, s); break;
         case 4: e = launch_gemv_bl_bits<4>(a, p, s); break;
@@ -83,17 +86,24 @@ static void dispatch(const GemvArgsB& a, const GemvPlanB& p, cudaStream_t s, con
         case 8: e = launch_gemv_bl_bits<8>(a, p, s); break;
         default: fail(MFQB_ERR_UNSUPPORTED, "NINT%d has no kernel", a.w.bits);
     }
-    if (e != cudaSuccess) fail(MFQB_ERR_CUDA, "NINT%d gs=%d %s launch: %s", a.w.bits, a.w.gs, what, cudaGetErrorString(e));
+    if (e != cudaSuccess)
+        fail(MFQB_ERR_CUDA, "%s%d gs=%d %s launch: %s", a.w.bits ? "NINT" : "NVQ index bits ", a.w.bits ? a.w.bits : a.w.index_bits, a.w.gs, what,
+             cudaGetErrorString(e));
 }
 
 constexpr size_t kGemvSmemLimit = 200 * 1024;
 
+// Shared-memory tables of the record's codec (lattice records: signed table + state scales).
+static size_t codec_ctx_bytes(const NintDevB& w) { return w.table ? (size_t)w.table_words * 4 + 64 : 0; }
+// CTAs of `smem` bytes each that fit an SM, at most `cap`.
+static int ctas_per_sm(size_t smem, int cap) { return std::max(1, std::min(cap, (int)((220 * 1024) / (smem + 1024)))); }
+
 static size_t gemv1_smem(const NintDevB& w, int rb_per_cta) {
-    return (size_t)rb_per_cta * 16 * 8 + (size_t)8 * gemv1_bl_stages(w.rec_words) * w.rec_words * 4;
+    return codec_ctx_bytes(w) + (size_t)rb_per_cta * 16 * 8 + (size_t)8 * gemv1_bl_stages(w.rec_words) * w.rec_words * 4;
 }
 static size_t gemvn_smem(const NintDevB& w, int rb_per_cta, int passes, int kt) {
     const int mb = 2 * passes, tg = kt * kChunkGroupsB;
-    return (size_t)(mb + 1) * rb_per_cta * 16 * 4 + (size_t)mb * tg * 8 + (size_t)mb * tg * gemv1_bl_qstride(w.t8) * 8 +
+    return codec_ctx_bytes(w) + (size_t)(mb + 1) * rb_per_cta * 16 * 4 + (size_t)mb * tg * 8 + (size_t)mb * tg * gemv1_bl_qstride(w.t8) * 8 +
            (size_t)8 * gemv1_bl_stages(w.rec_words) * w.rec_words * 4;
 }
 // Bytes of the quantised planes of `rows` activation rows for this weight.
@@ -145,7 +155,7 @@ static int gemvn_kt(const NintDevB& w, int passes) {
 }
 
 // y[m, n] = x[m, k] * W^T for m <= 8 (the caller loops larger batches)
-void launch_nint_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtype, int ldy, int device, cudaStream_t s) {
+void launch_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtype, int ldy, int device, cudaStream_t s) {
     GemvArgsB a{};
     a.w = w;
     a.x = static_cast<const __nv_bfloat16*>(x);
@@ -157,14 +167,14 @@ void launch_nint_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y
     const int sms = device_sm_count(device);
     if (m == 1) {
         // three CTAs per SM, all resident at once; row-blocks are split evenly inside the kernel
-        p.grid = std::min(w.nrb, 3 * sms);
+        p.grid = std::min(w.nrb, ctas_per_sm(gemv1_smem(w, 1), 3) * sms);
         a.rb_per_cta = (w.nrb + p.grid - 1) / p.grid;
         p.smem = gemv1_smem(w, a.rb_per_cta);
     } else {
         launch_x_planes(w, x, m, planes_scratch(device, nint_bl_planes_bytes(w, m)), &a.xq_g, &a.gtab_g, s);
         p.passes = passes_for(m);
         a.kt_chunks = gemvn_kt(w, p.passes);
-        p.grid = std::min(w.nrb, (p.passes == 4 ? 2 : 3) * sms);
+        p.grid = std::min(w.nrb, ctas_per_sm(gemvn_smem(w, 1, p.passes, a.kt_chunks), p.passes == 4 ? 2 : 3) * sms);
         a.rb_per_cta = (w.nrb + p.grid - 1) / p.grid;
         p.smem = gemvn_smem(w, a.rb_per_cta, p.passes, a.kt_chunks);
     }

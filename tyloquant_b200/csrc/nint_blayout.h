@@ -46,7 +46,13 @@ struct NintDevB {
     int bits, gs, sub_bits;
     int t8;              // octets per group
     int wc;              // code words per lane per item
-    int rec_words;       // (wc + 2) * 32
+    int rec_words;       // (wc + scale words) * 32
+    // Lattice (NVQ) weights only: the signed codebook table and the joint scale/codebook states.
+    const uint32_t* table;   // [banks][entries][16 sign patterns] of four int8 each
+    int table_words;
+    int index_bits, entries, banks, jsc;
+    float lut[16];           // scale of each state (JSC); plain NVQ uses the sub-scale itself
+    uint32_t bankmap;        // 2 bits per state: codebook bank
 };
 
 constexpr int kChunkGroupsB = 8;

@@ -74,6 +74,59 @@ __device__ __forceinline__ void imma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1,
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void imma_s8u8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void imma_s8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// low plane (unsigned activations bytes) / high plane (signed), A signed or unsigned
+template <bool A_SIGNED>
+__device__ __forceinline__ void imma_planes(int (&dlo)[4], int (&dhi)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t lo0,
+                                            uint32_t lo1, uint32_t hi0, uint32_t hi1) {
+    if constexpr (A_SIGNED) {
+        imma_s8u8(dlo, a0, a1, a2, a3, lo0, lo1);
+        imma_s8s8(dhi, a0, a1, a2, a3, hi0, hi1);
+    } else {
+        imma_u8u8(dlo, a0, a1, a2, a3, lo0, lo1);
+        imma_u8s8(dhi, a0, a1, a2, a3, hi0, hi1);
+    }
+}
+
+// ---- weight codecs -------------------------------------------------------------------------------
+// A codec tells the kernels how one lane's words of a record become tensor-core A registers and
+// float scales.  Interface:
+//   T (octets per group), WC (code words per lane), SW (scale words per lane), A_SIGNED, HAS_MIN,
+//   NEEDS_OWN_SCALE (areg reads the lane's own scale words), MIN_CTAS (launch bound);
+//   Ctx: per-CTA context; ctx_bytes(w) bytes at the start of dynamic shared memory, init() fills them;
+//   areg(qw, r, ctx, own_sw): register r = ((f*T + t)*4 + a) of the lane's stream;
+//   scales(sw, ctx, ss, sm): the four sub-scales / sub-mins of a lane's scale words, in the order
+//   (row lo, group even), (lo, odd), (hi, even), (hi, odd).
+template <int BITS, int T_>
+struct NintCodec {
+    static constexpr int T = T_;
+    using BU = ByteUnit<BITS>;
+    static constexpr int WC = BU::words_for(8 * T), SW = 2;
+    static constexpr bool A_SIGNED = false, HAS_MIN = true, NEEDS_OWN_SCALE = false;
+    static constexpr int MIN_CTAS = WC > 48 ? 1 : (WC > 24 ? 2 : 3);
+    struct Ctx {
+        __device__ __forceinline__ void init(unsigned char*, const NintDevB&, int, int) {}
+    };
+    __host__ __device__ static size_t ctx_bytes(const NintDevB&) { return 0; }
+    __device__ static __forceinline__ uint32_t areg(const uint32_t* qw, int r, const Ctx&, const uint32_t*) { return BU::at(qw, r); }
+    __device__ static __forceinline__ void scales(const uint32_t* sw, const Ctx&, float (&ss)[4], float (&sm)[4]) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            ss[i] = (float)((sw[0] >> (8 * i)) & 0xFF);
+            sm[i] = (float)((sw[1] >> (8 * i)) & 0xFF);
+        }
+    }
+};
+
 // Records per warp ring: about 6 KB of ring per warp, between 2 and 6 stages.
 __host__ __device__ constexpr int gemv1_bl_stages(int rec_words) {
     return 6144 / (rec_words * 4) < 2 ? 2 : (6144 / (rec_words * 4) > 6 ? 6 : 6144 / (rec_words * 4));
@@ -236,20 +289,20 @@ __device__ __forceinline__ void x_chunk_quant(const XChunkRaw<T>& raw, int c, ui
 // 16-byte asynchronous copies; the first S items are requested before the kernel waits for its
 // predecessor in the stream, since weights are constants.  The activation row is read straight
 // from global memory, one chunk ahead, and quantised in registers by the warp that needs it.
-template <int BITS, int T>
-__global__ void __launch_bounds__(256, (ByteUnit<BITS>::words_for(8 * T) > 48 ? 1 : (ByteUnit<BITS>::words_for(8 * T) > 24 ? 2 : 3))) nint_gemv1_bl_kernel(const GemvArgsB a) {
-    constexpr int G = kChunkGroupsB;
-    using BU = ByteUnit<BITS>;
-    constexpr int WC = BU::words_for(8 * T), REC = (WC + 2) * 32;
+template <class C>
+__global__ void __launch_bounds__(256, C::MIN_CTAS) gemv1_bl_kernel(const GemvArgsB a) {
+    constexpr int G = kChunkGroupsB, T = C::T, WC = C::WC, SW = C::SW, REC = (WC + SW) * 32;
     constexpr int S = gemv1_bl_stages(REC);
     const NintDevB& w = a.w;
 
     extern __shared__ __align__(16) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const int q = lane >> 2, c = lane & 3;
-    float* ypart = reinterpret_cast<float*>(smem);
+    typename C::Ctx ctx;
+    ctx.init(smem, w, tid, blockDim.x);   // constant tables: visible after the first __syncthreads
+    float* ypart = reinterpret_cast<float*>(smem + C::ctx_bytes(w));
     uint32_t* anch = reinterpret_cast<uint32_t*>(ypart + (size_t)a.rb_per_cta * 16);
-    uint32_t* ring = anch + (size_t)a.rb_per_cta * 16 + (size_t)warp * S * REC;
+    uint32_t* ring = anch + (size_t)a.rb_per_cta * 16 + (size_t)warp * S * REC;   // ctx_bytes is a multiple of 16
 
     // balanced split of the row-blocks over gridDim.x: CTA b owns [b*R/grid, (b+1)*R/grid) of the
     // R row-blocks of the whole matrix, or of its pair's expert in routed mode
@@ -326,7 +379,9 @@ __global__ void __launch_bounds__(256, (ByteUnit<BITS>::words_for(8 * T) > 48 ? 
         uint32_t qw[WC];
 #pragma unroll
         for (int j = 0; j < WC; ++j) qw[j] = rec[j * 32 + lane];
-        const uint32_t s0 = rec[WC * 32 + lane], s1 = rec[(WC + 1) * 32 + lane];
+        uint32_t sw[SW];
+#pragma unroll
+        for (int j = 0; j < SW; ++j) sw[j] = rec[(WC + j) * 32 + lane];
         __syncwarp();          // every lane has read the stage before it is refilled
         issue();
         int dlo[4] = {0, 0, 0, 0}, dhi[4] = {0, 0, 0, 0};
@@ -335,10 +390,10 @@ __global__ void __launch_bounds__(256, (ByteUnit<BITS>::words_for(8 * T) > 48 ? 
 #pragma unroll
             for (int t = 0; t < T; ++t) {
                 const int r = (f * T + t) * 4;
-                const uint32_t a0 = BU::at(qw, r), a1 = BU::at(qw, r + 1), a2 = BU::at(qw, r + 2), a3 = BU::at(qw, r + 3);
+                const uint32_t a0 = C::areg(qw, r, ctx, sw), a1 = C::areg(qw, r + 1, ctx, sw), a2 = C::areg(qw, r + 2, ctx, sw),
+                               a3 = C::areg(qw, r + 3, ctx, sw);
                 const uint32_t mb0 = f ? m10 : m00, mb1 = f ? m11 : m01;
-                imma_u8u8(dlo, a0, a1, a2, a3, xlo[t] & mb0, xlo[t] & mb1);
-                imma_u8s8(dhi, a0, a1, a2, a3, xhi[t] & mb0, xhi[t] & mb1);
+                imma_planes<C::A_SIGNED>(dlo, dhi, a0, a1, a2, a3, xlo[t] & mb0, xlo[t] & mb1, xhi[t] & mb0, xhi[t] & mb1);
             }
         }
         // D = 256 * high + low: sums of q * xi for rows (q, q+8) x groups (2c, 2c+1)
@@ -347,10 +402,13 @@ __global__ void __launch_bounds__(256, (ByteUnit<BITS>::words_for(8 * T) > 48 ? 
         const uint32_t an_lo = anch[rbl * 16 + q], an_hi = anch[rbl * 16 + q + 8];
         const float2 f_lo = __half22float2(*reinterpret_cast<const __half2*>(&an_lo));   // (ns, nm)
         const float2 f_hi = __half22float2(*reinterpret_cast<const __half2*>(&an_hi));
-        const float ss0 = (float)(s0 & 0xFF), ss1 = (float)((s0 >> 8) & 0xFF), ss2 = (float)((s0 >> 16) & 0xFF), ss3 = (float)(s0 >> 24);
-        const float sm0 = (float)(s1 & 0xFF), sm1 = (float)((s1 >> 8) & 0xFF), sm2 = (float)((s1 >> 16) & 0xFF), sm3 = (float)(s1 >> 24);
-        float v_lo = f_lo.x * fmaf(ss1, d1, ss0 * d0) - f_lo.y * fmaf(sm1, gt.w, sm0 * gt.y);
-        float v_hi = f_hi.x * fmaf(ss3, d3, ss2 * d2) - f_hi.y * fmaf(sm3, gt.w, sm2 * gt.y);
+        float ss[4], sm[4];
+        C::scales(sw, ctx, ss, sm);
+        float v_lo = f_lo.x * fmaf(ss[1], d1, ss[0] * d0), v_hi = f_hi.x * fmaf(ss[3], d3, ss[2] * d2);
+        if constexpr (C::HAS_MIN) {
+            v_lo -= f_lo.y * fmaf(sm[1], gt.w, sm[0] * gt.y);
+            v_hi -= f_hi.y * fmaf(sm[3], gt.w, sm[2] * gt.y);
+        }
         // the four lanes of a quad hold different groups of the same two rows
         v_lo += __shfl_xor_sync(0xffffffffu, v_lo, 1);
         v_hi += __shfl_xor_sync(0xffffffffu, v_hi, 1);

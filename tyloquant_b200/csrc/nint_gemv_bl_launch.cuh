@@ -33,15 +33,19 @@ static cudaError_t launch_kernel_pdl(Kernel kernel, const GemvArgsB& a, const Ge
     return cudaLaunchKernelEx(&cfg, kernel, a);
 }
 
-template <int BITS, int T>
-static cudaError_t launch_gemv_bl_one(const GemvArgsB& a, const GemvPlanB& p, cudaStream_t stream) {
+template <class C>
+static cudaError_t launch_gemv_codec(const GemvArgsB& a, const GemvPlanB& p, cudaStream_t stream) {
     switch (p.passes) {
-        case 0: return launch_kernel_pdl(nint_gemv1_bl_kernel<BITS, T>, a, p, stream);
-        case 1: return launch_kernel_pdl(nint_gemvn_bl_kernel<BITS, T, 1>, a, p, stream);
-        case 2: return launch_kernel_pdl(nint_gemvn_bl_kernel<BITS, T, 2>, a, p, stream);
-        case 4: return launch_kernel_pdl(nint_gemvn_bl_kernel<BITS, T, 4>, a, p, stream);
+        case 0: return launch_kernel_pdl(gemv1_bl_kernel<C>, a, p, stream);
+        case 1: return launch_kernel_pdl(gemvn_bl_kernel<C, 1>, a, p, stream);
+        case 2: return launch_kernel_pdl(gemvn_bl_kernel<C, 2>, a, p, stream);
+        case 4: return launch_kernel_pdl(gemvn_bl_kernel<C, 4>, a, p, stream);
         default: return cudaErrorInvalidValue;
     }
+}
+template <int BITS, int T>
+static cudaError_t launch_gemv_bl_one(const GemvArgsB& a, const GemvPlanB& p, cudaStream_t stream) {
+    return launch_gemv_codec<NintCodec<BITS, T>>(a, p, stream);
 }
 
 #define MFQB_GEMV_BL_INSTANTIATE(BITS)                                                                              \

@@ -38,11 +38,9 @@ __global__ void __launch_bounds__(256) x_planes_kernel(const __nv_bfloat16* __re
                       gtab_g + (size_t)row * ngp + g0);
 }
 
-template <int BITS, int T, int P>
-__global__ void __launch_bounds__(256, (P >= 4 || ByteUnit<BITS>::words_for(8 * T) > 24) ? 2 : 3) nint_gemvn_bl_kernel(const GemvArgsB a) {
-    constexpr int G = kChunkGroupsB, MB = 2 * P;
-    using BU = ByteUnit<BITS>;
-    constexpr int WC = BU::words_for(8 * T), REC = (WC + 2) * 32;
+template <class C, int P>
+__global__ void __launch_bounds__(256, (P >= 4 || C::MIN_CTAS < 3) ? (C::MIN_CTAS < 2 ? 1 : 2) : 3) gemvn_bl_kernel(const GemvArgsB a) {
+    constexpr int G = kChunkGroupsB, MB = 2 * P, T = C::T, WC = C::WC, SW = C::SW, REC = (WC + SW) * 32;
     constexpr int S = gemv1_bl_stages(REC), QS = gemv1_bl_qstride(T);
     const NintDevB& w = a.w;
 
@@ -52,7 +50,9 @@ __global__ void __launch_bounds__(256, (P >= 4 || ByteUnit<BITS>::words_for(8 * 
     const int q = lane >> 2, c = lane & 3;
     const int KT = a.kt_chunks, tile_groups = KT * G;
     const int ystride = a.rb_per_cta * 16;
-    float* ypart = reinterpret_cast<float*>(smem);                                  // [MB][rb_per_cta * 16]
+    typename C::Ctx ctx;
+    ctx.init(smem, w, tid, blockDim.x);   // constant tables: visible after the first __syncthreads
+    float* ypart = reinterpret_cast<float*>(smem + C::ctx_bytes(w));                // [MB][rb_per_cta * 16]
     uint32_t* anch = reinterpret_cast<uint32_t*>(ypart + (size_t)MB * ystride);     // [rb_per_cta * 16]
     float2* gtab = reinterpret_cast<float2*>(anch + ystride);                       // [MB][tile_groups]
     uint2* xq = reinterpret_cast<uint2*>(gtab + (size_t)MB * tile_groups);          // [MB][tile_groups * QS]
@@ -150,12 +150,13 @@ __global__ void __launch_bounds__(256, (P >= 4 || ByteUnit<BITS>::words_for(8 * 
             uint32_t qw[WC];
 #pragma unroll
             for (int j = 0; j < WC; ++j) qw[j] = rec[j * 32 + lane];
-            uint32_t sc[2][2];   // scale words of the lanes that own (rows q, q+8) x groups 4f + 2(c&1) + {0,1}
+            uint32_t sc[2][SW], own[SW];   // scale words of the lanes that own (rows q, q+8) x groups 4f + 2(c&1) + {0,1}; this lane's
 #pragma unroll
-            for (int f = 0; f < 2; ++f) {
-                sc[f][0] = rec[WC * 32 + 4 * q + 2 * f + (c & 1)];
-                sc[f][1] = rec[(WC + 1) * 32 + 4 * q + 2 * f + (c & 1)];
-            }
+            for (int f = 0; f < 2; ++f)
+#pragma unroll
+                for (int j = 0; j < SW; ++j) sc[f][j] = rec[(WC + j) * 32 + 4 * q + 2 * f + (c & 1)];
+#pragma unroll
+            for (int j = 0; j < SW; ++j) own[j] = C::NEEDS_OWN_SCALE ? rec[(WC + j) * 32 + lane] : 0u;
             __syncwarp();          // every lane has read the stage before it is refilled
             issue();
 
@@ -172,28 +173,28 @@ __global__ void __launch_bounds__(256, (P >= 4 || ByteUnit<BITS>::words_for(8 * 
 #pragma unroll
                 for (int t = 0; t < T; ++t) {
                     const int r = (f * T + t) * 4;
-                    const uint32_t a0 = BU::at(qw, r), a1 = BU::at(qw, r + 1), a2 = BU::at(qw, r + 2), a3 = BU::at(qw, r + 3);
+                    const uint32_t a0 = C::areg(qw, r, ctx, own), a1 = C::areg(qw, r + 1, ctx, own), a2 = C::areg(qw, r + 2, ctx, own),
+                                   a3 = C::areg(qw, r + 3, ctx, own);
 #pragma unroll
                     for (int p = 0; p < P; ++p) {
                         const uint2 v = xq[((size_t)(2 * p + (q >> 2)) * tile_groups + segl * G + 4 * f + o) * QS + 2 * t + (c & 1)];
-                        imma_u8u8(dlo[p], a0, a1, a2, a3, v.x & mA, v.x & mB);
-                        imma_u8s8(dhi[p], a0, a1, a2, a3, v.y & mA, v.y & mB);
+                        imma_planes<C::A_SIGNED>(dlo[p], dhi[p], a0, a1, a2, a3, v.x & mA, v.x & mB, v.y & mA, v.y & mB);
                     }
                 }
-                const float ss0 = (float)(sc[f][0] & 0xFF), ss1 = (float)((sc[f][0] >> 8) & 0xFF);
-                const float ss2 = (float)((sc[f][0] >> 16) & 0xFF), ss3 = (float)(sc[f][0] >> 24);
-                const float sm0 = (float)(sc[f][1] & 0xFF), sm1 = (float)((sc[f][1] >> 8) & 0xFF);
-                const float sm2 = (float)((sc[f][1] >> 16) & 0xFF), sm3 = (float)(sc[f][1] >> 24);
+                float ss[4], sm[4];
+                C::scales(sc[f], ctx, ss, sm);
 #pragma unroll
                 for (int p = 0; p < P; ++p) {
                     // (sx, sx*X) of groups 4f + 2(c&1) + {0,1} for batch row 2p + (c>>1)
                     const float4 gt = *reinterpret_cast<const float4*>(gtab + (size_t)(2 * p + (c >> 1)) * tile_groups + segl * G + 4 * f + 2 * (c & 1));
                     const float d0 = (float)(dhi[p][0] * 256 + dlo[p][0]) * gt.x, d1 = (float)(dhi[p][1] * 256 + dlo[p][1]) * gt.z;
                     const float d2 = (float)(dhi[p][2] * 256 + dlo[p][2]) * gt.x, d3 = (float)(dhi[p][3] * 256 + dlo[p][3]) * gt.z;
-                    A_lo[p] = fmaf(ss1, d1, fmaf(ss0, d0, A_lo[p]));
-                    A_hi[p] = fmaf(ss3, d3, fmaf(ss2, d2, A_hi[p]));
-                    M_lo[p] = fmaf(sm1, gt.w, fmaf(sm0, gt.y, M_lo[p]));
-                    M_hi[p] = fmaf(sm3, gt.w, fmaf(sm2, gt.y, M_hi[p]));
+                    A_lo[p] = fmaf(ss[1], d1, fmaf(ss[0], d0, A_lo[p]));
+                    A_hi[p] = fmaf(ss[3], d3, fmaf(ss[2], d2, A_hi[p]));
+                    if constexpr (C::HAS_MIN) {
+                        M_lo[p] = fmaf(sm[1], gt.w, fmaf(sm[0], gt.y, M_lo[p]));
+                        M_hi[p] = fmaf(sm[3], gt.w, fmaf(sm[2], gt.y, M_hi[p]));
+                    }
                 }
             }
             const uint32_t an_lo = anch[rbl * 16 + q], an_hi = anch[rbl * 16 + q + 8];

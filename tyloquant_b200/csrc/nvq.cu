@@ -1,24 +1,23 @@
 // NVQ3 (D4 lattice vector quantization) on the device: handle, bit-exact decoder, GEMV.
 //   w[n, k] = (+-code[index][k % 4]) * (anchor[n] * s[n, k / 24])
 // Replaces nvq_dequant_kernel / nvq_gemv_* (mfq/kernels/cuda/nvq_matmul.cu:421-471, 1057-1219)
-// without their int8 activation quantization.
+// on the int8 tensor-core kernels shared with NINT (activations quantised per group to int16 planes).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include <algorithm>
 
 #include "cuda_util.h"
-#include "nint_gemv_m1.cuh"
 #include "nvq.h"
-#include "nvq_layout.h"
+#include "nvq_blayout.h"
 
 namespace mfqb {
 
-uint64_t selfcheck_nvq_layout(const HostNvq& t);
+void launch_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtype, int ldy, int device, cudaStream_t s);
 
 struct NvqDevice {
-    NvqDev d{};
-    DevBuf items, anchors, cb;
+    NintDevB d{};
+    DevBuf items, anchors, table;
     int device = 0;
 };
 void NvqDeviceDeleter::operator()(NvqDevice* p) const { delete p; }
@@ -34,17 +33,19 @@ void check_nvq_dtype(const std::string& dtype, const HostNvq& t) {
 }
 
 NvqDevicePtr make_nvq_device(const HostNvq& t, int device, mfqb_weight_info* info) {
-    NvqPacked p = pack_nvq_device(t);
+    if ((size_t)t.banks * t.entries * 64 > 128 * 1024)
+        fail(MFQB_ERR_UNSUPPORTED, "NVQ codebook of %d banks x %d entries is too large for the shared-memory table", t.banks, t.entries);
+    NvqPackedB p = pack_nvq_bytes(t);
     NvqDevicePtr w(new NvqDevice);
     DeviceGuard guard(device);
     w->device = device;
     w->items.upload(p.items.data(), p.items.size() * 4);
     w->anchors.upload(p.anchors.data(), p.anchors.size() * 4);
-    w->cb.upload(p.cb.data(), p.cb.size() * 4);
+    w->table.upload(p.table.data(), p.table.size() * 4);
     w->d = p.d;
     w->d.items = static_cast<const uint32_t*>(w->items.p);
     w->d.anchors = static_cast<const uint32_t*>(w->anchors.p);
-    w->d.cb = static_cast<const NvqPair*>(w->cb.p);
+    w->d.table = static_cast<const uint32_t*>(w->table.p);
     if (info) {
         info->family = MFQB_FAMILY_NVQ;
         info->bits = t.index_bits;
@@ -55,69 +56,61 @@ NvqDevicePtr make_nvq_device(const HostNvq& t, int device, mfqb_weight_info* inf
         info->device = device;
         info->jsc_banks = t.jsc ? t.banks : 0;
         info->payload_bytes = nvq_payload_bytes(t);
-        info->device_bytes = w->items.bytes + w->anchors.bytes + w->cb.bytes;
+        info->device_bytes = w->items.bytes + w->anchors.bytes + w->table.bytes;
     }
     return w;
 }
 
 // ---- reference decoder on the GPU -----------------------------------------------------------
-// One thread per (row, group).  w = fl(signed_code * fl(anchor * s)): two separately rounded
-// float32 products, as nvq_quant.dequantize / dequantize_nvq_jsc compute it
+// One thread per (row, group, vector).  w = fl(signed_code * fl(anchor * s)): two separately
+// rounded float32 products, as nvq_quant.dequantize / dequantize_nvq_jsc compute it
 // (mfq/quantize/nvq_quant.py:612-626, mfq/quantize/nvq_jsc.py:1053-1079).
-__global__ void nvq_dequant_kernel(const NvqDev w, void* out, int out_dtype) {
-    const size_t total = (size_t)w.n * w.ng;
+__global__ void nvq_bl_dequant_kernel(const NintDevB w, void* out, int out_dtype) {
+    const int fb = w.index_bits + 4;
+    const size_t total = (size_t)w.n * w.ng * 6;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
-        const int grp = (int)(idx % w.ng), row = (int)(idx / w.ng);
-        const int rb = row >> 4, q = row & 7, r = (row >> 3) & 1, ch = grp / kNvqChunkGroups, g = grp % kNvqChunkGroups;
+        const int v = (int)(idx % 6);
+        const size_t rg = idx / 6;
+        const int grp = (int)(rg % w.ng), row = (int)(rg / w.ng);
+        const int rb = row >> 4, q = row & 7, hi = (row >> 3) & 1, ch = grp / kChunkGroupsB, g = grp % kChunkGroupsB;
+        const int f = g >> 2, o = g & 3;
+        const int lane = 4 * q + 2 * (o & 1) + (v & 1);
+        const int reg = (f * 3 + (v >> 1)) * 4 + 2 * (o >> 1) + hi;
         const uint32_t* rec = w.items + ((size_t)rb * w.nchunks + ch) * w.rec_words;
-        const uint32_t sword = rec[w.wc * 32 + (g >> 2) * 8 + q];
-        const uint32_t state = (sword >> ((g & 3) * 4 + 16 * r)) & 15u;
+        const int pos = reg * fb, wi = pos >> 5, sh = pos & 31;
+        unsigned long long bits = rec[wi * 32 + lane];
+        if (sh + fb > 32) bits |= (unsigned long long)rec[(wi + 1) * 32 + lane] << 32;
+        const uint32_t field = (uint32_t)(bits >> sh) & ((1u << fb) - 1u);
+        const uint32_t state = (rec[w.wc * 32 + 4 * q + (g >> 1)] >> (8 * (2 * hi + (g & 1)))) & 15u;
         const float anchor = __half2float(__ushort_as_half((unsigned short)(w.anchors[row] & 0xFFFFu)));
-        const float s = w.jsc ? w.lut[state] : (float)state;
-        const float scale = __fmul_rn(anchor, s);
+        const float scale = __fmul_rn(anchor, w.jsc ? w.lut[state] : (float)state);
         const uint32_t bank = (w.bankmap >> (2 * state)) & 3u;
-        const int pr = g >> 1, h = g & 1;
-        for (int v = 0; v < 6; ++v) {
-            int c, u;
-            if (h == 0) { if (v < 4) { c = v; u = 0; } else { c = v - 4; u = 1; } }
-            else { if (v < 2) { c = v + 2; u = 1; } else { c = v - 2; u = 2; } }
-            const int pos = ((pr * 2 + r) * 3 + u) * w.fb, wi = pos >> 5, sh = pos & 31, lane = 4 * q + c;
-            unsigned long long bits = rec[wi * 32 + lane];
-            if (sh + w.fb > 32) bits |= (unsigned long long)rec[(wi + 1) * 32 + lane] << 32;
-            const uint32_t f = (uint32_t)(bits >> sh) & ((1u << w.fb) - 1u);
-            const uint32_t index = f & ((1u << w.index_bits) - 1u), sg = f >> w.index_bits;
-            const NvqPair e = w.cb[bank * w.entries + index];
-            const uint32_t pair[2] = {e.x, e.y};
-            for (int j = 0; j < 4; ++j) {
-                const int k = grp * kNvqGroup + v * 4 + j;
-                if (k >= w.k) break;
-                float code = __uint_as_float(((pair[j >> 1] >> ((j & 1) * 16)) & 0xFFFFu) << 16);
-                if ((sg >> j) & 1u) code = -code;
-                const float val = __fmul_rn(code, scale);
-                const size_t o = (size_t)row * w.k + k;
-                if (out_dtype == MFQB_F32) reinterpret_cast<float*>(out)[o] = val;
-                else reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(val);
-            }
+        const uint32_t codes = w.table[((size_t)bank * w.entries + (field >> 4)) * 16 + (field & 15u)];
+        for (int j = 0; j < 4; ++j) {
+            const int k = grp * 24 + v * 4 + j;
+            if (k >= w.k) break;
+            const float val = __fmul_rn((float)(int)(signed char)(codes >> (8 * j)), scale);
+            const size_t off = (size_t)row * w.k + k;
+            if (out_dtype == MFQB_F32) reinterpret_cast<float*>(out)[off] = val;
+            else reinterpret_cast<__nv_bfloat16*>(out)[off] = __float2bfloat16_rn(val);
         }
     }
 }
 
 void nvq_dequant(const NvqDevice& w, void* out, int out_dtype, cudaStream_t stream) {
-    const size_t total = (size_t)w.d.n * w.d.ng;
+    const size_t total = (size_t)w.d.n * w.d.ng * 6;
     const int block = 256, grid = (int)std::min<size_t>((total + block - 1) / block, 148 * 16);
-    nvq_dequant_kernel<<<grid, block, 0, stream>>>(w.d, out, out_dtype);
+    nvq_bl_dequant_kernel<<<grid, block, 0, stream>>>(w.d, out, out_dtype);
     MFQB_CUDA(cudaGetLastError());
 }
 
-// GEMV: defined in nvq_gemv.cu
-void nvq_gemv_m1(const NvqDev& w, const void* x, void* y, int y_dtype, int device, cudaStream_t stream);
-
 void nvq_mul_mat(const NvqDevice& w, const void* x_bf16, int m, void* y, int y_dtype, cudaStream_t stream) {
-    // The weight-streaming kernel takes one activation row; further rows re-stream the weight.
     const size_t ysz = y_dtype == MFQB_F32 ? 4 : 2;
-    for (int i = 0; i < m; ++i)
-        nvq_gemv_m1(w.d, static_cast<const char*>(x_bf16) + (size_t)i * w.d.k * 2,
-                    static_cast<char*>(y) + (size_t)i * w.d.n * ysz, y_dtype, w.device, stream);
+    for (int m0 = 0; m0 < m; m0 += 8) {   // batch rows one launch covers
+        const int mm = std::min(8, m - m0);
+        launch_bl_gemv(w.d, static_cast<const char*>(x_bf16) + (size_t)m0 * w.d.k * 2, mm, static_cast<char*>(y) + (size_t)m0 * w.d.n * ysz,
+                       y_dtype, w.d.n, w.device, stream);
+    }
 }
 
 }  // namespace mfqb

@@ -17,6 +17,5 @@ void check_nvq_dtype(const std::string& dtype, const HostNvq& t);
 NvqDevicePtr make_nvq_device(const HostNvq& t, int device, mfqb_weight_info* info);
 void nvq_dequant(const NvqDevice& w, void* out, int out_dtype, cudaStream_t stream);
 void nvq_mul_mat(const NvqDevice& w, const void* x_bf16, int m, void* y, int y_dtype, cudaStream_t stream);
-uint64_t selfcheck_nvq_layout(const HostNvq& t);
 
 }  // namespace mfqb

@@ -9,6 +9,7 @@
 #include "nint_gemm_tc.cuh"
 #include "nint_blayout.h"
 #include "nvq.h"
+#include "nvq_blayout.h"
 
 namespace mfqb {
 
@@ -129,7 +130,7 @@ using namespace mfqb;
 
 namespace mfqb {
 void launch_nint_bl_dequant(const NintDevB& w, void* out, int out_dtype, cudaStream_t s);
-void launch_nint_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtype, int ldy, int device, cudaStream_t s);
+void launch_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtype, int ldy, int device, cudaStream_t s);
 bool nint_bl_supported(int bits, int gs);
 }
 
@@ -247,7 +248,7 @@ int mfqb_mul_mat(const mfqb_weight* w, const void* x, int m, void* y, int y_dtyp
             if (m > 16 && launch_nint_gemm(w->nint, x, m, y, y_dtype, w->device, stream)) return;
             for (int m0 = 0; m0 < m; m0 += 8) {   // batch rows one GEMV launch covers
                 const int mm = std::min(8, m - m0);
-                launch_nint_bl_gemv(w->nint, static_cast<const char*>(x) + (size_t)m0 * k * 2, mm,
+                launch_bl_gemv(w->nint, static_cast<const char*>(x) + (size_t)m0 * k * 2, mm,
                                     static_cast<char*>(y) + (size_t)m0 * n * ysz, y_dtype, (int)n, w->device, stream);
             }
         } else {
@@ -290,7 +291,7 @@ int mfqb_selfcheck_layout(const char* dtype, const void* blob, uint64_t nbytes, 
             check_nint_supported(t);
             *mismatches = selfcheck_nint_bytes(t);
         } else if (dtype_is_nvq(d)) {
-            *mismatches = selfcheck_nvq_layout(parse_nvq(blob, nbytes));
+            *mismatches = selfcheck_nvq_bytes(parse_nvq(blob, nbytes));
         } else {
             fail(MFQB_ERR_UNSUPPORTED, "dtype '%s' is outside the packed-weight execution path", dtype);
         }
