@@ -98,8 +98,21 @@ static size_t codec_ctx_bytes(const NintDevB& w) { return w.table ? (size_t)w.ta
 // CTAs of `smem` bytes each that fit an SM, at most `cap`.
 static int ctas_per_sm(size_t smem, int cap) { return std::max(1, std::min(cap, (int)((220 * 1024) / (smem + 1024)))); }
 
-static size_t gemv1_smem(const NintDevB& w, int rb_per_cta) {
-    return codec_ctx_bytes(w) + (size_t)rb_per_cta * 16 * 8 + (size_t)8 * gemv1_bl_stages(w.rec_words) * w.rec_words * 4;
+// Per-warp copies of the partial sums while they stay small; shared copy with atomics beyond.
+static bool gemv1_private_sums(int rb_per_cta) { return rb_per_cta <= 8; }
+static size_t gemv1_smem(const NintDevB& w, int rb_per_cta, int warps) {
+    const int copies = gemv1_private_sums(rb_per_cta) ? warps : 1;
+    return codec_ctx_bytes(w) + (size_t)(copies + 1) * rb_per_cta * 16 * 4 + (size_t)warps * gemv1_bl_stages(w.rec_words) * w.rec_words * 4;
+}
+// Warps per CTA of the single-row kernel: each warp owns whole chunks of K, so 8 to 12 warps are
+// chosen to make the largest number of chunks per warp as small as possible (lattice and wide
+// records stay at 8: their kernels are built for 256 threads).
+static int gemv1_warps(const NintDevB& w) {
+    if (w.table || w.wc > 24) return 8;
+    int best = 8;
+    for (int n = 9; n <= 12; ++n)
+        if ((w.nchunks + n - 1) / n < (w.nchunks + best - 1) / best) best = n;
+    return best;
 }
 static size_t gemvn_smem(const NintDevB& w, int rb_per_cta, int passes, int kt) {
     const int mb = 2 * passes, tg = kt * kChunkGroupsB;
@@ -167,9 +180,12 @@ void launch_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtyp
     const int sms = device_sm_count(device);
     if (m == 1) {
         // three CTAs per SM, all resident at once; row-blocks are split evenly inside the kernel
-        p.grid = std::min(w.nrb, ctas_per_sm(gemv1_smem(w, 1), 3) * sms);
+        const int warps = gemv1_warps(w);
+        p.threads = warps * 32;
+        p.grid = std::min(w.nrb, ctas_per_sm(gemv1_smem(w, 1, warps), warps > 8 ? 2 : 3) * sms);
         a.rb_per_cta = (w.nrb + p.grid - 1) / p.grid;
-        p.smem = gemv1_smem(w, a.rb_per_cta);
+        a.private_sums = gemv1_private_sums(a.rb_per_cta);
+        p.smem = gemv1_smem(w, a.rb_per_cta, warps);
     } else {
         launch_x_planes(w, x, m, planes_scratch(device, nint_bl_planes_bytes(w, m)), &a.xq_g, &a.gtab_g, s);
         p.passes = passes_for(m);
@@ -189,7 +205,8 @@ void launch_nint_bl_gemv_routed(GemvArgsB a, int pairs, int device, cudaStream_t
     const int want = (3 * device_sm_count(device) + pairs - 1) / std::max(pairs, 1);
     const int splits = std::max(1, std::min(a.rb_per_expert, want));
     a.rb_per_cta = (a.rb_per_expert + splits - 1) / splits;
-    p.smem = gemv1_smem(w, a.rb_per_cta);
+    a.private_sums = gemv1_private_sums(a.rb_per_cta);
+    p.smem = gemv1_smem(w, a.rb_per_cta, 8);
     p.grid = splits;
     p.grid_y = pairs;
     dispatch(a, p, s, "routed GEMV");

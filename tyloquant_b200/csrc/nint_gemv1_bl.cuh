@@ -47,6 +47,7 @@ struct GemvArgsB {
     const int* pair_order;
     int n_experts;
     int kt_chunks;           // batched kernel: chunks of K staged per tile (a multiple of the warps per CTA)
+    int private_sums;        // single-row kernel: one copy of the partial sums per warp instead of shared-memory atomics
     // Batched kernel: the activation rows already quantised by x_planes_kernel, row r at
     // xq_g + r * ngp * QS and gtab_g + r * ngp (ngp = nchunks * 8 groups, QS quads per group).
     const uint2* xq_g;
@@ -206,8 +207,17 @@ struct XChunkRaw {
     uint2 v[JJ];   // four bf16 each
 };
 template <int T>
-__device__ __forceinline__ void x_chunk_load(const __nv_bfloat16* __restrict__ xrow, bool vec_ok, int k, int gs, int g, int c,
+__device__ __forceinline__ void x_chunk_load(const __nv_bfloat16* __restrict__ xrow, bool fast, bool vec_ok, int k, int gs, int g, int c,
                                              XChunkRaw<T>& raw) {
+    if (fast) {   // the whole chunk lies inside the row, groups are whole quads, 8-byte loads are aligned
+#pragma unroll
+        for (int jj = 0; jj < XChunkRaw<T>::JJ; ++jj) {
+            const int j = c + 4 * jj;
+            raw.v[jj] = make_uint2(0u, 0u);
+            if (j < 2 * T) raw.v[jj] = __ldg(reinterpret_cast<const uint2*>(xrow + g * gs + 4 * j));
+        }
+        return;
+    }
 #pragma unroll
     for (int jj = 0; jj < XChunkRaw<T>::JJ; ++jj) {
         const int j = c + 4 * jj, k0 = g * gs + 4 * j;
@@ -229,41 +239,36 @@ __device__ __forceinline__ void x_chunk_load(const __nv_bfloat16* __restrict__ x
 template <int T>
 __device__ __forceinline__ void x_chunk_quant(const XChunkRaw<T>& raw, int c, uint32_t (&xlo)[T], uint32_t (&xhi)[T], float4& gt) {
     constexpr int JJ = XChunkRaw<T>::JJ;
-    float v[JJ][4];
-    uint32_t ab = 0u;   // largest magnitude of the group as float bits (orders like the value; NaN is largest)
+    // largest magnitude of the group from the bf16 bit patterns (they order like the values; NaN is largest)
+    uint32_t m2 = 0u;
 #pragma unroll
-    for (int jj = 0; jj < JJ; ++jj) {
-        v[jj][0] = __uint_as_float(raw.v[jj].x << 16);
-        v[jj][1] = __uint_as_float(raw.v[jj].x & 0xFFFF0000u);
-        v[jj][2] = __uint_as_float(raw.v[jj].y << 16);
-        v[jj][3] = __uint_as_float(raw.v[jj].y & 0xFFFF0000u);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) ab = max(ab, __float_as_uint(v[jj][i]) & 0x7FFFFFFFu);
-    }
+    for (int jj = 0; jj < JJ; ++jj)
+        m2 = __vimax3_s16x2(m2, raw.v[jj].x & 0x7FFF7FFFu, raw.v[jj].y & 0x7FFF7FFFu);
+    uint32_t ab = max(m2 & 0xFFFFu, m2 >> 16);
     ab = max(ab, __shfl_xor_sync(0xffffffffu, ab, 1));
     ab = max(ab, __shfl_xor_sync(0xffffffffu, ab, 2));
-    const uint32_t eb = max(ab >> 23, 15u);
+    const uint32_t eb = max(ab >> 7, 15u);
     const float sx = __uint_as_float(eb >= 255u ? 0x7FC00000u : (eb - 14u) << 23);   // NaN for a group holding inf or NaN
     const float inv = __uint_as_float((268u - min(eb, 254u)) << 23);
     constexpr float kMagic = 12582912.f;   // 1.5 * 2^23
-    float xs = 0.f;
     uint32_t mine_lo[JJ], mine_hi[JJ];
+    int xsum_lo = 0, xsum_hi = 0;
 #pragma unroll
     for (int jj = 0; jj < JJ; ++jj) {
-        uint32_t f[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float r = fmaf(v[jj][i], inv, kMagic);
-            xs += r - kMagic;
-            f[i] = __float_as_uint(r);
-        }
-        const uint32_t t01 = __byte_perm(f[0], f[1], 0x5140), t23 = __byte_perm(f[2], f[3], 0x5140);
+        const uint32_t f0 = __float_as_uint(fmaf(__uint_as_float(raw.v[jj].x << 16), inv, kMagic));
+        const uint32_t f1 = __float_as_uint(fmaf(__uint_as_float(raw.v[jj].x & 0xFFFF0000u), inv, kMagic));
+        const uint32_t f2 = __float_as_uint(fmaf(__uint_as_float(raw.v[jj].y << 16), inv, kMagic));
+        const uint32_t f3 = __float_as_uint(fmaf(__uint_as_float(raw.v[jj].y & 0xFFFF0000u), inv, kMagic));
+        const uint32_t t01 = __byte_perm(f0, f1, 0x5140), t23 = __byte_perm(f2, f3, 0x5140);
         mine_lo[jj] = __byte_perm(t01, t23, 0x5410);
         mine_hi[jj] = __byte_perm(t01, t23, 0x7632);
+        xsum_lo = (int)__dp4a(mine_lo[jj], 0x01010101u, (unsigned)xsum_lo);   // unsigned low bytes
+        xsum_hi = __dp4a((int)mine_hi[jj], 0x01010101, xsum_hi);              // signed high bytes
     }
-    xs += __shfl_xor_sync(0xffffffffu, xs, 1);
-    xs += __shfl_xor_sync(0xffffffffu, xs, 2);
-    const float sxx = sx * xs;
+    int xsi = xsum_hi * 256 + xsum_lo;   // sum of the lane's xi
+    xsi += __shfl_xor_sync(0xffffffffu, xsi, 1);
+    xsi += __shfl_xor_sync(0xffffffffu, xsi, 2);
+    const float sxx = sx * (float)xsi;
     // quad 2t + (c&1) belongs to this lane when (t & 1) == (c >> 1), else to lane c ^ 2; either way slot t >> 1
     const bool own_even = (c >> 1) == 0;
 #pragma unroll
@@ -284,13 +289,14 @@ __device__ __forceinline__ void x_chunk_quant(const XChunkRaw<T>& raw, int c, ui
     gt.w = __shfl_sync(0xffffffffu, sxx, 8 * c + 4);
 }
 
-// Shared memory: partial sums [rb_per_cta][16] f32 | anchors [rb_per_cta][16] u32 | per warp a
-// ring of S item records.  Every warp streams its own items (chunk-major) through its ring with
+// Shared memory: partial sums [warps or 1][rb_per_cta][16] f32 | anchors [rb_per_cta][16] u32 |
+// per warp a ring of S item records.  With few row-blocks per CTA every warp adds into its own
+// copy of the partial sums (plain read-modify-write), else all share one through atomics.  Every warp streams its own items (chunk-major) through its ring with
 // 16-byte asynchronous copies; the first S items are requested before the kernel waits for its
 // predecessor in the stream, since weights are constants.  The activation row is read straight
 // from global memory, one chunk ahead, and quantised in registers by the warp that needs it.
 template <class C>
-__global__ void __launch_bounds__(256, C::MIN_CTAS) gemv1_bl_kernel(const GemvArgsB a) {
+__global__ void __launch_bounds__(C::MIN_CTAS >= 3 ? 384 : 256, C::MIN_CTAS >= 3 ? 2 : C::MIN_CTAS) gemv1_bl_kernel(const GemvArgsB a) {
     constexpr int G = kChunkGroupsB, T = C::T, WC = C::WC, SW = C::SW, REC = (WC + SW) * 32;
     constexpr int S = gemv1_bl_stages(REC);
     const NintDevB& w = a.w;
@@ -301,7 +307,8 @@ __global__ void __launch_bounds__(256, C::MIN_CTAS) gemv1_bl_kernel(const GemvAr
     typename C::Ctx ctx;
     ctx.init(smem, w, tid, blockDim.x);   // constant tables: visible after the first __syncthreads
     float* ypart = reinterpret_cast<float*>(smem + C::ctx_bytes(w));
-    uint32_t* anch = reinterpret_cast<uint32_t*>(ypart + (size_t)a.rb_per_cta * 16);
+    const int ycopies = a.private_sums ? nwarps : 1, ystride = a.rb_per_cta * 16;
+    uint32_t* anch = reinterpret_cast<uint32_t*>(ypart + (size_t)ycopies * ystride);
     uint32_t* ring = anch + (size_t)a.rb_per_cta * 16 + (size_t)warp * S * REC;   // ctx_bytes is a multiple of 16
 
     // balanced split of the row-blocks over gridDim.x: CTA b owns [b*R/grid, (b+1)*R/grid) of the
@@ -327,28 +334,30 @@ __global__ void __launch_bounds__(256, C::MIN_CTAS) gemv1_bl_kernel(const GemvAr
     // row-block of the CTA.  Two cursors walk that sequence (issue runs S items ahead).
     const int my_segs = warp < w.nchunks ? (w.nchunks - warp + nwarps - 1) / nwarps : 0;
     const int n_mine = my_segs * nrb;
-    int iss_i = 0, iss_seg = warp, iss_rbl = 0, iss_stage = 0;
+    // the record pointer walks (chunk, row-block) incrementally: next row-block, or back to the CTA's
+    // first row-block of the warp's next chunk
+    int iss_i = 0, iss_rbl = 0, iss_stage = 0;
+    const uint32_t* iss_src = w.items + ((size_t)rb0 * w.nchunks + warp) * REC + lane * 4;
+    const long long step_rb = (long long)w.nchunks * REC, step_seg = (long long)nwarps * REC - (long long)(nrb - 1) * w.nchunks * REC;
     auto issue = [&]() {
         if (iss_i < n_mine) {
-            const uint32_t* src = w.items + ((size_t)(rb0 + iss_rbl) * w.nchunks + iss_seg) * REC;
-            uint32_t* dst = ring + iss_stage * REC;
+            uint32_t* dst = ring + iss_stage * REC + lane * 4;
 #pragma unroll
             for (int off = 0; off < REC; off += 128)
-                if (off + 128 <= REC || lane * 4 < REC - off) cp_async16_b(dst + off + lane * 4, src + off + lane * 4);
+                if (off + 128 <= REC || lane * 4 < REC - off) cp_async16_b(dst + off, iss_src + off);
         }
         cp_async_commit_b();   // one group per item slot, empty past the end: keeps the wait count uniform
         ++iss_i;
-        if (++iss_rbl == nrb) { iss_rbl = 0; iss_seg += nwarps; }
+        if (++iss_rbl == nrb) { iss_rbl = 0; iss_src += step_seg; }
+        else iss_src += step_rb;
         if (++iss_stage == S) iss_stage = 0;
     };
 
     pdl_launch_dependents_b();
 #pragma unroll
     for (int i = 0; i < S; ++i) issue();
-    for (int i = tid; i < nrb * 16; i += blockDim.x) {
-        ypart[i] = 0.f;
-        anch[i] = __ldg(w.anchors + rb0 * 16 + i);
-    }
+    for (int i = tid; i < ycopies * ystride; i += blockDim.x) ypart[i] = 0.f;
+    for (int i = tid; i < nrb * 16; i += blockDim.x) anch[i] = __ldg(w.anchors + rb0 * 16 + i);
     __syncthreads();
     pdl_wait_b();
 
@@ -360,18 +369,22 @@ __global__ void __launch_bounds__(256, C::MIN_CTAS) gemv1_bl_kernel(const GemvAr
     const uint32_t m10 = (live && (q >> 1) == 2) ? 0xFFFFFFFFu : 0u, m11 = (live && (q >> 1) == 3) ? 0xFFFFFFFFu : 0u;
 
     const bool vec_ok = (reinterpret_cast<uintptr_t>(xrow) & 7) == 0;
+    const bool fast_ok = vec_ok && (w.gs & 7) == 0;   // then chunks that end inside the row load without per-element checks
+    const int chunk_len = G * w.gs;
+    float* ymine = ypart + (a.private_sums ? warp * ystride : 0);
     int cur_seg = -1;
     uint32_t xlo[T], xhi[T];
     float4 gt = make_float4(0.f, 0.f, 0.f, 0.f);   // (sx, sx*X) of groups 2c, 2c+1 of the chunk
     XChunkRaw<T> raw;                              // the activations of the warp's next chunk, requested one chunk ahead
-    if (n_mine > 0) x_chunk_load<T>(xrow, vec_ok, w.k, w.gs, warp * G + q, c, raw);
+    if (n_mine > 0) x_chunk_load<T>(xrow, fast_ok && (warp + 1) * chunk_len <= w.k, vec_ok, w.k, w.gs, warp * G + q, c, raw);
 
     int seg = warp, rbl = 0, stage = 0;
     for (int i = 0; i < n_mine; ++i) {
         if (seg != cur_seg) {
             cur_seg = seg;
             x_chunk_quant<T>(raw, c, xlo, xhi, gt);
-            if (seg + nwarps < w.nchunks) x_chunk_load<T>(xrow, vec_ok, w.k, w.gs, (seg + nwarps) * G + q, c, raw);
+            if (seg + nwarps < w.nchunks)
+                x_chunk_load<T>(xrow, fast_ok && (seg + nwarps + 1) * chunk_len <= w.k, vec_ok, w.k, w.gs, (seg + nwarps) * G + q, c, raw);
         }
         asm volatile("cp.async.wait_group %0;\n" ::"n"(S - 1) : "memory");
         __syncwarp();
@@ -415,8 +428,13 @@ __global__ void __launch_bounds__(256, C::MIN_CTAS) gemv1_bl_kernel(const GemvAr
         v_lo += __shfl_xor_sync(0xffffffffu, v_lo, 2);
         v_hi += __shfl_xor_sync(0xffffffffu, v_hi, 2);
         if (c == 0) {
-            atomicAdd(ypart + rbl * 16 + q, v_lo);
-            atomicAdd(ypart + rbl * 16 + q + 8, v_hi);
+            if (a.private_sums) {   // this warp's own copy: no other warp touches it
+                ymine[rbl * 16 + q] += v_lo;
+                ymine[rbl * 16 + q + 8] += v_hi;
+            } else {
+                atomicAdd(ypart + rbl * 16 + q, v_lo);
+                atomicAdd(ypart + rbl * 16 + q + 8, v_hi);
+            }
         }
         if (++rbl == nrb) { rbl = 0; seg += nwarps; }
         if (++stage == S) stage = 0;
@@ -426,7 +444,8 @@ __global__ void __launch_bounds__(256, C::MIN_CTAS) gemv1_bl_kernel(const GemvAr
     for (int i = tid; i < nrb * 16; i += blockDim.x) {
         const int row = rbl0 * 16 + i;   // row inside the problem (matrix, or the pair's expert)
         if (row < row_limit) {
-            const float v = ypart[i];
+            float v = ypart[i];
+            for (int cp = 1; cp < ycopies; ++cp) v += ypart[cp * ystride + i];
             if (a.y_dtype == 0 /* MFQB_F32 */) reinterpret_cast<float*>(a.y)[y_off + row] = v;
             else reinterpret_cast<__nv_bfloat16*>(a.y)[y_off + row] = __float2bfloat16_rn(v);
         }
