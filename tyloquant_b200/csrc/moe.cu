@@ -35,7 +35,7 @@ struct PlanBufs {
 
 void launch_nint_bl_dequant(const NintDevB& w, void* out, int out_dtype, cudaStream_t s);
 void launch_nint_bl_gemv_routed(GemvArgsB a, int pairs, int device, cudaStream_t s);
-void launch_nint_bl_gemv_tiles(GemvArgsB a, int max_tiles, int device, cudaStream_t s);
+void launch_nint_bl_gemv_tiles(GemvArgsB a, int tile_m, int max_tiles, int device, cudaStream_t s);
 void check_nint_supported(const HostNint& t);
 size_t nint_bl_planes_bytes(const NintDevB& w, int rows);
 void launch_x_planes(const NintDevB& w, const void* x, int rows, void* planes, const uint2** xq_g, const float2** gtab_g, cudaStream_t s);
@@ -206,7 +206,13 @@ int mfqb_moe_dequant_expert(const mfqb_moe_weight* w, int expert, void* out, int
 }
 
 // Tiles of 8 pairs per expert pay off once an expert sees several pairs on average.
-static bool moe_use_tiles(const mfqb_moe_weight* w, int pairs) { return pairs >= 4 * w->info.n_experts; }
+// Pairs per route-plan tile (2, 4 or 8, sized to the average number of pairs an expert sees), or
+// 0: fewer pairs than experts, every pair runs as a single-row problem of its own.
+static int moe_tile_m(const mfqb_moe_weight* w, int pairs) {
+    const int e = w->info.n_experts;
+    if (pairs < e) return 0;
+    return pairs <= 5 * e / 2 ? 2 : (pairs <= 5 * e ? 4 : 8);
+}
 
 // Bytes of quantised activation planes the tile path needs for `rows` input rows: one set per
 // distinct group size among the held cohorts (cohorts of equal group size share theirs).
@@ -222,10 +228,10 @@ static size_t moe_planes_bytes(const mfqb_moe_weight* w, int rows) {
 }
 
 // plan == nullptr: one single-row problem per pair.  Otherwise the batched kernel runs over the
-// plan's tiles (the plan must have been built for these ids with tile_m = 8) and `planes` is
+// plan's tiles (the plan must have been built for these ids with the same tile_m) and `planes` is
 // moe_planes_bytes() of device memory for the quantised input rows.
 static void mul_mat_id_impl(const mfqb_moe_weight* w, const void* x, int x_per_pair, const int32_t* ids, int tokens, int routes,
-                            void* out, int out_dtype, const PlanBufs* plan, void* planes, cudaStream_t stream) {
+                            void* out, int out_dtype, const PlanBufs* plan, int tile_m, void* planes, cudaStream_t stream) {
     const int pairs = tokens * routes, ope = w->info.out_per_expert;
     const int in_rows = x_per_pair ? pairs : tokens;
     struct PlaneSet { int gs; const uint2* xq; const float2* gtab; };
@@ -255,7 +261,7 @@ static void mul_mat_id_impl(const mfqb_moe_weight* w, const void* x, int x_per_p
             a.tile_bounds = plan->tile_bounds;
             a.pair_order = plan->pair_order;
             a.n_experts = w->info.n_experts;
-            const int max_tiles = pairs / 8 + std::min(pairs, w->info.n_experts);
+            const int max_tiles = pairs / tile_m + std::min(pairs, w->info.n_experts);
             if (max_tiles > 65535) fail(MFQB_ERR_ARG, "mfqb_mul_mat_id: too many route tiles (%d)", max_tiles);
             const PlaneSet* ps = nullptr;
             for (const PlaneSet& c : sets)
@@ -269,7 +275,7 @@ static void mul_mat_id_impl(const mfqb_moe_weight* w, const void* x, int x_per_p
             }
             a.xq_g = ps->xq;
             a.gtab_g = ps->gtab;
-            launch_nint_bl_gemv_tiles(a, max_tiles, w->info.device, stream);
+            launch_nint_bl_gemv_tiles(a, tile_m, max_tiles, w->info.device, stream);
             continue;
         }
         a.route_ids = ids;
@@ -294,14 +300,15 @@ int mfqb_mul_mat_id(const mfqb_moe_weight* w, const void* x, int x_per_pair, con
         if (tokens == 0) return;
         DeviceGuard guard(w->info.device);
         const int pairs = tokens * routes;
-        if (moe_use_tiles(w, pairs)) {   // larger batches: route plan in library scratch, batched kernel over its tiles
+        const int tile_m = moe_tile_m(w, pairs);
+        if (tile_m) {   // larger batches: route plan in library scratch, batched kernel over its tiles
             const size_t b_plan = PlanBufs::bytes(w->info.n_experts, pairs);
             char* s = static_cast<char*>(scratch_get(w->info.device, b_plan + moe_planes_bytes(w, x_per_pair ? pairs : tokens), 1));
             PlanBufs plan = PlanBufs::carve(s, w->info.n_experts);
-            launch_route_plan(ids, pairs, w->info.n_experts, 8, plan.expert_bounds, plan.tile_bounds, plan.pair_order, stream);
-            mul_mat_id_impl(w, x, x_per_pair, ids, tokens, routes, out, out_dtype, &plan, s + b_plan, stream);
+            launch_route_plan(ids, pairs, w->info.n_experts, tile_m, plan.expert_bounds, plan.tile_bounds, plan.pair_order, stream);
+            mul_mat_id_impl(w, x, x_per_pair, ids, tokens, routes, out, out_dtype, &plan, tile_m, s + b_plan, stream);
         } else {
-            mul_mat_id_impl(w, x, x_per_pair, ids, tokens, routes, out, out_dtype, nullptr, nullptr, stream);
+            mul_mat_id_impl(w, x, x_per_pair, ids, tokens, routes, out, out_dtype, nullptr, 0, nullptr, stream);
         }
     });
 }
@@ -318,7 +325,8 @@ int mfqb_moe_ffn(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* down, co
         DeviceGuard guard(gate_up->info.device);
         const size_t pairs = (size_t)tokens * routes;
         const size_t b_gu = pairs * f2 * 4, b_hid = (pairs * f * 2 + 255) / 256 * 256, b_dn = pairs * h * 4;
-        const bool tiles = moe_use_tiles(gate_up, (int)pairs);
+        const int tile_m = moe_tile_m(gate_up, (int)pairs);
+        const bool tiles = tile_m != 0;
         const size_t b_plan = tiles ? PlanBufs::bytes(gate_up->info.n_experts, pairs) : 0;
         const size_t b_pgu = tiles ? moe_planes_bytes(gate_up, tokens) : 0, b_pdn = tiles ? moe_planes_bytes(down, (int)pairs) : 0;
         char* s = static_cast<char*>(scratch_get(gate_up->info.device, b_gu + b_hid + b_dn + b_plan + b_pgu + b_pdn));
@@ -328,12 +336,12 @@ int mfqb_moe_ffn(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* down, co
         PlanBufs plan{};
         if (tiles) {   // one route plan serves both matmuls
             plan = PlanBufs::carve(s + b_gu + b_hid + b_dn, gate_up->info.n_experts);
-            launch_route_plan(ids, (int)pairs, gate_up->info.n_experts, 8, plan.expert_bounds, plan.tile_bounds, plan.pair_order, stream);
+            launch_route_plan(ids, (int)pairs, gate_up->info.n_experts, tile_m, plan.expert_bounds, plan.tile_bounds, plan.pair_order, stream);
         }
         char* planes = s + b_gu + b_hid + b_dn + b_plan;
-        mul_mat_id_impl(gate_up, x, 0, ids, tokens, routes, gu, MFQB_F32, tiles ? &plan : nullptr, planes, stream);
+        mul_mat_id_impl(gate_up, x, 0, ids, tokens, routes, gu, MFQB_F32, tiles ? &plan : nullptr, tile_m, planes, stream);
         launch_swiglu(gu, MFQB_F32, (int)pairs, f, hid, stream);
-        mul_mat_id_impl(down, hid, 1, ids, tokens, routes, dn, MFQB_F32, tiles ? &plan : nullptr, planes + b_pgu, stream);
+        mul_mat_id_impl(down, hid, 1, ids, tokens, routes, dn, MFQB_F32, tiles ? &plan : nullptr, tile_m, planes + b_pgu, stream);
         launch_weighted_reduce(dn, MFQB_F32, weights, tokens, routes, h, y, y_dtype, stream);
     });
 }
@@ -378,7 +386,8 @@ int mfqb_moe_ffn_static(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* d
         if (tokens <= 0 || routes < 1) return;
         const size_t pairs = (size_t)tokens * routes;
         const size_t b_gu = pairs * f2 * 4, b_hid = (pairs * f * 2 + 255) / 256 * 256, b_dn = pairs * h * 4;
-        const bool tiles = moe_use_tiles(gate_up, (int)pairs);
+        const int tile_m = moe_tile_m(gate_up, (int)pairs);
+        const bool tiles = tile_m != 0;
         const size_t b_plan = tiles ? PlanBufs::bytes(gate_up->info.n_experts, pairs) + moe_planes_bytes(gate_up, tokens) +
                                           moe_planes_bytes(down, (int)pairs)
                                     : 0;
@@ -399,12 +408,12 @@ int mfqb_moe_ffn_static(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* d
         PlanBufs plan{};
         if (tiles) {   // the route plan lives in the same fixed array
             plan = PlanBufs::carve(s + b_gu + b_hid + b_dn, gate_up->info.n_experts);
-            launch_route_plan(ids, (int)pairs, gate_up->info.n_experts, 8, plan.expert_bounds, plan.tile_bounds, plan.pair_order, stream);
+            launch_route_plan(ids, (int)pairs, gate_up->info.n_experts, tile_m, plan.expert_bounds, plan.tile_bounds, plan.pair_order, stream);
         }
         char* planes = reinterpret_cast<char*>(s) + b_gu + b_hid + b_dn + (tiles ? PlanBufs::bytes(gate_up->info.n_experts, pairs) : 0);   // inside the fixed array, after the plan
-        mul_mat_id_impl(gate_up, x, 0, ids, tokens, routes, gu, MFQB_F32, tiles ? &plan : nullptr, planes, stream);
+        mul_mat_id_impl(gate_up, x, 0, ids, tokens, routes, gu, MFQB_F32, tiles ? &plan : nullptr, tile_m, planes, stream);
         launch_swiglu(gu, MFQB_F32, (int)pairs, f, hid, stream);
-        mul_mat_id_impl(down, hid, 1, ids, tokens, routes, dn, MFQB_F32, tiles ? &plan : nullptr, planes + b_pgu, stream);
+        mul_mat_id_impl(down, hid, 1, ids, tokens, routes, dn, MFQB_F32, tiles ? &plan : nullptr, tile_m, planes + b_pgu, stream);
         launch_weighted_reduce(dn, MFQB_F32, weights, tokens, routes, h, y, y_dtype, stream);
     });
 }

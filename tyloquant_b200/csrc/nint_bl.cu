@@ -212,15 +212,17 @@ void launch_nint_bl_gemv_routed(GemvArgsB a, int pairs, int device, cudaStream_t
     dispatch(a, p, s, "routed GEMV");
 }
 
-// Batched kernel over route-plan tiles (up to 8 pairs of one expert each) for one cohort.
-void launch_nint_bl_gemv_tiles(GemvArgsB a, int max_tiles, int device, cudaStream_t s) {
+// Batched kernel over route-plan tiles (up to tile_m = 2, 4 or 8 pairs of one expert each) for one cohort.
+void launch_nint_bl_gemv_tiles(GemvArgsB a, int tile_m, int max_tiles, int device, cudaStream_t s) {
     const NintDevB& w = a.w;
-    a.m = 8;
+    a.m = tile_m;
     GemvPlanB p;
-    p.passes = 4;
+    p.passes = tile_m / 2;
     a.kt_chunks = gemvn_kt(w, p.passes);
+    // max_tiles is an upper bound and a launch covers one cohort only, so most of its tiles return at
+    // once: split an expert's rows finely (about eight row-blocks per CTA) to keep the SMs busy
     const int want = (2 * device_sm_count(device) + max_tiles - 1) / std::max(max_tiles, 1);
-    const int splits = std::max(std::max(1, (a.rb_per_expert + 47) / 48), std::min(a.rb_per_expert, want));
+    const int splits = std::max(1, std::min(a.rb_per_expert, std::max(a.rb_per_expert / 8, want)));
     a.rb_per_cta = (a.rb_per_expert + splits - 1) / splits;
     p.smem = gemvn_smem(w, a.rb_per_cta, p.passes, a.kt_chunks);
     p.grid = splits;
