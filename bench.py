@@ -167,7 +167,7 @@ def main() -> None:
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
     base = {"metric": "packed GEMV HBM GB/s", "unit": "GB/s", "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 x, u3 codes, f32 accumulate",
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u3 codes x s16 activations (bf16 quantised per group, two s8 planes), s32 accumulate, f32 scales",
             "data": "synthetic", "config": {"workload": WORKLOAD, "pool": POOL, "l2_policy": "inputs larger than L2 "
                                             f"({POOL} x 7.2 MB weights per step)", "parallelism": f"replicas x{args.gpus}"}}
 
@@ -310,13 +310,13 @@ def main() -> None:
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": POOL * N_COLS * 2,
                 "d2h_bytes_per_step": POOL * N_ROWS * 2, "ms_per_step": e2e_ms,
                 "api": "mfqb_mul_mat_host (pinned host x and y, weights resident)"},
-        "roofline": {"bound": "hbm", "kernel": "nint_gemv_kernel<3,6,5>", "achieved": achieved, "peak": peaks["hbm_gbs"],
+        "roofline": {"bound": "hbm", "kernel": "gemv1_bl_kernel<NintCodec<3,3>>", "achieved": achieved, "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": f"{peak_kind} copy bandwidth",
                      "us_per_launch": launch_us, "algorithmic_bytes_per_launch": algorithmic_bytes(payload, 1, N_ROWS, N_COLS),
                      "device_bytes_per_launch": weights[0].device_bytes,
                      # dram__bytes_read.sum + dram__bytes_write.sum of one launch, ncu --set full capture
                      # summarised in profiles/nint_gemv_m1_nint3_4096x4096.md
-                     "traffic": 7434496},
+                     "traffic": 7979264},
     })
     if args.gpus == 1:
         cb, _ = cpu_reference_arm(3, 3, budget_s=12.0)

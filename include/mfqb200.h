@@ -238,7 +238,15 @@ int mfqb_moe_ffn(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* down, co
  *   -> allreduce ... -> destroy.   All ranks must issue the same sequence of allreduce calls
  * with the same n.  A wait that passes its deadline (default 2 s) sets the status word to
  * MFQB_ERR_TIMEOUT and lets the kernel return; mfqb_comm_status reads it without
- * synchronising.  max_elems <= 262144 floats, world <= 8.
+ * synchronising.  max_elems <= 524288 floats, world <= 8.
+ *
+ * mfqb_mul_mat_allreduce is the row-parallel linear itself (forward_tensor_parallel_flat +
+ * reduce, cpp_runtime/mfq_decode.cpp:9137-9207): every rank holds an input-axis slice of the
+ * weight (mfqb_weight_from_blob_slice, axis 1) and the matching slice x[m, k_slice]; the
+ * product kernel's own epilogue pushes its float32 partial rows to the peers and writes the sum
+ * over ranks, y[m, n], on every rank -- one kernel per rank instead of a product, a partial
+ * vector in memory and a collective.  It counts as one collective call per activation row in the
+ * sequence all ranks must share; n <= max_elems.
  * --------------------------------------------------------------------------------- */
 typedef struct mfqb_comm mfqb_comm;
 int mfqb_comm_create(int rank, int world, uint64_t max_elems, int device, mfqb_comm** out);
@@ -246,6 +254,8 @@ int mfqb_comm_handle(const mfqb_comm* c, void* handle64);
 int mfqb_comm_attach(mfqb_comm* c, int peer, const void* handle64);
 int mfqb_comm_set_timeout_ms(mfqb_comm* c, int ms);
 int mfqb_allreduce_f32(mfqb_comm* c, const float* in, float* out, uint64_t n, mfqb_stream_t stream);
+int mfqb_mul_mat_allreduce(const mfqb_weight* w, const void* x_bf16, int m, mfqb_comm* c, void* y, int y_dtype,
+                           mfqb_stream_t stream);
 int mfqb_comm_status(const mfqb_comm* c, int* status);
 int mfqb_comm_destroy(mfqb_comm* c);
 

@@ -67,6 +67,25 @@ def _worker(rank, world, port, q):
         y_ref = O.moe_ffn(x, O.dequant_nintm(O.unpack_nintm(gu_blob)), O.dequant_nintm(O.unpack_nintm(dn_blob)), rid, rw)
         res["ep_err"] = float(np.linalg.norm(y - y_ref) / np.linalg.norm(y_ref))
 
+        # 2b. row-parallel linear fused with its reduction: each rank holds a K-slice of the weight
+        from tyloquant_b200 import QuantWeight
+        for bits_, gs_, sb_, dtype_ in ((3, 24, 5, "NINT3"), (4, 32, 6, "NINT4")):
+            n_rows, k_cols = 200, 40 * gs_
+            blob = encode.random_nint_blob(n_rows, k_cols, bits_, gs_, sb_, seed=77)
+            cut = 16 * gs_
+            lo, hi = (0, cut) if rank == 0 else (cut, k_cols)
+            shard = QuantWeight.from_blob(dtype_, blob, device=rank, axis=1, begin=lo, end=hi)
+            xr = encode.bf16_round(np.random.default_rng(5).standard_normal((3, k_cols), dtype=np.float32))
+            y_f = c.matmul_allreduce(shard, torch.from_numpy(xr[:, lo:hi].copy()).cuda().to(torch.bfloat16), out_dtype=torch.float32)
+            y_want = O.linear(xr, O.dequant_nint(O.unpack_nint(blob)))
+            res[f"rowpar_err_{dtype_}"] = float(np.linalg.norm(y_f.cpu().numpy() - y_want) / np.linalg.norm(y_want))
+            ys = [torch.empty(y_f.shape) for _ in range(world)]
+            dist.all_gather(ys, y_f.cpu())
+            res[f"rowpar_same_{dtype_}"] = all(torch.equal(ys[0], t) for t in ys)
+            shard.free()
+        torch.cuda.synchronize()
+        res["status_ok2"] = c.status() == 0
+
         # 3. a rank that does not join: the other rank's wait runs out and reports it
         dist.barrier()
         c.set_timeout_ms(200)
@@ -103,5 +122,8 @@ def test_allreduce_expert_parallel_and_timeout_on_two_gpus():
             assert r[f"sum{n}"] and r[f"same{n}"], (rank, n)
         assert r["status_ok"]
         assert r["ep_err"] <= 4e-3
+        for dt in ("NINT3", "NINT4"):
+            assert r[f"rowpar_err_{dt}"] <= 1e-3 and r[f"rowpar_same_{dt}"], (rank, dt)
+        assert r["status_ok2"]
     assert results[0]["timeout_status"] == _capi.ERR_TIMEOUT
     assert results[0]["context_alive"]

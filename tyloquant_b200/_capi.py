@@ -87,6 +87,7 @@ _SIGNATURES = {
     "mfqb_comm_attach": (_i, [_vp, _i, _vp]),
     "mfqb_comm_set_timeout_ms": (_i, [_vp, _i]),
     "mfqb_allreduce_f32": (_i, [_vp, _vp, _vp, _u64, _vp]),
+    "mfqb_mul_mat_allreduce": (_i, [_vp, _vp, _i, _vp, _vp, _i, _vp]),
     "mfqb_comm_status": (_i, [_vp, _P(_i)]),
     "mfqb_comm_destroy": (_i, [_vp]),
     "mfqb_moe_ffn_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _i, _vp]),

@@ -58,6 +58,22 @@ class Communicator:
                                      torch.cuda.current_stream(self.device).cuda_stream))
         return out
 
+    def matmul_allreduce(self, weight, x, out_dtype=None):
+        """Row-parallel linear: ``weight`` is this rank's input-axis slice (``QuantWeight``), ``x`` the
+        matching slice ``[m, k_slice]`` in bf16; returns the sum over ranks ``[m, n]`` on every rank.
+        The product kernel itself pushes its partial rows to the peers and adds theirs."""
+        import torch
+        out_dtype = out_dtype or torch.bfloat16
+        if x.dtype != torch.bfloat16 or not x.is_cuda:
+            raise ValueError("matmul_allreduce takes a bf16 CUDA tensor")
+        x = x.contiguous().reshape(-1, weight.k)
+        y = torch.empty((x.shape[0], weight.n), dtype=out_dtype, device=x.device)
+        from ._capi import BF16, F32
+        check(lib.mfqb_mul_mat_allreduce(weight._h, x.data_ptr(), x.shape[0], self._h, y.data_ptr(),
+                                         F32 if out_dtype == torch.float32 else BF16,
+                                         torch.cuda.current_stream(self.device).cuda_stream))
+        return y
+
     def status(self) -> int:
         s = C.c_int()
         check(lib.mfqb_comm_status(self._h, C.byref(s)))

@@ -20,64 +20,27 @@
 #include <memory>
 #include <vector>
 
+#include "comm_dev.cuh"
 #include "cuda_util.h"
+#include "nint_blayout.h"
 
 namespace mfqb {
 
-constexpr int kCommMaxWorld = 8;
-constexpr int kCommMaxBlocks = 256;
-constexpr int kCommBlockElems = 1024;   // floats per CTA
-
-struct CommPeers {
-    float* slots[kCommMaxWorld];        // per peer: [2 sets][world][max_elems]
-    unsigned* flags[kCommMaxWorld];     // per peer: [2 sets][world][kCommMaxBlocks]
-};
-
-__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
-    unsigned v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ unsigned long long global_timer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-
-__global__ void __launch_bounds__(256) allreduce_oneshot_kernel(CommPeers peers, int rank, int world, unsigned long long max_elems,
-                                                                const float* __restrict__ in, float* __restrict__ out,
-                                                                unsigned long long n, unsigned seq, unsigned long long timeout_ns,
-                                                                int* __restrict__ status) {
-    const int set = seq & 1, b = blockIdx.x, tid = threadIdx.x;
+__global__ void __launch_bounds__(256) allreduce_oneshot_kernel(const PeerReduce pr, const float* __restrict__ in, float* __restrict__ out,
+                                                                unsigned long long n) {
+    const int set = pr.seq & 1, b = blockIdx.x, tid = threadIdx.x, world = pr.world;
     const unsigned long long lo = (unsigned long long)b * kCommBlockElems;
     const unsigned long long hi = lo + kCommBlockElems < n ? lo + kCommBlockElems : n;
     // push my part of the vector into slot `rank` of every rank (my own included)
     for (int p = 0; p < world; ++p) {
-        float* dst = peers.slots[p] + ((size_t)set * world + rank) * max_elems;
+        float* dst = pr.slots[p] + ((size_t)set * world + pr.rank) * pr.max_elems;
         for (unsigned long long i = lo + tid; i < hi; i += blockDim.x) dst[i] = in[i];
     }
-    __threadfence_system();
-    __syncthreads();
-    if (tid < world) st_release_sys(peers.flags[tid] + ((size_t)set * world + rank) * kCommMaxBlocks + b, seq);
-    // wait for every rank's part of this block, with a deadline
-    if (tid < world) {
-        const unsigned* f = peers.flags[rank] + ((size_t)set * world + tid) * kCommMaxBlocks + b;
-        const unsigned long long t0 = global_timer_ns();
-        while (ld_acquire_sys(f) != seq) {
-            if (global_timer_ns() - t0 > timeout_ns) {
-                atomicExch(status, MFQB_ERR_TIMEOUT);
-                break;
-            }
-        }
-    }
-    __syncthreads();
-    const float* mine = peers.slots[rank] + (size_t)set * world * max_elems;
+    peer_signal_and_wait(pr, b, MFQB_ERR_TIMEOUT);
+    const float* mine = pr.slots[pr.rank] + (size_t)set * world * pr.max_elems;
     for (unsigned long long i = lo + tid; i < hi; i += blockDim.x) {
         float acc = 0.f;
-        for (int r = 0; r < world; ++r) acc += mine[(size_t)r * max_elems + i];
+        for (int r = 0; r < world; ++r) acc += mine[(size_t)r * pr.max_elems + i];
         out[i] = acc;
     }
 }
@@ -85,6 +48,12 @@ __global__ void __launch_bounds__(256) allreduce_oneshot_kernel(CommPeers peers,
 }  // namespace mfqb
 
 using namespace mfqb;
+
+namespace mfqb {
+const NintDevB& weight_device_layout(const mfqb_weight* w);
+int weight_device_index(const mfqb_weight* w);
+void launch_bl_gemv_reduce(const NintDevB& w, const void* x, void* y, int y_dtype, int device, const PeerReduce& pr, cudaStream_t s);
+}
 
 struct mfqb_comm {
     int rank = 0, world = 1, device = 0;
@@ -160,24 +129,59 @@ int mfqb_comm_set_timeout_ms(mfqb_comm* c, int ms) {
     });
 }
 
+// Arguments of the next collective call of this communicator (advances its sequence number).
+static PeerReduce next_call(mfqb_comm* c, const char* who) {
+    PeerReduce pr{};
+    for (int p = 0; p < c->world; ++p) {
+        if (!c->peer_base[p]) fail(MFQB_ERR_ARG, "%s: rank %d has not been attached", who, p);
+        pr.slots[p] = static_cast<float*>(c->peer_base[p]);
+        pr.flags[p] = reinterpret_cast<unsigned*>(static_cast<char*>(c->peer_base[p]) + c->slots_bytes());
+    }
+    c->seq += 1;
+    if (c->seq == 0) c->seq = 2;   // flags start at zero: never use 0 as a sequence number again
+    pr.rank = c->rank;
+    pr.world = c->world;
+    pr.seq = c->seq;
+    pr.max_elems = c->max_elems;
+    pr.timeout_ns = c->timeout_ns;
+    pr.status = c->status_dev;
+    return pr;
+}
+
 int mfqb_allreduce_f32(mfqb_comm* c, const float* in, float* out, uint64_t n, mfqb_stream_t stream) {
     return guarded([&] {
         if (!c || !in || !out) fail(MFQB_ERR_ARG, "mfqb_allreduce_f32: null argument");
         if (n == 0) return;
         if (n > c->max_elems) fail(MFQB_ERR_ARG, "mfqb_allreduce_f32: %llu elements exceed the communicator's %llu", (unsigned long long)n, (unsigned long long)c->max_elems);
-        CommPeers peers{};
-        for (int p = 0; p < c->world; ++p) {
-            if (!c->peer_base[p]) fail(MFQB_ERR_ARG, "mfqb_allreduce_f32: rank %d has not been attached", p);
-            peers.slots[p] = static_cast<float*>(c->peer_base[p]);
-            peers.flags[p] = reinterpret_cast<unsigned*>(static_cast<char*>(c->peer_base[p]) + c->slots_bytes());
-        }
         DeviceGuard guard(c->device);
-        c->seq += 1;
-        if (c->seq == 0) c->seq = 2;   // flags start at zero: never use 0 as a sequence number again
         const int grid = (int)((n + kCommBlockElems - 1) / kCommBlockElems);
-        allreduce_oneshot_kernel<<<grid, 256, 0, stream>>>(peers, c->rank, c->world, c->max_elems, in, out, n, c->seq, c->timeout_ns,
-                                                           c->status_dev);
+        if (grid > kCommMaxBlocks) fail(MFQB_ERR_ARG, "mfqb_allreduce_f32: at most %d elements per call", kCommMaxBlocks * kCommBlockElems);
+        const PeerReduce pr = next_call(c, "mfqb_allreduce_f32");
+        allreduce_oneshot_kernel<<<grid, 256, 0, stream>>>(pr, in, out, n);
         MFQB_CUDA(cudaGetLastError());
+    });
+}
+
+// Row-parallel product that ends in the reduction: y = sum over ranks of (x_shard * W_shard^T).
+// Every rank holds a K-slice of the weight (same rows) and the matching slice of x; the GEMV
+// kernel's own epilogue pushes its float32 partial rows into every peer's slots, signals, waits
+// for the peers' parts of the same rows and writes the summed row: one kernel per rank, no
+// partial vector in HBM, no second launch.
+int mfqb_mul_mat_allreduce(const mfqb_weight* w, const void* x, int m, mfqb_comm* c, void* y, int y_dtype, mfqb_stream_t stream) {
+    return guarded([&] {
+        if (!w || !x || !c || !y) fail(MFQB_ERR_ARG, "mfqb_mul_mat_allreduce: null argument");
+        if (m < 1) fail(MFQB_ERR_ARG, "mfqb_mul_mat_allreduce: m must be >= 1");
+        if (y_dtype != MFQB_F32 && y_dtype != MFQB_BF16) fail(MFQB_ERR_ARG, "mfqb_mul_mat_allreduce: bad output dtype");
+        const NintDevB& d = weight_device_layout(w);
+        if (weight_device_index(w) != c->device) fail(MFQB_ERR_ARG, "mfqb_mul_mat_allreduce: weight and communicator live on different devices");
+        if ((uint64_t)d.n > c->max_elems) fail(MFQB_ERR_ARG, "mfqb_mul_mat_allreduce: %d rows exceed the communicator's %llu elements", d.n, (unsigned long long)c->max_elems);
+        DeviceGuard guard(c->device);
+        const size_t ysz = y_dtype == MFQB_F32 ? 4 : 2;
+        for (int i = 0; i < m; ++i) {   // one activation row per call of the fused kernel
+            const PeerReduce pr = next_call(c, "mfqb_mul_mat_allreduce");
+            launch_bl_gemv_reduce(d, static_cast<const char*>(x) + (size_t)i * d.k * 2, static_cast<char*>(y) + (size_t)i * d.n * ysz, y_dtype,
+                                  c->device, pr, stream);
+        }
     });
 }
 

@@ -197,6 +197,28 @@ void launch_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtyp
     dispatch(a, p, s, "GEMV");
 }
 
+// Single-row product whose epilogue reduces over ranks (row-parallel shards): see PeerReduce.
+void launch_bl_gemv_reduce(const NintDevB& w, const void* x, void* y, int y_dtype, int device, const PeerReduce& pr, cudaStream_t s) {
+    GemvArgsB a{};
+    a.w = w;
+    a.x = static_cast<const __nv_bfloat16*>(x);
+    a.y = y;
+    a.m = 1;
+    a.ldy = w.n;
+    a.y_dtype = y_dtype;
+    a.reduce = pr;
+    GemvPlanB p;
+    const int warps = gemv1_warps(w), sms = device_sm_count(device);
+    p.threads = warps * 32;
+    // every CTA waits for its peers inside the kernel: the whole grid must be resident at once
+    p.grid = std::min(std::min(w.nrb, kCommMaxBlocks), ctas_per_sm(gemv1_smem(w, 1, warps), warps > 8 ? 2 : 3) * sms);
+    a.rb_per_cta = (w.nrb + p.grid - 1) / p.grid;
+    a.private_sums = gemv1_private_sums(a.rb_per_cta);
+    p.smem = gemv1_smem(w, a.rb_per_cta, warps);
+    if (p.smem > kGemvSmemLimit) fail(MFQB_ERR_UNSUPPORTED, "weight of %d rows is too tall for one resident grid", w.n);
+    dispatch(a, p, s, "row-parallel GEMV");
+}
+
 // Routed single-row launch over (splits, pairs) CTAs for one cohort; see GemvArgsB.
 void launch_nint_bl_gemv_routed(GemvArgsB a, int pairs, int device, cudaStream_t s) {
     const NintDevB& w = a.w;

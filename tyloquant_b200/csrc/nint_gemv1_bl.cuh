@@ -18,6 +18,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include "comm_dev.cuh"
 #include "common.h"
 #include "lane_unit.h"
 #include "nint_blayout.h"
@@ -48,6 +49,9 @@ struct GemvArgsB {
     int n_experts;
     int kt_chunks;           // batched kernel: chunks of K staged per tile (a multiple of the warps per CTA)
     int private_sums;        // single-row kernel: one copy of the partial sums per warp instead of shared-memory atomics
+    // Single-row kernel, row-parallel product: when reduce.world > 0 the CTA's summed rows are this
+    // rank's partial result; they go to the peers and the sum over ranks is written to y.
+    PeerReduce reduce;
     // Batched kernel: the activation rows already quantised by x_planes_kernel, row r at
     // xq_g + r * ngp * QS and gtab_g + r * ngp (ngp = nchunks * 8 groups, QS quads per group).
     const uint2* xq_g;
@@ -441,6 +445,32 @@ __global__ void __launch_bounds__(C::MIN_CTAS >= 3 ? 384 : 256, C::MIN_CTAS >= 3
     }
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     __syncthreads();
+    if (a.reduce.world > 0) {
+        // push this rank's partial rows into slot `rank` of every rank, then sum the ranks' parts of
+        // the same rows (the peers' CTAs with this block index own them too: same shape, same grid)
+        const PeerReduce& pr = a.reduce;
+        const int set = pr.seq & 1;
+        for (int i = tid; i < nrb * 16; i += blockDim.x) {
+            const int row = rbl0 * 16 + i;
+            if (row < row_limit) {
+                float v = ypart[i];
+                for (int cp = 1; cp < ycopies; ++cp) v += ypart[cp * ystride + i];
+                for (int p = 0; p < pr.world; ++p) pr.slots[p][((size_t)set * pr.world + pr.rank) * pr.max_elems + row] = v;
+            }
+        }
+        peer_signal_and_wait(pr, blockIdx.x, MFQB_ERR_TIMEOUT);
+        const float* mine = pr.slots[pr.rank] + (size_t)set * pr.world * pr.max_elems;
+        for (int i = tid; i < nrb * 16; i += blockDim.x) {
+            const int row = rbl0 * 16 + i;
+            if (row < row_limit) {
+                float v = 0.f;
+                for (int r = 0; r < pr.world; ++r) v += mine[(size_t)r * pr.max_elems + row];   // rank order: same bits on every rank
+                if (a.y_dtype == 0 /* MFQB_F32 */) reinterpret_cast<float*>(a.y)[y_off + row] = v;
+                else reinterpret_cast<__nv_bfloat16*>(a.y)[y_off + row] = __float2bfloat16_rn(v);
+            }
+        }
+        return;
+    }
     for (int i = tid; i < nrb * 16; i += blockDim.x) {
         const int row = rbl0 * 16 + i;   // row inside the problem (matrix, or the pair's expert)
         if (row < row_limit) {

@@ -21,6 +21,7 @@ struct NvqDevice {
     int device = 0;
 };
 void NvqDeviceDeleter::operator()(NvqDevice* p) const { delete p; }
+const NintDevB& nvq_device_layout(const NvqDevice& w) { return w.d; }
 
 void check_nvq_dtype(const std::string& dtype, const HostNvq& t) {
     const std::string d = dtype == "NIQ3" ? "NVQ3" : dtype;

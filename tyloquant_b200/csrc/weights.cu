@@ -151,6 +151,9 @@ void check_nint_supported(const HostNint& t) {
     if (!nint_bl_supported(b, t.gs)) fail(MFQB_ERR_UNSUPPORTED, "NINT%d with groupsize %d is outside the runtime catalog", b, t.gs);
 }
 
+const NintDevB& weight_device_layout(const mfqb_weight* w);
+int weight_device_index(const mfqb_weight* w);
+
 static mfqb_weight* make_nint_weight(const HostNint& t, int device) {
     check_nint_supported(t);
     NintPackedB p = pack_nint_bytes(t);
@@ -176,6 +179,9 @@ static mfqb_weight* make_nint_weight(const HostNint& t, int device) {
     i.device_bytes = w->items.bytes + w->anchors.bytes;
     return w.release();
 }
+
+const NintDevB& weight_device_layout(const mfqb_weight* w) { return w->family == MFQB_FAMILY_NINT ? w->nint : nvq_device_layout(*w->nvq); }
+int weight_device_index(const mfqb_weight* w) { return w->device; }
 
 }  // namespace mfqb
 
