@@ -295,6 +295,8 @@ def main() -> None:
         e2e_ms = float(t.item())
     e2e_value = world * step_bytes / (e2e_ms * 1e-3) / 1e9
 
+    tp = tp_rowparallel_bench(dev, rank, world, dist) if dist is not None else None
+
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -318,6 +320,8 @@ def main() -> None:
                      # summarised in profiles/nint_gemv_m1_nint3_4096x4096.md
                      "traffic": 7979264},
     })
+    if tp is not None:
+        line["tp_rowparallel"] = tp
     if args.gpus == 1:
         cb, _ = cpu_reference_arm(3, 3, budget_s=12.0)
         line["cpu_baseline"] = cb
@@ -436,6 +440,75 @@ def gemm_bench(dev: int, peak_tflops: float, reps: int = 5) -> dict:
         tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
         out[name] = {"ms": ms, "TFLOPs": tf, "frac_of_bf16_peak": tf / peak_tflops, "weight_payload_MB": w.payload_bytes / 1e6}
         w.free()
+    return out
+
+
+def tp_rowparallel_bench(dev: int, rank: int, world: int, dist, iters: int = 200) -> dict:
+    """Row-parallel linears of a Llama-3-8B-shaped layer (o_proj 4096x4096 NINT4, down 4096x14336 NINT6)
+    with the input axis sharded over the ranks on group boundaries: the product kernel that reduces
+    over NVLink in its own epilogue against the same product followed by the stand-alone all-reduce.
+    Every rank runs it; times are device times (CUDA events), max over ranks."""
+    import torch
+
+    from tyloquant_b200 import QuantWeight, comm, encode
+
+    d = f"cuda:{dev}"
+    c = comm.Communicator(rank, world, 1 << 14, dev).connect()
+    out = {}
+    for name, (n, k, bits, gs, sb) in {"o_proj_NINT4_4096x4096": (4096, 4096, 4, 24, 6), "down_NINT6_4096x14336": (4096, 14336, 6, 24, 7)}.items():
+        ng = (k + gs - 1) // gs
+        g0, g1 = comm.shard_range(ng, rank, world, 16)
+        lo, hi = g0 * gs, min(g1 * gs, k)
+        pool = []
+        for i in range(6):   # distinct shards, together larger than one L2 share of a rank's traffic
+            blob = encode.random_nint_blob(n, k, bits, gs, sb, seed=7000 + i, device=d)
+            pool.append(QuantWeight.from_blob(f"NINT{bits}", blob, device=dev, axis=1, begin=lo, end=hi))
+        x = torch.randn((1, hi - lo), device=d, generator=torch.Generator(d).manual_seed(9)).to(torch.bfloat16)
+        part = torch.empty((1, n), dtype=torch.float32, device=d)
+        y = torch.empty((1, n), dtype=torch.float32, device=d)
+        from tyloquant_b200._capi import F32, check, lib
+        sp = 0
+        res = {}
+        for mode in ("fused", "product_then_allreduce"):
+            def call(w):   # straight C-ABI calls on the capture stream `sp`
+                if mode == "fused":
+                    check(lib.mfqb_mul_mat_allreduce(w._h, x.data_ptr(), 1, c._h, y.data_ptr(), F32, sp))
+                else:
+                    check(lib.mfqb_mul_mat(w._h, x.data_ptr(), 1, part.data_ptr(), F32, sp))
+                    check(lib.mfqb_allreduce_f32(c._h, part.data_ptr(), y.data_ptr(), n, sp))
+            # the sequence numbers of the collective live on the device, so the calls replay from a graph
+            stream = torch.cuda.Stream(device=dev)
+            with torch.cuda.stream(stream):
+                sp = stream.cuda_stream
+                for w in pool:
+                    call(w)
+                stream.synchronize()
+                dist.barrier()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    for w in pool:
+                        call(w)
+                for _ in range(3):
+                    g.replay()
+                stream.synchronize()
+                dist.barrier()
+                reps = max(1, iters // len(pool))
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for _ in range(reps):
+                    g.replay()
+                e1.record(stream)
+                stream.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) * 1e3 / (reps * len(pool))], device=d)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            res[mode + "_us"] = float(t.item())
+        res["shard_payload_MB"] = pool[0].payload_bytes / 1e6
+        res["status"] = c.status()
+        out[name] = res
+        for w in pool:
+            w.free()
+    dist.barrier()
+    c.close()
     return out
 
 

@@ -230,15 +230,17 @@ int mfqb_moe_ffn(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* down, co
  * (cpp_runtime/mfq_decode.cpp:9009-9114: float32 ncclAllReduce, or copy-to-primary and add)
  * for the decode-sized vectors of row-parallel linears and expert-parallel FFN partials:
  * a one-shot all-reduce over NVLink peer memory -- every rank stores its vector into every
- * peer, raises a flag, waits (bounded) for the peers' flags and adds the slots in rank order,
- * so all ranks end with bit-identical sums.  One process per GPU; the per-rank buffers are
+ * peer (each value paired with the call's number in one 8-byte store), waits (bounded) until
+ * its own slots carry that number and adds them in rank order, so all ranks end with
+ * bit-identical sums.  The call number lives in device memory: calls may be captured into a
+ * CUDA graph and replayed.  One process per GPU; the per-rank buffers are
  * shared with CUDA IPC handles that the caller exchanges (64 bytes each).
  *
  *   create -> handle (send to every peer) -> attach(peer, its handle) for every other rank
  *   -> allreduce ... -> destroy.   All ranks must issue the same sequence of allreduce calls
  * with the same n.  A wait that passes its deadline (default 2 s) sets the status word to
  * MFQB_ERR_TIMEOUT and lets the kernel return; mfqb_comm_status reads it without
- * synchronising.  max_elems <= 524288 floats, world <= 8.
+ * synchronising.  max_elems <= 4194304 floats, world <= 8.
  *
  * mfqb_mul_mat_allreduce is the row-parallel linear itself (forward_tensor_parallel_flat +
  * reduce, cpp_runtime/mfq_decode.cpp:9137-9207): every rank holds an input-axis slice of the

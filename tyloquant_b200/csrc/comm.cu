@@ -4,17 +4,18 @@
 // ncclAllReduce per row-parallel op, or by copying shards to the primary device and adding
 // (cpp_runtime/mfq_decode.cpp:9009-9114).  At decode sizes (one to a few hundred rows of a few
 // thousand floats) that is latency, not bandwidth: here every rank pushes its partial vector
-// straight into a slot of every peer's buffer with plain stores, raises one flag per (peer, CTA),
-// waits -- bounded -- for the same flags from its peers and adds the slots in rank order, so the
-// result is bit-identical on every rank.  One kernel, no host round trip, NVSwitch carries
-// world-1 copies of the vector per rank.
+// straight into a slot of every peer's buffer, each value together with the number of the call in
+// one 8-byte store, polls -- bounded -- its own slots until every rank's pair carries that number
+// and adds them in rank order, so the result is bit-identical on every rank.  One kernel, no
+// fence, no flag, no host round trip; NVSwitch carries world-1 copies of the vector per rank.
 //
 // Buffers are cudaMalloc'd per rank and shared between the one-process-per-GPU ranks through CUDA
 // IPC handles (exchanged by the caller, e.g. over torch.distributed).  Two slot sets alternate
-// with the call sequence number; a rank cannot run two calls ahead of a peer, because call s+1
-// needs that peer's flag of call s+1, which the peer raises only after it finished call s.
-// Every wait has a deadline; when it passes, the kernel records MFQB_ERR_TIMEOUT in a
-// host-visible status word and returns, leaving the context usable.
+// with the call number; a rank cannot run two calls ahead of a peer, because call s+1 needs that
+// peer's values of call s+1, which the peer sends only after it finished call s.  The call number
+// is kept in device memory (the last CTA of a call advances it), so launches carry no per-call
+// argument and replay from CUDA graphs.  Every wait has a deadline; when it passes, the kernel
+// records MFQB_ERR_TIMEOUT in a host-visible status word and returns, leaving the context usable.
 #include <cuda_runtime.h>
 
 #include <memory>
@@ -28,21 +29,12 @@ namespace mfqb {
 
 __global__ void __launch_bounds__(256) allreduce_oneshot_kernel(const PeerReduce pr, const float* __restrict__ in, float* __restrict__ out,
                                                                 unsigned long long n) {
-    const int set = pr.seq & 1, b = blockIdx.x, tid = threadIdx.x, world = pr.world;
-    const unsigned long long lo = (unsigned long long)b * kCommBlockElems;
+    const unsigned seq = peer_call_seq(pr);
+    const unsigned long long lo = (unsigned long long)blockIdx.x * kCommBlockElems;
     const unsigned long long hi = lo + kCommBlockElems < n ? lo + kCommBlockElems : n;
-    // push my part of the vector into slot `rank` of every rank (my own included)
-    for (int p = 0; p < world; ++p) {
-        float* dst = pr.slots[p] + ((size_t)set * world + pr.rank) * pr.max_elems;
-        for (unsigned long long i = lo + tid; i < hi; i += blockDim.x) dst[i] = in[i];
-    }
-    peer_signal_and_wait(pr, b, MFQB_ERR_TIMEOUT);
-    const float* mine = pr.slots[pr.rank] + (size_t)set * world * pr.max_elems;
-    for (unsigned long long i = lo + tid; i < hi; i += blockDim.x) {
-        float acc = 0.f;
-        for (int r = 0; r < world; ++r) acc += mine[(size_t)r * pr.max_elems + i];
-        out[i] = acc;
-    }
+    for (unsigned long long i = lo + threadIdx.x; i < hi; i += blockDim.x) peer_push(pr, seq, i, in[i]);
+    for (unsigned long long i = lo + threadIdx.x; i < hi; i += blockDim.x) out[i] = peer_sum(pr, seq, i, MFQB_ERR_TIMEOUT);
+    peer_call_done(pr, seq);
 }
 
 }  // namespace mfqb
@@ -58,15 +50,14 @@ void launch_bl_gemv_reduce(const NintDevB& w, const void* x, void* y, int y_dtyp
 struct mfqb_comm {
     int rank = 0, world = 1, device = 0;
     uint64_t max_elems = 0;
-    unsigned seq = 0;
+    DevBuf counters;                    // [0] sequence number of the last finished call, [1] CTAs done in the current one
     uint64_t timeout_ns = 2000000000ull;
-    DevBuf local;                       // slots then flags of this rank
+    DevBuf local;                       // the slots of this rank
     void* peer_base[kCommMaxWorld] = {nullptr};
     bool opened[kCommMaxWorld] = {false};
     int* status_host = nullptr;         // pinned, mapped
     int* status_dev = nullptr;
-    size_t slots_bytes() const { return (size_t)2 * world * max_elems * sizeof(float); }
-    size_t flags_bytes() const { return (size_t)2 * world * kCommMaxBlocks * sizeof(unsigned); }
+    size_t slots_bytes() const { return (size_t)2 * world * max_elems * sizeof(uint2); }
 };
 
 extern "C" {
@@ -77,16 +68,17 @@ int mfqb_comm_create(int rank, int world, uint64_t max_elems, int device, mfqb_c
         if (!out) fail(MFQB_ERR_ARG, "mfqb_comm_create: null output");
         if (world < 1 || world > kCommMaxWorld || rank < 0 || rank >= world)
             fail(MFQB_ERR_ARG, "mfqb_comm_create: rank %d / world %d out of range (world <= %d)", rank, world, kCommMaxWorld);
-        if (max_elems == 0 || max_elems > (uint64_t)kCommMaxBlocks * kCommBlockElems)
-            fail(MFQB_ERR_ARG, "mfqb_comm_create: max_elems must be in [1, %d]", kCommMaxBlocks * kCommBlockElems);
+        if (max_elems == 0 || max_elems > (1u << 22)) fail(MFQB_ERR_ARG, "mfqb_comm_create: max_elems must be in [1, %d]", 1 << 22);
         auto c = std::make_unique<mfqb_comm>();
         c->rank = rank;
         c->world = world;
         c->device = device;
         c->max_elems = max_elems;
         DeviceGuard guard(device);
-        c->local.alloc(c->slots_bytes() + c->flags_bytes());
+        c->local.alloc(c->slots_bytes());
         MFQB_CUDA(cudaMemset(c->local.p, 0, c->local.bytes));
+        c->counters.alloc(2 * sizeof(unsigned));
+        MFQB_CUDA(cudaMemset(c->counters.p, 0, c->counters.bytes));
         MFQB_CUDA(cudaHostAlloc((void**)&c->status_host, sizeof(int), cudaHostAllocMapped));
         *c->status_host = 0;
         MFQB_CUDA(cudaHostGetDevicePointer((void**)&c->status_dev, c->status_host, 0));
@@ -129,19 +121,17 @@ int mfqb_comm_set_timeout_ms(mfqb_comm* c, int ms) {
     });
 }
 
-// Arguments of the next collective call of this communicator (advances its sequence number).
+// Arguments of a collective call of this communicator (the sequence number advances on the device).
 static PeerReduce next_call(mfqb_comm* c, const char* who) {
     PeerReduce pr{};
     for (int p = 0; p < c->world; ++p) {
         if (!c->peer_base[p]) fail(MFQB_ERR_ARG, "%s: rank %d has not been attached", who, p);
-        pr.slots[p] = static_cast<float*>(c->peer_base[p]);
-        pr.flags[p] = reinterpret_cast<unsigned*>(static_cast<char*>(c->peer_base[p]) + c->slots_bytes());
+        pr.slots[p] = static_cast<uint2*>(c->peer_base[p]);
     }
-    c->seq += 1;
-    if (c->seq == 0) c->seq = 2;   // flags start at zero: never use 0 as a sequence number again
     pr.rank = c->rank;
     pr.world = c->world;
-    pr.seq = c->seq;
+    pr.seq_dev = static_cast<unsigned*>(c->counters.p);
+    pr.done_ctr = pr.seq_dev + 1;
     pr.max_elems = c->max_elems;
     pr.timeout_ns = c->timeout_ns;
     pr.status = c->status_dev;
@@ -155,7 +145,6 @@ int mfqb_allreduce_f32(mfqb_comm* c, const float* in, float* out, uint64_t n, mf
         if (n > c->max_elems) fail(MFQB_ERR_ARG, "mfqb_allreduce_f32: %llu elements exceed the communicator's %llu", (unsigned long long)n, (unsigned long long)c->max_elems);
         DeviceGuard guard(c->device);
         const int grid = (int)((n + kCommBlockElems - 1) / kCommBlockElems);
-        if (grid > kCommMaxBlocks) fail(MFQB_ERR_ARG, "mfqb_allreduce_f32: at most %d elements per call", kCommMaxBlocks * kCommBlockElems);
         const PeerReduce pr = next_call(c, "mfqb_allreduce_f32");
         allreduce_oneshot_kernel<<<grid, 256, 0, stream>>>(pr, in, out, n);
         MFQB_CUDA(cudaGetLastError());

@@ -211,7 +211,7 @@ void launch_bl_gemv_reduce(const NintDevB& w, const void* x, void* y, int y_dtyp
     const int warps = gemv1_warps(w), sms = device_sm_count(device);
     p.threads = warps * 32;
     // every CTA waits for its peers inside the kernel: the whole grid must be resident at once
-    p.grid = std::min(std::min(w.nrb, kCommMaxBlocks), ctas_per_sm(gemv1_smem(w, 1, warps), warps > 8 ? 2 : 3) * sms);
+    p.grid = std::min(w.nrb, ctas_per_sm(gemv1_smem(w, 1, warps), warps > 8 ? 2 : 3) * sms);
     a.rb_per_cta = (w.nrb + p.grid - 1) / p.grid;
     a.private_sums = gemv1_private_sums(a.rb_per_cta);
     p.smem = gemv1_smem(w, a.rb_per_cta, warps);

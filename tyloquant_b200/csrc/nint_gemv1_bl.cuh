@@ -446,29 +446,28 @@ __global__ void __launch_bounds__(C::MIN_CTAS >= 3 ? 384 : 256, C::MIN_CTAS >= 3
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     __syncthreads();
     if (a.reduce.world > 0) {
-        // push this rank's partial rows into slot `rank` of every rank, then sum the ranks' parts of
-        // the same rows (the peers' CTAs with this block index own them too: same shape, same grid)
+        // every thread owns one row of the CTA: it pushes this rank's partial value into slot `rank` of
+        // every rank and sums the ranks' values of that row (the peers' CTAs with this block index
+        // own the same rows: same shape, same grid)
         const PeerReduce& pr = a.reduce;
-        const int set = pr.seq & 1;
+        const unsigned seq = peer_call_seq(pr);   // after griddepcontrol.wait: the previous call has published its number
         for (int i = tid; i < nrb * 16; i += blockDim.x) {
             const int row = rbl0 * 16 + i;
             if (row < row_limit) {
                 float v = ypart[i];
                 for (int cp = 1; cp < ycopies; ++cp) v += ypart[cp * ystride + i];
-                for (int p = 0; p < pr.world; ++p) pr.slots[p][((size_t)set * pr.world + pr.rank) * pr.max_elems + row] = v;
+                peer_push(pr, seq, row, v);
             }
         }
-        peer_signal_and_wait(pr, blockIdx.x, MFQB_ERR_TIMEOUT);
-        const float* mine = pr.slots[pr.rank] + (size_t)set * pr.world * pr.max_elems;
         for (int i = tid; i < nrb * 16; i += blockDim.x) {
             const int row = rbl0 * 16 + i;
             if (row < row_limit) {
-                float v = 0.f;
-                for (int r = 0; r < pr.world; ++r) v += mine[(size_t)r * pr.max_elems + row];   // rank order: same bits on every rank
+                const float v = peer_sum(pr, seq, row, MFQB_ERR_TIMEOUT);
                 if (a.y_dtype == 0 /* MFQB_F32 */) reinterpret_cast<float*>(a.y)[y_off + row] = v;
                 else reinterpret_cast<__nv_bfloat16*>(a.y)[y_off + row] = __float2bfloat16_rn(v);
             }
         }
+        peer_call_done(pr, seq);
         return;
     }
     for (int i = tid; i < nrb * 16; i += blockDim.x) {
