@@ -296,6 +296,7 @@ def main() -> None:
     e2e_value = world * step_bytes / (e2e_ms * 1e-3) / 1e9
 
     tp = tp_rowparallel_bench(dev, rank, world, dist) if dist is not None else None
+    ep = ep_moe_bench(dev, rank, world, dist) if dist is not None else None
 
     if rank != 0:
         if dist is not None:
@@ -322,6 +323,8 @@ def main() -> None:
     })
     if tp is not None:
         line["tp_rowparallel"] = tp
+    if ep is not None:
+        line["ep_moe_cfg4"] = ep
     if args.gpus == 1:
         cb, _ = cpu_reference_arm(3, 3, budget_s=12.0)
         line["cpu_baseline"] = cb
@@ -509,6 +512,68 @@ def tp_rowparallel_bench(dev: int, rank: int, world: int, dist, iters: int = 200
             w.free()
     dist.barrier()
     c.close()
+    return out
+
+
+def ep_moe_bench(dev: int, rank: int, world: int, dist, token_counts=(1, 32, 256), reps: int = 5) -> dict:
+    """BASELINE config 4 expert-parallel: every rank holds a contiguous range of the 128 experts
+    (reference slice planner), router and route plan are replicated, the partial [T, H] outputs are
+    summed by the one-shot NVLink all-reduce.  A step = router + local expert FFN + all-reduce;
+    16 different inputs per CUDA graph.  Device times, max over ranks."""
+    import torch
+
+    from tyloquant_b200 import comm, encode, moe
+    from tyloquant_b200._capi import check, lib
+
+    d = f"cuda:{dev}"
+    h, e_count, f, k = 2048, 128, 768, 8
+    bits = np.random.default_rng(4003).choice([2, 3, 4, 6], e_count)
+    gen = torch.Generator(d).manual_seed(4001)   # same seed on every rank: same weights and inputs
+    wgu = (torch.randn((e_count, 2 * f, h), device=d, generator=gen) * 0.02).to(torch.bfloat16).float()
+    wdn = (torch.randn((e_count, h, f), device=d, generator=gen) * 0.02).to(torch.bfloat16).float()
+    b, e = comm.shard_range(e_count, rank, world, 128)
+    gu = moe.MoeWeight(encode.quantize_expertwise(wgu, bits, device=d), dev, b, e)
+    dn = moe.MoeWeight(encode.quantize_expertwise(wdn, bits, device=d), dev, b, e)
+    del wgu, wdn
+    c = comm.Communicator(rank, world, max(token_counts) * h, dev).connect()
+    out = {"experts_per_rank": e - b}
+    nsets = 16
+    for t in token_counts:
+        xs = [torch.randn((t, h), device=d, generator=gen).to(torch.bfloat16) for _ in range(nsets)]
+        zs = [torch.randn((t, e_count), device=d, generator=gen) for _ in range(nsets)]
+        ysum = torch.empty((t, h), dtype=torch.float32, device=d)
+        stream = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(stream):
+            def step():
+                for x, z in zip(xs, zs):
+                    ids, wts = moe.moe_topk(z, k)
+                    part = moe.moe_ffn(gu, dn, x, ids, wts, out_dtype=torch.float32)
+                    check(lib.mfqb_allreduce_f32(c._h, part.data_ptr(), ysum.data_ptr(), t * h, stream.cuda_stream))
+            step()
+            stream.synchronize()
+            dist.barrier()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                step()
+            for _ in range(2):
+                g.replay()
+            stream.synchronize()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(reps):
+                g.replay()
+            e1.record(stream)
+            stream.synchronize()
+        tt = torch.tensor([e0.elapsed_time(e1) * 1e3 / (reps * nsets)], device=d)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        us = float(tt.item())
+        out[f"T{t}"] = {"us_per_layer_step": us, "tokens_per_s": t / us * 1e6}
+    out["status"] = c.status()
+    dist.barrier()
+    c.close()
+    gu.free()
+    dn.free()
     return out
 
 
