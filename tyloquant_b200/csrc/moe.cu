@@ -37,6 +37,7 @@ void launch_nint_bl_dequant(const NintDevB& w, void* out, int out_dtype, cudaStr
 void launch_nint_bl_gemv_routed(GemvArgsB a, int pairs, int device, cudaStream_t s);
 void launch_nint_bl_gemv_tiles(GemvArgsB a, int tile_m, int max_tiles, int device, cudaStream_t s);
 void check_nint_supported(const HostNint& t);
+bool launch_moe_hetero_gemv1(GemvArgsB base, const NintDevB* pools, const int* held, int npools, int pairs, int device, cudaStream_t s);
 size_t nint_bl_planes_bytes(const NintDevB& w, int rows);
 void launch_x_planes(const NintDevB& w, const void* x, int rows, void* planes, const uint2** xq_g, const float2** gtab_g, cudaStream_t s);
 
@@ -241,6 +242,26 @@ static void mul_mat_id_impl(const mfqb_moe_weight* w, const void* x, int x_per_p
     // summed afterwards), so clear the output when the handle is partial.
     if (w->info.expert_end - w->info.expert_begin != w->info.n_experts)
         MFQB_CUDA(cudaMemsetAsync(out, 0, (size_t)pairs * ope * (out_dtype == MFQB_F32 ? 4 : 2), stream));
+    if (!plan && pairs <= 32768) {   // decode sizes: all cohorts in one launch when their codecs allow
+        GemvArgsB a{};
+        a.x = static_cast<const __nv_bfloat16*>(x);
+        a.y = out;
+        a.ldy = ope;
+        a.y_dtype = out_dtype;
+        a.route_ids = ids;
+        a.expert_pool = static_cast<const int*>(w->d_expert_pool.p);
+        a.expert_local = static_cast<const int*>(w->d_expert_local.p);
+        a.rb_per_expert = w->padded / 16;
+        a.routes = routes;
+        a.x_per_pair = x_per_pair ? 1 : 0;
+        NintDevB devs[16];
+        int held[16];
+        for (size_t pi = 0; pi < w->pools.size(); ++pi) {
+            devs[pi] = w->pools[pi]->d;
+            held[pi] = w->pools[pi]->held;
+        }
+        if (launch_moe_hetero_gemv1(a, devs, held, (int)w->pools.size(), pairs, w->info.device, stream)) return;
+    }
     for (size_t pi = 0; pi < w->pools.size(); ++pi) {
         const MoePool& pool = *w->pools[pi];
         if (!pool.held) continue;

@@ -300,12 +300,10 @@ __device__ __forceinline__ void x_chunk_quant(const XChunkRaw<T>& raw, int c, ui
 // predecessor in the stream, since weights are constants.  The activation row is read straight
 // from global memory, one chunk ahead, and quantised in registers by the warp that needs it.
 template <class C>
-__global__ void __launch_bounds__(C::MIN_CTAS >= 3 ? 384 : 256, C::MIN_CTAS >= 3 ? 2 : C::MIN_CTAS) gemv1_bl_kernel(const GemvArgsB a) {
+__device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB& w, unsigned char* smem) {
     constexpr int G = kChunkGroupsB, T = C::T, WC = C::WC, SW = C::SW, REC = (WC + SW) * 32;
     constexpr int S = gemv1_bl_stages(REC);
-    const NintDevB& w = a.w;
 
-    extern __shared__ __align__(16) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const int q = lane >> 2, c = lane & 3;
     typename C::Ctx ctx;
@@ -479,6 +477,12 @@ __global__ void __launch_bounds__(C::MIN_CTAS >= 3 ? 384 : 256, C::MIN_CTAS >= 3
             else reinterpret_cast<__nv_bfloat16*>(a.y)[y_off + row] = __float2bfloat16_rn(v);
         }
     }
+}
+
+template <class C>
+__global__ void __launch_bounds__(C::MIN_CTAS >= 3 ? 384 : 256, C::MIN_CTAS >= 3 ? 2 : C::MIN_CTAS) gemv1_bl_kernel(const GemvArgsB a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    gemv1_bl_body<C>(a, a.w, smem);
 }
 
 }  // namespace mfqb
