@@ -263,20 +263,56 @@ int mfqb_mul_mat(const mfqb_weight* w, const void* x, int m, void* y, int y_dtyp
     });
 }
 
+// Copies `words` 32-bit words (activations in mapped pinned host memory -> device staging).
+__global__ void host_to_device_words_kernel(const uint32_t* __restrict__ src, uint32_t* __restrict__ dst, size_t words) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < words; i += (size_t)gridDim.x * blockDim.x) dst[i] = src[i];
+}
+
+// Device staging of the host-buffer entry point: per device one stream and two buffers that grow on
+// demand and are then reused, so a call costs two copies, the kernel and one synchronisation.
+namespace {
+struct HostCallState {
+    std::mutex mu;
+    cudaStream_t stream[64] = {nullptr};
+    DevBuf x[64], y[64];
+};
+HostCallState g_host_call;
+}  // namespace
+
 int mfqb_mul_mat_host(const mfqb_weight* w, const void* x_host, int m, void* y_host, int y_dtype) {
     return guarded([&] {
         if (!w || !x_host || !y_host) fail(MFQB_ERR_ARG, "mfqb_mul_mat_host: null argument");
         if (m < 1) fail(MFQB_ERR_ARG, "mfqb_mul_mat_host: m must be >= 1");
+        if (w->device < 0 || w->device >= 64) fail(MFQB_ERR_ARG, "device index %d out of range", w->device);
         DeviceGuard guard(w->device);
         const size_t xb = (size_t)m * w->info.k * 2, yb = (size_t)m * w->info.n * (y_dtype == MFQB_F32 ? 4 : 2);
-        DevBuf dx, dy;
-        dx.alloc(xb);
-        dy.alloc(yb);
-        cudaStream_t s = nullptr;
-        MFQB_CUDA(cudaMemcpyAsync(dx.p, x_host, xb, cudaMemcpyHostToDevice, s));
-        const int rc = mfqb_mul_mat(w, dx.p, m, dy.p, y_dtype, s);
+        std::lock_guard<std::mutex> lock(g_host_call.mu);
+        cudaStream_t& s = g_host_call.stream[w->device];
+        if (!s) MFQB_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+        DevBuf& dx = g_host_call.x[w->device];
+        DevBuf& dy = g_host_call.y[w->device];
+        if (dx.bytes < xb) dx.alloc(xb + xb / 2);
+        if (dy.bytes < yb) dy.alloc(yb + yb / 2);
+        // Pinned, mapped host buffers (cudaHostAlloc / cudaHostRegister, which is what a caller that
+        // cares about latency passes): a small kernel pulls x over PCIe into the staging buffer and the
+        // product kernel writes y straight into host memory -- no copy-engine round trips.  Pageable
+        // buffers take the two cudaMemcpyAsync.
+        void *x_map = nullptr, *y_map = nullptr;
+        const bool mapped = (xb % 4 == 0) && (reinterpret_cast<uintptr_t>(x_host) % 4 == 0) &&
+                            cudaHostGetDevicePointer(&x_map, const_cast<void*>(x_host), 0) == cudaSuccess &&
+                            cudaHostGetDevicePointer(&y_map, y_host, 0) == cudaSuccess;
+        if (!mapped) (void)cudaGetLastError();   // not an error: the buffers are simply pageable
+        if (mapped) {
+            const size_t words = xb / 4;
+            host_to_device_words_kernel<<<(unsigned)std::min<size_t>((words + 255) / 256, 64), 256, 0, s>>>(
+                static_cast<const uint32_t*>(x_map), static_cast<uint32_t*>(dx.p), words);
+            MFQB_CUDA(cudaGetLastError());
+        } else {
+            MFQB_CUDA(cudaMemcpyAsync(dx.p, x_host, xb, cudaMemcpyHostToDevice, s));
+        }
+        const int rc = mfqb_mul_mat(w, dx.p, m, mapped ? y_map : dy.p, y_dtype, s);
         if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
-        MFQB_CUDA(cudaMemcpyAsync(y_host, dy.p, yb, cudaMemcpyDeviceToHost, s));
+        if (!mapped) MFQB_CUDA(cudaMemcpyAsync(y_host, dy.p, yb, cudaMemcpyDeviceToHost, s));
         MFQB_CUDA(cudaStreamSynchronize(s));
     });
 }
