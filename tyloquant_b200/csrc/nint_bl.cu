@@ -105,10 +105,10 @@ static size_t gemv1_smem(const NintDevB& w, int rb_per_cta, int warps) {
     return codec_ctx_bytes(w) + (size_t)(copies + 1) * rb_per_cta * 16 * 4 + (size_t)warps * gemv1_bl_stages(w.rec_words) * w.rec_words * 4;
 }
 // Warps per CTA of the single-row kernel: each warp owns whole chunks of K, so 8 to 12 warps are
-// chosen to make the largest number of chunks per warp as small as possible (lattice and wide
-// records stay at 8: their kernels are built for 256 threads).
+// chosen to make the largest number of chunks per warp as small as possible (wide records and the
+// larger lattice codebooks stay at 8: their kernels are built for 256 threads).
 static int gemv1_warps(const NintDevB& w) {
-    if (w.table || w.wc > 24) return 8;
+    if ((w.table && w.index_bits != 8) || w.wc > 24) return 8;
     int best = 8;
     for (int n = 9; n <= 12; ++n)
         if ((w.nchunks + n - 1) / n < (w.nchunks + best - 1) / best) best = n;
