@@ -318,7 +318,7 @@ def main() -> None:
                      "us_per_launch": launch_us, "algorithmic_bytes_per_launch": algorithmic_bytes(payload, 1, N_ROWS, N_COLS),
                      "device_bytes_per_launch": weights[0].device_bytes,
                      # dram__bytes_read.sum + dram__bytes_write.sum of one launch, ncu --set full capture
-                     # summarised in profiles/nint_gemv_m1_nint3_4096x4096.md
+                     # summarised in profiles/gemv1_bl_nint3_4096x4096.md
                      "traffic": 7979264},
     })
     if tp is not None:

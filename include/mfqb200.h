@@ -106,9 +106,14 @@ int mfqb_weight_free(mfqb_weight* w);
  * (mfq/kernels/cuda/nint_matmul.cu:136-161,442-481, nvq_matmul.cu:421-471). */
 int mfqb_dequant(const mfqb_weight* w, void* out, int out_dtype, mfqb_stream_t stream);
 
-/* y[m, n] = x[m, k] . W^T with float32 accumulation.  x is row-major bf16 with exactly
- * k columns; y is row-major [m, n] in y_dtype.  Any m >= 1 is accepted: m <= 16 runs the
- * weight-streaming kernel, larger m the tensor-core tile kernel.
+/* y[m, n] = x[m, k] . W^T.  x is row-major bf16 with exactly k columns; y is row-major [m, n] in
+ * y_dtype.  Any m >= 1 is accepted.  m <= 16 (and every m for lattice weights) runs the
+ * weight-streaming kernels: the weights stay integer codes on the int8 tensor cores, x is quantised
+ * inside the kernel, group by group, to 16-bit integers with a power-of-two scale (exact for a bf16
+ * value unless it lies more than 2^7 below its group's largest magnitude; the product is within
+ * 1e-5 relative L2 of the float32 reference), sums are exact in int32 and the scales are applied
+ * in float32.  Larger m for NINT runs the tcgen05 tile kernel (f16 operands, float32 accumulation).
+ * An infinity or NaN in x makes the outputs NaN.
  * Stands in for nint_matmul / nvq_matmul / QuantLinear::forward
  * (cpp_runtime/mfq_decode.cpp:8130-8315, 7884-7932, 9209). */
 int mfqb_mul_mat(const mfqb_weight* w, const void* x_bf16, int m, void* y, int y_dtype,
