@@ -160,6 +160,9 @@ def main() -> None:
                     "(small, for profilers) and print its line")
     ap.add_argument("--reps", type=int, default=3, help="launch rounds for --only")
     ap.add_argument("--tokens", type=int, nargs="*", default=None, help="token counts for --only moe")
+    ap.add_argument("--parallel-extras", action="store_true",
+                    help="at --gpus > 1 also time the fused row-parallel linear and the expert-parallel MoE layer "
+                         "(keys tp_rowparallel, ep_moe_cfg4)")
     args = ap.parse_args()
     steps, warmup = max(args.steps, 1), max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -295,8 +298,8 @@ def main() -> None:
         e2e_ms = float(t.item())
     e2e_value = world * step_bytes / (e2e_ms * 1e-3) / 1e9
 
-    tp = tp_rowparallel_bench(dev, rank, world, dist) if dist is not None else None
-    ep = ep_moe_bench(dev, rank, world, dist) if dist is not None else None
+    tp = tp_rowparallel_bench(dev, rank, world, dist) if dist is not None and args.parallel_extras else None
+    ep = ep_moe_bench(dev, rank, world, dist) if dist is not None and args.parallel_extras else None
 
     if rank != 0:
         if dist is not None:
