@@ -37,6 +37,7 @@ void launch_nint_bl_dequant(const NintDevB& w, void* out, int out_dtype, cudaStr
 void launch_nint_bl_gemv_routed(GemvArgsB a, int pairs, int device, cudaStream_t s);
 void launch_nint_bl_gemv_tiles(GemvArgsB a, int tile_m, int max_tiles, int device, cudaStream_t s);
 void check_nint_supported(const HostNint& t);
+int nint_bl_max_passes(const NintDevB& w);
 bool launch_moe_hetero_gemv1(GemvArgsB base, const NintDevB* pools, const int* held, int npools, int pairs, int device, cudaStream_t s);
 size_t nint_bl_planes_bytes(const NintDevB& w, int rows);
 void launch_x_planes(const NintDevB& w, const void* x, int rows, void* planes, const uint2** xq_g, const float2** gtab_g, cudaStream_t s);
@@ -206,13 +207,15 @@ int mfqb_moe_dequant_expert(const mfqb_moe_weight* w, int expert, void* out, int
     });
 }
 
-// Tiles of 8 pairs per expert pay off once an expert sees several pairs on average.
 // Pairs per route-plan tile (2, 4 or 8, sized to the average number of pairs an expert sees), or
 // 0: fewer pairs than experts, every pair runs as a single-row problem of its own.
 static int moe_tile_m(const mfqb_moe_weight* w, int pairs) {
     const int e = w->info.n_experts;
     if (pairs < e) return 0;
-    return pairs <= 5 * e / 2 ? 2 : (pairs <= 5 * e ? 4 : 8);
+    int cap = 8;   // cohorts with wide records fit fewer batch rows per CTA
+    for (const auto& pool : w->pools)
+        if (pool->held) cap = std::min(cap, 2 * nint_bl_max_passes(pool->d));
+    return std::min(cap, pairs <= 5 * e / 2 ? 2 : (pairs <= 5 * e ? 4 : 8));
 }
 
 // Bytes of quantised activation planes the tile path needs for `rows` input rows: one set per
@@ -346,7 +349,7 @@ int mfqb_moe_ffn(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* down, co
         DeviceGuard guard(gate_up->info.device);
         const size_t pairs = (size_t)tokens * routes;
         const size_t b_gu = pairs * f2 * 4, b_hid = (pairs * f * 2 + 255) / 256 * 256, b_dn = pairs * h * 4;
-        const int tile_m = moe_tile_m(gate_up, (int)pairs);
+        const int tile_m = std::min(moe_tile_m(gate_up, (int)pairs), moe_tile_m(down, (int)pairs));
         const bool tiles = tile_m != 0;
         const size_t b_plan = tiles ? PlanBufs::bytes(gate_up->info.n_experts, pairs) : 0;
         const size_t b_pgu = tiles ? moe_planes_bytes(gate_up, tokens) : 0, b_pdn = tiles ? moe_planes_bytes(down, (int)pairs) : 0;
@@ -407,7 +410,7 @@ int mfqb_moe_ffn_static(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* d
         if (tokens <= 0 || routes < 1) return;
         const size_t pairs = (size_t)tokens * routes;
         const size_t b_gu = pairs * f2 * 4, b_hid = (pairs * f * 2 + 255) / 256 * 256, b_dn = pairs * h * 4;
-        const int tile_m = moe_tile_m(gate_up, (int)pairs);
+        const int tile_m = std::min(moe_tile_m(gate_up, (int)pairs), moe_tile_m(down, (int)pairs));
         const bool tiles = tile_m != 0;
         const size_t b_plan = tiles ? PlanBufs::bytes(gate_up->info.n_experts, pairs) + moe_planes_bytes(gate_up, tokens) +
                                           moe_planes_bytes(down, (int)pairs)

@@ -114,11 +114,12 @@ static int gemv1_warps(const NintDevB& w) {
         if ((w.nchunks + n - 1) / n < (w.nchunks + best - 1) / best) best = n;
     return best;
 }
-static size_t gemvn_smem(const NintDevB& w, int rb_per_cta, int passes, int kt) {
-    const int mb = 2 * passes, tg = kt * kChunkGroupsB;
-    return codec_ctx_bytes(w) + (size_t)(mb + 1) * rb_per_cta * 16 * 4 + (size_t)mb * tg * 8 + (size_t)mb * tg * gemv1_bl_qstride(w.t8) * 8 +
-           (size_t)8 * gemv1_bl_stages(w.rec_words) * w.rec_words * 4;
+static size_t gemvn_smem(const NintDevB& w, int rb_per_cta, int passes) {
+    const int mb = 2 * passes;
+    return codec_ctx_bytes(w) + (size_t)(mb + 1) * rb_per_cta * 16 * 4 + (size_t)8 * 2 * mb * gemvn_bl_row_bytes(w.t8) +
+           (size_t)8 * gemvn_bl_stages(w.rec_words, passes) * w.rec_words * 4;
 }
+
 // Bytes of the quantised planes of `rows` activation rows for this weight.
 size_t nint_bl_planes_bytes(const NintDevB& w, int rows) {
     return (size_t)rows * w.nchunks * kChunkGroupsB * (gemv1_bl_qstride(w.t8) + 1) * 8;
@@ -158,13 +159,11 @@ static void* planes_scratch(int device, size_t bytes) {
 
 static int passes_for(int m) { return m <= 2 ? 1 : (m <= 4 ? 2 : 4); }
 
-// K tile of the batched kernel: whole K when its planes fit in about 48 KB, else a multiple of the
-// eight warps that does.
-static int gemvn_kt(const NintDevB& w, int passes) {
-    const size_t per_chunk = (size_t)2 * passes * kChunkGroupsB * 8 * (1 + gemv1_bl_qstride(w.t8));
-    int kt = (w.nchunks + 7) / 8 * 8;
-    while (kt > 8 && kt * per_chunk > 48 * 1024) kt -= 8;
-    return kt;
+// Largest number of two-row passes (4, 2 or 1) whose plane buffers and record rings fit one CTA.
+int nint_bl_max_passes(const NintDevB& w) {
+    for (int p = 4; p > 1; p /= 2)
+        if (gemvn_smem(w, 2, p) <= kGemvSmemLimit) return p;
+    return 1;
 }
 
 // y[m, n] = x[m, k] * W^T for m <= 8 (the caller loops larger batches)
@@ -187,12 +186,22 @@ void launch_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtyp
         a.private_sums = gemv1_private_sums(a.rb_per_cta);
         p.smem = gemv1_smem(w, a.rb_per_cta, warps);
     } else {
+        const int max_rows = 2 * nint_bl_max_passes(w);
+        if (m > max_rows) {   // wide records: the batch goes through in several launches
+            const size_t ysz = y_dtype == MFQB_F32 ? 4 : 2;
+            for (int m0 = 0; m0 < m; m0 += max_rows)
+                launch_bl_gemv(w, static_cast<const char*>(x) + (size_t)m0 * w.k * 2, std::min(max_rows, m - m0),
+                               static_cast<char*>(y) + (size_t)m0 * ldy * ysz, y_dtype, ldy, device, s);
+            return;
+        }
         launch_x_planes(w, x, m, planes_scratch(device, nint_bl_planes_bytes(w, m)), &a.xq_g, &a.gtab_g, s);
         p.passes = passes_for(m);
-        a.kt_chunks = gemvn_kt(w, p.passes);
-        p.grid = std::min(w.nrb, ctas_per_sm(gemvn_smem(w, 1, p.passes, a.kt_chunks), p.passes == 4 ? 2 : 3) * sms);
+        // at least two row-blocks per CTA where the matrix allows: a chunk's planes then serve several items
+        const int cap = ctas_per_sm(gemvn_smem(w, 2, p.passes), p.passes == 4 ? 2 : 3) * sms;
+        p.grid = std::max(1, std::min(w.nrb >= 2 * sms ? w.nrb / 2 : w.nrb, cap));
         a.rb_per_cta = (w.nrb + p.grid - 1) / p.grid;
-        p.smem = gemvn_smem(w, a.rb_per_cta, p.passes, a.kt_chunks);
+        p.smem = gemvn_smem(w, a.rb_per_cta, p.passes);
+        if (p.smem > kGemvSmemLimit) fail(MFQB_ERR_UNSUPPORTED, "batched product: %d row-blocks per CTA do not fit shared memory", a.rb_per_cta);
     }
     dispatch(a, p, s, "GEMV");
 }
@@ -240,13 +249,12 @@ void launch_nint_bl_gemv_tiles(GemvArgsB a, int tile_m, int max_tiles, int devic
     a.m = tile_m;
     GemvPlanB p;
     p.passes = tile_m / 2;
-    a.kt_chunks = gemvn_kt(w, p.passes);
     // max_tiles is an upper bound and a launch covers one cohort only, so most of its tiles return at
     // once: split an expert's rows finely (about eight row-blocks per CTA) to keep the SMs busy
     const int want = (2 * device_sm_count(device) + max_tiles - 1) / std::max(max_tiles, 1);
     const int splits = std::max(1, std::min(a.rb_per_expert, std::max(a.rb_per_expert / 8, want)));
     a.rb_per_cta = (a.rb_per_expert + splits - 1) / splits;
-    p.smem = gemvn_smem(w, a.rb_per_cta, p.passes, a.kt_chunks);
+    p.smem = gemvn_smem(w, a.rb_per_cta, p.passes);
     p.grid = splits;
     p.grid_y = max_tiles;
     dispatch(a, p, s, "routed tile GEMV");

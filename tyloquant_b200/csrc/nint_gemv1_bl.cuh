@@ -47,7 +47,6 @@ struct GemvArgsB {
     const int* tile_bounds;
     const int* pair_order;
     int n_experts;
-    int kt_chunks;           // batched kernel: chunks of K staged per tile (a multiple of the warps per CTA)
     int private_sums;        // single-row kernel: one copy of the partial sums per warp instead of shared-memory atomics
     // Single-row kernel, row-parallel product: when reduce.world > 0 the CTA's summed rows are this
     // rank's partial result; they go to the peers and the sum over ranks is written to y.
