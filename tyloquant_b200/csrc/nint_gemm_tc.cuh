@@ -234,9 +234,10 @@ inline GemmPlan plan_nint_gemm(const NintDevB& w, int m) {
     GemmPlan p{};
     if (w.gs % 8 != 0 || w.t8 * 8 != w.gs) return p;
     const int atoms = kChunkGroupsB * w.gs / 64;
-    // wide token tiles amortise the dequantisation; wide groups (4 or more atoms per chunk) take the
-    // narrower tile so that the ring holds more than one chunk
-    int bn = (w.gs >= 32) ? 128 : 256;
+    // wide token tiles amortise the dequantisation: 256 tokens when the ring then still holds one whole
+    // chunk (atoms stages), else 128
+    int bn = 256;
+    if ((int)((220 * 1024) / (128 * 128 + bn * 128)) < atoms) bn = 128;
     while (bn > 64 && bn / 2 >= m) bn /= 2;
     p.bn = bn;
     const int stage_bytes = 128 * 128 + bn * 128;

@@ -1,7 +1,8 @@
-// Single-row (m = 1) GEMV for NINT weights in the byte-lane layout: the decode hot path.
+// Single-row (m = 1) GEMV for weights in the byte-lane layout (NINT codes, or lattice vectors
+// through a codec): the decode hot path.
 //
-// The weights never leave the integer domain.  The activation row is quantised once per CTA,
-// group by group, to 16-bit integers  x_k ~ sx_g * xi_k  (sx_g a power of two chosen from the
+// The weights never leave the integer domain.  The activation row is quantised, by the warp
+// that needs it, group by group, to 16-bit integers  x_k ~ sx_g * xi_k  (sx_g a power of two chosen from the
 // group's largest magnitude, so a bf16 input is reproduced exactly unless it is more than 2^7
 // below that magnitude) and split into a low unsigned and a high signed byte plane.  The int8
 // tensor-core instruction mma.m16n8k32 then forms  D[row][g] = sum_k q[row][k] * xi[k]  exactly:
