@@ -260,14 +260,17 @@ def main() -> None:
         barrier()
         sampler = ClockSampler(dev)
         sampler.start()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(steps):
+        # one event per step boundary: the total (first to last) is the timed region, the gaps give the spread
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        marks[0].record(stream)
+        for i in range(steps):
             run_step()
-        e1.record(stream)
+            marks[i + 1].record(stream)
         barrier()
         clocks = sampler.stop()
-        ms = e0.elapsed_time(e1)
+        ms = marks[0].elapsed_time(marks[-1])
+        per_step = sorted(marks[i].elapsed_time(marks[i + 1]) for i in range(steps))
+        step_p50, step_p95 = per_step[len(per_step) // 2], per_step[min(len(per_step) - 1, int(0.95 * len(per_step)))]
     if dist is not None:
         t = torch.tensor([ms], device=f"cuda:{dev}")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -311,7 +314,8 @@ def main() -> None:
     achieved = algorithmic_bytes(payload, 1, N_ROWS, N_COLS) / (launch_us * 1e-6) / 1e9
     line = dict(base)
     line.update({
-        "value": value, "ms_per_step": ms_per_step, "clocks": clocks, "gpu_launches": POOL * steps,
+        "value": value, "ms_per_step": ms_per_step, "ms_per_step_p50": step_p50, "ms_per_step_p95": step_p95, "clocks": clocks,
+        "gpu_launches": POOL * steps,
         "graph_replay": graph is not None,
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": POOL * N_COLS * 2,
                 "d2h_bytes_per_step": POOL * N_ROWS * 2, "ms_per_step": e2e_ms,

@@ -47,7 +47,7 @@ def test_router_matches_torch_topk():
     assert torch.allclose(w, torch.softmax(tv, dim=1), rtol=2e-6, atol=1e-7)
 
 
-@pytest.mark.parametrize("tokens,experts,k", [(1, 128, 8), (40, 128, 8), (300, 64, 4), (3, 7, 2)])
+@pytest.mark.parametrize("tokens,experts,k", [(1, 128, 8), (40, 128, 8), (300, 64, 4), (3, 7, 2), (700, 128, 8)])
 def test_route_plan_matches_oracle(tokens, experts, k):
     rng = np.random.default_rng(tokens)
     ids = np.stack([rng.choice(experts, k, replace=False) for _ in range(tokens)]).astype(np.int32)
@@ -132,6 +132,37 @@ def test_mixed_precision_layer_and_expert_shards(tokens):
     # expert-parallel shards: each holds a contiguous expert range; their outputs add up
     parts = []
     for b, e in ((0, 6), (6, 16)):
+        sgu, sdn = moe.MoeWeight(gu_blob, expert_begin=b, expert_end=e), moe.MoeWeight(dn_blob, expert_begin=b, expert_end=e)
+        parts.append(moe.moe_ffn(sgu, sdn, bf16_tensor(x), ids, wts))
+        sgu.free()
+        sdn.free()
+    assert rel_l2((parts[0] + parts[1]).cpu().numpy(), y) <= 1e-5
+    gu.free()
+    dn.free()
+
+
+@pytest.mark.parametrize("tokens", [16, 40])
+def test_route_plan_tiles_of_two_and_four_pairs_all_cohorts_in_one_launch(tokens):
+    """48 experts, top-4: 16 tokens give tiles of two pairs, 40 tokens tiles of four; with the four
+    canonical precisions every cohort runs in the same launch.  Also through an expert shard."""
+    e_count, h, f, k = 48, 256, 96, 4
+    bits = np.random.default_rng(5003).choice([2, 3, 4, 6], e_count)
+    gu_blob, dn_blob = _moe_case(e_count, h, f, bits, seed=5001)
+    gu_ref = O.dequant_nintm(O.unpack_nintm(gu_blob))
+    dn_ref = O.dequant_nintm(O.unpack_nintm(dn_blob))
+    gu, dn = moe.MoeWeight(gu_blob), moe.MoeWeight(dn_blob)
+    rng = np.random.default_rng(5002 + tokens)
+    x = encode.bf16_round(rng.standard_normal((tokens, h), dtype=np.float32))
+    z = rng.standard_normal((tokens, e_count)).astype(np.float32)
+    ids, wts = moe.moe_topk(torch.from_numpy(z).cuda(), k)
+    rid, rw = O.moe_topk(z, k)
+    out = gu.matmul_id(bf16_tensor(x), ids, out_dtype=torch.float32).cpu().numpy()
+    want = np.stack([[gu_ref[rid[t, r]] @ x[t] for r in range(k)] for t in range(tokens)])
+    assert rel_l2(out, want) <= REL_L2
+    y = moe.moe_ffn(gu, dn, bf16_tensor(x), ids, wts).cpu().numpy()
+    assert rel_l2(y, O.moe_ffn(x, gu_ref, dn_ref, rid, rw)) <= 4e-3
+    parts = []
+    for b, e in ((0, 20), (20, 48)):
         sgu, sdn = moe.MoeWeight(gu_blob, expert_begin=b, expert_end=e), moe.MoeWeight(dn_blob, expert_begin=b, expert_end=e)
         parts.append(moe.moe_ffn(sgu, sdn, bf16_tensor(x), ids, wts))
         sgu.free()

@@ -38,6 +38,8 @@ void launch_nint_bl_gemv_routed(GemvArgsB a, int pairs, int device, cudaStream_t
 void launch_nint_bl_gemv_tiles(GemvArgsB a, int tile_m, int max_tiles, int device, cudaStream_t s);
 void check_nint_supported(const HostNint& t);
 int nint_bl_max_passes(const NintDevB& w);
+bool launch_moe_hetero_tiles(GemvArgsB base, const NintDevB* pools, const int* held, const uint2* const* xq, const float2* const* gtab,
+                             int npools, int tile_m, int max_tiles, int device, cudaStream_t s);
 bool launch_moe_hetero_gemv1(GemvArgsB base, const NintDevB* pools, const int* held, int npools, int pairs, int device, cudaStream_t s);
 size_t nint_bl_planes_bytes(const NintDevB& w, int rows);
 void launch_x_planes(const NintDevB& w, const void* x, int rows, void* planes, const uint2** xq_g, const float2** gtab_g, cudaStream_t s);
@@ -265,6 +267,52 @@ static void mul_mat_id_impl(const mfqb_moe_weight* w, const void* x, int x_per_p
         }
         if (launch_moe_hetero_gemv1(a, devs, held, (int)w->pools.size(), pairs, w->info.device, stream)) return;
     }
+    // quantised planes of the input rows, one set per distinct group size among the held cohorts
+    const uint2* pool_xq[16] = {nullptr};
+    const float2* pool_gtab[16] = {nullptr};
+    if (plan) {
+        for (size_t pi = 0; pi < w->pools.size(); ++pi) {
+            const MoePool& pool = *w->pools[pi];
+            if (!pool.held) continue;
+            const PlaneSet* ps = nullptr;
+            for (const PlaneSet& c : sets)
+                if (c.gs == pool.d.gs) ps = &c;
+            if (!ps) {
+                PlaneSet n{pool.d.gs, nullptr, nullptr};
+                launch_x_planes(pool.d, x, in_rows, planes_next, &n.xq, &n.gtab, stream);
+                planes_next += (nint_bl_planes_bytes(pool.d, in_rows) + 255) / 256 * 256;
+                sets.push_back(n);
+                ps = &sets.back();
+            }
+            pool_xq[pi] = ps->xq;
+            pool_gtab[pi] = ps->gtab;
+        }
+    }
+    const int max_tiles = plan ? pairs / tile_m + std::min(pairs, w->info.n_experts) : 0;
+    if (plan && max_tiles > 65535) fail(MFQB_ERR_ARG, "mfqb_mul_mat_id: too many route tiles (%d)", max_tiles);
+    if (plan && w->pools.size() <= 16) {   // all cohorts in one launch when their codecs allow
+        GemvArgsB a{};
+        a.x = static_cast<const __nv_bfloat16*>(x);
+        a.y = out;
+        a.ldy = ope;
+        a.y_dtype = out_dtype;
+        a.expert_pool = static_cast<const int*>(w->d_expert_pool.p);
+        a.expert_local = static_cast<const int*>(w->d_expert_local.p);
+        a.rb_per_expert = w->padded / 16;
+        a.routes = routes;
+        a.x_per_pair = x_per_pair ? 1 : 0;
+        a.expert_bounds = plan->expert_bounds;
+        a.tile_bounds = plan->tile_bounds;
+        a.pair_order = plan->pair_order;
+        a.n_experts = w->info.n_experts;
+        NintDevB devs[16];
+        int held[16];
+        for (size_t pi = 0; pi < w->pools.size(); ++pi) {
+            devs[pi] = w->pools[pi]->d;
+            held[pi] = w->pools[pi]->held;
+        }
+        if (launch_moe_hetero_tiles(a, devs, held, pool_xq, pool_gtab, (int)w->pools.size(), tile_m, max_tiles, w->info.device, stream)) return;
+    }
     for (size_t pi = 0; pi < w->pools.size(); ++pi) {
         const MoePool& pool = *w->pools[pi];
         if (!pool.held) continue;
@@ -285,20 +333,8 @@ static void mul_mat_id_impl(const mfqb_moe_weight* w, const void* x, int x_per_p
             a.tile_bounds = plan->tile_bounds;
             a.pair_order = plan->pair_order;
             a.n_experts = w->info.n_experts;
-            const int max_tiles = pairs / tile_m + std::min(pairs, w->info.n_experts);
-            if (max_tiles > 65535) fail(MFQB_ERR_ARG, "mfqb_mul_mat_id: too many route tiles (%d)", max_tiles);
-            const PlaneSet* ps = nullptr;
-            for (const PlaneSet& c : sets)
-                if (c.gs == pool.d.gs) ps = &c;
-            if (!ps) {   // first cohort of this group size: quantise the input rows once
-                PlaneSet n{pool.d.gs, nullptr, nullptr};
-                launch_x_planes(pool.d, x, in_rows, planes_next, &n.xq, &n.gtab, stream);
-                planes_next += (nint_bl_planes_bytes(pool.d, in_rows) + 255) / 256 * 256;
-                sets.push_back(n);
-                ps = &sets.back();
-            }
-            a.xq_g = ps->xq;
-            a.gtab_g = ps->gtab;
+            a.xq_g = pool_xq[pi];
+            a.gtab_g = pool_gtab[pi];
             launch_nint_bl_gemv_tiles(a, tile_m, max_tiles, w->info.device, stream);
             continue;
         }

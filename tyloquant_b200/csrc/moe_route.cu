@@ -119,6 +119,47 @@ __global__ void route_place_kernel(const int32_t* __restrict__ ids, int pairs, i
     }
 }
 
+// The same plan in one launch for decode-sized batches: one CTA counts with shared-memory
+// atomics, scans, and places (a warp per expert walks the pairs in order, as above).
+constexpr int kRoutePlanSmallExperts = 1024, kRoutePlanSmallPairs = 4096;
+__global__ void __launch_bounds__(1024) route_plan_small_kernel(const int32_t* __restrict__ ids, int pairs, int experts, int tile_m,
+                                                                int32_t* __restrict__ expert_bounds, int32_t* __restrict__ tile_bounds,
+                                                                int32_t* __restrict__ pair_order) {
+    __shared__ int bounds[kRoutePlanSmallExperts + 1];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    for (int e = tid; e <= experts; e += blockDim.x) bounds[e] = 0;
+    __syncthreads();
+    for (int p = tid; p < pairs; p += blockDim.x) {
+        const int e = ids[p];
+        if (e >= 0 && e < experts) atomicAdd(&bounds[e + 1], 1);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int run = 0, tiles = 0;
+        expert_bounds[0] = 0;
+        tile_bounds[0] = 0;
+        for (int e = 0; e < experts; ++e) {
+            const int c = bounds[e + 1];
+            bounds[e] = run;   // start of expert e's segment
+            run += c;
+            tiles += (c + tile_m - 1) / tile_m;
+            expert_bounds[e + 1] = run;
+            tile_bounds[e + 1] = tiles;
+        }
+    }
+    __syncthreads();
+    for (int e = warp; e < experts; e += nwarps) {
+        int at = bounds[e];
+        for (int base = 0; base < pairs; base += 32) {
+            const int p = base + lane;
+            const bool hit = p < pairs && ids[p] == e;
+            const unsigned m = __ballot_sync(0xffffffffu, hit);
+            if (hit) pair_order[at + __popc(m & ((1u << lane) - 1u))] = p;
+            at += __popc(m);
+        }
+    }
+}
+
 // ---- pointwise glue -----------------------------------------------------------------------------
 template <typename T>
 __device__ __forceinline__ float to_f32(T v);
@@ -176,6 +217,11 @@ void launch_weighted_reduce(const void* src, int in_dtype, const float* weights,
 
 void launch_route_plan(const int32_t* ids, int pairs, int experts, int tile_m, int32_t* expert_bounds, int32_t* tile_bounds,
                        int32_t* pair_order, cudaStream_t stream) {
+    if (experts <= kRoutePlanSmallExperts && pairs <= kRoutePlanSmallPairs) {
+        route_plan_small_kernel<<<1, 1024, 0, stream>>>(ids, pairs, experts, tile_m, expert_bounds, tile_bounds, pair_order);
+        MFQB_CUDA(cudaGetLastError());
+        return;
+    }
     const int blocks = (experts + 3) / 4;
     route_count_kernel<<<blocks, 128, 0, stream>>>(ids, pairs, experts, expert_bounds + 1);
     route_scan_kernel<<<1, 32, 0, stream>>>(experts, tile_m, expert_bounds, tile_bounds);

@@ -47,12 +47,10 @@ __host__ __device__ constexpr int gemvn_bl_stages(int rec_words, int passes) {
 __host__ __device__ constexpr int gemvn_bl_row_bytes(int t8) { return 64 * (gemv1_bl_qstride(t8) + 1); }
 
 template <class C, int P>
-__global__ void __launch_bounds__(256, (P >= 4 || C::MIN_CTAS < 3) ? (C::MIN_CTAS < 2 ? 1 : 2) : 3) gemvn_bl_kernel(const GemvArgsB a) {
+__device__ __forceinline__ void gemvn_bl_body(const GemvArgsB& a, const NintDevB& w, unsigned char* smem) {
     constexpr int G = kChunkGroupsB, MB = 2 * P, T = C::T, WC = C::WC, SW = C::SW, REC = (WC + SW) * 32;
     constexpr int S = gemvn_bl_stages(REC, P), QS = gemv1_bl_qstride(T), PLB = gemvn_bl_row_bytes(T);
-    const NintDevB& w = a.w;
 
-    extern __shared__ __align__(16) unsigned char smem[];
     __shared__ int row_src[MB], row_dst[MB];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const int q = lane >> 2, c = lane & 3;
@@ -233,6 +231,12 @@ __global__ void __launch_bounds__(256, (P >= 4 || C::MIN_CTAS < 3) ? (C::MIN_CTA
             else reinterpret_cast<__nv_bfloat16*>(a.y)[off] = __float2bfloat16_rn(v);
         }
     }
+}
+
+template <class C, int P>
+__global__ void __launch_bounds__(256, (P >= 4 || C::MIN_CTAS < 3) ? (C::MIN_CTAS < 2 ? 1 : 2) : 3) gemvn_bl_kernel(const GemvArgsB a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    gemvn_bl_body<C, P>(a, a.w, smem);
 }
 
 }  // namespace mfqb
