@@ -209,7 +209,7 @@ int mfqb_moe_dequant_expert(const mfqb_moe_weight* w, int expert, void* out, int
     });
 }
 
-// Pairs per route-plan tile (2, 4 or 8, sized to the average number of pairs an expert sees), or
+// Pairs per route-plan tile (2, 4 or 8, by the average number of pairs an expert sees), or
 // 0: fewer pairs than experts, every pair runs as a single-row problem of its own.
 static int moe_tile_m(const mfqb_moe_weight* w, int pairs) {
     const int e = w->info.n_experts;
@@ -217,7 +217,8 @@ static int moe_tile_m(const mfqb_moe_weight* w, int pairs) {
     int cap = 8;   // cohorts with wide records fit fewer batch rows per CTA
     for (const auto& pool : w->pools)
         if (pool->held) cap = std::min(cap, 2 * nint_bl_max_passes(pool->d));
-    return std::min(cap, pairs <= 5 * e / 2 ? 2 : (pairs <= 5 * e ? 4 : 8));
+    // measured on the 128-expert top-8 layer: tiles of four win from two to about twenty pairs per expert
+    return std::min(cap, 2 * pairs <= 3 * e ? 2 : (pairs <= 24 * e ? 4 : 8));
 }
 
 // Bytes of quantised activation planes the tile path needs for `rows` input rows: one set per
