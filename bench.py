@@ -426,7 +426,7 @@ def sweep(dev: int, peak: float, only: str | None = None, reps: int = 10) -> dic
 
 
 def gemm_bench(dev: int, peak_tflops: float, reps: int = 5) -> dict:
-    """BASELINE config 2: M = 512 tokens, N = 14336, K = 4096, NINT4 (4,32,6) and NINT8 (8,32,7):
+    """BASELINE config 2: M = 512 tokens, N = 14336, K = 4096, NINT4 (4,32,6), NINT8 (8,48,7) and its control (8,32,7):
     TFLOP/s of mfqb_mul_mat (x conversion pre-pass + tcgen05 tile kernel) against the dense bf16 peak."""
     import torch
 
@@ -435,7 +435,7 @@ def gemm_bench(dev: int, peak_tflops: float, reps: int = 5) -> dict:
     d = f"cuda:{dev}"
     m, n, k = 512, 14336, 4096
     out = {}
-    for name, (b, gs, sb) in (("NINT4_gs32", (4, 32, 6)), ("NINT8_gs32", (8, 32, 7)), ("NINT4_gs24", (4, 24, 6))):
+    for name, (b, gs, sb) in (("NINT4_gs32", (4, 32, 6)), ("NINT8_gs48", (8, 48, 7)), ("NINT8_gs32", (8, 32, 7)), ("NINT4_gs24", (4, 24, 6))):
         w = QuantWeight.from_blob(f"NINT{b}", encode.random_nint_blob(n, k, b, gs, sb, seed=2001, device=d), device=dev)
         x = torch.randn((m, k), device=d).to(torch.bfloat16)
         for _ in range(3):

@@ -21,7 +21,8 @@ def _status():
     return s.value
 
 
-@pytest.mark.parametrize("profile", [(4, 24, 6), (4, 32, 6), (8, 32, 7), (3, 24, 5), (2, 16, 5), (6, 24, 7), (5, 24, 7)])
+@pytest.mark.parametrize("profile", [(4, 24, 6), (4, 32, 6), (8, 32, 7), (3, 24, 5), (2, 16, 5), (6, 24, 7), (5, 24, 7), (8, 48, 7), (6, 40, 7),
+                                     (5, 64, 7)])
 def test_tile_gemm_matches_oracle(profile):
     bits, gs, sb = profile
     for (n, k, ms) in [(256, 1000, (17, 64, 200)), (130, 4096, (33,))]:
