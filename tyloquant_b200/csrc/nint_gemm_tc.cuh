@@ -34,17 +34,19 @@ struct GemmArgs {
     int m, kx;
     void* y;             // [m, n]
     int y_dtype;
-    int bn;              // tokens per tile: 64, 128 or 256
-    int stages;          // ring depth in 64-column atoms
+    int bn;              // tokens per tile: 64, 128, 256 or 512
+    int stages;          // depth of the weight ring, in 64-column atoms (at least one chunk)
+    int xstages;         // depth of the activation ring, in atoms
     int* error;          // device word: set to MFQB_ERR_TIMEOUT when a wait expires
 };
 
 constexpr int kGemmProducerWarps = 16;
 constexpr int kGemmThreads = (kGemmProducerWarps + 2) * 32;   // + mma warp + x loader warp
 
-// The ring is counted in atoms: one stage = 64 columns of K = a 128 x 64 f16 slab of W (16 KB) and
-// a BN x 64 f16 slab of x, each a K-major tile with the 128-byte swizzle.  A chunk of 8 groups is
-// ATOMS consecutive stages.  Two producer warps share one row-block record: warp half f decodes
+// Two rings, both counted in atoms of 64 columns of K, each atom a K-major tile with the 128-byte
+// swizzle: the weight ring holds 128 x 64 f16 slabs of W (16 KB; a chunk of 8 groups is ATOMS
+// consecutive stages and is decoded as a whole, so the ring holds at least one chunk), the
+// activation ring BN x 64 f16 slabs of x, which only need to run a little ahead of the tensor core.  Two producer warps share one row-block record: warp half f decodes
 // the registers of family f (groups 4f .. 4f+3) of the byte-lane layout.
 template <int BITS, int T>
 __global__ void __launch_bounds__(kGemmThreads, 1) nint_gemm_tc_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x_map) {
@@ -58,12 +60,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) nint_gemm_tc_kernel(const Gem
     constexpr int FW = SPLIT ? (4 * T) / BU::NP * BU::U : WC;
     constexpr int NPROD = kGemmProducerWarps * 32;
     const NintDevB& w = a.w;
-    const int BN = a.bn, NS = a.stages;
+    const int BN = a.bn, NS = a.stages, NB = a.xstages;
 
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    const int stage_bytes = 128 * 128 + BN * 128;   // A atom then B atom
-    __shared__ __align__(8) uint64_t full_bar[8], empty_bar[8], done_bar;
+    constexpr int stage_bytes = 128 * 128;           // one weight atom
+    const int xstage_bytes = BN * 128;               // one activation atom
+    unsigned char* xtiles = tiles + (size_t)NS * stage_bytes;
+    __shared__ __align__(8) uint64_t full_bar[8], empty_bar[8], xfull_bar[4], xempty_bar[4], done_bar;
     __shared__ uint32_t tmem_base_slot;
     __shared__ int failed;
 
@@ -73,8 +77,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) nint_gemm_tc_kernel(const Gem
 
     if (tid == 0) {
         for (int i = 0; i < 8; ++i) {
-            mbar_init(&full_bar[i], NPROD + 1);   // producers + the x loader's expect_tx arrival
+            mbar_init(&full_bar[i], NPROD);
             mbar_init(&empty_bar[i], 1);
+        }
+        for (int i = 0; i < 4; ++i) {
+            mbar_init(&xfull_bar[i], 1);   // the x loader's expect_tx arrival
+            mbar_init(&xempty_bar[i], 1);
         }
         mbar_init(&done_bar, 1);
         failed = 0;
@@ -166,25 +174,29 @@ __global__ void __launch_bounds__(kGemmThreads, 1) nint_gemm_tc_kernel(const Gem
         if (lane == 0) {
             const int natoms = w.nchunks * ATOMS;
             for (int ai = 0; ai < natoms; ++ai) {
-                const int st = ai % NS, use = ai / NS;
-                if (use > 0 && !mbar_wait(&empty_bar[st], (use - 1) & 1)) { failed = 1; break; }
-                mbar_arrive_expect_tx(&full_bar[st], (uint32_t)(BN * 128));
-                tma_load_2d(tiles + st * stage_bytes + 128 * 128, &x_map, ai * 64, tok0, &full_bar[st]);
+                const int st = ai % NB, use = ai / NB;
+                if (use > 0 && !mbar_wait(&xempty_bar[st], (use - 1) & 1)) { failed = 1; break; }
+                mbar_arrive_expect_tx(&xfull_bar[st], (uint32_t)xstage_bytes);
+                for (int r0 = 0; r0 < BN; r0 += 256)   // a box holds at most 256 rows
+                    tma_load_2d(xtiles + (size_t)st * xstage_bytes + (size_t)r0 * 128, &x_map, ai * 64, tok0 + r0, &xfull_bar[st]);
             }
         }
     } else if (lane == 0) {
         // ------------------------------ mma issuer ------------------------------
-        const uint32_t idesc = instr_desc_f16(128, BN);
+        const uint32_t idesc = instr_desc_f16(128, BN < 256 ? BN : 256);
         const int natoms = w.nchunks * ATOMS;
         for (int ai = 0; ai < natoms; ++ai) {
-            const int st = ai % NS, use = ai / NS;
-            if (!mbar_wait(&full_bar[st], use & 1)) { failed = 1; break; }
+            const int st = ai % NS, xs = ai % NB;
+            if (!mbar_wait(&full_bar[st], (ai / NS) & 1) || !mbar_wait(&xfull_bar[xs], (ai / NB) & 1)) { failed = 1; break; }
             tc_fence_after_sync();
-            const uint32_t a_base = smem_u32(tiles + st * stage_bytes), b_base = a_base + 128 * 128;
+            const uint32_t a_base = smem_u32(tiles + st * stage_bytes), b_base = smem_u32(xtiles + (size_t)xs * xstage_bytes);
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-                tc_mma_f16(tmem_d, smem_desc_sw128(a_base + j * 32), smem_desc_sw128(b_base + j * 32), idesc, ai > 0 || j > 0);
+                for (int h = 0; h < BN; h += 256)   // one instruction covers at most 256 token columns
+                    tc_mma_f16(tmem_d + (uint32_t)h, smem_desc_sw128(a_base + j * 32), smem_desc_sw128(b_base + h * 128 + j * 32), idesc,
+                               ai > 0 || j > 0);
             tc_commit(&empty_bar[st]);
+            tc_commit(&xempty_bar[xs]);
         }
         tc_commit(&done_bar);
     }
@@ -226,7 +238,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) nint_gemm_tc_kernel(const Gem
 }
 
 struct GemmPlan {
-    int bn, stages, grid_x, grid_y;
+    int bn, stages, xstages, grid_x, grid_y;
     size_t smem;
 };
 // The group size must be a multiple of 8 (a chunk is then whole swizzle atoms); returns bn = 0 otherwise.
@@ -234,18 +246,22 @@ inline GemmPlan plan_nint_gemm(const NintDevB& w, int m) {
     GemmPlan p{};
     if (w.gs % 8 != 0 || w.t8 * 8 != w.gs) return p;
     const int atoms = kChunkGroupsB * w.gs / 64;
-    // wide token tiles amortise the dequantisation: 256 tokens when the ring then still holds one whole
-    // chunk (atoms stages), else 128
-    int bn = 256;
-    if ((int)((220 * 1024) / (128 * 128 + bn * 128)) < atoms) bn = 128;
+    // Wide token tiles amortise the dequantisation: the widest of 512, 256, 128 tokens for which the
+    // weight ring still holds one whole chunk beside an activation ring of two (512) or three atoms.
+    int bn = 512;
+    auto weight_stages = [](int bn_) {
+        const int xst = bn_ >= 512 ? 2 : 3;
+        return std::min(8, (int)((220 * 1024 - (size_t)xst * bn_ * 128) / (128 * 128)));
+    };
+    while (bn > 128 && weight_stages(bn) < atoms) bn /= 2;
     while (bn > 64 && bn / 2 >= m) bn /= 2;
     p.bn = bn;
-    const int stage_bytes = 128 * 128 + bn * 128;
-    p.stages = std::min(8, (int)((220 * 1024) / stage_bytes));
+    p.xstages = bn >= 512 ? 2 : 3;
+    p.stages = weight_stages(bn);
     if (p.stages < atoms) { p.bn = 0; return p; }
     p.grid_x = (w.n + 127) / 128;
     p.grid_y = (m + bn - 1) / bn;
-    p.smem = (size_t)p.stages * stage_bytes + 1024;
+    p.smem = (size_t)p.stages * 128 * 128 + (size_t)p.xstages * bn * 128 + 1024;
     return p;
 }
 

@@ -72,7 +72,7 @@ static CUtensorMap make_x_map(const void* x16, int m, int kx, int bn) {
     CUtensorMap map;
     const cuuint64_t dims[2] = {(cuuint64_t)kx, (cuuint64_t)m};
     const cuuint64_t strides[1] = {(cuuint64_t)kx * sizeof(__half)};
-    const cuuint32_t box[2] = {64u, (cuuint32_t)bn};
+    const cuuint32_t box[2] = {64u, (cuuint32_t)std::min(bn, 256)};   // a box holds at most 256 rows; wider tiles take two loads
     const cuuint32_t elem[2] = {1u, 1u};
     const CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x16), dims, strides, box, elem,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -94,6 +94,7 @@ static bool launch_nint_gemm(const NintDevB& w, const void* x, int m, void* y, i
     a.y_dtype = y_dtype;
     a.bn = p.bn;
     a.stages = p.stages;
+    a.xstages = p.xstages;
     a.error = gemm_status_word(device);
     DevBuf& xb = g_gemm.x16[device];
     const size_t need = (size_t)m * a.kx * sizeof(__half);
