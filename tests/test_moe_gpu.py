@@ -142,10 +142,10 @@ def test_mixed_precision_layer_and_expert_shards(tokens):
 
 
 @pytest.mark.parametrize("tokens", [16, 40, 400])
-def test_route_plan_tiles_of_two_four_and_eight_pairs(tokens):
+def test_route_plan_tiles_and_grouped_tile_kernel(tokens):
     """48 experts, top-4: 16 tokens give tiles of two pairs, 40 tokens tiles of four (with the four
-    canonical precisions every cohort then runs in the same launch), 400 tokens tiles of eight (one
-    launch per cohort).  Also through an expert shard."""
+    canonical precisions every cohort then runs in the same launch), 400 tokens (33 pairs per expert)
+    go to the tensor-core tile kernel grouped by expert.  Also through an expert shard."""
     e_count, h, f, k = 48, 256, 96, 4
     bits = np.random.default_rng(5003).choice([2, 3, 4, 6], e_count)
     gu_blob, dn_blob = _moe_case(e_count, h, f, bits, seed=5001)

@@ -38,6 +38,12 @@ void launch_nint_bl_gemv_routed(GemvArgsB a, int pairs, int device, cudaStream_t
 void launch_nint_bl_gemv_tiles(GemvArgsB a, int tile_m, int max_tiles, int device, cudaStream_t s);
 void check_nint_supported(const HostNint& t);
 int nint_bl_max_passes(const NintDevB& w);
+bool nint_gemm_grouped_supported(const NintDevB& w, int bn, int rows_per_expert);
+size_t nint_gemm_grouped_x_bytes(int pairs, int k);
+void launch_x_gather_f16(const void* x, const int* pair_order, int div, int pairs, int k, void* x16, cudaStream_t s);
+void launch_nint_gemm_grouped(const NintDevB& w, const void* x16, int pairs, int bn, const int* expert_bounds, const int* tile_bounds,
+                              const int* pair_order, const int* expert_pool, const int* expert_local, int n_experts, int pool,
+                              int rb_per_expert, int rows_per_expert, int max_tiles, void* y, int y_dtype, int device, cudaStream_t s);
 bool launch_moe_hetero_tiles(GemvArgsB base, const NintDevB* pools, const int* held, const uint2* const* xq, const float2* const* gtab,
                              int npools, int tile_m, int max_tiles, int device, cudaStream_t s);
 bool launch_moe_hetero_gemv1(GemvArgsB base, const NintDevB* pools, const int* held, int npools, int pairs, int device, cudaStream_t s);
@@ -221,6 +227,20 @@ static int moe_tile_m(const mfqb_moe_weight* w, int pairs) {
     return std::min(cap, 2 * pairs <= 3 * e ? 2 : (pairs <= 24 * e ? 4 : 8));
 }
 
+// Token tile of the tensor-core tile kernel for large batches (the route plan is then built with
+// this tile size), or 0 to stay on the integer kernels.  Measured on the 128-expert top-8 layer:
+// from about two dozen pairs per expert one f16 decode of an expert's weights per tile beats the
+// batched integer passes over them (the tile kernel's time hardly depends on the batch).
+static int moe_gemm_bn(const mfqb_moe_weight* w, int pairs) {
+    const int e = w->info.n_experts;
+    if (pairs < 24 * e) return 0;
+    int bn = 32;
+    while (bn < 256 && 4 * bn < 5 * (pairs / e)) bn *= 2;   // room for experts that draw more than the average
+    for (const auto& pool : w->pools)
+        if (pool->held && !nint_gemm_grouped_supported(pool->d, bn, w->info.out_per_expert)) return 0;
+    return bn;
+}
+
 // Bytes of quantised activation planes the tile path needs for `rows` input rows: one set per
 // distinct group size among the held cohorts (cohorts of equal group size share theirs).
 static size_t moe_planes_bytes(const mfqb_moe_weight* w, int rows) {
@@ -238,7 +258,7 @@ static size_t moe_planes_bytes(const mfqb_moe_weight* w, int rows) {
 // plan's tiles (the plan must have been built for these ids with the same tile_m) and `planes` is
 // moe_planes_bytes() of device memory for the quantised input rows.
 static void mul_mat_id_impl(const mfqb_moe_weight* w, const void* x, int x_per_pair, const int32_t* ids, int tokens, int routes,
-                            void* out, int out_dtype, const PlanBufs* plan, int tile_m, void* planes, cudaStream_t stream) {
+                            void* out, int out_dtype, const PlanBufs* plan, int tile_m, void* planes, cudaStream_t stream, bool gemm = false) {
     const int pairs = tokens * routes, ope = w->info.out_per_expert;
     const int in_rows = x_per_pair ? pairs : tokens;
     struct PlaneSet { int gs; const uint2* xq; const float2* gtab; };
@@ -267,6 +287,19 @@ static void mul_mat_id_impl(const mfqb_moe_weight* w, const void* x, int x_per_p
             held[pi] = w->pools[pi]->held;
         }
         if (launch_moe_hetero_gemv1(a, devs, held, (int)w->pools.size(), pairs, w->info.device, stream)) return;
+    }
+    if (plan && gemm) {   // large batches: tensor-core tile kernel, `planes` holds the gathered f16 rows
+        launch_x_gather_f16(x, plan->pair_order, x_per_pair ? 1 : routes, pairs, w->info.k, planes, stream);
+        const int tiles = pairs / tile_m + std::min(pairs, w->info.n_experts);
+        if (tiles > 65535) fail(MFQB_ERR_ARG, "mfqb_mul_mat_id: too many route tiles (%d)", tiles);
+        for (size_t pi = 0; pi < w->pools.size(); ++pi) {
+            const MoePool& pool = *w->pools[pi];
+            if (!pool.held) continue;
+            launch_nint_gemm_grouped(pool.d, planes, pairs, tile_m, plan->expert_bounds, plan->tile_bounds, plan->pair_order,
+                                     static_cast<const int*>(w->d_expert_pool.p), static_cast<const int*>(w->d_expert_local.p),
+                                     w->info.n_experts, (int)pi, w->padded / 16, ope, tiles, out, out_dtype, w->info.device, stream);
+        }
+        return;
     }
     // quantised planes of the input rows, one set per distinct group size among the held cohorts
     const uint2* pool_xq[16] = {nullptr};
@@ -361,13 +394,15 @@ int mfqb_mul_mat_id(const mfqb_moe_weight* w, const void* x, int x_per_pair, con
         if (tokens == 0) return;
         DeviceGuard guard(w->info.device);
         const int pairs = tokens * routes;
-        const int tile_m = moe_tile_m(w, pairs);
-        if (tile_m) {   // larger batches: route plan in library scratch, batched kernel over its tiles
+        const int gemm_bn = moe_gemm_bn(w, pairs);
+        const int tile_m = gemm_bn ? gemm_bn : moe_tile_m(w, pairs);
+        if (tile_m) {   // larger batches: route plan in library scratch, batched or tile kernel over its tiles
             const size_t b_plan = PlanBufs::bytes(w->info.n_experts, pairs);
-            char* s = static_cast<char*>(scratch_get(w->info.device, b_plan + moe_planes_bytes(w, x_per_pair ? pairs : tokens), 1));
+            const size_t b_in = gemm_bn ? nint_gemm_grouped_x_bytes(pairs, w->info.k) : moe_planes_bytes(w, x_per_pair ? pairs : tokens);
+            char* s = static_cast<char*>(scratch_get(w->info.device, b_plan + b_in, 1));
             PlanBufs plan = PlanBufs::carve(s, w->info.n_experts);
             launch_route_plan(ids, pairs, w->info.n_experts, tile_m, plan.expert_bounds, plan.tile_bounds, plan.pair_order, stream);
-            mul_mat_id_impl(w, x, x_per_pair, ids, tokens, routes, out, out_dtype, &plan, tile_m, s + b_plan, stream);
+            mul_mat_id_impl(w, x, x_per_pair, ids, tokens, routes, out, out_dtype, &plan, tile_m, s + b_plan, stream, gemm_bn != 0);
         } else {
             mul_mat_id_impl(w, x, x_per_pair, ids, tokens, routes, out, out_dtype, nullptr, 0, nullptr, stream);
         }
@@ -386,10 +421,14 @@ int mfqb_moe_ffn(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* down, co
         DeviceGuard guard(gate_up->info.device);
         const size_t pairs = (size_t)tokens * routes;
         const size_t b_gu = pairs * f2 * 4, b_hid = (pairs * f * 2 + 255) / 256 * 256, b_dn = pairs * h * 4;
-        const int tile_m = std::min(moe_tile_m(gate_up, (int)pairs), moe_tile_m(down, (int)pairs));
+        // large batches: both matmuls on the tensor-core tile kernel, when every cohort of both has one
+        const int gemm_bn = std::min(moe_gemm_bn(gate_up, (int)pairs), moe_gemm_bn(down, (int)pairs));
+        const bool gemm = gemm_bn != 0;
+        const int tile_m = gemm ? gemm_bn : std::min(moe_tile_m(gate_up, (int)pairs), moe_tile_m(down, (int)pairs));
         const bool tiles = tile_m != 0;
         const size_t b_plan = tiles ? PlanBufs::bytes(gate_up->info.n_experts, pairs) : 0;
-        const size_t b_pgu = tiles ? moe_planes_bytes(gate_up, tokens) : 0, b_pdn = tiles ? moe_planes_bytes(down, (int)pairs) : 0;
+        const size_t b_pgu = gemm ? (nint_gemm_grouped_x_bytes((int)pairs, h) + 255) / 256 * 256 : (tiles ? moe_planes_bytes(gate_up, tokens) : 0);
+        const size_t b_pdn = gemm ? nint_gemm_grouped_x_bytes((int)pairs, f) : (tiles ? moe_planes_bytes(down, (int)pairs) : 0);
         char* s = static_cast<char*>(scratch_get(gate_up->info.device, b_gu + b_hid + b_dn + b_plan + b_pgu + b_pdn));
         float* gu = reinterpret_cast<float*>(s);
         void* hid = s + b_gu;
@@ -400,9 +439,9 @@ int mfqb_moe_ffn(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* down, co
             launch_route_plan(ids, (int)pairs, gate_up->info.n_experts, tile_m, plan.expert_bounds, plan.tile_bounds, plan.pair_order, stream);
         }
         char* planes = s + b_gu + b_hid + b_dn + b_plan;
-        mul_mat_id_impl(gate_up, x, 0, ids, tokens, routes, gu, MFQB_F32, tiles ? &plan : nullptr, tile_m, planes, stream);
+        mul_mat_id_impl(gate_up, x, 0, ids, tokens, routes, gu, MFQB_F32, tiles ? &plan : nullptr, tile_m, planes, stream, gemm);
         launch_swiglu(gu, MFQB_F32, (int)pairs, f, hid, stream);
-        mul_mat_id_impl(down, hid, 1, ids, tokens, routes, dn, MFQB_F32, tiles ? &plan : nullptr, tile_m, planes + b_pgu, stream);
+        mul_mat_id_impl(down, hid, 1, ids, tokens, routes, dn, MFQB_F32, tiles ? &plan : nullptr, tile_m, planes + b_pgu, stream, gemm);
         launch_weighted_reduce(dn, MFQB_F32, weights, tokens, routes, h, y, y_dtype, stream);
     });
 }

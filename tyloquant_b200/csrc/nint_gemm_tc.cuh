@@ -38,6 +38,16 @@ struct GemmArgs {
     int stages;          // depth of the weight ring, in 64-column atoms (at least one chunk)
     int xstages;         // depth of the activation ring, in atoms
     int* error;          // device word: set to MFQB_ERR_TIMEOUT when a wait expires
+    // Grouped mode (expert matmul over a route plan whose tile size is bn): blockIdx.y is a tile of
+    // up to bn pairs of one expert; x16 holds the input rows in plan order (row p = pair
+    // pair_order[p]), the tile's expert selects rb_per_expert row-blocks of w, and the result of
+    // column i goes to row pair_order[p0 + i] of y [pairs, ldy].  tile_bounds == nullptr: plain GEMM.
+    const int* expert_bounds;
+    const int* tile_bounds;
+    const int* pair_order;
+    const int* expert_pool;
+    const int* expert_local;
+    int n_experts, pool, rb_per_expert, ldy;
 };
 
 constexpr int kGemmProducerWarps = 16;
@@ -73,7 +83,28 @@ __global__ void __launch_bounds__(kGemmThreads, 1) nint_gemm_tc_kernel(const Gem
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int q = lane >> 2, c = lane & 3;
-    const int row0 = blockIdx.x * 128, tok0 = blockIdx.y * BN;
+    int row0 = blockIdx.x * 128, tok0 = blockIdx.y * BN;
+    int rb_first = blockIdx.x * 8, rb_end = w.nrb, ncols = a.m - tok0, row_limit = w.n, ldy = w.n;
+    const bool grouped = a.tile_bounds != nullptr;
+    if (grouped) {
+        const int t = blockIdx.y;
+        if (t >= a.tile_bounds[a.n_experts]) return;   // before any barrier or tensor-memory allocation: the whole CTA leaves
+        int lo = 0, hi = a.n_experts - 1;   // expert e with tile_bounds[e] <= t < tile_bounds[e + 1]
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (a.tile_bounds[mid] <= t) lo = mid;
+            else hi = mid - 1;
+        }
+        if (a.expert_pool[lo] != a.pool) return;
+        tok0 = a.expert_bounds[lo] + (t - a.tile_bounds[lo]) * BN;
+        ncols = a.expert_bounds[lo + 1] - tok0;
+        const int rb_base = a.expert_local[lo] * a.rb_per_expert;
+        rb_first = rb_base + blockIdx.x * 8;
+        rb_end = rb_base + a.rb_per_expert;
+        row_limit = a.ldy;   // rows of one expert
+        ldy = a.ldy;
+    }
+    if (ncols > BN) ncols = BN;
 
     if (tid == 0) {
         for (int i = 0; i < 8; ++i) {
@@ -97,8 +128,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) nint_gemm_tc_kernel(const Gem
     if (warp < kGemmProducerWarps) {
         // ------------------------------ producers ------------------------------
         const int rbl = warp >> 1, f = warp & 1;         // row-block of the tile, family of the chunk
-        const int rb = blockIdx.x * 8 + rbl;
-        const bool rb_valid = rb < w.nrb;
+        const int rb = rb_first + rbl;
+        const bool rb_valid = rb < rb_end;
         bool alive = true;
         const int w0 = SPLIT ? f * FW : 0;               // first code word of this warp's registers
         const int r0 = SPLIT ? 0 : f * 4 * T;            // register index of (t = 0, a = 0) inside those words
@@ -211,18 +242,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1) nint_gemm_tc_kernel(const Gem
         const int cols_per_part = BN / 4 < 32 ? 32 : BN / 4;
         const int c_begin = part * cols_per_part, c_end = min(BN, c_begin + cols_per_part);
         if (ok && c_begin < BN) {
-            const int n = row0 + lane_quarter * 32 + lane;
+            const int n = row0 + lane_quarter * 32 + lane;   // row of the matrix, or of the tile's expert
             for (int cb = c_begin; cb < c_end; cb += 32) {
                 uint32_t r[32];
                 tmem_ld32(tmem_d + ((uint32_t)(lane_quarter * 32) << 16) + (uint32_t)cb, r);
-                if (n < w.n) {
+                if (n < row_limit) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        const int tok = tok0 + cb + i;
-                        if (tok < a.m) {
+                        if (cb + i < ncols) {
+                            const size_t out_row = grouped ? (size_t)a.pair_order[tok0 + cb + i] : (size_t)(tok0 + cb + i);
                             const float v = __uint_as_float(r[i]);
-                            if (a.y_dtype == 0 /* MFQB_F32 */) reinterpret_cast<float*>(a.y)[(size_t)tok * w.n + n] = v;
-                            else reinterpret_cast<__nv_bfloat16*>(a.y)[(size_t)tok * w.n + n] = __float2bfloat16_rn(v);
+                            if (a.y_dtype == 0 /* MFQB_F32 */) reinterpret_cast<float*>(a.y)[out_row * ldy + n] = v;
+                            else reinterpret_cast<__nv_bfloat16*>(a.y)[out_row * ldy + n] = __float2bfloat16_rn(v);
                         }
                     }
                 }
@@ -261,6 +292,22 @@ inline GemmPlan plan_nint_gemm(const NintDevB& w, int m) {
     if (p.stages < atoms) { p.bn = 0; return p; }
     p.grid_x = (w.n + 127) / 128;
     p.grid_y = (m + bn - 1) / bn;
+    p.smem = (size_t)p.stages * 128 * 128 + (size_t)p.xstages * bn * 128 + 1024;
+    return p;
+}
+
+// Plan of the grouped mode for a fixed token tile (the route plan's tile size, 32 .. 256); grid_x
+// covers one expert's rows.  bn = 0 when this weight has no tile kernel for it.
+inline GemmPlan plan_nint_gemm_grouped(const NintDevB& w, int bn, int rows_per_expert, int max_tiles) {
+    GemmPlan p{};
+    if (w.gs % 8 != 0 || w.t8 * 8 != w.gs || bn < 32 || bn > 256 || (bn & (bn - 1))) return p;
+    const int atoms = kChunkGroupsB * w.gs / 64;
+    p.bn = bn;
+    p.xstages = 3;
+    p.stages = std::min(8, (int)((220 * 1024 - (size_t)p.xstages * bn * 128) / (128 * 128)));
+    if (p.stages < atoms) { p.bn = 0; return p; }
+    p.grid_x = (rows_per_expert + 127) / 128;
+    p.grid_y = max_tiles;
     p.smem = (size_t)p.stages * 128 * 128 + (size_t)p.xstages * bn * 128 + 1024;
     return p;
 }

@@ -120,6 +120,76 @@ static bool launch_nint_gemm(const NintDevB& w, const void* x, int m, void* y, i
     return true;
 }
 
+// Rows of x (bf16 [rows, k]) gathered in route-plan order and converted to f16 [pairs, kx]:
+// out row p = x row (pair_order[p] / div).
+__global__ void x_gather_f16_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ pair_order, int div, int pairs, int k, int kx,
+                                    __half* __restrict__ out) {
+    const size_t total = (size_t)pairs * kx;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t p = i / kx, c = i % kx;
+        float v = c < (size_t)k ? __bfloat162float(x[(size_t)(pair_order[p] / div) * k + c]) : 0.f;
+        v = fminf(fmaxf(v, -65504.f), 65504.f);
+        out[i] = __float2half_rn(v);
+    }
+}
+
+// True when the grouped tile kernel can run this cohort tensor with `bn`-pair tiles.
+bool nint_gemm_grouped_supported(const NintDevB& w, int bn, int rows_per_expert) { return plan_nint_gemm_grouped(w, bn, rows_per_expert, 1).bn != 0; }
+
+// Bytes of the gathered f16 input the grouped kernel reads.
+size_t nint_gemm_grouped_x_bytes(int pairs, int k) { return (size_t)pairs * ((k + 7) / 8 * 8) * sizeof(__half); }
+
+void launch_x_gather_f16(const void* x, const int* pair_order, int div, int pairs, int k, void* x16, cudaStream_t s) {
+    const int kx = (k + 7) / 8 * 8;
+    const size_t total = (size_t)pairs * kx;
+    x_gather_f16_kernel<<<(int)std::min<size_t>((total + 255) / 256, 148 * 8), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), pair_order, div, pairs, k,
+                                                                                      kx, static_cast<__half*>(x16));
+    MFQB_CUDA(cudaGetLastError());
+}
+
+// Expert matmul of one cohort on the tile kernel: x16 = launch_x_gather_f16 output for this plan.
+void launch_nint_gemm_grouped(const NintDevB& w, const void* x16, int pairs, int bn, const int* expert_bounds, const int* tile_bounds,
+                              const int* pair_order, const int* expert_pool, const int* expert_local, int n_experts, int pool,
+                              int rb_per_expert, int rows_per_expert, int max_tiles, void* y, int y_dtype, int device, cudaStream_t s) {
+    const GemmPlan p = plan_nint_gemm_grouped(w, bn, rows_per_expert, max_tiles);
+    if (p.bn == 0) fail(MFQB_ERR_UNSUPPORTED, "NINT%d gs=%d has no grouped tile kernel for tiles of %d", w.bits, w.gs, bn);
+    GemmArgs a{};
+    {
+        std::lock_guard<std::mutex> lock(g_gemm.mu);
+        a.error = gemm_status_word(device);
+    }
+    a.w = w;
+    a.m = pairs;
+    a.kx = (w.k + 7) / 8 * 8;
+    a.x16 = static_cast<const __half*>(x16);
+    a.y = y;
+    a.y_dtype = y_dtype;
+    a.bn = p.bn;
+    a.stages = p.stages;
+    a.xstages = p.xstages;
+    a.expert_bounds = expert_bounds;
+    a.tile_bounds = tile_bounds;
+    a.pair_order = pair_order;
+    a.expert_pool = expert_pool;
+    a.expert_local = expert_local;
+    a.n_experts = n_experts;
+    a.pool = pool;
+    a.rb_per_expert = rb_per_expert;
+    a.ldy = rows_per_expert;
+    const CUtensorMap x_map = make_x_map(x16, pairs, a.kx, p.bn);
+    cudaError_t e;
+    switch (w.bits) {
+        case 2: e = launch_nint_gemm_bits<2>(a, p, x_map, s); break;
+        case 3: e = launch_nint_gemm_bits<3>(a, p, x_map, s); break;
+        case 4: e = launch_nint_gemm_bits<4>(a, p, x_map, s); break;
+        case 5: e = launch_nint_gemm_bits<5>(a, p, x_map, s); break;
+        case 6: e = launch_nint_gemm_bits<6>(a, p, x_map, s); break;
+        case 8: e = launch_nint_gemm_bits<8>(a, p, x_map, s); break;
+        default: e = cudaErrorNotSupported; break;
+    }
+    if (e != cudaSuccess) fail(MFQB_ERR_CUDA, "NINT%d gs=%d grouped GEMM launch: %s", w.bits, w.gs, cudaGetErrorString(e));
+}
+
 int gemm_device_status(int device) {
     std::lock_guard<std::mutex> lock(g_gemm.mu);
     return g_gemm.status_host[device] ? *static_cast<volatile int*>(g_gemm.status_host[device]) : 0;
