@@ -132,6 +132,15 @@ struct NintCodec {
     }
 };
 
+// Split of R row-blocks over g CTAs: every CTA gets R / g, the first R % g one more.  CTAs are
+// handed to the SMs round robin, so the extra row-blocks land on distinct SMs instead of pairing up
+// on one (which an even spread of the remainder over the block indices does).
+__device__ __forceinline__ void split_row_blocks(int b, int g, int total, int& first, int& count) {
+    const int base = total / g, extra = total % g;
+    first = b * base + min(b, extra);
+    count = base + (b < extra ? 1 : 0);
+}
+
 // Records per warp ring: about 6 KB of ring per warp, between 2 and 6 stages.
 __host__ __device__ constexpr int gemv1_bl_stages(int rec_words) {
     return 6144 / (rec_words * 4) < 2 ? 2 : (6144 / (rec_words * 4) > 6 ? 6 : 6144 / (rec_words * 4));
@@ -313,7 +322,7 @@ __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB
     uint32_t* anch = reinterpret_cast<uint32_t*>(ypart + (size_t)ycopies * ystride);
     uint32_t* ring = anch + (size_t)a.rb_per_cta * 16 + (size_t)warp * S * REC;   // ctx_bytes is a multiple of 16
 
-    // balanced split of the row-blocks over gridDim.x: CTA b owns [b*R/grid, (b+1)*R/grid) of the
+    // split of the row-blocks over gridDim.x (split_row_blocks): CTA b owns a contiguous range of the
     // R row-blocks of the whole matrix, or of its pair's expert in routed mode
     int rb_base = 0, rb_total = w.nrb;
     const __nv_bfloat16* xrow = a.x;
@@ -327,8 +336,8 @@ __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB
         xrow += (size_t)(a.x_per_pair ? pair : pair / a.routes) * w.k;
         y_off = (size_t)pair * a.ldy;
     }
-    const int rbl0 = (int)(((long long)blockIdx.x * rb_total) / gridDim.x);
-    const int nrb = (int)(((long long)(blockIdx.x + 1) * rb_total) / gridDim.x) - rbl0;
+    int rbl0, nrb;
+    split_row_blocks(blockIdx.x, gridDim.x, rb_total, rbl0, nrb);
     const int rb0 = rb_base + rbl0;
     const int row_limit = a.route_ids != nullptr ? a.ldy : w.n;   // rows this problem has (an expert's rows are padded to whole blocks)
 

@@ -83,14 +83,12 @@ __device__ __forceinline__ void gemvn_bl_body(const GemvArgsB& a, const NintDevB
             row_src[tid] = a.x_per_pair ? pair : pair / a.routes;
             row_dst[tid] = pair;
         }
-        rbl0 = (int)(((long long)blockIdx.x * a.rb_per_expert) / gridDim.x);
-        nrb = (int)(((long long)(blockIdx.x + 1) * a.rb_per_expert) / gridDim.x) - rbl0;
+        split_row_blocks(blockIdx.x, gridDim.x, a.rb_per_expert, rbl0, nrb);
         rb0 = a.expert_local[e] * a.rb_per_expert + rbl0;
         row_limit = a.ldy;
     } else {
         if (tid < MB) row_src[tid] = row_dst[tid] = tid;
-        rbl0 = (int)(((long long)blockIdx.x * w.nrb) / gridDim.x);
-        nrb = (int)(((long long)(blockIdx.x + 1) * w.nrb) / gridDim.x) - rbl0;
+        split_row_blocks(blockIdx.x, gridDim.x, w.nrb, rbl0, nrb);
         rb0 = rbl0;
     }
     pdl_launch_dependents_b();
