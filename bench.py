@@ -99,15 +99,35 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def profile_traffic(name: str):
+    """DRAM bytes per launch recorded with the ncu summary profiles/<name>.md, or None."""
+    path = os.path.join(ROOT, "profiles", name + ".json")
+    try:
+        with open(path) as f:
+            return json.load(f).get("dram_bytes_per_launch")
+    except (OSError, ValueError):
+        return None
+
+
 def algorithmic_bytes(payload: int, m: int, n: int, k: int) -> int:
     """Packed payload of the weight record (file streams) + x (bf16) + y (bf16)."""
     return payload + m * k * 2 + m * n * 2
 
 
+def _encode_standalone():
+    """The blob writers, loaded by path: importing the package would load the CUDA library,
+    which the reference arm must not touch."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("_mfqb_encode_standalone", os.path.join(ROOT, "tyloquant_b200", "encode.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
 def cpu_reference_arm(steps: int, warmup: int, budget_s: float = 20.0):
     """Reference CPU path (oracle port): dequantize once, then float32 x @ W.T per call."""
     from oracle import mfq_oracle as O
-    from tyloquant_b200 import encode
+    encode = _encode_standalone()
 
     try:   # torchrun exports OMP_NUM_THREADS=1: the reference arm may use every host core
         import torch
@@ -159,10 +179,10 @@ def main() -> None:
     ap.add_argument("--only", default=None, help="run one sweep case by name with a few plain launches "
                     "(small, for profilers) and print its line")
     ap.add_argument("--reps", type=int, default=3, help="launch rounds for --only")
+    ap.add_argument("--match", default=None, help="with --only sweep: run the cases whose name contains this text")
     ap.add_argument("--tokens", type=int, nargs="*", default=None, help="token counts for --only moe")
-    ap.add_argument("--parallel-extras", action="store_true",
-                    help="at --gpus > 1 also time the fused row-parallel linear and the expert-parallel MoE layer "
-                         "(keys tp_rowparallel, ep_moe_cfg4)")
+    ap.add_argument("--no-parallel", action="store_true",
+                    help="at --gpus > 1 skip the sharded paths (keys tp_rowparallel, ep_moe_cfg4) and time the replicas only")
     args = ap.parse_args()
     steps, warmup = max(args.steps, 1), max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -180,6 +200,9 @@ def main() -> None:
         return
     if args.only == "moe":
         print(json.dumps(moe_layer_bench(local_rank, measured_peaks()[0]["hbm_gbs"], token_counts=tuple(args.tokens or (1, 8, 32, 64, 128, 256, 1024)))))
+        return
+    if args.only == "sweep":   # every sweep case, graph-timed, nothing else
+        print(json.dumps({"sweep": sweep(local_rank, measured_peaks()[0]["hbm_gbs"], match=args.match)}))
         return
     if args.only:
         print(json.dumps(sweep(local_rank, measured_peaks()[0]["hbm_gbs"], only=args.only, reps=args.reps)))
@@ -283,26 +306,40 @@ def main() -> None:
     yh = torch.empty((1, N_ROWS), dtype=torch.int16).pin_memory()
     e2e_steps = max(3, min(steps, 10))
 
-    def e2e_step():
+    import ctypes as C
+    yhs = [torch.empty((1, N_ROWS), dtype=torch.int16).pin_memory() for _ in range(POOL)]
+    h_arr = (C.c_void_p * POOL)(*[w._h for w in weights])
+    x_arr = (C.c_void_p * POOL)(*[xh.data_ptr()] * POOL)
+    y_arr = (C.c_void_p * POOL)(*[y.data_ptr() for y in yhs])
+
+    def e2e_step():   # one call: the step's 48 products, x pulled from and y written to pinned host memory
+        check(lib.mfqb_mul_mat_host_multi(h_arr, POOL, x_arr, 1, y_arr, BF16))
+
+    def e2e_step_single():   # one call per product
         for w in weights:
             check(lib.mfqb_mul_mat_host(w._h, xh.data_ptr(), 1, yh.data_ptr(), BF16))
 
-    for _ in range(2):
-        e2e_step()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_step()
-    torch.cuda.synchronize(dev)
-    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-    if dist is not None:
-        t = torch.tensor([e2e_ms], device=f"cuda:{dev}")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+    def time_e2e(fn):
+        for _ in range(2):
+            fn()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            fn()
+        torch.cuda.synchronize(dev)
+        ms_ = (time.perf_counter() - t0) * 1e3 / e2e_steps
+        if dist is not None:
+            t_ = torch.tensor([ms_], device=f"cuda:{dev}")
+            dist.all_reduce(t_, op=dist.ReduceOp.MAX)
+            ms_ = float(t_.item())
+        return ms_
+
+    e2e_ms = time_e2e(e2e_step)
+    e2e_single_ms = time_e2e(e2e_step_single)
     e2e_value = world * step_bytes / (e2e_ms * 1e-3) / 1e9
 
-    tp = tp_rowparallel_bench(dev, rank, world, dist) if dist is not None and args.parallel_extras else None
-    ep = ep_moe_bench(dev, rank, world, dist) if dist is not None and args.parallel_extras else None
+    tp = tp_rowparallel_bench(dev, rank, world, dist) if dist is not None and not args.no_parallel else None
+    ep = ep_moe_bench(dev, rank, world, dist) if dist is not None and not args.no_parallel else None
 
     if rank != 0:
         if dist is not None:
@@ -319,14 +356,16 @@ def main() -> None:
         "graph_replay": graph is not None,
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": POOL * N_COLS * 2,
                 "d2h_bytes_per_step": POOL * N_ROWS * 2, "ms_per_step": e2e_ms,
-                "api": "mfqb_mul_mat_host (pinned host x and y, weights resident)"},
-        "roofline": {"bound": "hbm", "kernel": "gemv1_bl_kernel<NintCodec<3,3>>", "achieved": achieved, "peak": peaks["hbm_gbs"],
+                "api": "mfqb_mul_mat_host_multi: the step's 48 products in one call (pinned host x and y, weights resident)",
+                "one_call_per_product": {"api": "mfqb_mul_mat_host", "ms_per_step": e2e_single_ms,
+                                         "value": world * step_bytes / (e2e_single_ms * 1e-3) / 1e9}},
+        "roofline": {"bound": "hbm", "kernel": "gemvs_kernel<NintCodec<3,3>>", "achieved": achieved, "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": f"{peak_kind} copy bandwidth",
                      "us_per_launch": launch_us, "algorithmic_bytes_per_launch": algorithmic_bytes(payload, 1, N_ROWS, N_COLS),
                      "device_bytes_per_launch": weights[0].device_bytes,
-                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch, ncu --set full capture
-                     # summarised in profiles/gemv1_bl_nint3_4096x4096.md
-                     "traffic": 7979264},
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel and shape, from
+                     # the ncu capture summarised under profiles/ (the JSON beside the summary)
+                     "traffic": profile_traffic("gemvs_nint3_4096x4096")},
     })
     if tp is not None:
         line["tp_rowparallel"] = tp
@@ -344,7 +383,7 @@ def main() -> None:
         dist.destroy_process_group()
 
 
-def sweep(dev: int, peak: float, only: str | None = None, reps: int = 10) -> dict:
+def sweep(dev: int, peak: float, only: str | None = None, reps: int = 10, match: str | None = None) -> dict:
     """GB/s of one GEMV launch per profile and shape (pool of distinct weights > L2, graph replay).
 
     With ``only`` a single case runs, without a graph and with a pool just above L2, so that a
@@ -370,8 +409,10 @@ def sweep(dev: int, peak: float, only: str | None = None, reps: int = 10) -> dic
 
     cases = [(f"NINT{b}_4096x4096_m1", nint_case(b, gs, sb, 4096, 4096), 4096, 4096, 1)
              for b, (_, gs, sb) in encode.CANONICAL_NINT.items()]
-    cases += [("NINT4_14336x4096_m1", nint_case(4, 24, 6, 14336, 4096), 14336, 4096, 1),
-              ("NINT6_14336x4096_m1", nint_case(6, 24, 7, 14336, 4096), 14336, 4096, 1),
+    # the FFN shape of the dense decoder (config 5), every canonical width: the target shape of the GEMV roofline
+    cases += [(f"NINT{b}_14336x4096_m1", nint_case(b, gs, sb, 14336, 4096), 14336, 4096, 1)
+              for b, (_, gs, sb) in encode.CANONICAL_NINT.items()]
+    cases += [
               ("NINT3_4096x4096_m8", nint_case(3, 24, 5, 4096, 4096), 4096, 4096, 8),
               ("NINT4_4096x14336_m1", nint_case(4, 24, 6, 4096, 14336), 4096, 14336, 1),
               ("NVQ3_17408x5120_m1", nvq_case(False, 17408, 5120), 17408, 5120, 1),
@@ -380,7 +421,7 @@ def sweep(dev: int, peak: float, only: str | None = None, reps: int = 10) -> dic
               ("NVQ3J-512_17408x5120_m1", nvq_case(True, 17408, 5120), 17408, 5120, 1)]
     blob_cache = {}
     for name, (dtype, make_blob), n, k, m in cases:
-        if only and name != only:
+        if (only and name != only) or (match and match not in name):
             continue
         key = name.rsplit("_m", 1)[0]
         if key not in blob_cache:

@@ -113,7 +113,15 @@ int mfqb_dequant(const mfqb_weight* w, void* out, int out_dtype, mfqb_stream_t s
  * value unless it lies more than 2^7 below its group's largest magnitude; the product is within
  * 1e-5 relative L2 of the float32 reference), sums are exact in int32 and the scales are applied
  * in float32.  Larger m for NINT runs the tcgen05 tile kernel (f16 operands, float32 accumulation).
- * An infinity or NaN in x makes the outputs NaN.
+ * An infinity or NaN in x makes the outputs NaN (on the tile kernel, finite magnitudes beyond
+ * 65504 saturate to +-65504 in the f16 copy of x).
+ * Library scratch: m >= 2 uses a per-device buffer (quantised planes, or the f16 copy of x) that
+ * only ever grows -- a block handed to a kernel or baked into a captured graph stays allocated.
+ * Growing calls cudaMalloc, so the first call with a given (or larger) m on a device must come
+ * outside stream capture; inside a capture it fails with MFQB_ERR_ARG instead.  The buffer holds
+ * one call's data at a time: calls with m >= 2 on one device must be ordered by their streams.
+ * A single-row (m = 1) product of a NINT weight uses a few KB of scratch owned by the weight
+ * handle: two such products of the SAME weight must not overlap on the GPU.
  * Stands in for nint_matmul / nvq_matmul / QuantLinear::forward
  * (cpp_runtime/mfq_decode.cpp:8130-8315, 7884-7932, 9209). */
 int mfqb_mul_mat(const mfqb_weight* w, const void* x_bf16, int m, void* y, int y_dtype,
@@ -129,6 +137,12 @@ int mfqb_device_status(int device, int* status);
  * what a host-side caller such as the numpy runtime mfq/runtime/linear.py:37-42 uses.) */
 int mfqb_mul_mat_host(const mfqb_weight* w, const void* x_bf16_host, int m, void* y_host,
                       int y_dtype);
+/* The same for `count` weights of one device in one call, weight i with its own xs_host[i]
+ * [m, k_i] and ys_host[i] [m, n_i]: everything is enqueued back to back and the call waits once
+ * (the host-side form of a group of linears that run together, QuantLinearGroup / NintLinearGroup,
+ * cpp_runtime/mfq_decode.cpp:8618-8743).  Pinned, mapped buffers are read and written in place. */
+int mfqb_mul_mat_host_multi(const mfqb_weight* const* ws, int count, const void* const* xs_bf16_host,
+                            int m, void* const* ys_host, int y_dtype);
 
 /* ---------------------------------------------------------------------------------
  * Tensor-parallel slice planner.  Same results and the same rejections as
@@ -224,8 +238,10 @@ int mfqb_moe_weighted_reduce(const void* expert_out, int in_dtype, const float* 
 /* Whole expert FFN (nint_moe_ffn_forward, cpp_runtime/mfq_decode.cpp:3394-3416):
  *   y[t] = sum_r weights[t, r] * down_e( silu(gate_e x[t]) * up_e x[t] ),  e = ids[t, r].
  * gate_up holds [E, 2F, H] (gate rows first), down [E, H, F].  The intermediates live in a
- * scratch buffer the library keeps per device (grown on demand with cudaMalloc, so the first
- * call for a given size must not be inside a stream capture). */
+ * per-device library buffer that only ever grows (see mfqb_mul_mat): the first call of a given
+ * size must come outside stream capture (inside one it fails with MFQB_ERR_ARG), one warm-up call
+ * per batch-size regime should precede a capture, and calls on one device must be ordered by
+ * their streams.  mfqb_mul_mat_id with tokens * routes >= n_experts uses a buffer of the same kind. */
 int mfqb_moe_ffn(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* down, const void* x_bf16,
                  const int32_t* ids, const float* weights, int tokens, int routes, void* y, int y_dtype,
                  mfqb_stream_t stream);
@@ -263,6 +279,14 @@ int mfqb_comm_set_timeout_ms(mfqb_comm* c, int ms);
 int mfqb_allreduce_f32(mfqb_comm* c, const float* in, float* out, uint64_t n, mfqb_stream_t stream);
 int mfqb_mul_mat_allreduce(const mfqb_weight* w, const void* x_bf16, int m, mfqb_comm* c, void* y, int y_dtype,
                            mfqb_stream_t stream);
+/* Recovery after MFQB_ERR_TIMEOUT.  Every rank calls it with none of its collectives in flight;
+ * it clears this rank's slots, its device-side call number and its status word.  The ranks must
+ * then synchronise on the host (a barrier of the caller's process group) before the next
+ * collective.  No counterpart in the reference (NCCL errors there end the process,
+ * cpp_runtime/mfq_decode.cpp:63-70). */
+int mfqb_comm_reset(mfqb_comm* c);
+/* Test hook: sets the device-side call number, e.g. just below the 32-bit wrap (every rank the same value). */
+int mfqb_comm_debug_set_seq(mfqb_comm* c, unsigned seq);
 int mfqb_comm_status(const mfqb_comm* c, int* status);
 int mfqb_comm_destroy(mfqb_comm* c);
 

@@ -10,8 +10,12 @@ small seeded tensors in every profile on the packed-weight execution path, and s
 * the serialized blob exactly as the reference wrote it, and
 * the float32 tensor the reference's decoder returned for it,
 
-in ``golden.npz`` (compressed), plus one complete ``.mfq`` file image.  The tests never
-import the reference; they only read these files.
+in ``golden.npz`` (compressed), plus one complete ``.mfq`` file image.  With ``--cfg1`` it
+writes ``golden_cfg1.npz`` instead: a 1024 x 4096 slice of the headline configuration (N(0, 0.02)
+weights rounded to bf16, NINT3 groupsize 24 sub-bits 5) encoded by the reference encoder, with the
+SHA-256 of the reference decoder's float32 output, a sample of its rows, and the reference
+runtime's products for seeded activations.  The tests never import the reference; they only read
+these files.
 """
 
 from __future__ import annotations
@@ -158,5 +162,38 @@ def main(ref_root: str) -> None:
     print("wrote", os.path.join(here, "golden.npz"), "with", len(out), "arrays")
 
 
+def main_cfg1(ref_root: str) -> None:
+    import hashlib
+
+    sys.path.insert(0, ref_root)
+    sys.dont_write_bytecode = True
+    from mfq.formats import io as mio
+    from mfq.formats.nint import NintSpec
+    from mfq.quantize import nint_quant
+    from mfq.runtime.linear import NintLinear
+
+    def bf16(x):
+        u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+        r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16
+        return r.astype(np.uint32).view(np.float32).reshape(x.shape)
+
+    n, k = 1024, 4096
+    w = bf16((np.random.default_rng(1001).standard_normal((n, k)) * 0.02).astype(np.float32))
+    t = nint_quant.quantize(w, NintSpec(bits=3, groupsize=24, sub_bits=5))
+    dtype, blob = mio._pack_tensor(t)
+    back = mio._unpack_tensor(dtype, blob)
+    ref = np.ascontiguousarray(nint_quant.dequantize(back), dtype=np.float32)
+    x = bf16(np.random.default_rng(1002).standard_normal((4, k)).astype(np.float32))
+    rows = np.arange(0, n, 37)
+    out = {"blob": np.frombuffer(blob, dtype=np.uint8), "dtype": np.array(dtype),
+           "w_sha256": np.array(hashlib.sha256(ref.tobytes()).hexdigest()),
+           "rows": rows, "w_rows": ref[rows], "x": x,
+           "y": NintLinear(back).forward(x).astype(np.float32)}
+    here = os.path.dirname(os.path.abspath(__file__))
+    np.savez_compressed(os.path.join(here, "golden_cfg1.npz"), **out)
+    print("wrote golden_cfg1.npz:", len(blob), "blob bytes")
+
+
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    args = [a for a in sys.argv[1:] if a != "--cfg1"]
+    (main_cfg1 if "--cfg1" in sys.argv else main)(args[0] if args else "/root/reference")

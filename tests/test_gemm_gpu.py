@@ -51,3 +51,63 @@ def test_config2_shape_nint4_gs32():
     assert _status() == 0
     assert rel_l2(y, O.linear(x, ref)) <= REL_L2
     w.free()
+
+
+def test_nonfinite_inputs_stay_nonfinite_on_the_tile_kernel():
+    """An infinity or a NaN in a row of x makes that row of the output NaN on every path: the
+    integer kernels (m <= 16) and the f16 tile kernel (m > 16) must agree on that."""
+    blob = encode.random_nint_blob(256, 1024, 4, 32, 6, seed=77)
+    w = QuantWeight.from_blob("NINT4", blob)
+    x = torch.randn(32, 1024, device="cuda", generator=torch.Generator("cuda").manual_seed(3)).to(torch.bfloat16)
+    x[5, 100] = float("inf")
+    x[9, 7] = float("-inf")
+    x[20, 512] = float("nan")
+    x[30, 3] = 3.0e38   # finite, beyond the f16 range: saturates, stays finite
+    y = w.matmul(x, out_dtype=torch.float32)
+    assert _status() == 0
+    for r in (5, 9, 20):
+        assert torch.isnan(y[r]).all(), r
+    finite_rows = [r for r in range(32) if r not in (5, 9, 20)]
+    assert torch.isfinite(y[finite_rows]).all()
+    w.free()
+
+
+def test_library_scratch_survives_growth_under_a_captured_graph():
+    """A graph captured at m = 4 keeps working after a later, larger call made the per-device
+    scratch grow (the old block must stay alive), and growth inside a capture is refused."""
+    from tyloquant_b200 import MfqbError
+    blob = encode.random_nint_blob(512, 2048, 3, 24, 5, seed=5)
+    ref = O.dequant_nint(O.unpack_nint(blob))
+    w = QuantWeight.from_blob("NINT3", blob)
+    rng = np.random.default_rng(11)
+    x4 = bf16_tensor(encode.bf16_round(rng.standard_normal((4, 2048), dtype=np.float32)))
+    y4 = torch.empty((4, 512), dtype=torch.float32, device="cuda")
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        w.matmul(x4, out=y4)
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            w.matmul(x4, out=y4)
+        # a much larger batched call on the same device: the planes buffer has to grow
+        big = QuantWeight.from_blob("NINT3", encode.random_nint_blob(64, 65536, 3, 24, 5, seed=6, device="cuda"))
+        big.matmul(torch.randn(8, 65536, device="cuda").to(torch.bfloat16))
+        y4.zero_()
+        g.replay()
+        stream.synchronize()
+    assert rel_l2(y4.cpu().numpy(), O.linear(x4.float().cpu().numpy(), ref)) <= REL_L2
+    # growth while capturing: refused with a message, the capture survives being abandoned
+    huge = QuantWeight.from_blob("NINT3", encode.random_nint_blob(64, 262144, 3, 24, 5, seed=7, device="cuda"))
+    xh = torch.randn(8, 262144, device="cuda").to(torch.bfloat16)
+    s2 = torch.cuda.Stream()
+    with torch.cuda.stream(s2):
+        g2 = torch.cuda.CUDAGraph()
+        try:
+            with pytest.raises(MfqbError):
+                with torch.cuda.graph(g2, stream=s2):
+                    huge.matmul(xh)
+        except RuntimeError:
+            pass   # torch may complain about the abandoned capture; the library call itself must have raised MfqbError
+    torch.cuda.synchronize()
+    for t in (w, big, huge):
+        t.free()

@@ -29,9 +29,14 @@ def test_router_ids_are_bit_exact(tokens, experts, k):
             assert np.array_equal(ids.cpu().numpy(), rid), mode
             np.testing.assert_allclose(w.cpu().numpy(), rw, rtol=2e-6, atol=1e-7)
         else:
-            # scores pass through expf/log1pf: allow swaps only between numerically tied scores
-            same = ids.cpu().numpy() == rid
-            assert same.mean() > 0.99
+            # scores pass through expf / log1pf, whose last bits may differ between the device and
+            # numpy: an id may differ from the oracle's only where the two scores involved are
+            # within 2 float32 units of each other (a numerical tie)
+            got = ids.cpu().numpy()
+            scores = O.router_scores(z, mode)
+            for t, r in zip(*np.nonzero(got != rid)):
+                a, b = scores[t, got[t, r]], scores[t, rid[t, r]]
+                assert abs(a - b) <= 2 * np.spacing(max(abs(a), abs(b)).astype(np.float32)), (mode, t, r, a, b)
     bias = torch.from_numpy(rng.standard_normal(experts).astype(np.float32)).cuda()
     ids, w = moe.moe_topk(zt, k, bias=bias)
     rid, rw = O.moe_topk(z, k, bias=bias.cpu().numpy())

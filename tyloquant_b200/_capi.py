@@ -67,6 +67,7 @@ _SIGNATURES = {
     "mfqb_mul_mat": (_i, [_vp, _vp, _i, _vp, _i, _vp]),
     "mfqb_device_status": (_i, [_i, _P(_i)]),
     "mfqb_mul_mat_host": (_i, [_vp, _vp, _i, _vp, _i]),
+    "mfqb_mul_mat_host_multi": (_i, [_P(_vp), _i, _P(_vp), _i, _P(_vp), _i]),
     "mfqb_tp_plan": (_i, [_i64, _i64, _i, _P(C.c_double), _P(_i64), _P(_i64)]),
     "mfqb_tp_validate": (_i, [_i64, _i64, _i, _P(_i64), _P(_i64)]),
     "mfqb_tp_granularity": (_i, [_i64, _i64, _i, _P(_i64)]),
@@ -88,6 +89,8 @@ _SIGNATURES = {
     "mfqb_comm_set_timeout_ms": (_i, [_vp, _i]),
     "mfqb_allreduce_f32": (_i, [_vp, _vp, _vp, _u64, _vp]),
     "mfqb_mul_mat_allreduce": (_i, [_vp, _vp, _i, _vp, _vp, _i, _vp]),
+    "mfqb_comm_reset": (_i, [_vp]),
+    "mfqb_comm_debug_set_seq": (_i, [_vp, C.c_uint]),
     "mfqb_comm_status": (_i, [_vp, _P(_i)]),
     "mfqb_comm_destroy": (_i, [_vp]),
     "mfqb_moe_ffn_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _i, _vp]),

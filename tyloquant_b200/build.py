@@ -25,6 +25,7 @@ NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 CUFLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
            "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",
            "-I", INCLUDE]
+CUFLAGS += os.environ.get("MFQB_EXTRA_CUFLAGS", "").split()   # e.g. development-only -D switches
 CXXFLAGS = ["-std=c++17", "-O2", "-fPIC", "-fvisibility=hidden", "-Wall", "-Wno-unknown-pragmas", "-I", INCLUDE]
 
 

@@ -74,6 +74,12 @@ class Communicator:
                                          torch.cuda.current_stream(self.device).cuda_stream))
         return y
 
+    def reset(self, group=None) -> None:
+        """After a timeout: clear this rank's slots and call number, then meet the other ranks."""
+        import torch.distributed as dist
+        check(lib.mfqb_comm_reset(self._h))
+        dist.barrier(group=group)
+
     def status(self) -> int:
         s = C.c_int()
         check(lib.mfqb_comm_status(self._h, C.byref(s)))

@@ -174,6 +174,32 @@ int mfqb_mul_mat_allreduce(const mfqb_weight* w, const void* x, int m, mfqb_comm
     });
 }
 
+// Recovery after MFQB_ERR_TIMEOUT: the ranks' device-side call numbers may differ (a rank that
+// timed out advanced alone).  Every rank calls this with none of its collectives in flight; it
+// clears this rank's slots, call number and status.  The ranks must then meet on the host (a
+// barrier of the caller's process group) before the next collective, so that no rank pushes into
+// slots a peer has yet to clear.
+int mfqb_comm_reset(mfqb_comm* c) {
+    return guarded([&] {
+        if (!c) fail(MFQB_ERR_ARG, "mfqb_comm_reset: null argument");
+        DeviceGuard guard(c->device);
+        MFQB_CUDA(cudaDeviceSynchronize());
+        MFQB_CUDA(cudaMemset(c->local.p, 0, c->local.bytes));
+        MFQB_CUDA(cudaMemset(c->counters.p, 0, c->counters.bytes));
+        *c->status_host = 0;
+    });
+}
+
+// Development hook for tests: sets the device-side call number (e.g. just below the 32-bit wrap).
+int mfqb_comm_debug_set_seq(mfqb_comm* c, unsigned seq) {
+    return guarded([&] {
+        if (!c) fail(MFQB_ERR_ARG, "mfqb_comm_debug_set_seq: null argument");
+        DeviceGuard guard(c->device);
+        MFQB_CUDA(cudaDeviceSynchronize());
+        MFQB_CUDA(cudaMemcpy(c->counters.p, &seq, sizeof(unsigned), cudaMemcpyHostToDevice));
+    });
+}
+
 int mfqb_comm_status(const mfqb_comm* c, int* status) {
     return guarded([&] {
         if (!c || !status) fail(MFQB_ERR_ARG, "mfqb_comm_status: null argument");

@@ -75,8 +75,10 @@ __device__ __forceinline__ float peer_sum(const PeerReduce& pr, unsigned seq, si
 __device__ __forceinline__ unsigned peer_call_seq(const PeerReduce& pr) {
     __shared__ unsigned s_seq;
     if (threadIdx.x == 0) {
+        // never 0 (slots start at zero), and the parity -- which selects the slot set -- must keep
+        // alternating across the wrap: 0xFFFFFFFF (odd) is followed by 2 (even)
         const unsigned s = *reinterpret_cast<volatile unsigned*>(pr.seq_dev) + 1u;
-        s_seq = s ? s : 1u;
+        s_seq = s ? s : 2u;
     }
     __syncthreads();
     return s_seq;

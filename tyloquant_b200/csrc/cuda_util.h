@@ -2,6 +2,8 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <mutex>
+
 #include "common.h"
 
 namespace mfqb {
@@ -49,6 +51,23 @@ struct DevBuf {
         bytes = 0;
     }
     ~DevBuf() { release(); }
+};
+
+// Library scratch that only ever grows: one block per device, handed to kernels that may still be
+// in flight (or baked into a captured graph) when a later call needs more.  A larger request
+// allocates a new block and keeps the old one alive until the process exits, so a pointer handed
+// out once stays valid.  Growing allocates, which a stream capture does not allow: the call then
+// fails with a message instead of breaking the capture.  Calls that share a block on one device
+// must be ordered by their streams (the block holds one call's intermediates at a time).
+struct GrowOnlyScratch {
+    void* get(int device, size_t bytes, cudaStream_t stream, const char* what);
+
+private:
+    struct PerDevice {
+        void* p = nullptr;
+        size_t bytes = 0;
+    };
+    PerDevice dev_[64];
 };
 
 }  // namespace mfqb

@@ -82,17 +82,11 @@ static HostNint gather_experts(const HostNint& t, const std::vector<int>& local,
     return r;
 }
 
-// Per-device scratch for the FFN intermediates; grown on demand.
-struct Scratch {
-    std::mutex mu;
-    DevBuf buf[64], plan[64];
-};
-static Scratch g_scratch;
-static void* scratch_get(int device, size_t bytes, int slot = 0) {
-    std::lock_guard<std::mutex> lock(g_scratch.mu);
-    DevBuf& b = slot ? g_scratch.plan[device] : g_scratch.buf[device];
-    if (b.bytes < bytes) b.alloc(bytes + bytes / 4);
-    return b.p;
+// Per-device scratch for the FFN intermediates (slot 0) and for a stand-alone routed matmul's plan
+// and planes (slot 1): grow-only, see GrowOnlyScratch.
+static void* scratch_get(int device, size_t bytes, cudaStream_t stream, int slot = 0) {
+    static GrowOnlyScratch pools[2];
+    return pools[slot].get(device, bytes, stream, slot ? "mfqb_mul_mat_id (route plan and activation planes)" : "mfqb_moe_ffn (intermediates)");
 }
 
 }  // namespace mfqb
@@ -399,7 +393,7 @@ int mfqb_mul_mat_id(const mfqb_moe_weight* w, const void* x, int x_per_pair, con
         if (tile_m) {   // larger batches: route plan in library scratch, batched or tile kernel over its tiles
             const size_t b_plan = PlanBufs::bytes(w->info.n_experts, pairs);
             const size_t b_in = gemm_bn ? nint_gemm_grouped_x_bytes(pairs, w->info.k) : moe_planes_bytes(w, x_per_pair ? pairs : tokens);
-            char* s = static_cast<char*>(scratch_get(w->info.device, b_plan + b_in, 1));
+            char* s = static_cast<char*>(scratch_get(w->info.device, b_plan + b_in, stream, 1));
             PlanBufs plan = PlanBufs::carve(s, w->info.n_experts);
             launch_route_plan(ids, pairs, w->info.n_experts, tile_m, plan.expert_bounds, plan.tile_bounds, plan.pair_order, stream);
             mul_mat_id_impl(w, x, x_per_pair, ids, tokens, routes, out, out_dtype, &plan, tile_m, s + b_plan, stream, gemm_bn != 0);
@@ -429,7 +423,7 @@ int mfqb_moe_ffn(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* down, co
         const size_t b_plan = tiles ? PlanBufs::bytes(gate_up->info.n_experts, pairs) : 0;
         const size_t b_pgu = gemm ? (nint_gemm_grouped_x_bytes((int)pairs, h) + 255) / 256 * 256 : (tiles ? moe_planes_bytes(gate_up, tokens) : 0);
         const size_t b_pdn = gemm ? nint_gemm_grouped_x_bytes((int)pairs, f) : (tiles ? moe_planes_bytes(down, (int)pairs) : 0);
-        char* s = static_cast<char*>(scratch_get(gate_up->info.device, b_gu + b_hid + b_dn + b_plan + b_pgu + b_pdn));
+        char* s = static_cast<char*>(scratch_get(gate_up->info.device, b_gu + b_hid + b_dn + b_plan + b_pgu + b_pdn, stream));
         float* gu = reinterpret_cast<float*>(s);
         void* hid = s + b_gu;
         float* dn = reinterpret_cast<float*>(s + b_gu + b_hid);

@@ -147,14 +147,10 @@ void launch_x_planes(const NintDevB& w, const void* x, int rows, void* planes, c
     MFQB_CUDA(cudaGetLastError());
 }
 
-// Library scratch for the planes of a plain batched product (grows on demand, per device).
-static void* planes_scratch(int device, size_t bytes) {
-    static std::mutex mu;
-    static DevBuf buf[64];
-    std::lock_guard<std::mutex> lock(mu);
-    if (device < 0 || device >= 64) fail(MFQB_ERR_ARG, "device index %d out of range", device);
-    if (buf[device].bytes < bytes) buf[device].alloc(bytes + bytes / 2);
-    return buf[device].p;
+// Library scratch for the planes of a plain batched product (per device, grow-only).
+static void* planes_scratch(int device, size_t bytes, cudaStream_t s) {
+    static GrowOnlyScratch pool;
+    return pool.get(device, bytes, s, "mfqb_mul_mat (quantised activation planes)");
 }
 
 static int passes_for(int m) { return m <= 2 ? 1 : (m <= 4 ? 2 : 4); }
@@ -194,7 +190,7 @@ void launch_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtyp
                                static_cast<char*>(y) + (size_t)m0 * ldy * ysz, y_dtype, ldy, device, s);
             return;
         }
-        launch_x_planes(w, x, m, planes_scratch(device, nint_bl_planes_bytes(w, m)), &a.xq_g, &a.gtab_g, s);
+        launch_x_planes(w, x, m, planes_scratch(device, nint_bl_planes_bytes(w, m), s), &a.xq_g, &a.gtab_g, s);
         p.passes = passes_for(m);
         // at least two row-blocks per CTA where the matrix allows: a chunk's planes then serve several items
         const int cap = ctas_per_sm(gemvn_smem(w, 2, p.passes), p.passes == 4 ? 2 : 3) * sms;
@@ -204,6 +200,81 @@ void launch_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtyp
         if (p.smem > kGemvSmemLimit) fail(MFQB_ERR_UNSUPPORTED, "batched product: %d row-blocks per CTA do not fit shared memory", a.rb_per_cta);
     }
     dispatch(a, p, s, "GEMV");
+}
+
+// Streamed single-row product (nint_gemvs.cuh).  `fix` is the weight's own scratch for row-blocks
+// that straddle CTAs: [sms][16] (value, flag) pairs, all zero between calls.  Returns false when the
+// activation planes of this row length and a useful ring do not fit one CTA; the caller then
+// takes the ring kernel.
+static cudaError_t dispatch_gemvs(const GemvSArgs& a, const GemvSPlan& p, cudaStream_t s) {
+    switch (a.w.bits) {
+        case 2: return launch_gemvs_bits<2>(a, p, s);
+        case 3: return launch_gemvs_bits<3>(a, p, s);
+        case 4: return launch_gemvs_bits<4>(a, p, s);
+        case 5: return launch_gemvs_bits<5>(a, p, s);
+        case 6: return launch_gemvs_bits<6>(a, p, s);
+        case 8: return launch_gemvs_bits<8>(a, p, s);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+#ifdef MFQB_GEMVS_TRACE
+static unsigned long long* g_gemvs_trace = nullptr;
+extern "C" __attribute__((visibility("default"))) void mfqb_debug_set_gemvs_trace(void* p) { g_gemvs_trace = static_cast<unsigned long long*>(p); }
+#endif
+
+size_t gemvs_fix_bytes(int device) { return (size_t)device_sm_count(device) * 16 * sizeof(uint2); }
+
+bool launch_bl_gemvs(const NintDevB& w, const void* x, int x_dtype, void* y, int y_dtype, int device, void* fix, int* error, cudaStream_t s) {
+    if (w.table || !fix) return false;   // lattice records stay on the ring kernel
+    const int sms = device_sm_count(device);
+    const long long total = (long long)w.nrb * w.nchunks;
+    if (total < 1 || total * (sms + 1) >= (1ll << 31)) return false;
+    const int grid = (int)std::min<long long>(sms, total);
+    const size_t recb = (size_t)w.rec_words * 4;
+    const int ngp = w.nchunks * kChunkGroupsB;
+    const size_t planes = (size_t)ngp * 16 + 288 + (size_t)ngp * gemvs_group_bytes(w.t8) + 128;   // group table, maxima, sums | zeros | planes
+    const long long n_b = (total + grid - 1) / grid;
+    GemvSArgs a{};
+    GemvSPlan p;
+    bool found = false;
+    // two CTAs (this product's and the next one's) share an SM when a CTA stays below half of it
+    for (size_t budget : {(size_t)110 * 1024, (size_t)200 * 1024}) {
+        for (int warps : {16, 12, 8, 4}) {
+            if (warps * 32 > gemvs_max_threads(w.wc)) continue;
+            const long long n_w = (n_b + warps - 1) / warps;
+            const int maxseg = (int)((n_w - 1) / w.nchunks) + 2;
+            const size_t fixed = planes + (size_t)warps * maxseg * 64 + 16;
+            if (fixed >= budget) continue;
+            int stages = (int)std::min<size_t>(8, (budget - fixed) / (warps * (recb + 8)));
+            stages = (int)std::min<long long>(stages, std::max<long long>(n_w, 1));
+            const int need = (int)std::min<long long>(warps >= 8 ? 3 : 2, std::max<long long>(n_w, 1));
+            if (stages < need) continue;
+            p.grid = grid;
+            p.threads = warps * 32;
+            p.smem = fixed + (size_t)warps * stages * (recb + 8);
+            a.stages = stages;
+            a.maxseg = maxseg;
+            found = true;
+            break;
+        }
+        if (found) break;
+    }
+    if (!found) return false;
+    a.w = w;
+    a.x = x;
+    a.x_dtype = x_dtype;
+    a.y = y;
+    a.y_dtype = y_dtype;
+    a.fix_slots = static_cast<uint2*>(fix);
+    a.error = error;
+#ifdef MFQB_GEMVS_TRACE
+    a.trace = g_gemvs_trace;
+#endif
+    const cudaError_t e = dispatch_gemvs(a, p, s);
+    if (e != cudaSuccess) fail(MFQB_ERR_CUDA, "NINT%d gs=%d streamed GEMV launch (%d x %d threads, %zu bytes): %s", w.bits, w.gs, p.grid, p.threads, p.smem,
+                               cudaGetErrorString(e));
+    return true;
 }
 
 // Single-row product whose epilogue reduces over ranks (row-parallel shards): see PeerReduce.

@@ -149,6 +149,13 @@ __host__ __device__ constexpr int gemv1_bl_stages(int rec_words) {
 // quads, padded so that the eight groups a warp reads together start in distinct banks.
 __host__ __device__ constexpr int gemv1_bl_qstride(int t8) { return (2 * t8) % 8 == 0 ? 2 * t8 + 1 : 2 * t8; }
 
+// The group scales the kernels multiply integer sums by carry a factor 2^-24, and every output is
+// multiplied by 2^24 once at the end: float(sum) * scale then stays finite for every finite bf16
+// input (a sum reaches 2^23 and a scale 2^113 for magnitudes next to the bf16 maximum).  The price:
+// groups whose largest magnitude is below 2^-88 keep fewer than 16 bits.
+constexpr uint32_t kXScaleShift = 24u;
+constexpr float kXScaleUndo = 16777216.f;   // 2^24
+
 // Quantises groups [g0, g0 + ngroups) of one activation row into shared memory (ngroups a multiple
 // of 8): xq[gl * QS + j] = (low bytes, high bytes) of the four slots 4j..4j+3 of group g0 + gl,
 // gtab[gl] = (sx_g, sx_g * X_g).  Four threads per group; every thread of the CTA must call it.
@@ -184,9 +191,9 @@ __device__ __forceinline__ void stage_x_planes(const __nv_bfloat16* __restrict__
         }
         ab = max(ab, __shfl_xor_sync(0xffffffffu, ab, 1));
         ab = max(ab, __shfl_xor_sync(0xffffffffu, ab, 2));
-        const uint32_t eb = max(ab >> 23, 15u);
+        const uint32_t eb = max(ab >> 23, 15u + kXScaleShift);
         // eb = 255: an infinity or NaN in the group; its scale becomes NaN and so does every output
-        const float sx = __uint_as_float(eb >= 255u ? 0x7FC00000u : (eb - 14u) << 23);
+        const float sx = __uint_as_float(eb >= 255u ? 0x7FC00000u : (eb - 14u - kXScaleShift) << 23);
         const float inv = __uint_as_float((268u - min(eb, 254u)) << 23);
         constexpr float kMagic = 12582912.f;   // 1.5 * 2^23: the low 16 mantissa bits hold round(x * inv) in two's complement
         float xs = 0.f;
@@ -260,8 +267,8 @@ __device__ __forceinline__ void x_chunk_quant(const XChunkRaw<T>& raw, int c, ui
     uint32_t ab = max(m2 & 0xFFFFu, m2 >> 16);
     ab = max(ab, __shfl_xor_sync(0xffffffffu, ab, 1));
     ab = max(ab, __shfl_xor_sync(0xffffffffu, ab, 2));
-    const uint32_t eb = max(ab >> 7, 15u);
-    const float sx = __uint_as_float(eb >= 255u ? 0x7FC00000u : (eb - 14u) << 23);   // NaN for a group holding inf or NaN
+    const uint32_t eb = max(ab >> 7, 15u + kXScaleShift);
+    const float sx = __uint_as_float(eb >= 255u ? 0x7FC00000u : (eb - 14u - kXScaleShift) << 23);   // NaN for a group holding inf or NaN
     const float inv = __uint_as_float((268u - min(eb, 254u)) << 23);
     constexpr float kMagic = 12582912.f;   // 1.5 * 2^23
     uint32_t mine_lo[JJ], mine_hi[JJ];
@@ -463,7 +470,7 @@ __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB
             if (row < row_limit) {
                 float v = ypart[i];
                 for (int cp = 1; cp < ycopies; ++cp) v += ypart[cp * ystride + i];
-                peer_push(pr, seq, row, v);
+                peer_push(pr, seq, row, v * kXScaleUndo);
             }
         }
         for (int i = tid; i < nrb * 16; i += blockDim.x) {
@@ -482,6 +489,7 @@ __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB
         if (row < row_limit) {
             float v = ypart[i];
             for (int cp = 1; cp < ycopies; ++cp) v += ypart[cp * ystride + i];
+            v *= kXScaleUndo;
             if (a.y_dtype == 0 /* MFQB_F32 */) reinterpret_cast<float*>(a.y)[y_off + row] = v;
             else reinterpret_cast<__nv_bfloat16*>(a.y)[y_off + row] = __float2bfloat16_rn(v);
         }

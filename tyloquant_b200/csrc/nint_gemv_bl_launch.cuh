@@ -2,6 +2,7 @@
 // (nint_gemv_bl_b*.cu) instantiates launch_gemv_bl_bits<BITS> so the widths compile in parallel.
 #pragma once
 #include "nint_gemvn_bl.cuh"
+#include "nint_gemvs.cuh"
 
 namespace mfqb {
 
@@ -13,6 +14,40 @@ struct GemvPlanB {
 
 template <int BITS>
 cudaError_t launch_gemv_bl_bits(const GemvArgsB& a, const GemvPlanB& p, cudaStream_t stream);
+
+// Streamed single-row kernel (nint_gemvs.cuh): grid = CTAs (one per SM), threads, dynamic shared memory.
+struct GemvSPlan {
+    int grid = 1, threads = 256;
+    size_t smem = 0;
+};
+template <int BITS>
+cudaError_t launch_gemvs_bits(const GemvSArgs& a, const GemvSPlan& p, cudaStream_t stream);
+
+template <class C>
+static cudaError_t launch_gemvs_codec(const GemvSArgs& a, const GemvSPlan& p, cudaStream_t stream) {
+    auto kernel = gemvs_kernel<C>;
+    // once per kernel and device: allow the largest dynamic shared memory any plan asks for
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)p.grid);
+    cfg.blockDim = dim3((unsigned)p.threads);
+    cfg.dynamicSmemBytes = p.smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, a);
+}
 
 template <typename Kernel>
 static cudaError_t launch_kernel_pdl(Kernel kernel, const GemvArgsB& a, const GemvPlanB& p, cudaStream_t stream) {
@@ -53,6 +88,23 @@ static cudaError_t launch_gemv_bl_one(const GemvArgsB& a, const GemvPlanB& p, cu
     static cudaError_t launch_if_catalog(const GemvArgsB& a, const GemvPlanB& p, cudaStream_t stream) {             \
         if constexpr (nint_bl_in_catalog(BITS, T)) return launch_gemv_bl_one<BITS, T>(a, p, stream);                \
         else return cudaErrorInvalidValue;                                                                          \
+    }                                                                                                               \
+    template <int T>                                                                                                \
+    static cudaError_t launch_s_if_catalog(const GemvSArgs& a, const GemvSPlan& p, cudaStream_t stream) {           \
+        if constexpr (nint_bl_in_catalog(BITS, T)) return launch_gemvs_codec<NintCodec<BITS, T>>(a, p, stream);     \
+        else return cudaErrorInvalidValue;                                                                          \
+    }                                                                                                               \
+    template <>                                                                                                     \
+    cudaError_t launch_gemvs_bits<BITS>(const GemvSArgs& a, const GemvSPlan& p, cudaStream_t stream) {              \
+        switch (a.w.t8) {                                                                                           \
+            case 2: return launch_s_if_catalog<2>(a, p, stream);                                                    \
+            case 3: return launch_s_if_catalog<3>(a, p, stream);                                                    \
+            case 4: return launch_s_if_catalog<4>(a, p, stream);                                                    \
+            case 5: return launch_s_if_catalog<5>(a, p, stream);                                                    \
+            case 6: return launch_s_if_catalog<6>(a, p, stream);                                                    \
+            case 8: return launch_s_if_catalog<8>(a, p, stream);                                                    \
+            default: return cudaErrorInvalidValue;                                                                  \
+        }                                                                                                           \
     }                                                                                                               \
     template <>                                                                                                     \
     cudaError_t launch_gemv_bl_bits<BITS>(const GemvArgsB& a, const GemvPlanB& p, cudaStream_t stream) {            \

@@ -223,7 +223,7 @@ __device__ __forceinline__ void gemvn_bl_body(const GemvArgsB& a, const NintDevB
         const int m = i / (nrb * 16), j = i % (nrb * 16);
         const int row = rbl0 * 16 + j;   // row inside the problem (matrix, or the tile's expert)
         if (row < row_limit) {
-            const float v = ypart[(size_t)m * ystride + j];
+            const float v = ypart[(size_t)m * ystride + j] * kXScaleUndo;
             const size_t off = (size_t)row_dst[m] * a.ldy + row;
             if (a.y_dtype == 0 /* MFQB_F32 */) reinterpret_cast<float*>(a.y)[off] = v;
             else reinterpret_cast<__nv_bfloat16*>(a.y)[off] = __float2bfloat16_rn(v);

@@ -18,6 +18,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // returns false (the caller records the failure and leaves).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = 1u << 22) {
     const uint32_t addr = smem_u32(bar);
+#pragma unroll 1
     for (uint32_t it = 0; it < limit; ++it) {
         uint32_t done;
         asm volatile(

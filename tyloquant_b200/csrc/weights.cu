@@ -4,6 +4,8 @@
 #include <algorithm>
 #include <memory>
 #include <mutex>
+#include <utility>
+#include <vector>
 
 #include "cuda_util.h"
 #include "nint_gemm_tc.cuh"
@@ -26,27 +28,48 @@ int device_sm_count(int device) {
     return cache[device];
 }
 
+void* GrowOnlyScratch::get(int device, size_t bytes, cudaStream_t stream, const char* what) {
+    static std::mutex mu;   // one lock for every pool: growth is rare
+    std::lock_guard<std::mutex> lock(mu);
+    if (device < 0 || device >= 64) fail(MFQB_ERR_ARG, "device index %d out of range", device);
+    PerDevice& d = dev_[device];
+    if (d.bytes >= bytes) return d.p;
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &st) != cudaSuccess) (void)cudaGetLastError();
+    if (st != cudaStreamCaptureStatusNone)
+        fail(MFQB_ERR_ARG,
+             "%s needs %zu bytes of library scratch (it holds %zu) while the stream is being captured: "
+             "run one call of this size outside the capture first",
+             what, bytes, d.bytes);
+    void* p = nullptr;
+    const size_t want = bytes + bytes / 2;
+    MFQB_CUDA(cudaMalloc(&p, want));
+    d.p = p;   // the previous block stays allocated: earlier launches and captured graphs may still use it
+    d.bytes = want;
+    return p;
+}
+
 // ---- tcgen05 prefill GEMM: x conversion pre-pass, per-device scratch and status word -----------
 __global__ void x_to_f16_kernel(const __nv_bfloat16* __restrict__ x, int m, int k, int kx, __half* __restrict__ out) {
     const size_t total = (size_t)m * kx;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t r = i / kx, c = i % kx;
-        // bf16 -> f16: exact for |x| in [2^-14, 65504]; larger magnitudes saturate to +-65504
-        float v = c < (size_t)k ? __bfloat162float(x[r * k + c]) : 0.f;
-        v = fminf(fmaxf(v, -65504.f), 65504.f);
-        out[i] = __float2half_rn(v);
+        // bf16 -> f16: exact for |x| in [2^-14, 65504]; larger finite magnitudes saturate to +-65504;
+        // an infinity or NaN stays non-finite (NaN), so it poisons the outputs as on the integer kernels
+        const float v = c < (size_t)k ? __bfloat162float(x[r * k + c]) : 0.f;
+        out[i] = isfinite(v) ? __float2half_rn(fminf(fmaxf(v, -65504.f), 65504.f)) : __ushort_as_half((unsigned short)0x7E00);
     }
 }
 
 struct GemmDeviceState {
     std::mutex mu;
-    DevBuf x16[64];
+    GrowOnlyScratch x16;
     int* status_host[64] = {nullptr};
     int* status_dev[64] = {nullptr};
 };
 static GemmDeviceState g_gemm;
 
-static int* gemm_status_word(int device) {   // pinned, mapped: the host can read it without a sync
+int* gemm_status_word(int device) {   // pinned, mapped: the host can read it without a sync
     if (!g_gemm.status_host[device]) {
         MFQB_CUDA(cudaHostAlloc((void**)&g_gemm.status_host[device], sizeof(int), cudaHostAllocMapped));
         *g_gemm.status_host[device] = 0;
@@ -82,6 +105,11 @@ static CUtensorMap make_x_map(const void* x16, int m, int kx, int bn) {
 }
 
 // Returns false when this weight has no tensor-core tile kernel (the caller falls back to GEMV passes).
+int* device_status_word(int device) {
+    std::lock_guard<std::mutex> lock(g_gemm.mu);
+    return gemm_status_word(device);
+}
+
 static bool launch_nint_gemm(const NintDevB& w, const void* x, int m, void* y, int y_dtype, int device, cudaStream_t s) {
     const GemmPlan p = plan_nint_gemm(w, m);
     if (p.bn == 0) return false;
@@ -96,15 +124,13 @@ static bool launch_nint_gemm(const NintDevB& w, const void* x, int m, void* y, i
     a.stages = p.stages;
     a.xstages = p.xstages;
     a.error = gemm_status_word(device);
-    DevBuf& xb = g_gemm.x16[device];
-    const size_t need = (size_t)m * a.kx * sizeof(__half);
-    if (xb.bytes < need) xb.alloc(need + need / 2);
-    a.x16 = static_cast<const __half*>(xb.p);
+    void* xb = g_gemm.x16.get(device, (size_t)m * a.kx * sizeof(__half), s, "mfqb_mul_mat (f16 copy of the activations)");
+    a.x16 = static_cast<const __half*>(xb);
     const size_t total = (size_t)m * a.kx;
     x_to_f16_kernel<<<(int)std::min<size_t>((total + 255) / 256, 148 * 8), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), m, w.k,
-                                                                                      a.kx, static_cast<__half*>(xb.p));
+                                                                                      a.kx, static_cast<__half*>(xb));
     MFQB_CUDA(cudaGetLastError());
-    const CUtensorMap x_map = make_x_map(xb.p, m, a.kx, p.bn);
+    const CUtensorMap x_map = make_x_map(xb, m, a.kx, p.bn);
     cudaError_t e;
     switch (w.bits) {
         case 2: e = launch_nint_gemm_bits<2>(a, p, x_map, s); break;
@@ -127,9 +153,8 @@ __global__ void x_gather_f16_kernel(const __nv_bfloat16* __restrict__ x, const i
     const size_t total = (size_t)pairs * kx;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t p = i / kx, c = i % kx;
-        float v = c < (size_t)k ? __bfloat162float(x[(size_t)(pair_order[p] / div) * k + c]) : 0.f;
-        v = fminf(fmaxf(v, -65504.f), 65504.f);
-        out[i] = __float2half_rn(v);
+        const float v = c < (size_t)k ? __bfloat162float(x[(size_t)(pair_order[p] / div) * k + c]) : 0.f;
+        out[i] = isfinite(v) ? __float2half_rn(fminf(fmaxf(v, -65504.f), 65504.f)) : __ushort_as_half((unsigned short)0x7E00);
     }
 }
 
@@ -203,6 +228,8 @@ namespace mfqb {
 void launch_nint_bl_dequant(const NintDevB& w, void* out, int out_dtype, cudaStream_t s);
 void launch_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtype, int ldy, int device, cudaStream_t s);
 bool nint_bl_supported(int bits, int gs);
+size_t gemvs_fix_bytes(int device);
+bool launch_bl_gemvs(const NintDevB& w, const void* x, int x_dtype, void* y, int y_dtype, int device, void* fix, int* error, cudaStream_t s);
 }
 
 struct mfqb_weight {
@@ -210,6 +237,8 @@ struct mfqb_weight {
     mfqb_weight_info info{};
     NintDevB nint{};
     DevBuf items, anchors;
+    DevBuf fix;          // streamed single-row kernel: partial rows of row-blocks shared by two CTAs, and their counters
+    int* status = nullptr;   // the device's host-visible status word
     NvqDevicePtr nvq;
 };
 
@@ -234,6 +263,9 @@ static mfqb_weight* make_nint_weight(const HostNint& t, int device) {
     w->device = device;
     w->items.upload(p.items.data(), p.items.size() * 4);
     w->anchors.upload(p.anchors.data(), p.anchors.size() * 4);
+    w->fix.alloc(gemvs_fix_bytes(device));
+    MFQB_CUDA(cudaMemset(w->fix.p, 0, w->fix.bytes));
+    w->status = device_status_word(device);
     w->nint = p.d;
     w->nint.items = static_cast<const uint32_t*>(w->items.p);
     w->nint.anchors = static_cast<const uint32_t*>(w->anchors.p);
@@ -323,6 +355,7 @@ int mfqb_mul_mat(const mfqb_weight* w, const void* x, int m, void* y, int y_dtyp
         if (w->family == MFQB_FAMILY_NINT) {
             // more than 16 rows: tensor-core tile kernel (x conversion buffer is library scratch)
             if (m > 16 && launch_nint_gemm(w->nint, x, m, y, y_dtype, w->device, stream)) return;
+            if (m == 1 && launch_bl_gemvs(w->nint, x, MFQB_BF16, y, y_dtype, w->device, w->fix.p, w->status, stream)) return;
             for (int m0 = 0; m0 < m; m0 += 8) {   // batch rows one GEMV launch covers
                 const int mm = std::min(8, m - m0);
                 launch_bl_gemv(w->nint, static_cast<const char*>(x) + (size_t)m0 * k * 2, mm,
@@ -343,48 +376,94 @@ __global__ void host_to_device_words_kernel(const uint32_t* __restrict__ src, ui
 // demand and are then reused, so a call costs two copies, the kernel and one synchronisation.
 namespace {
 struct HostCallState {
-    std::mutex mu;
+    std::mutex mu[64];
     cudaStream_t stream[64] = {nullptr};
+    cudaEvent_t done[64] = {nullptr};
     DevBuf x[64], y[64];
 };
 HostCallState g_host_call;
 }  // namespace
 
+// Host-buffer products: `count` weights of one device, each with its own x and y in host memory.
+// Everything is enqueued on the device's staging stream and the call waits once, at the end.
+static void mul_mat_host_impl(const mfqb_weight* const* ws, int count, const void* const* xs, int m, void* const* ys, int y_dtype) {
+    const mfqb_weight* w0 = ws[0];
+    if (w0->device < 0 || w0->device >= 64) fail(MFQB_ERR_ARG, "device index %d out of range", w0->device);
+    const int device = w0->device;
+    DeviceGuard guard(device);
+    const size_t ysz = y_dtype == MFQB_F32 ? 4 : 2;
+    size_t x_total = 0, y_total = 0;
+    for (int i = 0; i < count; ++i) {
+        if (!ws[i] || !xs[i] || !ys[i]) fail(MFQB_ERR_ARG, "mfqb_mul_mat_host: null argument");
+        if (ws[i]->device != device) fail(MFQB_ERR_ARG, "mfqb_mul_mat_host_multi: weights live on different devices");
+        x_total += ((size_t)m * ws[i]->info.k * 2 + 255) / 256 * 256;
+        y_total += ((size_t)m * ws[i]->info.n * ysz + 255) / 256 * 256;
+    }
+    std::lock_guard<std::mutex> lock(g_host_call.mu[device]);   // per device: calls on different GPUs do not serialise
+    cudaStream_t& s = g_host_call.stream[device];
+    if (!s) MFQB_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    cudaEvent_t& ev = g_host_call.done[device];
+    if (!ev) MFQB_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    DevBuf& dx = g_host_call.x[device];
+    DevBuf& dy = g_host_call.y[device];
+    if (dx.bytes < x_total) dx.alloc(x_total + x_total / 2);   // nothing of this stream is in flight between calls
+    size_t x_off = 0, y_off = 0;
+    bool any_copy_back = false;
+    // Pinned, mapped host buffers (cudaHostAlloc / cudaHostRegister, which is what a caller that
+    // cares about latency passes): a small kernel pulls x over PCIe into the staging buffer and the
+    // product kernel writes y straight into host memory -- no copy-engine round trips.  Pageable
+    // buffers take the two cudaMemcpyAsync.
+    std::vector<std::pair<size_t, int>> copy_back;   // (offset in dy, index)
+    for (int i = 0; i < count; ++i) {
+        const size_t xb = (size_t)m * ws[i]->info.k * 2, yb = (size_t)m * ws[i]->info.n * ysz;
+        void *x_map = nullptr, *y_map = nullptr;
+        const bool mapped = (xb % 4 == 0) && (reinterpret_cast<uintptr_t>(xs[i]) % 4 == 0) &&
+                            cudaHostGetDevicePointer(&x_map, const_cast<void*>(xs[i]), 0) == cudaSuccess &&
+                            cudaHostGetDevicePointer(&y_map, ys[i], 0) == cudaSuccess;
+        if (!mapped) (void)cudaGetLastError();   // not an error: the buffers are simply pageable
+        char* xd = static_cast<char*>(dx.p) + x_off;
+        if (mapped) {
+            const size_t words = xb / 4;
+            host_to_device_words_kernel<<<(unsigned)std::min<size_t>((words + 255) / 256, 64), 256, 0, s>>>(
+                static_cast<const uint32_t*>(x_map), reinterpret_cast<uint32_t*>(xd), words);
+            MFQB_CUDA(cudaGetLastError());
+        } else {
+            MFQB_CUDA(cudaMemcpyAsync(xd, xs[i], xb, cudaMemcpyHostToDevice, s));
+            if (!any_copy_back && dy.bytes < y_total) dy.alloc(y_total + y_total / 2);
+            any_copy_back = true;
+            copy_back.emplace_back(y_off, i);
+        }
+        void* yd = mapped ? y_map : static_cast<void*>(static_cast<char*>(dy.p) + y_off);
+        const int rc = mfqb_mul_mat(ws[i], xd, m, yd, y_dtype, s);
+        if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
+        x_off += (xb + 255) / 256 * 256;
+        y_off += (yb + 255) / 256 * 256;
+    }
+    for (const auto& cb : copy_back)
+        MFQB_CUDA(cudaMemcpyAsync(ys[cb.second], static_cast<char*>(dy.p) + cb.first, (size_t)m * ws[cb.second]->info.n * ysz,
+                                  cudaMemcpyDeviceToHost, s));
+    // wait by polling an event: the answer comes back a few microseconds sooner than through a blocking synchronise
+    MFQB_CUDA(cudaEventRecord(ev, s));
+    for (;;) {
+        const cudaError_t q = cudaEventQuery(ev);
+        if (q == cudaSuccess) break;
+        if (q != cudaErrorNotReady) MFQB_CUDA(q);
+    }
+}
+
 int mfqb_mul_mat_host(const mfqb_weight* w, const void* x_host, int m, void* y_host, int y_dtype) {
     return guarded([&] {
         if (!w || !x_host || !y_host) fail(MFQB_ERR_ARG, "mfqb_mul_mat_host: null argument");
         if (m < 1) fail(MFQB_ERR_ARG, "mfqb_mul_mat_host: m must be >= 1");
-        if (w->device < 0 || w->device >= 64) fail(MFQB_ERR_ARG, "device index %d out of range", w->device);
-        DeviceGuard guard(w->device);
-        const size_t xb = (size_t)m * w->info.k * 2, yb = (size_t)m * w->info.n * (y_dtype == MFQB_F32 ? 4 : 2);
-        std::lock_guard<std::mutex> lock(g_host_call.mu);
-        cudaStream_t& s = g_host_call.stream[w->device];
-        if (!s) MFQB_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
-        DevBuf& dx = g_host_call.x[w->device];
-        DevBuf& dy = g_host_call.y[w->device];
-        if (dx.bytes < xb) dx.alloc(xb + xb / 2);
-        if (dy.bytes < yb) dy.alloc(yb + yb / 2);
-        // Pinned, mapped host buffers (cudaHostAlloc / cudaHostRegister, which is what a caller that
-        // cares about latency passes): a small kernel pulls x over PCIe into the staging buffer and the
-        // product kernel writes y straight into host memory -- no copy-engine round trips.  Pageable
-        // buffers take the two cudaMemcpyAsync.
-        void *x_map = nullptr, *y_map = nullptr;
-        const bool mapped = (xb % 4 == 0) && (reinterpret_cast<uintptr_t>(x_host) % 4 == 0) &&
-                            cudaHostGetDevicePointer(&x_map, const_cast<void*>(x_host), 0) == cudaSuccess &&
-                            cudaHostGetDevicePointer(&y_map, y_host, 0) == cudaSuccess;
-        if (!mapped) (void)cudaGetLastError();   // not an error: the buffers are simply pageable
-        if (mapped) {
-            const size_t words = xb / 4;
-            host_to_device_words_kernel<<<(unsigned)std::min<size_t>((words + 255) / 256, 64), 256, 0, s>>>(
-                static_cast<const uint32_t*>(x_map), static_cast<uint32_t*>(dx.p), words);
-            MFQB_CUDA(cudaGetLastError());
-        } else {
-            MFQB_CUDA(cudaMemcpyAsync(dx.p, x_host, xb, cudaMemcpyHostToDevice, s));
-        }
-        const int rc = mfqb_mul_mat(w, dx.p, m, mapped ? y_map : dy.p, y_dtype, s);
-        if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
-        if (!mapped) MFQB_CUDA(cudaMemcpyAsync(y_host, dy.p, yb, cudaMemcpyDeviceToHost, s));
-        MFQB_CUDA(cudaStreamSynchronize(s));
+        mul_mat_host_impl(&w, 1, &x_host, m, &y_host, y_dtype);
+    });
+}
+
+int mfqb_mul_mat_host_multi(const mfqb_weight* const* ws, int count, const void* const* xs_host, int m, void* const* ys_host, int y_dtype) {
+    return guarded([&] {
+        if (!ws || !xs_host || !ys_host) fail(MFQB_ERR_ARG, "mfqb_mul_mat_host_multi: null argument");
+        if (count < 1 || m < 1) fail(MFQB_ERR_ARG, "mfqb_mul_mat_host_multi: count and m must be >= 1");
+        mul_mat_host_impl(ws, count, xs_host, m, ys_host, y_dtype);
     });
 }
 

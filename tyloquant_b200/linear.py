@@ -55,8 +55,9 @@ class QuantWeight:
         check(lib.mfqb_dequant(self._h, out.data_ptr(), F32 if tdt == torch.float32 else BF16, _stream_ptr(self.device)))
         return out
 
-    def matmul(self, x, out_dtype=None):
-        """``y = x @ W.T`` for a bf16 CUDA tensor ``x`` of shape [m, k] (or [k])."""
+    def matmul(self, x, out_dtype=None, out=None):
+        """``y = x @ W.T`` for a bf16 CUDA tensor ``x`` of shape [m, k] (or [k]); ``out``: an
+        existing [m, n] float32 or bfloat16 tensor to write (graph capture wants fixed buffers)."""
         torch = _torch()
         squeeze = x.dim() == 1
         x2 = x.reshape(1, -1) if squeeze else x
@@ -65,8 +66,10 @@ class QuantWeight:
         if x2.shape[-1] != self.k:
             raise ValueError(f"x has {x2.shape[-1]} columns, the weight has k={self.k}")
         x2 = x2.contiguous()
-        tdt = out_dtype or torch.bfloat16
-        y = torch.empty((x2.shape[0], self.n), dtype=tdt, device=x2.device)
+        tdt = out.dtype if out is not None else (out_dtype or torch.bfloat16)
+        y = out if out is not None else torch.empty((x2.shape[0], self.n), dtype=tdt, device=x2.device)
+        if y.shape != (x2.shape[0], self.n) or not y.is_contiguous():
+            raise ValueError("out must be a contiguous [m, n] tensor")
         check(lib.mfqb_mul_mat(self._h, x2.data_ptr(), x2.shape[0], y.data_ptr(),
                                F32 if tdt == torch.float32 else BF16, _stream_ptr(self.device)))
         return y[0] if squeeze else y
