@@ -28,6 +28,10 @@ import sys
 import threading
 import time
 
+if "reference" in sys.argv:   # torchrun exports OMP_NUM_THREADS=1; the CPU arm may use every host core (set before numpy loads its BLAS)
+    for _v in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+        os.environ[_v] = str(os.cpu_count() or 1)
+
 import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -179,6 +183,7 @@ def main() -> None:
     ap.add_argument("--only", default=None, help="run one sweep case by name with a few plain launches "
                     "(small, for profilers) and print its line")
     ap.add_argument("--reps", type=int, default=3, help="launch rounds for --only")
+    ap.add_argument("--gemv1-kernel", type=int, default=0, help="mfqb_tune gemv1_kernel: 0 by shape, 1 ring kernel, 2 streamed kernel")
     ap.add_argument("--match", default=None, help="with --only sweep: run the cases whose name contains this text")
     ap.add_argument("--tokens", type=int, nargs="*", default=None, help="token counts for --only moe")
     ap.add_argument("--no-parallel", action="store_true",
@@ -198,9 +203,15 @@ def main() -> None:
         pk = measured_peaks()[0]
         print(json.dumps(gemm_bench(local_rank, pk.get("bf16_tflops_sustained", pk["bf16_tflops"]))))
         return
+    if args.only == "decoder":
+        print(json.dumps({"decoder_cfg5": decoder_bench(local_rank, 0, 1, None)}))
+        return
     if args.only == "moe":
         print(json.dumps(moe_layer_bench(local_rank, measured_peaks()[0]["hbm_gbs"], token_counts=tuple(args.tokens or (1, 8, 32, 64, 128, 256, 1024)))))
         return
+    if args.impl != "reference" and args.gemv1_kernel:
+        from tyloquant_b200._capi import check as _check, lib as _lib
+        _check(_lib.mfqb_tune(b"gemv1_kernel", args.gemv1_kernel))
     if args.only == "sweep":   # every sweep case, graph-timed, nothing else
         print(json.dumps({"sweep": sweep(local_rank, measured_peaks()[0]["hbm_gbs"], match=args.match)}))
         return
@@ -340,6 +351,7 @@ def main() -> None:
 
     tp = tp_rowparallel_bench(dev, rank, world, dist) if dist is not None and not args.no_parallel else None
     ep = ep_moe_bench(dev, rank, world, dist) if dist is not None and not args.no_parallel else None
+    dc = decoder_bench(dev, rank, world, dist) if not args.no_sweep and not (dist is not None and args.no_parallel) else None
 
     if rank != 0:
         if dist is not None:
@@ -371,6 +383,8 @@ def main() -> None:
         line["tp_rowparallel"] = tp
     if ep is not None:
         line["ep_moe_cfg4"] = ep
+    if dc is not None:
+        line["decoder_cfg5"] = dc
     if args.gpus == 1:
         cb, _ = cpu_reference_arm(3, 3, budget_s=12.0)
         line["cpu_baseline"] = cb
@@ -520,13 +534,16 @@ def tp_rowparallel_bench(dev: int, rank: int, world: int, dist, iters: int = 200
         from tyloquant_b200._capi import F32, check, lib
         sp = 0
         res = {}
-        for mode in ("fused", "product_then_allreduce"):
+        for mode in ("fused", "product_then_allreduce", "product_then_nccl"):
             def call(w):   # straight C-ABI calls on the capture stream `sp`
                 if mode == "fused":
                     check(lib.mfqb_mul_mat_allreduce(w._h, x.data_ptr(), 1, c._h, y.data_ptr(), F32, sp))
-                else:
+                elif mode == "product_then_allreduce":
                     check(lib.mfqb_mul_mat(w._h, x.data_ptr(), 1, part.data_ptr(), F32, sp))
                     check(lib.mfqb_allreduce_f32(c._h, part.data_ptr(), y.data_ptr(), n, sp))
+                else:   # what the reference does: float32 ncclAllReduce in place after the product
+                    check(lib.mfqb_mul_mat(w._h, x.data_ptr(), 1, part.data_ptr(), F32, sp))
+                    dist.all_reduce(part)
             # the sequence numbers of the collective live on the device, so the calls replay from a graph
             stream = torch.cuda.Stream(device=dev)
             with torch.cuda.stream(stream):
@@ -622,6 +639,73 @@ def ep_moe_bench(dev: int, rank: int, world: int, dist, token_counts=(1, 32, 256
     c.close()
     gu.free()
     dn.free()
+    return out
+
+
+def decoder_bench(dev: int, rank: int, world: int, dist, batches=(1, 16), steps: int = 24) -> dict:
+    """BASELINE config 5: random-init 32-layer dense decoder (hidden 4096, 32 query / 8 KV heads of
+    128, FFN 14336 SwiGLU, vocabulary 128256, RMSNorm, rotary embedding), attention projections NINT4
+    (4, 24, 6), FFN and lm_head NINT6 (6, 24, 7), bf16 KV cache holding a 4096-token context, greedy
+    decode at batch 1 and 16.  With world > 1 the model is tensor-parallel over the ranks (heads, FFN
+    columns and vocabulary sharded; the two row-parallel products of a layer end in the NVLink
+    reduction).  Two steps are captured in one CUDA graph and replayed; tokens/s is for the whole job.
+    The cache is filled with seeded values instead of running a prefill (only its size matters here)."""
+    import torch
+
+    from tyloquant_b200 import comm as commod, decoder as D
+
+    d = f"cuda:{dev}"
+    ctx = 4096
+    cfg = dict(hidden=4096, n_q_heads=32, n_kv_heads=8, ffn=14336, vocab=128256, layers=32,
+               max_ctx=ctx + 2 * steps + 8, max_batch=max(batches))
+    c = commod.Communicator(rank, world, max(batches) * cfg["hidden"], dev).connect() if world > 1 else None
+    dec, _ = D.random_decoder(**cfg, rank=rank, world=world, comm=c, device=dev, seed=5000)
+    wbytes = sum(w.payload_bytes for w in dec._keep if hasattr(w, "payload_bytes"))
+    kv_bytes_per_seq = 2 * cfg["layers"] * (cfg["n_kv_heads"] // world) * ctx * 128 * 2
+    out = {"weight_payload_GB_per_rank": wbytes / 1e9, "kv_GB_per_sequence_per_rank": kv_bytes_per_seq / 1e9,
+           "context": ctx, "tensor_parallel": world}
+    peak = measured_peaks()[0]["hbm_gbs"]
+    for b in batches:
+        dec.fill_cache(ctx, seed=5001)
+        ids = torch.randint(0, cfg["vocab"], (b,), device=d, generator=torch.Generator(d).manual_seed(5002), dtype=torch.int32)
+        a, b2 = ids.clone(), torch.empty_like(ids)
+        stream = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(stream):
+            dec.step(a, b2)                      # warm-up outside the capture, then rewind the cache position
+            stream.synchronize()
+            dec.fill_cache(ctx, seed=5001)
+            if dist is not None:
+                dist.barrier()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                dec.step(a, b2)
+                dec.step(b2, a)
+            g.replay()                           # one untimed replay (positions ctx, ctx + 1)
+            stream.synchronize()
+            if dist is not None:
+                dist.barrier()
+            reps = max(1, steps // 2 - 1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(reps):
+                g.replay()
+            e1.record(stream)
+            stream.synchronize()
+        ms = e0.elapsed_time(e1) / (2 * reps)
+        if dist is not None:
+            t = torch.tensor([ms], device=d)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        step_bytes = wbytes + b * kv_bytes_per_seq   # per rank: every weight once, every sequence's cache once
+        out[f"batch{b}"] = {"ms_per_step": ms, "tokens_per_s": b / ms * 1e3, "GBps_per_rank": step_bytes / ms / 1e6,
+                            "frac_of_hbm_peak": step_bytes / ms / 1e6 / peak,
+                            "tokens_per_s_ceiling_at_peak": b / (step_bytes / (peak * 1e9)) }
+    if c is not None:
+        out["comm_status"] = c.status()
+        dist.barrier()
+    dec.free()
+    if c is not None:
+        c.close()
     return out
 
 

@@ -96,6 +96,9 @@ int mfqb_weight_from_blob(const char* dtype, const void* blob, uint64_t nbytes, 
 int mfqb_weight_from_blob_slice(const char* dtype, const void* blob, uint64_t nbytes, int axis,
                                 int64_t begin, int64_t end, int device, mfqb_weight** out);
 int mfqb_weight_info_get(const mfqb_weight* w, mfqb_weight_info* info);
+/* A second handle with its own device copy of the same weight, on the same device (device-to-device
+ * copy: the host-side re-layout is not repeated).  No counterpart in the reference. */
+int mfqb_weight_clone(const mfqb_weight* w, mfqb_weight** out);
 int mfqb_weight_free(mfqb_weight* w);
 
 /* Reference decoder on the GPU: writes the [n, k] row-major dequantized tensor.
@@ -126,6 +129,12 @@ int mfqb_dequant(const mfqb_weight* w, void* out, int out_dtype, mfqb_stream_t s
  * (cpp_runtime/mfq_decode.cpp:8130-8315, 7884-7932, 9209). */
 int mfqb_mul_mat(const mfqb_weight* w, const void* x_bf16, int m, void* y, int y_dtype,
                  mfqb_stream_t stream);
+
+/* Tuning switches, for measurements.  "gemv1_kernel": which kernel a single-row product of a plain
+ * NINT weight takes -- 0 by shape (default), 1 the per-warp ring kernel, 2 the streamed kernel.
+ * No counterpart in the reference (its switches are MFQ_* environment variables,
+ * docs/developer-architecture-and-operator-reference.md:1048-1078). */
+int mfqb_tune(const char* key, int value);
 
 /* Status word of the device-side bounded waits of the tile kernel on `device`: 0, or
  * MFQB_ERR_TIMEOUT when a wait inside a kernel ran out (the kernel then returned early and
@@ -313,6 +322,51 @@ int mfqb_comm_destroy(mfqb_comm* c);
 int mfqb_moe_ffn_static(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* down, const void* x_bf16,
                         const int32_t* ids, const float* weights, int tokens, int routes, void* y,
                         int y_dtype, mfqb_stream_t stream);
+
+/* ---------------------------------------------------------------------------------
+ * Dense decoder step: the runtime layer around the packed-weight products.  Stands in for
+ * QuantLinear / FFN / FullBlock::forward / Model::next_token of the reference runtime
+ * (cpp_runtime/mfq_decode.cpp:9116-9407, 10456-10602, 12210-12400, 13993-14145) for one model
+ * family: Llama-shaped blocks (RMSNorm, rotary embedding with the halves convention, grouped-query
+ * attention over a bf16 KV cache, SwiGLU FFN), greedy decoding.  The projections are weight handles
+ * of this library, borrowed for the decoder's lifetime; q|k|v and gate|up are single fused handles.
+ * With world > 1 every rank holds n_q/world query heads, n_kv/world KV heads (and their cache),
+ * ffn/world FFN columns and a slice of the vocabulary; o_proj and down_proj hold the matching input
+ * slices and end in a sum over the ranks of `comm`.
+ * --------------------------------------------------------------------------------- */
+typedef struct mfqb_decoder mfqb_decoder;
+typedef struct mfqb_decoder_config {
+    int hidden, n_q_heads, n_kv_heads, head_dim; /* head_dim must be 128; hidden = n_q_heads * 128 */
+    int ffn, vocab, layers;
+    int max_ctx, max_batch;
+    float rope_theta, rms_eps;
+} mfqb_decoder_config;
+int mfqb_decoder_create(const mfqb_decoder_config* cfg, int rank, int world, mfqb_comm* comm, int device,
+                        mfqb_decoder** out);
+/* This rank's shapes: qkv [(n_q + 2 n_kv)/world * 128, hidden] (query rows, key rows, value rows);
+ * o [hidden, n_q/world * 128]; gate_up [2 * ffn/world, hidden] (gate rows first); down [hidden, ffn/world]. */
+int mfqb_decoder_set_layer(mfqb_decoder* d, int layer, const mfqb_weight* qkv, const mfqb_weight* o,
+                           const mfqb_weight* gate_up, const mfqb_weight* down);
+/* lm_head: rows [begin, begin + rows) of the vocabulary (mfqb_decoder_vocab_shard) x hidden;
+ * embedding: bf16 [vocab, hidden] in device memory (replicated). */
+int mfqb_decoder_vocab_shard(const mfqb_decoder* d, int* begin, int* rows);
+int mfqb_decoder_set_head(mfqb_decoder* d, const mfqb_weight* lm_head, const void* embedding_bf16);
+/* Fills the first ctx_len cache positions of every sequence with seeded values of unit scale (a
+ * stand-in for the prefill pass, which is outside this path) and sets every position to ctx_len. */
+int mfqb_decoder_fill_cache(mfqb_decoder* d, int ctx_len, unsigned seed, mfqb_stream_t stream);
+/* One greedy step for `batch` sequences: ids_in [batch] -> ids_out [batch] (device int32), positions
+ * advance by one.  All device work goes to `stream`; the call can be captured in a CUDA graph after
+ * one warm-up call (library scratch, see mfqb_mul_mat). */
+int mfqb_decoder_step(mfqb_decoder* d, const int32_t* ids_in, int batch, int32_t* ids_out,
+                      mfqb_stream_t stream);
+/* Parity hooks: one block on a given residual stream (float32 [rows, hidden] in and out, cache
+ * positions as currently set, the step's key/value rows are written); and a read-back of one
+ * sequence's cache rows, which = 0 keys / 1 values, as bf16 [n_kv/world][ctx][128]. */
+int mfqb_decoder_layer(mfqb_decoder* d, int layer, const float* h_in, int rows, float* h_out,
+                       mfqb_stream_t stream);
+int mfqb_decoder_read_cache(const mfqb_decoder* d, int layer, int row, int which, int ctx, void* out_bf16,
+                            mfqb_stream_t stream);
+int mfqb_decoder_free(mfqb_decoder* d);
 
 /* ---------------------------------------------------------------------------------
  * Host-side self-check of the device layout (no GPU): packs the blob into the device

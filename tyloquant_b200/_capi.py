@@ -32,6 +32,12 @@ class WeightInfo(C.Structure):
                 ("payload_bytes", C.c_uint64), ("device_bytes", C.c_uint64)]
 
 
+class DecoderConfig(C.Structure):
+    _fields_ = [("hidden", C.c_int), ("n_q_heads", C.c_int), ("n_kv_heads", C.c_int), ("head_dim", C.c_int),
+                ("ffn", C.c_int), ("vocab", C.c_int), ("layers", C.c_int), ("max_ctx", C.c_int), ("max_batch", C.c_int),
+                ("rope_theta", C.c_float), ("rms_eps", C.c_float)]
+
+
 class MoeInfo(C.Structure):
     _fields_ = [("n_experts", C.c_int), ("out_per_expert", C.c_int), ("k", C.c_int), ("expert_begin", C.c_int),
                 ("expert_end", C.c_int), ("n_pools", C.c_int), ("device", C.c_int), ("payload_bytes", C.c_uint64),
@@ -66,6 +72,17 @@ _SIGNATURES = {
     "mfqb_dequant": (_i, [_vp, _vp, _i, _vp]),
     "mfqb_mul_mat": (_i, [_vp, _vp, _i, _vp, _i, _vp]),
     "mfqb_device_status": (_i, [_i, _P(_i)]),
+    "mfqb_tune": (_i, [_cp, _i]),
+    "mfqb_weight_clone": (_i, [_vp, _P(_vp)]),
+    "mfqb_decoder_create": (_i, [_vp, _i, _i, _vp, _i, _P(_vp)]),
+    "mfqb_decoder_set_layer": (_i, [_vp, _i, _vp, _vp, _vp, _vp]),
+    "mfqb_decoder_vocab_shard": (_i, [_vp, _P(_i), _P(_i)]),
+    "mfqb_decoder_set_head": (_i, [_vp, _vp, _vp]),
+    "mfqb_decoder_fill_cache": (_i, [_vp, _i, C.c_uint, _vp]),
+    "mfqb_decoder_step": (_i, [_vp, _vp, _i, _vp, _vp]),
+    "mfqb_decoder_layer": (_i, [_vp, _i, _vp, _i, _vp, _vp]),
+    "mfqb_decoder_read_cache": (_i, [_vp, _i, _i, _i, _i, _vp, _vp]),
+    "mfqb_decoder_free": (_i, [_vp]),
     "mfqb_mul_mat_host": (_i, [_vp, _vp, _i, _vp, _i]),
     "mfqb_mul_mat_host_multi": (_i, [_P(_vp), _i, _P(_vp), _i, _P(_vp), _i]),
     "mfqb_tp_plan": (_i, [_i64, _i64, _i, _P(C.c_double), _P(_i64), _P(_i64)]),

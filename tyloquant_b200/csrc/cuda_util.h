@@ -36,6 +36,10 @@ struct DevBuf {
     DevBuf() = default;
     DevBuf(const DevBuf&) = delete;
     DevBuf& operator=(const DevBuf&) = delete;
+    DevBuf(DevBuf&& o) noexcept : p(o.p), bytes(o.bytes) {
+        o.p = nullptr;
+        o.bytes = 0;
+    }
     void alloc(size_t n) {
         release();
         if (n) MFQB_CUDA(cudaMalloc(&p, n));

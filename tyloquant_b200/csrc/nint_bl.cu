@@ -226,7 +226,7 @@ extern "C" __attribute__((visibility("default"))) void mfqb_debug_set_gemvs_trac
 size_t gemvs_fix_bytes(int device) { return (size_t)device_sm_count(device) * 16 * sizeof(uint2); }
 
 bool launch_bl_gemvs(const NintDevB& w, const void* x, int x_dtype, void* y, int y_dtype, int device, void* fix, int* error, cudaStream_t s) {
-    if (w.table || !fix) return false;   // lattice records stay on the ring kernel
+    if (w.table || !fix || x_dtype != MFQB_BF16) return false;   // lattice records stay on the ring kernel
     const int sms = device_sm_count(device);
     const long long total = (long long)w.nrb * w.nchunks;
     if (total < 1 || total * (sms + 1) >= (1ll << 31)) return false;
@@ -239,26 +239,28 @@ bool launch_bl_gemvs(const NintDevB& w, const void* x, int x_dtype, void* y, int
     GemvSPlan p;
     bool found = false;
     // two CTAs (this product's and the next one's) share an SM when a CTA stays below half of it
-    for (size_t budget : {(size_t)110 * 1024, (size_t)200 * 1024}) {
-        for (int warps : {16, 12, 8, 4}) {
-            if (warps * 32 > gemvs_max_threads(w.wc)) continue;
-            const long long n_w = (n_b + warps - 1) / warps;
-            const int maxseg = (int)((n_w - 1) / w.nchunks) + 2;
-            const size_t fixed = planes + (size_t)warps * maxseg * 64 + 16;
-            if (fixed >= budget) continue;
-            int stages = (int)std::min<size_t>(8, (budget - fixed) / (warps * (recb + 8)));
-            stages = (int)std::min<long long>(stages, std::max<long long>(n_w, 1));
-            const int need = (int)std::min<long long>(warps >= 8 ? 3 : 2, std::max<long long>(n_w, 1));
-            if (stages < need) continue;
-            p.grid = grid;
-            p.threads = warps * 32;
-            p.smem = fixed + (size_t)warps * stages * (recb + 8);
-            a.stages = stages;
-            a.maxseg = maxseg;
-            found = true;
-            break;
-        }
-        if (found) break;
+    // Most warps first (they hide the latency of the arithmetic and share the staging work), as long as
+    // every warp keeps two records in flight.  A CTA below half an SM lets the next product's CTA
+    // move in early; records too wide for eight such warps take the whole SM instead.
+    struct Try { size_t budget; int warps; };
+    for (const Try t : {Try{110 * 1024, 16}, Try{110 * 1024, 12}, Try{110 * 1024, 8}, Try{200 * 1024, 8}, Try{110 * 1024, 4}, Try{200 * 1024, 4}}) {
+        const int warps = t.warps;
+        if (warps * 32 > gemvs_max_threads(w.wc)) continue;
+        const long long n_w = (n_b + warps - 1) / warps;
+        const int maxseg = (int)((n_w - 1) / w.nchunks) + 2;
+        const size_t fixed = planes + (size_t)warps * maxseg * 64 + 16;
+        if (fixed >= t.budget) continue;
+        int stages = (int)std::min<size_t>(8, (t.budget - fixed) / (warps * (recb + 8)));
+        stages = (int)std::min<long long>(stages, std::max<long long>(n_w, 1));
+        const int need = (int)std::min<long long>(2, std::max<long long>(n_w, 1));
+        if (stages < need) continue;
+        p.grid = grid;
+        p.threads = warps * 32;
+        p.smem = fixed + (size_t)warps * stages * (recb + 8);
+        a.stages = stages;
+        a.maxseg = maxseg;
+        found = true;
+        break;
     }
     if (!found) return false;
     a.w = w;

@@ -42,12 +42,12 @@ struct GemvSArgs {
     int stages;             // ring records per warp
     int maxseg;             // row-block segments one warp can touch
 #ifdef MFQB_GEMVS_TRACE
-    unsigned long long* trace;   // development builds only: [grid][8] timestamps of the kernel's phases
+    unsigned long long* trace;   // development builds only: [grid][16] timestamps of the kernel's phases
 #endif
 };
 
 #ifdef MFQB_GEMVS_TRACE
-#define MFQB_TRACE(slot) do { if (a.trace && threadIdx.x == 0) a.trace[blockIdx.x * 8 + (slot)] = global_timer_ns(); } while (0)
+#define MFQB_TRACE(slot) do { if (a.trace && threadIdx.x == 0) a.trace[blockIdx.x * 16 + (slot)] = global_timer_ns(); } while (0)
 #else
 #define MFQB_TRACE(slot) do { } while (0)
 #endif
@@ -87,12 +87,20 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar_addr, uint32_t p
     return false;
 }
 // Arms the barrier for `bytes` and starts the bulk copy that completes on it (issued by one lane).
-__device__ __forceinline__ void ring_request(uint32_t slot_addr, const void* gsrc, uint32_t bytes, uint32_t bar_addr) {
+// Weights are read once per call: the copy carries an evict-first L2 policy, so the stream does not
+// push the activations, anchors and other small reused data out of L2.
+__device__ __forceinline__ void ring_request(uint32_t slot_addr, const void* gsrc, uint32_t bytes, uint32_t bar_addr, uint64_t policy) {
     asm volatile(
         "mbarrier.arrive.expect_tx.shared::cta.b64 _, [%3], %2;\n\t"
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-        ::"r"(slot_addr), "l"(gsrc), "r"(bytes), "r"(bar_addr));
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+        ::"r"(slot_addr), "l"(gsrc), "r"(bytes), "r"(bar_addr), "l"(policy));
 }
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 // D (s32) = A (u8, 16x32) * B: first step of an accumulation (no input accumulator to clear first)
 __device__ __forceinline__ void imma_u8u8_z(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
@@ -103,6 +111,24 @@ __device__ __forceinline__ void imma_u8s8_z(int (&d)[4], uint32_t a0, uint32_t a
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
                  : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+// Copies a kernel parameter into a register the compiler cannot re-derive from the parameter
+// bank: a field first read late in the kernel would otherwise be fetched from the constant cache
+// at that point, and after megabytes of weights have gone through L2 that fetch can miss all the
+// way to HBM.  Every parameter is pinned at the top, while the kernel still waits for its
+// predecessor anyway.
+__device__ __forceinline__ uint32_t pin_u32(uint32_t v) {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %1;" : "=r"(r) : "r"(v));
+    return r;
+}
+__device__ __forceinline__ int pin_i32(int v) { return (int)pin_u32((uint32_t)v); }
+template <class P>
+__device__ __forceinline__ P* pin_ptr(P* p) {
+    unsigned long long r;
+    asm volatile("mov.u64 %0, %1;" : "=l"(r) : "l"((unsigned long long)(uintptr_t)p));
+    return reinterpret_cast<P*>((uintptr_t)r);
 }
 
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
@@ -125,7 +151,8 @@ __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r
 //   gtab[g] = (sx_g, sx_g * sum of the group's integers)
 // One thread per octet (eight slots) of a group: pass 1 finds the groups' largest magnitudes
 // (shared-memory atomic max on the float bits), pass 2 quantises with the group's power-of-two
-// scale and adds up the integers, pass 3 writes the group table.  gmax / gsum: [ngp] words.
+// scale and adds up the integers, pass 3 writes the group table.  gmax / gsum: [ngp] words, zeroed
+// by the caller (with a barrier) beforehand.
 // Groups past the row's last group quantise zeros.  Every thread of the CTA must call it.
 template <typename XT>
 __device__ __forceinline__ void gemvs_load_octet(const XT* __restrict__ xrow, int k, int gs, int g, int t, bool fast, float (&v)[8]) {
@@ -188,16 +215,39 @@ __device__ __forceinline__ int gemvs_quant_octet(const float (&v)[8], uint32_t e
     return xs;
 }
 
+// Long rows and float32 rows: two reads of x (the second hits L1).  Kept out of line: rarely taken.
+template <int T, typename XT>
+static __device__ __noinline__ void gemvs_stage_x_two_reads(const XT* __restrict__ xrow, int k, int gs, int units, bool fast, uint32_t* xq,
+                                                            uint32_t* gmax, int* gsum) {
+    constexpr uint32_t SH = sizeof(XT) == 2 ? 0u : 1u;
+    for (int u = threadIdx.x; u < units; u += blockDim.x) {
+        const int g = u / T, t = u - g * T;
+        float v[8];
+        gemvs_load_octet<XT>(xrow, k, gs, g, t, fast, v);
+        uint32_t ab = 0u;   // largest magnitude as float bits (orders like the value; NaN is largest)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ab = max(ab, __float_as_uint(v[i]) & 0x7FFFFFFFu);
+        if (ab) atomicMax(gmax + g, ab);
+    }
+    __syncthreads();
+    for (int u = threadIdx.x; u < units; u += blockDim.x) {
+        const int g = u / T, t = u - g * T;
+        float v[8];
+        gemvs_load_octet<XT>(xrow, k, gs, g, t, fast, v);
+        const int xs = gemvs_quant_octet<T>(v, max(gmax[g] >> 23, 15u + kXScaleShift), SH, g, t, xq);
+        if (xs) atomicAdd(gsum + g, xs);
+    }
+}
+
 template <int T, typename XT>
 __device__ __forceinline__ void gemvs_stage_x(const XT* __restrict__ xrow, int k, int gs, int ngp, uint32_t* xq, float2* gtab, uint32_t* gmax,
-                                              int* gsum) {
+                                              int* gsum, const GemvSArgs& a) {
     // a bf16 magnitude rounds to at most 32640 on the 16-bit grid; a float32 one could reach 32768, so it gets one bit of headroom
     constexpr uint32_t SH = sizeof(XT) == 2 ? 0u : 1u;
     constexpr int MAXU = 4;   // octets a thread keeps in registers between the passes
     const int units = ngp * T;
     const bool fast = (gs & 7) == 0 && (reinterpret_cast<uintptr_t>(xrow) & 15) == 0;
-    for (int g = threadIdx.x; g < ngp; g += blockDim.x) { gmax[g] = 0u; gsum[g] = 0; }
-    __syncthreads();
+    MFQB_TRACE(7);
     bool in_regs = false;
     if constexpr (sizeof(XT) == 2) {
         if (units <= MAXU * (int)blockDim.x) {   // one global read: the raw octets wait in registers for their group's maximum
@@ -219,7 +269,9 @@ __device__ __forceinline__ void gemvs_stage_x(const XT* __restrict__ xrow, int k
                 const uint32_t ab = max(m2 & 0xFFFFu, m2 >> 16) << 16;
                 if (u < units && ab) atomicMax(gmax + u / T, ab);
             }
+            MFQB_TRACE(8);
             __syncthreads();
+            MFQB_TRACE(9);
 #pragma unroll
             for (int i = 0; i < MAXU; ++i) {
                 const int u = threadIdx.x + i * blockDim.x;
@@ -235,25 +287,8 @@ __device__ __forceinline__ void gemvs_stage_x(const XT* __restrict__ xrow, int k
             }
         }
     }
-    if (!in_regs) {   // long rows and float32 rows: two reads of x (the second hits L1)
-        for (int u = threadIdx.x; u < units; u += blockDim.x) {
-            const int g = u / T, t = u - g * T;
-            float v[8];
-            gemvs_load_octet<XT>(xrow, k, gs, g, t, fast, v);
-            uint32_t ab = 0u;   // largest magnitude as float bits (orders like the value; NaN is largest)
-#pragma unroll
-            for (int i = 0; i < 8; ++i) ab = max(ab, __float_as_uint(v[i]) & 0x7FFFFFFFu);
-            if (ab) atomicMax(gmax + g, ab);
-        }
-        __syncthreads();
-        for (int u = threadIdx.x; u < units; u += blockDim.x) {
-            const int g = u / T, t = u - g * T;
-            float v[8];
-            gemvs_load_octet<XT>(xrow, k, gs, g, t, fast, v);
-            const int xs = gemvs_quant_octet<T>(v, max(gmax[g] >> 23, 15u + kXScaleShift), SH, g, t, xq);
-            if (xs) atomicAdd(gsum + g, xs);
-        }
-    }
+    if (!in_regs) gemvs_stage_x_two_reads<T, XT>(xrow, k, gs, units, fast, xq, gmax, gsum);
+    MFQB_TRACE(10);
     __syncthreads();
     for (int g = threadIdx.x; g < ngp; g += blockDim.x) {
         const uint32_t eb = max(gmax[g] >> 23, 15u + kXScaleShift);
@@ -277,12 +312,20 @@ __device__ __forceinline__ void gemvs_body(const GemvSArgs& a, unsigned char* sm
     const NintDevB& w = a.w;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, W = blockDim.x >> 5;
     const int q = lane >> 2, c = lane & 3;
-    const int S = a.stages, nch = w.nchunks, ngp = nch * kChunkGroupsB;
+    const int S = pin_i32(a.stages), nch = pin_i32(w.nchunks), ngp = nch * kChunkGroupsB;
+    const int p_maxseg = pin_i32(a.maxseg), p_n = pin_i32(w.n), p_k = pin_i32(w.k), p_gs = pin_i32(w.gs);
+    const int p_xdt = pin_i32(a.x_dtype), p_ydt = pin_i32(a.y_dtype), p_nrb = pin_i32(w.nrb);
+    const void* p_x = pin_ptr(a.x);
+    void* p_y = pin_ptr(a.y);
+    uint2* p_slots = pin_ptr(a.fix_slots);
+    int* p_err = pin_ptr(a.error);
+    const uint32_t* p_items = pin_ptr(w.items);
+    const uint32_t* p_anchors = pin_ptr(w.anchors);
 
     // shared memory: barriers | partial rows | group table | group maxima and sums | zero block | planes | rings
     uint64_t* bars_all = reinterpret_cast<uint64_t*>(smem);
     float* parts = reinterpret_cast<float*>(smem + (((size_t)W * S * 8 + 15) & ~(size_t)15));
-    float2* gtab = reinterpret_cast<float2*>(parts + (size_t)W * a.maxseg * 16);
+    float2* gtab = reinterpret_cast<float2*>(parts + (size_t)W * p_maxseg * 16);
     uint32_t* gmax = reinterpret_cast<uint32_t*>(gtab + ngp);
     int* gsum = reinterpret_cast<int*>(gmax + ngp);
     uint32_t* zero_blk = reinterpret_cast<uint32_t*>(gsum + ngp);
@@ -294,7 +337,7 @@ __device__ __forceinline__ void gemvs_body(const GemvSArgs& a, unsigned char* sm
     __shared__ int wstart[33];   // first record of every warp of the CTA, then the CTA's end
     __shared__ int wrb[32];      // row-block of that record
     __shared__ int head_cnt;     // warps that have handed over their part of the CTA's first row-block
-    const int total = w.nrb * nch;
+    const int total = p_nrb * nch;
     const int G = gridDim.x, b = blockIdx.x;
     const int lo_b = (int)((unsigned)total * (unsigned)b / (unsigned)G), hi_b = (int)((unsigned)total * (unsigned)(b + 1) / (unsigned)G);
     const int n_b = hi_b - lo_b;
@@ -312,25 +355,33 @@ __device__ __forceinline__ void gemvs_body(const GemvSArgs& a, unsigned char* sm
     }
     __syncwarp();
     pdl_launch_dependents_b();
-    const uint32_t* src0 = w.items + (size_t)w_lo * REC;
+    const uint32_t* src0 = p_items + (size_t)w_lo * REC;
+    const uint64_t policy = l2_evict_first_policy();
     if (lane == 0) {
         const int pre = min(S, n_w);
-        for (int s = 0; s < pre; ++s) {
-            mbar_arrive_expect_tx(&bars[s], REC * 4);
-            bulk_copy_g2s(ring + (size_t)s * REC, src0 + (size_t)s * REC, REC * 4, &bars[s]);
-        }
+        for (int s = 0; s < pre; ++s)
+            ring_request(smem_u32(ring + (size_t)s * REC), src0 + (size_t)s * REC, REC * 4, smem_u32(&bars[s]), policy);
+    }
+    // The activation row may still be written by the previous kernel, so it is not read yet -- but
+    // asking L2 to fetch its lines is harmless (L2 is the point of coherence) and spares the first
+    // read after the wait a trip to HBM.  Every CTA asks for a slice.
+    {
+        const size_t xbytes = (size_t)p_k * (p_xdt == MFQB_F32 ? 4 : 2);
+        const size_t line = ((size_t)b * blockDim.x + tid) * 128;
+        if (line < xbytes) prefetch_l2(static_cast<const char*>(p_x) + line);
     }
     if (tid < 72) zero_blk[tid] = 0u;
+    for (int g = tid; g < ngp; g += blockDim.x) { gmax[g] = 0u; gsum[g] = 0; }   // staging accumulators: cleared while the predecessor still runs
     uint32_t an_lo = 0u, an_hi = 0u;   // anchors (f16 scale | f16 min << 16) of the lane's two rows: weights, so before the wait
     if (n_w > 0) {
-        an_lo = __ldg(w.anchors + (size_t)rb * 16 + q);
-        an_hi = __ldg(w.anchors + (size_t)rb * 16 + q + 8);
+        an_lo = __ldg(p_anchors + (size_t)rb * 16 + q);
+        an_hi = __ldg(p_anchors + (size_t)rb * 16 + q + 8);
     }
+    __syncthreads();
     MFQB_TRACE(1);
     pdl_wait_b();   // the activations come from the previous kernel
     MFQB_TRACE(2);
-    if (a.x_dtype == MFQB_F32) gemvs_stage_x<T, float>(static_cast<const float*>(a.x), w.k, w.gs, ngp, xq, gtab, gmax, gsum);
-    else gemvs_stage_x<T, __nv_bfloat16>(static_cast<const __nv_bfloat16*>(a.x), w.k, w.gs, ngp, xq, gtab, gmax, gsum);
+    gemvs_stage_x<T, __nv_bfloat16>(static_cast<const __nv_bfloat16*>(p_x), p_k, p_gs, ngp, xq, gtab, gmax, gsum, a);
     __syncthreads();
     MFQB_TRACE(3);
 
@@ -363,7 +414,7 @@ __device__ __forceinline__ void gemvs_body(const GemvSArgs& a, unsigned char* sm
     int seg = 0, stage = 0;
     uint32_t parity = 0;
     float acc_s_lo = 0.f, acc_s_hi = 0.f, acc_m_lo = 0.f, acc_m_hi = 0.f;
-    float* my_parts = parts + (size_t)warp * a.maxseg * 16;
+    float* my_parts = parts + (size_t)warp * p_maxseg * 16;
     bool failed = false;
 
     auto flush = [&]() {
@@ -389,8 +440,8 @@ __device__ __forceinline__ void gemvs_body(const GemvSArgs& a, unsigned char* sm
                 if (lane < 16) {
                     float v = 0.f;
                     for (int wv = 0; wv < W; ++wv)
-                        if (wstart[wv + 1] > wstart[wv] && wstart[wv] < head_end) v += parts[(size_t)wv * a.maxseg * 16 + lane];
-                    st_pair_sys(a.fix_slots + (size_t)b * 16 + lane, __float_as_uint(v), 1u);
+                        if (wstart[wv + 1] > wstart[wv] && wstart[wv] < head_end) v += parts[(size_t)wv * p_maxseg * 16 + lane];
+                    st_pair_sys(p_slots + (size_t)b * 16 + lane, __float_as_uint(v), 1u);
                 }
             }
         }
@@ -421,7 +472,7 @@ __device__ __forceinline__ void gemvs_body(const GemvSArgs& a, unsigned char* sm
         auto refill = [&]() {
             __syncwarp();   // every lane has read the slot
             if (to_request > 0) {
-                if (lane == 0) ring_request(slot_addr, src_next, REC * 4, bar_addr);
+                if (lane == 0) ring_request(slot_addr, src_next, REC * 4, bar_addr, policy);
                 src_next += REC * 4;
                 --to_request;
             }
@@ -487,22 +538,23 @@ __device__ __forceinline__ void gemvs_body(const GemvSArgs& a, unsigned char* sm
         bar_addr += 8u;
         slot_addr += REC * 4;
         if (++stage == S) { stage = 0; parity ^= 1u; bar_addr = bar0; slot_addr = slot0; }
-        if (++ch == nch) {   // the row-block is complete for this warp: hand its rows over, next row-block
-            ch = 0;
+        ++ch;
+        if (ch == nch || i + 1 == n_w) {   // the row-block, or the warp's range, ends here: hand the rows over
             flush();
-            ++rb;
-            if (i + 1 < n_w) {
-                an_lo = __ldg(w.anchors + (size_t)rb * 16 + q);
-                an_hi = __ldg(w.anchors + (size_t)rb * 16 + q + 8);
+            if (ch == nch) {
+                ch = 0;
+                ++rb;
+                if (i + 1 < n_w) {
+                    an_lo = __ldg(p_anchors + (size_t)rb * 16 + q);
+                    an_hi = __ldg(p_anchors + (size_t)rb * 16 + q + 8);
+                }
             }
         }
     }
     if (failed) {
         // a copy never arrived: record it, give the other copies in flight a bounded chance to land, leave
-        if (lane == 0 && a.error) *a.error = MFQB_ERR_TIMEOUT;
+        if (lane == 0 && p_err) *p_err = MFQB_ERR_TIMEOUT;
         for (int s = 0; s < S; ++s) (void)mbar_wait(&bars[s], parity ^ (s < stage ? 1u : 0u), 1u << 16);
-    } else if (n_w > 0 && ch != 0) {
-        flush();
     }
     // The CTA's last row-block when it continues in later CTAs: the warp that will finish it asks for
     // the published pairs now, so the answers travel while the CTA's warps meet at the barrier.
@@ -515,7 +567,7 @@ __device__ __forceinline__ void gemvs_body(const GemvSArgs& a, unsigned char* sm
 #pragma unroll
     for (int j = 0; j < PRE; ++j) {
         pre[j] = make_uint2(0u, 0u);
-        if (tail_warp && lane < 16 && b + 1 + j <= tail_b_last) pre[j] = ld_pair_sys(a.fix_slots + (size_t)(b + 1 + j) * 16 + lane);
+        if (tail_warp && lane < 16 && b + 1 + j <= tail_b_last) pre[j] = ld_pair_sys(p_slots + (size_t)(b + 1 + j) * 16 + lane);
     }
     MFQB_TRACE(4);
     __syncthreads();
@@ -533,29 +585,31 @@ __device__ __forceinline__ void gemvs_body(const GemvSArgs& a, unsigned char* sm
         while (who) {
             const int wv = __ffs(who) - 1;
             who &= who - 1;
-            if (lane < 16) v += parts[((size_t)wv * a.maxseg + (rr - wrb[wv])) * 16 + lane];
+            if (lane < 16) v += parts[((size_t)wv * p_maxseg + (rr - wrb[wv])) * 16 + lane];
         }
+        MFQB_TRACE(12);
         if (e != r1 && lane < 16) {
             for (int bb = b + 1; bb <= tail_b_last; ++bb) {
-                uint2* slot = a.fix_slots + (size_t)bb * 16 + lane;
+                uint2* slot = p_slots + (size_t)bb * 16 + lane;
                 uint2 pv = make_uint2(0u, 0u);
 #pragma unroll
                 for (int j = 0; j < PRE; ++j)
                     if (bb == b + 1 + j) pv = pre[j];
                 for (unsigned spins = 0; pv.y == 0u && spins < kGemvsPollLimit; ++spins) pv = ld_pair_sys(slot);
                 if (pv.y == 0u) {
-                    if (a.error) *a.error = MFQB_ERR_TIMEOUT;   // the publisher never came: give up on this row-block
+                    if (p_err) *p_err = MFQB_ERR_TIMEOUT;   // the publisher never came: give up on this row-block
                 } else {
                     v += __uint_as_float(pv.x);
                     st_pair_sys(slot, 0u, 0u);
                 }
             }
         }
+        MFQB_TRACE(11);
         v *= kXScaleUndo;
         const int row = rr * 16 + lane;
-        if (lane < 16 && row < w.n) {
-            if (a.y_dtype == MFQB_F32) reinterpret_cast<float*>(a.y)[row] = v;
-            else reinterpret_cast<__nv_bfloat16*>(a.y)[row] = __float2bfloat16_rn(v);
+        if (lane < 16 && row < p_n) {
+            if (p_ydt == MFQB_F32) reinterpret_cast<float*>(p_y)[row] = v;
+            else reinterpret_cast<__nv_bfloat16*>(p_y)[row] = __float2bfloat16_rn(v);
         }
     }
     MFQB_TRACE(6);

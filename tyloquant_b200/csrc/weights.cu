@@ -232,6 +232,15 @@ size_t gemvs_fix_bytes(int device);
 bool launch_bl_gemvs(const NintDevB& w, const void* x, int x_dtype, void* y, int y_dtype, int device, void* fix, int* error, cudaStream_t s);
 }
 
+// Which single-row kernel a plain NINT weight takes: 0 = by shape (default), 1 = always the ring
+// kernel, 2 = always the streamed kernel (mfqb_tune("gemv1_kernel", v)).
+static int g_gemv1_choice = 0;
+static bool gemv1_use_streamed(const NintDevB& w) {
+    if (g_gemv1_choice == 1) return false;
+    if (g_gemv1_choice == 2) return true;
+    return true;
+}
+
 struct mfqb_weight {
     int family = 0, device = 0;
     mfqb_weight_info info{};
@@ -326,6 +335,29 @@ int mfqb_weight_info_get(const mfqb_weight* w, mfqb_weight_info* info) {
     });
 }
 
+int mfqb_weight_clone(const mfqb_weight* src, mfqb_weight** out) {
+    return guarded([&] {
+        if (!src || !out) fail(MFQB_ERR_ARG, "mfqb_weight_clone: null argument");
+        if (src->family != MFQB_FAMILY_NINT) fail(MFQB_ERR_UNSUPPORTED, "mfqb_weight_clone: only scalar-quantised (NINT) weights");
+        DeviceGuard guard(src->device);
+        auto w = std::make_unique<mfqb_weight>();
+        w->family = src->family;
+        w->device = src->device;
+        w->info = src->info;
+        w->items.alloc(src->items.bytes);
+        w->anchors.alloc(src->anchors.bytes);
+        MFQB_CUDA(cudaMemcpy(w->items.p, src->items.p, src->items.bytes, cudaMemcpyDeviceToDevice));
+        MFQB_CUDA(cudaMemcpy(w->anchors.p, src->anchors.p, src->anchors.bytes, cudaMemcpyDeviceToDevice));
+        w->fix.alloc(src->fix.bytes);
+        MFQB_CUDA(cudaMemset(w->fix.p, 0, w->fix.bytes));
+        w->status = src->status;
+        w->nint = src->nint;
+        w->nint.items = static_cast<const uint32_t*>(w->items.p);
+        w->nint.anchors = static_cast<const uint32_t*>(w->anchors.p);
+        *out = w.release();
+    });
+}
+
 int mfqb_weight_free(mfqb_weight* w) {
     return guarded([&] {
         if (!w) return;
@@ -355,7 +387,9 @@ int mfqb_mul_mat(const mfqb_weight* w, const void* x, int m, void* y, int y_dtyp
         if (w->family == MFQB_FAMILY_NINT) {
             // more than 16 rows: tensor-core tile kernel (x conversion buffer is library scratch)
             if (m > 16 && launch_nint_gemm(w->nint, x, m, y, y_dtype, w->device, stream)) return;
-            if (m == 1 && launch_bl_gemvs(w->nint, x, MFQB_BF16, y, y_dtype, w->device, w->fix.p, w->status, stream)) return;
+            if (m == 1 && gemv1_use_streamed(w->nint) &&
+                launch_bl_gemvs(w->nint, x, MFQB_BF16, y, y_dtype, w->device, w->fix.p, w->status, stream))
+                return;
             for (int m0 = 0; m0 < m; m0 += 8) {   // batch rows one GEMV launch covers
                 const int mm = std::min(8, m - m0);
                 launch_bl_gemv(w->nint, static_cast<const char*>(x) + (size_t)m0 * k * 2, mm,
@@ -464,6 +498,14 @@ int mfqb_mul_mat_host_multi(const mfqb_weight* const* ws, int count, const void*
         if (!ws || !xs_host || !ys_host) fail(MFQB_ERR_ARG, "mfqb_mul_mat_host_multi: null argument");
         if (count < 1 || m < 1) fail(MFQB_ERR_ARG, "mfqb_mul_mat_host_multi: count and m must be >= 1");
         mul_mat_host_impl(ws, count, xs_host, m, ys_host, y_dtype);
+    });
+}
+
+int mfqb_tune(const char* key, int value) {
+    return guarded([&] {
+        if (!key) fail(MFQB_ERR_ARG, "mfqb_tune: null key");
+        if (std::string(key) == "gemv1_kernel" && value >= 0 && value <= 2) g_gemv1_choice = value;
+        else fail(MFQB_ERR_ARG, "mfqb_tune: unknown key '%s' or value %d out of range", key, value);
     });
 }
 

@@ -39,6 +39,12 @@ class QuantWeight:
         del keep
         return cls(h)
 
+    def clone(self) -> "QuantWeight":
+        """A second handle with its own device copy (no host-side re-layout)."""
+        h = C.c_void_p()
+        check(lib.mfqb_weight_clone(self._h, C.byref(h)))
+        return QuantWeight(h)
+
     @property
     def payload_bytes(self) -> int:
         return self.info.payload_bytes
