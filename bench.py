@@ -186,6 +186,7 @@ def main() -> None:
     ap.add_argument("--gemv1-kernel", type=int, default=0, help="mfqb_tune gemv1_kernel: 0 by shape, 1 ring kernel, 2 streamed kernel")
     ap.add_argument("--match", default=None, help="with --only sweep: run the cases whose name contains this text")
     ap.add_argument("--tokens", type=int, nargs="*", default=None, help="token counts for --only moe")
+    ap.add_argument("--batch", type=int, nargs="*", default=None, help="batch sizes for --only decoder")
     ap.add_argument("--no-parallel", action="store_true",
                     help="at --gpus > 1 skip the sharded paths (keys tp_rowparallel, ep_moe_cfg4) and time the replicas only")
     args = ap.parse_args()
@@ -204,7 +205,7 @@ def main() -> None:
         print(json.dumps(gemm_bench(local_rank, pk.get("bf16_tflops_sustained", pk["bf16_tflops"]))))
         return
     if args.only == "decoder":
-        print(json.dumps({"decoder_cfg5": decoder_bench(local_rank, 0, 1, None)}))
+        print(json.dumps({"decoder_cfg5": decoder_bench(local_rank, 0, 1, None, batches=tuple(args.batch or (1, 16)))}))
         return
     if args.only == "moe":
         print(json.dumps(moe_layer_bench(local_rank, measured_peaks()[0]["hbm_gbs"], token_counts=tuple(args.tokens or (1, 8, 32, 64, 128, 256, 1024)))))
@@ -312,12 +313,46 @@ def main() -> None:
     ms_per_step = ms / steps
     value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
 
+    # ---- the same 48 products, several weights per launch (what a decoder does for q|k|v, gate|up) ----
+    import ctypes as C
+
+    def grouped_ms(per_launch: int, reps: int = 200) -> float:
+        calls = []
+        for i in range(0, POOL, per_launch):
+            ws = weights[i:i + per_launch]
+            calls.append(((C.c_void_p * len(ws))(*[w._h for w in ws]), len(ws),
+                          (C.c_void_p * len(ws))(*[y.data_ptr() for y in ys[i:i + per_launch]])))
+
+        def go():
+            sp = torch.cuda.current_stream(dev).cuda_stream
+            for hs, cnt, ps in calls:
+                check(lib.mfqb_mul_mat_multi(hs, cnt, x.data_ptr(), ps, BF16, sp))
+        with torch.cuda.stream(stream):
+            go()
+            stream.synchronize()
+            gg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gg, stream=stream):
+                go()
+            for _ in range(5):
+                gg.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(reps):
+                gg.replay()
+            e1.record(stream)
+            stream.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    grouped = {}
+    for per_launch in (2, 4, 8):
+        gms = grouped_ms(per_launch)
+        grouped[f"x{per_launch}"] = {"ms_per_step": gms, "GBps": step_bytes / (gms * 1e-3) / 1e9}
+
     # ---- end to end through the host-buffer entry point ---------------------------------
     xh = torch.from_numpy(encode.bf16_bits(x.float().cpu().numpy()).astype(np.int16)).pin_memory()
     yh = torch.empty((1, N_ROWS), dtype=torch.int16).pin_memory()
     e2e_steps = max(3, min(steps, 10))
 
-    import ctypes as C
     yhs = [torch.empty((1, N_ROWS), dtype=torch.int16).pin_memory() for _ in range(POOL)]
     h_arr = (C.c_void_p * POOL)(*[w._h for w in weights])
     x_arr = (C.c_void_p * POOL)(*[xh.data_ptr()] * POOL)
@@ -371,13 +406,15 @@ def main() -> None:
                 "api": "mfqb_mul_mat_host_multi: the step's 48 products in one call (pinned host x and y, weights resident)",
                 "one_call_per_product": {"api": "mfqb_mul_mat_host", "ms_per_step": e2e_single_ms,
                                          "value": world * step_bytes / (e2e_single_ms * 1e-3) / 1e9}},
-        "roofline": {"bound": "hbm", "kernel": "gemvs_kernel<NintCodec<3,3>>", "achieved": achieved, "peak": peaks["hbm_gbs"],
+        "roofline": {"bound": "hbm", "kernel": "gemv1_bl_kernel<NintCodec<3,3>>", "achieved": achieved, "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": f"{peak_kind} copy bandwidth",
                      "us_per_launch": launch_us, "algorithmic_bytes_per_launch": algorithmic_bytes(payload, 1, N_ROWS, N_COLS),
                      "device_bytes_per_launch": weights[0].device_bytes,
                      # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel and shape, from
                      # the ncu capture summarised under profiles/ (the JSON beside the summary)
-                     "traffic": profile_traffic("gemvs_nint3_4096x4096")},
+                     "traffic": profile_traffic("gemv1_bl_nint3_4096x4096"),
+                     # the same products with 2, 4 or 8 weights per launch (mfqb_mul_mat_multi)
+                     "weights_per_launch": {k: dict(v, frac=v["GBps"] / peaks["hbm_gbs"]) for k, v in grouped.items()}},
     })
     if tp is not None:
         line["tp_rowparallel"] = tp

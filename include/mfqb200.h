@@ -130,6 +130,21 @@ int mfqb_dequant(const mfqb_weight* w, void* out, int out_dtype, mfqb_stream_t s
 int mfqb_mul_mat(const mfqb_weight* w, const void* x_bf16, int m, void* y, int y_dtype,
                  mfqb_stream_t stream);
 
+/* One activation row x [1, k] against up to 8 NINT weights of one shape class (same code width,
+ * group size and k; the row counts may differ) in ONE launch: ys[i] [1, n_i] = x . W_i^T.  What a
+ * decoder does for q|k|v and gate|up -- the reference's NintLinearGroup / nvq_matmul_multi2
+ * (cpp_runtime/mfq_decode.cpp:8618-8743, 7981-8070).  Same arithmetic as mfqb_mul_mat with m = 1. */
+int mfqb_mul_mat_multi(const mfqb_weight* const* ws, int count, const void* x_bf16, void* const* ys,
+                       int y_dtype, mfqb_stream_t stream);
+
+/* Down projection of a gated FFN with the activation fused: gate_up [m, 2k] float32 (gate columns
+ * first), y [m, n] = (up * gate / (1 + exp(-gate))) . W^T  (the reference's mul_mat_swiglu /
+ * fused_swiglu_matmul, mfq/kernels/cuda/glu.cuh:6-17 + the linear call that follows it).  For m = 1
+ * on NINT weights the activation is computed inside the single-row kernel as it loads the row; other
+ * cases run the activation kernel into library scratch, then mfqb_mul_mat. */
+int mfqb_mul_mat_swiglu(const mfqb_weight* w, const void* gate_up_f32, int m, void* y, int y_dtype,
+                        mfqb_stream_t stream);
+
 /* Tuning switches, for measurements.  "gemv1_kernel": which kernel a single-row product of a plain
  * NINT weight takes -- 0 by shape (default), 1 the per-warp ring kernel, 2 the streamed kernel.
  * No counterpart in the reference (its switches are MFQ_* environment variables,
@@ -310,12 +325,13 @@ int mfqb_comm_destroy(mfqb_comm* c);
  * MFQB_STATIC_SCRATCH_BYTES that is part of the library image; every GPU that loads the library
  * holds that much memory until the process exits.
  *
- *  - tokens * routes * (2F*4 + F*2 + H*4) bytes (rounded up a little) must fit; a larger call is
- *    rejected with MFQB_ERR_ARG and a message giving both numbers -- use mfqb_moe_ffn then.
+ *  - 64 KiB of counters + tokens * routes * (2F*4 + F*4 + H*4) bytes (rounded up a little; plus the
+ *    route plan and the quantised planes for batches that take the tiled kernels) must fit; a larger
+ *    call is rejected with MFQB_ERR_ARG and a message giving both numbers -- use mfqb_moe_ffn then.
  *  - The first call on a device looks the array's device address up (once per device, with that
  *    device current).  Make that first call before any stream capture.
  *  - All calls share the one array and it keeps the previous call's contents; each call clears
- *    the part it uses first.  Two calls whose device work overlaps (different streams, or
+ *    the counters at its start first (everything else is written before it is read).  Two calls whose device work overlaps (different streams, or
  *    different host threads) race on it: serialise them.
  *  - It calls no cudaMalloc / cudaFree and no library routine that allocates. */
 #define MFQB_STATIC_SCRATCH_BYTES (8u << 20)

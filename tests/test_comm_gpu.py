@@ -1,6 +1,8 @@
-"""Multi-GPU: one-shot NVLink all-reduce and the expert-parallel FFN, as child processes on two
-GPUs (skipped on a single-GPU box).  Failures are made on the host: a rank that does not join
-makes the peer's bounded wait run out, which must surface as a status, not a hang."""
+"""Multi-GPU: one-shot NVLink all-reduce, the expert-parallel FFN, the row-parallel product that
+reduces in its epilogue and the tensor-parallel decoder step, as child processes on 2, 4 and 8 GPUs
+(each case is skipped on a box with fewer).  Failures are made on the host: a rank that does not
+join makes the peer's bounded wait run out, which must surface as a status, not a hang; the
+communicator is then reset and used again."""
 
 import os
 import socket
@@ -72,8 +74,8 @@ def _worker(rank, world, port, q):
         for bits_, gs_, sb_, dtype_ in ((3, 24, 5, "NINT3"), (4, 32, 6, "NINT4")):
             n_rows, k_cols = 200, 40 * gs_
             blob = encode.random_nint_blob(n_rows, k_cols, bits_, gs_, sb_, seed=77)
-            cut = 16 * gs_
-            lo, hi = (0, cut) if rank == 0 else (cut, k_cols)
+            g0, g1 = comm.shard_range(40, rank, world, 16)   # whole groups, reference granularity rule
+            lo, hi = g0 * gs_, g1 * gs_
             shard = QuantWeight.from_blob(dtype_, blob, device=rank, axis=1, begin=lo, end=hi)
             xr = encode.bf16_round(np.random.default_rng(5).standard_normal((3, k_cols), dtype=np.float32))
             y_f = c.matmul_allreduce(shard, torch.from_numpy(xr[:, lo:hi].copy()).cuda().to(torch.bfloat16), out_dtype=torch.float32)
@@ -86,7 +88,40 @@ def _worker(rank, world, port, q):
         torch.cuda.synchronize()
         res["status_ok2"] = c.status() == 0
 
-        # 3. a rank that does not join: the other rank's wait runs out and reports it
+        # 2c. the call number across its 32-bit wrap: the slot sets must keep alternating
+        dist.barrier()
+        _capi.check(_capi.lib.mfqb_comm_debug_set_seq(c._h, 0xFFFFFFFD))
+        dist.barrier()
+        ok = True
+        for i in range(6):
+            x = torch.full((300,), float(rank + 1 + i), device="cuda")
+            ok = ok and bool(torch.equal(c.allreduce(x).cpu(), torch.full((300,), float(sum(r + 1 + i for r in range(world))))))
+        torch.cuda.synchronize()
+        res["wrap_ok"] = ok and c.status() == 0
+
+        # 2d. tensor-parallel decoder steps: every rank must emit the same tokens
+        from tyloquant_b200 import decoder as D
+        cd = comm.Communicator(rank, world, 3 * 1024, rank).connect()
+        dec, _ = D.random_decoder(hidden=1024, n_q_heads=8, n_kv_heads=8, ffn=512 * world, vocab=3000, layers=2, max_ctx=48, max_batch=3,
+                                  rank=rank, world=world, comm=cd, device=rank, seed=31)
+        dec.fill_cache(16, seed=4)
+        toks = []
+        for batch in (1, 3):
+            a = torch.arange(1, batch + 1, dtype=torch.int32, device="cuda")
+            for _ in range(2):
+                a = dec.step(a)
+            torch.cuda.synchronize()
+            toks.append(a.cpu())
+        gathered = [None] * world
+        dist.all_gather_object(gathered, [t.tolist() for t in toks])
+        res["decoder_same"] = all(g == gathered[0] for g in gathered)
+        res["decoder_range"] = all(0 <= v < 3000 for t in toks for v in t.tolist())
+        res["decoder_status"] = cd.status() == 0
+        dec.free()
+        cd.close()
+
+        # 3. a rank that does not join: the other rank's wait runs out and reports it; then the
+        # communicator is reset on every rank and works again
         dist.barrier()
         c.set_timeout_ms(200)
         if rank == 0:
@@ -95,24 +130,31 @@ def _worker(rank, world, port, q):
             res["timeout_status"] = c.status()
             res["context_alive"] = bool((torch.ones(4, device="cuda") * 2).sum().item() == 8.0)
         dist.barrier()
+        c.reset()
+        c.set_timeout_ms(2000)
+        y = c.allreduce(torch.full((128,), float(rank), device="cuda"))
+        torch.cuda.synchronize()
+        res["after_reset"] = bool(torch.equal(y.cpu(), torch.full((128,), float(sum(range(world)))))) and c.status() == 0
+        dist.barrier()
         c.close()
     finally:
         q.put((rank, res))
         dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_allreduce_expert_parallel_and_timeout_on_two_gpus():
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_allreduce_expert_parallel_decoder_and_timeout(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     from tyloquant_b200 import _capi
-    world = 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
     procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
-    results = dict(q.get(timeout=300) for _ in range(world))
+    results = dict(q.get(timeout=600) for _ in range(world))
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
@@ -121,9 +163,12 @@ def test_allreduce_expert_parallel_and_timeout_on_two_gpus():
         for n in (1, 2048, 5000, 1 << 16):
             assert r[f"sum{n}"] and r[f"same{n}"], (rank, n)
         assert r["status_ok"]
-        assert r["ep_err"] <= 4e-3
+        assert r["ep_err"] <= 1e-3
         for dt in ("NINT3", "NINT4"):
             assert r[f"rowpar_err_{dt}"] <= 1e-3 and r[f"rowpar_same_{dt}"], (rank, dt)
         assert r["status_ok2"]
+        assert r["wrap_ok"]
+        assert r["decoder_same"] and r["decoder_range"] and r["decoder_status"]
+        assert r["after_reset"]
     assert results[0]["timeout_status"] == _capi.ERR_TIMEOUT
     assert results[0]["context_alive"]

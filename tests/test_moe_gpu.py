@@ -13,7 +13,7 @@ from tyloquant_b200 import encode, moe  # noqa: E402
 from test_nint_gpu import rel_l2, bf16_tensor, REL_L2  # noqa: E402
 
 
-@pytest.mark.parametrize("tokens,experts,k", [(1, 128, 8), (33, 128, 8), (7, 256, 6), (5, 16, 16), (64, 4096, 4)])
+@pytest.mark.parametrize("tokens,experts,k", [(1, 128, 8), (33, 128, 8), (7, 256, 6), (5, 16, 16), (9, 384, 12), (3, 100, 8), (64, 4096, 4)])
 def test_router_ids_are_bit_exact(tokens, experts, k):
     rng = np.random.default_rng(tokens + experts)
     z = rng.standard_normal((tokens, experts)).astype(np.float32)
@@ -99,19 +99,9 @@ def test_golden_nintm_ffn_matches_oracle(golden):
         assert rel_l2(out, want) <= REL_L2
         y = moe.moe_ffn(gu, dn, bf16_tensor(x), ids, wts).cpu().numpy()
         y_ref = O.moe_ffn(x, gu_ref, dn_ref, rid, rw)
-        # the hidden activation between the two matmuls is stored as bf16 (the reference stores
-        # fp16): against the all-float32 oracle that rounding alone is ~1.5e-3 relative
-        assert rel_l2(y, y_ref) <= 4e-3
-        # same FFN with the oracle's hidden rounded to bf16: the stated bound holds
-        f = gu_ref.shape[1] // 2
-        y_r = np.zeros_like(y_ref)
-        for t in range(tokens):
-            for r in range(2):
-                e = int(rid[t, r])
-                g = gu_ref[e] @ x[t]
-                hid = O.bf16_round(O.swiglu(g[:f], g[f:]))
-                y_r[t] += rw[t, r] * (dn_ref[e] @ hid)
-        assert rel_l2(y, y_r) <= REL_L2
+        # nothing is rounded between the two matmuls (the activation stays float32, or is never
+        # stored at all at decode sizes): the stated bound holds against the all-float32 oracle
+        assert rel_l2(y, y_ref) <= REL_L2
     gu.free()
     dn.free()
 
@@ -132,7 +122,7 @@ def test_mixed_precision_layer_and_expert_shards(tokens):
     rid, rw = O.moe_topk(z, k)
     assert np.array_equal(ids.cpu().numpy(), rid)
     y = moe.moe_ffn(gu, dn, bf16_tensor(x), ids, wts).cpu().numpy()
-    assert rel_l2(y, O.moe_ffn(x, gu_ref, dn_ref, rid, rw)) <= 4e-3
+    assert rel_l2(y, O.moe_ffn(x, gu_ref, dn_ref, rid, rw)) <= REL_L2
     assert sum(gu.expert_bytes(e) for e in range(e_count)) == gu.info.payload_bytes
     # expert-parallel shards: each holds a contiguous expert range; their outputs add up
     parts = []
@@ -166,7 +156,7 @@ def test_route_plan_tiles_and_grouped_tile_kernel(tokens):
     want = np.stack([[gu_ref[rid[t, r]] @ x[t] for r in range(k)] for t in range(tokens)])
     assert rel_l2(out, want) <= REL_L2
     y = moe.moe_ffn(gu, dn, bf16_tensor(x), ids, wts).cpu().numpy()
-    assert rel_l2(y, O.moe_ffn(x, gu_ref, dn_ref, rid, rw)) <= 4e-3
+    assert rel_l2(y, O.moe_ffn(x, gu_ref, dn_ref, rid, rw)) <= REL_L2
     parts = []
     for b, e in ((0, 20), (20, 48)):
         sgu, sdn = moe.MoeWeight(gu_blob, expert_begin=b, expert_end=e), moe.MoeWeight(dn_blob, expert_begin=b, expert_end=e)

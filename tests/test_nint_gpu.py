@@ -153,3 +153,71 @@ def test_long_rows_and_nonfinite_inputs():
         if rows.shape[0] == 2:
             assert torch.isfinite(y[0]).all()
     w.free()
+
+
+def test_streamed_single_row_kernel_matches_oracle():
+    """The alternative single-row kernel (records streamed by bulk copies through per-warp rings, work
+    split evenly over the SMs, row-blocks shared between CTAs finished through a global scratch),
+    selected with mfqb_tune: same bound as the default kernel, on shapes whose row-blocks straddle
+    CTAs in different ways, twice in a row on the same weight (its scratch must be left clean)."""
+    from tyloquant_b200._capi import check, lib
+    check(lib.mfqb_tune(b"gemv1_kernel", 2))
+    try:
+        for bits, (b, gs, sb) in encode.CANONICAL_NINT.items():
+            for (n, k) in [(16, gs), (130, 1000), (2400, 4096), (4096, 768), (300, 14336)]:
+                blob = encode.random_nint_blob(n, k, b, gs, sb, seed=n + k + bits, device="cuda")
+                ref = O.dequant_nint(O.unpack_nint(blob))
+                w = QuantWeight.from_blob(f"NINT{b}", blob)
+                for rep in range(2):
+                    check_products(w, ref, 1, seed=rep + n)
+                w.free()
+    finally:
+        check(lib.mfqb_tune(b"gemv1_kernel", 0))
+
+
+@pytest.mark.parametrize("profile", [(3, 24, 5), (4, 32, 6), (6, 32, 7), (8, 48, 7)])
+def test_multi_weight_launch_matches_single_launches(profile):
+    """Several weights against one activation row in one launch (q|k|v, gate|up: the reference's
+    NintLinearGroup, cpp_runtime/mfq_decode.cpp:8618-8743): equal to one launch per weight up to
+    the order of the float32 additions of the warps' partial sums (and one bf16 rounding)."""
+    bits, gs, sb = profile
+    k = 1000
+    ns = [16, 130, 2400, 512, 48]
+    ws = [QuantWeight.from_blob(f"NINT{bits}", encode.random_nint_blob(n, k, bits, gs, sb, seed=31 * i + bits)) for i, n in enumerate(ns)]
+    x = bf16_tensor(np.random.default_rng(77).standard_normal((1, k), dtype=np.float32))
+    for dt in (torch.float32, torch.bfloat16):
+        got = QuantWeight.matmul_multi(ws, x, out_dtype=dt)
+        for w, y in zip(ws, got):
+            want = w.matmul(x, out_dtype=dt)[0].float()
+            tol = 1e-5 if dt == torch.float32 else 2.0 ** -7
+            assert float((y.float() - want).abs().max()) <= tol * float(want.abs().max())
+    # mismatched shape classes are refused
+    other = QuantWeight.from_blob("NINT3", encode.random_nint_blob(32, k + 24, 3, 24, 5, seed=1))
+    with pytest.raises(Exception):
+        QuantWeight.matmul_multi([ws[0], other], x)
+    for w in ws + [other]:
+        w.free()
+
+
+@pytest.mark.parametrize("profile", [(3, 24, 5), (4, 32, 6), (6, 32, 7)])
+def test_down_projection_with_fused_swiglu(profile):
+    """mfqb_mul_mat_swiglu: float32 gate|up rows -> up * silu(gate) -> down projection
+    (mfq/kernels/cuda/glu.cuh:6-17 followed by the linear).  One row: the activation is computed
+    inside the single-row kernel (no rounding before the integer quantisation); several rows: the
+    activation kernel rounds to bf16 first, and the oracle does the same."""
+    bits, gs, sb = profile
+    n, k = 200, 1000
+    blob = encode.random_nint_blob(n, k, bits, gs, sb, seed=4400 + bits)
+    w_ref = O.dequant_nint(O.unpack_nint(blob)).astype(np.float64)
+    w = QuantWeight.from_blob(f"NINT{bits}", blob)
+    rng = np.random.default_rng(4401)
+    for m in (1, 3):
+        gu = (rng.standard_normal((m, 2 * k)) * 2.0).astype(np.float32)
+        g, u = gu[:, :k].astype(np.float64), gu[:, k:].astype(np.float64)
+        act = u * g / (1.0 + np.exp(-g))
+        if m > 1:
+            act = encode.bf16_round(act.astype(np.float32)).astype(np.float64)
+        want = act @ w_ref.T
+        got = w.matmul_swiglu(torch.from_numpy(gu).cuda(), out_dtype=torch.float32).cpu().numpy().astype(np.float64)
+        assert rel_l2(got, want) <= REL_L2, (profile, m, rel_l2(got, want))
+    w.free()

@@ -24,30 +24,76 @@ namespace mfqb {
 
 constexpr int kHeadDim = 128;
 
+// Every kernel of the step is launched with the programmatic-dependent-launch attribute: it becomes
+// resident while its predecessor still runs, and waits here until that one has completed.
+__device__ __forceinline__ void dep_wait() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+template <typename... KArgs, typename... Args>
+static void launch_dep(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    MFQB_CUDA(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
+}
+
 // ---- glue kernels --------------------------------------------------------------------------------
 
 // h [rows, H] (float32 residual stream) += delta [rows, H] (optional); xn = h / rms(h) * gamma as bf16.
-__global__ void __launch_bounds__(256) add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, const float* __restrict__ gamma,
-                                                           __nv_bfloat16* __restrict__ xn, int H, float eps) {
-    __shared__ float red[8];
-    float* row = h + (size_t)blockIdx.x * H;
-    const float* drow = delta ? delta + (size_t)blockIdx.x * H : nullptr;
+// One CTA of 1024 threads per row, four columns per thread and pass: a row of up to 8192 columns is
+// read once and stays in registers between the sum of squares and the scaling (H is a multiple of 4).
+__global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, const float* __restrict__ gamma,
+                                                            __nv_bfloat16* __restrict__ xn, int H, float eps) {
+    constexpr int KEEP = 2;
+    __shared__ float red[32];
+    const int tid = threadIdx.x, nv = H >> 2;
+    float4* row = reinterpret_cast<float4*>(h + (size_t)blockIdx.x * H);
+    const float4* drow = delta ? reinterpret_cast<const float4*>(delta + (size_t)blockIdx.x * H) : nullptr;
+    const float4* g4 = reinterpret_cast<const float4*>(gamma);
+    uint2* out = reinterpret_cast<uint2*>(xn + (size_t)blockIdx.x * H);
+    float4 v[KEEP], g[KEEP];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j)   // gamma is a constant of the model: fetched while the predecessor still runs
+        if (tid + j * 1024 < nv) g[j] = __ldg(g4 + tid + j * 1024);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float v = row[i];
+    auto take = [&](int i) {
+        float4 t = row[i];
         if (drow) {
-            v += drow[i];
-            row[i] = v;
+            const float4 d = drow[i];
+            t.x += d.x; t.y += d.y; t.z += d.z; t.w += d.w;
+            row[i] = t;
         }
-        ss += v * v;
-    }
+        ss += t.x * t.x + t.y * t.y + t.z * t.z + t.w * t.w;
+        return t;
+    };
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j)
+        if (tid + j * 1024 < nv) v[j] = take(tid + j * 1024);
+    for (int i = tid + KEEP * 1024; i < nv; i += 1024) take(i);
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    if ((tid & 31) == 0) red[tid >> 5] = ss;
     __syncthreads();
-    float tot = 0.f;
-    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += red[i];
+    float tot = red[tid & 31];
+    for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
     const float inv = rsqrtf(tot / (float)H + eps);
-    for (int i = threadIdx.x; i < H; i += blockDim.x) xn[(size_t)blockIdx.x * H + i] = __float2bfloat16_rn(row[i] * inv * gamma[i]);
+    auto put = [&](int i, const float4& t, const float4& gm) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(t.x * inv * gm.x, t.y * inv * gm.y), hi = __floats2bfloat162_rn(t.z * inv * gm.z, t.w * inv * gm.w);
+        out[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+    };
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j)
+        if (tid + j * 1024 < nv) put(tid + j * 1024, v[j], g[j]);
+    for (int i = tid + KEEP * 1024; i < nv; i += 1024) put(i, row[i], __ldg(g4 + i));
 }
 
 // qkv [rows, (nq + 2 nkv) * 128] float32 -> rotary embedding on q and k (halves convention: pairs
@@ -56,6 +102,7 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(float* __restrict__ h,
 __global__ void __launch_bounds__(64) rope_kv_write_kernel(const float* __restrict__ qkv, const int* __restrict__ pos, float* __restrict__ q_out,
                                                            __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache, int nq, int nkv,
                                                            int max_ctx, float theta) {
+    dep_wait();
     const int row = blockIdx.y, head = blockIdx.x, i = threadIdx.x;   // 64 threads: one rotation pair each
     const int p = pos[row];
     const float* src = qkv + ((size_t)row * (nq + 2 * nkv) + head) * kHeadDim;
@@ -83,68 +130,109 @@ __global__ void __launch_bounds__(64) rope_kv_write_kernel(const float* __restri
 }
 
 // Grouped-query decode attention, first pass: CTA (split, kv head, row) scans its slice of the cache for
-// the G = nq / nkv query heads that share the KV head.  Four warps take tokens round robin; a lane
-// holds four of the 128 dimensions; scores are warp-reduced, the soft-max runs online per warp and
+// the G = nq / nkv query heads that share the KV head.  A half-warp holds one token (16 lanes x 8
+// dimensions = one 16-byte load per lane for K and for V); the CTA's eight half-warps take tokens
+// round robin, two tokens per half-warp and iteration, so that four 16-byte loads per lane are in
+// flight.  Scores are reduced inside the half-warp, the soft-max runs online per half-warp and
 // head.  Writes (max, sum, unnormalised output[128]) per (row, query head, split).
+__device__ __forceinline__ void bf16x8_to_f32(const uint4& r, float* f) {
+    f[0] = __uint_as_float(r.x << 16); f[1] = __uint_as_float(r.x & 0xFFFF0000u);
+    f[2] = __uint_as_float(r.y << 16); f[3] = __uint_as_float(r.y & 0xFFFF0000u);
+    f[4] = __uint_as_float(r.z << 16); f[5] = __uint_as_float(r.z & 0xFFFF0000u);
+    f[6] = __uint_as_float(r.w << 16); f[7] = __uint_as_float(r.w & 0xFFFF0000u);
+}
 template <int G>
 __global__ void __launch_bounds__(128) attn_decode_partial_kernel(const float* __restrict__ q, const __nv_bfloat16* __restrict__ kcache,
                                                                   const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ pos,
                                                                   float* __restrict__ part, int nq, int nkv, int max_ctx, int nsplit) {
+    dep_wait();
     const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31, l16 = lane & 15, slot = threadIdx.x >> 4;   // slot: half-warp 0..7 of the CTA
     const int len = pos[row] + 1;   // the token written by this step takes part
     const int per = (len + nsplit - 1) / nsplit;
     const int t0 = split * per, t1 = min(len, t0 + per);
-    float qv[G][4];
+    float qv[G][8];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-        const float4 v = *reinterpret_cast<const float4*>(q + ((size_t)row * nq + kvh * G + g) * kHeadDim + 4 * lane);
-        qv[g][0] = v.x; qv[g][1] = v.y; qv[g][2] = v.z; qv[g][3] = v.w;
+        const float4* src = reinterpret_cast<const float4*>(q + ((size_t)row * nq + kvh * G + g) * kHeadDim + 8 * l16);
+        const float4 a = src[0], b = src[1];
+        qv[g][0] = a.x; qv[g][1] = a.y; qv[g][2] = a.z; qv[g][3] = a.w;
+        qv[g][4] = b.x; qv[g][5] = b.y; qv[g][6] = b.z; qv[g][7] = b.w;
     }
-    float m[G], l[G], acc[G][4];
+    float m[G], l[G], acc[G][8];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
         m[g] = -INFINITY;
         l[g] = 0.f;
-        acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[g][i] = 0.f;
     }
-    const __nv_bfloat16* kb = kcache + ((size_t)row * nkv + kvh) * max_ctx * kHeadDim + 4 * lane;
-    const __nv_bfloat16* vb = vcache + ((size_t)row * nkv + kvh) * max_ctx * kHeadDim + 4 * lane;
-    for (int t = t0 + warp; t < t1; t += 4) {
-        const uint2 kr = *reinterpret_cast<const uint2*>(kb + (size_t)t * kHeadDim);
-        const uint2 vr = *reinterpret_cast<const uint2*>(vb + (size_t)t * kHeadDim);
-        const float k0 = __uint_as_float(kr.x << 16), k1 = __uint_as_float(kr.x & 0xFFFF0000u), k2 = __uint_as_float(kr.y << 16),
-                    k3 = __uint_as_float(kr.y & 0xFFFF0000u);
-        const float v0 = __uint_as_float(vr.x << 16), v1 = __uint_as_float(vr.x & 0xFFFF0000u), v2 = __uint_as_float(vr.y << 16),
-                    v3 = __uint_as_float(vr.y & 0xFFFF0000u);
+    const __nv_bfloat16* kb = kcache + ((size_t)row * nkv + kvh) * max_ctx * kHeadDim + 8 * l16;
+    const __nv_bfloat16* vb = vcache + ((size_t)row * nkv + kvh) * max_ctx * kHeadDim + 8 * l16;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    for (int base = t0; base < t1; base += 16) {   // uniform trip count over the CTA: the shuffles below need whole warps
+        const int ta = base + slot, tb = ta + 8;
+        const bool va = ta < t1, vb2 = tb < t1;
+        const uint4 kra = va ? *reinterpret_cast<const uint4*>(kb + (size_t)ta * kHeadDim) : zero;
+        const uint4 krb = vb2 ? *reinterpret_cast<const uint4*>(kb + (size_t)tb * kHeadDim) : zero;
+        const uint4 vra = va ? *reinterpret_cast<const uint4*>(vb + (size_t)ta * kHeadDim) : zero;
+        const uint4 vrb = vb2 ? *reinterpret_cast<const uint4*>(vb + (size_t)tb * kHeadDim) : zero;
+        float ka[8], kbv[8], fa[8], fb[8];
+        bf16x8_to_f32(kra, ka);
+        bf16x8_to_f32(krb, kbv);
+        bf16x8_to_f32(vra, fa);
+        bf16x8_to_f32(vrb, fb);
+        float sa[G], sb[G];
 #pragma unroll
         for (int g = 0; g < G; ++g) {
-            float s = qv[g][0] * k0 + qv[g][1] * k1 + qv[g][2] * k2 + qv[g][3] * k3;
-            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-            const float mn = fmaxf(m[g], s), corr = __expf(m[g] - mn), p = __expf(s - mn);
-            l[g] = l[g] * corr + p;
-            acc[g][0] = acc[g][0] * corr + p * v0;
-            acc[g][1] = acc[g][1] * corr + p * v1;
-            acc[g][2] = acc[g][2] * corr + p * v2;
-            acc[g][3] = acc[g][3] * corr + p * v3;
-            m[g] = mn;
+            float x = 0.f, y = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                x += qv[g][i] * ka[i];
+                y += qv[g][i] * kbv[i];
+            }
+            sa[g] = x;
+            sb[g] = y;
+        }
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1)
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                sa[g] += __shfl_xor_sync(0xffffffffu, sa[g], o);
+                sb[g] += __shfl_xor_sync(0xffffffffu, sb[g], o);
+            }
+        if (va) {   // uniform over the half-warp; tb valid implies ta valid
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float s1 = vb2 ? sb[g] : -INFINITY;
+                const float mn = fmaxf(m[g], fmaxf(sa[g], s1));
+                const float corr = __expf(m[g] - mn), pa = __expf(sa[g] - mn), pb = __expf(s1 - mn);
+                l[g] = l[g] * corr + pa + pb;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[g][i] = acc[g][i] * corr + pa * fa[i] + pb * fb[i];
+                m[g] = mn;
+            }
         }
     }
-    // the four warps of the CTA meet in shared memory
-    __shared__ float sm_m[4][G], sm_l[4][G], sm_acc[4][G][kHeadDim];
+    // the eight half-warps of the CTA meet in shared memory
+    __shared__ float sm_m[8][G], sm_l[8][G];
+    __shared__ __align__(16) float sm_acc[8][G][kHeadDim];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-        if (lane == 0) { sm_m[warp][g] = m[g]; sm_l[warp][g] = l[g]; }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) sm_acc[warp][g][4 * lane + i] = acc[g][i];
+        if (l16 == 0) { sm_m[slot][g] = m[g]; sm_l[slot][g] = l[g]; }
+        float4* dst = reinterpret_cast<float4*>(&sm_acc[slot][g][8 * l16]);
+        dst[0] = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+        dst[1] = make_float4(acc[g][4], acc[g][5], acc[g][6], acc[g][7]);
     }
     __syncthreads();
     for (int idx = threadIdx.x; idx < G * kHeadDim; idx += blockDim.x) {
         const int g = idx / kHeadDim, d = idx % kHeadDim;
         float mm = -INFINITY;
-        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, sm_m[w][g]);
+#pragma unroll
+        for (int w = 0; w < 8; ++w) mm = fmaxf(mm, sm_m[w][g]);
         float ll = 0.f, aa = 0.f;
-        for (int w = 0; w < 4; ++w) {
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
             const float c = sm_m[w][g] == -INFINITY ? 0.f : __expf(sm_m[w][g] - mm);
             ll += sm_l[w][g] * c;
             aa += sm_acc[w][g][d] * c;
@@ -157,6 +245,7 @@ __global__ void __launch_bounds__(128) attn_decode_partial_kernel(const float* _
 
 // Second pass: merges the splits of one (row, query head) and writes the bf16 attention output.
 __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ out, int nq, int nsplit) {
+    dep_wait();
     const int head = blockIdx.x, row = blockIdx.y, d = threadIdx.x;
     const float* src = part + ((size_t)row * nq + head) * nsplit * (kHeadDim + 2);
     float mm = -INFINITY;
@@ -174,6 +263,7 @@ __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* __r
 // gate_up [rows, 2F] float32 (gate columns first) -> act = up * gate / (1 + exp(-gate)) as bf16 [rows, F]
 // (mfq/kernels/cuda/glu.cuh:6-17).
 __global__ void swiglu_rows_kernel(const float* __restrict__ gu, __nv_bfloat16* __restrict__ act, int rows, int F) {
+    dep_wait();
     const size_t total = (size_t)rows * F;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t r = i / F, c = i % F;
@@ -185,6 +275,7 @@ __global__ void swiglu_rows_kernel(const float* __restrict__ gu, __nv_bfloat16* 
 // logits [rows, n] float32 -> (largest value, its index + index_base) per row; ties go to the smaller index.
 __global__ void __launch_bounds__(1024) argmax_rows_kernel(const float* __restrict__ logits, int n, int index_base, float* __restrict__ best_val,
                                                            int* __restrict__ best_idx) {
+    dep_wait();
     __shared__ float sv[32];
     __shared__ int si[32];
     const float* row = logits + (size_t)blockIdx.x * n;
@@ -215,6 +306,7 @@ __global__ void __launch_bounds__(1024) argmax_rows_kernel(const float* __restri
 
 // Vocabulary shards: gathered [world][rows] (value, index as float) -> winning token per row (smaller rank on ties).
 __global__ void argmax_pick_kernel(const float* __restrict__ gathered, int world, int rows, int* __restrict__ token) {
+    dep_wait();
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= rows) return;
     float bv = -INFINITY;
@@ -227,6 +319,7 @@ __global__ void argmax_pick_kernel(const float* __restrict__ gathered, int world
 }
 // This rank's (value, index) pairs into its slot of a zeroed [world][rows][2] vector (summing the ranks' vectors gathers them).
 __global__ void argmax_pack_kernel(const float* __restrict__ val, const int* __restrict__ idx, int rank, int world, int rows, float* __restrict__ out) {
+    dep_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= world * rows * 2) return;
     const int w = i / (rows * 2), r = (i / 2) % rows, f = i & 1;
@@ -235,6 +328,7 @@ __global__ void argmax_pack_kernel(const float* __restrict__ val, const int* __r
 
 // Embedding rows: h[r, :] = table[ids[r], :] (bf16 table) as float32.
 __global__ void embed_rows_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table, float* __restrict__ h, int H, int vocab) {
+    dep_wait();
     const int r = blockIdx.x;
     const int id = min(max(ids[r], 0), vocab - 1);
     for (int i = threadIdx.x; i < H; i += blockDim.x) h[(size_t)r * H + i] = __bfloat162float(table[(size_t)id * H + i]);
@@ -252,6 +346,7 @@ __global__ void fill_f32_kernel(float* p, size_t n, float v) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) p[i] = v;
 }
 __global__ void add_one_kernel(int* p, int n) {
+    dep_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) p[i] += 1;
 }
@@ -270,7 +365,7 @@ struct mfqb_decoder {
     mfqb_decoder_config cfg{};
     int rank = 0, world = 1, device = 0;
     mfqb_comm* comm = nullptr;       // borrowed; null when world == 1
-    int nq = 0, nkv = 0, f = 0, vshard = 0, vbase = 0, nsplit = 16;
+    int nq = 0, nkv = 0, f = 0, vshard = 0, vbase = 0, sms = 0;
     std::vector<DecoderLayer> layers;
     const mfqb_weight* lm_head = nullptr;
     const void* embedding = nullptr;   // bf16 [vocab, H] on the device, borrowed
@@ -278,6 +373,14 @@ struct mfqb_decoder {
     // workspaces
     DevBuf h, xn, qkv, q, attn, proj, proj_sum, gu, act, logits, part, best_val, best_idx, gathered, gathered_sum, pos;
 };
+
+// Context splits of the decode attention: enough CTAs to fill every SM about four times over, each
+// split at least one round of the CTA's half-warps.
+constexpr int kMaxSplits = 64;
+static int attn_splits(const mfqb_decoder* d, int rows) {
+    const int want = (4 * d->sms + d->nkv * rows - 1) / (d->nkv * rows);
+    return std::max(1, std::min(kMaxSplits, want));
+}
 
 static void check_weight_shape(const mfqb_weight* w, int64_t n, int64_t k, const char* what) {
     mfqb_weight_info info;
@@ -309,27 +412,27 @@ static const float* layer_forward(mfqb_decoder* d, int li, int rows, const float
     DecoderLayer& L = d->layers[li];
     const int H = d->cfg.hidden;
     const int G = d->cfg.n_q_heads / d->cfg.n_kv_heads;
-    add_rmsnorm_kernel<<<rows, 256, 0, s>>>(static_cast<float*>(d->h.p), delta, static_cast<const float*>(L.gamma_attn.p),
-                                            static_cast<__nv_bfloat16*>(d->xn.p), H, d->cfg.rms_eps);
+    launch_dep(add_rmsnorm_kernel, dim3(rows), dim3(1024), s, static_cast<float*>(d->h.p), delta, static_cast<const float*>(L.gamma_attn.p),
+               static_cast<__nv_bfloat16*>(d->xn.p), H, d->cfg.rms_eps);
     mul_mat(L.qkv, d->xn.p, rows, d->qkv.p, s);
-    rope_kv_write_kernel<<<dim3(d->nq + 2 * d->nkv, rows), 64, 0, s>>>(static_cast<const float*>(d->qkv.p), static_cast<const int*>(d->pos.p),
-                                                                     static_cast<float*>(d->q.p), static_cast<__nv_bfloat16*>(L.kcache.p),
-                                                                     static_cast<__nv_bfloat16*>(L.vcache.p), d->nq, d->nkv, d->cfg.max_ctx,
-                                                                     d->cfg.rope_theta);
-    const dim3 agrid(d->nsplit, d->nkv, rows);
+    launch_dep(rope_kv_write_kernel, dim3(d->nq + 2 * d->nkv, rows), dim3(64), s, static_cast<const float*>(d->qkv.p),
+               static_cast<const int*>(d->pos.p), static_cast<float*>(d->q.p), static_cast<__nv_bfloat16*>(L.kcache.p),
+               static_cast<__nv_bfloat16*>(L.vcache.p), d->nq, d->nkv, d->cfg.max_ctx, d->cfg.rope_theta);
+    const int nsplit = attn_splits(d, rows);
+    const dim3 agrid(nsplit, d->nkv, rows);
     const float* qp = static_cast<const float*>(d->q.p);
     const __nv_bfloat16 *kc = static_cast<const __nv_bfloat16*>(L.kcache.p), *vc = static_cast<const __nv_bfloat16*>(L.vcache.p);
     const int* pos = static_cast<const int*>(d->pos.p);
     float* part = static_cast<float*>(d->part.p);
     switch (G) {
-        case 1: attn_decode_partial_kernel<1><<<agrid, 128, 0, s>>>(qp, kc, vc, pos, part, d->nq, d->nkv, d->cfg.max_ctx, d->nsplit); break;
-        case 2: attn_decode_partial_kernel<2><<<agrid, 128, 0, s>>>(qp, kc, vc, pos, part, d->nq, d->nkv, d->cfg.max_ctx, d->nsplit); break;
-        case 4: attn_decode_partial_kernel<4><<<agrid, 128, 0, s>>>(qp, kc, vc, pos, part, d->nq, d->nkv, d->cfg.max_ctx, d->nsplit); break;
-        case 8: attn_decode_partial_kernel<8><<<agrid, 128, 0, s>>>(qp, kc, vc, pos, part, d->nq, d->nkv, d->cfg.max_ctx, d->nsplit); break;
+        case 1: launch_dep(attn_decode_partial_kernel<1>, agrid, dim3(128), s, qp, kc, vc, pos, part, d->nq, d->nkv, d->cfg.max_ctx, nsplit); break;
+        case 2: launch_dep(attn_decode_partial_kernel<2>, agrid, dim3(128), s, qp, kc, vc, pos, part, d->nq, d->nkv, d->cfg.max_ctx, nsplit); break;
+        case 4: launch_dep(attn_decode_partial_kernel<4>, agrid, dim3(128), s, qp, kc, vc, pos, part, d->nq, d->nkv, d->cfg.max_ctx, nsplit); break;
+        case 8: launch_dep(attn_decode_partial_kernel<8>, agrid, dim3(128), s, qp, kc, vc, pos, part, d->nq, d->nkv, d->cfg.max_ctx, nsplit); break;
         default: fail(MFQB_ERR_UNSUPPORTED, "query heads per KV head must be 1, 2, 4 or 8, got %d", G);
     }
-    attn_decode_merge_kernel<<<dim3(d->nq, rows), 128, 0, s>>>(part, static_cast<__nv_bfloat16*>(d->attn.p), d->nq, d->nsplit);
-    MFQB_CUDA(cudaGetLastError());
+    launch_dep(attn_decode_merge_kernel, dim3(d->nq, rows), dim3(128), s, static_cast<const float*>(part), static_cast<__nv_bfloat16*>(d->attn.p),
+               d->nq, nsplit);
     // output projection: row-parallel under tensor parallelism
     const float* o_out;
     if (d->world > 1 && rows == 1) {
@@ -340,12 +443,16 @@ static const float* layer_forward(mfqb_decoder* d, int li, int rows, const float
         mul_mat(L.o, d->attn.p, rows, d->proj.p, s);
         o_out = rank_sum(d, static_cast<const float*>(d->proj.p), static_cast<float*>(d->proj_sum.p), (size_t)rows * H, s);
     }
-    add_rmsnorm_kernel<<<rows, 256, 0, s>>>(static_cast<float*>(d->h.p), o_out, static_cast<const float*>(L.gamma_ffn.p),
-                                            static_cast<__nv_bfloat16*>(d->xn.p), H, d->cfg.rms_eps);
+    launch_dep(add_rmsnorm_kernel, dim3(rows), dim3(1024), s, static_cast<float*>(d->h.p), o_out, static_cast<const float*>(L.gamma_ffn.p),
+               static_cast<__nv_bfloat16*>(d->xn.p), H, d->cfg.rms_eps);
     mul_mat(L.gate_up, d->xn.p, rows, d->gu.p, s);
-    swiglu_rows_kernel<<<std::min(1024, (rows * d->f + 255) / 256), 256, 0, s>>>(static_cast<const float*>(d->gu.p), static_cast<__nv_bfloat16*>(d->act.p),
-                                                                               rows, d->f);
-    MFQB_CUDA(cudaGetLastError());
+    if (d->world == 1 && rows == 1) {   // the down projection computes the activation as it loads its row
+        const int rc = mfqb_mul_mat_swiglu(L.down, d->gu.p, 1, d->proj.p, MFQB_F32, s);
+        if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
+        return static_cast<const float*>(d->proj.p);
+    }
+    launch_dep(swiglu_rows_kernel, dim3(std::min(1024, (rows * d->f + 255) / 256)), dim3(256), s, static_cast<const float*>(d->gu.p),
+               static_cast<__nv_bfloat16*>(d->act.p), rows, d->f);
     if (d->world > 1 && rows == 1) {
         const int rc = mfqb_mul_mat_allreduce(L.down, d->act.p, 1, d->comm, d->proj_sum.p, MFQB_F32, s);
         if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
@@ -365,7 +472,7 @@ int mfqb_decoder_create(const mfqb_decoder_config* cfg, int rank, int world, mfq
         if (world > 1 && !comm) fail(MFQB_ERR_ARG, "mfqb_decoder_create: tensor parallelism needs a communicator");
         if (cfg->head_dim != kHeadDim) fail(MFQB_ERR_UNSUPPORTED, "head_dim must be %d", kHeadDim);
         if (cfg->n_q_heads % cfg->n_kv_heads || cfg->n_kv_heads % world || cfg->ffn % world || cfg->layers < 1 || cfg->max_batch < 1 ||
-            cfg->hidden != cfg->n_q_heads * kHeadDim)
+            cfg->hidden != cfg->n_q_heads * kHeadDim || cfg->hidden % 8)
             fail(MFQB_ERR_ARG, "mfqb_decoder_create: head counts, FFN width and hidden size must divide over %d ranks (hidden = heads x 128)", world);
         auto d = std::make_unique<mfqb_decoder>();
         d->cfg = *cfg;
@@ -373,6 +480,7 @@ int mfqb_decoder_create(const mfqb_decoder_config* cfg, int rank, int world, mfq
         d->world = world;
         d->comm = world > 1 ? comm : nullptr;
         d->device = device;
+        d->sms = device_sm_count(device);
         d->nq = cfg->n_q_heads / world;
         d->nkv = cfg->n_kv_heads / world;
         d->f = cfg->ffn / world;
@@ -404,7 +512,7 @@ int mfqb_decoder_create(const mfqb_decoder_config* cfg, int rank, int world, mfq
         d->gu.alloc(B * 2 * d->f * 4);
         d->act.alloc(B * d->f * 2);
         d->logits.alloc(B * std::max(d->vshard, 1) * 4);
-        d->part.alloc(B * d->nq * d->nsplit * (kHeadDim + 2) * 4);
+        d->part.alloc(B * d->nq * kMaxSplits * (kHeadDim + 2) * 4);
         d->best_val.alloc(B * 4);
         d->best_idx.alloc(B * 4);
         d->gathered.alloc((size_t)world * B * 2 * 4);
@@ -476,25 +584,25 @@ int mfqb_decoder_step(mfqb_decoder* d, const int32_t* ids_in, int batch, int32_t
         DeviceGuard guard(d->device);
         cudaStream_t s = stream;
         const int H = d->cfg.hidden;
-        embed_rows_kernel<<<batch, 256, 0, s>>>(ids_in, static_cast<const __nv_bfloat16*>(d->embedding), static_cast<float*>(d->h.p), H, d->cfg.vocab);
+        launch_dep(embed_rows_kernel, dim3(batch), dim3(256), s, static_cast<const int*>(ids_in), static_cast<const __nv_bfloat16*>(d->embedding),
+                   static_cast<float*>(d->h.p), H, d->cfg.vocab);
         const float* delta = nullptr;
         for (int li = 0; li < d->cfg.layers; ++li) delta = layer_forward(d, li, batch, delta, s);
-        add_rmsnorm_kernel<<<batch, 256, 0, s>>>(static_cast<float*>(d->h.p), delta, static_cast<const float*>(d->gamma_final.p),
-                                                 static_cast<__nv_bfloat16*>(d->xn.p), H, d->cfg.rms_eps);
+        launch_dep(add_rmsnorm_kernel, dim3(batch), dim3(1024), s, static_cast<float*>(d->h.p), delta, static_cast<const float*>(d->gamma_final.p),
+                   static_cast<__nv_bfloat16*>(d->xn.p), H, d->cfg.rms_eps);
         mul_mat(d->lm_head, d->xn.p, batch, d->logits.p, s);
-        argmax_rows_kernel<<<batch, 1024, 0, s>>>(static_cast<const float*>(d->logits.p), d->vshard, d->vbase, static_cast<float*>(d->best_val.p),
-                                                  static_cast<int*>(d->best_idx.p));
+        launch_dep(argmax_rows_kernel, dim3(batch), dim3(1024), s, static_cast<const float*>(d->logits.p), d->vshard, d->vbase,
+                   static_cast<float*>(d->best_val.p), static_cast<int*>(d->best_idx.p));
         if (d->world == 1) {
             MFQB_CUDA(cudaMemcpyAsync(ids_out, d->best_idx.p, (size_t)batch * 4, cudaMemcpyDeviceToDevice, s));
         } else {
             const int n = d->world * batch * 2;
-            argmax_pack_kernel<<<(n + 255) / 256, 256, 0, s>>>(static_cast<const float*>(d->best_val.p), static_cast<const int*>(d->best_idx.p), d->rank,
-                                                              d->world, batch, static_cast<float*>(d->gathered.p));
+            launch_dep(argmax_pack_kernel, dim3((n + 255) / 256), dim3(256), s, static_cast<const float*>(d->best_val.p),
+                       static_cast<const int*>(d->best_idx.p), d->rank, d->world, batch, static_cast<float*>(d->gathered.p));
             const float* g = rank_sum(d, static_cast<const float*>(d->gathered.p), static_cast<float*>(d->gathered_sum.p), (size_t)n, s);
-            argmax_pick_kernel<<<(batch + 127) / 128, 128, 0, s>>>(g, d->world, batch, ids_out);
+            launch_dep(argmax_pick_kernel, dim3((batch + 127) / 128), dim3(128), s, g, d->world, batch, static_cast<int*>(ids_out));
         }
-        add_one_kernel<<<(batch + 127) / 128, 128, 0, s>>>(static_cast<int*>(d->pos.p), batch);
-        MFQB_CUDA(cudaGetLastError());
+        launch_dep(add_one_kernel, dim3((batch + 127) / 128), dim3(128), s, static_cast<int*>(d->pos.p), batch);
     });
 }
 
@@ -509,8 +617,8 @@ int mfqb_decoder_layer(mfqb_decoder* d, int layer, const float* h_in, int rows, 
         MFQB_CUDA(cudaMemcpyAsync(d->h.p, h_in, bytes, cudaMemcpyDeviceToDevice, stream));
         const float* delta = layer_forward(d, layer, rows, nullptr, stream);
         // fold the FFN output in with a norm whose bf16 output is discarded
-        add_rmsnorm_kernel<<<rows, 256, 0, stream>>>(static_cast<float*>(d->h.p), delta, static_cast<const float*>(d->gamma_final.p),
-                                                    static_cast<__nv_bfloat16*>(d->xn.p), d->cfg.hidden, d->cfg.rms_eps);
+        launch_dep(add_rmsnorm_kernel, dim3(rows), dim3(1024), stream, static_cast<float*>(d->h.p), delta, static_cast<const float*>(d->gamma_final.p),
+                   static_cast<__nv_bfloat16*>(d->xn.p), d->cfg.hidden, d->cfg.rms_eps);
         MFQB_CUDA(cudaMemcpyAsync(h_out, d->h.p, bytes, cudaMemcpyDeviceToDevice, stream));
     });
 }

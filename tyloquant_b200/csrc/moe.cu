@@ -9,6 +9,7 @@
 #include <cuda_bf16.h>
 
 #include <algorithm>
+#include <climits>
 #include <memory>
 #include <mutex>
 
@@ -17,6 +18,9 @@
 
 namespace mfqb {
 void launch_swiglu(const void* gate_up, int in_dtype, int rows, int f, void* hidden, cudaStream_t s);
+void launch_swiglu_f32(const float* gate_up, int rows, int f, float* hidden, cudaStream_t s);
+int moe_hetero_gemv1_splits(int rb_per_expert, int pairs, int device);
+bool moe_hetero_supported(const NintDevB* pools, const int* held, int npools);
 void launch_weighted_reduce(const void* src, int in_dtype, const float* weights, int tokens, int routes, int h, void* y, int y_dtype,
                             cudaStream_t s);
 
@@ -40,7 +44,7 @@ void check_nint_supported(const HostNint& t);
 int nint_bl_max_passes(const NintDevB& w);
 bool nint_gemm_grouped_supported(const NintDevB& w, int bn, int rows_per_expert);
 size_t nint_gemm_grouped_x_bytes(int pairs, int k);
-void launch_x_gather_f16(const void* x, const int* pair_order, int div, int pairs, int k, void* x16, cudaStream_t s);
+void launch_x_gather_f16(const void* x, bool x_f32, const int* pair_order, int div, int pairs, int k, void* x16, cudaStream_t s);
 void launch_nint_gemm_grouped(const NintDevB& w, const void* x16, int pairs, int bn, const int* expert_bounds, const int* tile_bounds,
                               const int* pair_order, const int* expert_pool, const int* expert_local, int n_experts, int pool,
                               int rb_per_expert, int rows_per_expert, int max_tiles, void* y, int y_dtype, int device, cudaStream_t s);
@@ -48,7 +52,8 @@ bool launch_moe_hetero_tiles(GemvArgsB base, const NintDevB* pools, const int* h
                              int npools, int tile_m, int max_tiles, int device, cudaStream_t s);
 bool launch_moe_hetero_gemv1(GemvArgsB base, const NintDevB* pools, const int* held, int npools, int pairs, int device, cudaStream_t s);
 size_t nint_bl_planes_bytes(const NintDevB& w, int rows);
-void launch_x_planes(const NintDevB& w, const void* x, int rows, void* planes, const uint2** xq_g, const float2** gtab_g, cudaStream_t s);
+void launch_x_planes(const NintDevB& w, const void* x, int rows, void* planes, const uint2** xq_g, const float2** gtab_g, cudaStream_t s,
+                     bool x_f32);
 
 struct MoePool {
     NintDevB d{};
@@ -251,8 +256,26 @@ static size_t moe_planes_bytes(const mfqb_moe_weight* w, int rows) {
 // plan == nullptr: one single-row problem per pair.  Otherwise the batched kernel runs over the
 // plan's tiles (the plan must have been built for these ids with the same tile_m) and `planes` is
 // moe_planes_bytes() of device memory for the quantised input rows.
+constexpr size_t kFfnCounterBytes = 64 * 1024;   // route-sum counters at the start of the FFN scratch: zero between calls
+struct FfnLayout {
+    bool gemm, tiles, fused_tail;
+    int tile_m;
+    size_t o_gu, o_hid, o_dn, o_plan, o_planes, b_pgu, total;
+};
+
+// x_mode: 0 = x is bf16; 1 = float32; 2 = float32 gate|up products [pairs, 2k], the SwiGLU activation is
+// formed while loading (single-row path only).  `tail` (single-row path only): the product ends the
+// FFN -- see GemvArgsB::route_w.
+struct FfnTail {
+    const float* route_w;
+    float* pair_out;
+    unsigned* token_count;
+    void* y;
+    int y_dtype;
+};
 static void mul_mat_id_impl(const mfqb_moe_weight* w, const void* x, int x_per_pair, const int32_t* ids, int tokens, int routes,
-                            void* out, int out_dtype, const PlanBufs* plan, int tile_m, void* planes, cudaStream_t stream, bool gemm = false) {
+                            void* out, int out_dtype, const PlanBufs* plan, int tile_m, void* planes, cudaStream_t stream, bool gemm = false,
+                            int x_mode = 0, const FfnTail* tail = nullptr) {
     const int pairs = tokens * routes, ope = w->info.out_per_expert;
     const int in_rows = x_per_pair ? pairs : tokens;
     struct PlaneSet { int gs; const uint2* xq; const float2* gtab; };
@@ -260,8 +283,9 @@ static void mul_mat_id_impl(const mfqb_moe_weight* w, const void* x, int x_per_p
     char* planes_next = static_cast<char*>(planes);
     // Routes to experts this handle does not hold produce zeros (expert-parallel shards are
     // summed afterwards), so clear the output when the handle is partial.
-    if (w->info.expert_end - w->info.expert_begin != w->info.n_experts)
+    if (!tail && w->info.expert_end - w->info.expert_begin != w->info.n_experts)
         MFQB_CUDA(cudaMemsetAsync(out, 0, (size_t)pairs * ope * (out_dtype == MFQB_F32 ? 4 : 2), stream));
+    if ((x_mode == 2 || tail) && plan) fail(MFQB_ERR_ARG, "mul_mat_id: the fused activation and the fused route sum belong to the single-row path");
     if (!plan && pairs <= 32768) {   // decode sizes: all cohorts in one launch when their codecs allow
         GemvArgsB a{};
         a.x = static_cast<const __nv_bfloat16*>(x);
@@ -274,6 +298,15 @@ static void mul_mat_id_impl(const mfqb_moe_weight* w, const void* x, int x_per_p
         a.rb_per_expert = w->padded / 16;
         a.routes = routes;
         a.x_per_pair = x_per_pair ? 1 : 0;
+        a.n_experts = w->info.n_experts;
+        a.x_mode = x_mode;
+        if (tail) {
+            a.route_w = tail->route_w;
+            a.pair_out = tail->pair_out;
+            a.token_count = tail->token_count;
+            a.y_final = tail->y;
+            a.y_final_dtype = tail->y_dtype;
+        }
         NintDevB devs[16];
         int held[16];
         for (size_t pi = 0; pi < w->pools.size(); ++pi) {
@@ -282,8 +315,9 @@ static void mul_mat_id_impl(const mfqb_moe_weight* w, const void* x, int x_per_p
         }
         if (launch_moe_hetero_gemv1(a, devs, held, (int)w->pools.size(), pairs, w->info.device, stream)) return;
     }
+    if (x_mode == 2 || tail) fail(MFQB_ERR_UNSUPPORTED, "mul_mat_id: this record's cohorts have no all-cohort single-row kernel");
     if (plan && gemm) {   // large batches: tensor-core tile kernel, `planes` holds the gathered f16 rows
-        launch_x_gather_f16(x, plan->pair_order, x_per_pair ? 1 : routes, pairs, w->info.k, planes, stream);
+        launch_x_gather_f16(x, x_mode == 1, plan->pair_order, x_per_pair ? 1 : routes, pairs, w->info.k, planes, stream);
         const int tiles = pairs / tile_m + std::min(pairs, w->info.n_experts);
         if (tiles > 65535) fail(MFQB_ERR_ARG, "mfqb_mul_mat_id: too many route tiles (%d)", tiles);
         for (size_t pi = 0; pi < w->pools.size(); ++pi) {
@@ -307,7 +341,7 @@ static void mul_mat_id_impl(const mfqb_moe_weight* w, const void* x, int x_per_p
                 if (c.gs == pool.d.gs) ps = &c;
             if (!ps) {
                 PlaneSet n{pool.d.gs, nullptr, nullptr};
-                launch_x_planes(pool.d, x, in_rows, planes_next, &n.xq, &n.gtab, stream);
+                launch_x_planes(pool.d, x, in_rows, planes_next, &n.xq, &n.gtab, stream, x_mode == 1);
                 planes_next += (nint_bl_planes_bytes(pool.d, in_rows) + 255) / 256 * 256;
                 sets.push_back(n);
                 ps = &sets.back();
@@ -341,6 +375,7 @@ static void mul_mat_id_impl(const mfqb_moe_weight* w, const void* x, int x_per_p
         }
         if (launch_moe_hetero_tiles(a, devs, held, pool_xq, pool_gtab, (int)w->pools.size(), tile_m, max_tiles, w->info.device, stream)) return;
     }
+    if (!plan && x_mode != 0) fail(MFQB_ERR_UNSUPPORTED, "mul_mat_id: the per-cohort single-row launches take bf16 activations");
     for (size_t pi = 0; pi < w->pools.size(); ++pi) {
         const MoePool& pool = *w->pools[pi];
         if (!pool.held) continue;
@@ -403,40 +438,93 @@ int mfqb_mul_mat_id(const mfqb_moe_weight* w, const void* x, int x_per_pair, con
     });
 }
 
+// True when the all-cohort single-row kernel can run both matmuls of the FFN with nothing stored in
+// between: SwiGLU formed while the down matmul loads, the weighted route sum in its epilogue.
+static bool ffn_fused_tail_ok(const mfqb_moe_weight* down, int tokens, int pairs) {
+    NintDevB devs[16];
+    int held[16];
+    if (down->pools.size() > 16 || pairs > 32768) return false;
+    for (size_t pi = 0; pi < down->pools.size(); ++pi) {
+        devs[pi] = down->pools[pi]->d;
+        held[pi] = down->pools[pi]->held;
+    }
+    if (!moe_hetero_supported(devs, held, (int)down->pools.size())) return false;
+    return (size_t)tokens * moe_hetero_gemv1_splits(down->padded / 16, pairs, down->info.device) * 4 <= kFfnCounterBytes;
+}
+
+// The FFN proper, on caller-provided scratch `s` laid out as
+//   [route-sum counters (zero between calls) | gate|up products | activation | down products | route plan | planes].
+static void moe_ffn_run(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* down, const void* x, const int32_t* ids, const float* weights,
+                        int tokens, int routes, void* y, int y_dtype, char* s, const FfnLayout& L, cudaStream_t stream) {
+    const int f = gate_up->info.out_per_expert / 2, h = gate_up->info.k;
+    const size_t pairs = (size_t)tokens * routes;
+    float* gu = reinterpret_cast<float*>(s + L.o_gu);
+    float* hid = reinterpret_cast<float*>(s + L.o_hid);
+    float* dn = reinterpret_cast<float*>(s + L.o_dn);
+    PlanBufs plan{};
+    if (L.tiles) {   // one route plan serves both matmuls
+        plan = PlanBufs::carve(s + L.o_plan, gate_up->info.n_experts);
+        launch_route_plan(ids, (int)pairs, gate_up->info.n_experts, L.tile_m, plan.expert_bounds, plan.tile_bounds, plan.pair_order, stream);
+    }
+    char* planes = s + L.o_planes;
+    mul_mat_id_impl(gate_up, x, 0, ids, tokens, routes, gu, MFQB_F32, L.tiles ? &plan : nullptr, L.tile_m, planes, stream, L.gemm);
+    if (L.fused_tail) {   // decode sizes: the down matmul reads the gate|up products and ends in the route sum
+        const FfnTail tail{weights, dn, reinterpret_cast<unsigned*>(s), y, y_dtype};
+        mul_mat_id_impl(down, gu, 1, ids, tokens, routes, dn, MFQB_F32, nullptr, 0, nullptr, stream, false, 2, &tail);
+        return;
+    }
+    if (!L.tiles) {   // cohorts without an all-cohort kernel: bf16 activation through the per-cohort launches
+        launch_swiglu(gu, MFQB_F32, (int)pairs, f, hid, stream);
+        mul_mat_id_impl(down, hid, 1, ids, tokens, routes, dn, MFQB_F32, nullptr, 0, nullptr, stream);
+    } else {          // the activation stays float32: no rounding between the two matmuls
+        launch_swiglu_f32(gu, (int)pairs, f, hid, stream);
+        mul_mat_id_impl(down, hid, 1, ids, tokens, routes, dn, MFQB_F32, &plan, L.tile_m, planes + L.b_pgu, stream, L.gemm, 1);
+    }
+    launch_weighted_reduce(dn, MFQB_F32, weights, tokens, routes, h, y, y_dtype, stream);
+}
+
+static void check_ffn_args(const char* who, const mfqb_moe_weight* gate_up, const mfqb_moe_weight* down, int tokens, int routes) {
+    const int h = gate_up->info.k, f2 = gate_up->info.out_per_expert, f = f2 / 2;
+    if (f2 % 2 || down->info.k != f || down->info.out_per_expert != h || down->info.n_experts != gate_up->info.n_experts)
+        fail(MFQB_ERR_ARG, "%s: gate_up [E, 2F, H] and down [E, H, F] shapes do not match", who);
+    if (gate_up->info.device != down->info.device) fail(MFQB_ERR_ARG, "%s: weights live on different devices", who);
+    if (routes < 1 || routes > 64) fail(MFQB_ERR_ARG, "%s: routes per token must be in [1, 64], got %d", who, routes);
+    if ((long long)tokens * routes > INT_MAX) fail(MFQB_ERR_ARG, "%s: %d tokens x %d routes is more than the kernels index", who, tokens, routes);
+}
+
+static FfnLayout ffn_layout(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* down, int tokens, int routes, bool allow_gemm) {
+    FfnLayout L{};
+    const int h = gate_up->info.k, f2 = gate_up->info.out_per_expert, f = f2 / 2;
+    const size_t pairs = (size_t)tokens * routes;
+    auto up256 = [](size_t v) { return (v + 255) / 256 * 256; };
+    // large batches: both matmuls on the tensor-core tile kernel, when every cohort of both has one
+    const int gemm_bn = allow_gemm ? std::min(moe_gemm_bn(gate_up, (int)pairs), moe_gemm_bn(down, (int)pairs)) : 0;
+    L.gemm = gemm_bn != 0;
+    L.tile_m = L.gemm ? gemm_bn : std::min(moe_tile_m(gate_up, (int)pairs), moe_tile_m(down, (int)pairs));
+    L.tiles = L.tile_m != 0;
+    L.fused_tail = !L.tiles && ffn_fused_tail_ok(down, tokens, (int)pairs) && ffn_fused_tail_ok(gate_up, tokens, (int)pairs);
+    const size_t b_plan = L.tiles ? PlanBufs::bytes(gate_up->info.n_experts, pairs) : 0;
+    L.b_pgu = L.gemm ? up256(nint_gemm_grouped_x_bytes((int)pairs, h)) : (L.tiles ? moe_planes_bytes(gate_up, tokens) : 0);
+    const size_t b_pdn = L.gemm ? nint_gemm_grouped_x_bytes((int)pairs, f) : (L.tiles ? moe_planes_bytes(down, (int)pairs) : 0);
+    L.o_gu = kFfnCounterBytes;
+    L.o_hid = L.o_gu + up256(pairs * f2 * 4);
+    L.o_dn = L.o_hid + up256(pairs * f * 4);
+    L.o_plan = L.o_dn + up256(pairs * h * 4);
+    L.o_planes = L.o_plan + b_plan;
+    L.total = L.o_planes + L.b_pgu + b_pdn;
+    return L;
+}
+
 int mfqb_moe_ffn(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* down, const void* x, const int32_t* ids, const float* weights,
                  int tokens, int routes, void* y, int y_dtype, mfqb_stream_t stream) {
     return guarded([&] {
         if (!gate_up || !down || !x || !ids || !weights || !y) fail(MFQB_ERR_ARG, "mfqb_moe_ffn: null argument");
-        const int h = gate_up->info.k, f2 = gate_up->info.out_per_expert, f = f2 / 2;
-        if (f2 % 2 || down->info.k != f || down->info.out_per_expert != h || down->info.n_experts != gate_up->info.n_experts)
-            fail(MFQB_ERR_ARG, "mfqb_moe_ffn: gate_up [E, 2F, H] and down [E, H, F] shapes do not match");
-        if (gate_up->info.device != down->info.device) fail(MFQB_ERR_ARG, "mfqb_moe_ffn: weights live on different devices");
+        check_ffn_args("mfqb_moe_ffn", gate_up, down, tokens, routes);
         if (tokens <= 0) return;
         DeviceGuard guard(gate_up->info.device);
-        const size_t pairs = (size_t)tokens * routes;
-        const size_t b_gu = pairs * f2 * 4, b_hid = (pairs * f * 2 + 255) / 256 * 256, b_dn = pairs * h * 4;
-        // large batches: both matmuls on the tensor-core tile kernel, when every cohort of both has one
-        const int gemm_bn = std::min(moe_gemm_bn(gate_up, (int)pairs), moe_gemm_bn(down, (int)pairs));
-        const bool gemm = gemm_bn != 0;
-        const int tile_m = gemm ? gemm_bn : std::min(moe_tile_m(gate_up, (int)pairs), moe_tile_m(down, (int)pairs));
-        const bool tiles = tile_m != 0;
-        const size_t b_plan = tiles ? PlanBufs::bytes(gate_up->info.n_experts, pairs) : 0;
-        const size_t b_pgu = gemm ? (nint_gemm_grouped_x_bytes((int)pairs, h) + 255) / 256 * 256 : (tiles ? moe_planes_bytes(gate_up, tokens) : 0);
-        const size_t b_pdn = gemm ? nint_gemm_grouped_x_bytes((int)pairs, f) : (tiles ? moe_planes_bytes(down, (int)pairs) : 0);
-        char* s = static_cast<char*>(scratch_get(gate_up->info.device, b_gu + b_hid + b_dn + b_plan + b_pgu + b_pdn, stream));
-        float* gu = reinterpret_cast<float*>(s);
-        void* hid = s + b_gu;
-        float* dn = reinterpret_cast<float*>(s + b_gu + b_hid);
-        PlanBufs plan{};
-        if (tiles) {   // one route plan serves both matmuls
-            plan = PlanBufs::carve(s + b_gu + b_hid + b_dn, gate_up->info.n_experts);
-            launch_route_plan(ids, (int)pairs, gate_up->info.n_experts, tile_m, plan.expert_bounds, plan.tile_bounds, plan.pair_order, stream);
-        }
-        char* planes = s + b_gu + b_hid + b_dn + b_plan;
-        mul_mat_id_impl(gate_up, x, 0, ids, tokens, routes, gu, MFQB_F32, tiles ? &plan : nullptr, tile_m, planes, stream, gemm);
-        launch_swiglu(gu, MFQB_F32, (int)pairs, f, hid, stream);
-        mul_mat_id_impl(down, hid, 1, ids, tokens, routes, dn, MFQB_F32, tiles ? &plan : nullptr, tile_m, planes + b_pgu, stream, gemm);
-        launch_weighted_reduce(dn, MFQB_F32, weights, tokens, routes, h, y, y_dtype, stream);
+        const FfnLayout L = ffn_layout(gate_up, down, tokens, routes, true);
+        char* s = static_cast<char*>(scratch_get(gate_up->info.device, L.total, stream));
+        moe_ffn_run(gate_up, down, x, ids, weights, tokens, routes, y, y_dtype, s, L, stream);
     });
 }
 
@@ -473,42 +561,22 @@ int mfqb_moe_ffn_static(const mfqb_moe_weight* gate_up, const mfqb_moe_weight* d
                         const float* weights, int tokens, int routes, void* y, int y_dtype, mfqb_stream_t stream) {
     return guarded([&] {
         if (!gate_up || !down || !x || !ids || !weights || !y) fail(MFQB_ERR_ARG, "mfqb_moe_ffn_static: null argument");
-        const int h = gate_up->info.k, f2 = gate_up->info.out_per_expert, f = f2 / 2;
-        if (f2 % 2 || down->info.k != f || down->info.out_per_expert != h || down->info.n_experts != gate_up->info.n_experts)
-            fail(MFQB_ERR_ARG, "mfqb_moe_ffn_static: gate_up [E, 2F, H] and down [E, H, F] shapes do not match");
-        if (gate_up->info.device != down->info.device) fail(MFQB_ERR_ARG, "mfqb_moe_ffn_static: weights live on different devices");
-        if (tokens <= 0 || routes < 1) return;
-        const size_t pairs = (size_t)tokens * routes;
-        const size_t b_gu = pairs * f2 * 4, b_hid = (pairs * f * 2 + 255) / 256 * 256, b_dn = pairs * h * 4;
-        const int tile_m = std::min(moe_tile_m(gate_up, (int)pairs), moe_tile_m(down, (int)pairs));
-        const bool tiles = tile_m != 0;
-        const size_t b_plan = tiles ? PlanBufs::bytes(gate_up->info.n_experts, pairs) + moe_planes_bytes(gate_up, tokens) +
-                                          moe_planes_bytes(down, (int)pairs)
-                                    : 0;
-        const size_t b_pgu = tiles ? moe_planes_bytes(gate_up, tokens) : 0;
-        if (b_gu + b_hid + b_dn + b_plan > (size_t)MFQB_STATIC_SCRATCH_BYTES)
+        check_ffn_args("mfqb_moe_ffn_static", gate_up, down, tokens, routes);
+        if (tokens <= 0) return;
+        // the tensor-core tile path keeps its own growing buffers: this entry point stays on the integer kernels
+        const FfnLayout L = ffn_layout(gate_up, down, tokens, routes, false);
+        if (L.total > (size_t)MFQB_STATIC_SCRATCH_BYTES)
             fail(MFQB_ERR_ARG,
                  "mfqb_moe_ffn_static: %d tokens x %d routes need %llu bytes of scratch, the built-in array holds %llu; "
                  "use mfqb_moe_ffn or fewer tokens per call",
-                 tokens, routes, (unsigned long long)(b_gu + b_hid + b_dn + b_plan), (unsigned long long)MFQB_STATIC_SCRATCH_BYTES);
+                 tokens, routes, (unsigned long long)L.total, (unsigned long long)MFQB_STATIC_SCRATCH_BYTES);
         DeviceGuard guard(gate_up->info.device);
         unsigned char* s = ffn_static_scratch(gate_up->info.device);
-        // The array still holds whatever the previous call left: start the two accumulation targets
-        // from zero so that a route to an expert nobody holds contributes nothing.
-        MFQB_CUDA(cudaMemsetAsync(s, 0, b_gu + b_hid + b_dn + b_plan, stream));
-        float* gu = reinterpret_cast<float*>(s);
-        void* hid = s + b_gu;
-        float* dn = reinterpret_cast<float*>(s + b_gu + b_hid);
-        PlanBufs plan{};
-        if (tiles) {   // the route plan lives in the same fixed array
-            plan = PlanBufs::carve(s + b_gu + b_hid + b_dn, gate_up->info.n_experts);
-            launch_route_plan(ids, (int)pairs, gate_up->info.n_experts, tile_m, plan.expert_bounds, plan.tile_bounds, plan.pair_order, stream);
-        }
-        char* planes = reinterpret_cast<char*>(s) + b_gu + b_hid + b_dn + (tiles ? PlanBufs::bytes(gate_up->info.n_experts, pairs) : 0);   // inside the fixed array, after the plan
-        mul_mat_id_impl(gate_up, x, 0, ids, tokens, routes, gu, MFQB_F32, tiles ? &plan : nullptr, tile_m, planes, stream);
-        launch_swiglu(gu, MFQB_F32, (int)pairs, f, hid, stream);
-        mul_mat_id_impl(down, hid, 1, ids, tokens, routes, dn, MFQB_F32, tiles ? &plan : nullptr, tile_m, planes + b_pgu, stream);
-        launch_weighted_reduce(dn, MFQB_F32, weights, tokens, routes, h, y, y_dtype, stream);
+        // The array still holds whatever the previous call left.  Only the route-sum counters must start at
+        // zero (every other region is fully written before it is read); they are left zero by every
+        // completed call, so this matters after a call that was interrupted.
+        MFQB_CUDA(cudaMemsetAsync(s, 0, kFfnCounterBytes, stream));
+        moe_ffn_run(gate_up, down, x, ids, weights, tokens, routes, y, y_dtype, reinterpret_cast<char*>(s), L, stream);
     });
 }
 

@@ -27,24 +27,28 @@ constexpr bool hetero_has_codec(int bits, int t8) {
            (bits == 8 && t8 == 3) || (bits == 8 && t8 == 6);
 }
 
+template <int XMODE>
 __global__ void __launch_bounds__(256, 2) moe_hetero_gemv1_kernel(const __grid_constant__ HeteroArgs h) {
     extern __shared__ __align__(16) unsigned char smem[];
     pdl_wait_b();   // the routing table comes from the previous kernel
     const int e = h.base.route_ids[blockIdx.y];
-    if (e < 0) return;
-    const int pool = h.base.expert_pool[e];
-    if (pool < 0) return;
+    // an id outside [0, n_experts) is ignored like a route to an expert that is not held here
+    const int pool = (e >= 0 && e < h.base.n_experts) ? h.base.expert_pool[e] : -1;
+    if (pool < 0) {
+        if (h.base.route_w != nullptr) routed_absent_pair(h.base, blockIdx.y);
+        return;
+    }
     GemvArgsB a = h.base;
     a.pool = pool;
     const NintDevB& w = h.pools[pool];
     switch (w.bits * 16 + w.t8) {
-        case 2 * 16 + 2: gemv1_bl_body<NintCodec<2, 2>>(a, w, smem); break;
-        case 3 * 16 + 3: gemv1_bl_body<NintCodec<3, 3>>(a, w, smem); break;
-        case 4 * 16 + 3: gemv1_bl_body<NintCodec<4, 3>>(a, w, smem); break;
-        case 5 * 16 + 4: gemv1_bl_body<NintCodec<5, 4>>(a, w, smem); break;
-        case 6 * 16 + 3: gemv1_bl_body<NintCodec<6, 3>>(a, w, smem); break;
-        case 8 * 16 + 3: gemv1_bl_body<NintCodec<8, 3>>(a, w, smem); break;
-        case 8 * 16 + 6: gemv1_bl_body<NintCodec<8, 6>>(a, w, smem); break;
+        case 2 * 16 + 2: gemv1_bl_body<NintCodec<2, 2>, XMODE>(a, w, smem); break;
+        case 3 * 16 + 3: gemv1_bl_body<NintCodec<3, 3>, XMODE>(a, w, smem); break;
+        case 4 * 16 + 3: gemv1_bl_body<NintCodec<4, 3>, XMODE>(a, w, smem); break;
+        case 5 * 16 + 4: gemv1_bl_body<NintCodec<5, 4>, XMODE>(a, w, smem); break;
+        case 6 * 16 + 3: gemv1_bl_body<NintCodec<6, 3>, XMODE>(a, w, smem); break;
+        case 8 * 16 + 3: gemv1_bl_body<NintCodec<8, 3>, XMODE>(a, w, smem); break;
+        case 8 * 16 + 6: gemv1_bl_body<NintCodec<8, 6>, XMODE>(a, w, smem); break;
         default: break;
     }
 }
@@ -149,6 +153,12 @@ bool launch_moe_hetero_tiles(GemvArgsB base, const NintDevB* pools, const int* h
     return true;
 }
 
+// CTAs per pair (row splits) the all-cohort single-row launch uses for `pairs` pairs.
+int moe_hetero_gemv1_splits(int rb_per_expert, int pairs, int device) {
+    const int want = (2 * device_sm_count(device) + pairs - 1) / std::max(pairs, 1);
+    return std::max(1, std::min(rb_per_expert, want));
+}
+
 // Launches the routed single-row matmul for all `npools` cohorts at once; returns false when a
 // cohort has no codec in this kernel (the caller then launches cohort by cohort).
 bool launch_moe_hetero_gemv1(GemvArgsB base, const NintDevB* pools, const int* held, int npools, int pairs, int device, cudaStream_t s) {
@@ -162,16 +172,16 @@ bool launch_moe_hetero_gemv1(GemvArgsB base, const NintDevB* pools, const int* h
         ring = std::max(ring, (size_t)8 * gemv1_bl_stages(pools[i].rec_words) * pools[i].rec_words * 4);
     }
     base.m = 1;
-    const int want = (2 * device_sm_count(device) + pairs - 1) / std::max(pairs, 1);
-    const int splits = std::max(1, std::min(base.rb_per_expert, want));
+    const int splits = moe_hetero_gemv1_splits(base.rb_per_expert, pairs, device);
     base.rb_per_cta = (base.rb_per_expert + splits - 1) / splits;
     base.private_sums = base.rb_per_cta <= 8;
     h.base = base;
     const size_t smem = (size_t)((base.private_sums ? 8 : 1) + 1) * base.rb_per_cta * 16 * 4 + ring;
-    static bool attr_set[64] = {false};
-    if (smem > 48 * 1024 && !attr_set[device]) {
-        MFQB_CUDA(cudaFuncSetAttribute(moe_hetero_gemv1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        attr_set[device] = true;
+    auto kernel = base.x_mode == 2 ? moe_hetero_gemv1_kernel<2> : (base.x_mode == 1 ? moe_hetero_gemv1_kernel<1> : moe_hetero_gemv1_kernel<0>);
+    static bool attr_set[3][64] = {};
+    if (smem > 48 * 1024 && !attr_set[base.x_mode][device]) {
+        MFQB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        attr_set[base.x_mode][device] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)splits, (unsigned)pairs);
@@ -183,7 +193,7 @@ bool launch_moe_hetero_gemv1(GemvArgsB base, const NintDevB* pools, const int* h
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    MFQB_CUDA(cudaLaunchKernelEx(&cfg, moe_hetero_gemv1_kernel, h));
+    MFQB_CUDA(cudaLaunchKernelEx(&cfg, kernel, h));
     return true;
 }
 

@@ -76,6 +76,84 @@ __global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__
     if (lane < k) weights[(size_t)row * k + lane] = v * scale;
 }
 
+// The same selection for up to 32 * EPL experts: a lane keeps its experts' weights and scores in
+// registers (computed once), and a bit per expert marks the ones already chosen.  Same operations in
+// the same order as moe_topk_kernel, so both give identical ids and weights.
+template <int EPL>
+__global__ void __launch_bounds__(128) moe_topk_regs_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+                                                             int32_t* __restrict__ ids, float* __restrict__ weights, int tokens,
+                                                             int experts, int k, int mode, int normalize, float norm_floor,
+                                                             float scale) {
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= tokens) return;
+    const float* z = logits + (size_t)row * experts;
+    float raw[EPL], bs_add[EPL];
+    unsigned taken = 0u;   // bit j: expert lane + 32 j is out of range or already chosen
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+        const int e = lane + 32 * j;
+        const bool ok = e < experts;
+        const float v = ok ? z[e] : 0.f;
+        raw[j] = isnan(v) ? -FLT_MAX : v;
+        bs_add[j] = (ok && bias) ? bias[e] : 0.f;
+        if (!ok) taken |= 1u << j;
+    }
+    float smax = 0.f, ssum = 1.f;
+    if (mode == MFQB_ROUTER_SOFTMAX) {
+        smax = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < EPL; ++j)
+            if (!((taken >> j) & 1u)) smax = fmaxf(smax, raw[j]);
+        for (int o = 16; o; o >>= 1) smax = fmaxf(smax, __shfl_xor_sync(0xffffffffu, smax, o));
+        ssum = 0.f;
+#pragma unroll
+        for (int j = 0; j < EPL; ++j)
+            if (!((taken >> j) & 1u)) ssum += expf(raw[j] - smax);
+        for (int o = 16; o; o >>= 1) ssum += __shfl_xor_sync(0xffffffffu, ssum, o);
+    }
+    float wg[EPL], sc[EPL];
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+        float wv;
+        if (mode == MFQB_ROUTER_DELAYED_SOFTMAX) wv = raw[j];
+        else if (mode == MFQB_ROUTER_SIGMOID) wv = 1.0f / (1.0f + expf(-raw[j]));
+        else if (mode == MFQB_ROUTER_SQRT_SOFTPLUS) wv = sqrtf(raw[j] > 20.0f ? raw[j] : log1pf(expf(raw[j])));
+        else wv = expf(raw[j] - smax) / ssum;
+        wg[j] = wv;
+        sc[j] = wv + bs_add[j];
+    }
+    float my_weight = 0.f;   // lane r keeps the weight of rank r
+    for (int r = 0; r < k; ++r) {
+        float bs = -INFINITY, bw = -INFINITY;
+        int be = INT_MAX;
+#pragma unroll
+        for (int j = 0; j < EPL; ++j)
+            if (!((taken >> j) & 1u) && score_before(sc[j], lane + 32 * j, bs, be)) { bs = sc[j]; bw = wg[j]; be = lane + 32 * j; }
+        for (int o = 16; o; o >>= 1) {
+            const float os = __shfl_xor_sync(0xffffffffu, bs, o), ow = __shfl_xor_sync(0xffffffffu, bw, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+            if (score_before(os, oe, bs, be)) { bs = os; bw = ow; be = oe; }
+        }
+        if (lane == (be & 31)) taken |= 1u << (be >> 5);
+        if (lane == r) my_weight = bw;
+        if (lane == 0) ids[(size_t)row * k + r] = be;
+    }
+    float v = lane < k ? my_weight : 0.f;
+    if (mode == MFQB_ROUTER_DELAYED_SOFTMAX) {
+        float m = lane < k ? v : -INFINITY;
+        for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        v = lane < k ? expf(v - m) : 0.f;
+        float d = v;
+        for (int o = 16; o; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        v /= d;
+    } else if (normalize) {
+        float d = v;
+        for (int o = 16; o; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        v /= fmaxf(d, norm_floor);
+    }
+    if (lane < k) weights[(size_t)row * k + lane] = v * scale;
+}
+
 // ---- route plan ------------------------------------------------------------------------------
 // counts -> exclusive scan -> stable placement (one warp per expert walks the pairs in order),
 // so every expert's segment lists its pairs in ascending order: the plan is deterministic.
@@ -168,13 +246,15 @@ __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
-template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gate_up, int rows, int f, __nv_bfloat16* __restrict__ hidden) {
+template <typename T, typename O>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, int rows, int f, O* __restrict__ hidden) {
     const size_t total = (size_t)rows * f;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t r = i / f, j = i % f;
         const float g = to_f32(gate_up[r * 2 * f + j]), u = to_f32(gate_up[r * 2 * f + f + j]);
-        hidden[i] = __float2bfloat16_rn(u * g / (1.0f + expf(-g)));
+        const float v = u * g / (1.0f + expf(-g));
+        if constexpr (sizeof(O) == 4) hidden[i] = v;
+        else hidden[i] = __float2bfloat16_rn(v);
     }
 }
 
@@ -195,8 +275,17 @@ void launch_swiglu(const void* gate_up, int in_dtype, int rows, int f, void* hid
     const size_t total = (size_t)rows * f;
     if (total == 0) return;
     const int block = 256, grid = (int)std::min<size_t>((total + block - 1) / block, 148 * 8);
-    if (in_dtype == MFQB_F32) swiglu_kernel<float><<<grid, block, 0, s>>>(static_cast<const float*>(gate_up), rows, f, static_cast<__nv_bfloat16*>(hidden));
-    else swiglu_kernel<__nv_bfloat16><<<grid, block, 0, s>>>(static_cast<const __nv_bfloat16*>(gate_up), rows, f, static_cast<__nv_bfloat16*>(hidden));
+    if (in_dtype == MFQB_F32) swiglu_kernel<float, __nv_bfloat16><<<grid, block, 0, s>>>(static_cast<const float*>(gate_up), rows, f, static_cast<__nv_bfloat16*>(hidden));
+    else swiglu_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, block, 0, s>>>(static_cast<const __nv_bfloat16*>(gate_up), rows, f, static_cast<__nv_bfloat16*>(hidden));
+    MFQB_CUDA(cudaGetLastError());
+}
+
+// float32 gate|up -> float32 activation (the library's own intermediate: no rounding between the two expert matmuls)
+void launch_swiglu_f32(const float* gate_up, int rows, int f, float* hidden, cudaStream_t s) {
+    const size_t total = (size_t)rows * f;
+    if (total == 0) return;
+    const int block = 256, grid = (int)std::min<size_t>((total + block - 1) / block, 148 * 8);
+    swiglu_kernel<float, float><<<grid, block, 0, s>>>(gate_up, rows, f, hidden);
     MFQB_CUDA(cudaGetLastError());
 }
 
@@ -244,8 +333,11 @@ int mfqb_moe_topk(const float* logits, int tokens, int experts, int k, int mode,
         if (k < 1 || k > 16 || k > experts) fail(MFQB_ERR_ARG, "mfqb_moe_topk: top_k must be in [1, min(16, experts)]");
         if (mode < 0 || mode > 3) fail(MFQB_ERR_ARG, "mfqb_moe_topk: unknown router mode %d", mode);
         if (tokens == 0) return;
-        moe_topk_kernel<<<(tokens + 3) / 4, 128, 0, stream>>>(logits, bias, ids, weights, tokens, experts, k, mode, normalize,
-                                                             norm_floor, scale);
+        const dim3 grid((tokens + 3) / 4), block(128);
+        if (experts <= 128) moe_topk_regs_kernel<4><<<grid, block, 0, stream>>>(logits, bias, ids, weights, tokens, experts, k, mode, normalize, norm_floor, scale);
+        else if (experts <= 256) moe_topk_regs_kernel<8><<<grid, block, 0, stream>>>(logits, bias, ids, weights, tokens, experts, k, mode, normalize, norm_floor, scale);
+        else if (experts <= 512) moe_topk_regs_kernel<16><<<grid, block, 0, stream>>>(logits, bias, ids, weights, tokens, experts, k, mode, normalize, norm_floor, scale);
+        else moe_topk_kernel<<<grid, block, 0, stream>>>(logits, bias, ids, weights, tokens, experts, k, mode, normalize, norm_floor, scale);
         MFQB_CUDA(cudaGetLastError());
     });
 }

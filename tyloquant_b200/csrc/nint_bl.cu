@@ -1,6 +1,7 @@
 // Byte-lane NINT: decoder kernel and the launch planning of the GEMV kernels.
 #include <algorithm>
 #include <mutex>
+#include <type_traits>
 
 #include "common.h"
 #include "cuda_util.h"
@@ -125,8 +126,9 @@ size_t nint_bl_planes_bytes(const NintDevB& w, int rows) {
     return (size_t)rows * w.nchunks * kChunkGroupsB * (gemv1_bl_qstride(w.t8) + 1) * 8;
 }
 
-// Quantises x [rows, k] into `planes` (nint_bl_planes_bytes): xq for all rows, then gtab.
-void launch_x_planes(const NintDevB& w, const void* x, int rows, void* planes, const uint2** xq_g, const float2** gtab_g, cudaStream_t s) {
+// Quantises x [rows, k] (bf16, or float32 when x_f32) into `planes` (nint_bl_planes_bytes): xq for all rows, then gtab.
+void launch_x_planes(const NintDevB& w, const void* x, int rows, void* planes, const uint2** xq_g, const float2** gtab_g, cudaStream_t s,
+                     bool x_f32) {
     const int ngp = w.nchunks * kChunkGroupsB, qs = gemv1_bl_qstride(w.t8);
     uint2* xq = static_cast<uint2*>(planes);
     float2* gtab = reinterpret_cast<float2*>(xq + (size_t)rows * ngp * qs);
@@ -134,14 +136,18 @@ void launch_x_planes(const NintDevB& w, const void* x, int rows, void* planes, c
     *gtab_g = gtab;
     // 64 groups per CTA: one pass of its 256 threads (four threads per group)
     const dim3 grid((unsigned)((ngp + 63) / 64), (unsigned)rows);
-    const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
+    auto go = [&](auto t8) {
+        constexpr int T = decltype(t8)::value;
+        if (x_f32) x_planes_kernel<T, float><<<grid, 256, 0, s>>>(static_cast<const float*>(x), w.k, w.gs, ngp, 64, xq, gtab);
+        else x_planes_kernel<T, __nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), w.k, w.gs, ngp, 64, xq, gtab);
+    };
     switch (w.t8) {
-        case 2: x_planes_kernel<2><<<grid, 256, 0, s>>>(xb, w.k, w.gs, ngp, 64, xq, gtab); break;
-        case 3: x_planes_kernel<3><<<grid, 256, 0, s>>>(xb, w.k, w.gs, ngp, 64, xq, gtab); break;
-        case 4: x_planes_kernel<4><<<grid, 256, 0, s>>>(xb, w.k, w.gs, ngp, 64, xq, gtab); break;
-        case 5: x_planes_kernel<5><<<grid, 256, 0, s>>>(xb, w.k, w.gs, ngp, 64, xq, gtab); break;
-        case 6: x_planes_kernel<6><<<grid, 256, 0, s>>>(xb, w.k, w.gs, ngp, 64, xq, gtab); break;
-        case 8: x_planes_kernel<8><<<grid, 256, 0, s>>>(xb, w.k, w.gs, ngp, 64, xq, gtab); break;
+        case 2: go(std::integral_constant<int, 2>{}); break;
+        case 3: go(std::integral_constant<int, 3>{}); break;
+        case 4: go(std::integral_constant<int, 4>{}); break;
+        case 5: go(std::integral_constant<int, 5>{}); break;
+        case 6: go(std::integral_constant<int, 6>{}); break;
+        case 8: go(std::integral_constant<int, 8>{}); break;
         default: fail(MFQB_ERR_UNSUPPORTED, "group size %d has no kernel", w.gs);
     }
     MFQB_CUDA(cudaGetLastError());
@@ -162,8 +168,9 @@ int nint_bl_max_passes(const NintDevB& w) {
     return 1;
 }
 
-// y[m, n] = x[m, k] * W^T for m <= 8 (the caller loops larger batches)
-void launch_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtype, int ldy, int device, cudaStream_t s) {
+// y[m, n] = x[m, k] * W^T for m <= 8 (the caller loops larger batches).  swiglu (m = 1 only): x is the
+// float32 gate|up row [2k] and the product is taken with up * silu(gate).
+void launch_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtype, int ldy, int device, cudaStream_t s, bool swiglu) {
     GemvArgsB a{};
     a.w = w;
     a.x = static_cast<const __nv_bfloat16*>(x);
@@ -181,16 +188,21 @@ void launch_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtyp
         a.rb_per_cta = (w.nrb + p.grid - 1) / p.grid;
         a.private_sums = gemv1_private_sums(a.rb_per_cta);
         p.smem = gemv1_smem(w, a.rb_per_cta, warps);
+        if (swiglu) {
+            p.passes = -2;
+            a.x_mode = 2;
+        }
     } else {
+        if (swiglu) fail(MFQB_ERR_ARG, "the fused activation belongs to the single-row kernel");
         const int max_rows = 2 * nint_bl_max_passes(w);
         if (m > max_rows) {   // wide records: the batch goes through in several launches
             const size_t ysz = y_dtype == MFQB_F32 ? 4 : 2;
             for (int m0 = 0; m0 < m; m0 += max_rows)
                 launch_bl_gemv(w, static_cast<const char*>(x) + (size_t)m0 * w.k * 2, std::min(max_rows, m - m0),
-                               static_cast<char*>(y) + (size_t)m0 * ldy * ysz, y_dtype, ldy, device, s);
+                               static_cast<char*>(y) + (size_t)m0 * ldy * ysz, y_dtype, ldy, device, s, false);
             return;
         }
-        launch_x_planes(w, x, m, planes_scratch(device, nint_bl_planes_bytes(w, m), s), &a.xq_g, &a.gtab_g, s);
+        launch_x_planes(w, x, m, planes_scratch(device, nint_bl_planes_bytes(w, m), s), &a.xq_g, &a.gtab_g, s, false);
         p.passes = passes_for(m);
         // at least two row-blocks per CTA where the matrix allows: a chunk's planes then serve several items
         const int cap = ctas_per_sm(gemvn_smem(w, 2, p.passes), p.passes == 4 ? 2 : 3) * sms;
@@ -248,7 +260,8 @@ bool launch_bl_gemvs(const NintDevB& w, const void* x, int x_dtype, void* y, int
         if (warps * 32 > gemvs_max_threads(w.wc)) continue;
         const long long n_w = (n_b + warps - 1) / warps;
         const int maxseg = (int)((n_w - 1) / w.nchunks) + 2;
-        const size_t fixed = planes + (size_t)warps * maxseg * 64 + 16;
+        const int maxrb = (int)(n_b / w.nchunks) + 2;
+        const size_t fixed = planes + (size_t)warps * maxseg * 64 + (size_t)(maxrb + 3) / 4 * 16 + 16;
         if (fixed >= t.budget) continue;
         int stages = (int)std::min<size_t>(8, (t.budget - fixed) / (warps * (recb + 8)));
         stages = (int)std::min<long long>(stages, std::max<long long>(n_w, 1));
@@ -259,6 +272,7 @@ bool launch_bl_gemvs(const NintDevB& w, const void* x, int x_dtype, void* y, int
         p.smem = fixed + (size_t)warps * stages * (recb + 8);
         a.stages = stages;
         a.maxseg = maxseg;
+        a.maxrb = maxrb;
         found = true;
         break;
     }
@@ -277,6 +291,40 @@ bool launch_bl_gemvs(const NintDevB& w, const void* x, int x_dtype, void* y, int
     if (e != cudaSuccess) fail(MFQB_ERR_CUDA, "NINT%d gs=%d streamed GEMV launch (%d x %d threads, %zu bytes): %s", w.bits, w.gs, p.grid, p.threads, p.smem,
                                cudaGetErrorString(e));
     return true;
+}
+
+// Several weights of one shape class applied to the same activation row in one launch (q|k|v, gate|up:
+// the reference's NintLinearGroup, cpp_runtime/mfq_decode.cpp:8618-8743): grid = (CTAs per weight, weights).
+void launch_bl_gemv_multi(const NintDevB* ws, void* const* ys, int count, const void* x, int y_dtype, int device, cudaStream_t s) {
+    if (count < 1 || count > kGemvMultiMax) fail(MFQB_ERR_ARG, "a multi-weight launch takes 1 to %d weights, got %d", kGemvMultiMax, count);
+    GemvArgsB a{};
+    a.w = ws[0];
+    a.x = static_cast<const __nv_bfloat16*>(x);
+    a.m = 1;
+    a.y_dtype = y_dtype;
+    a.multi_count = count;
+    int max_nrb = 0;
+    for (int i = 0; i < count; ++i) {
+        const NintDevB& w = ws[i];
+        if (w.table || w.bits != ws[0].bits || w.gs != ws[0].gs || w.k != ws[0].k || w.rec_words != ws[0].rec_words)
+            fail(MFQB_ERR_ARG, "the weights of a multi-weight launch must share family, code width, group size and k");
+        a.multi[i] = GemvMultiEntry{w.items, w.anchors, ys[i], w.n, w.nrb};
+        max_nrb = std::max(max_nrb, w.nrb);
+    }
+    a.ldy = 0;
+    GemvPlanB p;
+    const int warps = gemv1_warps(ws[0]), sms = device_sm_count(device);
+    p.threads = warps * 32;
+    p.passes = -1;
+    // all CTAs resident at once: the SMs' slots shared out over the weights
+    const int per_weight = std::max(1, ctas_per_sm(gemv1_smem(ws[0], 1, warps), warps > 8 ? 2 : 3) * sms / count);
+    p.grid = std::min(max_nrb, per_weight);
+    p.grid_y = count;
+    a.rb_per_cta = (max_nrb + p.grid - 1) / p.grid;
+    a.private_sums = gemv1_private_sums(a.rb_per_cta);
+    p.smem = gemv1_smem(ws[0], a.rb_per_cta, warps);
+    if (p.smem > kGemvSmemLimit) fail(MFQB_ERR_UNSUPPORTED, "multi-weight launch: %d row-blocks per CTA do not fit shared memory", a.rb_per_cta);
+    dispatch(a, p, s, "multi-weight GEMV");
 }
 
 // Single-row product whose epilogue reduces over ranks (row-parallel shards): see PeerReduce.

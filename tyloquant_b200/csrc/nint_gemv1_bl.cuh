@@ -26,6 +26,15 @@
 
 namespace mfqb {
 
+// One weight of a multi-weight launch (several weights of one shape class applied to the same x).
+struct GemvMultiEntry {
+    const uint32_t* items;
+    const uint32_t* anchors;
+    void* y;
+    int n, nrb;
+};
+constexpr int kGemvMultiMax = 8;
+
 struct GemvArgsB {
     NintDevB w;
     const __nv_bfloat16* x;  // [m, k]
@@ -52,6 +61,23 @@ struct GemvArgsB {
     // Single-row kernel, row-parallel product: when reduce.world > 0 the CTA's summed rows are this
     // rank's partial result; they go to the peers and the sum over ranks is written to y.
     PeerReduce reduce;
+    // Single-row kernel, expert FFN: x_mode 1 reads x as float32 [rows, k]; x_mode 2 reads the gate|up
+    // products of the pair, float32 [pairs, 2k] (gate columns first), and forms the SwiGLU activation
+    // up * gate / (1 + exp(-gate)) while loading (mfq/kernels/cuda/glu.cuh:6-17) -- the activation is
+    // never stored.  With route_w set, the routed product also ends the FFN: a CTA writes its rows to
+    // pair_out [pairs, ldy] float32, and the last of a token's `routes` CTAs to arrive adds them with
+    // the route weights, in route order, into y_final [tokens, ldy] (moe_weighted_reduce,
+    // mfq/kernels/cuda/moe.cu:2957-2977).  token_count: [tokens * gridDim.x] zeros, left zero again.
+    // Single-row kernel, multi-weight launch: blockIdx.y selects one of multi_count weights that share
+    // x, the code width, the group size and k (w then describes their common geometry).
+    int multi_count;
+    GemvMultiEntry multi[kGemvMultiMax];
+    int x_mode;
+    const float* route_w;
+    float* pair_out;
+    unsigned* token_count;
+    void* y_final;
+    int y_final_dtype;
     // Batched kernel: the activation rows already quantised by x_planes_kernel, row r at
     // xq_g + r * ngp * QS and gtab_g + r * ngp (ngp = nchunks * 8 groups, QS quads per group).
     const uint2* xq_g;
@@ -159,11 +185,12 @@ constexpr float kXScaleUndo = 16777216.f;   // 2^24
 // Quantises groups [g0, g0 + ngroups) of one activation row into shared memory (ngroups a multiple
 // of 8): xq[gl * QS + j] = (low bytes, high bytes) of the four slots 4j..4j+3 of group g0 + gl,
 // gtab[gl] = (sx_g, sx_g * X_g).  Four threads per group; every thread of the CTA must call it.
-template <int T>
-__device__ __forceinline__ void stage_x_planes(const __nv_bfloat16* __restrict__ xrow, int k, int gs, int g0, int ngroups, uint2* xq,
+template <int T, typename XT = __nv_bfloat16>
+__device__ __forceinline__ void stage_x_planes(const XT* __restrict__ xrow, int k, int gs, int g0, int ngroups, uint2* xq,
                                                float2* gtab) {
     constexpr int QS = gemv1_bl_qstride(T);
-    const bool vec_ok = (reinterpret_cast<uintptr_t>(xrow) & 7) == 0;
+    constexpr uint32_t SH = sizeof(XT) == 2 ? 0u : 1u;   // float32 rows: one bit of head-room (a magnitude could round up to 2^15)
+    const bool vec_ok = sizeof(XT) == 2 && (reinterpret_cast<uintptr_t>(xrow) & 7) == 0;
     for (int u = threadIdx.x; u < ngroups * 4; u += blockDim.x) {
         const int gl = u >> 2, g = g0 + gl, c = u & 3;
         float v[(2 * T + 3) / 4][4];
@@ -183,7 +210,7 @@ __device__ __forceinline__ void stage_x_planes(const __nv_bfloat16* __restrict__
                 } else {
 #pragma unroll
                     for (int i = 0; i < 4; ++i)
-                        if (4 * j + i < gs && k0 + i < k) v[jj][i] = __bfloat162float(xrow[k0 + i]);
+                        if (4 * j + i < gs && k0 + i < k) v[jj][i] = (float)xrow[k0 + i];
                 }
             }
 #pragma unroll
@@ -193,8 +220,8 @@ __device__ __forceinline__ void stage_x_planes(const __nv_bfloat16* __restrict__
         ab = max(ab, __shfl_xor_sync(0xffffffffu, ab, 2));
         const uint32_t eb = max(ab >> 23, 15u + kXScaleShift);
         // eb = 255: an infinity or NaN in the group; its scale becomes NaN and so does every output
-        const float sx = __uint_as_float(eb >= 255u ? 0x7FC00000u : (eb - 14u - kXScaleShift) << 23);
-        const float inv = __uint_as_float((268u - min(eb, 254u)) << 23);
+        const float sx = __uint_as_float(eb >= 255u ? 0x7FC00000u : (eb - 14u - kXScaleShift + SH) << 23);
+        const float inv = __uint_as_float((268u - SH - min(eb, 254u)) << 23);
         constexpr float kMagic = 12582912.f;   // 1.5 * 2^23: the low 16 mantissa bits hold round(x * inv) in two's complement
         float xs = 0.f;
 #pragma unroll
@@ -309,13 +336,136 @@ __device__ __forceinline__ void x_chunk_quant(const XChunkRaw<T>& raw, int c, ui
     gt.w = __shfl_sync(0xffffffffu, sxx, 8 * c + 4);
 }
 
+// Float32 forms of the two functions above (x_mode 1 and 2).  A float32 magnitude could round up to
+// 2^15 on the 16-bit grid, so these groups get one bit of head-room.
+template <int T>
+struct XChunkRawF {
+    static constexpr int JJ = (2 * T + 3) / 4;
+    float v[JJ][4];
+};
+template <int T, int XMODE>
+__device__ __forceinline__ void x_chunk_load_f(const float* __restrict__ xrow, int k, int gs, int g, int c, XChunkRawF<T>& raw) {
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(xrow) & 15) == 0 && (gs & 3) == 0 && (k & 3) == 0;
+#pragma unroll
+    for (int jj = 0; jj < XChunkRawF<T>::JJ; ++jj) {
+        const int j = c + 4 * jj, k0 = g * gs + 4 * j;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) raw.v[jj][i] = 0.f;
+        if (j < 2 * T && 4 * j < gs && k0 < k) {
+            float a[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {1.f, 1.f, 1.f, 1.f};
+            if (vec_ok && k0 + 3 < k) {
+                const float4 va = __ldg(reinterpret_cast<const float4*>(xrow + k0));
+                a[0] = va.x; a[1] = va.y; a[2] = va.z; a[3] = va.w;
+                if constexpr (XMODE == 2) {
+                    const float4 vu = __ldg(reinterpret_cast<const float4*>(xrow + k + k0));
+                    u[0] = vu.x; u[1] = vu.y; u[2] = vu.z; u[3] = vu.w;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (4 * j + i < gs && k0 + i < k) {
+                        a[i] = __ldg(xrow + k0 + i);
+                        if constexpr (XMODE == 2) u[i] = __ldg(xrow + k + k0 + i);
+                    }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if constexpr (XMODE == 2) raw.v[jj][i] = u[i] * a[i] / (1.0f + expf(-a[i]));
+                else raw.v[jj][i] = a[i];
+            }
+        }
+    }
+}
+template <int T>
+__device__ __forceinline__ void x_chunk_quant_f(const XChunkRawF<T>& raw, int c, uint32_t (&xlo)[T], uint32_t (&xhi)[T], float4& gt) {
+    constexpr int JJ = XChunkRawF<T>::JJ;
+    uint32_t ab = 0u;   // largest magnitude of the group as float bits (NaN is largest)
+#pragma unroll
+    for (int jj = 0; jj < JJ; ++jj)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) ab = max(ab, __float_as_uint(raw.v[jj][i]) & 0x7FFFFFFFu);
+    ab = max(ab, __shfl_xor_sync(0xffffffffu, ab, 1));
+    ab = max(ab, __shfl_xor_sync(0xffffffffu, ab, 2));
+    const uint32_t eb = max(ab >> 23, 15u + kXScaleShift);
+    const float sx = __uint_as_float(eb >= 255u ? 0x7FC00000u : (eb - 13u - kXScaleShift) << 23);   // NaN for a group holding inf or NaN
+    const float inv = __uint_as_float((267u - min(eb, 254u)) << 23);
+    constexpr float kMagic = 12582912.f;   // 1.5 * 2^23
+    uint32_t mine_lo[JJ], mine_hi[JJ];
+    int xsum_lo = 0, xsum_hi = 0;
+#pragma unroll
+    for (int jj = 0; jj < JJ; ++jj) {
+        const uint32_t f0 = __float_as_uint(fmaf(raw.v[jj][0], inv, kMagic)), f1 = __float_as_uint(fmaf(raw.v[jj][1], inv, kMagic));
+        const uint32_t f2 = __float_as_uint(fmaf(raw.v[jj][2], inv, kMagic)), f3 = __float_as_uint(fmaf(raw.v[jj][3], inv, kMagic));
+        const uint32_t t01 = __byte_perm(f0, f1, 0x5140), t23 = __byte_perm(f2, f3, 0x5140);
+        mine_lo[jj] = __byte_perm(t01, t23, 0x5410);
+        mine_hi[jj] = __byte_perm(t01, t23, 0x7632);
+        xsum_lo = (int)__dp4a(mine_lo[jj], 0x01010101u, (unsigned)xsum_lo);
+        xsum_hi = __dp4a((int)mine_hi[jj], 0x01010101, xsum_hi);
+    }
+    int xsi = xsum_hi * 256 + xsum_lo;
+    xsi += __shfl_xor_sync(0xffffffffu, xsi, 1);
+    xsi += __shfl_xor_sync(0xffffffffu, xsi, 2);
+    const float sxx = sx * (float)xsi;
+    const bool own_even = (c >> 1) == 0;
+#pragma unroll
+    for (int jj = 0; jj < JJ; ++jj) {
+        const uint32_t other_lo = __shfl_xor_sync(0xffffffffu, mine_lo[jj], 2), other_hi = __shfl_xor_sync(0xffffffffu, mine_hi[jj], 2);
+        if (2 * jj < T) {
+            xlo[2 * jj] = own_even ? mine_lo[jj] : other_lo;
+            xhi[2 * jj] = own_even ? mine_hi[jj] : other_hi;
+        }
+        if (2 * jj + 1 < T) {
+            xlo[2 * jj + 1] = own_even ? other_lo : mine_lo[jj];
+            xhi[2 * jj + 1] = own_even ? other_hi : mine_hi[jj];
+        }
+    }
+    gt.x = __shfl_sync(0xffffffffu, sx, 8 * c);
+    gt.y = __shfl_sync(0xffffffffu, sxx, 8 * c);
+    gt.z = __shfl_sync(0xffffffffu, sx, 8 * c + 4);
+    gt.w = __shfl_sync(0xffffffffu, sxx, 8 * c + 4);
+}
+
+// Routed product that also ends the expert FFN (GemvArgsB::route_w): this CTA's rows of its pair are in
+// pair_out; the last of the token's CTAs with this block index adds the token's routes and writes y_final.
+__device__ __forceinline__ void routed_finish_token(const GemvArgsB& a, int pair, int rbl0, int nrb, int row_limit) {
+    __shared__ unsigned s_old;
+    const int token = pair / a.routes;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_old = atomicAdd(a.token_count + (size_t)token * gridDim.x + blockIdx.x, 1u);
+    __syncthreads();
+    if (s_old != (unsigned)(a.routes - 1)) return;
+    __threadfence();
+    for (int i = threadIdx.x; i < nrb * 16; i += blockDim.x) {
+        const int row = rbl0 * 16 + i;
+        if (row < row_limit) {
+            float acc = 0.f;
+            for (int r = 0; r < a.routes; ++r)
+                acc += __ldg(a.route_w + (size_t)token * a.routes + r) * __ldcg(a.pair_out + ((size_t)token * a.routes + r) * a.ldy + row);
+            if (a.y_final_dtype == 0 /* MFQB_F32 */) reinterpret_cast<float*>(a.y_final)[(size_t)token * a.ldy + row] = acc;
+            else reinterpret_cast<__nv_bfloat16*>(a.y_final)[(size_t)token * a.ldy + row] = __float2bfloat16_rn(acc);
+        }
+    }
+    if (threadIdx.x == 0) a.token_count[(size_t)token * gridDim.x + blockIdx.x] = 0u;
+}
+// The same for a CTA whose pair's expert is not held here (expert-parallel shard): its rows count as zeros.
+__device__ __forceinline__ void routed_absent_pair(const GemvArgsB& a, int pair) {
+    int rbl0, nrb;
+    split_row_blocks(blockIdx.x, gridDim.x, a.rb_per_expert, rbl0, nrb);
+    for (int i = threadIdx.x; i < nrb * 16; i += blockDim.x) {
+        const int row = rbl0 * 16 + i;
+        if (row < a.ldy) a.pair_out[(size_t)pair * a.ldy + row] = 0.f;
+    }
+    routed_finish_token(a, pair, rbl0, nrb, a.ldy);
+}
+
 // Shared memory: partial sums [warps or 1][rb_per_cta][16] f32 | anchors [rb_per_cta][16] u32 |
 // per warp a ring of S item records.  With few row-blocks per CTA every warp adds into its own
 // copy of the partial sums (plain read-modify-write), else all share one through atomics.  Every warp streams its own items (chunk-major) through its ring with
 // 16-byte asynchronous copies; the first S items are requested before the kernel waits for its
 // predecessor in the stream, since weights are constants.  The activation row is read straight
 // from global memory, one chunk ahead, and quantised in registers by the warp that needs it.
-template <class C>
+template <class C, int XMODE = 0>
 __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB& w, unsigned char* smem) {
     constexpr int G = kChunkGroupsB, T = C::T, WC = C::WC, SW = C::SW, REC = (WC + SW) * 32;
     constexpr int S = gemv1_bl_stages(REC);
@@ -340,7 +490,7 @@ __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB
         if (e < 0 || a.expert_pool[e] != a.pool) return;
         rb_total = a.rb_per_expert;
         rb_base = a.expert_local[e] * a.rb_per_expert;
-        xrow += (size_t)(a.x_per_pair ? pair : pair / a.routes) * w.k;
+        if constexpr (XMODE == 0) xrow += (size_t)(a.x_per_pair ? pair : pair / a.routes) * w.k;
         y_off = (size_t)pair * a.ldy;
     }
     int rbl0, nrb;
@@ -348,15 +498,26 @@ __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB
     const int rb0 = rb_base + rbl0;
     const int row_limit = a.route_ids != nullptr ? a.ldy : w.n;   // rows this problem has (an expert's rows are padded to whole blocks)
 
-    // items of this warp, chunk-major: chunk = warp, warp + nwarps, ...; inside a chunk every
-    // row-block of the CTA.  Two cursors walk that sequence (issue runs S items ahead).
-    const int my_segs = warp < w.nchunks ? (w.nchunks - warp + nwarps - 1) / nwarps : 0;
-    const int n_mine = my_segs * nrb;
-    // the record pointer walks (chunk, row-block) incrementally: next row-block, or back to the CTA's
-    // first row-block of the warp's next chunk
+    // items of this warp, chunk-major: chunk = seg0, seg0 + cw, ...; inside a chunk the row-blocks
+    // rg, rg + rgroups, ... of the CTA.  Rows with at least as many chunks as the CTA has warps give every
+    // warp its own chunks and all row-blocks (cw = nwarps, one group); shorter rows (an expert's down
+    // projection) split the warps into groups that share the chunks and take the row-blocks in turn.
+    // Two cursors walk the sequence (issue runs S items ahead).
+    int cw = nwarps, rgroups = 1, seg0 = warp, rg = 0;
+    if (w.nchunks < nwarps) {
+        cw = w.nchunks;
+        rgroups = nwarps / cw;
+        rg = warp / cw;
+        seg0 = warp - rg * cw;
+    }
+    const int my_segs = rg < rgroups ? (w.nchunks - seg0 + cw - 1) / cw : 0;
+    const int my_rbs = rg < min(rgroups, nrb) ? (nrb - rg + rgroups - 1) / rgroups : 0;
+    const int n_mine = my_segs * my_rbs;
+    // the record pointer walks (chunk, row-block) incrementally: the warp's next row-block, or back to
+    // its first row-block of its next chunk
     int iss_i = 0, iss_rbl = 0, iss_stage = 0;
-    const uint32_t* iss_src = w.items + ((size_t)rb0 * w.nchunks + warp) * REC + lane * 4;
-    const long long step_rb = (long long)w.nchunks * REC, step_seg = (long long)nwarps * REC - (long long)(nrb - 1) * w.nchunks * REC;
+    const uint32_t* iss_src = w.items + ((size_t)(rb0 + rg) * w.nchunks + seg0) * REC + lane * 4;
+    const long long step_rb = (long long)rgroups * w.nchunks * REC, step_seg = (long long)cw * REC - (long long)(my_rbs - 1) * step_rb;
     auto issue = [&]() {
         if (iss_i < n_mine) {
             uint32_t* dst = ring + iss_stage * REC + lane * 4;
@@ -366,7 +527,7 @@ __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB
         }
         cp_async_commit_b();   // one group per item slot, empty past the end: keeps the wait count uniform
         ++iss_i;
-        if (++iss_rbl == nrb) { iss_rbl = 0; iss_src += step_seg; }
+        if (++iss_rbl == my_rbs) { iss_rbl = 0; iss_src += step_seg; }
         else iss_src += step_rb;
         if (++iss_stage == S) iss_stage = 0;
     };
@@ -394,15 +555,30 @@ __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB
     uint32_t xlo[T], xhi[T];
     float4 gt = make_float4(0.f, 0.f, 0.f, 0.f);   // (sx, sx*X) of groups 2c, 2c+1 of the chunk
     XChunkRaw<T> raw;                              // the activations of the warp's next chunk, requested one chunk ahead
-    if (n_mine > 0) x_chunk_load<T>(xrow, fast_ok && (warp + 1) * chunk_len <= w.k, vec_ok, w.k, w.gs, warp * G + q, c, raw);
+    XChunkRawF<T> rawf;
+    // float32 rows: [rows, k], or the pair's gate|up products [pairs, 2k]
+    const float* xrow_f = nullptr;
+    if constexpr (XMODE != 0) {
+        const size_t xr = a.route_ids != nullptr ? (size_t)(a.x_per_pair ? blockIdx.y : blockIdx.y / a.routes) : 0;
+        xrow_f = reinterpret_cast<const float*>(a.x) + xr * (XMODE == 2 ? 2 : 1) * w.k;
+    }
+    if (n_mine > 0) {
+        if constexpr (XMODE == 0) x_chunk_load<T>(xrow, fast_ok && (seg0 + 1) * chunk_len <= w.k, vec_ok, w.k, w.gs, seg0 * G + q, c, raw);
+        else x_chunk_load_f<T, XMODE>(xrow_f, w.k, w.gs, seg0 * G + q, c, rawf);
+    }
 
-    int seg = warp, rbl = 0, stage = 0;
+    int seg = seg0, rbl = rg, stage = 0;
     for (int i = 0; i < n_mine; ++i) {
         if (seg != cur_seg) {
             cur_seg = seg;
-            x_chunk_quant<T>(raw, c, xlo, xhi, gt);
-            if (seg + nwarps < w.nchunks)
-                x_chunk_load<T>(xrow, fast_ok && (seg + nwarps + 1) * chunk_len <= w.k, vec_ok, w.k, w.gs, (seg + nwarps) * G + q, c, raw);
+            if constexpr (XMODE == 0) {
+                x_chunk_quant<T>(raw, c, xlo, xhi, gt);
+                if (seg + cw < w.nchunks)
+                    x_chunk_load<T>(xrow, fast_ok && (seg + cw + 1) * chunk_len <= w.k, vec_ok, w.k, w.gs, (seg + cw) * G + q, c, raw);
+            } else {
+                x_chunk_quant_f<T>(rawf, c, xlo, xhi, gt);
+                if (seg + cw < w.nchunks) x_chunk_load_f<T, XMODE>(xrow_f, w.k, w.gs, (seg + cw) * G + q, c, rawf);
+            }
         }
         asm volatile("cp.async.wait_group %0;\n" ::"n"(S - 1) : "memory");
         __syncwarp();
@@ -454,7 +630,8 @@ __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB
                 atomicAdd(ypart + rbl * 16 + q + 8, v_hi);
             }
         }
-        if (++rbl == nrb) { rbl = 0; seg += nwarps; }
+        rbl += rgroups;
+        if (rbl >= nrb) { rbl = rg; seg += cw; }
         if (++stage == S) stage = 0;
     }
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
@@ -490,16 +667,41 @@ __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB
             float v = ypart[i];
             for (int cp = 1; cp < ycopies; ++cp) v += ypart[cp * ystride + i];
             v *= kXScaleUndo;
-            if (a.y_dtype == 0 /* MFQB_F32 */) reinterpret_cast<float*>(a.y)[y_off + row] = v;
+            if (a.route_w != nullptr) a.pair_out[y_off + row] = v;
+            else if (a.y_dtype == 0 /* MFQB_F32 */) reinterpret_cast<float*>(a.y)[y_off + row] = v;
             else reinterpret_cast<__nv_bfloat16*>(a.y)[y_off + row] = __float2bfloat16_rn(v);
         }
     }
+    if (a.route_w != nullptr) routed_finish_token(a, blockIdx.y, rbl0, nrb, row_limit);
 }
 
 template <class C>
 __global__ void __launch_bounds__(C::MIN_CTAS >= 3 ? 384 : 256, C::MIN_CTAS >= 3 ? 2 : C::MIN_CTAS) gemv1_bl_kernel(const GemvArgsB a) {
     extern __shared__ __align__(16) unsigned char smem[];
     gemv1_bl_body<C>(a, a.w, smem);
+}
+
+// x is the float32 gate|up row [2k] of a gated FFN: the SwiGLU activation is computed as the row is
+// loaded (x_chunk_load_f, mode 2), so the down projection needs no activation kernel before it.
+template <class C>
+__global__ void __launch_bounds__(C::MIN_CTAS >= 3 ? 384 : 256, C::MIN_CTAS >= 3 ? 2 : C::MIN_CTAS) gemv1_bl_swiglu_kernel(const GemvArgsB a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    gemv1_bl_body<C, 2>(a, a.w, smem);
+}
+
+// Several weights, one x: blockIdx.y picks the weight, the CTAs of a row of the grid split its row-blocks.
+template <class C>
+__global__ void __launch_bounds__(C::MIN_CTAS >= 3 ? 384 : 256, C::MIN_CTAS >= 3 ? 2 : C::MIN_CTAS) gemv1_bl_multi_kernel(const __grid_constant__ GemvArgsB a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const GemvMultiEntry& e = a.multi[blockIdx.y];
+    if ((int)blockIdx.x >= e.nrb) return;   // fewer row-blocks than CTAs in this row of the grid
+    GemvArgsB b = a;
+    b.w.items = e.items;
+    b.w.anchors = e.anchors;
+    b.w.n = e.n;
+    b.w.nrb = e.nrb;
+    b.y = e.y;
+    gemv1_bl_body<C>(b, b.w, smem);
 }
 
 }  // namespace mfqb

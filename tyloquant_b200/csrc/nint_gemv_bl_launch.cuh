@@ -8,7 +8,7 @@ namespace mfqb {
 
 struct GemvPlanB {
     int grid = 1, grid_y = 1, threads = 256;
-    int passes = 0;      // 0: single-row kernel; 1, 2, 4: batched kernel with that many two-row passes
+    int passes = 0;      // 0: single-row kernel; 1, 2, 4: batched kernel with that many two-row passes; -1: multi-weight single-row launch; -2: single-row kernel on a float32 gate|up row
     size_t smem = 0;
 };
 
@@ -71,6 +71,8 @@ static cudaError_t launch_kernel_pdl(Kernel kernel, const GemvArgsB& a, const Ge
 template <class C>
 static cudaError_t launch_gemv_codec(const GemvArgsB& a, const GemvPlanB& p, cudaStream_t stream) {
     switch (p.passes) {
+        case -2: return launch_kernel_pdl(gemv1_bl_swiglu_kernel<C>, a, p, stream);
+        case -1: return launch_kernel_pdl(gemv1_bl_multi_kernel<C>, a, p, stream);
         case 0: return launch_kernel_pdl(gemv1_bl_kernel<C>, a, p, stream);
         case 1: return launch_kernel_pdl(gemvn_bl_kernel<C, 1>, a, p, stream);
         case 2: return launch_kernel_pdl(gemvn_bl_kernel<C, 2>, a, p, stream);

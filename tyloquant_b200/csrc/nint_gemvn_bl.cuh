@@ -29,14 +29,14 @@ namespace mfqb {
 
 // Quantises rows of x into the global plane buffers the batched kernel reads: grid = (K splits,
 // rows), every CTA a range of whole chunks.
-template <int T>
-__global__ void __launch_bounds__(256) x_planes_kernel(const __nv_bfloat16* __restrict__ x, int k, int gs, int ngp, int groups_per_cta,
+template <int T, typename XT>
+__global__ void __launch_bounds__(256) x_planes_kernel(const XT* __restrict__ x, int k, int gs, int ngp, int groups_per_cta,
                                                        uint2* __restrict__ xq_g, float2* __restrict__ gtab_g) {
     constexpr int QS = gemv1_bl_qstride(T);
     const int row = blockIdx.y, g0 = blockIdx.x * groups_per_cta;
     if (g0 >= ngp) return;
-    stage_x_planes<T>(x + (size_t)row * k, k, gs, g0, min(groups_per_cta, ngp - g0), xq_g + ((size_t)row * ngp + g0) * QS,
-                      gtab_g + (size_t)row * ngp + g0);
+    stage_x_planes<T, XT>(x + (size_t)row * k, k, gs, g0, min(groups_per_cta, ngp - g0), xq_g + ((size_t)row * ngp + g0) * QS,
+                          gtab_g + (size_t)row * ngp + g0);
 }
 
 // Ring depth of the batched kernel (the plane buffers take the shared memory of one or two stages).

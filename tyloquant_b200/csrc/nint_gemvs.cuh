@@ -6,9 +6,9 @@
 // float32), organised for the memory system instead of for the matrix shape:
 //
 //   * Work is the flat sequence of (row-block, chunk) records in storage order.  The grid is one
-//     CTA per SM; CTA b owns the contiguous range [I*b/G, I*(b+1)/G) of the I records, every warp a
-//     contiguous part of that, so all SMs stream the same number of bytes whatever the matrix
-//     shape, and every warp reads one long run of consecutive addresses.
+//     CTA per SM; CTA b owns the contiguous range [I*b/G, I*(b+1)/G) of the I records, so all SMs
+//     stream the same number of bytes whatever the matrix shape, and every warp takes a contiguous
+//     part of that: one long run of consecutive addresses.
 //   * A warp moves its records with one bulk asynchronous copy each (cp.async.bulk, completion
 //     counted on an mbarrier) through a private ring; the first records are requested before the
 //     kernel waits for its predecessor in the stream, since weights are constants.  A CTA takes
@@ -20,11 +20,13 @@
 //   * A lane keeps float32 running sums for its two rows over a whole row-block segment; row
 //     anchors, the reduction over the quad and the shared-memory hand-over happen once per
 //     segment, not once per record.
-//   * A row-block whose records straddle CTAs is finished by the CTA that holds its first records,
-//     which reaches them last.  The CTAs that hold its later records reach theirs first: as soon
-//     as the warps concerned are done they publish their sixteen partial rows to a small global
-//     scratch, each value with a flag in one 8-byte store.  At its end the owner polls those pairs
-//     (bounded), adds them in CTA order and clears them; a publisher never waits for anybody.
+//   * No CTA-wide barrier after staging.  A row-block's sixteen rows are finished by the last of
+//     the warps that hold records of it (a shared-memory counter per row-block), which adds the
+//     warps' segments in warp order and writes the output.  A row-block whose records straddle
+//     CTAs is finished by the CTA that holds its first records, which reaches them last: the CTAs
+//     that hold its later records reach theirs first and publish their partial rows to a small
+//     global scratch, each value with a flag in one 8-byte store; the owner polls those pairs
+//     (bounded), adds them in CTA order and clears them.  A publisher never waits for anybody.
 #pragma once
 #include "nint_gemv1_bl.cuh"
 #include "tc05.cuh"
@@ -41,6 +43,7 @@ struct GemvSArgs {
     int* error;             // device status word (host-visible): set when a bounded wait expires
     int stages;             // ring records per warp
     int maxseg;             // row-block segments one warp can touch
+    int maxrb;              // row-blocks one CTA can touch
 #ifdef MFQB_GEMVS_TRACE
     unsigned long long* trace;   // development builds only: [grid][16] timestamps of the kernel's phases
 #endif
@@ -328,7 +331,8 @@ __device__ __forceinline__ void gemvs_body(const GemvSArgs& a, unsigned char* sm
     float2* gtab = reinterpret_cast<float2*>(parts + (size_t)W * p_maxseg * 16);
     uint32_t* gmax = reinterpret_cast<uint32_t*>(gtab + ngp);
     int* gsum = reinterpret_cast<int*>(gmax + ngp);
-    uint32_t* zero_blk = reinterpret_cast<uint32_t*>(gsum + ngp);
+    int* rb_cnt = gsum + ngp;   // [maxrb] warps that have handed over their segment of each row-block of the CTA
+    uint32_t* zero_blk = reinterpret_cast<uint32_t*>(rb_cnt + ((a.maxrb + 3) & ~3));
     uint32_t* xq = zero_blk + 72;   // 288 bytes of zeros: T rows of 32 bytes and one row more
     uint32_t* ring_all = reinterpret_cast<uint32_t*>((reinterpret_cast<uintptr_t>(xq + (size_t)ngp * T * 8) + 127) & ~(uintptr_t)127);
     uint64_t* bars = bars_all + warp * S;
@@ -336,35 +340,34 @@ __device__ __forceinline__ void gemvs_body(const GemvSArgs& a, unsigned char* sm
 
     __shared__ int wstart[33];   // first record of every warp of the CTA, then the CTA's end
     __shared__ int wrb[32];      // row-block of that record
-    __shared__ int head_cnt;     // warps that have handed over their part of the CTA's first row-block
     const int total = p_nrb * nch;
     const int G = gridDim.x, b = blockIdx.x;
     const int lo_b = (int)((unsigned)total * (unsigned)b / (unsigned)G), hi_b = (int)((unsigned)total * (unsigned)(b + 1) / (unsigned)G);
     const int n_b = hi_b - lo_b;
     const int w_lo = lo_b + (int)((unsigned)n_b * (unsigned)warp / (unsigned)W), w_hi = lo_b + (int)((unsigned)n_b * (unsigned)(warp + 1) / (unsigned)W);
     const int n_w = w_hi - w_lo;
-    int rb = w_lo / nch, ch = w_lo - rb * nch;
+    const int rb_main = w_lo / nch;   // row-block the warp starts in
+    const int rb_first = lo_b / nch;  // first row-block of the CTA
+    int rb = rb_main, ch = w_lo - rb_main * nch;
     MFQB_TRACE(0);
     if (lane == 0) {
         wstart[warp] = w_lo;
-        wrb[warp] = rb;
+        wrb[warp] = rb_main;
         if (warp == W - 1) wstart[W] = hi_b;
-        if (warp == 0) head_cnt = 0;
         for (int s = 0; s < S; ++s) mbar_init(&bars[s], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
     pdl_launch_dependents_b();
-    const uint32_t* src0 = p_items + (size_t)w_lo * REC;
+    const uint32_t* src0 = p_items + (size_t)w_lo * REC;   // the warp's records are consecutive in memory
     const uint64_t policy = l2_evict_first_policy();
     if (lane == 0) {
         const int pre = min(S, n_w);
-        for (int s = 0; s < pre; ++s)
-            ring_request(smem_u32(ring + (size_t)s * REC), src0 + (size_t)s * REC, REC * 4, smem_u32(&bars[s]), policy);
+        for (int s = 0; s < pre; ++s) ring_request(smem_u32(ring + (size_t)s * REC), src0 + (size_t)s * REC, REC * 4, smem_u32(&bars[s]), policy);
     }
     // The activation row may still be written by the previous kernel, so it is not read yet -- but
     // asking L2 to fetch its lines is harmless (L2 is the point of coherence) and spares the first
-    // read after the wait a trip to HBM.  Every CTA asks for a slice.
+    // read after the wait a trip to HBM.
     {
         const size_t xbytes = (size_t)p_k * (p_xdt == MFQB_F32 ? 4 : 2);
         const size_t line = ((size_t)b * blockDim.x + tid) * 128;
@@ -372,6 +375,7 @@ __device__ __forceinline__ void gemvs_body(const GemvSArgs& a, unsigned char* sm
     }
     if (tid < 72) zero_blk[tid] = 0u;
     for (int g = tid; g < ngp; g += blockDim.x) { gmax[g] = 0u; gsum[g] = 0; }   // staging accumulators: cleared while the predecessor still runs
+    for (int r = tid; r < a.maxrb; r += blockDim.x) rb_cnt[r] = 0;
     uint32_t an_lo = 0u, an_hi = 0u;   // anchors (f16 scale | f16 min << 16) of the lane's two rows: weights, so before the wait
     if (n_w > 0) {
         an_lo = __ldg(p_anchors + (size_t)rb * 16 + q);
@@ -384,16 +388,6 @@ __device__ __forceinline__ void gemvs_body(const GemvSArgs& a, unsigned char* sm
     gemvs_stage_x<T, __nv_bfloat16>(static_cast<const __nv_bfloat16*>(p_x), p_k, p_gs, ngp, xq, gtab, gmax, gsum, a);
     __syncthreads();
     MFQB_TRACE(3);
-
-    // The CTA's first row-block when its first records belong to an earlier CTA: the warps that
-    // hold records of it hand their rows over first thing, and the last of them publishes the sum.
-    const int rb_first = lo_b / nch, rb_last = n_b > 0 ? (hi_b - 1) / nch : rb_first;
-    const bool head_open = n_b > 0 && lo_b != rb_first * nch;
-    const int head_end = min(hi_b, (rb_first + 1) * nch);
-    int n_head = 0;   // warps with records of the first row-block
-    if (head_open)
-        for (int wv = 0; wv < W; ++wv) n_head += (wstart[wv + 1] > wstart[wv] && wstart[wv] < head_end) ? 1 : 0;
-    const bool head_warp = head_open && n_w > 0 && w_lo < head_end;
 
     // B operand by ldmatrix: lane l supplies the address of row n = l%8 (column n = group n of the
     // chunk) of matrix m = l/8 (m&1: k-half, m>>1: byte plane).  The row is live in the steps of
@@ -411,12 +405,15 @@ __device__ __forceinline__ void gemvs_body(const GemvSArgs& a, unsigned char* sm
     const uint32_t gt_addr0 = smem_u32(gtab) + (uint32_t)(2 * c) * 8u;
     const uint32_t ring_addr = smem_u32(ring) + (uint32_t)lane * 4u;
 
-    int seg = 0, stage = 0;
+    int stage = 0;
     uint32_t parity = 0;
     float acc_s_lo = 0.f, acc_s_hi = 0.f, acc_m_lo = 0.f, acc_m_hi = 0.f;
     float* my_parts = parts + (size_t)warp * p_maxseg * 16;
     bool failed = false;
 
+    // Hands the warp's sums of the current row-block over; the last warp of the row-block to do so
+    // finishes it: adds the segments in warp order, then publishes (the row-block began in an earlier
+    // CTA), or collects what later CTAs published and writes the output rows.
     auto flush = [&]() {
         const float2 f_lo = __half22float2(*reinterpret_cast<const __half2*>(&an_lo));   // (ns, nm)
         const float2 f_hi = __half22float2(*reinterpret_cast<const __half2*>(&an_hi));
@@ -425,35 +422,61 @@ __device__ __forceinline__ void gemvs_body(const GemvSArgs& a, unsigned char* sm
         v_hi += __shfl_xor_sync(0xffffffffu, v_hi, 1);
         v_lo += __shfl_xor_sync(0xffffffffu, v_lo, 2);
         v_hi += __shfl_xor_sync(0xffffffffu, v_hi, 2);
+        const int seg = rb - rb_main;
         if (c == 0) {
             my_parts[seg * 16 + q] = v_lo;
             my_parts[seg * 16 + q + 8] = v_hi;
         }
-        if (seg == 0 && head_warp) {
-            __threadfence_block();
-            __syncwarp();
-            int old = 0;
-            if (lane == 0) old = atomicAdd(&head_cnt, 1);
-            old = __shfl_sync(0xffffffffu, old, 0);
-            if (old == n_head - 1) {   // the other warps' rows of this row-block are in shared memory
-                __threadfence_block();
-                if (lane < 16) {
-                    float v = 0.f;
-                    for (int wv = 0; wv < W; ++wv)
-                        if (wstart[wv + 1] > wstart[wv] && wstart[wv] < head_end) v += parts[(size_t)wv * p_maxseg * 16 + lane];
-                    st_pair_sys(p_slots + (size_t)b * 16 + lane, __float_as_uint(v), 1u);
+        acc_s_lo = acc_s_hi = acc_m_lo = acc_m_hi = 0.f;
+        __threadfence_block();
+        __syncwarp();
+        const int r0 = rb * nch, r1 = r0 + nch, rs = max(lo_b, r0), re = min(hi_b, r1);
+        // warps with records of this row-block: lane l answers for warp l
+        const bool over = lane < W && wstart[lane + 1] > wstart[lane] && wstart[lane] < re && wstart[lane + 1] > rs;
+        unsigned who = __ballot_sync(0xffffffffu, over);
+        int old = 0;
+        if (lane == 0) old = atomicAdd(rb_cnt + (rb - rb_first), 1);
+        old = __shfl_sync(0xffffffffu, old, 0);
+        if (old != __popc(who) - 1) return;   // another warp will finish it
+        __threadfence_block();
+        float v = 0.f;
+        while (who) {
+            const int wv = __ffs(who) - 1;
+            who &= who - 1;
+            if (lane < 16) v += parts[((size_t)wv * p_maxseg + (rb - wrb[wv])) * 16 + lane];
+        }
+        if (lane >= 16) return;
+        if (rs != r0) {   // the row-block began in an earlier CTA: publish this CTA's share to it
+            st_pair_sys(p_slots + (size_t)b * 16 + lane, __float_as_uint(v), 1u);
+            return;
+        }
+        if (re != r1) {   // it continues in later CTAs: add what they published, in CTA order
+            const int b_last = gemvs_cta_of(r1 - 1, total, G);
+            for (int bb = b + 1; bb <= b_last; ++bb) {
+                uint2* slot = p_slots + (size_t)bb * 16 + lane;
+                uint2 pv = ld_pair_sys(slot);
+                for (unsigned spins = 0; pv.y == 0u && spins < kGemvsPollLimit; ++spins) pv = ld_pair_sys(slot);
+                if (pv.y == 0u) {
+                    if (p_err) *p_err = MFQB_ERR_TIMEOUT;   // the publisher never came: give up on this row-block
+                } else {
+                    v += __uint_as_float(pv.x);
+                    st_pair_sys(slot, 0u, 0u);
                 }
             }
         }
-        ++seg;
-        acc_s_lo = acc_s_hi = acc_m_lo = acc_m_hi = 0.f;
+        v *= kXScaleUndo;
+        const int row = rb * 16 + lane;
+        if (row < p_n) {
+            if (p_ydt == MFQB_F32) reinterpret_cast<float*>(p_y)[row] = v;
+            else reinterpret_cast<__nv_bfloat16*>(p_y)[row] = __float2bfloat16_rn(v);
+        }
     };
 
     // Ring cursors as shared-memory addresses, advanced by constants: slot of the record being read,
     // its barrier, and the global address of the next record to request.
     const uint32_t bar0 = smem_u32(bars), slot0 = smem_u32(ring);
     uint32_t bar_addr = bar0, slot_addr = slot0;
-    const unsigned char* src_next = reinterpret_cast<const unsigned char*>(src0) + (size_t)min(S, n_w) * (REC * 4);
+    const uint32_t* src_next = src0 + (size_t)min(S, n_w) * REC;   // next record to request
     int to_request = n_w - min(S, n_w);
     for (int i = 0; i < n_w; ++i) {
         if (!mbar_try_once(bar_addr, parity)) {
@@ -473,7 +496,7 @@ __device__ __forceinline__ void gemvs_body(const GemvSArgs& a, unsigned char* sm
             __syncwarp();   // every lane has read the slot
             if (to_request > 0) {
                 if (lane == 0) ring_request(slot_addr, src_next, REC * 4, bar_addr, policy);
-                src_next += REC * 4;
+                src_next += REC;
                 --to_request;
             }
         };
@@ -556,63 +579,10 @@ __device__ __forceinline__ void gemvs_body(const GemvSArgs& a, unsigned char* sm
         if (lane == 0 && p_err) *p_err = MFQB_ERR_TIMEOUT;
         for (int s = 0; s < S; ++s) (void)mbar_wait(&bars[s], parity ^ (s < stage ? 1u : 0u), 1u << 16);
     }
-    // The CTA's last row-block when it continues in later CTAs: the warp that will finish it asks for
-    // the published pairs now, so the answers travel while the CTA's warps meet at the barrier.
-    constexpr int PRE = 3;
-    const int tail_r1 = (rb_last + 1) * nch;
-    const bool tail_open = n_b > 0 && hi_b < tail_r1 && !(head_open && rb_last == rb_first);
-    const int tail_b_last = tail_open ? gemvs_cta_of(tail_r1 - 1, total, G) : b;
-    const bool tail_warp = tail_open && warp == (rb_last - rb_first - (head_open ? 1 : 0)) % W;
-    uint2 pre[PRE];
-#pragma unroll
-    for (int j = 0; j < PRE; ++j) {
-        pre[j] = make_uint2(0u, 0u);
-        if (tail_warp && lane < 16 && b + 1 + j <= tail_b_last) pre[j] = ld_pair_sys(p_slots + (size_t)(b + 1 + j) * 16 + lane);
-    }
     MFQB_TRACE(4);
-    __syncthreads();
-    MFQB_TRACE(5);
-    if (n_b == 0) return;
-
-    // Row-blocks that begin in this CTA: sum the warps' segments in warp order; if the row-block
-    // continues in later CTAs, add the rows they published (CTA order), clear their flags, write.
-    for (int rr = rb_first + (head_open ? 1 : 0) + warp; rr <= rb_last; rr += W) {
-        const int r0 = rr * nch, r1 = r0 + nch, e = min(hi_b, r1);
-        // warps with records of this row-block: lane l answers for warp l, then the rows add them in warp order
-        const bool mine = lane < W && wstart[lane + 1] > wstart[lane] && wstart[lane] < e && wstart[lane + 1] > r0;
-        unsigned who = __ballot_sync(0xffffffffu, mine);
-        float v = 0.f;
-        while (who) {
-            const int wv = __ffs(who) - 1;
-            who &= who - 1;
-            if (lane < 16) v += parts[((size_t)wv * p_maxseg + (rr - wrb[wv])) * 16 + lane];
-        }
-        MFQB_TRACE(12);
-        if (e != r1 && lane < 16) {
-            for (int bb = b + 1; bb <= tail_b_last; ++bb) {
-                uint2* slot = p_slots + (size_t)bb * 16 + lane;
-                uint2 pv = make_uint2(0u, 0u);
-#pragma unroll
-                for (int j = 0; j < PRE; ++j)
-                    if (bb == b + 1 + j) pv = pre[j];
-                for (unsigned spins = 0; pv.y == 0u && spins < kGemvsPollLimit; ++spins) pv = ld_pair_sys(slot);
-                if (pv.y == 0u) {
-                    if (p_err) *p_err = MFQB_ERR_TIMEOUT;   // the publisher never came: give up on this row-block
-                } else {
-                    v += __uint_as_float(pv.x);
-                    st_pair_sys(slot, 0u, 0u);
-                }
-            }
-        }
-        MFQB_TRACE(11);
-        v *= kXScaleUndo;
-        const int row = rr * 16 + lane;
-        if (lane < 16 && row < p_n) {
-            if (p_ydt == MFQB_F32) reinterpret_cast<float*>(p_y)[row] = v;
-            else reinterpret_cast<__nv_bfloat16*>(p_y)[row] = __float2bfloat16_rn(v);
-        }
-    }
-    MFQB_TRACE(6);
+#ifdef MFQB_GEMVS_TRACE
+    if (a.trace && lane == 0) atomicMax(a.trace + blockIdx.x * 16 + 6, global_timer_ns());   // last warp of the CTA to get here
+#endif
 }
 
 // Largest block per record width, two CTAs per SM: 64, 85 or 128 registers per thread.

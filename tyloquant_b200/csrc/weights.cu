@@ -7,6 +7,8 @@
 #include <utility>
 #include <vector>
 
+#include <climits>
+
 #include "cuda_util.h"
 #include "nint_gemm_tc.cuh"
 #include "nint_blayout.h"
@@ -44,6 +46,7 @@ void* GrowOnlyScratch::get(int device, size_t bytes, cudaStream_t stream, const 
     void* p = nullptr;
     const size_t want = bytes + bytes / 2;
     MFQB_CUDA(cudaMalloc(&p, want));
+    MFQB_CUDA(cudaMemset(p, 0, want));   // some users keep self-resetting counters in their block: they start at zero
     d.p = p;   // the previous block stays allocated: earlier launches and captured graphs may still use it
     d.bytes = want;
     return p;
@@ -148,12 +151,13 @@ static bool launch_nint_gemm(const NintDevB& w, const void* x, int m, void* y, i
 
 // Rows of x (bf16 [rows, k]) gathered in route-plan order and converted to f16 [pairs, kx]:
 // out row p = x row (pair_order[p] / div).
-__global__ void x_gather_f16_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ pair_order, int div, int pairs, int k, int kx,
+template <typename XT>
+__global__ void x_gather_f16_kernel(const XT* __restrict__ x, const int* __restrict__ pair_order, int div, int pairs, int k, int kx,
                                     __half* __restrict__ out) {
     const size_t total = (size_t)pairs * kx;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t p = i / kx, c = i % kx;
-        const float v = c < (size_t)k ? __bfloat162float(x[(size_t)(pair_order[p] / div) * k + c]) : 0.f;
+        const float v = c < (size_t)k ? (float)x[(size_t)(pair_order[p] / div) * k + c] : 0.f;
         out[i] = isfinite(v) ? __float2half_rn(fminf(fmaxf(v, -65504.f), 65504.f)) : __ushort_as_half((unsigned short)0x7E00);
     }
 }
@@ -164,11 +168,12 @@ bool nint_gemm_grouped_supported(const NintDevB& w, int bn, int rows_per_expert)
 // Bytes of the gathered f16 input the grouped kernel reads.
 size_t nint_gemm_grouped_x_bytes(int pairs, int k) { return (size_t)pairs * ((k + 7) / 8 * 8) * sizeof(__half); }
 
-void launch_x_gather_f16(const void* x, const int* pair_order, int div, int pairs, int k, void* x16, cudaStream_t s) {
+void launch_x_gather_f16(const void* x, bool x_f32, const int* pair_order, int div, int pairs, int k, void* x16, cudaStream_t s) {
     const int kx = (k + 7) / 8 * 8;
     const size_t total = (size_t)pairs * kx;
-    x_gather_f16_kernel<<<(int)std::min<size_t>((total + 255) / 256, 148 * 8), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), pair_order, div, pairs, k,
-                                                                                      kx, static_cast<__half*>(x16));
+    const int grid = (int)std::min<size_t>((total + 255) / 256, 148 * 8);
+    if (x_f32) x_gather_f16_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(x), pair_order, div, pairs, k, kx, static_cast<__half*>(x16));
+    else x_gather_f16_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), pair_order, div, pairs, k, kx, static_cast<__half*>(x16));
     MFQB_CUDA(cudaGetLastError());
 }
 
@@ -226,9 +231,11 @@ using namespace mfqb;
 
 namespace mfqb {
 void launch_nint_bl_dequant(const NintDevB& w, void* out, int out_dtype, cudaStream_t s);
-void launch_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtype, int ldy, int device, cudaStream_t s);
+void launch_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtype, int ldy, int device, cudaStream_t s, bool swiglu = false);
 bool nint_bl_supported(int bits, int gs);
 size_t gemvs_fix_bytes(int device);
+void launch_swiglu(const void* gate_up, int in_dtype, int rows, int f, void* hidden, cudaStream_t s);
+void launch_bl_gemv_multi(const NintDevB* ws, void* const* ys, int count, const void* x, int y_dtype, int device, cudaStream_t s);
 bool launch_bl_gemvs(const NintDevB& w, const void* x, int x_dtype, void* y, int y_dtype, int device, void* fix, int* error, cudaStream_t s);
 }
 
@@ -238,7 +245,8 @@ static int g_gemv1_choice = 0;
 static bool gemv1_use_streamed(const NintDevB& w) {
     if (g_gemv1_choice == 1) return false;
     if (g_gemv1_choice == 2) return true;
-    return true;
+    (void)w;
+    return false;   // measured on B200: the ring kernel is as fast or faster on every shape of the sweep
 }
 
 struct mfqb_weight {
@@ -398,6 +406,42 @@ int mfqb_mul_mat(const mfqb_weight* w, const void* x, int m, void* y, int y_dtyp
         } else {
             nvq_mul_mat(*w->nvq, x, m, y, y_dtype, stream);
         }
+    });
+}
+
+int mfqb_mul_mat_swiglu(const mfqb_weight* w, const void* gate_up, int m, void* y, int y_dtype, mfqb_stream_t stream) {
+    return guarded([&] {
+        if (!w || !gate_up || !y) fail(MFQB_ERR_ARG, "mfqb_mul_mat_swiglu: null argument");
+        if (m < 1) fail(MFQB_ERR_ARG, "mfqb_mul_mat_swiglu: m must be >= 1, got %d", m);
+        if (y_dtype != MFQB_F32 && y_dtype != MFQB_BF16) fail(MFQB_ERR_ARG, "mfqb_mul_mat_swiglu: bad output dtype");
+        if (w->info.k > INT_MAX) fail(MFQB_ERR_ARG, "mfqb_mul_mat_swiglu: row length out of range");
+        DeviceGuard guard(w->device);
+        if (m == 1 && w->family == MFQB_FAMILY_NINT) {   // activation computed as the down projection loads its row
+            launch_bl_gemv(w->nint, gate_up, 1, y, y_dtype, (int)w->info.n, w->device, stream, true);
+            return;
+        }
+        static GrowOnlyScratch pool;
+        void* act = pool.get(w->device, (size_t)m * w->info.k * 2, stream, "mfqb_mul_mat_swiglu (activation rows)");
+        launch_swiglu(gate_up, MFQB_F32, m, (int)w->info.k, act, stream);
+        const int rc = mfqb_mul_mat(w, act, m, y, y_dtype, stream);
+        if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
+    });
+}
+
+int mfqb_mul_mat_multi(const mfqb_weight* const* ws, int count, const void* x, void* const* ys, int y_dtype, mfqb_stream_t stream) {
+    return guarded([&] {
+        if (!ws || !x || !ys) fail(MFQB_ERR_ARG, "mfqb_mul_mat_multi: null argument");
+        if (count < 1 || count > 8) fail(MFQB_ERR_ARG, "mfqb_mul_mat_multi: 1 to 8 weights per call, got %d", count);
+        if (y_dtype != MFQB_F32 && y_dtype != MFQB_BF16) fail(MFQB_ERR_ARG, "mfqb_mul_mat_multi: bad output dtype");
+        NintDevB devs[8];
+        for (int i = 0; i < count; ++i) {
+            if (!ws[i] || !ys[i]) fail(MFQB_ERR_ARG, "mfqb_mul_mat_multi: null weight or output");
+            if (ws[i]->family != MFQB_FAMILY_NINT) fail(MFQB_ERR_UNSUPPORTED, "mfqb_mul_mat_multi: scalar-quantised (NINT) weights only");
+            if (ws[i]->device != ws[0]->device) fail(MFQB_ERR_ARG, "mfqb_mul_mat_multi: weights live on different devices");
+            devs[i] = ws[i]->nint;
+        }
+        DeviceGuard guard(ws[0]->device);
+        launch_bl_gemv_multi(devs, ys, count, x, y_dtype, ws[0]->device, stream);
     });
 }
 

@@ -80,6 +80,35 @@ class QuantWeight:
                                F32 if tdt == torch.float32 else BF16, _stream_ptr(self.device)))
         return y[0] if squeeze else y
 
+    def matmul_swiglu(self, gate_up, out_dtype=None):
+        """``(up * silu(gate)) @ W.T`` for a float32 CUDA tensor ``gate_up`` [m, 2k] (gate columns first)."""
+        torch = _torch()
+        gu = gate_up.reshape(-1, 2 * self.k).contiguous()
+        if gu.dtype != torch.float32 or not gu.is_cuda or gu.device.index != self.device:
+            raise ValueError(f"gate_up must be a float32 tensor on cuda:{self.device}")
+        tdt = out_dtype or torch.bfloat16
+        y = torch.empty((gu.shape[0], self.n), dtype=tdt, device=gu.device)
+        check(lib.mfqb_mul_mat_swiglu(self._h, gu.data_ptr(), gu.shape[0], y.data_ptr(),
+                                      F32 if tdt == torch.float32 else BF16, _stream_ptr(self.device)))
+        return y
+
+    @staticmethod
+    def matmul_multi(weights, x, out_dtype=None):
+        """One bf16 row ``x`` [k] against up to 8 NINT weights of one shape class in a single launch
+        (q|k|v, gate|up): returns the list of ``x @ W_i.T``."""
+        torch = _torch()
+        dev = weights[0].device
+        x1 = x.reshape(-1).contiguous()
+        if x1.dtype != torch.bfloat16 or not x1.is_cuda or x1.device.index != dev:
+            raise ValueError(f"x must be a bfloat16 tensor on cuda:{dev}")
+        tdt = out_dtype or torch.bfloat16
+        ys = [torch.empty((w.n,), dtype=tdt, device=x1.device) for w in weights]
+        hs = (C.c_void_p * len(weights))(*[w._h for w in weights])
+        ps = (C.c_void_p * len(weights))(*[y.data_ptr() for y in ys])
+        check(lib.mfqb_mul_mat_multi(hs, len(weights), x1.data_ptr(), ps,
+                                     F32 if tdt == torch.float32 else BF16, _stream_ptr(dev)))
+        return ys
+
     def matmul_host(self, x_bits, out_f32: bool = False):
         """Host-buffer product: ``x_bits`` is a uint16 numpy array of bf16 bit patterns [m, k];
         returns a numpy array (uint16 bf16 bits, or float32)."""
