@@ -190,6 +190,14 @@ def main() -> None:
     ap.add_argument("--no-parallel", action="store_true",
                     help="at --gpus > 1 skip the sharded paths (keys tp_rowparallel, ep_moe_cfg4) and time the replicas only")
     args = ap.parse_args()
+    # The result line is the only thing that may reach standard output: libraries that print there
+    # from native code (the collective library's version banner) go to standard error instead.
+    result_out = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+
+    def emit(obj) -> None:
+        result_out.write(json.dumps(obj) + "\n")
+        result_out.flush()
     steps, warmup = max(args.steps, 1), max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -202,22 +210,22 @@ def main() -> None:
 
     if args.only == "gemm":
         pk = measured_peaks()[0]
-        print(json.dumps(gemm_bench(local_rank, pk.get("bf16_tflops_sustained", pk["bf16_tflops"]))))
+        emit(gemm_bench(local_rank, pk.get("bf16_tflops_sustained", pk["bf16_tflops"])))
         return
     if args.only == "decoder":
-        print(json.dumps({"decoder_cfg5": decoder_bench(local_rank, 0, 1, None, batches=tuple(args.batch or (1, 16)))}))
+        emit({"decoder_cfg5": decoder_bench(local_rank, 0, 1, None, batches=tuple(args.batch or (1, 16)))})
         return
     if args.only == "moe":
-        print(json.dumps(moe_layer_bench(local_rank, measured_peaks()[0]["hbm_gbs"], token_counts=tuple(args.tokens or (1, 8, 32, 64, 128, 256, 1024)))))
+        emit(moe_layer_bench(local_rank, measured_peaks()[0]["hbm_gbs"], token_counts=tuple(args.tokens or (1, 8, 32, 64, 128, 256, 1024))))
         return
     if args.impl != "reference" and args.gemv1_kernel:
         from tyloquant_b200._capi import check as _check, lib as _lib
         _check(_lib.mfqb_tune(b"gemv1_kernel", args.gemv1_kernel))
     if args.only == "sweep":   # every sweep case, graph-timed, nothing else
-        print(json.dumps({"sweep": sweep(local_rank, measured_peaks()[0]["hbm_gbs"], match=args.match)}))
+        emit({"sweep": sweep(local_rank, measured_peaks()[0]["hbm_gbs"], match=args.match)})
         return
     if args.only:
-        print(json.dumps(sweep(local_rank, measured_peaks()[0]["hbm_gbs"], only=args.only, reps=args.reps)))
+        emit(sweep(local_rank, measured_peaks()[0]["hbm_gbs"], only=args.only, reps=args.reps))
         return
 
     if args.impl == "reference":
@@ -228,7 +236,7 @@ def main() -> None:
         line.update({"impl": "reference", "value": cb["value"], "ms_per_step": ms, "n_gpus": args.gpus,
                      "cpu_baseline": cb, "gpu_launches": 0,
                      "e2e": {"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
-        print(json.dumps(line))
+        emit(line)
         return
 
     import torch
@@ -429,7 +437,7 @@ def main() -> None:
             line["sweep"] = sweep(dev, peaks["hbm_gbs"])
             line["moe_layer_cfg4"] = moe_layer_bench(dev, peaks["hbm_gbs"])
             line["gemm_cfg2"] = gemm_bench(dev, peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]))
-    print(json.dumps(line))
+    emit(line)
     if dist is not None:
         dist.destroy_process_group()
 

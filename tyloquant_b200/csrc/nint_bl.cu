@@ -302,13 +302,13 @@ void launch_bl_gemv_multi(const NintDevB* ws, void* const* ys, int count, const 
     a.x = static_cast<const __nv_bfloat16*>(x);
     a.m = 1;
     a.y_dtype = y_dtype;
-    a.multi_count = count;
+    GemvMultiTable table{};
     int max_nrb = 0;
     for (int i = 0; i < count; ++i) {
         const NintDevB& w = ws[i];
         if (w.table || w.bits != ws[0].bits || w.gs != ws[0].gs || w.k != ws[0].k || w.rec_words != ws[0].rec_words)
             fail(MFQB_ERR_ARG, "the weights of a multi-weight launch must share family, code width, group size and k");
-        a.multi[i] = GemvMultiEntry{w.items, w.anchors, ys[i], w.n, w.nrb};
+        table.e[i] = GemvMultiEntry{w.items, w.anchors, ys[i], w.n, w.nrb};
         max_nrb = std::max(max_nrb, w.nrb);
     }
     a.ldy = 0;
@@ -316,11 +316,12 @@ void launch_bl_gemv_multi(const NintDevB* ws, void* const* ys, int count, const 
     const int warps = gemv1_warps(ws[0]), sms = device_sm_count(device);
     p.threads = warps * 32;
     p.passes = -1;
+    p.multi = &table;
     // all CTAs resident at once: the SMs' slots shared out over the weights
     const int per_weight = std::max(1, ctas_per_sm(gemv1_smem(ws[0], 1, warps), warps > 8 ? 2 : 3) * sms / count);
-    p.grid = std::min(max_nrb, per_weight);
+    a.rb_per_cta = (max_nrb + std::min(max_nrb, per_weight) - 1) / std::min(max_nrb, per_weight);
+    p.grid = (max_nrb + a.rb_per_cta - 1) / a.rb_per_cta;   // no more CTAs than that many row-blocks each need: an even split
     p.grid_y = count;
-    a.rb_per_cta = (max_nrb + p.grid - 1) / p.grid;
     a.private_sums = gemv1_private_sums(a.rb_per_cta);
     p.smem = gemv1_smem(ws[0], a.rb_per_cta, warps);
     if (p.smem > kGemvSmemLimit) fail(MFQB_ERR_UNSUPPORTED, "multi-weight launch: %d row-blocks per CTA do not fit shared memory", a.rb_per_cta);

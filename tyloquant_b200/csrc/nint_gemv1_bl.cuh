@@ -34,6 +34,9 @@ struct GemvMultiEntry {
     int n, nrb;
 };
 constexpr int kGemvMultiMax = 8;
+struct GemvMultiTable {
+    GemvMultiEntry e[kGemvMultiMax];
+};
 
 struct GemvArgsB {
     NintDevB w;
@@ -68,10 +71,6 @@ struct GemvArgsB {
     // pair_out [pairs, ldy] float32, and the last of a token's `routes` CTAs to arrive adds them with
     // the route weights, in route order, into y_final [tokens, ldy] (moe_weighted_reduce,
     // mfq/kernels/cuda/moe.cu:2957-2977).  token_count: [tokens * gridDim.x] zeros, left zero again.
-    // Single-row kernel, multi-weight launch: blockIdx.y selects one of multi_count weights that share
-    // x, the code width, the group size and k (w then describes their common geometry).
-    int multi_count;
-    GemvMultiEntry multi[kGemvMultiMax];
     int x_mode;
     const float* route_w;
     float* pair_out;
@@ -504,14 +503,17 @@ __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB
     // projection) split the warps into groups that share the chunks and take the row-blocks in turn.
     // Two cursors walk the sequence (issue runs S items ahead).
     int cw = nwarps, rgroups = 1, seg0 = warp, rg = 0;
-    if (w.nchunks < nwarps) {
+    int my_segs, my_rbs = nrb;
+    if (w.nchunks < nwarps) {   // every warp of a group has one chunk
         cw = w.nchunks;
         rgroups = nwarps / cw;
         rg = warp / cw;
         seg0 = warp - rg * cw;
+        my_segs = rg < rgroups ? 1 : 0;
+        my_rbs = rg < min(rgroups, nrb) ? (nrb - rg + rgroups - 1) / rgroups : 0;
+    } else {
+        my_segs = (w.nchunks - warp + nwarps - 1) / nwarps;
     }
-    const int my_segs = rg < rgroups ? (w.nchunks - seg0 + cw - 1) / cw : 0;
-    const int my_rbs = rg < min(rgroups, nrb) ? (nrb - rg + rgroups - 1) / rgroups : 0;
     const int n_mine = my_segs * my_rbs;
     // the record pointer walks (chunk, row-block) incrementally: the warp's next row-block, or back to
     // its first row-block of its next chunk
@@ -689,11 +691,12 @@ __global__ void __launch_bounds__(C::MIN_CTAS >= 3 ? 384 : 256, C::MIN_CTAS >= 3
     gemv1_bl_body<C, 2>(a, a.w, smem);
 }
 
-// Several weights, one x: blockIdx.y picks the weight, the CTAs of a row of the grid split its row-blocks.
+// Several weights that share x, the code width, the group size and k (a.w describes their common
+// geometry): blockIdx.y picks the weight, the CTAs of a row of the grid split its row-blocks.
 template <class C>
-__global__ void __launch_bounds__(C::MIN_CTAS >= 3 ? 384 : 256, C::MIN_CTAS >= 3 ? 2 : C::MIN_CTAS) gemv1_bl_multi_kernel(const __grid_constant__ GemvArgsB a) {
+__global__ void __launch_bounds__(C::MIN_CTAS >= 3 ? 384 : 256, C::MIN_CTAS >= 3 ? 2 : C::MIN_CTAS) gemv1_bl_multi_kernel(const GemvArgsB a, const __grid_constant__ GemvMultiTable table) {
     extern __shared__ __align__(16) unsigned char smem[];
-    const GemvMultiEntry& e = a.multi[blockIdx.y];
+    const GemvMultiEntry& e = table.e[blockIdx.y];
     if ((int)blockIdx.x >= e.nrb) return;   // fewer row-blocks than CTAs in this row of the grid
     GemvArgsB b = a;
     b.w.items = e.items;

@@ -8,6 +8,7 @@ namespace mfqb {
 
 struct GemvPlanB {
     int grid = 1, grid_y = 1, threads = 256;
+    const GemvMultiTable* multi = nullptr;   // the weights of a multi-weight launch (passes == -1)
     int passes = 0;      // 0: single-row kernel; 1, 2, 4: batched kernel with that many two-row passes; -1: multi-weight single-row launch; -2: single-row kernel on a float32 gate|up row
     size_t smem = 0;
 };
@@ -49,8 +50,8 @@ static cudaError_t launch_gemvs_codec(const GemvSArgs& a, const GemvSPlan& p, cu
     return cudaLaunchKernelEx(&cfg, kernel, a);
 }
 
-template <typename Kernel>
-static cudaError_t launch_kernel_pdl(Kernel kernel, const GemvArgsB& a, const GemvPlanB& p, cudaStream_t stream) {
+template <typename Kernel, typename... Extra>
+static cudaError_t launch_kernel_pdl(Kernel kernel, const GemvArgsB& a, const GemvPlanB& p, cudaStream_t stream, const Extra&... extra) {
     if (p.smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem);
         if (e != cudaSuccess) return e;
@@ -65,14 +66,14 @@ static cudaError_t launch_kernel_pdl(Kernel kernel, const GemvArgsB& a, const Ge
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kernel, a);
+    return cudaLaunchKernelEx(&cfg, kernel, a, extra...);
 }
 
 template <class C>
 static cudaError_t launch_gemv_codec(const GemvArgsB& a, const GemvPlanB& p, cudaStream_t stream) {
     switch (p.passes) {
         case -2: return launch_kernel_pdl(gemv1_bl_swiglu_kernel<C>, a, p, stream);
-        case -1: return launch_kernel_pdl(gemv1_bl_multi_kernel<C>, a, p, stream);
+        case -1: return p.multi ? launch_kernel_pdl(gemv1_bl_multi_kernel<C>, a, p, stream, *p.multi) : cudaErrorInvalidValue;
         case 0: return launch_kernel_pdl(gemv1_bl_kernel<C>, a, p, stream);
         case 1: return launch_kernel_pdl(gemvn_bl_kernel<C, 1>, a, p, stream);
         case 2: return launch_kernel_pdl(gemvn_bl_kernel<C, 2>, a, p, stream);
