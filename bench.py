@@ -187,6 +187,7 @@ def main() -> None:
     ap.add_argument("--match", default=None, help="with --only sweep: run the cases whose name contains this text")
     ap.add_argument("--tokens", type=int, nargs="*", default=None, help="token counts for --only moe")
     ap.add_argument("--batch", type=int, nargs="*", default=None, help="batch sizes for --only decoder")
+    ap.add_argument("--layers", type=int, default=32, help="blocks of the --only decoder model (fewer: a small case for profilers)")
     ap.add_argument("--no-parallel", action="store_true",
                     help="at --gpus > 1 skip the sharded paths (keys tp_rowparallel, ep_moe_cfg4) and time the replicas only")
     args = ap.parse_args()
@@ -213,7 +214,7 @@ def main() -> None:
         emit(gemm_bench(local_rank, pk.get("bf16_tflops_sustained", pk["bf16_tflops"])))
         return
     if args.only == "decoder":
-        emit({"decoder_cfg5": decoder_bench(local_rank, 0, 1, None, batches=tuple(args.batch or (1, 16)))})
+        emit({"decoder_cfg5": decoder_bench(local_rank, 0, 1, None, batches=tuple(args.batch or (1, 16)), layers=args.layers)})
         return
     if args.only == "moe":
         emit(moe_layer_bench(local_rank, measured_peaks()[0]["hbm_gbs"], token_counts=tuple(args.tokens or (1, 8, 32, 64, 128, 256, 1024))))
@@ -687,7 +688,7 @@ def ep_moe_bench(dev: int, rank: int, world: int, dist, token_counts=(1, 32, 256
     return out
 
 
-def decoder_bench(dev: int, rank: int, world: int, dist, batches=(1, 16), steps: int = 24) -> dict:
+def decoder_bench(dev: int, rank: int, world: int, dist, batches=(1, 16), steps: int = 24, layers: int = 32) -> dict:
     """BASELINE config 5: random-init 32-layer dense decoder (hidden 4096, 32 query / 8 KV heads of
     128, FFN 14336 SwiGLU, vocabulary 128256, RMSNorm, rotary embedding), attention projections NINT4
     (4, 24, 6), FFN and lm_head NINT6 (6, 24, 7), bf16 KV cache holding a 4096-token context, greedy
@@ -701,7 +702,7 @@ def decoder_bench(dev: int, rank: int, world: int, dist, batches=(1, 16), steps:
 
     d = f"cuda:{dev}"
     ctx = 4096
-    cfg = dict(hidden=4096, n_q_heads=32, n_kv_heads=8, ffn=14336, vocab=128256, layers=32,
+    cfg = dict(hidden=4096, n_q_heads=32, n_kv_heads=8, ffn=14336, vocab=128256, layers=layers,
                max_ctx=ctx + 2 * steps + 8, max_batch=max(batches))
     c = commod.Communicator(rank, world, max(batches) * cfg["hidden"], dev).connect() if world > 1 else None
     dec, _ = D.random_decoder(**cfg, rank=rank, world=world, comm=c, device=dev, seed=5000)

@@ -145,6 +145,16 @@ int mfqb_mul_mat_multi(const mfqb_weight* const* ws, int count, const void* x_bf
 int mfqb_mul_mat_swiglu(const mfqb_weight* w, const void* gate_up_f32, int m, void* y, int y_dtype,
                         mfqb_stream_t stream);
 
+/* Gate|up projection of a gated FFN with the activation in the epilogue.  The weight's rows come in
+ * 16-row blocks that alternate gate rows and up rows (block 2i = gate rows 16i .. 16i+15, block
+ * 2i+1 = the up rows of the same indices: a row permutation applied when the fused weight is
+ * packed); y [m, n / 2] = up * gate / (1 + exp(-gate)).  The same composition as
+ * mfqb_mul_mat_swiglu (mfq/kernels/cuda/glu.cuh:6-17) with the activation on the producing side,
+ * so the following down projection is a plain mfqb_mul_mat.  m = 1 on NINT weights runs in the
+ * single-row kernel; other cases take the product into library scratch and apply the activation. */
+int mfqb_mul_mat_glu(const mfqb_weight* w, const void* x_bf16, int m, void* y, int y_dtype,
+                     mfqb_stream_t stream);
+
 /* Tuning switches, for measurements.  "gemv1_kernel": which kernel a single-row product of a plain
  * NINT weight takes -- 0 by shape (default), 1 the per-warp ring kernel, 2 the streamed kernel.
  * No counterpart in the reference (its switches are MFQ_* environment variables,
@@ -329,7 +339,10 @@ int mfqb_comm_destroy(mfqb_comm* c);
  *    route plan and the quantised planes for batches that take the tiled kernels) must fit; a larger
  *    call is rejected with MFQB_ERR_ARG and a message giving both numbers -- use mfqb_moe_ffn then.
  *  - The first call on a device looks the array's device address up (once per device, with that
- *    device current).  Make that first call before any stream capture.
+ *    device current), and the first launch of each kernel variant (the single-row kernel for few
+ *    tokens, the tiled kernels per tile size for larger batches) sets its function attributes and
+ *    makes the driver load its code.  Make one call per batch-size regime you will use before any
+ *    stream capture; after that the call can be recorded into a graph.
  *  - All calls share the one array and it keeps the previous call's contents; each call clears
  *    the counters at its start first (everything else is written before it is read).  Two calls whose device work overlaps (different streams, or
  *    different host threads) race on it: serialise them.
@@ -360,7 +373,9 @@ typedef struct mfqb_decoder_config {
 int mfqb_decoder_create(const mfqb_decoder_config* cfg, int rank, int world, mfqb_comm* comm, int device,
                         mfqb_decoder** out);
 /* This rank's shapes: qkv [(n_q + 2 n_kv)/world * 128, hidden] (query rows, key rows, value rows);
- * o [hidden, n_q/world * 128]; gate_up [2 * ffn/world, hidden] (gate rows first); down [hidden, ffn/world]. */
+ * o [hidden, n_q/world * 128]; gate_up [2 * ffn/world, hidden] in 16-row blocks that
+ * alternate gate rows and up rows (the layout of mfqb_mul_mat_glu); down [hidden, ffn/world];
+ * ffn/world must be a multiple of 16. */
 int mfqb_decoder_set_layer(mfqb_decoder* d, int layer, const mfqb_weight* qkv, const mfqb_weight* o,
                            const mfqb_weight* gate_up, const mfqb_weight* down);
 /* lm_head: rows [begin, begin + rows) of the vocabulary (mfqb_decoder_vocab_shard) x hidden;

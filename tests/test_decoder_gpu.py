@@ -55,9 +55,8 @@ def _block_oracle(h, w, kc, vc, pos, nq, nkv):
         out[hq] = (p / p.sum()) @ vc[hq // g]
     h = h + w["o"] @ _bf(out.reshape(-1))
     xn = _rmsnorm(h)
-    gu = w["gate_up"] @ xn
-    f = gu.shape[0] // 2
-    act = _bf(O.swiglu(gu[:f], gu[f:]))
+    gu = (w["gate_up"] @ xn).reshape(-1, 2, 16)   # 16-row blocks alternate gate and up rows
+    act = _bf(O.swiglu(gu[:, 0].reshape(-1), gu[:, 1].reshape(-1)))
     return h + w["down"] @ act, k, v
 
 

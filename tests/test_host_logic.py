@@ -146,3 +146,20 @@ def test_package_encoders_produce_blobs_the_oracle_reads():
         ref = encode.bf16_round(np.random.default_rng(bits).standard_normal((20, 100), dtype=np.float32) * np.float32(0.02))
         snr = 10 * np.log10((ref ** 2).sum() / ((w - ref) ** 2).sum())
         assert snr > 5 * b - 2, (b, snr)
+
+
+def test_header_sizes_are_checked_before_anything_is_allocated_for_them():
+    """A few dozen bytes that claim gigabytes: the NINT reader compares the tail length with the header
+    before it sizes its arrays, the container reader bounds the record count by the bytes that are left."""
+    import struct
+    out, ng, gs = 2, 50_000_000, 24
+    head = struct.pack("<BBiii", 3, 5, gs, 0, ng * gs) + struct.pack("<I", 2) + struct.pack("<qq", out, ng * gs)
+    head += struct.pack("<II", out, ng) + b"\0" * (4 * out)
+    addr, n, keep = _capi.buffer_address(head)
+    bad = C.c_uint64()
+    assert lib.mfqb_selfcheck_layout(b"NINT3", addr, n, C.byref(bad)) == _capi.ERR_FORMAT
+    assert b"tail" in lib.mfqb_last_error()
+    image = b"MFQ1" + struct.pack("<I", 1) + struct.pack("<I", 0) + struct.pack("<I", 0xFFFFFFF0)
+    with pytest.raises(MfqbError) as e:
+        T.MfqFile(image=image)
+    assert e.value.code == _capi.ERR_FORMAT and "record count" in str(e.value)

@@ -221,3 +221,25 @@ def test_down_projection_with_fused_swiglu(profile):
         got = w.matmul_swiglu(torch.from_numpy(gu).cuda(), out_dtype=torch.float32).cpu().numpy().astype(np.float64)
         assert rel_l2(got, want) <= REL_L2, (profile, m, rel_l2(got, want))
     w.free()
+
+
+@pytest.mark.parametrize("profile", [(3, 24, 5), (4, 32, 6), (6, 32, 7)])
+def test_gated_projection_with_interleaved_row_blocks(profile):
+    """mfqb_mul_mat_glu: the fused gate|up weight stores 16-row blocks alternately (gate, up) and
+    the kernel writes up * silu(gate) (mfq/kernels/cuda/glu.cuh:6-17) -- one row in the single-row
+    kernel's epilogue, several rows through the product and an activation pass."""
+    bits, gs, sb = profile
+    rng = np.random.default_rng(4500 + bits)
+    for n, k in ((2 * 16 * 7, 1000), (2 * 16 * 150, 520), (2 * 16 * 37 + 32, 4096)):
+        blob = encode.random_nint_blob(n, k, bits, gs, sb, seed=4501 + n)
+        w_ref = O.dequant_nint(O.unpack_nint(blob)).astype(np.float64).reshape(n // 32, 2, 16, k)
+        gate, up = w_ref[:, 0].reshape(n // 2, k), w_ref[:, 1].reshape(n // 2, k)
+        w = QuantWeight.from_blob(f"NINT{bits}", blob)
+        for m in (1, 3):
+            x = encode.bf16_round(rng.standard_normal((m, k), dtype=np.float32))
+            g, u = x.astype(np.float64) @ gate.T, x.astype(np.float64) @ up.T
+            want = u * g / (1.0 + np.exp(-g))
+            got = w.matmul_glu(bf16_tensor(x), out_dtype=torch.float32).cpu().numpy().astype(np.float64)
+            assert got.shape == want.shape
+            assert rel_l2(got, want) <= REL_L2, (profile, n, k, m, rel_l2(got, want))
+        w.free()

@@ -58,6 +58,18 @@ def test_static_scratch_ffn_matches_allocating_ffn_twice_in_a_row():
         assert np.isfinite(b).all()
         # same kernels on the same inputs; partial sums meet in shared memory in arbitrary order
         assert np.linalg.norm(a - b) / np.linalg.norm(a) < 1e-5
+        # the same call recorded into a CUDA graph (after the warm-up above) and replayed
+        y_g = torch.zeros_like(y_b)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            rc_g = lib.mfqb_moe_ffn_static(gu._h, dn._h, x.data_ptr(), ids.data_ptr(), wts.data_ptr(), tokens, k, y_g.data_ptr(), F32,
+                                           torch.cuda.current_stream().cuda_stream)
+        assert rc_g == 0, lib.mfqb_last_error()
+        y_g.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        c = y_g.cpu().numpy().astype(np.float64)
+        assert np.linalg.norm(a - c) / np.linalg.norm(a) < 1e-5
     # beyond the built-in array: a clear refusal, nothing launched
     per_pair = 2 * f * 4 + f * 4 + h * 4
     too_many = (8 << 20) // (per_pair * k) + 8

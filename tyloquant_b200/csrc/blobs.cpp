@@ -85,6 +85,10 @@ HostNint parse_nint(const void* blob, uint64_t nbytes) {
     const uint64_t packed_tail = 2 * packed_nbytes(nsub, t.sub_bits) + packed_nbytes(nq, t.bits);
     const uint64_t legacy_tail = 2 * nsub + nq;  // whole-uint8 storage of older writers
     const uint64_t remaining = nbytes - c.off;
+    // sizes come from the header: nothing is allocated for them before the tail length has confirmed them
+    if (remaining != legacy_tail && remaining != packed_tail)
+        fail(MFQB_ERR_FORMAT, "invalid NINT blob tail: remaining=%llu packed=%llu legacy=%llu",
+             (unsigned long long)remaining, (unsigned long long)packed_tail, (unsigned long long)legacy_tail);
     t.ss.resize(nsub);
     t.sm.resize(nsub);
     t.q.resize(nq);

@@ -69,6 +69,8 @@ static void parse_image(mfqb_file& f, int si, bool first) {
         }
     }
     const uint32_t nrec = c.get<uint32_t>("record count");
+    // a table entry is at least two empty strings and a size (16 bytes): a larger count cannot be true
+    if (nrec > (s.size - c.off) / 16) fail(MFQB_ERR_FORMAT, "MFQ record count %u does not fit the file", nrec);
     std::vector<Record> recs;
     recs.reserve(nrec);
     for (uint32_t i = 0; i < nrec; ++i) {

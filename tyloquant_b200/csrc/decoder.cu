@@ -18,6 +18,8 @@
 #include <memory>
 #include <vector>
 
+#include <cmath>
+
 #include "cuda_util.h"
 
 namespace mfqb {
@@ -96,68 +98,110 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ h
     for (int i = tid + KEEP * 1024; i < nv; i += 1024) put(i, row[i], __ldg(g4 + i));
 }
 
-// qkv [rows, (nq + 2 nkv) * 128] float32 -> rotary embedding on q and k (halves convention: pairs
-// (i, i + 64)), q kept as float32 pre-scaled by 1/sqrt(128), k and v written as bf16 into the cache
-// at position pos[row].  Cache layout: [rows][nkv][max_ctx][128] for K and for V.
-__global__ void __launch_bounds__(64) rope_kv_write_kernel(const float* __restrict__ qkv, const int* __restrict__ pos, float* __restrict__ q_out,
-                                                           __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache, int nq, int nkv,
-                                                           int max_ctx, float theta) {
+// cos and sin of position x frequency for the 64 rotation pairs, once per step and sequence:
+// table [rows][64] (cos, sin).  The frequencies theta^(-2i/128) come from the host.
+__global__ void __launch_bounds__(64) rope_table_kernel(const int* __restrict__ pos, const float* __restrict__ inv_freq, float2* __restrict__ table) {
     dep_wait();
-    const int row = blockIdx.y, head = blockIdx.x, i = threadIdx.x;   // 64 threads: one rotation pair each
-    const int p = pos[row];
-    const float* src = qkv + ((size_t)row * (nq + 2 * nkv) + head) * kHeadDim;
-    const float a = src[i], b = src[i + 64];
-    if (head >= nq + nkv) {   // value head: plain copy into the cache
-        __nv_bfloat16* dst = vcache + (((size_t)row * nkv + (head - nq - nkv)) * max_ctx + p) * kHeadDim;
-        dst[i] = __float2bfloat16_rn(a);
-        dst[i + 64] = __float2bfloat16_rn(b);
-        return;
-    }
-    const float freq = powf(theta, -(float)(2 * i) / (float)kHeadDim);
     float sn, cs;
-    sincosf((float)p * freq, &sn, &cs);
-    const float ra = a * cs - b * sn, rb = b * cs + a * sn;
-    if (head < nq) {
-        float* dst = q_out + ((size_t)row * nq + head) * kHeadDim;
-        const float scale = 0.08838834764831845f;   // 1 / sqrt(128)
-        dst[i] = ra * scale;
-        dst[i + 64] = rb * scale;
-    } else {
-        __nv_bfloat16* dst = kcache + (((size_t)row * nkv + (head - nq)) * max_ctx + p) * kHeadDim;
-        dst[i] = __float2bfloat16_rn(ra);
-        dst[i + 64] = __float2bfloat16_rn(rb);
-    }
+    sincosf((float)pos[blockIdx.x] * inv_freq[threadIdx.x], &sn, &cs);
+    table[blockIdx.x * 64 + threadIdx.x] = make_float2(cs, sn);
 }
 
-// Grouped-query decode attention, first pass: CTA (split, kv head, row) scans its slice of the cache for
-// the G = nq / nkv query heads that share the KV head.  A half-warp holds one token (16 lanes x 8
-// dimensions = one 16-byte load per lane for K and for V); the CTA's eight half-warps take tokens
-// round robin, two tokens per half-warp and iteration, so that four 16-byte loads per lane are in
-// flight.  Scores are reduced inside the half-warp, the soft-max runs online per half-warp and
-// head.  Writes (max, sum, unnormalised output[128]) per (row, query head, split).
+// Rotary embedding (halves convention: pairs (i, i + 64)) of one 128-wide head at `src`: the lane's
+// eight dimensions 8 * l16 .. 8 * l16 + 7, times `scale`; tab = the sequence's 64 (cos, sin) pairs.
+__device__ __forceinline__ void rope8(const float* __restrict__ src, const float2* __restrict__ tab, int l16, float scale, float* out) {
+    const int base = 8 * (l16 & 7);   // pair index i = base + j in [0, 64)
+    const float4 lo0 = *reinterpret_cast<const float4*>(src + base), lo1 = *reinterpret_cast<const float4*>(src + base + 4);
+    const float4 hi0 = *reinterpret_cast<const float4*>(src + 64 + base), hi1 = *reinterpret_cast<const float4*>(src + 64 + base + 4);
+    const float lo[8] = {lo0.x, lo0.y, lo0.z, lo0.w, lo1.x, lo1.y, lo1.z, lo1.w};
+    const float hi[8] = {hi0.x, hi0.y, hi0.z, hi0.w, hi1.x, hi1.y, hi1.z, hi1.w};
+    const float4* t4 = reinterpret_cast<const float4*>(tab + base);   // two (cos, sin) pairs per load
+#pragma unroll
+    for (int j = 0; j < 8; j += 2) {
+        const float4 t = __ldg(t4 + (j >> 1));
+        const float ra0 = lo[j] * t.x - hi[j] * t.y, rb0 = hi[j] * t.x + lo[j] * t.y;
+        const float ra1 = lo[j + 1] * t.z - hi[j + 1] * t.w, rb1 = hi[j + 1] * t.z + lo[j + 1] * t.w;
+        out[j] = (l16 < 8 ? ra0 : rb0) * scale;
+        out[j + 1] = (l16 < 8 ? ra1 : rb1) * scale;
+    }
+}
+__device__ __forceinline__ uint4 pack_bf16x8(const float* f) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+    const __nv_bfloat162 c = __floats2bfloat162_rn(f[4], f[5]), d = __floats2bfloat162_rn(f[6], f[7]);
+    return make_uint4(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b), *reinterpret_cast<const uint32_t*>(&c),
+                      *reinterpret_cast<const uint32_t*>(&d));
+}
 __device__ __forceinline__ void bf16x8_to_f32(const uint4& r, float* f) {
     f[0] = __uint_as_float(r.x << 16); f[1] = __uint_as_float(r.x & 0xFFFF0000u);
     f[2] = __uint_as_float(r.y << 16); f[3] = __uint_as_float(r.y & 0xFFFF0000u);
     f[4] = __uint_as_float(r.z << 16); f[5] = __uint_as_float(r.z & 0xFFFF0000u);
     f[6] = __uint_as_float(r.w << 16); f[7] = __uint_as_float(r.w & 0xFFFF0000u);
 }
+
+constexpr int kMaxSplits = 64;
+constexpr int kPartStride = kHeadDim + 4;   // a split's record per head: 128 output values | max | sum | pad (528 bytes)
+
+// Grouped-query decode attention for one new token per sequence, one launch: rotary embedding,
+// cache write, scan and merge.  qkv [rows, (nq + 2 nkv) * 128] float32 is the fused projection;
+// the caches are [rows][nkv][max_ctx][128] bf16 for K and for V.
+//
+// CTA (split, kv head, row) scans its slice of the context for the G = nq / nkv query heads that share
+// the KV head.  Every CTA rotates those heads' queries itself (pre-scaled by 1/sqrt(128)); the CTA
+// whose slice holds the new position rotates the new key, rounds key and value to bf16 and writes
+// them into the caches before it scans (no other CTA reads that position in this step).  A
+// half-warp holds one token (16 lanes x 8 dimensions = one 16-byte load per lane for K and for V);
+// the CTA's eight half-warps take four tokens each per round of 32, eight 16-byte loads per lane in
+// flight, the first round requested before the queries are rotated.  Scores are reduced inside the
+// half-warp, the soft-max runs online per half-warp and head.  Each CTA leaves (unnormalised
+// output[128], max, sum) per head in `part`; the last CTA of a (row, kv head) to arrive -- a counter
+// per pair, left at zero -- merges the splits, a warp per head, and writes the bf16 attention output.
 template <int G>
-__global__ void __launch_bounds__(128) attn_decode_partial_kernel(const float* __restrict__ q, const __nv_bfloat16* __restrict__ kcache,
-                                                                  const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ pos,
-                                                                  float* __restrict__ part, int nq, int nkv, int max_ctx, int nsplit) {
+__global__ void __launch_bounds__(128, G <= 4 ? 4 : 2) attn_decode_kernel(const float* __restrict__ qkv, __nv_bfloat16* kcache, __nv_bfloat16* vcache,
+                                                             const int* __restrict__ pos, float* part, unsigned* counters,
+                                                             __nv_bfloat16* __restrict__ out, int nq, int nkv, int max_ctx, int nsplit,
+                                                             const float2* __restrict__ rope_table) {
     dep_wait();
     const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
     const int lane = threadIdx.x & 31, l16 = lane & 15, slot = threadIdx.x >> 4;   // slot: half-warp 0..7 of the CTA
-    const int len = pos[row] + 1;   // the token written by this step takes part
+    const int p = pos[row], len = p + 1;   // the token written by this step takes part
     const int per = (len + nsplit - 1) / nsplit;
     const int t0 = split * per, t1 = min(len, t0 + per);
-    float qv[G][8];
+    const float* qkv_row = qkv + (size_t)row * (nq + 2 * nkv) * kHeadDim;
+    const float2* tab = rope_table + (size_t)row * 64;
+    __nv_bfloat16* kb = kcache + ((size_t)row * nkv + kvh) * max_ctx * kHeadDim + 8 * l16;
+    __nv_bfloat16* vb = vcache + ((size_t)row * nkv + kvh) * max_ctx * kHeadDim + 8 * l16;
+    if (t0 <= p && p < t1) {   // this CTA's slice holds the new position (uniform over the CTA)
+        if (threadIdx.x < 32) {   // warp 0 writes the new key and value
+            float f[8];
+            if (lane < 16) {
+                rope8(qkv_row + (size_t)(nq + kvh) * kHeadDim, tab, l16, 1.0f, f);
+                *reinterpret_cast<uint4*>(kb + (size_t)p * kHeadDim) = pack_bf16x8(f);
+            } else {
+                const float* src = qkv_row + (size_t)(nq + nkv + kvh) * kHeadDim + 8 * l16;
+                const float4 a = *reinterpret_cast<const float4*>(src), b = *reinterpret_cast<const float4*>(src + 4);
+                f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+                *reinterpret_cast<uint4*>(vb + (size_t)p * kHeadDim) = pack_bf16x8(f);
+            }
+        }
+        __syncthreads();   // visible to the whole CTA before anyone reads that position
+    }
+    constexpr int TPR = 4;   // tokens per half-warp and round: slot, slot + 8, + 16, + 24 of a 32-token round
+    uint4 ck[TPR], cv[TPR];
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    auto fetch = [&](int base) {
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-        const float4* src = reinterpret_cast<const float4*>(q + ((size_t)row * nq + kvh * G + g) * kHeadDim + 8 * l16);
-        const float4 a = src[0], b = src[1];
-        qv[g][0] = a.x; qv[g][1] = a.y; qv[g][2] = a.z; qv[g][3] = a.w;
-        qv[g][4] = b.x; qv[g][5] = b.y; qv[g][6] = b.z; qv[g][7] = b.w;
+        for (int i = 0; i < TPR; ++i) {
+            const int t = base + slot + 8 * i;
+            const bool ok = t < t1;
+            ck[i] = ok ? *reinterpret_cast<const uint4*>(kb + (size_t)t * kHeadDim) : zero;
+            cv[i] = ok ? *reinterpret_cast<const uint4*>(vb + (size_t)t * kHeadDim) : zero;
+        }
+    };
+    if (t0 < t1) fetch(t0);
+    float qv[G][8];
+    if (t0 < t1) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) rope8(qkv_row + (size_t)(kvh * G + g) * kHeadDim, tab, l16, 0.08838834764831845f /* 1/sqrt(128) */, qv[g]);
     }
     float m[G], l[G], acc[G][8];
 #pragma unroll
@@ -167,52 +211,59 @@ __global__ void __launch_bounds__(128) attn_decode_partial_kernel(const float* _
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[g][i] = 0.f;
     }
-    const __nv_bfloat16* kb = kcache + ((size_t)row * nkv + kvh) * max_ctx * kHeadDim + 8 * l16;
-    const __nv_bfloat16* vb = vcache + ((size_t)row * nkv + kvh) * max_ctx * kHeadDim + 8 * l16;
-    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-    for (int base = t0; base < t1; base += 16) {   // uniform trip count over the CTA: the shuffles below need whole warps
-        const int ta = base + slot, tb = ta + 8;
-        const bool va = ta < t1, vb2 = tb < t1;
-        const uint4 kra = va ? *reinterpret_cast<const uint4*>(kb + (size_t)ta * kHeadDim) : zero;
-        const uint4 krb = vb2 ? *reinterpret_cast<const uint4*>(kb + (size_t)tb * kHeadDim) : zero;
-        const uint4 vra = va ? *reinterpret_cast<const uint4*>(vb + (size_t)ta * kHeadDim) : zero;
-        const uint4 vrb = vb2 ? *reinterpret_cast<const uint4*>(vb + (size_t)tb * kHeadDim) : zero;
-        float ka[8], kbv[8], fa[8], fb[8];
-        bf16x8_to_f32(kra, ka);
-        bf16x8_to_f32(krb, kbv);
-        bf16x8_to_f32(vra, fa);
-        bf16x8_to_f32(vrb, fb);
-        float sa[G], sb[G];
+    for (int base = t0; base < t1; base += 8 * TPR) {   // uniform trip count over the CTA: the shuffles below need whole warps
+        float sc[TPR][G];
 #pragma unroll
-        for (int g = 0; g < G; ++g) {
-            float x = 0.f, y = 0.f;
+        for (int i = 0; i < TPR; ++i) {
+            float kf[8];
+            bf16x8_to_f32(ck[i], kf);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                x += qv[g][i] * ka[i];
-                y += qv[g][i] * kbv[i];
+            for (int g = 0; g < G; ++g) {
+                float x = 0.f;
+#pragma unroll
+                for (int d = 0; d < 8; ++d) x += qv[g][d] * kf[d];
+                sc[i][g] = x;
             }
-            sa[g] = x;
-            sb[g] = y;
         }
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1)
 #pragma unroll
-            for (int g = 0; g < G; ++g) {
-                sa[g] += __shfl_xor_sync(0xffffffffu, sa[g], o);
-                sb[g] += __shfl_xor_sync(0xffffffffu, sb[g], o);
-            }
-        if (va) {   // uniform over the half-warp; tb valid implies ta valid
+            for (int i = 0; i < TPR; ++i)
+#pragma unroll
+                for (int g = 0; g < G; ++g) sc[i][g] += __shfl_xor_sync(0xffffffffu, sc[i][g], o);
+        if (base + slot < t1) {   // uniform over the half-warp; a later token of the round is valid only if the earlier ones are
+            float pr[TPR][G];
 #pragma unroll
             for (int g = 0; g < G; ++g) {
-                const float s1 = vb2 ? sb[g] : -INFINITY;
-                const float mn = fmaxf(m[g], fmaxf(sa[g], s1));
-                const float corr = __expf(m[g] - mn), pa = __expf(sa[g] - mn), pb = __expf(s1 - mn);
-                l[g] = l[g] * corr + pa + pb;
+                float mn = m[g];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) acc[g][i] = acc[g][i] * corr + pa * fa[i] + pb * fb[i];
+                for (int i = 0; i < TPR; ++i) {
+                    if (base + slot + 8 * i >= t1) sc[i][g] = -INFINITY;
+                    mn = fmaxf(mn, sc[i][g]);
+                }
+                const float corr = __expf(m[g] - mn);
+                float ps = 0.f;
+#pragma unroll
+                for (int i = 0; i < TPR; ++i) {
+                    pr[i][g] = __expf(sc[i][g] - mn);
+                    ps += pr[i][g];
+                }
+                l[g] = l[g] * corr + ps;
+#pragma unroll
+                for (int d = 0; d < 8; ++d) acc[g][d] *= corr;
                 m[g] = mn;
             }
+#pragma unroll
+            for (int i = 0; i < TPR; ++i) {
+                float vf[8];
+                bf16x8_to_f32(cv[i], vf);
+#pragma unroll
+                for (int g = 0; g < G; ++g)
+#pragma unroll
+                    for (int d = 0; d < 8; ++d) acc[g][d] += pr[i][g] * vf[d];
+            }
         }
+        if (base + 8 * TPR < t1) fetch(base + 8 * TPR);
     }
     // the eight half-warps of the CTA meet in shared memory
     __shared__ float sm_m[8][G], sm_l[8][G];
@@ -237,39 +288,42 @@ __global__ void __launch_bounds__(128) attn_decode_partial_kernel(const float* _
             ll += sm_l[w][g] * c;
             aa += sm_acc[w][g][d] * c;
         }
-        float* dst = part + (((size_t)row * nq + kvh * G + g) * nsplit + split) * (kHeadDim + 2);
-        if (d == 0) { dst[0] = mm; dst[1] = ll; }
-        dst[2 + d] = aa;
+        float* dst = part + (((size_t)row * nq + kvh * G + g) * nsplit + split) * kPartStride;
+        dst[d] = aa;
+        if (d == 0) { dst[kHeadDim] = mm; dst[kHeadDim + 1] = ll; }
     }
-}
-
-// Second pass: merges the splits of one (row, query head) and writes the bf16 attention output.
-__global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ out, int nq, int nsplit) {
-    dep_wait();
-    const int head = blockIdx.x, row = blockIdx.y, d = threadIdx.x;
-    const float* src = part + ((size_t)row * nq + head) * nsplit * (kHeadDim + 2);
-    float mm = -INFINITY;
-    for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, src[(size_t)s * (kHeadDim + 2)]);
-    float ll = 0.f, aa = 0.f;
-    for (int s = 0; s < nsplit; ++s) {
-        const float ms = src[(size_t)s * (kHeadDim + 2)];
-        const float c = ms == -INFINITY ? 0.f : __expf(ms - mm);
-        ll += src[(size_t)s * (kHeadDim + 2) + 1] * c;
-        aa += src[(size_t)s * (kHeadDim + 2) + 2 + d] * c;
+    // the last CTA of this (row, kv head) merges the splits: a warp per head, a lane per four dimensions
+    __shared__ unsigned s_prev;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_prev = atomicAdd(counters + (size_t)row * nkv + kvh, 1u);
+    __syncthreads();
+    if (s_prev != (unsigned)(nsplit - 1)) return;
+    __threadfence();
+    for (int g = threadIdx.x >> 5; g < G; g += 4) {
+        const float* src = part + ((size_t)row * nq + kvh * G + g) * nsplit * kPartStride;
+        // weights of the splits (nsplit <= 64: two per lane)
+        const bool h0 = lane < nsplit, h1 = lane + 32 < nsplit;
+        const float2 ml0 = h0 ? __ldcg(reinterpret_cast<const float2*>(src + (size_t)lane * kPartStride + kHeadDim)) : make_float2(-INFINITY, 0.f);
+        const float2 ml1 = h1 ? __ldcg(reinterpret_cast<const float2*>(src + (size_t)(lane + 32) * kPartStride + kHeadDim)) : make_float2(-INFINITY, 0.f);
+        float mm = fmaxf(ml0.x, ml1.x);
+        for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+        const float c0 = ml0.x == -INFINITY ? 0.f : __expf(ml0.x - mm), c1 = ml1.x == -INFINITY ? 0.f : __expf(ml1.x - mm);
+        float ll = ml0.y * c0 + ml1.y * c1;
+        for (int o = 16; o > 0; o >>= 1) ll += __shfl_xor_sync(0xffffffffu, ll, o);
+        float4 aa = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 16
+        for (int sp = 0; sp < nsplit; ++sp) {
+            const float c = __shfl_sync(0xffffffffu, sp < 32 ? c0 : c1, sp & 31);
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (size_t)sp * kPartStride) + lane);
+            aa.x += c * v.x; aa.y += c * v.y; aa.z += c * v.z; aa.w += c * v.w;
+        }
+        const float inv = 1.0f / ll;
+        const __nv_bfloat162 o01 = __floats2bfloat162_rn(aa.x * inv, aa.y * inv), o23 = __floats2bfloat162_rn(aa.z * inv, aa.w * inv);
+        *reinterpret_cast<uint2*>(out + ((size_t)row * nq + kvh * G + g) * kHeadDim + 4 * lane) =
+            make_uint2(*reinterpret_cast<const uint32_t*>(&o01), *reinterpret_cast<const uint32_t*>(&o23));
     }
-    out[((size_t)row * nq + head) * kHeadDim + d] = __float2bfloat16_rn(aa / ll);
-}
-
-// gate_up [rows, 2F] float32 (gate columns first) -> act = up * gate / (1 + exp(-gate)) as bf16 [rows, F]
-// (mfq/kernels/cuda/glu.cuh:6-17).
-__global__ void swiglu_rows_kernel(const float* __restrict__ gu, __nv_bfloat16* __restrict__ act, int rows, int F) {
-    dep_wait();
-    const size_t total = (size_t)rows * F;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        const size_t r = i / F, c = i % F;
-        const float g = gu[r * 2 * F + c], u = gu[r * 2 * F + F + c];
-        act[i] = __float2bfloat16_rn(u * g / (1.f + __expf(-g)));
-    }
+    if (threadIdx.x == 0) counters[(size_t)row * nkv + kvh] = 0u;
 }
 
 // logits [rows, n] float32 -> (largest value, its index + index_base) per row; ties go to the smaller index.
@@ -365,21 +419,28 @@ struct mfqb_decoder {
     mfqb_decoder_config cfg{};
     int rank = 0, world = 1, device = 0;
     mfqb_comm* comm = nullptr;       // borrowed; null when world == 1
-    int nq = 0, nkv = 0, f = 0, vshard = 0, vbase = 0, sms = 0;
+    int nq = 0, nkv = 0, f = 0, vshard = 0, vbase = 0, sms = 0, attn_per_sm = 4;
     std::vector<DecoderLayer> layers;
     const mfqb_weight* lm_head = nullptr;
     const void* embedding = nullptr;   // bf16 [vocab, H] on the device, borrowed
     DevBuf gamma_final;
     // workspaces
-    DevBuf h, xn, qkv, q, attn, proj, proj_sum, gu, act, logits, part, best_val, best_idx, gathered, gathered_sum, pos;
+    DevBuf h, xn, qkv, attn, attn_count, inv_freq, rope_table, proj, proj_sum, act, logits, part, best_val, best_idx, gathered, gathered_sum, pos;
 };
 
-// Context splits of the decode attention: enough CTAs to fill every SM about four times over, each
-// split at least one round of the CTA's half-warps.
-constexpr int kMaxSplits = 64;
-static int attn_splits(const mfqb_decoder* d, int rows) {
-    const int want = (4 * d->sms + d->nkv * rows - 1) / (d->nkv * rows);
-    return std::max(1, std::min(kMaxSplits, want));
+// Context splits of the decode attention: as many CTAs as are resident at once (one wave: the merge
+// by the last CTA of a head group then follows the scan directly), but at least so many that a CTA
+// scans no more than 256 positions of a long context.
+static int attn_splits(const mfqb_decoder* d, int rows, int ctx_bound) {
+    const int one_wave = d->attn_per_sm * d->sms / (d->nkv * rows);
+    const int by_length = (ctx_bound + 255) / 256;
+    return std::max(1, std::min(kMaxSplits, std::max(one_wave, by_length)));
+}
+
+// The step's rotation table (cos, sin per sequence and pair), before the first block that uses it.
+static void launch_rope_table(mfqb_decoder* d, int rows, cudaStream_t s) {
+    launch_dep(rope_table_kernel, dim3(rows), dim3(64), s, static_cast<const int*>(d->pos.p), static_cast<const float*>(d->inv_freq.p),
+               static_cast<float2*>(d->rope_table.p));
 }
 
 static void check_weight_shape(const mfqb_weight* w, int64_t n, int64_t k, const char* what) {
@@ -415,24 +476,21 @@ static const float* layer_forward(mfqb_decoder* d, int li, int rows, const float
     launch_dep(add_rmsnorm_kernel, dim3(rows), dim3(1024), s, static_cast<float*>(d->h.p), delta, static_cast<const float*>(L.gamma_attn.p),
                static_cast<__nv_bfloat16*>(d->xn.p), H, d->cfg.rms_eps);
     mul_mat(L.qkv, d->xn.p, rows, d->qkv.p, s);
-    launch_dep(rope_kv_write_kernel, dim3(d->nq + 2 * d->nkv, rows), dim3(64), s, static_cast<const float*>(d->qkv.p),
-               static_cast<const int*>(d->pos.p), static_cast<float*>(d->q.p), static_cast<__nv_bfloat16*>(L.kcache.p),
-               static_cast<__nv_bfloat16*>(L.vcache.p), d->nq, d->nkv, d->cfg.max_ctx, d->cfg.rope_theta);
-    const int nsplit = attn_splits(d, rows);
+    const int nsplit = attn_splits(d, rows, d->cfg.max_ctx);
     const dim3 agrid(nsplit, d->nkv, rows);
-    const float* qp = static_cast<const float*>(d->q.p);
-    const __nv_bfloat16 *kc = static_cast<const __nv_bfloat16*>(L.kcache.p), *vc = static_cast<const __nv_bfloat16*>(L.vcache.p);
-    const int* pos = static_cast<const int*>(d->pos.p);
-    float* part = static_cast<float*>(d->part.p);
+    auto attn = [&](auto kernel) {
+        launch_dep(kernel, agrid, dim3(128), s, static_cast<const float*>(d->qkv.p), static_cast<__nv_bfloat16*>(L.kcache.p),
+                   static_cast<__nv_bfloat16*>(L.vcache.p), static_cast<const int*>(d->pos.p), static_cast<float*>(d->part.p),
+                   static_cast<unsigned*>(d->attn_count.p), static_cast<__nv_bfloat16*>(d->attn.p), d->nq, d->nkv, d->cfg.max_ctx, nsplit,
+                   static_cast<const float2*>(d->rope_table.p));
+    };
     switch (G) {
-        case 1: launch_dep(attn_decode_partial_kernel<1>, agrid, dim3(128), s, qp, kc, vc, pos, part, d->nq, d->nkv, d->cfg.max_ctx, nsplit); break;
-        case 2: launch_dep(attn_decode_partial_kernel<2>, agrid, dim3(128), s, qp, kc, vc, pos, part, d->nq, d->nkv, d->cfg.max_ctx, nsplit); break;
-        case 4: launch_dep(attn_decode_partial_kernel<4>, agrid, dim3(128), s, qp, kc, vc, pos, part, d->nq, d->nkv, d->cfg.max_ctx, nsplit); break;
-        case 8: launch_dep(attn_decode_partial_kernel<8>, agrid, dim3(128), s, qp, kc, vc, pos, part, d->nq, d->nkv, d->cfg.max_ctx, nsplit); break;
+        case 1: attn(attn_decode_kernel<1>); break;
+        case 2: attn(attn_decode_kernel<2>); break;
+        case 4: attn(attn_decode_kernel<4>); break;
+        case 8: attn(attn_decode_kernel<8>); break;
         default: fail(MFQB_ERR_UNSUPPORTED, "query heads per KV head must be 1, 2, 4 or 8, got %d", G);
     }
-    launch_dep(attn_decode_merge_kernel, dim3(d->nq, rows), dim3(128), s, static_cast<const float*>(part), static_cast<__nv_bfloat16*>(d->attn.p),
-               d->nq, nsplit);
     // output projection: row-parallel under tensor parallelism
     const float* o_out;
     if (d->world > 1 && rows == 1) {
@@ -445,14 +503,11 @@ static const float* layer_forward(mfqb_decoder* d, int li, int rows, const float
     }
     launch_dep(add_rmsnorm_kernel, dim3(rows), dim3(1024), s, static_cast<float*>(d->h.p), o_out, static_cast<const float*>(L.gamma_ffn.p),
                static_cast<__nv_bfloat16*>(d->xn.p), H, d->cfg.rms_eps);
-    mul_mat(L.gate_up, d->xn.p, rows, d->gu.p, s);
-    if (d->world == 1 && rows == 1) {   // the down projection computes the activation as it loads its row
-        const int rc = mfqb_mul_mat_swiglu(L.down, d->gu.p, 1, d->proj.p, MFQB_F32, s);
+    // gate|up with the activation in the epilogue: the fused weight alternates 16-row blocks of gate and up rows
+    {
+        const int rc = mfqb_mul_mat_glu(L.gate_up, d->xn.p, rows, d->act.p, MFQB_BF16, s);
         if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
-        return static_cast<const float*>(d->proj.p);
     }
-    launch_dep(swiglu_rows_kernel, dim3(std::min(1024, (rows * d->f + 255) / 256)), dim3(256), s, static_cast<const float*>(d->gu.p),
-               static_cast<__nv_bfloat16*>(d->act.p), rows, d->f);
     if (d->world > 1 && rows == 1) {
         const int rc = mfqb_mul_mat_allreduce(L.down, d->act.p, 1, d->comm, d->proj_sum.p, MFQB_F32, s);
         if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
@@ -472,7 +527,7 @@ int mfqb_decoder_create(const mfqb_decoder_config* cfg, int rank, int world, mfq
         if (world > 1 && !comm) fail(MFQB_ERR_ARG, "mfqb_decoder_create: tensor parallelism needs a communicator");
         if (cfg->head_dim != kHeadDim) fail(MFQB_ERR_UNSUPPORTED, "head_dim must be %d", kHeadDim);
         if (cfg->n_q_heads % cfg->n_kv_heads || cfg->n_kv_heads % world || cfg->ffn % world || cfg->layers < 1 || cfg->max_batch < 1 ||
-            cfg->hidden != cfg->n_q_heads * kHeadDim || cfg->hidden % 8)
+            cfg->hidden != cfg->n_q_heads * kHeadDim || cfg->hidden % 8 || (cfg->ffn / world) % 16)
             fail(MFQB_ERR_ARG, "mfqb_decoder_create: head counts, FFN width and hidden size must divide over %d ranks (hidden = heads x 128)", world);
         auto d = std::make_unique<mfqb_decoder>();
         d->cfg = *cfg;
@@ -505,14 +560,34 @@ int mfqb_decoder_create(const mfqb_decoder_config* cfg, int rank, int world, mfq
         d->h.alloc(B * H * 4);
         d->xn.alloc(B * H * 2);
         d->qkv.alloc(B * (d->nq + 2 * d->nkv) * kHeadDim * 4);
-        d->q.alloc(B * d->nq * kHeadDim * 4);
+        {   // rotary frequencies theta^(-2i/128), i = 0..63
+            float freq[kHeadDim / 2];
+            for (int i = 0; i < kHeadDim / 2; ++i) freq[i] = (float)std::pow((double)cfg->rope_theta, -2.0 * i / kHeadDim);
+            d->inv_freq.alloc(sizeof(freq));
+            MFQB_CUDA(cudaMemcpy(d->inv_freq.p, freq, sizeof(freq), cudaMemcpyHostToDevice));
+        }
+        {   // resident CTAs per SM of the attention kernel this model uses
+            int per_sm = 0;
+            cudaError_t e = cudaErrorInvalidValue;
+            switch (cfg->n_q_heads / cfg->n_kv_heads) {
+                case 1: e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_kernel<1>, 128, 0); break;
+                case 2: e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_kernel<2>, 128, 0); break;
+                case 4: e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_kernel<4>, 128, 0); break;
+                case 8: e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_kernel<8>, 128, 0); break;
+                default: fail(MFQB_ERR_UNSUPPORTED, "query heads per KV head must be 1, 2, 4 or 8, got %d", cfg->n_q_heads / cfg->n_kv_heads);
+            }
+            MFQB_CUDA(e);
+            d->attn_per_sm = std::max(1, per_sm);
+        }
+        d->attn_count.alloc(B * d->nkv * 4);
+        MFQB_CUDA(cudaMemset(d->attn_count.p, 0, B * d->nkv * 4));
         d->attn.alloc(B * d->nq * kHeadDim * 2);
         d->proj.alloc(B * H * 4);
         d->proj_sum.alloc(B * H * 4);
-        d->gu.alloc(B * 2 * d->f * 4);
         d->act.alloc(B * d->f * 2);
         d->logits.alloc(B * std::max(d->vshard, 1) * 4);
-        d->part.alloc(B * d->nq * kMaxSplits * (kHeadDim + 2) * 4);
+        d->part.alloc(B * d->nq * kMaxSplits * kPartStride * 4);
+        d->rope_table.alloc(B * 64 * sizeof(float2));
         d->best_val.alloc(B * 4);
         d->best_idx.alloc(B * 4);
         d->gathered.alloc((size_t)world * B * 2 * 4);
@@ -586,6 +661,7 @@ int mfqb_decoder_step(mfqb_decoder* d, const int32_t* ids_in, int batch, int32_t
         const int H = d->cfg.hidden;
         launch_dep(embed_rows_kernel, dim3(batch), dim3(256), s, static_cast<const int*>(ids_in), static_cast<const __nv_bfloat16*>(d->embedding),
                    static_cast<float*>(d->h.p), H, d->cfg.vocab);
+        launch_rope_table(d, batch, s);
         const float* delta = nullptr;
         for (int li = 0; li < d->cfg.layers; ++li) delta = layer_forward(d, li, batch, delta, s);
         launch_dep(add_rmsnorm_kernel, dim3(batch), dim3(1024), s, static_cast<float*>(d->h.p), delta, static_cast<const float*>(d->gamma_final.p),
@@ -615,6 +691,7 @@ int mfqb_decoder_layer(mfqb_decoder* d, int layer, const float* h_in, int rows, 
         DeviceGuard guard(d->device);
         const size_t bytes = (size_t)rows * d->cfg.hidden * 4;
         MFQB_CUDA(cudaMemcpyAsync(d->h.p, h_in, bytes, cudaMemcpyDeviceToDevice, stream));
+        launch_rope_table(d, rows, stream);
         const float* delta = layer_forward(d, layer, rows, nullptr, stream);
         // fold the FFN output in with a norm whose bf16 output is discarded
         launch_dep(add_rmsnorm_kernel, dim3(rows), dim3(1024), stream, static_cast<float*>(d->h.p), delta, static_cast<const float*>(d->gamma_final.p),

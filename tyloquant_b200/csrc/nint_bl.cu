@@ -169,8 +169,9 @@ int nint_bl_max_passes(const NintDevB& w) {
 }
 
 // y[m, n] = x[m, k] * W^T for m <= 8 (the caller loops larger batches).  swiglu (m = 1 only): x is the
-// float32 gate|up row [2k] and the product is taken with up * silu(gate).
-void launch_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtype, int ldy, int device, cudaStream_t s, bool swiglu) {
+// float32 gate|up row [2k] and the product is taken with up * silu(gate).  glu (m = 1 only): the weight's
+// 16-row blocks alternate gate and up rows and y [n / 2] receives up * silu(gate).
+void launch_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtype, int ldy, int device, cudaStream_t s, bool swiglu, bool glu) {
     GemvArgsB a{};
     a.w = w;
     a.x = static_cast<const __nv_bfloat16*>(x);
@@ -186,6 +187,12 @@ void launch_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtyp
         p.threads = warps * 32;
         p.grid = std::min(w.nrb, ctas_per_sm(gemv1_smem(w, 1, warps), warps > 8 ? 2 : 3) * sms);
         a.rb_per_cta = (w.nrb + p.grid - 1) / p.grid;
+        if (glu) {   // (gate, up) pairs of row-blocks stay together
+            if ((w.nrb & 1) || (w.n & 31)) fail(MFQB_ERR_ARG, "gated product: the weight needs whole (gate, up) pairs of 16-row blocks, n = %d", w.n);
+            p.grid = std::min(w.nrb / 2, p.grid);
+            a.rb_per_cta = 2 * ((w.nrb / 2 + p.grid - 1) / p.grid);
+            a.glu = 1;
+        }
         a.private_sums = gemv1_private_sums(a.rb_per_cta);
         p.smem = gemv1_smem(w, a.rb_per_cta, warps);
         if (swiglu) {
@@ -193,13 +200,13 @@ void launch_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtyp
             a.x_mode = 2;
         }
     } else {
-        if (swiglu) fail(MFQB_ERR_ARG, "the fused activation belongs to the single-row kernel");
+        if (swiglu || glu) fail(MFQB_ERR_ARG, "the fused activation belongs to the single-row kernel");
         const int max_rows = 2 * nint_bl_max_passes(w);
         if (m > max_rows) {   // wide records: the batch goes through in several launches
             const size_t ysz = y_dtype == MFQB_F32 ? 4 : 2;
             for (int m0 = 0; m0 < m; m0 += max_rows)
                 launch_bl_gemv(w, static_cast<const char*>(x) + (size_t)m0 * w.k * 2, std::min(max_rows, m - m0),
-                               static_cast<char*>(y) + (size_t)m0 * ldy * ysz, y_dtype, ldy, device, s, false);
+                               static_cast<char*>(y) + (size_t)m0 * ldy * ysz, y_dtype, ldy, device, s, false, false);
             return;
         }
         launch_x_planes(w, x, m, planes_scratch(device, nint_bl_planes_bytes(w, m), s), &a.xq_g, &a.gtab_g, s, false);
@@ -341,12 +348,24 @@ void launch_bl_gemv_reduce(const NintDevB& w, const void* x, void* y, int y_dtyp
     GemvPlanB p;
     const int warps = gemv1_warps(w), sms = device_sm_count(device);
     p.threads = warps * 32;
-    // every CTA waits for its peers inside the kernel: the whole grid must be resident at once
+    // Every CTA waits for its peers inside the kernel, so the whole grid must be resident at once: the
+    // grid is sized from the occupancy the runtime reports for this kernel, block size and shared memory
+    // (which itself grows with the row-blocks per CTA, hence the second look).
     p.grid = std::min(w.nrb, ctas_per_sm(gemv1_smem(w, 1, warps), warps > 8 ? 2 : 3) * sms);
-    a.rb_per_cta = (w.nrb + p.grid - 1) / p.grid;
-    a.private_sums = gemv1_private_sums(a.rb_per_cta);
-    p.smem = gemv1_smem(w, a.rb_per_cta, warps);
-    if (p.smem > kGemvSmemLimit) fail(MFQB_ERR_UNSUPPORTED, "weight of %d rows is too tall for one resident grid", w.n);
+    for (int round = 0; round < 3; ++round) {
+        a.rb_per_cta = (w.nrb + p.grid - 1) / p.grid;
+        a.private_sums = gemv1_private_sums(a.rb_per_cta);
+        p.smem = gemv1_smem(w, a.rb_per_cta, warps);
+        if (p.smem > kGemvSmemLimit) fail(MFQB_ERR_UNSUPPORTED, "weight of %d rows is too tall for one resident grid", w.n);
+        int per_sm = 0;
+        GemvPlanB query = p;
+        query.occupancy_out = &per_sm;
+        dispatch(a, query, s, "row-parallel GEMV (occupancy)");
+        if (per_sm < 1) fail(MFQB_ERR_UNSUPPORTED, "row-parallel GEMV: a CTA of %d threads and %zu bytes does not fit an SM", p.threads, p.smem);
+        if (p.grid <= per_sm * sms) break;
+        if (round == 2) fail(MFQB_ERR_UNSUPPORTED, "row-parallel GEMV: no grid of this weight's %d row-blocks is resident at once", w.nrb);
+        p.grid = per_sm * sms;
+    }
     dispatch(a, p, s, "row-parallel GEMV");
 }
 

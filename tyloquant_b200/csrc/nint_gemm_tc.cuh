@@ -36,7 +36,8 @@ struct GemmArgs {
     int y_dtype;
     int bn;              // tokens per tile: 64, 128, 256 or 512
     int stages;          // depth of the weight ring, in 64-column atoms (at least one chunk)
-    int xstages;         // depth of the activation ring, in atoms
+    int xstages;         // depth of the activation ring, in stages of xcols columns
+    int xcols;           // columns of K per activation stage: 64 (128-byte rows, 128-byte swizzle) or 32 (64-byte rows, 64-byte swizzle)
     int* error;          // device word: set to MFQB_ERR_TIMEOUT when a wait expires
     // Grouped mode (expert matmul over a route plan whose tile size is bn): blockIdx.y is a tile of
     // up to bn pairs of one expert; x16 holds the input rows in plan order (row p = pair
@@ -75,7 +76,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) nint_gemm_tc_kernel(const Gem
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int stage_bytes = 128 * 128;           // one weight atom
-    const int xstage_bytes = BN * 128;               // one activation atom
+    const int XC = a.xcols, xper = 64 / XC;          // activation stages per weight atom
+    const int xstage_bytes = BN * XC * 2;            // one activation stage
     unsigned char* xtiles = tiles + (size_t)NS * stage_bytes;
     __shared__ __align__(8) uint64_t full_bar[8], empty_bar[8], xfull_bar[4], xempty_bar[4], done_bar;
     __shared__ uint32_t tmem_base_slot;
@@ -203,31 +205,40 @@ __global__ void __launch_bounds__(kGemmThreads, 1) nint_gemm_tc_kernel(const Gem
     } else if (warp == kGemmProducerWarps + 1) {
         // ------------------------------ x loader (TMA) ------------------------------
         if (lane == 0) {
-            const int natoms = w.nchunks * ATOMS;
-            for (int ai = 0; ai < natoms; ++ai) {
-                const int st = ai % NB, use = ai / NB;
+            const int nx = w.nchunks * ATOMS * xper;
+            for (int xi = 0; xi < nx; ++xi) {
+                const int st = xi % NB, use = xi / NB;
                 if (use > 0 && !mbar_wait(&xempty_bar[st], (use - 1) & 1)) { failed = 1; break; }
                 mbar_arrive_expect_tx(&xfull_bar[st], (uint32_t)xstage_bytes);
                 for (int r0 = 0; r0 < BN; r0 += 256)   // a box holds at most 256 rows
-                    tma_load_2d(xtiles + (size_t)st * xstage_bytes + (size_t)r0 * 128, &x_map, ai * 64, tok0 + r0, &xfull_bar[st]);
+                    tma_load_2d(xtiles + (size_t)st * xstage_bytes + (size_t)r0 * XC * 2, &x_map, xi * XC, tok0 + r0, &xfull_bar[st]);
             }
         }
     } else if (lane == 0) {
         // ------------------------------ mma issuer ------------------------------
         const uint32_t idesc = instr_desc_f16(128, BN < 256 ? BN : 256);
         const int natoms = w.nchunks * ATOMS;
-        for (int ai = 0; ai < natoms; ++ai) {
-            const int st = ai % NS, xs = ai % NB;
-            if (!mbar_wait(&full_bar[st], (ai / NS) & 1) || !mbar_wait(&xfull_bar[xs], (ai / NB) & 1)) { failed = 1; break; }
-            tc_fence_after_sync();
-            const uint32_t a_base = smem_u32(tiles + st * stage_bytes), b_base = smem_u32(xtiles + (size_t)xs * xstage_bytes);
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-                for (int h = 0; h < BN; h += 256)   // one instruction covers at most 256 token columns
-                    tc_mma_f16(tmem_d + (uint32_t)h, smem_desc_sw128(a_base + j * 32), smem_desc_sw128(b_base + h * 128 + j * 32), idesc,
-                               ai > 0 || j > 0);
-            tc_commit(&empty_bar[st]);
-            tc_commit(&xempty_bar[xs]);
+        bool ok = true;
+        for (int ai = 0; ai < natoms && ok; ++ai) {
+            const int st = ai % NS;
+            if (!mbar_wait(&full_bar[st], (ai / NS) & 1)) { failed = 1; break; }
+            const uint32_t a_base = smem_u32(tiles + st * stage_bytes);
+            for (int xh = 0; xh < xper; ++xh) {   // the activation stages under this weight atom
+                const int xi = ai * xper + xh, xs = xi % NB;
+                if (!mbar_wait(&xfull_bar[xs], (xi / NB) & 1)) { failed = 1; ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t b_base = smem_u32(xtiles + (size_t)xs * xstage_bytes);
+                const int nj = 4 / xper;   // K = 16 slices per activation stage
+                for (int jj = 0; jj < nj; ++jj) {
+                    const int j = xh * nj + jj;
+                    for (int h = 0; h < BN; h += 256) {   // one instruction covers at most 256 token columns
+                        const uint64_t bdesc = XC == 64 ? smem_desc_sw128(b_base + h * 128 + jj * 32) : smem_desc_sw64(b_base + h * 64 + jj * 32);
+                        tc_mma_f16(tmem_d + (uint32_t)h, smem_desc_sw128(a_base + j * 32), bdesc, idesc, ai > 0 || j > 0);
+                    }
+                }
+                tc_commit(&xempty_bar[xs]);
+            }
+            if (ok) tc_commit(&empty_bar[st]);
         }
         tc_commit(&done_bar);
     }
@@ -268,8 +279,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) nint_gemm_tc_kernel(const Gem
     }
 }
 
+// Dynamic shared memory a tile kernel may plan with: 227 KB per CTA less the alignment slack and the barriers.
+constexpr size_t kGemmSmemBudget = 227 * 1024 - 1024 - 512;
 struct GemmPlan {
-    int bn, stages, xstages, grid_x, grid_y;
+    int bn, stages, xstages, xcols, grid_x, grid_y;
     size_t smem;
 };
 // The group size must be a multiple of 8 (a chunk is then whole swizzle atoms); returns bn = 0 otherwise.
@@ -277,22 +290,37 @@ inline GemmPlan plan_nint_gemm(const NintDevB& w, int m) {
     GemmPlan p{};
     if (w.gs % 8 != 0 || w.t8 * 8 != w.gs) return p;
     const int atoms = kChunkGroupsB * w.gs / 64;
-    // Wide token tiles amortise the dequantisation: the widest of 512, 256, 128 tokens for which the
-    // weight ring still holds one whole chunk beside an activation ring of two (512) or three atoms.
-    int bn = 512;
-    auto weight_stages = [](int bn_) {
-        const int xst = bn_ >= 512 ? 2 : 3;
-        return std::min(8, (int)((220 * 1024 - (size_t)xst * bn_ * 128) / (128 * 128)));
-    };
-    while (bn > 128 && weight_stages(bn) < atoms) bn /= 2;
-    while (bn > 64 && bn / 2 >= m) bn /= 2;
+    // 512-token tiles amortise the dequantisation best.  With two 64-column activation stages (128 KB) the
+    // weight ring holds five atoms: one whole chunk of up to four atoms, whose decode then overlaps the
+    // tensor core only a little.  Measured, that still beats a two-chunk weight ring
+    // fed by three 32-column stages (424 against 578 TFLOP/s for group size 32): every stage is a
+    // separate trip to L2, and the tile's activation feed -- 64 bytes per clock per SM at the tensor
+    // core's full rate -- is what bounds the kernel.  The 32-column stages remain for chunks that
+    // would not fit otherwise.
+    auto stages_for = [](int bn_, int xcols, int xst) { return std::min(8, (int)((kGemmSmemBudget - (size_t)xst * bn_ * xcols * 2) / (128 * 128))); };
+    int bn = 512, xcols = 64, xst = 2;
+    if (atoms > 5) {   // (a six-atom chunk fits beside two 64-column stages, but measured slower than the 32-column form)
+        if (stages_for(512, 32, 3) >= atoms) { xcols = 32; xst = 3; }
+        else {
+            bn = 256;
+            xst = 3;
+            while (bn > 128 && stages_for(bn, 64, 3) < atoms) bn /= 2;
+        }
+    }
+    while (bn > 64 && bn / 2 >= m) {
+        bn /= 2;
+        xcols = 64;
+        xst = 3;
+    }
     p.bn = bn;
-    p.xstages = bn >= 512 ? 2 : 3;
-    p.stages = weight_stages(bn);
+    p.xstages = xst;
+    p.xcols = xcols;
+    p.stages = stages_for(bn, xcols, xst);
+    if (bn == 512 && xcols == 64) p.stages = std::min(p.stages, 5);   // five beat six (578 against 505 TFLOP/s on 14336 x 4096, 512 tokens)
     if (p.stages < atoms) { p.bn = 0; return p; }
     p.grid_x = (w.n + 127) / 128;
     p.grid_y = (m + bn - 1) / bn;
-    p.smem = (size_t)p.stages * 128 * 128 + (size_t)p.xstages * bn * 128 + 1024;
+    p.smem = (size_t)p.stages * 128 * 128 + (size_t)p.xstages * bn * p.xcols * 2 + 1024;
     return p;
 }
 
@@ -304,7 +332,8 @@ inline GemmPlan plan_nint_gemm_grouped(const NintDevB& w, int bn, int rows_per_e
     const int atoms = kChunkGroupsB * w.gs / 64;
     p.bn = bn;
     p.xstages = 3;
-    p.stages = std::min(8, (int)((220 * 1024 - (size_t)p.xstages * bn * 128) / (128 * 128)));
+    p.xcols = 64;
+    p.stages = std::min(8, (int)((kGemmSmemBudget - (size_t)p.xstages * bn * 128) / (128 * 128)));
     if (p.stages < atoms) { p.bn = 0; return p; }
     p.grid_x = (rows_per_expert + 127) / 128;
     p.grid_y = max_tiles;

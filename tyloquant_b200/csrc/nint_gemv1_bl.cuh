@@ -72,6 +72,9 @@ struct GemvArgsB {
     // the route weights, in route order, into y_final [tokens, ldy] (moe_weighted_reduce,
     // mfq/kernels/cuda/moe.cu:2957-2977).  token_count: [tokens * gridDim.x] zeros, left zero again.
     int x_mode;
+    // Single-row kernel, gated FFN: the weight's 16-row blocks alternate (gate rows, up rows); the kernel
+    // writes up * silu(gate), n / 2 values, instead of the n products.
+    int glu;
     const float* route_w;
     float* pair_out;
     unsigned* token_count;
@@ -493,7 +496,13 @@ __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB
         y_off = (size_t)pair * a.ldy;
     }
     int rbl0, nrb;
-    split_row_blocks(blockIdx.x, gridDim.x, rb_total, rbl0, nrb);
+    if (a.glu) {   // whole (gate, up) pairs of row-blocks per CTA
+        split_row_blocks(blockIdx.x, gridDim.x, rb_total >> 1, rbl0, nrb);
+        rbl0 *= 2;
+        nrb *= 2;
+    } else {
+        split_row_blocks(blockIdx.x, gridDim.x, rb_total, rbl0, nrb);
+    }
     const int rb0 = rb_base + rbl0;
     const int row_limit = a.route_ids != nullptr ? a.ldy : w.n;   // rows this problem has (an expert's rows are padded to whole blocks)
 
@@ -661,6 +670,25 @@ __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB
             }
         }
         peer_call_done(pr, seq);
+        return;
+    }
+    if (a.glu) {
+        const int half = w.n >> 1;
+        for (int i = tid; i < nrb * 8; i += blockDim.x) {
+            const int pr = i >> 4, r = i & 15, row = (rbl0 >> 1) * 16 + i;
+            if (row < half) {
+                float g = ypart[pr * 32 + r], u = ypart[pr * 32 + 16 + r];
+                for (int cp = 1; cp < ycopies; ++cp) {
+                    g += ypart[cp * ystride + pr * 32 + r];
+                    u += ypart[cp * ystride + pr * 32 + 16 + r];
+                }
+                g *= kXScaleUndo;
+                u *= kXScaleUndo;
+                const float v = u * g / (1.0f + expf(-g));
+                if (a.y_dtype == 0 /* MFQB_F32 */) reinterpret_cast<float*>(a.y)[row] = v;
+                else reinterpret_cast<__nv_bfloat16*>(a.y)[row] = __float2bfloat16_rn(v);
+            }
+        }
         return;
     }
     for (int i = tid; i < nrb * 16; i += blockDim.x) {

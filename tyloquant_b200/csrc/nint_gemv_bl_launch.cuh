@@ -9,6 +9,7 @@ namespace mfqb {
 struct GemvPlanB {
     int grid = 1, grid_y = 1, threads = 256;
     const GemvMultiTable* multi = nullptr;   // the weights of a multi-weight launch (passes == -1)
+    int* occupancy_out = nullptr;            // set: nothing is launched, the kernel's resident CTAs per SM for (threads, smem) are stored here
     int passes = 0;      // 0: single-row kernel; 1, 2, 4: batched kernel with that many two-row passes; -1: multi-weight single-row launch; -2: single-row kernel on a float32 gate|up row
     size_t smem = 0;
 };
@@ -56,6 +57,7 @@ static cudaError_t launch_kernel_pdl(Kernel kernel, const GemvArgsB& a, const Ge
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem);
         if (e != cudaSuccess) return e;
     }
+    if (p.occupancy_out) return cudaOccupancyMaxActiveBlocksPerMultiprocessor(p.occupancy_out, kernel, p.threads, p.smem);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)p.grid, (unsigned)p.grid_y);
     cfg.blockDim = dim3((unsigned)p.threads);

@@ -13,7 +13,7 @@
 
 namespace mfqb {
 
-void launch_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtype, int ldy, int device, cudaStream_t s, bool swiglu = false);
+void launch_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtype, int ldy, int device, cudaStream_t s, bool swiglu = false, bool glu = false);
 
 struct NvqDevice {
     NintDevB d{};

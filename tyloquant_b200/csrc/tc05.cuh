@@ -61,6 +61,18 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
     return d;
 }
 
+// The same for a K-major tile whose rows are 64 bytes (32 f16 columns) with the 64-byte swizzle;
+// eight-row groups are 512 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw64(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(512 >> 4) << 32;                        // stride byte offset: 8 rows x 64 bytes
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)4 << 61;                                 // layout type: 64-byte swizzle
+    return d;
+}
+
 // Instruction descriptor: f16 x f16 -> f32, both operands K-major, tile M x N.
 __host__ __device__ constexpr uint32_t instr_desc_f16(int m, int n) {
     return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);

@@ -83,7 +83,7 @@ int* gemm_status_word(int device) {   // pinned, mapped: the host can read it wi
 
 // Tensor map of the f16 activations [m, kx] for 64-column x bn-row boxes with the 128-byte swizzle.
 // cuTensorMapEncodeTiled is looked up through the runtime, so the library links only libcudart.
-static CUtensorMap make_x_map(const void* x16, int m, int kx, int bn) {
+static CUtensorMap make_x_map(const void* x16, int m, int kx, int bn, int xcols = 64) {
     typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -98,10 +98,10 @@ static CUtensorMap make_x_map(const void* x16, int m, int kx, int bn) {
     CUtensorMap map;
     const cuuint64_t dims[2] = {(cuuint64_t)kx, (cuuint64_t)m};
     const cuuint64_t strides[1] = {(cuuint64_t)kx * sizeof(__half)};
-    const cuuint32_t box[2] = {64u, (cuuint32_t)std::min(bn, 256)};   // a box holds at most 256 rows; wider tiles take two loads
+    const cuuint32_t box[2] = {(cuuint32_t)xcols, (cuuint32_t)std::min(bn, 256)};   // a box holds at most 256 rows; wider tiles take two loads
     const cuuint32_t elem[2] = {1u, 1u};
     const CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x16), dims, strides, box, elem,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, xcols == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) fail(MFQB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
     return map;
@@ -126,6 +126,7 @@ static bool launch_nint_gemm(const NintDevB& w, const void* x, int m, void* y, i
     a.bn = p.bn;
     a.stages = p.stages;
     a.xstages = p.xstages;
+    a.xcols = p.xcols;
     a.error = gemm_status_word(device);
     void* xb = g_gemm.x16.get(device, (size_t)m * a.kx * sizeof(__half), s, "mfqb_mul_mat (f16 copy of the activations)");
     a.x16 = static_cast<const __half*>(xb);
@@ -133,7 +134,7 @@ static bool launch_nint_gemm(const NintDevB& w, const void* x, int m, void* y, i
     x_to_f16_kernel<<<(int)std::min<size_t>((total + 255) / 256, 148 * 8), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), m, w.k,
                                                                                       a.kx, static_cast<__half*>(xb));
     MFQB_CUDA(cudaGetLastError());
-    const CUtensorMap x_map = make_x_map(xb, m, a.kx, p.bn);
+    const CUtensorMap x_map = make_x_map(xb, m, a.kx, p.bn, p.xcols);
     cudaError_t e;
     switch (w.bits) {
         case 2: e = launch_nint_gemm_bits<2>(a, p, x_map, s); break;
@@ -197,6 +198,7 @@ void launch_nint_gemm_grouped(const NintDevB& w, const void* x16, int pairs, int
     a.bn = p.bn;
     a.stages = p.stages;
     a.xstages = p.xstages;
+    a.xcols = p.xcols;
     a.expert_bounds = expert_bounds;
     a.tile_bounds = tile_bounds;
     a.pair_order = pair_order;
@@ -231,7 +233,7 @@ using namespace mfqb;
 
 namespace mfqb {
 void launch_nint_bl_dequant(const NintDevB& w, void* out, int out_dtype, cudaStream_t s);
-void launch_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtype, int ldy, int device, cudaStream_t s, bool swiglu = false);
+void launch_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtype, int ldy, int device, cudaStream_t s, bool swiglu = false, bool glu = false);
 bool nint_bl_supported(int bits, int gs);
 size_t gemvs_fix_bytes(int device);
 void launch_swiglu(const void* gate_up, int in_dtype, int rows, int f, void* hidden, cudaStream_t s);
@@ -304,6 +306,20 @@ const NintDevB& weight_device_layout(const mfqb_weight* w) { return w->family ==
 int weight_device_index(const mfqb_weight* w) { return w->device; }
 
 }  // namespace mfqb
+
+// prod [rows, n] float32 whose columns come in 16-wide blocks alternating gate and up -> y [rows, n / 2] = up * silu(gate)
+__global__ void glu_blocks_kernel(const float* __restrict__ prod, int rows, int n, void* __restrict__ y, int y_dtype) {
+    const int half = n >> 1;
+    const size_t total = (size_t)rows * half;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / half;
+        const int j = (int)(i % half), blk = j >> 4, lane = j & 15;
+        const float g = prod[r * n + blk * 32 + lane], u = prod[r * n + blk * 32 + 16 + lane];
+        const float v = u * g / (1.0f + expf(-g));
+        if (y_dtype == MFQB_F32) static_cast<float*>(y)[i] = v;
+        else static_cast<__nv_bfloat16*>(y)[i] = __float2bfloat16_rn(v);
+    }
+}
 
 extern "C" {
 #pragma GCC visibility push(default)
@@ -425,6 +441,27 @@ int mfqb_mul_mat_swiglu(const mfqb_weight* w, const void* gate_up, int m, void* 
         launch_swiglu(gate_up, MFQB_F32, m, (int)w->info.k, act, stream);
         const int rc = mfqb_mul_mat(w, act, m, y, y_dtype, stream);
         if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
+    });
+}
+
+int mfqb_mul_mat_glu(const mfqb_weight* w, const void* x, int m, void* y, int y_dtype, mfqb_stream_t stream) {
+    return guarded([&] {
+        if (!w || !x || !y) fail(MFQB_ERR_ARG, "mfqb_mul_mat_glu: null argument");
+        if (m < 1) fail(MFQB_ERR_ARG, "mfqb_mul_mat_glu: m must be >= 1, got %d", m);
+        if (y_dtype != MFQB_F32 && y_dtype != MFQB_BF16) fail(MFQB_ERR_ARG, "mfqb_mul_mat_glu: bad output dtype");
+        if (w->info.n % 32) fail(MFQB_ERR_ARG, "mfqb_mul_mat_glu: the weight needs whole (gate, up) pairs of 16-row blocks, n = %lld", (long long)w->info.n);
+        DeviceGuard guard(w->device);
+        if (m == 1 && w->family == MFQB_FAMILY_NINT) {   // activation applied where the kernel writes its rows
+            launch_bl_gemv(w->nint, x, 1, y, y_dtype, (int)w->info.n, w->device, stream, false, true);
+            return;
+        }
+        static GrowOnlyScratch pool;
+        float* prod = static_cast<float*>(pool.get(w->device, (size_t)m * w->info.n * 4, stream, "mfqb_mul_mat_glu (gate and up products)"));
+        const int rc = mfqb_mul_mat(w, x, m, prod, MFQB_F32, stream);
+        if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
+        const size_t total = (size_t)m * (w->info.n / 2);
+        glu_blocks_kernel<<<(unsigned)std::min<size_t>((total + 255) / 256, 148 * 8), 256, 0, stream>>>(prod, m, (int)w->info.n, y, y_dtype);
+        MFQB_CUDA(cudaGetLastError());
     });
 }
 

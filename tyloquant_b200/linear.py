@@ -80,6 +80,19 @@ class QuantWeight:
                                F32 if tdt == torch.float32 else BF16, _stream_ptr(self.device)))
         return y[0] if squeeze else y
 
+    def matmul_glu(self, x, out_dtype=None):
+        """Gated product for a weight whose 16-row blocks alternate gate and up rows:
+        ``up * silu(gate)`` of ``x @ W.T``, shape [m, n / 2]."""
+        torch = _torch()
+        x2 = x.reshape(-1, self.k).contiguous()
+        if x2.dtype != torch.bfloat16 or not x2.is_cuda or x2.device.index != self.device:
+            raise ValueError(f"x must be a bfloat16 tensor on cuda:{self.device}")
+        tdt = out_dtype or torch.bfloat16
+        y = torch.empty((x2.shape[0], self.n // 2), dtype=tdt, device=x2.device)
+        check(lib.mfqb_mul_mat_glu(self._h, x2.data_ptr(), x2.shape[0], y.data_ptr(),
+                                   F32 if tdt == torch.float32 else BF16, _stream_ptr(self.device)))
+        return y
+
     def matmul_swiglu(self, gate_up, out_dtype=None):
         """``(up * silu(gate)) @ W.T`` for a float32 CUDA tensor ``gate_up`` [m, 2k] (gate columns first)."""
         torch = _torch()
