@@ -161,6 +161,69 @@ static void* planes_scratch(int device, size_t bytes, cudaStream_t s) {
 
 static int passes_for(int m) { return m <= 2 ? 1 : (m <= 4 ? 2 : 4); }
 
+// ---- f16 batched kernel (nint_gemvh_bl.cuh) ------------------------------------------------------
+// Needs group sizes that are whole octets (padded group sizes keep the integer kernels) and two ring
+// stages beside the activation buffers.
+static size_t gemvh_smem(const NintDevB& w, int rb_per_cta, int nt) {
+    const int mb = 8 * nt;
+    return codec_ctx_bytes(w) + (size_t)(mb + 1) * rb_per_cta * 16 * 4 + (size_t)8 * 2 * mb * gemvh_row_bytes(w.t8) +
+           (size_t)8 * gemvh_stages(w.rec_words) * w.rec_words * 4;
+}
+bool nint_bl_gemvh_supported(const NintDevB& w, int rows_per_launch) {
+    return w.gs == 8 * w.t8 && gemvh_smem(w, 1, rows_per_launch > 8 ? 2 : 1) <= kGemvSmemLimit;
+}
+// Elements per row of the f16 copy of the activations (whole chunks) and bytes of the copy of `rows` rows plus their scales.
+int nint_bl_x16_stride(const NintDevB& w) { return w.nchunks * kChunkGroupsB * w.gs; }
+size_t nint_bl_x16_bytes(const NintDevB& w, int rows) { return ((size_t)rows * nint_bl_x16_stride(w) * 2 + 255) / 256 * 256 + (size_t)rows * 4; }
+// Scales and converts x [rows, k] into `buf` (nint_bl_x16_bytes): the f16 rows, then the rows' inverse scales.
+void launch_x_rows_f16(const NintDevB& w, const void* x, int rows, bool x_f32, void* buf, const __half** x16, const float** scale, cudaStream_t s) {
+    const int kx = nint_bl_x16_stride(w);
+    __half* out = static_cast<__half*>(buf);
+    float* sc = reinterpret_cast<float*>(static_cast<char*>(buf) + ((size_t)rows * kx * 2 + 255) / 256 * 256);
+    // launched as a programmatic dependent: it becomes resident while the previous kernel drains and waits
+    // for it (the previous product may still read this buffer) before it touches memory
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)rows);
+    cfg.blockDim = dim3(1024);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (x_f32) MFQB_CUDA(cudaLaunchKernelEx(&cfg, x_rows_f16_kernel<float>, static_cast<const float*>(x), w.k, kx, out, sc));
+    else MFQB_CUDA(cudaLaunchKernelEx(&cfg, x_rows_f16_kernel<__nv_bfloat16>, static_cast<const __nv_bfloat16*>(x), w.k, kx, out, sc));
+    *x16 = out;
+    *scale = sc;
+}
+static void* x16_scratch(int device, size_t bytes, cudaStream_t s) {
+    static GrowOnlyScratch pool;
+    return pool.get(device, bytes, s, "mfqb_mul_mat (f16 activation rows)");
+}
+// y[m, n] = x[m, k] * W^T for 5 <= m <= 16 on the f16 batched kernel
+static void launch_bl_gemvh(const NintDevB& w, const void* x, int m, void* y, int y_dtype, int ldy, int device, cudaStream_t s) {
+    GemvArgsB a{};
+    a.w = w;
+    a.y = y;
+    a.m = m;
+    a.ldy = ldy;
+    a.y_dtype = y_dtype;
+    launch_x_rows_f16(w, x, m, false, x16_scratch(device, nint_bl_x16_bytes(w, m), s), &a.x16, &a.x16_scale, s);
+    a.x16_stride = nint_bl_x16_stride(w);
+    const int nt = m > 8 ? 2 : 1, sms = device_sm_count(device);
+    GemvPlanB p;
+    p.passes = nt == 2 ? 116 : 108;
+    // at least two row-blocks per CTA where the matrix allows: a chunk's activations then serve several records
+    // (tall matrices take several waves of CTAs rather than more than eight row-blocks each)
+    const int cap = ctas_per_sm(gemvh_smem(w, 2, nt), 2) * sms;
+    p.grid = std::max(1, std::min(w.nrb >= 2 * sms ? w.nrb / 2 : w.nrb, cap));
+    a.rb_per_cta = std::min(8, (w.nrb + p.grid - 1) / p.grid);
+    p.grid = (w.nrb + a.rb_per_cta - 1) / a.rb_per_cta;
+    p.smem = gemvh_smem(w, a.rb_per_cta, nt);
+    if (p.smem > kGemvSmemLimit) fail(MFQB_ERR_UNSUPPORTED, "batched product: %d row-blocks per CTA do not fit shared memory", a.rb_per_cta);
+    dispatch(a, p, s, "batched GEMV (f16)");
+}
+
 // Largest number of two-row passes (4, 2 or 1) whose plane buffers and record rings fit one CTA.
 int nint_bl_max_passes(const NintDevB& w) {
     for (int p = 4; p > 1; p /= 2)
@@ -201,6 +264,10 @@ void launch_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtyp
         }
     } else {
         if (swiglu || glu) fail(MFQB_ERR_ARG, "the fused activation belongs to the single-row kernel");
+        if (m >= 5 && m <= 16 && nint_bl_gemvh_supported(w, m)) {   // from five rows on the f16 formulation is cheaper
+            launch_bl_gemvh(w, x, m, y, y_dtype, ldy, device, s);
+            return;
+        }
         const int max_rows = 2 * nint_bl_max_passes(w);
         if (m > max_rows) {   // wide records: the batch goes through in several launches
             const size_t ysz = y_dtype == MFQB_F32 ? 4 : 2;

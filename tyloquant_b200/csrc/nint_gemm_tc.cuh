@@ -218,27 +218,41 @@ __global__ void __launch_bounds__(kGemmThreads, 1) nint_gemm_tc_kernel(const Gem
         // ------------------------------ mma issuer ------------------------------
         const uint32_t idesc = instr_desc_f16(128, BN < 256 ? BN : 256);
         const int natoms = w.nchunks * ATOMS;
-        bool ok = true;
-        for (int ai = 0; ai < natoms && ok; ++ai) {
-            const int st = ai % NS;
-            if (!mbar_wait(&full_bar[st], (ai / NS) & 1)) { failed = 1; break; }
-            const uint32_t a_base = smem_u32(tiles + st * stage_bytes);
-            for (int xh = 0; xh < xper; ++xh) {   // the activation stages under this weight atom
-                const int xi = ai * xper + xh, xs = xi % NB;
-                if (!mbar_wait(&xfull_bar[xs], (xi / NB) & 1)) { failed = 1; ok = false; break; }
+        if (XC == 64) {   // one activation stage per weight atom
+            for (int ai = 0; ai < natoms; ++ai) {
+                const int st = ai % NS, xs = ai % NB;
+                if (!mbar_wait(&full_bar[st], (ai / NS) & 1) || !mbar_wait(&xfull_bar[xs], (ai / NB) & 1)) { failed = 1; break; }
                 tc_fence_after_sync();
-                const uint32_t b_base = smem_u32(xtiles + (size_t)xs * xstage_bytes);
-                const int nj = 4 / xper;   // K = 16 slices per activation stage
-                for (int jj = 0; jj < nj; ++jj) {
-                    const int j = xh * nj + jj;
-                    for (int h = 0; h < BN; h += 256) {   // one instruction covers at most 256 token columns
-                        const uint64_t bdesc = XC == 64 ? smem_desc_sw128(b_base + h * 128 + jj * 32) : smem_desc_sw64(b_base + h * 64 + jj * 32);
-                        tc_mma_f16(tmem_d + (uint32_t)h, smem_desc_sw128(a_base + j * 32), bdesc, idesc, ai > 0 || j > 0);
-                    }
-                }
+                const uint32_t a_base = smem_u32(tiles + st * stage_bytes), b_base = smem_u32(xtiles + (size_t)xs * xstage_bytes);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    for (int h = 0; h < BN; h += 256)   // one instruction covers at most 256 token columns
+                        tc_mma_f16(tmem_d + (uint32_t)h, smem_desc_sw128(a_base + j * 32), smem_desc_sw128(b_base + h * 128 + j * 32), idesc,
+                                   ai > 0 || j > 0);
+                tc_commit(&empty_bar[st]);
                 tc_commit(&xempty_bar[xs]);
             }
-            if (ok) tc_commit(&empty_bar[st]);
+        } else {          // two 32-column activation stages (64-byte rows) per weight atom
+            bool ok = true;
+            for (int ai = 0; ai < natoms && ok; ++ai) {
+                const int st = ai % NS;
+                if (!mbar_wait(&full_bar[st], (ai / NS) & 1)) { failed = 1; break; }
+                const uint32_t a_base = smem_u32(tiles + st * stage_bytes);
+#pragma unroll
+                for (int xh = 0; xh < 2; ++xh) {
+                    const int xi = ai * 2 + xh, xs = xi % NB;
+                    if (!mbar_wait(&xfull_bar[xs], (xi / NB) & 1)) { failed = 1; ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t b_base = smem_u32(xtiles + (size_t)xs * xstage_bytes);
+#pragma unroll
+                    for (int jj = 0; jj < 2; ++jj)
+                        for (int h = 0; h < BN; h += 256)
+                            tc_mma_f16(tmem_d + (uint32_t)h, smem_desc_sw128(a_base + (xh * 2 + jj) * 32), smem_desc_sw64(b_base + h * 64 + jj * 32), idesc,
+                                       ai > 0 || xh > 0 || jj > 0);
+                    tc_commit(&xempty_bar[xs]);
+                }
+                if (ok) tc_commit(&empty_bar[st]);
+            }
         }
         tc_commit(&done_bar);
     }

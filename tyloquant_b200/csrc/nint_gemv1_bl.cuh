@@ -71,6 +71,11 @@ struct GemvArgsB {
     // pair_out [pairs, ldy] float32, and the last of a token's `routes` CTAs to arrive adds them with
     // the route weights, in route order, into y_final [tokens, ldy] (moe_weighted_reduce,
     // mfq/kernels/cuda/moe.cu:2957-2977).  token_count: [tokens * gridDim.x] zeros, left zero again.
+    // f16 batched kernel (nint_gemvh_bl.cuh): the activation rows scaled and converted to f16, [rows][x16_stride]
+    // with x16_stride >= nchunks * 8 * gs (zero padded), and the inverse scale of every row.
+    const __half* x16;
+    int x16_stride;
+    const float* x16_scale;
     int x_mode;
     // Single-row kernel, gated FFN: the weight's 16-row blocks alternate (gate rows, up rows); the kernel
     // writes up * silu(gate), n / 2 values, instead of the n products.
@@ -145,6 +150,7 @@ struct NintCodec {
     using BU = ByteUnit<BITS>;
     static constexpr int WC = BU::words_for(8 * T), SW = 2;
     static constexpr bool A_SIGNED = false, HAS_MIN = true, NEEDS_OWN_SCALE = false;
+    static constexpr int QMID = 1 << (BITS - 1);   // centre of the code range (the f16 kernel decodes d * (q - QMID) - (m - d * QMID))
     static constexpr int MIN_CTAS = WC > 48 ? 1 : (WC > 24 ? 2 : 3);
     struct Ctx {
         __device__ __forceinline__ void init(unsigned char*, const NintDevB&, int, int) {}

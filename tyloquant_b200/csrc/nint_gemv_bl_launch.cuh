@@ -2,6 +2,7 @@
 // (nint_gemv_bl_b*.cu) instantiates launch_gemv_bl_bits<BITS> so the widths compile in parallel.
 #pragma once
 #include "nint_gemvn_bl.cuh"
+#include "nint_gemvh_bl.cuh"
 #include "nint_gemvs.cuh"
 
 namespace mfqb {
@@ -10,7 +11,7 @@ struct GemvPlanB {
     int grid = 1, grid_y = 1, threads = 256;
     const GemvMultiTable* multi = nullptr;   // the weights of a multi-weight launch (passes == -1)
     int* occupancy_out = nullptr;            // set: nothing is launched, the kernel's resident CTAs per SM for (threads, smem) are stored here
-    int passes = 0;      // 0: single-row kernel; 1, 2, 4: batched kernel with that many two-row passes; -1: multi-weight single-row launch; -2: single-row kernel on a float32 gate|up row
+    int passes = 0;      // 0: single-row kernel; 1, 2, 4: batched kernel with that many two-row passes; -1: multi-weight single-row launch; -2: single-row kernel on a float32 gate|up row; 108, 116: f16 batched kernel for up to 8 or 16 rows
     size_t smem = 0;
 };
 
@@ -80,6 +81,8 @@ static cudaError_t launch_gemv_codec(const GemvArgsB& a, const GemvPlanB& p, cud
         case 1: return launch_kernel_pdl(gemvn_bl_kernel<C, 1>, a, p, stream);
         case 2: return launch_kernel_pdl(gemvn_bl_kernel<C, 2>, a, p, stream);
         case 4: return launch_kernel_pdl(gemvn_bl_kernel<C, 4>, a, p, stream);
+        case 108: return launch_kernel_pdl(gemvh_bl_kernel<C, 1>, a, p, stream);
+        case 116: return launch_kernel_pdl(gemvh_bl_kernel<C, 2>, a, p, stream);
         default: return cudaErrorInvalidValue;
     }
 }

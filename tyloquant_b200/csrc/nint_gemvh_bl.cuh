@@ -1,0 +1,299 @@
+// Batched GEMV (5 to 16 activation rows per launch) with the weights dequantised to f16 in registers.
+//
+// The integer kernels put the eight groups of a chunk (single row) or two batch rows x four groups
+// (batched) into the n8 slot of the int8 mma, because group scales have to be applied to integer
+// sums.  From eight batch rows on it pays to apply the scales to the weights instead: a lane turns
+// each of its byte-lane registers (four codes of one weight row and group) into two f16x2
+// registers w = d * q - m, which ARE the A fragment of mma.m16n8k16 (f16 x f16 -> f32), and the
+// eight columns carry eight batch rows.  One byte-lane step (f, t) -- rows q, q+8 x groups
+// 4f + (c>>1), 4f + 2 + (c>>1) x slots 8t + 4(c&1) + {0..3} -- is two such mma per eight batch
+// rows (codes 0,1 are the fragment's k = 2c, 2c+1, codes 2,3 its k = 2c+8, 2c+9; the k order of
+// an mma is free as long as B follows it), 4T mma per record instead of 4T per two rows, and the
+// accumulators are final values: no per-group scaling afterwards.
+//
+// Activations: every row is scaled by a power of two so that its largest magnitude lands near 2^14
+// and converted to f16 once per call (x_rows_f16_kernel; exact for a bf16 input within 2^-28 of
+// the row's largest magnitude), the inverse factor is applied to the finished sums.  A warp owns
+// whole chunks of K and, with the first record of a chunk, requests that chunk's slice of all
+// batch rows into one of its two private buffers (same asynchronous copy group), as in the integer
+// batched kernel.  Weights are rounded to f16 once (d and m rounded to f16, one fused multiply-add):
+// about 3e-4 relative L2 on the product, inside the path's 1e-3 bound.
+//
+// Tile mode (expert matmul with a route plan): blockIdx.y is a tile of up to 8 NT (token, route)
+// pairs of one expert; x rows are taken through pair_order and results scatter back to pair order.
+#pragma once
+#include <cuda_fp16.h>
+
+#include "nint_gemv1_bl.cuh"
+
+namespace mfqb {
+
+// x [rows, k] (bf16 or float32) -> out [rows, kx] f16, each row times 2^e with e chosen from the row's
+// largest magnitude (kx >= k, zero padded); row_scale[row] = 2^-e.  One CTA of 1024 threads per row.
+template <typename XT>
+__global__ void __launch_bounds__(1024) x_rows_f16_kernel(const XT* __restrict__ x, int k, int kx, __half* __restrict__ out,
+                                                          float* __restrict__ row_scale) {
+    __shared__ uint32_t red[32];
+    pdl_wait_b();
+    pdl_launch_dependents_b();
+    const XT* row = x + (size_t)blockIdx.x * k;
+    uint32_t ab = 0u;   // largest magnitude as float bits (orders like the value; NaN and infinity are largest)
+    for (int i = threadIdx.x; i < k; i += blockDim.x) ab = max(ab, __float_as_uint(fabsf((float)row[i])));
+    for (int o = 16; o > 0; o >>= 1) ab = max(ab, __shfl_xor_sync(0xffffffffu, ab, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ab;
+    __syncthreads();
+    ab = red[threadIdx.x & 31];
+    for (int o = 16; o > 0; o >>= 1) ab = max(ab, __shfl_xor_sync(0xffffffffu, ab, o));
+    // 2^e * max in [2^14, 2^15); a zero, subnormal or non-finite row keeps e = 0
+    const int eb = (int)(ab >> 23);
+    const bool plain = eb == 0 || eb == 255;
+    const float up = plain ? 1.f : __uint_as_float((uint32_t)(127 + 14 - (eb - 127)) << 23);     // 2^(14 - floor(log2 max))
+    const float down = plain ? 1.f : __uint_as_float((uint32_t)(127 - 14 + (eb - 127)) << 23);   // its inverse
+    if (threadIdx.x == 0) row_scale[blockIdx.x] = down;
+    __half* orow = out + (size_t)blockIdx.x * kx;
+    for (int i = threadIdx.x; i < kx; i += blockDim.x) {
+        const float v = i < k ? (float)row[i] : 0.f;
+        orow[i] = isfinite(v) ? __float2half_rn(v * up) : __ushort_as_half((unsigned short)0x7E00);   // non-finite input -> NaN
+    }
+}
+
+// Padding of a row of the per-warp activation buffers (bytes) so that the sixteen 8-byte reads of a
+// half-warp -- rows q = 0..3 (or 4..7) x offsets {0, 8, 16T, 16T + 8} -- fall into distinct banks.
+__host__ __device__ constexpr int gemvh_row_pad(int t8) {
+    for (int pad = 0; pad < 128; pad += 16) {
+        bool ok = true;
+        unsigned seen = 0u;   // 16 slots of 8 bytes in a 128-byte bank line
+        for (int q = 0; q < 4 && ok; ++q)
+            for (int j = 0; j < 4 && ok; ++j) {
+                const int off = (q * pad + (j >> 1) * 16 * t8 + (j & 1) * 8) % 128 / 8;
+                if (seen & (1u << off)) ok = false;
+                seen |= 1u << off;
+            }
+        if (ok) return pad;
+    }
+    return 16;
+}
+__host__ __device__ constexpr int gemvh_row_bytes(int t8) { return kChunkGroupsB * 8 * t8 * 2 + gemvh_row_pad(t8); }
+__host__ __device__ constexpr int gemvh_stages(int rec_words) { return gemv1_bl_stages(rec_words) > 4 ? 4 : gemv1_bl_stages(rec_words); }
+
+// The dequantised weights carry a factor 2^10 (taken out of the finished sums): f16 then keeps all its
+// bits for quantisation steps down to 2^-24 and represents weights up to 64.
+constexpr float kGemvhWeightScale = 1024.f, kGemvhWeightUndo = 1.f / 1024.f;
+
+__device__ __forceinline__ void hmma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Four codes of a byte-lane register -> two f16x2 registers of d * (q - QMID) + nm, codes (0,1) and (2,3).
+// A byte b becomes the f16 1024 + b by placing it under the exponent byte 0x64 (signed codes are
+// biased by 128 first); subtracting 1024 + QMID is exact.  Centring the codes keeps d * (q - QMID)
+// and nm = -(m - d * QMID) of the size of the weight itself, so the f16 roundings are relative to
+// the weight and not to the (larger) offset of an asymmetric code range.
+template <bool SIGNED, bool HAS_MIN, int QMID>
+__device__ __forceinline__ void codes_to_f16(uint32_t v, __half2 d, __half2 nm, uint32_t& w01, uint32_t& w23) {
+    if (SIGNED) v ^= 0x80808080u;
+    const uint32_t lo = __byte_perm(v, 0x64646464u, 0x4140), hi = __byte_perm(v, 0x64646464u, 0x4342);
+    const __half2 bias = __float2half2_rn((SIGNED ? 1152.f : 1024.f) + (float)QMID);
+    const __half2 q01 = __hsub2(*reinterpret_cast<const __half2*>(&lo), bias), q23 = __hsub2(*reinterpret_cast<const __half2*>(&hi), bias);
+    const __half2 r01 = HAS_MIN ? __hfma2(q01, d, nm) : __hmul2(q01, d), r23 = HAS_MIN ? __hfma2(q23, d, nm) : __hmul2(q23, d);
+    w01 = *reinterpret_cast<const uint32_t*>(&r01);
+    w23 = *reinterpret_cast<const uint32_t*>(&r23);
+}
+
+// Shared memory: partial sums [8 NT][rb_per_cta * 16] f32 | anchors [rb_per_cta * 16] | per warp two
+// activation buffers [8 NT rows][row bytes] | per warp a ring of S records.
+template <class C, int NT>
+__device__ __forceinline__ void gemvh_bl_body(const GemvArgsB& a, const NintDevB& w, unsigned char* smem) {
+    constexpr int G = kChunkGroupsB, MB = 8 * NT, T = C::T, WC = C::WC, SW = C::SW, REC = (WC + SW) * 32;
+    constexpr int S = gemvh_stages(REC), RS = gemvh_row_bytes(T), CHUNK_BYTES = G * 8 * T * 2, PIECES = CHUNK_BYTES / 16;
+
+    __shared__ int row_src[MB], row_dst[MB];
+    __shared__ float row_undo[MB];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    const int q = lane >> 2, c = lane & 3;
+    const int ystride = a.rb_per_cta * 16;
+    typename C::Ctx ctx;
+    ctx.init(smem, w, tid, blockDim.x);   // constant tables: visible after the first __syncthreads
+    float* ypart = reinterpret_cast<float*>(smem + C::ctx_bytes(w));                // [MB][rb_per_cta * 16]
+    uint32_t* anch = reinterpret_cast<uint32_t*>(ypart + (size_t)MB * ystride);     // [rb_per_cta * 16]
+    unsigned char* xb_all = reinterpret_cast<unsigned char*>(anch + ystride);       // [warp][2 buffers][MB rows][RS]
+    unsigned char* xb = xb_all + (size_t)warp * 2 * MB * RS;
+    uint32_t* ring = reinterpret_cast<uint32_t*>(xb_all + (size_t)nwarps * 2 * MB * RS) + (size_t)warp * S * REC;
+
+    int m_cur = a.m, rb0, nrb, rbl0 = 0, row_limit = w.n;
+    pdl_wait_b();   // the f16 rows (and, in tile mode, the route plan) come from the previous kernels
+    if (a.tile_bounds != nullptr) {
+        const int t = blockIdx.y;
+        if (t >= a.tile_bounds[a.n_experts]) return;
+        int lo = 0, hi = a.n_experts - 1;   // expert e with tile_bounds[e] <= t < tile_bounds[e + 1]
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (a.tile_bounds[mid] <= t) lo = mid;
+            else hi = mid - 1;
+        }
+        const int e = lo;
+        if (a.expert_pool[e] != a.pool) return;
+        const int p0 = a.expert_bounds[e] + (t - a.tile_bounds[e]) * MB;
+        m_cur = min(MB, a.expert_bounds[e + 1] - p0);
+        if (tid < MB) {
+            const int pair = tid < m_cur ? a.pair_order[p0 + tid] : 0;
+            row_src[tid] = a.x_per_pair ? pair : pair / a.routes;
+            row_dst[tid] = pair;
+        }
+        split_row_blocks(blockIdx.x, gridDim.x, a.rb_per_expert, rbl0, nrb);
+        rb0 = a.expert_local[e] * a.rb_per_expert + rbl0;
+        row_limit = a.ldy;
+    } else {
+        if (tid < MB) row_src[tid] = row_dst[tid] = tid;
+        split_row_blocks(blockIdx.x, gridDim.x, w.nrb, rbl0, nrb);
+        rb0 = rbl0;
+    }
+    pdl_launch_dependents_b();
+    for (int i = tid; i < MB * ystride; i += blockDim.x) ypart[i] = 0.f;
+    for (int i = tid; i < nrb * 16; i += blockDim.x) anch[i] = __ldg(w.anchors + rb0 * 16 + i);
+    // rows past the batch are never copied: their buffers stay zero and contribute nothing
+    for (int i = tid; i < nwarps * 2 * MB * RS / 16; i += blockDim.x) reinterpret_cast<uint4*>(xb_all)[i] = make_uint4(0u, 0u, 0u, 0u);
+    __syncthreads();   // row_src / row_dst, zeroed buffers
+    if (tid < MB) row_undo[tid] = tid < m_cur ? a.x16_scale[row_src[tid]] * kGemvhWeightUndo : 0.f;
+
+    // items of this warp, chunk-major: chunk = warp, warp + nwarps, ...; inside a chunk every
+    // row-block of the CTA.  The issue cursor runs `ahead` <= min(S, nrb) items in front, so the
+    // items in flight touch at most two chunks: the two activation buffers alternate by chunk.
+    const int my_segs = warp < w.nchunks ? (w.nchunks - warp + nwarps - 1) / nwarps : 0;
+    const int n_mine = my_segs * nrb, ahead = min(S, nrb);
+    int iss_i = 0, iss_seg = warp, iss_rbl = 0, iss_stage = 0, iss_buf = 0;
+    auto issue = [&]() {
+        if (iss_i < n_mine) {
+            const uint32_t* src = w.items + ((size_t)(rb0 + iss_rbl) * w.nchunks + iss_seg) * REC;
+            uint32_t* dst = ring + iss_stage * REC;
+#pragma unroll
+            for (int off = 0; off < REC; off += 128)
+                if (off + 128 <= REC || lane * 4 < REC - off) cp_async16_b(dst + off + lane * 4, src + off + lane * 4);
+            if (iss_rbl == 0) {   // first item of a chunk: its activations travel in the same group
+                unsigned char* pb = xb + (size_t)iss_buf * MB * RS;
+                for (int idx = lane; idx < m_cur * PIECES; idx += 32) {
+                    const int m = idx / PIECES, piece = idx % PIECES;
+                    const unsigned char* gsrc = reinterpret_cast<const unsigned char*>(a.x16 + (size_t)row_src[m] * a.x16_stride) +
+                                                (size_t)iss_seg * CHUNK_BYTES + piece * 16;
+                    cp_async16_b(pb + m * RS + piece * 16, gsrc);
+                }
+                iss_buf ^= 1;
+            }
+        }
+        cp_async_commit_b();   // one group per item slot, empty past the end: keeps the wait count uniform
+        ++iss_i;
+        if (++iss_rbl == nrb) { iss_rbl = 0; iss_seg += nwarps; }
+        if (++iss_stage == S) iss_stage = 0;
+    };
+    for (int i = 0; i < ahead; ++i) issue();
+
+    int rbl = 0, stage = 0, buf = 0;
+    for (int i = 0; i < n_mine; ++i) {
+        // the groups newer than this item's are the ahead - 1 items issued after it
+        switch (ahead) {
+            case 1: asm volatile("cp.async.wait_group 0;\n" ::: "memory"); break;
+            case 2: asm volatile("cp.async.wait_group 1;\n" ::: "memory"); break;
+            case 3: asm volatile("cp.async.wait_group 2;\n" ::: "memory"); break;
+            default: asm volatile("cp.async.wait_group 3;\n" ::: "memory"); break;
+        }
+        __syncwarp();
+        const uint32_t* rec = ring + stage * REC;
+        const unsigned char* pb = xb + (size_t)buf * MB * RS;
+        uint32_t qw[WC];
+#pragma unroll
+        for (int j = 0; j < WC; ++j) qw[j] = rec[j * 32 + lane];
+        // scale words of the lanes that own (rows q, q+8) x groups 4f + 2h + {0, 1}; this lane's own
+        uint32_t sc[2][2][SW], own[SW];
+#pragma unroll
+        for (int f = 0; f < 2; ++f)
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int j = 0; j < SW; ++j) sc[f][h][j] = rec[(WC + j) * 32 + 4 * q + 2 * f + h];
+#pragma unroll
+        for (int j = 0; j < SW; ++j) own[j] = C::NEEDS_OWN_SCALE ? rec[(WC + j) * 32 + lane] : 0u;
+        __syncwarp();          // every lane has read the stage before it is refilled
+        issue();               // item i + ahead: never into the activation buffer this item reads (see above)
+
+        const uint32_t an_lo = anch[rbl * 16 + q], an_hi = anch[rbl * 16 + q + 8];
+        const float2 f_lo = __half22float2(*reinterpret_cast<const __half2*>(&an_lo));   // (ns, nm)
+        const float2 f_hi = __half22float2(*reinterpret_cast<const __half2*>(&an_hi));
+        float acc[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+        const bool odd = (c >> 1) != 0;   // this lane's group of a pair: 4f + 2h + (c>>1)
+#pragma unroll
+        for (int f = 0; f < 2; ++f) {
+            // (d, -m) of rows q and q+8 for the two groups this lane decodes in family f
+            __half2 d_lo[2], d_hi[2], nm_lo[2], nm_hi[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                float ss[4], sm[4];
+                C::scales(sc[f][h], ctx, ss, sm);
+                const float dl = kGemvhWeightScale * f_lo.x * (odd ? ss[1] : ss[0]), dh = kGemvhWeightScale * f_hi.x * (odd ? ss[3] : ss[2]);
+                d_lo[h] = __float2half2_rn(dl);
+                d_hi[h] = __float2half2_rn(dh);
+                if constexpr (C::HAS_MIN) {
+                    nm_lo[h] = __float2half2_rn(fmaf(dl, (float)C::QMID, -kGemvhWeightScale * f_lo.y * (odd ? sm[1] : sm[0])));
+                    nm_hi[h] = __float2half2_rn(fmaf(dh, (float)C::QMID, -kGemvhWeightScale * f_hi.y * (odd ? sm[3] : sm[2])));
+                } else {
+                    nm_lo[h] = nm_hi[h] = __float2half2_rn(0.f);
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < T; ++t) {
+                const int r = (f * T + t) * 4;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    // registers r + 2h (row q) and r + 2h + 1 (row q + 8): group 4f + 2h + (c>>1), slots 8t + 4(c&1) + {0..3}
+                    uint32_t a0, a1, a2, a3;
+                    codes_to_f16<C::A_SIGNED, C::HAS_MIN, C::QMID>(C::areg(qw, r + 2 * h, ctx, own), d_lo[h], nm_lo[h], a0, a2);
+                    codes_to_f16<C::A_SIGNED, C::HAS_MIN, C::QMID>(C::areg(qw, r + 2 * h + 1, ctx, own), d_hi[h], nm_hi[h], a1, a3);
+                    const int xoff = ((4 * f + 2 * h + (c >> 1)) * 8 * T + 8 * t + 4 * (c & 1)) * 2;
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        const uint2 b = *reinterpret_cast<const uint2*>(pb + (8 * nt + q) * RS + xoff);
+                        hmma_16816(acc[nt], a0, a1, a2, a3, b.x, b.y);
+                    }
+                }
+            }
+        }
+        // acc[nt]: rows q (0, 1) and q+8 (2, 3) x batch rows 8 nt + 2c + {0, 1}
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const int m0 = 8 * nt + 2 * c;
+            if (m0 < m_cur) {
+                atomicAdd(ypart + (size_t)m0 * ystride + rbl * 16 + q, acc[nt][0]);
+                atomicAdd(ypart + (size_t)m0 * ystride + rbl * 16 + q + 8, acc[nt][2]);
+            }
+            if (m0 + 1 < m_cur) {
+                atomicAdd(ypart + (size_t)(m0 + 1) * ystride + rbl * 16 + q, acc[nt][1]);
+                atomicAdd(ypart + (size_t)(m0 + 1) * ystride + rbl * 16 + q + 8, acc[nt][3]);
+            }
+        }
+        if (++rbl == nrb) { rbl = 0; buf ^= 1; }
+        if (++stage == S) stage = 0;
+    }
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();
+    for (int i = tid; i < m_cur * nrb * 16; i += blockDim.x) {
+        const int m = i / (nrb * 16), j = i % (nrb * 16);
+        const int row = rbl0 * 16 + j;   // row inside the problem (matrix, or the tile's expert)
+        if (row < row_limit) {
+            const float v = ypart[(size_t)m * ystride + j] * row_undo[m];
+            const size_t off = (size_t)row_dst[m] * a.ldy + row;
+            if (a.y_dtype == 0 /* MFQB_F32 */) reinterpret_cast<float*>(a.y)[off] = v;
+            else reinterpret_cast<__nv_bfloat16*>(a.y)[off] = __float2bfloat16_rn(v);
+        }
+    }
+}
+
+template <class C, int NT>
+__global__ void __launch_bounds__(256, C::MIN_CTAS < 2 ? 1 : 2) gemvh_bl_kernel(const GemvArgsB a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    gemvh_bl_body<C, NT>(a, a.w, smem);
+}
+
+}  // namespace mfqb

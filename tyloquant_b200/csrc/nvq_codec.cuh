@@ -8,6 +8,7 @@ template <int IB, bool JSC>
 struct NvqCodec {
     static constexpr int T = 3, FB = IB + 4, WC = (24 * FB + 31) / 32, SW = 1;
     static constexpr bool A_SIGNED = true, HAS_MIN = false, NEEDS_OWN_SCALE = JSC;
+    static constexpr int QMID = 0;   // lattice codes are signed around zero
     static constexpr int MIN_CTAS = IB == 8 ? 3 : 2;
     static constexpr uint32_t OFFMASK = ((1u << FB) - 1u) << 2;   // a field as a byte offset into the signed table
 

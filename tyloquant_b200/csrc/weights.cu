@@ -237,6 +237,7 @@ void launch_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtyp
 bool nint_bl_supported(int bits, int gs);
 size_t gemvs_fix_bytes(int device);
 void launch_swiglu(const void* gate_up, int in_dtype, int rows, int f, void* hidden, cudaStream_t s);
+bool nint_bl_gemvh_supported(const NintDevB& w, int rows_per_launch);
 void launch_bl_gemv_multi(const NintDevB* ws, void* const* ys, int count, const void* x, int y_dtype, int device, cudaStream_t s);
 bool launch_bl_gemvs(const NintDevB& w, const void* x, int x_dtype, void* y, int y_dtype, int device, void* fix, int* error, cudaStream_t s);
 }
@@ -414,8 +415,9 @@ int mfqb_mul_mat(const mfqb_weight* w, const void* x, int m, void* y, int y_dtyp
             if (m == 1 && gemv1_use_streamed(w->nint) &&
                 launch_bl_gemvs(w->nint, x, MFQB_BF16, y, y_dtype, w->device, w->fix.p, w->status, stream))
                 return;
-            for (int m0 = 0; m0 < m; m0 += 8) {   // batch rows one GEMV launch covers
-                const int mm = std::min(8, m - m0);
+            const int per_launch = nint_bl_gemvh_supported(w->nint, 16) ? 16 : 8;   // batch rows one GEMV launch covers
+            for (int m0 = 0; m0 < m; m0 += per_launch) {
+                const int mm = std::min(per_launch, m - m0);
                 launch_bl_gemv(w->nint, static_cast<const char*>(x) + (size_t)m0 * k * 2, mm,
                                     static_cast<char*>(y) + (size_t)m0 * n * ysz, y_dtype, (int)n, w->device, stream);
             }
@@ -487,6 +489,19 @@ __global__ void host_to_device_words_kernel(const uint32_t* __restrict__ src, ui
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < words; i += (size_t)gridDim.x * blockDim.x) dst[i] = src[i];
 }
 
+// The same for up to 32 buffers in one launch (blockIdx.y picks the buffer): one trip over PCIe for all of them.
+struct HostGatherTable {
+    const uint32_t* src[32];
+    uint32_t* dst[32];
+    unsigned words[32];
+};
+__global__ void host_gather_words_kernel(const __grid_constant__ HostGatherTable t) {
+    const uint32_t* src = t.src[blockIdx.y];
+    uint32_t* dst = t.dst[blockIdx.y];
+    const unsigned words = t.words[blockIdx.y];
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < words; i += gridDim.x * blockDim.x) dst[i] = src[i];
+}
+
 // Device staging of the host-buffer entry point: per device one stream and two buffers that grow on
 // demand and are then reused, so a call costs two copies, the kernel and one synchronisation.
 namespace {
@@ -529,30 +544,50 @@ static void mul_mat_host_impl(const mfqb_weight* const* ws, int count, const voi
     // product kernel writes y straight into host memory -- no copy-engine round trips.  Pageable
     // buffers take the two cudaMemcpyAsync.
     std::vector<std::pair<size_t, int>> copy_back;   // (offset in dy, index)
+    // First every activation buffer is staged (the mapped ones 32 per launch), then the products run
+    // back to back: consecutive product kernels overlap through programmatic dependent launch, which
+    // a staging kernel between them would break.
+    std::vector<char*> xd(count);
+    std::vector<void*> yd(count);
+    HostGatherTable table{};
+    int pending = 0;
+    unsigned max_words = 0;
+    auto flush = [&]() {
+        if (!pending) return;
+        const dim3 grid(std::max(1u, std::min((max_words + 255) / 256, 16u)), (unsigned)pending);
+        host_gather_words_kernel<<<grid, 256, 0, s>>>(table);
+        MFQB_CUDA(cudaGetLastError());
+        pending = 0;
+        max_words = 0;
+    };
     for (int i = 0; i < count; ++i) {
         const size_t xb = (size_t)m * ws[i]->info.k * 2, yb = (size_t)m * ws[i]->info.n * ysz;
         void *x_map = nullptr, *y_map = nullptr;
-        const bool mapped = (xb % 4 == 0) && (reinterpret_cast<uintptr_t>(xs[i]) % 4 == 0) &&
+        const bool mapped = (xb % 4 == 0) && xb / 4 <= 0xFFFFFFFFull && (reinterpret_cast<uintptr_t>(xs[i]) % 4 == 0) &&
                             cudaHostGetDevicePointer(&x_map, const_cast<void*>(xs[i]), 0) == cudaSuccess &&
                             cudaHostGetDevicePointer(&y_map, ys[i], 0) == cudaSuccess;
         if (!mapped) (void)cudaGetLastError();   // not an error: the buffers are simply pageable
-        char* xd = static_cast<char*>(dx.p) + x_off;
+        xd[i] = static_cast<char*>(dx.p) + x_off;
         if (mapped) {
-            const size_t words = xb / 4;
-            host_to_device_words_kernel<<<(unsigned)std::min<size_t>((words + 255) / 256, 64), 256, 0, s>>>(
-                static_cast<const uint32_t*>(x_map), reinterpret_cast<uint32_t*>(xd), words);
-            MFQB_CUDA(cudaGetLastError());
+            table.src[pending] = static_cast<const uint32_t*>(x_map);
+            table.dst[pending] = reinterpret_cast<uint32_t*>(xd[i]);
+            table.words[pending] = (unsigned)(xb / 4);
+            max_words = std::max(max_words, (unsigned)(xb / 4));
+            if (++pending == 32) flush();
         } else {
-            MFQB_CUDA(cudaMemcpyAsync(xd, xs[i], xb, cudaMemcpyHostToDevice, s));
+            MFQB_CUDA(cudaMemcpyAsync(xd[i], xs[i], xb, cudaMemcpyHostToDevice, s));
             if (!any_copy_back && dy.bytes < y_total) dy.alloc(y_total + y_total / 2);
             any_copy_back = true;
             copy_back.emplace_back(y_off, i);
         }
-        void* yd = mapped ? y_map : static_cast<void*>(static_cast<char*>(dy.p) + y_off);
-        const int rc = mfqb_mul_mat(ws[i], xd, m, yd, y_dtype, s);
-        if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
+        yd[i] = mapped ? y_map : static_cast<void*>(static_cast<char*>(dy.p) + y_off);
         x_off += (xb + 255) / 256 * 256;
         y_off += (yb + 255) / 256 * 256;
+    }
+    flush();
+    for (int i = 0; i < count; ++i) {
+        const int rc = mfqb_mul_mat(ws[i], xd[i], m, yd[i], y_dtype, s);
+        if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
     }
     for (const auto& cb : copy_back)
         MFQB_CUDA(cudaMemcpyAsync(ys[cb.second], static_cast<char*>(dy.p) + cb.first, (size_t)m * ws[cb.second]->info.n * ysz,
