@@ -48,6 +48,11 @@ void launch_x_gather_f16(const void* x, bool x_f32, const int* pair_order, int d
 void launch_nint_gemm_grouped(const NintDevB& w, const void* x16, int pairs, int bn, const int* expert_bounds, const int* tile_bounds,
                               const int* pair_order, const int* expert_pool, const int* expert_local, int n_experts, int pool,
                               int rb_per_expert, int rows_per_expert, int max_tiles, void* y, int y_dtype, int device, cudaStream_t s);
+bool moe_hetero_tilesh_supported(const NintDevB* pools, const int* held, int npools);
+bool launch_moe_hetero_tilesh(GemvArgsB base, const NintDevB* pools, const int* held, int npools, int tile_m, int max_tiles, int device, cudaStream_t s);
+int nint_bl_x16_stride(const NintDevB& w);
+size_t x16_rows_bytes(int rows, int kx);
+void launch_x_rows_f16_stride(const void* x, int rows, int k, int kx, bool x_f32, void* buf, const __half** x16, const float** scale, cudaStream_t s);
 bool launch_moe_hetero_tiles(GemvArgsB base, const NintDevB* pools, const int* held, const uint2* const* xq, const float2* const* gtab,
                              int npools, int tile_m, int max_tiles, int device, cudaStream_t s);
 bool launch_moe_hetero_gemv1(GemvArgsB base, const NintDevB* pools, const int* held, int npools, int pairs, int device, cudaStream_t s);
@@ -216,12 +221,34 @@ int mfqb_moe_dequant_expert(const mfqb_moe_weight* w, int expert, void* out, int
 
 // Pairs per route-plan tile (2, 4 or 8, by the average number of pairs an expert sees), or
 // 0: fewer pairs than experts, every pair runs as a single-row problem of its own.
+// True when the f16 tile kernel can serve every held cohort of this record.
+static bool moe_f16_tiles_ok(const mfqb_moe_weight* w) {
+    NintDevB devs[16];
+    int held[16];
+    if (w->pools.size() > 16) return false;
+    for (size_t pi = 0; pi < w->pools.size(); ++pi) {
+        devs[pi] = w->pools[pi]->d;
+        held[pi] = w->pools[pi]->held;
+    }
+    return moe_hetero_tilesh_supported(devs, held, (int)w->pools.size());
+}
+// Row stride (elements) of the f16 copy of the input rows that serves every held cohort.
+static int moe_x16_stride(const mfqb_moe_weight* w) {
+    int kx = 0;
+    for (const auto& pool : w->pools)
+        if (pool->held) kx = std::max(kx, nint_bl_x16_stride(pool->d));
+    return kx;
+}
+
 static int moe_tile_m(const mfqb_moe_weight* w, int pairs) {
     const int e = w->info.n_experts;
     if (pairs < e) return 0;
     int cap = 8;   // cohorts with wide records fit fewer batch rows per CTA
     for (const auto& pool : w->pools)
         if (pool->held) cap = std::min(cap, 2 * nint_bl_max_passes(pool->d));
+    // from about three pairs per expert the f16 tile kernel (tiles of 8, then 16 pairs: an expert's weights are
+    // decoded once per tile) is cheaper than the integer passes over tiles of 2 or 4
+    if (pairs >= 3 * e && moe_f16_tiles_ok(w)) return pairs >= 10 * e ? 16 : 8;
     // measured on the 128-expert top-8 layer: tiles of four win from two to about twenty pairs per expert
     return std::min(cap, 2 * pairs <= 3 * e ? 2 : (pairs <= 24 * e ? 4 : 8));
 }
@@ -243,6 +270,7 @@ static int moe_gemm_bn(const mfqb_moe_weight* w, int pairs) {
 // Bytes of quantised activation planes the tile path needs for `rows` input rows: one set per
 // distinct group size among the held cohorts (cohorts of equal group size share theirs).
 static size_t moe_planes_bytes(const mfqb_moe_weight* w, int rows) {
+    const size_t f16_rows = (x16_rows_bytes(rows, moe_x16_stride(w)) + 255) / 256 * 256;   // the f16 tile kernel's input rows share the space
     size_t total = 0;
     for (size_t pi = 0; pi < w->pools.size(); ++pi) {
         if (!w->pools[pi]->held) continue;
@@ -250,7 +278,7 @@ static size_t moe_planes_bytes(const mfqb_moe_weight* w, int rows) {
         for (size_t pj = 0; pj < pi; ++pj) seen = seen || (w->pools[pj]->held && w->pools[pj]->d.gs == w->pools[pi]->d.gs);
         if (!seen) total += (nint_bl_planes_bytes(w->pools[pi]->d, rows) + 255) / 256 * 256;
     }
-    return total;
+    return std::max(total, f16_rows);
 }
 
 // plan == nullptr: one single-row problem per pair.  Otherwise the batched kernel runs over the
@@ -328,6 +356,33 @@ static void mul_mat_id_impl(const mfqb_moe_weight* w, const void* x, int x_per_p
                                      w->info.n_experts, (int)pi, w->padded / 16, ope, tiles, out, out_dtype, w->info.device, stream);
         }
         return;
+    }
+    if (plan && (tile_m == 8 || tile_m == 16) && moe_f16_tiles_ok(w)) {   // f16 tile kernel, all cohorts in one launch
+        const int max_tiles_h = pairs / tile_m + std::min(pairs, w->info.n_experts);
+        if (max_tiles_h > 65535) fail(MFQB_ERR_ARG, "mfqb_mul_mat_id: too many route tiles (%d)", max_tiles_h);
+        GemvArgsB a{};
+        a.y = out;
+        a.ldy = ope;
+        a.y_dtype = out_dtype;
+        a.expert_pool = static_cast<const int*>(w->d_expert_pool.p);
+        a.expert_local = static_cast<const int*>(w->d_expert_local.p);
+        a.rb_per_expert = w->padded / 16;
+        a.routes = routes;
+        a.x_per_pair = x_per_pair ? 1 : 0;
+        a.expert_bounds = plan->expert_bounds;
+        a.tile_bounds = plan->tile_bounds;
+        a.pair_order = plan->pair_order;
+        a.n_experts = w->info.n_experts;
+        a.x16_stride = moe_x16_stride(w);
+        launch_x_rows_f16_stride(x, in_rows, w->info.k, a.x16_stride, x_mode == 1, planes, &a.x16, &a.x16_scale, stream);
+        NintDevB devs[16];
+        int held[16];
+        for (size_t pi = 0; pi < w->pools.size(); ++pi) {
+            devs[pi] = w->pools[pi]->d;
+            held[pi] = w->pools[pi]->held;
+        }
+        if (launch_moe_hetero_tilesh(a, devs, held, (int)w->pools.size(), tile_m, max_tiles_h, w->info.device, stream)) return;
+        fail(MFQB_ERR_UNSUPPORTED, "mul_mat_id: tiles of %d pairs do not fit the f16 tile kernel for this record", tile_m);
     }
     // quantised planes of the input rows, one set per distinct group size among the held cohorts
     const uint2* pool_xq[16] = {nullptr};

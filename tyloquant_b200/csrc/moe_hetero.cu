@@ -153,6 +153,90 @@ bool launch_moe_hetero_tiles(GemvArgsB base, const NintDevB* pools, const int* h
     return true;
 }
 
+// The same over the f16 batched kernel: tiles of 8 (NT = 1) or 16 (NT = 2) pairs, the input rows as scaled f16
+// (base.x16, base.x16_stride, base.x16_scale).
+template <int NT>
+__global__ void __launch_bounds__(256, 2) moe_hetero_tilesh_kernel(const __grid_constant__ HeteroArgs h) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    pdl_wait_b();   // route plan and f16 rows come from the previous kernels
+    const int t = blockIdx.y, n_experts = h.base.n_experts;
+    if (t >= h.base.tile_bounds[n_experts]) return;
+    int lo = 0, hi = n_experts - 1;   // expert e with tile_bounds[e] <= t < tile_bounds[e + 1]
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (h.base.tile_bounds[mid] <= t) lo = mid;
+        else hi = mid - 1;
+    }
+    const int pool = h.base.expert_pool[lo];
+    if (pool < 0) return;
+    GemvArgsB a = h.base;
+    a.pool = pool;
+    const NintDevB& w = h.pools[pool];
+    switch (w.bits * 16 + w.t8) {
+        case 2 * 16 + 2: gemvh_bl_body<NintCodec<2, 2>, NT>(a, w, smem); break;
+        case 3 * 16 + 3: gemvh_bl_body<NintCodec<3, 3>, NT>(a, w, smem); break;
+        case 4 * 16 + 3: gemvh_bl_body<NintCodec<4, 3>, NT>(a, w, smem); break;
+        case 5 * 16 + 4: gemvh_bl_body<NintCodec<5, 4>, NT>(a, w, smem); break;
+        case 6 * 16 + 3: gemvh_bl_body<NintCodec<6, 3>, NT>(a, w, smem); break;
+        case 8 * 16 + 3: gemvh_bl_body<NintCodec<8, 3>, NT>(a, w, smem); break;
+        case 8 * 16 + 6: gemvh_bl_body<NintCodec<8, 6>, NT>(a, w, smem); break;
+        default: break;
+    }
+}
+
+// True when every held cohort can run on the f16 tile kernel (a codec here, group size in whole octets).
+bool moe_hetero_tilesh_supported(const NintDevB* pools, const int* held, int npools) {
+    if (!moe_hetero_supported(pools, held, npools)) return false;
+    for (int i = 0; i < npools; ++i)
+        if (held[i] && pools[i].gs != 8 * pools[i].t8) return false;
+    return true;
+}
+
+// Launches the f16 tile-mode matmul for all cohorts at once (tile_m = 8 or 16 pairs per tile).
+bool launch_moe_hetero_tilesh(GemvArgsB base, const NintDevB* pools, const int* held, int npools, int tile_m, int max_tiles, int device, cudaStream_t s) {
+    if ((tile_m != 8 && tile_m != 16) || !moe_hetero_tilesh_supported(pools, held, npools)) return false;
+    HeteroArgs h{};
+    for (int i = 0; i < npools; ++i)
+        if (held[i]) h.pools[i] = pools[i];
+    base.m = tile_m;
+    // most tiles of a launch sized by the upper bound are empty: split an expert's rows finely
+    const int want = (2 * device_sm_count(device) + max_tiles - 1) / std::max(max_tiles, 1);
+    const int splits = std::max(1, std::min(base.rb_per_expert, std::max(base.rb_per_expert / 8, want)));
+    base.rb_per_cta = (base.rb_per_expert + splits - 1) / splits;
+    size_t dyn = 0;
+    for (int i = 0; i < npools; ++i)
+        if (held[i])
+            dyn = std::max(dyn, (size_t)(tile_m + 1) * base.rb_per_cta * 16 * 4 + (size_t)8 * 2 * tile_m * gemvh_row_bytes(pools[i].t8) +
+                                    (size_t)8 * gemvh_stages(pools[i].rec_words) * pools[i].rec_words * 4);
+    if (dyn > 200 * 1024) return false;
+    h.base = base;
+    static bool attr_set[2][64] = {};   // per kernel (8 or 16 pairs) and device
+    auto launch = [&](auto kernel, int which) {
+        bool& done = attr_set[which][device];
+        if (!done) {
+            MFQB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+            done = true;
+        }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)splits, (unsigned)max_tiles);
+        cfg.blockDim = dim3(256);
+        cfg.dynamicSmemBytes = dyn;
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, h);
+        if (e != cudaSuccess)
+            fail(MFQB_ERR_CUDA, "all-cohort f16 tile launch (grid %d x %d, %zu bytes of shared memory, tile of %d): %s", splits, max_tiles, dyn, tile_m,
+                 cudaGetErrorString(e));
+    };
+    if (tile_m == 8) launch(moe_hetero_tilesh_kernel<1>, 0);
+    else launch(moe_hetero_tilesh_kernel<2>, 1);
+    return true;
+}
+
 // CTAs per pair (row splits) the all-cohort single-row launch uses for `pairs` pairs.
 int moe_hetero_gemv1_splits(int rb_per_expert, int pairs, int device) {
     const int want = (2 * device_sm_count(device) + pairs - 1) / std::max(pairs, 1);

@@ -174,10 +174,12 @@ bool nint_bl_gemvh_supported(const NintDevB& w, int rows_per_launch) {
 }
 // Elements per row of the f16 copy of the activations (whole chunks) and bytes of the copy of `rows` rows plus their scales.
 int nint_bl_x16_stride(const NintDevB& w) { return w.nchunks * kChunkGroupsB * w.gs; }
-size_t nint_bl_x16_bytes(const NintDevB& w, int rows) { return ((size_t)rows * nint_bl_x16_stride(w) * 2 + 255) / 256 * 256 + (size_t)rows * 4; }
-// Scales and converts x [rows, k] into `buf` (nint_bl_x16_bytes): the f16 rows, then the rows' inverse scales.
-void launch_x_rows_f16(const NintDevB& w, const void* x, int rows, bool x_f32, void* buf, const __half** x16, const float** scale, cudaStream_t s) {
-    const int kx = nint_bl_x16_stride(w);
+size_t x16_rows_bytes(int rows, int kx);
+size_t nint_bl_x16_bytes(const NintDevB& w, int rows) { return x16_rows_bytes(rows, nint_bl_x16_stride(w)); }
+// Scales and converts x [rows, k] into `buf`: the f16 rows [rows][kx] (kx >= k, a multiple of 8), then -- from the
+// next 256-byte boundary -- the rows' inverse scales.  x16_rows_bytes(rows, kx) bytes.
+size_t x16_rows_bytes(int rows, int kx) { return ((size_t)rows * kx * 2 + 255) / 256 * 256 + (size_t)rows * 4; }
+void launch_x_rows_f16_stride(const void* x, int rows, int k, int kx, bool x_f32, void* buf, const __half** x16, const float** scale, cudaStream_t s) {
     __half* out = static_cast<__half*>(buf);
     float* sc = reinterpret_cast<float*>(static_cast<char*>(buf) + ((size_t)rows * kx * 2 + 255) / 256 * 256);
     // launched as a programmatic dependent: it becomes resident while the previous kernel drains and waits
@@ -191,10 +193,13 @@ void launch_x_rows_f16(const NintDevB& w, const void* x, int rows, bool x_f32, v
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (x_f32) MFQB_CUDA(cudaLaunchKernelEx(&cfg, x_rows_f16_kernel<float>, static_cast<const float*>(x), w.k, kx, out, sc));
-    else MFQB_CUDA(cudaLaunchKernelEx(&cfg, x_rows_f16_kernel<__nv_bfloat16>, static_cast<const __nv_bfloat16*>(x), w.k, kx, out, sc));
+    if (x_f32) MFQB_CUDA(cudaLaunchKernelEx(&cfg, x_rows_f16_kernel<float>, static_cast<const float*>(x), k, kx, out, sc));
+    else MFQB_CUDA(cudaLaunchKernelEx(&cfg, x_rows_f16_kernel<__nv_bfloat16>, static_cast<const __nv_bfloat16*>(x), k, kx, out, sc));
     *x16 = out;
     *scale = sc;
+}
+void launch_x_rows_f16(const NintDevB& w, const void* x, int rows, bool x_f32, void* buf, const __half** x16, const float** scale, cudaStream_t s) {
+    launch_x_rows_f16_stride(x, rows, w.k, nint_bl_x16_stride(w), x_f32, buf, x16, scale, s);
 }
 static void* x16_scratch(int device, size_t bytes, cudaStream_t s) {
     static GrowOnlyScratch pool;
