@@ -187,6 +187,7 @@ def main() -> None:
     ap.add_argument("--match", default=None, help="with --only sweep: run the cases whose name contains this text")
     ap.add_argument("--tokens", type=int, nargs="*", default=None, help="token counts for --only moe")
     ap.add_argument("--batch", type=int, nargs="*", default=None, help="batch sizes for --only decoder")
+    ap.add_argument("--tune", nargs="*", default=[], help="KEY=VALUE pairs passed to mfqb_tune before anything runs")
     ap.add_argument("--layers", type=int, default=32, help="blocks of the --only decoder model (fewer: a small case for profilers)")
     ap.add_argument("--no-parallel", action="store_true",
                     help="at --gpus > 1 skip the sharded paths (keys tp_rowparallel, ep_moe_cfg4) and time the replicas only")
@@ -209,6 +210,11 @@ def main() -> None:
             "data": "synthetic", "config": {"workload": WORKLOAD, "pool": POOL, "l2_policy": "inputs larger than L2 "
                                             f"({POOL} x 7.2 MB weights per step)", "parallelism": f"replicas x{args.gpus}"}}
 
+    if args.tune and args.impl != "reference":
+        from tyloquant_b200._capi import check as _tcheck, lib as _tlib
+        for kv in args.tune:
+            key, _, val = kv.partition("=")
+            _tcheck(_tlib.mfqb_tune(key.encode(), int(val)))
     if args.only == "gemm":
         pk = measured_peaks()[0]
         emit(gemm_bench(local_rank, pk.get("bf16_tflops_sustained", pk["bf16_tflops"])))

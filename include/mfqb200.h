@@ -157,6 +157,8 @@ int mfqb_mul_mat_glu(const mfqb_weight* w, const void* x_bf16, int m, void* y, i
 
 /* Tuning switches, for measurements.  "gemv1_kernel": which kernel a single-row product of a plain
  * NINT weight takes -- 0 by shape (default), 1 the per-warp ring kernel, 2 the streamed kernel.
+ * "moe_f16_tiles_from_x2": twice the average number of (token, route) pairs per expert from which
+ * the expert matmuls take the f16 tile kernel instead of the integer tiles (default 4).
  * No counterpart in the reference (its switches are MFQ_* environment variables,
  * docs/developer-architecture-and-operator-reference.md:1048-1078). */
 int mfqb_tune(const char* key, int value);

@@ -50,9 +50,11 @@ void launch_nint_gemm_grouped(const NintDevB& w, const void* x16, int pairs, int
                               int rb_per_expert, int rows_per_expert, int max_tiles, void* y, int y_dtype, int device, cudaStream_t s);
 bool moe_hetero_tilesh_supported(const NintDevB* pools, const int* held, int npools);
 bool launch_moe_hetero_tilesh(GemvArgsB base, const NintDevB* pools, const int* held, int npools, int tile_m, int max_tiles, int device, cudaStream_t s);
-int nint_bl_x16_stride(const NintDevB& w);
-size_t x16_rows_bytes(int rows, int kx);
-void launch_x_rows_f16_stride(const void* x, int rows, int k, int kx, bool x_f32, void* buf, const __half** x16, const float** scale, cudaStream_t s);
+// Twice the pairs per expert from which the f16 tile kernel is used (mfqb_tune "moe_f16_tiles_from_x2"); defined with mfqb_tune.
+extern int g_moe_f16_from_x2;
+size_t nint_bl_frag_tile_units(const NintDevB& w, int nt);
+size_t x_frags_bytes(int in_rows, int tiles, size_t tile_units);
+void launch_x_frags(XFragArgs fa, int in_rows, int tiles, int max_nchunks, void* buf, const uint2** xf, const float** down, cudaStream_t s);
 bool launch_moe_hetero_tiles(GemvArgsB base, const NintDevB* pools, const int* held, const uint2* const* xq, const float2* const* gtab,
                              int npools, int tile_m, int max_tiles, int device, cudaStream_t s);
 bool launch_moe_hetero_gemv1(GemvArgsB base, const NintDevB* pools, const int* held, int npools, int pairs, int device, cudaStream_t s);
@@ -232,13 +234,22 @@ static bool moe_f16_tiles_ok(const mfqb_moe_weight* w) {
     }
     return moe_hetero_tilesh_supported(devs, held, (int)w->pools.size());
 }
-// Row stride (elements) of the f16 copy of the input rows that serves every held cohort.
-static int moe_x16_stride(const mfqb_moe_weight* w) {
-    int kx = 0;
+// 8-byte units per tile of the fragment-ordered input rows (the largest among the held cohorts) and the most chunks a row has.
+static size_t moe_frag_tile_units(const mfqb_moe_weight* w, int nt) {
+    size_t units = 0;
     for (const auto& pool : w->pools)
-        if (pool->held) kx = std::max(kx, nint_bl_x16_stride(pool->d));
-    return kx;
+        if (pool->held) units = std::max(units, nint_bl_frag_tile_units(pool->d, nt));
+    return units;
 }
+static int moe_max_nchunks(const mfqb_moe_weight* w) {
+    int n = 0;
+    for (const auto& pool : w->pools)
+        if (pool->held) n = std::max(n, pool->d.nchunks);
+    return n;
+}
+// Upper bound on the route plan's tiles for `pairs` pairs in tiles of tile_m.
+static int moe_max_tiles(const mfqb_moe_weight* w, int pairs, int tile_m) { return pairs / tile_m + std::min(pairs, w->info.n_experts); }
+
 
 static int moe_tile_m(const mfqb_moe_weight* w, int pairs) {
     const int e = w->info.n_experts;
@@ -248,7 +259,7 @@ static int moe_tile_m(const mfqb_moe_weight* w, int pairs) {
         if (pool->held) cap = std::min(cap, 2 * nint_bl_max_passes(pool->d));
     // from about three pairs per expert the f16 tile kernel (tiles of 8, then 16 pairs: an expert's weights are
     // decoded once per tile) is cheaper than the integer passes over tiles of 2 or 4
-    if (pairs >= 3 * e && moe_f16_tiles_ok(w)) return pairs >= 10 * e ? 16 : 8;
+    if (2 * (long long)pairs >= (long long)mfqb::g_moe_f16_from_x2 * e && moe_f16_tiles_ok(w)) return pairs >= 10 * e ? 16 : 8;
     // measured on the 128-expert top-8 layer: tiles of four win from two to about twenty pairs per expert
     return std::min(cap, 2 * pairs <= 3 * e ? 2 : (pairs <= 24 * e ? 4 : 8));
 }
@@ -269,8 +280,11 @@ static int moe_gemm_bn(const mfqb_moe_weight* w, int pairs) {
 
 // Bytes of quantised activation planes the tile path needs for `rows` input rows: one set per
 // distinct group size among the held cohorts (cohorts of equal group size share theirs).
-static size_t moe_planes_bytes(const mfqb_moe_weight* w, int rows) {
-    const size_t f16_rows = (x16_rows_bytes(rows, moe_x16_stride(w)) + 255) / 256 * 256;   // the f16 tile kernel's input rows share the space
+static size_t moe_planes_bytes(const mfqb_moe_weight* w, int rows, int pairs, int tile_m) {
+    // the f16 tile kernel's fragment-ordered input rows share the space
+    const size_t f16_rows = (tile_m == 8 || tile_m == 16)
+                                ? (x_frags_bytes(rows, moe_max_tiles(w, pairs, tile_m), moe_frag_tile_units(w, tile_m / 8)) + 255) / 256 * 256
+                                : 0;
     size_t total = 0;
     for (size_t pi = 0; pi < w->pools.size(); ++pi) {
         if (!w->pools[pi]->held) continue;
@@ -373,14 +387,29 @@ static void mul_mat_id_impl(const mfqb_moe_weight* w, const void* x, int x_per_p
         a.tile_bounds = plan->tile_bounds;
         a.pair_order = plan->pair_order;
         a.n_experts = w->info.n_experts;
-        a.x16_stride = moe_x16_stride(w);
-        launch_x_rows_f16_stride(x, in_rows, w->info.k, a.x16_stride, x_mode == 1, planes, &a.x16, &a.x16_scale, stream);
         NintDevB devs[16];
         int held[16];
+        XFragArgs fa{};
         for (size_t pi = 0; pi < w->pools.size(); ++pi) {
             devs[pi] = w->pools[pi]->d;
             held[pi] = w->pools[pi]->held;
+            fa.pool_t8[pi] = w->pools[pi]->d.t8;
+            fa.pool_nchunks[pi] = w->pools[pi]->held ? w->pools[pi]->d.nchunks : 0;
         }
+        fa.x = x;
+        fa.x_f32 = x_mode == 1;
+        fa.k = w->info.k;
+        fa.nt = tile_m / 8;
+        fa.tile_stride = moe_frag_tile_units(w, fa.nt);
+        fa.expert_bounds = plan->expert_bounds;
+        fa.tile_bounds = plan->tile_bounds;
+        fa.pair_order = plan->pair_order;
+        fa.expert_pool = static_cast<const int*>(w->d_expert_pool.p);
+        fa.n_experts = w->info.n_experts;
+        fa.routes = routes;
+        fa.x_per_pair = x_per_pair ? 1 : 0;
+        launch_x_frags(fa, in_rows, max_tiles_h, moe_max_nchunks(w), planes, &a.x16f, &a.x16_scale, stream);
+        a.x16f_tile_stride = fa.tile_stride;
         if (launch_moe_hetero_tilesh(a, devs, held, (int)w->pools.size(), tile_m, max_tiles_h, w->info.device, stream)) return;
         fail(MFQB_ERR_UNSUPPORTED, "mul_mat_id: tiles of %d pairs do not fit the f16 tile kernel for this record", tile_m);
     }
@@ -482,7 +511,7 @@ int mfqb_mul_mat_id(const mfqb_moe_weight* w, const void* x, int x_per_pair, con
         const int tile_m = gemm_bn ? gemm_bn : moe_tile_m(w, pairs);
         if (tile_m) {   // larger batches: route plan in library scratch, batched or tile kernel over its tiles
             const size_t b_plan = PlanBufs::bytes(w->info.n_experts, pairs);
-            const size_t b_in = gemm_bn ? nint_gemm_grouped_x_bytes(pairs, w->info.k) : moe_planes_bytes(w, x_per_pair ? pairs : tokens);
+            const size_t b_in = gemm_bn ? nint_gemm_grouped_x_bytes(pairs, w->info.k) : moe_planes_bytes(w, x_per_pair ? pairs : tokens, pairs, tile_m);
             char* s = static_cast<char*>(scratch_get(w->info.device, b_plan + b_in, stream, 1));
             PlanBufs plan = PlanBufs::carve(s, w->info.n_experts);
             launch_route_plan(ids, pairs, w->info.n_experts, tile_m, plan.expert_bounds, plan.tile_bounds, plan.pair_order, stream);
@@ -559,8 +588,8 @@ static FfnLayout ffn_layout(const mfqb_moe_weight* gate_up, const mfqb_moe_weigh
     L.tiles = L.tile_m != 0;
     L.fused_tail = !L.tiles && ffn_fused_tail_ok(down, tokens, (int)pairs) && ffn_fused_tail_ok(gate_up, tokens, (int)pairs);
     const size_t b_plan = L.tiles ? PlanBufs::bytes(gate_up->info.n_experts, pairs) : 0;
-    L.b_pgu = L.gemm ? up256(nint_gemm_grouped_x_bytes((int)pairs, h)) : (L.tiles ? moe_planes_bytes(gate_up, tokens) : 0);
-    const size_t b_pdn = L.gemm ? nint_gemm_grouped_x_bytes((int)pairs, f) : (L.tiles ? moe_planes_bytes(down, (int)pairs) : 0);
+    L.b_pgu = L.gemm ? up256(nint_gemm_grouped_x_bytes((int)pairs, h)) : (L.tiles ? moe_planes_bytes(gate_up, tokens, (int)pairs, L.tile_m) : 0);
+    const size_t b_pdn = L.gemm ? nint_gemm_grouped_x_bytes((int)pairs, f) : (L.tiles ? moe_planes_bytes(down, (int)pairs, (int)pairs, L.tile_m) : 0);
     L.o_gu = kFfnCounterBytes;
     L.o_hid = L.o_gu + up256(pairs * f2 * 4);
     L.o_dn = L.o_hid + up256(pairs * f * 4);

@@ -153,10 +153,10 @@ bool launch_moe_hetero_tiles(GemvArgsB base, const NintDevB* pools, const int* h
     return true;
 }
 
-// The same over the f16 batched kernel: tiles of 8 (NT = 1) or 16 (NT = 2) pairs, the input rows as scaled f16
-// (base.x16, base.x16_stride, base.x16_scale).
+// The same over the f16 batched kernel: tiles of 8 (NT = 1) or 16 (NT = 2) pairs, the input rows as scaled f16 in
+// fragment order (base.x16f, base.x16f_tile_stride, base.x16_scale).
 template <int NT>
-__global__ void __launch_bounds__(256, 2) moe_hetero_tilesh_kernel(const __grid_constant__ HeteroArgs h) {
+__global__ void __launch_bounds__(256, 3) moe_hetero_tilesh_kernel(const __grid_constant__ HeteroArgs h) {
     extern __shared__ __align__(16) unsigned char smem[];
     pdl_wait_b();   // route plan and f16 rows come from the previous kernels
     const int t = blockIdx.y, n_experts = h.base.n_experts;
@@ -206,8 +206,7 @@ bool launch_moe_hetero_tilesh(GemvArgsB base, const NintDevB* pools, const int* 
     size_t dyn = 0;
     for (int i = 0; i < npools; ++i)
         if (held[i])
-            dyn = std::max(dyn, (size_t)(tile_m + 1) * base.rb_per_cta * 16 * 4 + (size_t)8 * 2 * tile_m * gemvh_row_bytes(pools[i].t8) +
-                                    (size_t)8 * gemvh_stages(pools[i].rec_words) * pools[i].rec_words * 4);
+            dyn = std::max(dyn, (size_t)(tile_m + 1) * base.rb_per_cta * 16 * 4 + (size_t)8 * gemvh_stages(pools[i].rec_words) * pools[i].rec_words * 4);
     if (dyn > 200 * 1024) return false;
     h.base = base;
     static bool attr_set[2][64] = {};   // per kernel (8 or 16 pairs) and device

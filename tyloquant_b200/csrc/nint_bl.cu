@@ -161,49 +161,197 @@ static void* planes_scratch(int device, size_t bytes, cudaStream_t s) {
 
 static int passes_for(int m) { return m <= 2 ? 1 : (m <= 4 ? 2 : 4); }
 
+// up[row] = 2^e with 2^e * max|x[row]| in [2^14, 2^15) (1 for a zero, subnormal or non-finite row), down[row] = 2^-e.
+// One CTA of 1024 threads per row.
+template <typename XT>
+__global__ void __launch_bounds__(1024) x_row_scale_kernel(const XT* __restrict__ x, int k, float* __restrict__ up, float* __restrict__ down) {
+    __shared__ uint32_t red[32];
+    pdl_wait_b();
+    pdl_launch_dependents_b();
+    const XT* row = x + (size_t)blockIdx.x * k;
+    uint32_t ab = 0u;   // largest magnitude as float bits (orders like the value; NaN and infinity are largest)
+    for (int i = threadIdx.x; i < k; i += blockDim.x) ab = max(ab, __float_as_uint(fabsf((float)row[i])));
+    for (int o = 16; o > 0; o >>= 1) ab = max(ab, __shfl_xor_sync(0xffffffffu, ab, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ab;
+    __syncthreads();
+    ab = red[threadIdx.x & 31];
+    for (int o = 16; o > 0; o >>= 1) ab = max(ab, __shfl_xor_sync(0xffffffffu, ab, o));
+    if (threadIdx.x == 0) {
+        const int eb = (int)(ab >> 23);
+        const bool plain = eb == 0 || eb == 255;
+        up[blockIdx.x] = plain ? 1.f : __uint_as_float((uint32_t)(127 + 14 - (eb - 127)) << 23);     // 2^(14 - floor(log2 max))
+        down[blockIdx.x] = plain ? 1.f : __uint_as_float((uint32_t)(127 - 14 + (eb - 127)) << 23);   // its inverse
+    }
+}
+
+// x_frag_kernel: see XFragArgs.
+__global__ void __launch_bounds__(256) x_frag_kernel(const __grid_constant__ XFragArgs a) {
+    __shared__ int rows_s[16];
+    __shared__ float up_s[16];
+    pdl_wait_b();
+    pdl_launch_dependents_b();
+    const int t = blockIdx.y, MB = 8 * a.nt;
+    int pool = 0, m_cur = a.m, p0 = 0;
+    if (a.tile_bounds != nullptr) {
+        if (t >= a.tile_bounds[a.n_experts]) return;
+        int lo = 0, hi = a.n_experts - 1;   // expert e with tile_bounds[e] <= t < tile_bounds[e + 1]
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (a.tile_bounds[mid] <= t) lo = mid;
+            else hi = mid - 1;
+        }
+        pool = a.expert_pool[lo];
+        if (pool < 0) return;
+        p0 = a.expert_bounds[lo] + (t - a.tile_bounds[lo]) * MB;
+        m_cur = min(MB, a.expert_bounds[lo + 1] - p0);
+    }
+    const int T = a.pool_t8[pool], seg = blockIdx.x;
+    if (seg >= a.pool_nchunks[pool]) return;
+    if (threadIdx.x < 16) {
+        int r = -1;
+        if ((int)threadIdx.x < m_cur) {
+            if (a.tile_bounds != nullptr) {
+                const int pair = a.pair_order[p0 + threadIdx.x];
+                r = a.x_per_pair ? pair : pair / a.routes;
+            } else {
+                r = threadIdx.x;
+            }
+        }
+        rows_s[threadIdx.x] = r;
+        up_s[threadIdx.x] = (r >= 0 && a.up != nullptr) ? a.up[r] : 0.f;
+    }
+    __syncthreads();
+    if (a.up == nullptr) {   // no scale pass before this kernel: every CTA takes the rows' largest magnitudes itself, a warp per row
+        const int lane = threadIdx.x & 31;
+        for (int i = threadIdx.x >> 5; i < MB; i += (int)(blockDim.x >> 5)) {
+            const int r = rows_s[i];
+            if (r < 0) continue;
+            uint32_t ab = 0u;   // largest magnitude as float bits (orders like the value; NaN and infinity are largest)
+            if (a.x_f32) {
+                const float* row = static_cast<const float*>(a.x) + (size_t)r * a.k;
+                int j0 = 0;
+                if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {   // 16-byte loads over the aligned part
+                    const int nv = a.k >> 2;
+                    for (int j = lane; j < nv; j += 32) {
+                        const float4 v = __ldg(reinterpret_cast<const float4*>(row) + j);
+                        ab = max(max(ab, __float_as_uint(fabsf(v.x))), max(__float_as_uint(fabsf(v.y)), max(__float_as_uint(fabsf(v.z)), __float_as_uint(fabsf(v.w)))));
+                    }
+                    j0 = nv << 2;
+                }
+                for (int j = j0 + lane; j < a.k; j += 32) ab = max(ab, __float_as_uint(fabsf(row[j])));
+            } else {
+                const __nv_bfloat16* row = static_cast<const __nv_bfloat16*>(a.x) + (size_t)r * a.k;
+                int j0 = 0;
+                if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {   // eight bf16 per load: magnitude bits compare like the values
+                    const int nv = a.k >> 3;
+                    uint32_t hi = 0u, lo = 0u;
+                    for (int j = lane; j < nv; j += 32) {
+                        const uint4 v = __ldg(reinterpret_cast<const uint4*>(row) + j);
+                        const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            hi = max(hi, w4[i] & 0x7FFF0000u);
+                            lo = max(lo, (w4[i] << 16) & 0x7FFF0000u);
+                        }
+                    }
+                    ab = max(hi, lo);
+                    j0 = nv << 3;
+                }
+                for (int j = j0 + lane; j < a.k; j += 32) ab = max(ab, __float_as_uint(fabsf(__bfloat162float(row[j]))));
+            }
+            for (int o = 16; o > 0; o >>= 1) ab = max(ab, __shfl_xor_sync(0xffffffffu, ab, o));
+            if (lane == 0) {
+                const int eb = (int)(ab >> 23);
+                const bool plain = eb == 0 || eb == 255;
+                up_s[i] = plain ? 1.f : __uint_as_float((uint32_t)(127 + 14 - (eb - 127)) << 23);
+                if (blockIdx.x == 0) a.down_out[r] = plain ? 1.f : __uint_as_float((uint32_t)(127 - 14 + (eb - 127)) << 23);
+            }
+        }
+        __syncthreads();
+    }
+    uint2* dst = a.out + (size_t)t * a.tile_stride + (size_t)seg * 4 * T * a.nt * 32;
+    for (int idx = threadIdx.x; idx < 4 * T * a.nt * 32; idx += blockDim.x) {
+        const int lane = idx & 31, rest = idx >> 5, nt_i = rest % a.nt, j = rest / a.nt;
+        const int h = j & 1, ft = j >> 1, f = ft / T, tt = ft - f * T;
+        const int q = lane >> 2, c = lane & 3, r = rows_s[8 * nt_i + q];
+        const int kk = seg * 64 * T + (4 * f + 2 * h + (c >> 1)) * 8 * T + 8 * tt + 4 * (c & 1);
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (r >= 0) {
+            const float up = up_s[8 * nt_i + q];
+            const size_t e0 = (size_t)r * a.k + kk;
+            if (!a.x_f32 && kk + 3 < a.k && ((reinterpret_cast<uintptr_t>(a.x) + e0 * 2) & 7) == 0) {   // the four bf16 in one load
+                const uint2 w2 = __ldg(reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(a.x) + e0));
+                v[0] = __uint_as_float(w2.x << 16) * up;
+                v[1] = __uint_as_float(w2.x & 0xFFFF0000u) * up;
+                v[2] = __uint_as_float(w2.y << 16) * up;
+                v[3] = __uint_as_float(w2.y & 0xFFFF0000u) * up;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (kk + i < a.k)
+                        v[i] = (a.x_f32 ? static_cast<const float*>(a.x)[e0 + i] : __bfloat162float(static_cast<const __nv_bfloat16*>(a.x)[e0 + i])) * up;
+            }
+        }
+        __half hv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) hv[i] = isfinite(v[i]) ? __float2half_rn(v[i]) : __ushort_as_half((unsigned short)0x7E00);   // non-finite input -> NaN
+        uint2 pk;
+        pk.x = (uint32_t)__half_as_ushort(hv[0]) | ((uint32_t)__half_as_ushort(hv[1]) << 16);
+        pk.y = (uint32_t)__half_as_ushort(hv[2]) | ((uint32_t)__half_as_ushort(hv[3]) << 16);
+        dst[idx] = pk;
+    }
+}
+
 // ---- f16 batched kernel (nint_gemvh_bl.cuh) ------------------------------------------------------
-// Needs group sizes that are whole octets (padded group sizes keep the integer kernels) and two ring
-// stages beside the activation buffers.
+// Needs group sizes that are whole octets (padded group sizes keep the integer kernels).
 static size_t gemvh_smem(const NintDevB& w, int rb_per_cta, int nt) {
     const int mb = 8 * nt;
-    return codec_ctx_bytes(w) + (size_t)(mb + 1) * rb_per_cta * 16 * 4 + (size_t)8 * 2 * mb * gemvh_row_bytes(w.t8) +
-           (size_t)8 * gemvh_stages(w.rec_words) * w.rec_words * 4;
+    return codec_ctx_bytes(w) + (size_t)(mb + 1) * rb_per_cta * 16 * 4 + (size_t)8 * gemvh_stages(w.rec_words) * w.rec_words * 4;
 }
 bool nint_bl_gemvh_supported(const NintDevB& w, int rows_per_launch) {
-    return w.gs == 8 * w.t8 && gemvh_smem(w, 1, rows_per_launch > 8 ? 2 : 1) <= kGemvSmemLimit;
+    // (lattice records stay on the integer kernels: measured, their table lookups leave the f16 form no gain)
+    return !w.table && w.gs == 8 * w.t8 && gemvh_smem(w, 1, rows_per_launch > 8 ? 2 : 1) <= kGemvSmemLimit;
 }
-// Elements per row of the f16 copy of the activations (whole chunks) and bytes of the copy of `rows` rows plus their scales.
-int nint_bl_x16_stride(const NintDevB& w) { return w.nchunks * kChunkGroupsB * w.gs; }
-size_t x16_rows_bytes(int rows, int kx);
-size_t nint_bl_x16_bytes(const NintDevB& w, int rows) { return x16_rows_bytes(rows, nint_bl_x16_stride(w)); }
-// Scales and converts x [rows, k] into `buf`: the f16 rows [rows][kx] (kx >= k, a multiple of 8), then -- from the
-// next 256-byte boundary -- the rows' inverse scales.  x16_rows_bytes(rows, kx) bytes.
-size_t x16_rows_bytes(int rows, int kx) { return ((size_t)rows * kx * 2 + 255) / 256 * 256 + (size_t)rows * 4; }
-void launch_x_rows_f16_stride(const void* x, int rows, int k, int kx, bool x_f32, void* buf, const __half** x16, const float** scale, cudaStream_t s) {
-    __half* out = static_cast<__half*>(buf);
-    float* sc = reinterpret_cast<float*>(static_cast<char*>(buf) + ((size_t)rows * kx * 2 + 255) / 256 * 256);
-    // launched as a programmatic dependent: it becomes resident while the previous kernel drains and waits
-    // for it (the previous product may still read this buffer) before it touches memory
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)rows);
-    cfg.blockDim = dim3(1024);
-    cfg.stream = s;
+// 8-byte units of one tile (8 nt rows) of this weight's fragment-ordered activations.
+size_t nint_bl_frag_tile_units(const NintDevB& w, int nt) { return (size_t)w.nchunks * 4 * w.t8 * nt * 32; }
+// Bytes of the fragment buffer for `tiles` tiles of `tile_units` each plus the scales of `in_rows` source rows.
+size_t x_frags_bytes(int in_rows, int tiles, size_t tile_units) { return ((size_t)tiles * tile_units * 8 + 255) / 256 * 256 + (size_t)in_rows * 8; }
+
+// Row scales, then the fragments: fa carries the source rows, the tile description and the cohort geometry;
+// `buf` is x_frags_bytes(in_rows, tiles, fa.tile_stride).  Returns the fragment base and the inverse row scales.
+void launch_x_frags(XFragArgs fa, int in_rows, int tiles, int max_nchunks, void* buf, const uint2** xf, const float** down, cudaStream_t s) {
+    uint2* frags = static_cast<uint2*>(buf);
+    float* up = reinterpret_cast<float*>(static_cast<char*>(buf) + ((size_t)tiles * fa.tile_stride * 8 + 255) / 256 * 256);
+    float* dn = up + in_rows;
+    // both launched as programmatic dependents: they become resident while the previous kernel drains and wait
+    // for it (the previous product may still read this buffer) before they touch memory
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)in_rows);
+    cfg.blockDim = dim3(1024);
+    cfg.stream = s;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (x_f32) MFQB_CUDA(cudaLaunchKernelEx(&cfg, x_rows_f16_kernel<float>, static_cast<const float*>(x), k, kx, out, sc));
-    else MFQB_CUDA(cudaLaunchKernelEx(&cfg, x_rows_f16_kernel<__nv_bfloat16>, static_cast<const __nv_bfloat16*>(x), k, kx, out, sc));
-    *x16 = out;
-    *scale = sc;
-}
-void launch_x_rows_f16(const NintDevB& w, const void* x, int rows, bool x_f32, void* buf, const __half** x16, const float** scale, cudaStream_t s) {
-    launch_x_rows_f16_stride(x, rows, w.k, nint_bl_x16_stride(w), x_f32, buf, x16, scale, s);
+    if (tiles > 1 || max_nchunks > 24) {   // rows shared by many tiles or by many chunk CTAs: their scales once, in a pass of their own
+        if (fa.x_f32) MFQB_CUDA(cudaLaunchKernelEx(&cfg, x_row_scale_kernel<float>, static_cast<const float*>(fa.x), fa.k, up, dn));
+        else MFQB_CUDA(cudaLaunchKernelEx(&cfg, x_row_scale_kernel<__nv_bfloat16>, static_cast<const __nv_bfloat16*>(fa.x), fa.k, up, dn));
+        fa.up = up;
+    } else {           // one tile: the fragment kernel's CTAs find the scales themselves
+        fa.up = nullptr;
+        fa.down_out = dn;
+    }
+    fa.out = frags;
+    cfg.gridDim = dim3((unsigned)max_nchunks, (unsigned)tiles);
+    cfg.blockDim = dim3(256);
+    MFQB_CUDA(cudaLaunchKernelEx(&cfg, x_frag_kernel, fa));
+    *xf = frags;
+    *down = dn;
 }
 static void* x16_scratch(int device, size_t bytes, cudaStream_t s) {
     static GrowOnlyScratch pool;
-    return pool.get(device, bytes, s, "mfqb_mul_mat (f16 activation rows)");
+    return pool.get(device, bytes, s, "mfqb_mul_mat (f16 activation fragments)");
 }
 // y[m, n] = x[m, k] * W^T for 5 <= m <= 16 on the f16 batched kernel
 static void launch_bl_gemvh(const NintDevB& w, const void* x, int m, void* y, int y_dtype, int ldy, int device, cudaStream_t s) {
@@ -213,14 +361,22 @@ static void launch_bl_gemvh(const NintDevB& w, const void* x, int m, void* y, in
     a.m = m;
     a.ldy = ldy;
     a.y_dtype = y_dtype;
-    launch_x_rows_f16(w, x, m, false, x16_scratch(device, nint_bl_x16_bytes(w, m), s), &a.x16, &a.x16_scale, s);
-    a.x16_stride = nint_bl_x16_stride(w);
     const int nt = m > 8 ? 2 : 1, sms = device_sm_count(device);
+    XFragArgs fa{};
+    fa.x = x;
+    fa.k = w.k;
+    fa.nt = nt;
+    fa.m = m;
+    fa.tile_stride = nint_bl_frag_tile_units(w, nt);
+    fa.pool_t8[0] = w.t8;
+    fa.pool_nchunks[0] = w.nchunks;
+    launch_x_frags(fa, m, 1, w.nchunks, x16_scratch(device, x_frags_bytes(m, 1, fa.tile_stride), s), &a.x16f, &a.x16_scale, s);
+    a.x16f_tile_stride = fa.tile_stride;
     GemvPlanB p;
     p.passes = nt == 2 ? 116 : 108;
     // at least two row-blocks per CTA where the matrix allows: a chunk's activations then serve several records
     // (tall matrices take several waves of CTAs rather than more than eight row-blocks each)
-    const int cap = ctas_per_sm(gemvh_smem(w, 2, nt), 2) * sms;
+    const int cap = ctas_per_sm(gemvh_smem(w, 2, nt), 3) * sms;
     p.grid = std::max(1, std::min(w.nrb >= 2 * sms ? w.nrb / 2 : w.nrb, cap));
     a.rb_per_cta = std::min(8, (w.nrb + p.grid - 1) / p.grid);
     p.grid = (w.nrb + a.rb_per_cta - 1) / a.rb_per_cta;

@@ -26,6 +26,23 @@
 
 namespace mfqb {
 
+// Writes the scaled f16 activations in fragment order.  Grid (chunks, tiles), 256 threads.  A tile is
+// 8 nt rows: the whole batch of a plain product (tile_bounds == nullptr, rows 0 .. m-1), or a route-plan
+// tile of one expert, whose cohort fixes the geometry (octets per group T, chunks per row).  Layout of a
+// tile, in 8-byte units: [chunk][mma j = (f T + t) 2 + h][row octet][lane], lane (q, c) holding row 8 nt + q,
+// elements (4f + 2h + (c>>1)) 8T + 8t + 4(c&1) + {0..3} of the chunk.
+struct XFragArgs {
+    const void* x;        // [in_rows][k] bf16 or float32
+    int x_f32, k;
+    const float* up;      // scale of every source row, or nullptr: the kernel computes them (and writes the inverses to down_out)
+    float* down_out;
+    uint2* out;
+    size_t tile_stride;   // 8-byte units
+    int nt, m;
+    const int *expert_bounds, *tile_bounds, *pair_order, *expert_pool;
+    int n_experts, routes, x_per_pair;
+    int pool_t8[16], pool_nchunks[16];   // by cohort; a plain product uses entry 0
+};
 // One weight of a multi-weight launch (several weights of one shape class applied to the same x).
 struct GemvMultiEntry {
     const uint32_t* items;
@@ -71,10 +88,10 @@ struct GemvArgsB {
     // pair_out [pairs, ldy] float32, and the last of a token's `routes` CTAs to arrive adds them with
     // the route weights, in route order, into y_final [tokens, ldy] (moe_weighted_reduce,
     // mfq/kernels/cuda/moe.cu:2957-2977).  token_count: [tokens * gridDim.x] zeros, left zero again.
-    // f16 batched kernel (nint_gemvh_bl.cuh): the activation rows scaled and converted to f16, [rows][x16_stride]
-    // with x16_stride >= nchunks * 8 * gs (zero padded), and the inverse scale of every row.
-    const __half* x16;
-    int x16_stride;
+    // f16 batched kernel (nint_gemvh_bl.cuh): the scaled f16 activations in fragment order (x_frag_kernel), the
+    // distance between tiles in 8-byte units, and the inverse scale of every source row.
+    const uint2* x16f;
+    size_t x16f_tile_stride;
     const float* x16_scale;
     int x_mode;
     // Single-row kernel, gated FFN: the weight's 16-row blocks alternate (gate rows, up rows); the kernel

@@ -12,12 +12,14 @@
 // accumulators are final values: no per-group scaling afterwards.
 //
 // Activations: every row is scaled by a power of two so that its largest magnitude lands near 2^14
-// and converted to f16 once per call (x_rows_f16_kernel; exact for a bf16 input within 2^-28 of
-// the row's largest magnitude), the inverse factor is applied to the finished sums.  A warp owns
-// whole chunks of K and, with the first record of a chunk, requests that chunk's slice of all
-// batch rows into one of its two private buffers (same asynchronous copy group), as in the integer
-// batched kernel.  Weights are rounded to f16 once (d and m rounded to f16, one fused multiply-add):
-// about 3e-4 relative L2 on the product, inside the path's 1e-3 bound.
+// (x_row_scale_kernel; the inverse factor is applied to the finished sums) and written as f16 in the
+// order the B fragments are consumed (x_frag_kernel): per tile of 8 NT rows and chunk, for each mma
+// of the record the 32 lanes' 8 bytes next to each other, so a warp fetches a fragment with one
+// coalesced 256-byte read that the other row-blocks of the chunk and the other CTAs of the tile find
+// in L1 / L2 -- no shared-memory staging, which leaves room for four CTAs per SM.  Exact for a bf16
+// input within 2^-28 of the row's largest magnitude.  Weights are rounded to f16 once (d and the
+// centred offset rounded to f16, one fused multiply-add): about 3e-4 relative L2 on the product,
+// inside the path's 1e-3 bound.
 //
 // Tile mode (expert matmul with a route plan): blockIdx.y is a tile of up to 8 NT (token, route)
 // pairs of one expert; x rows are taken through pair_order and results scatter back to pair order.
@@ -28,52 +30,6 @@
 
 namespace mfqb {
 
-// x [rows, k] (bf16 or float32) -> out [rows, kx] f16, each row times 2^e with e chosen from the row's
-// largest magnitude (kx >= k, zero padded); row_scale[row] = 2^-e.  One CTA of 1024 threads per row.
-template <typename XT>
-__global__ void __launch_bounds__(1024) x_rows_f16_kernel(const XT* __restrict__ x, int k, int kx, __half* __restrict__ out,
-                                                          float* __restrict__ row_scale) {
-    __shared__ uint32_t red[32];
-    pdl_wait_b();
-    pdl_launch_dependents_b();
-    const XT* row = x + (size_t)blockIdx.x * k;
-    uint32_t ab = 0u;   // largest magnitude as float bits (orders like the value; NaN and infinity are largest)
-    for (int i = threadIdx.x; i < k; i += blockDim.x) ab = max(ab, __float_as_uint(fabsf((float)row[i])));
-    for (int o = 16; o > 0; o >>= 1) ab = max(ab, __shfl_xor_sync(0xffffffffu, ab, o));
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ab;
-    __syncthreads();
-    ab = red[threadIdx.x & 31];
-    for (int o = 16; o > 0; o >>= 1) ab = max(ab, __shfl_xor_sync(0xffffffffu, ab, o));
-    // 2^e * max in [2^14, 2^15); a zero, subnormal or non-finite row keeps e = 0
-    const int eb = (int)(ab >> 23);
-    const bool plain = eb == 0 || eb == 255;
-    const float up = plain ? 1.f : __uint_as_float((uint32_t)(127 + 14 - (eb - 127)) << 23);     // 2^(14 - floor(log2 max))
-    const float down = plain ? 1.f : __uint_as_float((uint32_t)(127 - 14 + (eb - 127)) << 23);   // its inverse
-    if (threadIdx.x == 0) row_scale[blockIdx.x] = down;
-    __half* orow = out + (size_t)blockIdx.x * kx;
-    for (int i = threadIdx.x; i < kx; i += blockDim.x) {
-        const float v = i < k ? (float)row[i] : 0.f;
-        orow[i] = isfinite(v) ? __float2half_rn(v * up) : __ushort_as_half((unsigned short)0x7E00);   // non-finite input -> NaN
-    }
-}
-
-// Padding of a row of the per-warp activation buffers (bytes) so that the sixteen 8-byte reads of a
-// half-warp -- rows q = 0..3 (or 4..7) x offsets {0, 8, 16T, 16T + 8} -- fall into distinct banks.
-__host__ __device__ constexpr int gemvh_row_pad(int t8) {
-    for (int pad = 0; pad < 128; pad += 16) {
-        bool ok = true;
-        unsigned seen = 0u;   // 16 slots of 8 bytes in a 128-byte bank line
-        for (int q = 0; q < 4 && ok; ++q)
-            for (int j = 0; j < 4 && ok; ++j) {
-                const int off = (q * pad + (j >> 1) * 16 * t8 + (j & 1) * 8) % 128 / 8;
-                if (seen & (1u << off)) ok = false;
-                seen |= 1u << off;
-            }
-        if (ok) return pad;
-    }
-    return 16;
-}
-__host__ __device__ constexpr int gemvh_row_bytes(int t8) { return kChunkGroupsB * 8 * t8 * 2 + gemvh_row_pad(t8); }
 __host__ __device__ constexpr int gemvh_stages(int rec_words) { return gemv1_bl_stages(rec_words) > 4 ? 4 : gemv1_bl_stages(rec_words); }
 
 // The dequantised weights carry a factor 2^10 (taken out of the finished sums): f16 then keeps all its
@@ -102,12 +58,11 @@ __device__ __forceinline__ void codes_to_f16(uint32_t v, __half2 d, __half2 nm, 
     w23 = *reinterpret_cast<const uint32_t*>(&r23);
 }
 
-// Shared memory: partial sums [8 NT][rb_per_cta * 16] f32 | anchors [rb_per_cta * 16] | per warp two
-// activation buffers [8 NT rows][row bytes] | per warp a ring of S records.
+// Shared memory: partial sums [8 NT][rb_per_cta * 16] f32 | anchors [rb_per_cta * 16] | per warp a ring of S records.
 template <class C, int NT>
 __device__ __forceinline__ void gemvh_bl_body(const GemvArgsB& a, const NintDevB& w, unsigned char* smem) {
     constexpr int G = kChunkGroupsB, MB = 8 * NT, T = C::T, WC = C::WC, SW = C::SW, REC = (WC + SW) * 32;
-    constexpr int S = gemvh_stages(REC), RS = gemvh_row_bytes(T), CHUNK_BYTES = G * 8 * T * 2, PIECES = CHUNK_BYTES / 16;
+    constexpr int S = gemvh_stages(REC), FRAGS = 4 * T * NT * 32;   // 8-byte units of one chunk of a tile
 
     __shared__ int row_src[MB], row_dst[MB];
     __shared__ float row_undo[MB];
@@ -118,12 +73,11 @@ __device__ __forceinline__ void gemvh_bl_body(const GemvArgsB& a, const NintDevB
     ctx.init(smem, w, tid, blockDim.x);   // constant tables: visible after the first __syncthreads
     float* ypart = reinterpret_cast<float*>(smem + C::ctx_bytes(w));                // [MB][rb_per_cta * 16]
     uint32_t* anch = reinterpret_cast<uint32_t*>(ypart + (size_t)MB * ystride);     // [rb_per_cta * 16]
-    unsigned char* xb_all = reinterpret_cast<unsigned char*>(anch + ystride);       // [warp][2 buffers][MB rows][RS]
-    unsigned char* xb = xb_all + (size_t)warp * 2 * MB * RS;
-    uint32_t* ring = reinterpret_cast<uint32_t*>(xb_all + (size_t)nwarps * 2 * MB * RS) + (size_t)warp * S * REC;
+    uint32_t* ring = anch + ystride + (size_t)warp * S * REC;
 
     int m_cur = a.m, rb0, nrb, rbl0 = 0, row_limit = w.n;
-    pdl_wait_b();   // the f16 rows (and, in tile mode, the route plan) come from the previous kernels
+    const uint2* xf = a.x16f;   // this tile's fragments
+    pdl_wait_b();   // the fragments (and, in tile mode, the route plan) come from the previous kernels
     if (a.tile_bounds != nullptr) {
         const int t = blockIdx.y;
         if (t >= a.tile_bounds[a.n_experts]) return;
@@ -135,6 +89,7 @@ __device__ __forceinline__ void gemvh_bl_body(const GemvArgsB& a, const NintDevB
         }
         const int e = lo;
         if (a.expert_pool[e] != a.pool) return;
+        xf += (size_t)t * a.x16f_tile_stride;
         const int p0 = a.expert_bounds[e] + (t - a.tile_bounds[e]) * MB;
         m_cur = min(MB, a.expert_bounds[e + 1] - p0);
         if (tid < MB) {
@@ -153,17 +108,14 @@ __device__ __forceinline__ void gemvh_bl_body(const GemvArgsB& a, const NintDevB
     pdl_launch_dependents_b();
     for (int i = tid; i < MB * ystride; i += blockDim.x) ypart[i] = 0.f;
     for (int i = tid; i < nrb * 16; i += blockDim.x) anch[i] = __ldg(w.anchors + rb0 * 16 + i);
-    // rows past the batch are never copied: their buffers stay zero and contribute nothing
-    for (int i = tid; i < nwarps * 2 * MB * RS / 16; i += blockDim.x) reinterpret_cast<uint4*>(xb_all)[i] = make_uint4(0u, 0u, 0u, 0u);
-    __syncthreads();   // row_src / row_dst, zeroed buffers
+    __syncthreads();   // row_src / row_dst
     if (tid < MB) row_undo[tid] = tid < m_cur ? a.x16_scale[row_src[tid]] * kGemvhWeightUndo : 0.f;
 
     // items of this warp, chunk-major: chunk = warp, warp + nwarps, ...; inside a chunk every
-    // row-block of the CTA.  The issue cursor runs `ahead` <= min(S, nrb) items in front, so the
-    // items in flight touch at most two chunks: the two activation buffers alternate by chunk.
+    // row-block of the CTA.  The issue cursor runs `ahead` = S items in front.
     const int my_segs = warp < w.nchunks ? (w.nchunks - warp + nwarps - 1) / nwarps : 0;
-    const int n_mine = my_segs * nrb, ahead = min(S, nrb);
-    int iss_i = 0, iss_seg = warp, iss_rbl = 0, iss_stage = 0, iss_buf = 0;
+    const int n_mine = my_segs * nrb, ahead = S;
+    int iss_i = 0, iss_seg = warp, iss_rbl = 0, iss_stage = 0;
     auto issue = [&]() {
         if (iss_i < n_mine) {
             const uint32_t* src = w.items + ((size_t)(rb0 + iss_rbl) * w.nchunks + iss_seg) * REC;
@@ -171,16 +123,6 @@ __device__ __forceinline__ void gemvh_bl_body(const GemvArgsB& a, const NintDevB
 #pragma unroll
             for (int off = 0; off < REC; off += 128)
                 if (off + 128 <= REC || lane * 4 < REC - off) cp_async16_b(dst + off + lane * 4, src + off + lane * 4);
-            if (iss_rbl == 0) {   // first item of a chunk: its activations travel in the same group
-                unsigned char* pb = xb + (size_t)iss_buf * MB * RS;
-                for (int idx = lane; idx < m_cur * PIECES; idx += 32) {
-                    const int m = idx / PIECES, piece = idx % PIECES;
-                    const unsigned char* gsrc = reinterpret_cast<const unsigned char*>(a.x16 + (size_t)row_src[m] * a.x16_stride) +
-                                                (size_t)iss_seg * CHUNK_BYTES + piece * 16;
-                    cp_async16_b(pb + m * RS + piece * 16, gsrc);
-                }
-                iss_buf ^= 1;
-            }
         }
         cp_async_commit_b();   // one group per item slot, empty past the end: keeps the wait count uniform
         ++iss_i;
@@ -189,7 +131,7 @@ __device__ __forceinline__ void gemvh_bl_body(const GemvArgsB& a, const NintDevB
     };
     for (int i = 0; i < ahead; ++i) issue();
 
-    int rbl = 0, stage = 0, buf = 0;
+    int rbl = 0, stage = 0, seg = warp;
     for (int i = 0; i < n_mine; ++i) {
         // the groups newer than this item's are the ahead - 1 items issued after it
         switch (ahead) {
@@ -200,7 +142,7 @@ __device__ __forceinline__ void gemvh_bl_body(const GemvArgsB& a, const NintDevB
         }
         __syncwarp();
         const uint32_t* rec = ring + stage * REC;
-        const unsigned char* pb = xb + (size_t)buf * MB * RS;
+        const uint2* xc = xf + (size_t)seg * FRAGS + lane;   // the chunk's fragments, this lane's 8 bytes of each
         uint32_t qw[WC];
 #pragma unroll
         for (int j = 0; j < WC; ++j) qw[j] = rec[j * 32 + lane];
@@ -215,7 +157,7 @@ __device__ __forceinline__ void gemvh_bl_body(const GemvArgsB& a, const NintDevB
 #pragma unroll
         for (int j = 0; j < SW; ++j) own[j] = C::NEEDS_OWN_SCALE ? rec[(WC + j) * 32 + lane] : 0u;
         __syncwarp();          // every lane has read the stage before it is refilled
-        issue();               // item i + ahead: never into the activation buffer this item reads (see above)
+        issue();               // item i + ahead
 
         const uint32_t an_lo = anch[rbl * 16 + q], an_hi = anch[rbl * 16 + q + 8];
         const float2 f_lo = __half22float2(*reinterpret_cast<const __half2*>(&an_lo));   // (ns, nm)
@@ -251,10 +193,9 @@ __device__ __forceinline__ void gemvh_bl_body(const GemvArgsB& a, const NintDevB
                     uint32_t a0, a1, a2, a3;
                     codes_to_f16<C::A_SIGNED, C::HAS_MIN, C::QMID>(C::areg(qw, r + 2 * h, ctx, own), d_lo[h], nm_lo[h], a0, a2);
                     codes_to_f16<C::A_SIGNED, C::HAS_MIN, C::QMID>(C::areg(qw, r + 2 * h + 1, ctx, own), d_hi[h], nm_hi[h], a1, a3);
-                    const int xoff = ((4 * f + 2 * h + (c >> 1)) * 8 * T + 8 * t + 4 * (c & 1)) * 2;
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt) {
-                        const uint2 b = *reinterpret_cast<const uint2*>(pb + (8 * nt + q) * RS + xoff);
+                        const uint2 b = __ldg(xc + (((f * T + t) * 2 + h) * NT + nt) * 32);
                         hmma_16816(acc[nt], a0, a1, a2, a3, b.x, b.y);
                     }
                 }
@@ -273,7 +214,7 @@ __device__ __forceinline__ void gemvh_bl_body(const GemvArgsB& a, const NintDevB
                 atomicAdd(ypart + (size_t)(m0 + 1) * ystride + rbl * 16 + q + 8, acc[nt][3]);
             }
         }
-        if (++rbl == nrb) { rbl = 0; buf ^= 1; }
+        if (++rbl == nrb) { rbl = 0; seg += nwarps; }
         if (++stage == S) stage = 0;
     }
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
