@@ -33,11 +33,11 @@ __device__ __forceinline__ void dep_wait() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 template <typename... KArgs, typename... Args>
-static void launch_dep(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t s, Args... args) {
+static void launch_dep_smem(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
-    cfg.dynamicSmemBytes = 0;
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -45,6 +45,10 @@ static void launch_dep(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStre
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     MFQB_CUDA(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
+}
+template <typename... KArgs, typename... Args>
+static void launch_dep(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t s, Args... args) {
+    launch_dep_smem(kernel, grid, block, 0, s, args...);
 }
 
 // ---- glue kernels --------------------------------------------------------------------------------
@@ -139,6 +143,16 @@ __device__ __forceinline__ void bf16x8_to_f32(const uint4& r, float* f) {
 }
 
 constexpr int kMaxSplits = 64;
+constexpr int kAttnStages = 3;   // rounds of 32 tokens in flight per CTA
+// Dynamic shared memory of the attention kernel: the K/V ring (stages x 4 tokens x (K, V) x 128 threads x 16 bytes),
+// reused afterwards for the eight half-warps' results ([8][G][128] + 2 x [8][G] floats).
+constexpr size_t attn_smem_bytes(int g) {
+    const size_t ring = (size_t)kAttnStages * 4 * 2 * 128 * 16, meet = (size_t)8 * g * (kHeadDim + 2) * 4;
+    return ring > meet ? ring : meet;
+}
+__device__ __forceinline__ void cp_async16_attn(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+}
 constexpr int kPartStride = kHeadDim + 4;   // a split's record per head: 128 output values | max | sum | pad (528 bytes)
 
 // Grouped-query decode attention for one new token per sequence, one launch: rotary embedding,
@@ -185,19 +199,27 @@ __global__ void __launch_bounds__(128, G <= 4 ? 4 : 2) attn_decode_kernel(const 
         }
         __syncthreads();   // visible to the whole CTA before anyone reads that position
     }
-    constexpr int TPR = 4;   // tokens per half-warp and round: slot, slot + 8, + 16, + 24 of a 32-token round
-    uint4 ck[TPR], cv[TPR];
-    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-    auto fetch = [&](int base) {
+    // A half-warp takes four tokens per round (slot, slot + 8, + 16, + 24 of a 32-token round).  Every lane copies
+    // the 16 bytes of K and of V it will use itself into its own slots of a ring in shared memory, kAttnStages
+    // rounds deep (asynchronous copies, no registers held, no synchronisation: a lane only reads what it copied),
+    // so the loads of the next rounds are in flight while a round is used.
+    constexpr int TPR = 4;
+    extern __shared__ __align__(16) unsigned char attn_smem[];
+    uint4* ring = reinterpret_cast<uint4*>(attn_smem);   // [stage][token of the round][K, V][thread]
+    auto slot_of = [&](int stage, int i, int kv) { return ring + ((stage * TPR + i) * 2 + kv) * 128 + threadIdx.x; };
+    auto request = [&](int base, int stage) {   // one copy group per round, empty past the end of the slice
 #pragma unroll
         for (int i = 0; i < TPR; ++i) {
             const int t = base + slot + 8 * i;
-            const bool ok = t < t1;
-            ck[i] = ok ? *reinterpret_cast<const uint4*>(kb + (size_t)t * kHeadDim) : zero;
-            cv[i] = ok ? *reinterpret_cast<const uint4*>(vb + (size_t)t * kHeadDim) : zero;
+            if (t < t1) {
+                cp_async16_attn(slot_of(stage, i, 0), kb + (size_t)t * kHeadDim);
+                cp_async16_attn(slot_of(stage, i, 1), vb + (size_t)t * kHeadDim);
+            }
         }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
     };
-    if (t0 < t1) fetch(t0);
+#pragma unroll
+    for (int sidx = 0; sidx < kAttnStages - 1; ++sidx) request(t0 + sidx * 8 * TPR, sidx);
     float qv[G][8];
     if (t0 < t1) {
 #pragma unroll
@@ -211,12 +233,17 @@ __global__ void __launch_bounds__(128, G <= 4 ? 4 : 2) attn_decode_kernel(const 
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[g][i] = 0.f;
     }
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    int stage = 0, req_stage = kAttnStages - 1;
     for (int base = t0; base < t1; base += 8 * TPR) {   // uniform trip count over the CTA: the shuffles below need whole warps
+        request(base + (kAttnStages - 1) * 8 * TPR, req_stage);   // the slot read in the previous iteration
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(kAttnStages - 1) : "memory");
         float sc[TPR][G];
 #pragma unroll
         for (int i = 0; i < TPR; ++i) {
             float kf[8];
-            bf16x8_to_f32(ck[i], kf);
+            const uint4 ck = base + slot + 8 * i < t1 ? *slot_of(stage, i, 0) : zero;
+            bf16x8_to_f32(ck, kf);
 #pragma unroll
             for (int g = 0; g < G; ++g) {
                 float x = 0.f;
@@ -256,18 +283,23 @@ __global__ void __launch_bounds__(128, G <= 4 ? 4 : 2) attn_decode_kernel(const 
 #pragma unroll
             for (int i = 0; i < TPR; ++i) {
                 float vf[8];
-                bf16x8_to_f32(cv[i], vf);
+                const uint4 cv = base + slot + 8 * i < t1 ? *slot_of(stage, i, 1) : zero;
+                bf16x8_to_f32(cv, vf);
 #pragma unroll
                 for (int g = 0; g < G; ++g)
 #pragma unroll
                     for (int d = 0; d < 8; ++d) acc[g][d] += pr[i][g] * vf[d];
             }
         }
-        if (base + 8 * TPR < t1) fetch(base + 8 * TPR);
+        if (++stage == kAttnStages) stage = 0;
+        if (++req_stage == kAttnStages) req_stage = 0;
     }
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();   // the ring is done with: its memory now holds the half-warps' results
     // the eight half-warps of the CTA meet in shared memory
-    __shared__ float sm_m[8][G], sm_l[8][G];
-    __shared__ __align__(16) float sm_acc[8][G][kHeadDim];
+    float(*sm_acc)[G][kHeadDim] = reinterpret_cast<float(*)[G][kHeadDim]>(attn_smem);                       // [8][G][128]
+    float(*sm_m)[G] = reinterpret_cast<float(*)[G]>(attn_smem + (size_t)8 * G * kHeadDim * 4);              // [8][G]
+    float(*sm_l)[G] = reinterpret_cast<float(*)[G]>(attn_smem + (size_t)8 * G * kHeadDim * 4 + 8 * G * 4);  // [8][G]
 #pragma unroll
     for (int g = 0; g < G; ++g) {
         if (l16 == 0) { sm_m[slot][g] = m[g]; sm_l[slot][g] = l[g]; }
@@ -479,7 +511,7 @@ static const float* layer_forward(mfqb_decoder* d, int li, int rows, const float
     const int nsplit = attn_splits(d, rows, d->cfg.max_ctx);
     const dim3 agrid(nsplit, d->nkv, rows);
     auto attn = [&](auto kernel) {
-        launch_dep(kernel, agrid, dim3(128), s, static_cast<const float*>(d->qkv.p), static_cast<__nv_bfloat16*>(L.kcache.p),
+        launch_dep_smem(kernel, agrid, dim3(128), attn_smem_bytes(G), s, static_cast<const float*>(d->qkv.p), static_cast<__nv_bfloat16*>(L.kcache.p),
                    static_cast<__nv_bfloat16*>(L.vcache.p), static_cast<const int*>(d->pos.p), static_cast<float*>(d->part.p),
                    static_cast<unsigned*>(d->attn_count.p), static_cast<__nv_bfloat16*>(d->attn.p), d->nq, d->nkv, d->cfg.max_ctx, nsplit,
                    static_cast<const float2*>(d->rope_table.p));
@@ -570,10 +602,22 @@ int mfqb_decoder_create(const mfqb_decoder_config* cfg, int rank, int world, mfq
             int per_sm = 0;
             cudaError_t e = cudaErrorInvalidValue;
             switch (cfg->n_q_heads / cfg->n_kv_heads) {
-                case 1: e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_kernel<1>, 128, 0); break;
-                case 2: e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_kernel<2>, 128, 0); break;
-                case 4: e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_kernel<4>, 128, 0); break;
-                case 8: e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_kernel<8>, 128, 0); break;
+                case 1:
+                    MFQB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem_bytes(1)));
+                    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_kernel<1>, 128, attn_smem_bytes(1));
+                    break;
+                case 2:
+                    MFQB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem_bytes(2)));
+                    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_kernel<2>, 128, attn_smem_bytes(2));
+                    break;
+                case 4:
+                    MFQB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem_bytes(4)));
+                    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_kernel<4>, 128, attn_smem_bytes(4));
+                    break;
+                case 8:
+                    MFQB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem_bytes(8)));
+                    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_kernel<8>, 128, attn_smem_bytes(8));
+                    break;
                 default: fail(MFQB_ERR_UNSUPPORTED, "query heads per KV head must be 1, 2, 4 or 8, got %d", cfg->n_q_heads / cfg->n_kv_heads);
             }
             MFQB_CUDA(e);

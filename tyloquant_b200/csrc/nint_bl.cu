@@ -161,6 +161,48 @@ static void* planes_scratch(int device, size_t bytes, cudaStream_t s) {
 
 static int passes_for(int m) { return m <= 2 ? 1 : (m <= 4 ? 2 : 4); }
 
+// This thread's share of the largest magnitude of a row, as float bits (they order like the values; NaN and
+// infinity are largest): threads tid, tid + nthreads, ... take 16-byte pieces where the row is aligned.
+__device__ __forceinline__ uint32_t row_absmax_part(const void* x, bool x_f32, size_t row, int k, int tid, int nthreads) {
+    uint32_t ab = 0u;
+    if (x_f32) {
+        const float* p = static_cast<const float*>(x) + row * k;
+        int j0 = 0;
+        if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+            const int nv = k >> 2;
+#pragma unroll 4
+            for (int j = tid; j < nv; j += nthreads) {
+                const float4 v = __ldg(reinterpret_cast<const float4*>(p) + j);
+                ab = max(max(ab, __float_as_uint(fabsf(v.x))), max(__float_as_uint(fabsf(v.y)), max(__float_as_uint(fabsf(v.z)), __float_as_uint(fabsf(v.w)))));
+            }
+            j0 = nv << 2;
+        }
+        for (int j = j0 + tid; j < k; j += nthreads) ab = max(ab, __float_as_uint(fabsf(p[j])));
+    } else {
+        const __nv_bfloat16* p = static_cast<const __nv_bfloat16*>(x) + row * k;
+        int j0 = 0;
+        if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+            const int nv = k >> 3;
+#pragma unroll 4
+            for (int j = tid; j < nv; j += nthreads) {
+                const uint4 v = __ldg(reinterpret_cast<const uint4*>(p) + j);
+                const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) ab = max(ab, max(w4[i] & 0x7FFF0000u, (w4[i] << 16) & 0x7FFF0000u));
+            }
+            j0 = nv << 3;
+        }
+        for (int j = j0 + tid; j < k; j += nthreads) ab = max(ab, __float_as_uint(fabsf(__bfloat162float(p[j]))));
+    }
+    return ab;
+}
+// (2^e, 2^-e) with 2^e * max in [2^14, 2^15); (1, 1) for a zero, subnormal or non-finite maximum.
+__device__ __forceinline__ float2 row_scale_pair(uint32_t absmax_bits) {
+    const int eb = (int)(absmax_bits >> 23);
+    if (eb == 0 || eb == 255) return make_float2(1.f, 1.f);
+    return make_float2(__uint_as_float((uint32_t)(127 + 14 - (eb - 127)) << 23), __uint_as_float((uint32_t)(127 - 14 + (eb - 127)) << 23));
+}
+
 // up[row] = 2^e with 2^e * max|x[row]| in [2^14, 2^15) (1 for a zero, subnormal or non-finite row), down[row] = 2^-e.
 // One CTA of 1024 threads per row.
 template <typename XT>
@@ -168,19 +210,16 @@ __global__ void __launch_bounds__(1024) x_row_scale_kernel(const XT* __restrict_
     __shared__ uint32_t red[32];
     pdl_wait_b();
     pdl_launch_dependents_b();
-    const XT* row = x + (size_t)blockIdx.x * k;
-    uint32_t ab = 0u;   // largest magnitude as float bits (orders like the value; NaN and infinity are largest)
-    for (int i = threadIdx.x; i < k; i += blockDim.x) ab = max(ab, __float_as_uint(fabsf((float)row[i])));
+    uint32_t ab = row_absmax_part(x, sizeof(XT) == 4, blockIdx.x, k, threadIdx.x, blockDim.x);
     for (int o = 16; o > 0; o >>= 1) ab = max(ab, __shfl_xor_sync(0xffffffffu, ab, o));
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ab;
     __syncthreads();
     ab = red[threadIdx.x & 31];
     for (int o = 16; o > 0; o >>= 1) ab = max(ab, __shfl_xor_sync(0xffffffffu, ab, o));
     if (threadIdx.x == 0) {
-        const int eb = (int)(ab >> 23);
-        const bool plain = eb == 0 || eb == 255;
-        up[blockIdx.x] = plain ? 1.f : __uint_as_float((uint32_t)(127 + 14 - (eb - 127)) << 23);     // 2^(14 - floor(log2 max))
-        down[blockIdx.x] = plain ? 1.f : __uint_as_float((uint32_t)(127 - 14 + (eb - 127)) << 23);   // its inverse
+        const float2 sc = row_scale_pair(ab);
+        up[blockIdx.x] = sc.x;
+        down[blockIdx.x] = sc.y;
     }
 }
 
@@ -218,57 +257,9 @@ __global__ void __launch_bounds__(256) x_frag_kernel(const __grid_constant__ XFr
             }
         }
         rows_s[threadIdx.x] = r;
-        up_s[threadIdx.x] = (r >= 0 && a.up != nullptr) ? a.up[r] : 0.f;
+        up_s[threadIdx.x] = r >= 0 ? a.up[r] : 0.f;
     }
     __syncthreads();
-    if (a.up == nullptr) {   // no scale pass before this kernel: every CTA takes the rows' largest magnitudes itself, a warp per row
-        const int lane = threadIdx.x & 31;
-        for (int i = threadIdx.x >> 5; i < MB; i += (int)(blockDim.x >> 5)) {
-            const int r = rows_s[i];
-            if (r < 0) continue;
-            uint32_t ab = 0u;   // largest magnitude as float bits (orders like the value; NaN and infinity are largest)
-            if (a.x_f32) {
-                const float* row = static_cast<const float*>(a.x) + (size_t)r * a.k;
-                int j0 = 0;
-                if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {   // 16-byte loads over the aligned part
-                    const int nv = a.k >> 2;
-                    for (int j = lane; j < nv; j += 32) {
-                        const float4 v = __ldg(reinterpret_cast<const float4*>(row) + j);
-                        ab = max(max(ab, __float_as_uint(fabsf(v.x))), max(__float_as_uint(fabsf(v.y)), max(__float_as_uint(fabsf(v.z)), __float_as_uint(fabsf(v.w)))));
-                    }
-                    j0 = nv << 2;
-                }
-                for (int j = j0 + lane; j < a.k; j += 32) ab = max(ab, __float_as_uint(fabsf(row[j])));
-            } else {
-                const __nv_bfloat16* row = static_cast<const __nv_bfloat16*>(a.x) + (size_t)r * a.k;
-                int j0 = 0;
-                if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {   // eight bf16 per load: magnitude bits compare like the values
-                    const int nv = a.k >> 3;
-                    uint32_t hi = 0u, lo = 0u;
-                    for (int j = lane; j < nv; j += 32) {
-                        const uint4 v = __ldg(reinterpret_cast<const uint4*>(row) + j);
-                        const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            hi = max(hi, w4[i] & 0x7FFF0000u);
-                            lo = max(lo, (w4[i] << 16) & 0x7FFF0000u);
-                        }
-                    }
-                    ab = max(hi, lo);
-                    j0 = nv << 3;
-                }
-                for (int j = j0 + lane; j < a.k; j += 32) ab = max(ab, __float_as_uint(fabsf(__bfloat162float(row[j]))));
-            }
-            for (int o = 16; o > 0; o >>= 1) ab = max(ab, __shfl_xor_sync(0xffffffffu, ab, o));
-            if (lane == 0) {
-                const int eb = (int)(ab >> 23);
-                const bool plain = eb == 0 || eb == 255;
-                up_s[i] = plain ? 1.f : __uint_as_float((uint32_t)(127 + 14 - (eb - 127)) << 23);
-                if (blockIdx.x == 0) a.down_out[r] = plain ? 1.f : __uint_as_float((uint32_t)(127 - 14 + (eb - 127)) << 23);
-            }
-        }
-        __syncthreads();
-    }
     uint2* dst = a.out + (size_t)t * a.tile_stride + (size_t)seg * 4 * T * a.nt * 32;
     for (int idx = threadIdx.x; idx < 4 * T * a.nt * 32; idx += blockDim.x) {
         const int lane = idx & 31, rest = idx >> 5, nt_i = rest % a.nt, j = rest / a.nt;
@@ -334,14 +325,9 @@ void launch_x_frags(XFragArgs fa, int in_rows, int tiles, int max_nchunks, void*
     cfg.stream = s;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (tiles > 1 || max_nchunks > 24) {   // rows shared by many tiles or by many chunk CTAs: their scales once, in a pass of their own
-        if (fa.x_f32) MFQB_CUDA(cudaLaunchKernelEx(&cfg, x_row_scale_kernel<float>, static_cast<const float*>(fa.x), fa.k, up, dn));
-        else MFQB_CUDA(cudaLaunchKernelEx(&cfg, x_row_scale_kernel<__nv_bfloat16>, static_cast<const __nv_bfloat16*>(fa.x), fa.k, up, dn));
-        fa.up = up;
-    } else {           // one tile: the fragment kernel's CTAs find the scales themselves
-        fa.up = nullptr;
-        fa.down_out = dn;
-    }
+    if (fa.x_f32) MFQB_CUDA(cudaLaunchKernelEx(&cfg, x_row_scale_kernel<float>, static_cast<const float*>(fa.x), fa.k, up, dn));
+    else MFQB_CUDA(cudaLaunchKernelEx(&cfg, x_row_scale_kernel<__nv_bfloat16>, static_cast<const __nv_bfloat16*>(fa.x), fa.k, up, dn));
+    fa.up = up;
     fa.out = frags;
     cfg.gridDim = dim3((unsigned)max_nchunks, (unsigned)tiles);
     cfg.blockDim = dim3(256);

@@ -34,8 +34,7 @@ namespace mfqb {
 struct XFragArgs {
     const void* x;        // [in_rows][k] bf16 or float32
     int x_f32, k;
-    const float* up;      // scale of every source row, or nullptr: the kernel computes them (and writes the inverses to down_out)
-    float* down_out;
+    const float* up;      // scale of every source row
     uint2* out;
     size_t tile_stride;   // 8-byte units
     int nt, m;

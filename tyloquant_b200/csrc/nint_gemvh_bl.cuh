@@ -172,14 +172,30 @@ __device__ __forceinline__ void gemvh_bl_body(const GemvArgsB& a, const NintDevB
             __half2 d_lo[2], d_hi[2], nm_lo[2], nm_hi[2];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                float ss[4], sm[4];
-                C::scales(sc[f][h], ctx, ss, sm);
-                const float dl = kGemvhWeightScale * f_lo.x * (odd ? ss[1] : ss[0]), dh = kGemvhWeightScale * f_hi.x * (odd ? ss[3] : ss[2]);
+                float s_lo, s_hi, m_lo = 0.f, m_hi = 0.f;   // sub-scale and sub-min of rows q, q+8 for this lane's group
+                if constexpr (!C::A_SIGNED && C::SW == 2) {
+                    // scalar codes: word 0 holds the four sub-scale bytes (row q even, odd group; row q+8 even, odd), word 1 the sub-mins
+                    const uint32_t sh = odd ? 8u : 0u;
+                    s_lo = (float)((sc[f][h][0] >> sh) & 0xFFu);
+                    s_hi = (float)((sc[f][h][0] >> (sh + 16u)) & 0xFFu);
+                    m_lo = (float)((sc[f][h][1] >> sh) & 0xFFu);
+                    m_hi = (float)((sc[f][h][1] >> (sh + 16u)) & 0xFFu);
+                } else {
+                    float ss[4], sm[4];
+                    C::scales(sc[f][h], ctx, ss, sm);
+                    s_lo = odd ? ss[1] : ss[0];
+                    s_hi = odd ? ss[3] : ss[2];
+                    if constexpr (C::HAS_MIN) {
+                        m_lo = odd ? sm[1] : sm[0];
+                        m_hi = odd ? sm[3] : sm[2];
+                    }
+                }
+                const float dl = kGemvhWeightScale * f_lo.x * s_lo, dh = kGemvhWeightScale * f_hi.x * s_hi;
                 d_lo[h] = __float2half2_rn(dl);
                 d_hi[h] = __float2half2_rn(dh);
                 if constexpr (C::HAS_MIN) {
-                    nm_lo[h] = __float2half2_rn(fmaf(dl, (float)C::QMID, -kGemvhWeightScale * f_lo.y * (odd ? sm[1] : sm[0])));
-                    nm_hi[h] = __float2half2_rn(fmaf(dh, (float)C::QMID, -kGemvhWeightScale * f_hi.y * (odd ? sm[3] : sm[2])));
+                    nm_lo[h] = __float2half2_rn(fmaf(dl, (float)C::QMID, -kGemvhWeightScale * f_lo.y * m_lo));
+                    nm_hi[h] = __float2half2_rn(fmaf(dh, (float)C::QMID, -kGemvhWeightScale * f_hi.y * m_hi));
                 } else {
                     nm_lo[h] = nm_hi[h] = __float2half2_rn(0.f);
                 }
@@ -232,7 +248,7 @@ __device__ __forceinline__ void gemvh_bl_body(const GemvArgsB& a, const NintDevB
 }
 
 template <class C, int NT>
-__global__ void __launch_bounds__(256, C::MIN_CTAS < 2 ? 1 : 2) gemvh_bl_kernel(const GemvArgsB a) {
+__global__ void __launch_bounds__(256, C::MIN_CTAS < 2 ? 1 : (NT == 1 ? 3 : 2)) gemvh_bl_kernel(const GemvArgsB a) {
     extern __shared__ __align__(16) unsigned char smem[];
     gemvh_bl_body<C, NT>(a, a.w, smem);
 }
