@@ -204,11 +204,13 @@ __global__ void __launch_bounds__(1024) route_plan_small_kernel(const int32_t* _
                                                                 int32_t* __restrict__ expert_bounds, int32_t* __restrict__ tile_bounds,
                                                                 int32_t* __restrict__ pair_order) {
     __shared__ int bounds[kRoutePlanSmallExperts + 1];
+    __shared__ int ids_s[kRoutePlanSmallPairs];   // the placement below walks the ids once per expert: from shared memory
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     for (int e = tid; e <= experts; e += blockDim.x) bounds[e] = 0;
     __syncthreads();
     for (int p = tid; p < pairs; p += blockDim.x) {
         const int e = ids[p];
+        ids_s[p] = e;
         if (e >= 0 && e < experts) atomicAdd(&bounds[e + 1], 1);
     }
     __syncthreads();
@@ -230,7 +232,7 @@ __global__ void __launch_bounds__(1024) route_plan_small_kernel(const int32_t* _
         int at = bounds[e];
         for (int base = 0; base < pairs; base += 32) {
             const int p = base + lane;
-            const bool hit = p < pairs && ids[p] == e;
+            const bool hit = p < pairs && ids_s[p] == e;
             const unsigned m = __ballot_sync(0xffffffffu, hit);
             if (hit) pair_order[at + __popc(m & ((1u << lane) - 1u))] = p;
             at += __popc(m);
