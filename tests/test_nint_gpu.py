@@ -246,3 +246,35 @@ def test_gated_projection_with_interleaved_row_blocks(profile):
             assert got.shape == want.shape
             assert rel_l2(got, want) <= REL_L2, (profile, n, k, m, rel_l2(got, want))
         w.free()
+
+
+@pytest.mark.parametrize("pinned", [True, False])
+def test_host_buffer_list_call_matches_single_products(pinned):
+    """mfqb_mul_mat_host_multi: a list of (weight, x, y) in host memory, one wait.  Consecutive products of one
+    shape class on the same host row share a staged copy and a launch (q, k, v of a block); the others run one
+    by one -- every result must equal the product of its own device call."""
+    import ctypes as C
+
+    from tyloquant_b200._capi import BF16 as BF, F32 as FF, check, lib
+    k = 1000
+    specs = [(3, 24, 5, 64), (3, 24, 5, 200), (3, 24, 5, 48), (4, 32, 6, 96), (3, 24, 5, 80), (3, 24, 5, 32)]
+    ws = [QuantWeight.from_blob(f"NINT{b}", encode.random_nint_blob(n, k, b, gs, sb, seed=70 + i)) for i, (b, gs, sb, n) in enumerate(specs)]
+    rng = np.random.default_rng(71)
+    xa = torch.from_numpy(encode.bf16_bits(encode.bf16_round(rng.standard_normal((1, k), dtype=np.float32))).astype(np.int16))
+    xb = torch.from_numpy(encode.bf16_bits(encode.bf16_round(rng.standard_normal((1, k), dtype=np.float32))).astype(np.int16))
+    if pinned:
+        xa, xb = xa.pin_memory(), xb.pin_memory()
+    x_of = [xa, xa, xa, xa, xb, xa]   # a run of three, a different class on the same row, another row, the first row again
+    ys = [torch.empty((1, n), dtype=torch.float32) for (_, _, _, n) in specs]
+    if pinned:
+        ys = [y.pin_memory() for y in ys]
+    h_arr = (C.c_void_p * len(ws))(*[w._h for w in ws])
+    x_arr = (C.c_void_p * len(ws))(*[x.data_ptr() for x in x_of])
+    y_arr = (C.c_void_p * len(ws))(*[y.data_ptr() for y in ys])
+    check(lib.mfqb_mul_mat_host_multi(h_arr, len(ws), x_arr, 1, y_arr, FF))
+    for w, x, y in zip(ws, x_of, ys):
+        xd = x.cuda().view(torch.bfloat16)
+        want = w.matmul(xd, out_dtype=torch.float32).cpu().numpy()
+        assert rel_l2(y.numpy(), want) < 1e-5
+    for w in ws:
+        w.free()

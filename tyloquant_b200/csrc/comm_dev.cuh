@@ -24,13 +24,16 @@ struct PeerReduce {
     int* status;   // host-visible word: set to MFQB_ERR_TIMEOUT when a wait expires
 };
 
+// A (value, call number) pair travels as ONE 64-bit relaxed system-scope access: single-copy atomic by the
+// memory model, so a reader never sees the value of one call with the number of another.
 __device__ __forceinline__ void st_pair_sys(uint2* p, unsigned a, unsigned b) {
-    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(a), "r"(b) : "memory");
+    const unsigned long long v = (unsigned long long)a | ((unsigned long long)b << 32);
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 __device__ __forceinline__ uint2 ld_pair_sys(const uint2* p) {
-    uint2 v;
-    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-    return v;
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return make_uint2((unsigned)v, (unsigned)(v >> 32));
 }
 __device__ __forceinline__ unsigned long long global_timer_ns() {
     unsigned long long t;

@@ -568,6 +568,17 @@ static void mul_mat_host_impl(const mfqb_weight* const* ws, int count, const voi
                             cudaHostGetDevicePointer(&x_map, const_cast<void*>(xs[i]), 0) == cudaSuccess &&
                             cudaHostGetDevicePointer(&y_map, ys[i], 0) == cudaSuccess;
         if (!mapped) (void)cudaGetLastError();   // not an error: the buffers are simply pageable
+        if (i > 0 && xs[i] == xs[i - 1] && ws[i]->info.k == ws[i - 1]->info.k) {   // the same host rows as the previous product: staged once
+            xd[i] = xd[i - 1];
+            if (!mapped) {
+                if (!any_copy_back && dy.bytes < y_total) dy.alloc(y_total + y_total / 2);
+                any_copy_back = true;
+                copy_back.emplace_back(y_off, i);
+            }
+            yd[i] = mapped ? y_map : static_cast<void*>(static_cast<char*>(dy.p) + y_off);
+            y_off += (yb + 255) / 256 * 256;
+            continue;
+        }
         xd[i] = static_cast<char*>(dx.p) + x_off;
         if (mapped) {
             table.src[pending] = static_cast<const uint32_t*>(x_map);
@@ -586,9 +597,18 @@ static void mul_mat_host_impl(const mfqb_weight* const* ws, int count, const voi
         y_off += (yb + 255) / 256 * 256;
     }
     flush();
-    for (int i = 0; i < count; ++i) {
-        const int rc = mfqb_mul_mat(ws[i], xd[i], m, yd[i], y_dtype, s);
+    // consecutive single-row products of one shape class on the same activations (q, k, v of a block) share a launch
+    auto same_class = [](const mfqb_weight* a, const mfqb_weight* b) {
+        return a->family == MFQB_FAMILY_NINT && b->family == MFQB_FAMILY_NINT && !a->nint.table && !b->nint.table && a->nint.bits == b->nint.bits &&
+               a->nint.gs == b->nint.gs && a->nint.k == b->nint.k && a->nint.rec_words == b->nint.rec_words;
+    };
+    for (int i = 0; i < count;) {
+        int run = 1;
+        if (m == 1)
+            while (i + run < count && run < 8 && xs[i + run] == xs[i] && same_class(ws[i], ws[i + run])) ++run;
+        const int rc = run > 1 ? mfqb_mul_mat_multi(ws + i, run, xd[i], yd.data() + i, y_dtype, s) : mfqb_mul_mat(ws[i], xd[i], m, yd[i], y_dtype, s);
         if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
+        i += run;
     }
     for (const auto& cb : copy_back)
         MFQB_CUDA(cudaMemcpyAsync(ys[cb.second], static_cast<char*>(dy.p) + cb.first, (size_t)m * ws[cb.second]->info.n * ysz,
