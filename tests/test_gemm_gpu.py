@@ -36,7 +36,13 @@ def test_tile_gemm_matches_oracle(profile):
             assert _status() == 0
             assert rel_l2(y32, y_ref) <= REL_L2, (profile, n, k, m)
             y16 = w.matmul(bf16_tensor(x)).float().cpu().numpy()
-            assert rel_l2(y16, O.bf16_round(y_ref)) <= REL_L2
+            # bf16 output: the same criterion as for the batched GEMV -- per element one bf16 step of the oracle value
+            # plus the accuracy bound (weights rounded to f16 once: a few 1e-4 relative L2, single elements a few times
+            # that), and the L2 distance that rounding an exact result to bf16 allows
+            step = np.exp2(np.floor(np.log2(np.maximum(np.abs(y_ref), 1e-30))) - 7)
+            rms = float(np.sqrt(np.mean(np.square(y_ref, dtype=np.float64))))
+            assert np.all(np.abs(y16 - O.bf16_round(y_ref)) <= step + 2 * REL_L2 * rms)
+            assert rel_l2(y16, y_ref) <= 3e-3
             assert np.abs(y16 - y_ref).max() <= MAX_ABS_BF16
         w.free()
 

@@ -52,6 +52,9 @@ struct GemmArgs {
 };
 
 constexpr int kGemmProducerWarps = 16;
+// The f16 weights carry a factor 2^10 (taken out of the accumulators in the epilogue): f16 keeps all its bits for
+// quantisation steps down to 2^-24 and represents weights up to 64.
+constexpr float kGemmWeightScale = 1024.f, kGemmWeightUndo = 1.f / 1024.f;
 constexpr int kGemmThreads = (kGemmProducerWarps + 2) * 32;   // + mma warp + x loader warp
 
 // Two rings, both counted in atoms of 64 columns of K, each atom a K-major tile with the 128-byte
@@ -145,6 +148,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) nint_gemm_tc_kernel(const Gem
             for (int j = 0; j < 4; ++j) nsc[j] = __ldg(rec + (WC + (j >> 1)) * 32 + 4 * q + 2 * f + (j & 1));
         };
         if (rb_valid) fetch(0);
+        // where each of the lane's registers of a chunk goes: atom (k / 64) and swizzled byte offset inside the atom
+        uint32_t slot_of[4 * T];
+#pragma unroll
+        for (int t = 0; t < T; ++t)
+#pragma unroll
+            for (int aa = 0; aa < 4; ++aa) {
+                const int row = rbl * 16 + q + 8 * (aa & 1);
+                const int k = (4 * f + 2 * (aa >> 1) + (c >> 1)) * GS + 8 * t + 4 * (c & 1), atom = k >> 6, kk = k & 63;
+                slot_of[t * 4 + aa] = ((uint32_t)atom << 14) | (uint32_t)(row * 128 + (((kk >> 3) ^ q) << 4) + (kk & 7) * 2);
+            }
         for (int ch = 0; ch < w.nchunks && alive; ++ch) {
             // acquire the chunk's stages
 #pragma unroll
@@ -165,29 +178,36 @@ __global__ void __launch_bounds__(kGemmThreads, 1) nint_gemm_tc_kernel(const Gem
                 const float2 f_lo = __half22float2(*reinterpret_cast<const __half2*>(&an_lo));   // (ns, nm)
                 const float2 f_hi = __half22float2(*reinterpret_cast<const __half2*>(&an_hi));
                 // register a of a step: row q + 8(a&1), group 4f + 2(a>>1) + (c>>1); its scale bytes sit in
-                // word (a>>1) of the pair fetched above, byte 2(a&1) + (c>>1)
-                float d[4], mn[4];
+                // word (a>>1) of the pair fetched above, byte 2(a&1) + (c>>1).  The weight is built in f16:
+                // d' (q - q_mid) + n' with d' = 2^10 d and n' = -(2^10 m - d' q_mid) rounded to f16 (the factor
+                // 2^10 keeps small quantisation steps normal numbers; the epilogue takes it out again).
+                __half2 d2[4], n2[4];
 #pragma unroll
                 for (int aa = 0; aa < 4; ++aa) {
                     const int sh = 8 * (2 * (aa & 1) + (c >> 1));
                     const float ss = (float)((sc[aa >> 1] >> sh) & 0xFF), sm = (float)((sc[2 + (aa >> 1)] >> sh) & 0xFF);
-                    d[aa] = ((aa & 1) ? f_hi.x : f_lo.x) * ss;
-                    mn[aa] = ((aa & 1) ? f_hi.y : f_lo.y) * sm;
+                    const float dd = kGemmWeightScale * ((aa & 1) ? f_hi.x : f_lo.x) * ss;
+                    d2[aa] = __float2half2_rn(dd);
+                    n2[aa] = __float2half2_rn(fmaf(dd, (float)(1 << (BITS - 1)), -kGemmWeightScale * ((aa & 1) ? f_hi.y : f_lo.y) * sm));
                 }
+                const __half2 bias = __float2half2_rn(1024.f + (float)(1 << (BITS - 1)));
+                const int st_base = (ch * ATOMS) % NS;
 #pragma unroll
                 for (int t = 0; t < T; ++t) {
 #pragma unroll
                     for (int aa = 0; aa < 4; ++aa) {
                         const uint32_t v = BU::at(qw, r0 + t * 4 + aa);
-                        const int row = rbl * 16 + q + 8 * (aa & 1);
-                        const __half2 h01 = __floats2half2_rn(fmaf(d[aa], (float)(v & 0xFF), -mn[aa]), fmaf(d[aa], (float)((v >> 8) & 0xFF), -mn[aa]));
-                        const __half2 h23 = __floats2half2_rn(fmaf(d[aa], (float)((v >> 16) & 0xFF), -mn[aa]), fmaf(d[aa], (float)(v >> 24), -mn[aa]));
-                        const int k = (4 * f + 2 * (aa >> 1) + (c >> 1)) * GS + 8 * t + 4 * (c & 1), atom = k >> 6, kk = k & 63;
-                        unsigned char* at = tiles + ((ch * ATOMS + atom) % NS) * stage_bytes;
-                        uint2 pk;
-                        pk.x = *reinterpret_cast<const uint32_t*>(&h01);
-                        pk.y = *reinterpret_cast<const uint32_t*>(&h23);
-                        *reinterpret_cast<uint2*>(at + row * 128 + (((kk >> 3) ^ q) << 4) + (kk & 7) * 2) = pk;
+                        // a code byte under the exponent byte 0x64 is the f16 1024 + q
+                        const uint32_t lo = __byte_perm(v, 0x64646464u, 0x4140), hi = __byte_perm(v, 0x64646464u, 0x4342);
+                        const __half2 h01 = __hfma2(__hsub2(*reinterpret_cast<const __half2*>(&lo), bias), d2[aa], n2[aa]);
+                        const __half2 h23 = __hfma2(__hsub2(*reinterpret_cast<const __half2*>(&hi), bias), d2[aa], n2[aa]);
+                        const uint32_t pk = slot_of[t * 4 + aa];   // atom of the chunk (high bits) and byte offset inside it, fixed per lane
+                        int st = st_base + (int)(pk >> 14);
+                        if (st >= NS) st -= NS;
+                        uint2 out;
+                        out.x = *reinterpret_cast<const uint32_t*>(&h01);
+                        out.y = *reinterpret_cast<const uint32_t*>(&h23);
+                        *reinterpret_cast<uint2*>(tiles + st * stage_bytes + (pk & 0x3FFFu)) = out;
                     }
                 }
             } else if (f == 0) {
@@ -276,7 +296,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) nint_gemm_tc_kernel(const Gem
                     for (int i = 0; i < 32; ++i) {
                         if (cb + i < ncols) {
                             const size_t out_row = grouped ? (size_t)a.pair_order[tok0 + cb + i] : (size_t)(tok0 + cb + i);
-                            const float v = __uint_as_float(r[i]);
+                            const float v = __uint_as_float(r[i]) * kGemmWeightUndo;
                             if (a.y_dtype == 0 /* MFQB_F32 */) reinterpret_cast<float*>(a.y)[out_row * ldy + n] = v;
                             else reinterpret_cast<__nv_bfloat16*>(a.y)[out_row * ldy + n] = __float2bfloat16_rn(v);
                         }
@@ -295,6 +315,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) nint_gemm_tc_kernel(const Gem
 
 // Dynamic shared memory a tile kernel may plan with: 227 KB per CTA less the alignment slack and the barriers.
 constexpr size_t kGemmSmemBudget = 227 * 1024 - 1024 - 512;
+// Measurement switch (mfqb_tune "gemm_plan"): 0 = by shape, 1 = 32-column activation stages and a two-chunk weight ring.
+extern int g_gemm_plan_choice;
 struct GemmPlan {
     int bn, stages, xstages, xcols, grid_x, grid_y;
     size_t smem;
@@ -313,7 +335,7 @@ inline GemmPlan plan_nint_gemm(const NintDevB& w, int m) {
     // would not fit otherwise.
     auto stages_for = [](int bn_, int xcols, int xst) { return std::min(8, (int)((kGemmSmemBudget - (size_t)xst * bn_ * xcols * 2) / (128 * 128))); };
     int bn = 512, xcols = 64, xst = 2;
-    if (atoms > 5) {   // (a six-atom chunk fits beside two 64-column stages, but measured slower than the 32-column form)
+    if (atoms > 5 || g_gemm_plan_choice == 1) {   // (a six-atom chunk fits beside two 64-column stages, but measured slower than the 32-column form)
         if (stages_for(512, 32, 3) >= atoms) { xcols = 32; xst = 3; }
         else {
             bn = 256;

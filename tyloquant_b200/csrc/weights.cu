@@ -239,6 +239,7 @@ size_t gemvs_fix_bytes(int device);
 void launch_swiglu(const void* gate_up, int in_dtype, int rows, int f, void* hidden, cudaStream_t s);
 bool nint_bl_gemvh_supported(const NintDevB& w, int rows_per_launch);
 int g_moe_f16_from_x2 = 4;   // see mfqb_tune
+int g_gemm_plan_choice = 0;   // see mfqb_tune
 void launch_bl_gemv_multi(const NintDevB* ws, void* const* ys, int count, const void* x, int y_dtype, int device, cudaStream_t s);
 bool launch_bl_gemvs(const NintDevB& w, const void* x, int x_dtype, void* y, int y_dtype, int device, void* fix, int* error, cudaStream_t s);
 }
@@ -643,6 +644,7 @@ int mfqb_tune(const char* key, int value) {
         if (!key) fail(MFQB_ERR_ARG, "mfqb_tune: null key");
         if (std::string(key) == "gemv1_kernel" && value >= 0 && value <= 2) g_gemv1_choice = value;
         else if (std::string(key) == "moe_f16_tiles_from_x2" && value >= 2 && value <= 1000000) g_moe_f16_from_x2 = value;
+        else if (std::string(key) == "gemm_plan" && value >= 0 && value <= 1) g_gemm_plan_choice = value;
         else fail(MFQB_ERR_ARG, "mfqb_tune: unknown key '%s' or value %d out of range", key, value);
     });
 }
