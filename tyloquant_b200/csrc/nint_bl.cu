@@ -595,6 +595,7 @@ void launch_nint_bl_gemv_routed(GemvArgsB a, int pairs, int device, cudaStream_t
     p.smem = gemv1_smem(w, a.rb_per_cta, 8);
     p.grid = splits;
     p.grid_y = pairs;
+    p.passes = -3;
     dispatch(a, p, s, "routed GEMV");
 }
 

@@ -489,7 +489,9 @@ __device__ __forceinline__ void routed_absent_pair(const GemvArgsB& a, int pair)
 // 16-byte asynchronous copies; the first S items are requested before the kernel waits for its
 // predecessor in the stream, since weights are constants.  The activation row is read straight
 // from global memory, one chunk ahead, and quantised in registers by the warp that needs it.
-template <class C, int XMODE = 0>
+// DENSE: the kernel serves plain products only (no routing table, no route sum, every warp its own chunks);
+// the routed launches of the expert path compile the general form.
+template <class C, int XMODE = 0, bool DENSE = false>
 __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB& w, unsigned char* smem) {
     constexpr int G = kChunkGroupsB, T = C::T, WC = C::WC, SW = C::SW, REC = (WC + SW) * 32;
     constexpr int S = gemv1_bl_stages(REC);
@@ -508,7 +510,8 @@ __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB
     int rb_base = 0, rb_total = w.nrb;
     const __nv_bfloat16* xrow = a.x;
     size_t y_off = 0;
-    if (a.route_ids != nullptr) {
+    const bool routed = !DENSE && a.route_ids != nullptr;
+    if (routed) {
         pdl_wait_b();   // the routing table comes from the previous kernel
         const int pair = blockIdx.y, e = a.route_ids[pair];
         if (e < 0 || a.expert_pool[e] != a.pool) return;
@@ -526,7 +529,7 @@ __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB
         split_row_blocks(blockIdx.x, gridDim.x, rb_total, rbl0, nrb);
     }
     const int rb0 = rb_base + rbl0;
-    const int row_limit = a.route_ids != nullptr ? a.ldy : w.n;   // rows this problem has (an expert's rows are padded to whole blocks)
+    const int row_limit = routed ? a.ldy : w.n;   // rows this problem has (an expert's rows are padded to whole blocks)
 
     // items of this warp, chunk-major: chunk = seg0, seg0 + cw, ...; inside a chunk the row-blocks
     // rg, rg + rgroups, ... of the CTA.  Rows with at least as many chunks as the CTA has warps give every
@@ -535,7 +538,7 @@ __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB
     // Two cursors walk the sequence (issue runs S items ahead).
     int cw = nwarps, rgroups = 1, seg0 = warp, rg = 0;
     int my_segs, my_rbs = nrb;
-    if (w.nchunks < nwarps) {   // every warp of a group has one chunk
+    if (!DENSE && w.nchunks < nwarps) {   // every warp of a group has one chunk
         cw = w.nchunks;
         rgroups = nwarps / cw;
         rg = warp / cw;
@@ -592,7 +595,7 @@ __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB
     // float32 rows: [rows, k], or the pair's gate|up products [pairs, 2k]
     const float* xrow_f = nullptr;
     if constexpr (XMODE != 0) {
-        const size_t xr = a.route_ids != nullptr ? (size_t)(a.x_per_pair ? blockIdx.y : blockIdx.y / a.routes) : 0;
+        const size_t xr = routed ? (size_t)(a.x_per_pair ? blockIdx.y : blockIdx.y / a.routes) : 0;
         xrow_f = reinterpret_cast<const float*>(a.x) + xr * (XMODE == 2 ? 2 : 1) * w.k;
     }
     if (n_mine > 0) {
@@ -719,18 +722,26 @@ __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB
             float v = ypart[i];
             for (int cp = 1; cp < ycopies; ++cp) v += ypart[cp * ystride + i];
             v *= kXScaleUndo;
-            if (a.route_w != nullptr) a.pair_out[y_off + row] = v;
+            if (!DENSE && a.route_w != nullptr) a.pair_out[y_off + row] = v;
             else if (a.y_dtype == 0 /* MFQB_F32 */) reinterpret_cast<float*>(a.y)[y_off + row] = v;
             else reinterpret_cast<__nv_bfloat16*>(a.y)[y_off + row] = __float2bfloat16_rn(v);
         }
     }
-    if (a.route_w != nullptr) routed_finish_token(a, blockIdx.y, rbl0, nrb, row_limit);
+    if (!DENSE && a.route_w != nullptr) routed_finish_token(a, blockIdx.y, rbl0, nrb, row_limit);
 }
 
 template <class C>
 __global__ void __launch_bounds__(C::MIN_CTAS >= 3 ? 384 : 256, C::MIN_CTAS >= 3 ? 2 : C::MIN_CTAS) gemv1_bl_kernel(const GemvArgsB a) {
     extern __shared__ __align__(16) unsigned char smem[];
-    gemv1_bl_body<C>(a, a.w, smem);
+    gemv1_bl_body<C, 0, true>(a, a.w, smem);
+}
+
+// The general form for one cohort of an expert record: blockIdx.y is a (token, route) pair (per-cohort launches of
+// records whose cohorts the all-cohort kernel does not hold).
+template <class C>
+__global__ void __launch_bounds__(C::MIN_CTAS >= 3 ? 384 : 256, C::MIN_CTAS >= 3 ? 2 : C::MIN_CTAS) gemv1_bl_routed_kernel(const GemvArgsB a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    gemv1_bl_body<C, 0, false>(a, a.w, smem);
 }
 
 // x is the float32 gate|up row [2k] of a gated FFN: the SwiGLU activation is computed as the row is
@@ -738,7 +749,7 @@ __global__ void __launch_bounds__(C::MIN_CTAS >= 3 ? 384 : 256, C::MIN_CTAS >= 3
 template <class C>
 __global__ void __launch_bounds__(C::MIN_CTAS >= 3 ? 384 : 256, C::MIN_CTAS >= 3 ? 2 : C::MIN_CTAS) gemv1_bl_swiglu_kernel(const GemvArgsB a) {
     extern __shared__ __align__(16) unsigned char smem[];
-    gemv1_bl_body<C, 2>(a, a.w, smem);
+    gemv1_bl_body<C, 2, true>(a, a.w, smem);
 }
 
 // Several weights that share x, the code width, the group size and k (a.w describes their common
@@ -754,7 +765,7 @@ __global__ void __launch_bounds__(C::MIN_CTAS >= 3 ? 384 : 256, C::MIN_CTAS >= 3
     b.w.n = e.n;
     b.w.nrb = e.nrb;
     b.y = e.y;
-    gemv1_bl_body<C>(b, b.w, smem);
+    gemv1_bl_body<C, 0, true>(b, b.w, smem);
 }
 
 }  // namespace mfqb
