@@ -491,7 +491,8 @@ __device__ __forceinline__ void routed_absent_pair(const GemvArgsB& a, int pair)
 // from global memory, one chunk ahead, and quantised in registers by the warp that needs it.
 // DENSE: the kernel serves plain products only (no routing table, no route sum, every warp its own chunks);
 // the routed launches of the expert path compile the general form.
-template <class C, int XMODE = 0, bool DENSE = false>
+// PLAIN_OUT (with DENSE): the rows are written as they are -- no sum over ranks, no gated epilogue.
+template <class C, int XMODE = 0, bool DENSE = false, bool PLAIN_OUT = false>
 __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB& w, unsigned char* smem) {
     constexpr int G = kChunkGroupsB, T = C::T, WC = C::WC, SW = C::SW, REC = (WC + SW) * 32;
     constexpr int S = gemv1_bl_stages(REC);
@@ -521,7 +522,7 @@ __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB
         y_off = (size_t)pair * a.ldy;
     }
     int rbl0, nrb;
-    if (a.glu) {   // whole (gate, up) pairs of row-blocks per CTA
+    if (!PLAIN_OUT && a.glu) {   // whole (gate, up) pairs of row-blocks per CTA
         split_row_blocks(blockIdx.x, gridDim.x, rb_total >> 1, rbl0, nrb);
         rbl0 *= 2;
         nrb *= 2;
@@ -672,7 +673,7 @@ __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB
     }
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     __syncthreads();
-    if (a.reduce.world > 0) {
+    if (!PLAIN_OUT && a.reduce.world > 0) {
         // every thread owns one row of the CTA: it pushes this rank's partial value into slot `rank` of
         // every rank and sums the ranks' values of that row (the peers' CTAs with this block index
         // own the same rows: same shape, same grid)
@@ -697,7 +698,7 @@ __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB
         peer_call_done(pr, seq);
         return;
     }
-    if (a.glu) {
+    if (!PLAIN_OUT && a.glu) {
         const int half = w.n >> 1;
         for (int i = tid; i < nrb * 8; i += blockDim.x) {
             const int pr = i >> 4, r = i & 15, row = (rbl0 >> 1) * 16 + i;
@@ -733,7 +734,15 @@ __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB
 template <class C>
 __global__ void __launch_bounds__(C::MIN_CTAS >= 3 ? 384 : 256, C::MIN_CTAS >= 3 ? 2 : C::MIN_CTAS) gemv1_bl_kernel(const GemvArgsB a) {
     extern __shared__ __align__(16) unsigned char smem[];
-    gemv1_bl_body<C, 0, true>(a, a.w, smem);
+    gemv1_bl_body<C, 0, true, true>(a, a.w, smem);
+}
+
+// The same with the epilogues that do more than write the rows: the sum over ranks (row-parallel shards) and
+// the gated activation over (gate, up) pairs of row-blocks.
+template <class C>
+__global__ void __launch_bounds__(C::MIN_CTAS >= 3 ? 384 : 256, C::MIN_CTAS >= 3 ? 2 : C::MIN_CTAS) gemv1_bl_epi_kernel(const GemvArgsB a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    gemv1_bl_body<C, 0, true, false>(a, a.w, smem);
 }
 
 // The general form for one cohort of an expert record: blockIdx.y is a (token, route) pair (per-cohort launches of
@@ -765,7 +774,7 @@ __global__ void __launch_bounds__(C::MIN_CTAS >= 3 ? 384 : 256, C::MIN_CTAS >= 3
     b.w.n = e.n;
     b.w.nrb = e.nrb;
     b.y = e.y;
-    gemv1_bl_body<C, 0, true>(b, b.w, smem);
+    gemv1_bl_body<C, 0, true, true>(b, b.w, smem);
 }
 
 }  // namespace mfqb
