@@ -492,7 +492,8 @@ __device__ __forceinline__ void routed_absent_pair(const GemvArgsB& a, int pair)
 // DENSE: the kernel serves plain products only (no routing table, no route sum, every warp its own chunks);
 // the routed launches of the expert path compile the general form.
 // PLAIN_OUT (with DENSE): the rows are written as they are -- no sum over ranks, no gated epilogue.
-template <class C, int XMODE = 0, bool DENSE = false, bool PLAIN_OUT = false>
+// ONE_RB (with PLAIN_OUT): the grid has one CTA per row-block (the 4096-row matrices): CTA b owns row-block b.
+template <class C, int XMODE = 0, bool DENSE = false, bool PLAIN_OUT = false, bool ONE_RB = false>
 __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB& w, unsigned char* smem) {
     constexpr int G = kChunkGroupsB, T = C::T, WC = C::WC, SW = C::SW, REC = (WC + SW) * 32;
     constexpr int S = gemv1_bl_stages(REC);
@@ -522,7 +523,10 @@ __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB
         y_off = (size_t)pair * a.ldy;
     }
     int rbl0, nrb;
-    if (!PLAIN_OUT && a.glu) {   // whole (gate, up) pairs of row-blocks per CTA
+    if constexpr (ONE_RB) {
+        rbl0 = blockIdx.x;
+        nrb = 1;
+    } else if (!PLAIN_OUT && a.glu) {   // whole (gate, up) pairs of row-blocks per CTA
         split_row_blocks(blockIdx.x, gridDim.x, rb_total >> 1, rbl0, nrb);
         rbl0 *= 2;
         nrb *= 2;
@@ -605,6 +609,7 @@ __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB
     }
 
     int seg = seg0, rbl = rg, stage = 0;
+    float sum_lo = 0.f, sum_hi = 0.f;
     for (int i = 0; i < n_mine; ++i) {
         if (seg != cur_seg) {
             cur_seg = seg;
@@ -658,7 +663,10 @@ __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB
         v_hi += __shfl_xor_sync(0xffffffffu, v_hi, 1);
         v_lo += __shfl_xor_sync(0xffffffffu, v_lo, 2);
         v_hi += __shfl_xor_sync(0xffffffffu, v_hi, 2);
-        if (c == 0) {
+        if constexpr (ONE_RB) {   // one row-block: the warp's items add up in registers
+            sum_lo += v_lo;
+            sum_hi += v_hi;
+        } else if (c == 0) {
             if (a.private_sums) {   // this warp's own copy: no other warp touches it
                 ymine[rbl * 16 + q] += v_lo;
                 ymine[rbl * 16 + q + 8] += v_hi;
@@ -670,6 +678,12 @@ __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB
         rbl += rgroups;
         if (rbl >= nrb) { rbl = rg; seg += cw; }
         if (++stage == S) stage = 0;
+    }
+    if constexpr (ONE_RB) {
+        if (c == 0 && n_mine > 0) {   // the launch gives this form per-warp copies of the sums
+            ymine[q] = sum_lo;
+            ymine[q + 8] = sum_hi;
+        }
     }
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     __syncthreads();
@@ -735,6 +749,13 @@ template <class C>
 __global__ void __launch_bounds__(C::MIN_CTAS >= 3 ? 384 : 256, C::MIN_CTAS >= 3 ? 2 : C::MIN_CTAS) gemv1_bl_kernel(const GemvArgsB a) {
     extern __shared__ __align__(16) unsigned char smem[];
     gemv1_bl_body<C, 0, true, true>(a, a.w, smem);
+}
+
+// One CTA per row-block (launched when the grid equals the number of row-blocks).
+template <class C>
+__global__ void __launch_bounds__(C::MIN_CTAS >= 3 ? 384 : 256, C::MIN_CTAS >= 3 ? 2 : C::MIN_CTAS) gemv1_bl_one_kernel(const GemvArgsB a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    gemv1_bl_body<C, 0, true, true, true>(a, a.w, smem);
 }
 
 // The same with the epilogues that do more than write the rows: the sum over ranks (row-parallel shards) and
