@@ -166,6 +166,7 @@ struct NintCodec {
     using BU = ByteUnit<BITS>;
     static constexpr int WC = BU::words_for(8 * T), SW = 2;
     static constexpr bool A_SIGNED = false, HAS_MIN = true, NEEDS_OWN_SCALE = false;
+    static constexpr bool PLAIN_FORM = true;   // plain products take the stripped kernels (see gemv1_bl_kernel)
     static constexpr int QMID = 1 << (BITS - 1);   // centre of the code range (the f16 kernel decodes d * (q - QMID) - (m - d * QMID))
     static constexpr int MIN_CTAS = WC > 48 ? 1 : (WC > 24 ? 2 : 3);
     struct Ctx {

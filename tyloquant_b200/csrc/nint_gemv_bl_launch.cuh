@@ -79,7 +79,7 @@ static cudaError_t launch_gemv_codec(const GemvArgsB& a, const GemvPlanB& p, cud
         case -2: return launch_kernel_pdl(gemv1_bl_swiglu_kernel<C>, a, p, stream);
         case -1: return p.multi ? launch_kernel_pdl(gemv1_bl_multi_kernel<C>, a, p, stream, *p.multi) : cudaErrorInvalidValue;
         case 0:
-            if (a.glu || a.reduce.world > 0) return launch_kernel_pdl(gemv1_bl_epi_kernel<C>, a, p, stream);
+            if (a.glu || a.reduce.world > 0 || !C::PLAIN_FORM) return launch_kernel_pdl(gemv1_bl_epi_kernel<C>, a, p, stream);
             if (a.route_ids == nullptr && p.grid_y == 1 && p.grid == a.w.nrb && a.private_sums) return launch_kernel_pdl(gemv1_bl_one_kernel<C>, a, p, stream);
             return launch_kernel_pdl(gemv1_bl_kernel<C>, a, p, stream);
         case 1: return launch_kernel_pdl(gemvn_bl_kernel<C, 1>, a, p, stream);
