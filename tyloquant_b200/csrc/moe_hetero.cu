@@ -42,13 +42,13 @@ __global__ void __launch_bounds__(256, 2) moe_hetero_gemv1_kernel(const __grid_c
     a.pool = pool;
     const NintDevB& w = h.pools[pool];
     switch (w.bits * 16 + w.t8) {
-        case 2 * 16 + 2: gemv1_bl_body<NintCodec<2, 2>, XMODE>(a, w, smem); break;
-        case 3 * 16 + 3: gemv1_bl_body<NintCodec<3, 3>, XMODE>(a, w, smem); break;
-        case 4 * 16 + 3: gemv1_bl_body<NintCodec<4, 3>, XMODE>(a, w, smem); break;
-        case 5 * 16 + 4: gemv1_bl_body<NintCodec<5, 4>, XMODE>(a, w, smem); break;
-        case 6 * 16 + 3: gemv1_bl_body<NintCodec<6, 3>, XMODE>(a, w, smem); break;
-        case 8 * 16 + 3: gemv1_bl_body<NintCodec<8, 3>, XMODE>(a, w, smem); break;
-        case 8 * 16 + 6: gemv1_bl_body<NintCodec<8, 6>, XMODE>(a, w, smem); break;
+        case 2 * 16 + 2: gemv1_bl_body<NintCodec<2, 2>, XMODE, false, true>(a, w, smem); break;
+        case 3 * 16 + 3: gemv1_bl_body<NintCodec<3, 3>, XMODE, false, true>(a, w, smem); break;
+        case 4 * 16 + 3: gemv1_bl_body<NintCodec<4, 3>, XMODE, false, true>(a, w, smem); break;
+        case 5 * 16 + 4: gemv1_bl_body<NintCodec<5, 4>, XMODE, false, true>(a, w, smem); break;
+        case 6 * 16 + 3: gemv1_bl_body<NintCodec<6, 3>, XMODE, false, true>(a, w, smem); break;
+        case 8 * 16 + 3: gemv1_bl_body<NintCodec<8, 3>, XMODE, false, true>(a, w, smem); break;
+        case 8 * 16 + 6: gemv1_bl_body<NintCodec<8, 6>, XMODE, false, true>(a, w, smem); break;
         default: break;
     }
 }

@@ -492,7 +492,7 @@ __device__ __forceinline__ void routed_absent_pair(const GemvArgsB& a, int pair)
 // from global memory, one chunk ahead, and quantised in registers by the warp that needs it.
 // DENSE: the kernel serves plain products only (no routing table, no route sum, every warp its own chunks);
 // the routed launches of the expert path compile the general form.
-// PLAIN_OUT (with DENSE): the rows are written as they are -- no sum over ranks, no gated epilogue.
+// PLAIN_OUT: no sum over ranks and no gated epilogue (the rows, or the routed pair's rows, are written as they are).
 // ONE_RB (with PLAIN_OUT): the grid has one CTA per row-block (the 4096-row matrices): CTA b owns row-block b.
 template <class C, int XMODE = 0, bool DENSE = false, bool PLAIN_OUT = false, bool ONE_RB = false>
 __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB& w, unsigned char* smem) {
