@@ -159,6 +159,8 @@ int mfqb_mul_mat_glu(const mfqb_weight* w, const void* x_bf16, int m, void* y, i
  * NINT weight takes -- 0 by shape (default), 1 the per-warp ring kernel, 2 the streamed kernel.
  * "moe_f16_tiles_from_x2": twice the average number of (token, route) pairs per expert from which
  * the expert matmuls take the f16 tile kernel instead of the integer tiles (default 4).
+ * "gemm_plan": 0 = ring sizes of the tensor-core tile kernel by shape (default), 1 = 32-column
+ * activation stages with a two-chunk weight ring for every shape.
  * No counterpart in the reference (its switches are MFQ_* environment variables,
  * docs/developer-architecture-and-operator-reference.md:1048-1078). */
 int mfqb_tune(const char* key, int value);
