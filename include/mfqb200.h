@@ -401,6 +401,8 @@ int mfqb_decoder_layer(mfqb_decoder* d, int layer, const float* h_in, int rows, 
                        mfqb_stream_t stream);
 int mfqb_decoder_read_cache(const mfqb_decoder* d, int layer, int row, int which, int ctx, void* out_bf16,
                             mfqb_stream_t stream);
+/* The logits of the last mfqb_decoder_step, this rank's vocabulary rows: out [rows, shard rows] float32. */
+int mfqb_decoder_read_logits(const mfqb_decoder* d, int rows, float* out, mfqb_stream_t stream);
 int mfqb_decoder_free(mfqb_decoder* d);
 
 /* ---------------------------------------------------------------------------------

@@ -112,6 +112,10 @@ def test_greedy_steps_and_graph_replay_agree():
                     dec.step(a, b)
                     stream.synchronize()
                     seq.append(b.cpu().numpy().copy())
+                    # the greedy choice is the arg-max of the step's logits (first index on ties)
+                    logits = dec.read_logits(len(ids))
+                    stream.synchronize()
+                    assert np.array_equal(seq[-1], logits.cpu().numpy().argmax(axis=1))
                     a, b = b, a
         outs.append(np.stack(seq))
         assert ((outs[-1] >= 0) & (outs[-1] < CFG["vocab"])).all()

@@ -85,6 +85,7 @@ _SIGNATURES = {
     "mfqb_decoder_step": (_i, [_vp, _vp, _i, _vp, _vp]),
     "mfqb_decoder_layer": (_i, [_vp, _i, _vp, _i, _vp, _vp]),
     "mfqb_decoder_read_cache": (_i, [_vp, _i, _i, _i, _i, _vp, _vp]),
+    "mfqb_decoder_read_logits": (_i, [_vp, _i, _vp, _vp]),
     "mfqb_decoder_free": (_i, [_vp]),
     "mfqb_mul_mat_host": (_i, [_vp, _vp, _i, _vp, _i]),
     "mfqb_mul_mat_host_multi": (_i, [_P(_vp), _i, _P(_vp), _i, _P(_vp), _i]),

@@ -359,35 +359,39 @@ __global__ void __launch_bounds__(128, G <= 4 ? 4 : 2) attn_decode_kernel(const 
 }
 
 // logits [rows, n] float32 -> (largest value, its index + index_base) per row; ties go to the smaller index.
-__global__ void __launch_bounds__(1024) argmax_rows_kernel(const float* __restrict__ logits, int n, int index_base, float* __restrict__ best_val,
-                                                           int* __restrict__ best_idx) {
+// Two launches: kArgmaxSlices CTAs per row take the best of a slice each, one warp per row merges them.
+constexpr int kArgmaxSlices = 64;
+__device__ __forceinline__ void argmax_take(float v, int i, float& bv, int& bi) {
+    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+}
+__global__ void __launch_bounds__(256) argmax_slices_kernel(const float* __restrict__ logits, int n, float* __restrict__ part_val, int* __restrict__ part_idx) {
     dep_wait();
-    __shared__ float sv[32];
-    __shared__ int si[32];
-    const float* row = logits + (size_t)blockIdx.x * n;
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    const float* row = logits + (size_t)blockIdx.y * n;
+    const int per = (n + kArgmaxSlices - 1) / kArgmaxSlices, i0 = blockIdx.x * per, i1 = min(n, i0 + per);
     float bv = -INFINITY;
     int bi = 0x7FFFFFFF;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const float v = row[i];
-        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
-    }
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-    }
+#pragma unroll 4
+    for (int i = i0 + threadIdx.x; i < i1; i += 256) argmax_take(row[i], i, bv, bi);
+    for (int o = 16; o > 0; o >>= 1) argmax_take(__shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o), bv, bi);
     if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
     __syncthreads();
-    if (threadIdx.x < 32) {
-        bv = threadIdx.x < (blockDim.x >> 5) ? sv[threadIdx.x] : -INFINITY;
-        bi = threadIdx.x < (blockDim.x >> 5) ? si[threadIdx.x] : 0x7FFFFFFF;
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-        }
-        if (threadIdx.x == 0) { best_val[blockIdx.x] = bv; best_idx[blockIdx.x] = bi + index_base; }
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w) argmax_take(sv[w], si[w], bv, bi);
+        part_val[blockIdx.y * kArgmaxSlices + blockIdx.x] = bv;
+        part_idx[blockIdx.y * kArgmaxSlices + blockIdx.x] = bi;
     }
+}
+__global__ void __launch_bounds__(32) argmax_merge_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx, int index_base,
+                                                          float* __restrict__ best_val, int* __restrict__ best_idx) {
+    dep_wait();
+    const int lane = threadIdx.x;
+    float bv = -INFINITY;
+    int bi = 0x7FFFFFFF;
+    for (int j = lane; j < kArgmaxSlices; j += 32) argmax_take(part_val[blockIdx.x * kArgmaxSlices + j], part_idx[blockIdx.x * kArgmaxSlices + j], bv, bi);
+    for (int o = 16; o > 0; o >>= 1) argmax_take(__shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o), bv, bi);
+    if (lane == 0) { best_val[blockIdx.x] = bv; best_idx[blockIdx.x] = bi + index_base; }
 }
 
 // Vocabulary shards: gathered [world][rows] (value, index as float) -> winning token per row (smaller rank on ties).
@@ -417,7 +421,12 @@ __global__ void embed_rows_kernel(const int* __restrict__ ids, const __nv_bfloat
     dep_wait();
     const int r = blockIdx.x;
     const int id = min(max(ids[r], 0), vocab - 1);
-    for (int i = threadIdx.x; i < H; i += blockDim.x) h[(size_t)r * H + i] = __bfloat162float(table[(size_t)id * H + i]);
+    const uint2* src = reinterpret_cast<const uint2*>(table + (size_t)id * H);   // H is a multiple of 8: four bf16 per load
+    float4* dst = reinterpret_cast<float4*>(h + (size_t)r * H);
+    for (int i = threadIdx.x; i < (H >> 2); i += blockDim.x) {
+        const uint2 v = __ldg(src + i);
+        dst[i] = make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xFFFF0000u), __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xFFFF0000u));
+    }
 }
 
 // Seeded synthetic cache contents (a stand-in for the prefill pass): values of unit scale.
@@ -457,7 +466,7 @@ struct mfqb_decoder {
     const void* embedding = nullptr;   // bf16 [vocab, H] on the device, borrowed
     DevBuf gamma_final;
     // workspaces
-    DevBuf h, xn, qkv, attn, attn_count, inv_freq, rope_table, proj, proj_sum, act, logits, part, best_val, best_idx, gathered, gathered_sum, pos;
+    DevBuf h, xn, qkv, attn, attn_count, inv_freq, rope_table, proj, proj_sum, act, logits, part, best_val, best_idx, part_val, part_idx, gathered, gathered_sum, pos;
 };
 
 // Context splits of the decode attention: as many CTAs as are resident at once (one wave: the merge
@@ -633,6 +642,8 @@ int mfqb_decoder_create(const mfqb_decoder_config* cfg, int rank, int world, mfq
         d->part.alloc(B * d->nq * kMaxSplits * kPartStride * 4);
         d->rope_table.alloc(B * 64 * sizeof(float2));
         d->best_val.alloc(B * 4);
+        d->part_val.alloc(B * kArgmaxSlices * 4);
+        d->part_idx.alloc(B * kArgmaxSlices * 4);
         d->best_idx.alloc(B * 4);
         d->gathered.alloc((size_t)world * B * 2 * 4);
         d->gathered_sum.alloc((size_t)world * B * 2 * 4);
@@ -703,7 +714,7 @@ int mfqb_decoder_step(mfqb_decoder* d, const int32_t* ids_in, int batch, int32_t
         DeviceGuard guard(d->device);
         cudaStream_t s = stream;
         const int H = d->cfg.hidden;
-        launch_dep(embed_rows_kernel, dim3(batch), dim3(256), s, static_cast<const int*>(ids_in), static_cast<const __nv_bfloat16*>(d->embedding),
+        launch_dep(embed_rows_kernel, dim3(batch), dim3(1024), s, static_cast<const int*>(ids_in), static_cast<const __nv_bfloat16*>(d->embedding),
                    static_cast<float*>(d->h.p), H, d->cfg.vocab);
         launch_rope_table(d, batch, s);
         const float* delta = nullptr;
@@ -711,8 +722,10 @@ int mfqb_decoder_step(mfqb_decoder* d, const int32_t* ids_in, int batch, int32_t
         launch_dep(add_rmsnorm_kernel, dim3(batch), dim3(1024), s, static_cast<float*>(d->h.p), delta, static_cast<const float*>(d->gamma_final.p),
                    static_cast<__nv_bfloat16*>(d->xn.p), H, d->cfg.rms_eps);
         mul_mat(d->lm_head, d->xn.p, batch, d->logits.p, s);
-        launch_dep(argmax_rows_kernel, dim3(batch), dim3(1024), s, static_cast<const float*>(d->logits.p), d->vshard, d->vbase,
-                   static_cast<float*>(d->best_val.p), static_cast<int*>(d->best_idx.p));
+        launch_dep(argmax_slices_kernel, dim3(kArgmaxSlices, batch), dim3(256), s, static_cast<const float*>(d->logits.p), d->vshard,
+                   static_cast<float*>(d->part_val.p), static_cast<int*>(d->part_idx.p));
+        launch_dep(argmax_merge_kernel, dim3(batch), dim3(32), s, static_cast<const float*>(d->part_val.p), static_cast<const int*>(d->part_idx.p),
+                   d->vbase, static_cast<float*>(d->best_val.p), static_cast<int*>(d->best_idx.p));
         if (d->world == 1) {
             MFQB_CUDA(cudaMemcpyAsync(ids_out, d->best_idx.p, (size_t)batch * 4, cudaMemcpyDeviceToDevice, s));
         } else {
@@ -741,6 +754,15 @@ int mfqb_decoder_layer(mfqb_decoder* d, int layer, const float* h_in, int rows, 
         launch_dep(add_rmsnorm_kernel, dim3(rows), dim3(1024), stream, static_cast<float*>(d->h.p), delta, static_cast<const float*>(d->gamma_final.p),
                    static_cast<__nv_bfloat16*>(d->xn.p), d->cfg.hidden, d->cfg.rms_eps);
         MFQB_CUDA(cudaMemcpyAsync(h_out, d->h.p, bytes, cudaMemcpyDeviceToDevice, stream));
+    });
+}
+
+// Copies the logits of the last step, this rank's vocabulary rows: out [rows, shard rows] float32.
+int mfqb_decoder_read_logits(const mfqb_decoder* d, int rows, float* out, mfqb_stream_t stream) {
+    return guarded([&] {
+        if (!d || !out || rows < 1 || rows > d->cfg.max_batch) fail(MFQB_ERR_ARG, "mfqb_decoder_read_logits: bad argument");
+        DeviceGuard guard(d->device);
+        MFQB_CUDA(cudaMemcpyAsync(out, d->logits.p, (size_t)rows * d->vshard * 4, cudaMemcpyDeviceToDevice, stream));
     });
 }
 

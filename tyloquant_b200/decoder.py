@@ -65,6 +65,15 @@ class Decoder:
         check(lib.mfqb_decoder_read_cache(self._h, layer, row, which, ctx, out.data_ptr(), _stream_ptr(self.device)))
         return out
 
+    def read_logits(self, rows: int):
+        """float32 [rows, vocabulary rows of this rank]: the logits of the last step."""
+        torch = _torch()
+        begin, n = C.c_int(), C.c_int()
+        check(lib.mfqb_decoder_vocab_shard(self._h, C.byref(begin), C.byref(n)))
+        out = torch.empty((rows, n.value), dtype=torch.float32, device=f"cuda:{self.device}")
+        check(lib.mfqb_decoder_read_logits(self._h, rows, out.data_ptr(), _stream_ptr(self.device)))
+        return out
+
     def free(self) -> None:
         if self._h:
             lib.mfqb_decoder_free(self._h)
