@@ -155,6 +155,17 @@ int mfqb_mul_mat_swiglu(const mfqb_weight* w, const void* gate_up_f32, int m, vo
 int mfqb_mul_mat_glu(const mfqb_weight* w, const void* x_bf16, int m, void* y, int y_dtype,
                      mfqb_stream_t stream);
 
+/* Residual add, RMSNorm and a single-row product in one launch (what a decoder block does before q|k|v
+ * and before gate|up; the reference runs rmsnorm and the linear as two kernels,
+ * cpp_runtime/mfq_decode.cpp:12210-12400): h [k] float32 residual row, delta [k] float32 or null,
+ * gamma [k] float32; y [1, n] = W . ((h + delta) / rms(h + delta) * gamma), or with gated != 0 the
+ * gated form of mfqb_mul_mat_glu ([1, n / 2]).  When h_out is not null it receives h + delta (it must
+ * be another buffer than h).  NINT weights, k a multiple of 4.  Every CTA of the product normalises the
+ * row for itself, which pays for short outputs; for the projections of an 8B-shaped decoder block the
+ * separate normalisation kernel measured faster, and the decoder below keeps it. */
+int mfqb_mul_mat_rmsnorm(const mfqb_weight* w, const float* h, const float* delta, const float* gamma, float eps,
+                         float* h_out, void* y, int y_dtype, int gated, mfqb_stream_t stream);
+
 /* Tuning switches, for measurements.  "gemv1_kernel": which kernel a single-row product of a plain
  * NINT weight takes -- 0 by shape (default), 1 the per-warp ring kernel, 2 the streamed kernel.
  * "moe_f16_tiles_from_x2": twice the average number of (token, route) pairs per expert from which

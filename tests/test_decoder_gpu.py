@@ -24,8 +24,9 @@ def _bf(x):
     return O.bf16_round(np.asarray(x, dtype=np.float32))
 
 
-def _rmsnorm(h, eps=1e-5):
-    return _bf(h / np.sqrt((h.astype(np.float64) ** 2).mean(axis=-1, keepdims=True) + eps).astype(np.float32))
+def _rmsnorm(h, eps=1e-5, rounded=True):
+    xn = (h / np.sqrt((h.astype(np.float64) ** 2).mean(axis=-1, keepdims=True) + eps)).astype(np.float32)
+    return _bf(xn) if rounded else xn
 
 
 def _rope(x, pos, theta=500000.0):
@@ -36,9 +37,9 @@ def _rope(x, pos, theta=500000.0):
     return np.concatenate([a * np.cos(ang) - b * np.sin(ang), b * np.cos(ang) + a * np.sin(ang)], axis=-1).astype(np.float32)
 
 
-def _block_oracle(h, w, kc, vc, pos, nq, nkv):
+def _block_oracle(h, w, kc, vc, pos, nq, nkv, rounded_norm=True):
     """h [H] float32, w: dequantized weights, kc / vc [nkv, pos, 128] float32 (cache before the step)."""
-    xn = _rmsnorm(h)
+    xn = _rmsnorm(h, rounded=rounded_norm)
     qkv = w["qkv"] @ xn
     q = qkv[:nq * 128].reshape(nq, 128)
     k = qkv[nq * 128:(nq + nkv) * 128].reshape(nkv, 128)
@@ -54,7 +55,7 @@ def _block_oracle(h, w, kc, vc, pos, nq, nkv):
         p = np.exp(s - s.max())
         out[hq] = (p / p.sum()) @ vc[hq // g]
     h = h + w["o"] @ _bf(out.reshape(-1))
-    xn = _rmsnorm(h)
+    xn = _rmsnorm(h, rounded=rounded_norm)
     gu = (w["gate_up"] @ xn).reshape(-1, 2, 16)   # 16-row blocks alternate gate and up rows
     act = _bf(O.swiglu(gu[:, 0].reshape(-1), gu[:, 1].reshape(-1)))
     return h + w["down"] @ act, k, v
@@ -78,6 +79,10 @@ def test_one_block_matches_the_float32_restatement():
             k_got = dec.read_cache(layer, r, 0, ctx + 1).float().cpu().numpy()[:, ctx]
             v_got = dec.read_cache(layer, r, 1, ctx + 1).float().cpu().numpy()[:, ctx]
             assert rel_l2(k_got, k_new) <= 4e-3 and rel_l2(v_got, v_new) <= 4e-3   # one bf16 rounding of values within 1e-3
+        # one row takes the single-row kernels; the same position of sequence 0 is computed again
+        got1 = dec.layer(layer, torch.from_numpy(h_in[:1]).cuda()).cpu().numpy()
+        want1, _, _ = _block_oracle(h_in[0], w, before_k[0], before_v[0], ctx, CFG["n_q_heads"], CFG["n_kv_heads"])
+        assert rel_l2(got1[0], want1) <= 1e-3, (layer, rel_l2(got1[0], want1))
     dec.free()
 
 

@@ -278,3 +278,32 @@ def test_host_buffer_list_call_matches_single_products(pinned):
         assert rel_l2(y.numpy(), want) < 1e-5
     for w in ws:
         w.free()
+
+
+@pytest.mark.parametrize("profile", [(3, 24, 5), (4, 32, 6), (6, 24, 7)])
+def test_product_with_fused_residual_add_and_rmsnorm(profile):
+    """mfqb_mul_mat_rmsnorm: y = W . ((h + delta) / rms(h + delta) * gamma) in one launch, plain and gated, with and
+    without delta; h + delta comes back when asked for."""
+    bits, gs, sb = profile
+    rng = np.random.default_rng(4600 + bits)
+    for n, k in ((2 * 16 * 9, 1000), (4096, 4096), (2 * 16 * 40, 520)):
+        blob = encode.random_nint_blob(n, k, bits, gs, sb, seed=4601 + n, device="cuda")
+        w_ref = O.dequant_nint(O.unpack_nint(blob)).astype(np.float64)
+        w = QuantWeight.from_blob(f"NINT{bits}", blob)
+        h = (rng.standard_normal(k) * 3.0).astype(np.float32)
+        d = rng.standard_normal(k).astype(np.float32)
+        g = (1.0 + 0.1 * rng.standard_normal(k)).astype(np.float32)
+        for delta in (None, d):
+            r = h.astype(np.float64) + (0.0 if delta is None else delta.astype(np.float64))
+            xn = r / np.sqrt((r ** 2).mean() + 1e-5) * g.astype(np.float64)
+            want = w_ref @ xn
+            dt = None if delta is None else torch.from_numpy(delta).cuda()
+            y, res = w.matmul_rmsnorm(torch.from_numpy(h).cuda(), torch.from_numpy(g).cuda(), delta=dt, out_dtype=torch.float32, return_residual=True)
+            assert rel_l2(y.cpu().numpy().astype(np.float64), want) <= REL_L2, (profile, n, k, delta is None)
+            assert np.array_equal(res.cpu().numpy(), (h + (0 if delta is None else delta)).astype(np.float32))
+            blocks = want.reshape(n // 32, 2, 16)
+            gate, up = blocks[:, 0].reshape(-1), blocks[:, 1].reshape(-1)
+            want_g = up * gate / (1.0 + np.exp(-gate))
+            yg = w.matmul_rmsnorm(torch.from_numpy(h).cuda(), torch.from_numpy(g).cuda(), delta=dt, gated=True, out_dtype=torch.float32)
+            assert rel_l2(yg.cpu().numpy().astype(np.float64), want_g) <= REL_L2
+        w.free()

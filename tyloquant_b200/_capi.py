@@ -73,6 +73,7 @@ _SIGNATURES = {
     "mfqb_mul_mat": (_i, [_vp, _vp, _i, _vp, _i, _vp]),
     "mfqb_device_status": (_i, [_i, _P(_i)]),
     "mfqb_tune": (_i, [_cp, _i]),
+    "mfqb_mul_mat_rmsnorm": (_i, [_vp, _vp, _vp, _vp, C.c_float, _vp, _vp, _i, _i, _vp]),
     "mfqb_mul_mat_glu": (_i, [_vp, _vp, _i, _vp, _i, _vp]),
     "mfqb_mul_mat_swiglu": (_i, [_vp, _vp, _i, _vp, _i, _vp]),
     "mfqb_mul_mat_multi": (_i, [_P(_vp), _i, _vp, _P(_vp), _i, _vp]),

@@ -461,12 +461,16 @@ struct mfqb_decoder {
     int rank = 0, world = 1, device = 0;
     mfqb_comm* comm = nullptr;       // borrowed; null when world == 1
     int nq = 0, nkv = 0, f = 0, vshard = 0, vbase = 0, sms = 0, attn_per_sm = 4;
+    // Single-row steps could run the residual add + RMSNorm inside the q|k|v, gate|up and lm_head products
+    // (mfqb_mul_mat_rmsnorm).  Measured on the 8B-shaped model it loses: every CTA of those products repeats the
+    // normalisation of the row (2.29 against 2.14 ms per step), so the two-kernel form stays the default.
+    bool fused_norm = false;
     std::vector<DecoderLayer> layers;
     const mfqb_weight* lm_head = nullptr;
     const void* embedding = nullptr;   // bf16 [vocab, H] on the device, borrowed
     DevBuf gamma_final;
     // workspaces
-    DevBuf h, xn, qkv, attn, attn_count, inv_freq, rope_table, proj, proj_sum, act, logits, part, best_val, best_idx, part_val, part_idx, gathered, gathered_sum, pos;
+    DevBuf h, h2, xn, qkv, attn, attn_count, inv_freq, rope_table, proj, proj_sum, act, logits, part, best_val, best_idx, part_val, part_idx, gathered, gathered_sum, pos;
 };
 
 // Context splits of the decode attention: as many CTAs as are resident at once (one wave: the merge
@@ -514,9 +518,20 @@ static const float* layer_forward(mfqb_decoder* d, int li, int rows, const float
     DecoderLayer& L = d->layers[li];
     const int H = d->cfg.hidden;
     const int G = d->cfg.n_q_heads / d->cfg.n_kv_heads;
-    launch_dep(add_rmsnorm_kernel, dim3(rows), dim3(1024), s, static_cast<float*>(d->h.p), delta, static_cast<const float*>(L.gamma_attn.p),
-               static_cast<__nv_bfloat16*>(d->xn.p), H, d->cfg.rms_eps);
-    mul_mat(L.qkv, d->xn.p, rows, d->qkv.p, s);
+    // One row: the residual add and the normalisation run inside the products that consume them (h + delta goes to
+    // h2, h2 + attention output back to h).  Batches: a normalisation kernel, then the batched product.
+    bool fused = rows == 1 && d->fused_norm;
+    if (fused) {
+        const int rc = mfqb_mul_mat_rmsnorm(L.qkv, static_cast<const float*>(d->h.p), delta, static_cast<const float*>(L.gamma_attn.p), d->cfg.rms_eps,
+                                            static_cast<float*>(d->h2.p), d->qkv.p, MFQB_F32, 0, s);
+        if (rc == MFQB_ERR_UNSUPPORTED) d->fused_norm = fused = false;   // weights this form does not take: the two-kernel form from here on
+        else if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
+    }
+    if (!fused) {
+        launch_dep(add_rmsnorm_kernel, dim3(rows), dim3(1024), s, static_cast<float*>(d->h.p), delta, static_cast<const float*>(L.gamma_attn.p),
+                   static_cast<__nv_bfloat16*>(d->xn.p), H, d->cfg.rms_eps);
+        mul_mat(L.qkv, d->xn.p, rows, d->qkv.p, s);
+    }
     const int nsplit = attn_splits(d, rows, d->cfg.max_ctx);
     const dim3 agrid(nsplit, d->nkv, rows);
     auto attn = [&](auto kernel) {
@@ -542,10 +557,14 @@ static const float* layer_forward(mfqb_decoder* d, int li, int rows, const float
         mul_mat(L.o, d->attn.p, rows, d->proj.p, s);
         o_out = rank_sum(d, static_cast<const float*>(d->proj.p), static_cast<float*>(d->proj_sum.p), (size_t)rows * H, s);
     }
-    launch_dep(add_rmsnorm_kernel, dim3(rows), dim3(1024), s, static_cast<float*>(d->h.p), o_out, static_cast<const float*>(L.gamma_ffn.p),
-               static_cast<__nv_bfloat16*>(d->xn.p), H, d->cfg.rms_eps);
     // gate|up with the activation in the epilogue: the fused weight alternates 16-row blocks of gate and up rows
-    {
+    if (fused) {
+        const int rc = mfqb_mul_mat_rmsnorm(L.gate_up, static_cast<const float*>(d->h2.p), o_out, static_cast<const float*>(L.gamma_ffn.p), d->cfg.rms_eps,
+                                            static_cast<float*>(d->h.p), d->act.p, MFQB_BF16, 1, s);
+        if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
+    } else {
+        launch_dep(add_rmsnorm_kernel, dim3(rows), dim3(1024), s, static_cast<float*>(d->h.p), o_out, static_cast<const float*>(L.gamma_ffn.p),
+                   static_cast<__nv_bfloat16*>(d->xn.p), H, d->cfg.rms_eps);
         const int rc = mfqb_mul_mat_glu(L.gate_up, d->xn.p, rows, d->act.p, MFQB_BF16, s);
         if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
     }
@@ -599,6 +618,7 @@ int mfqb_decoder_create(const mfqb_decoder_config* cfg, int rank, int world, mfq
         d->gamma_final.alloc(H * 4);
         launch_fill_f32(d->gamma_final.p, H, 1.f, nullptr);
         d->h.alloc(B * H * 4);
+        d->h2.alloc(B * H * 4);
         d->xn.alloc(B * H * 2);
         d->qkv.alloc(B * (d->nq + 2 * d->nkv) * kHeadDim * 4);
         {   // rotary frequencies theta^(-2i/128), i = 0..63
@@ -719,9 +739,18 @@ int mfqb_decoder_step(mfqb_decoder* d, const int32_t* ids_in, int batch, int32_t
         launch_rope_table(d, batch, s);
         const float* delta = nullptr;
         for (int li = 0; li < d->cfg.layers; ++li) delta = layer_forward(d, li, batch, delta, s);
-        launch_dep(add_rmsnorm_kernel, dim3(batch), dim3(1024), s, static_cast<float*>(d->h.p), delta, static_cast<const float*>(d->gamma_final.p),
-                   static_cast<__nv_bfloat16*>(d->xn.p), H, d->cfg.rms_eps);
-        mul_mat(d->lm_head, d->xn.p, batch, d->logits.p, s);
+        bool fused_head = batch == 1 && d->fused_norm;
+        if (fused_head) {
+            const int rc = mfqb_mul_mat_rmsnorm(d->lm_head, static_cast<const float*>(d->h.p), delta, static_cast<const float*>(d->gamma_final.p),
+                                                d->cfg.rms_eps, nullptr, d->logits.p, MFQB_F32, 0, s);
+            if (rc == MFQB_ERR_UNSUPPORTED) fused_head = false;
+            else if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
+        }
+        if (!fused_head) {
+            launch_dep(add_rmsnorm_kernel, dim3(batch), dim3(1024), s, static_cast<float*>(d->h.p), delta, static_cast<const float*>(d->gamma_final.p),
+                       static_cast<__nv_bfloat16*>(d->xn.p), H, d->cfg.rms_eps);
+            mul_mat(d->lm_head, d->xn.p, batch, d->logits.p, s);
+        }
         launch_dep(argmax_slices_kernel, dim3(kArgmaxSlices, batch), dim3(256), s, static_cast<const float*>(d->logits.p), d->vshard,
                    static_cast<float*>(d->part_val.p), static_cast<int*>(d->part_idx.p));
         launch_dep(argmax_merge_kernel, dim3(batch), dim3(32), s, static_cast<const float*>(d->part_val.p), static_cast<const int*>(d->part_idx.p),

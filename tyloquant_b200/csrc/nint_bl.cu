@@ -435,6 +435,42 @@ void launch_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtyp
     dispatch(a, p, s, "GEMV");
 }
 
+// Single-row product on the residual row with the add + RMSNorm fused in (GemvArgsB::norm_*): y = W . norm(h + delta),
+// or the gated form of it (glu).  The normalised row lives in shared memory behind the rings.
+void launch_bl_gemv_norm(const NintDevB& w, const float* h, const float* delta, const float* gamma, float eps, float* h_out, void* y, int y_dtype,
+                         bool glu, int device, cudaStream_t s) {
+    if (w.k % 4) fail(MFQB_ERR_ARG, "fused normalisation needs a row length that is a multiple of 4, got %d", w.k);
+    GemvArgsB a{};
+    a.w = w;
+    a.x = reinterpret_cast<const __nv_bfloat16*>(h);
+    a.y = y;
+    a.m = 1;
+    a.ldy = w.n;
+    a.y_dtype = y_dtype;
+    a.x_mode = 3;
+    a.norm_delta = delta;
+    a.norm_gamma = gamma;
+    a.norm_eps = eps;
+    a.norm_h_out = h_out;
+    GemvPlanB p;
+    const int warps = gemv1_warps(w), sms = device_sm_count(device);
+    const size_t row_bytes = (size_t)w.k * 4;
+    p.threads = warps * 32;
+    p.passes = -4;
+    p.grid = std::min(w.nrb, ctas_per_sm(gemv1_smem(w, 1, warps) + row_bytes, warps > 8 ? 2 : 3) * sms);
+    a.rb_per_cta = (w.nrb + p.grid - 1) / p.grid;
+    if (glu) {   // (gate, up) pairs of row-blocks stay together
+        if ((w.nrb & 1) || (w.n & 31)) fail(MFQB_ERR_ARG, "gated product: the weight needs whole (gate, up) pairs of 16-row blocks, n = %d", w.n);
+        p.grid = std::min(w.nrb / 2, p.grid);
+        a.rb_per_cta = 2 * ((w.nrb / 2 + p.grid - 1) / p.grid);
+        a.glu = 1;
+    }
+    a.private_sums = gemv1_private_sums(a.rb_per_cta);
+    p.smem = gemv1_smem(w, a.rb_per_cta, warps) + row_bytes;
+    if (p.smem > kGemvSmemLimit) fail(MFQB_ERR_UNSUPPORTED, "fused normalisation: a row of %d columns does not fit shared memory beside the rings", w.k);
+    dispatch(a, p, s, "GEMV with fused RMSNorm");
+}
+
 // Streamed single-row product (nint_gemvs.cuh).  `fix` is the weight's own scratch for row-blocks
 // that straddle CTAs: [sms][16] (value, flag) pairs, all zero between calls.  Returns false when the
 // activation planes of this row length and a useful ring do not fit one CTA; the caller then

@@ -93,6 +93,13 @@ struct GemvArgsB {
     size_t x16f_tile_stride;
     const float* x16_scale;
     int x_mode;
+    // Single-row kernel, x_mode 3 (residual add + RMSNorm fused into the product): x is the float32 residual row h [k];
+    // the product is taken with (h + norm_delta) / rms(h + norm_delta) * norm_gamma, and CTA 0 writes h + norm_delta to
+    // norm_h_out (a buffer other than x) when that is not null.  norm_delta may be null.
+    const float* norm_delta;
+    const float* norm_gamma;
+    float* norm_h_out;
+    float norm_eps;
     // Single-row kernel, gated FFN: the weight's 16-row blocks alternate (gate rows, up rows); the kernel
     // writes up * silu(gate), n / 2 values, instead of the n products.
     int glu;
@@ -361,7 +368,7 @@ __device__ __forceinline__ void x_chunk_quant(const XChunkRaw<T>& raw, int c, ui
     gt.w = __shfl_sync(0xffffffffu, sxx, 8 * c + 4);
 }
 
-// Float32 forms of the two functions above (x_mode 1 and 2).  A float32 magnitude could round up to
+// Float32 forms of the two functions above (x_mode 1, 2 and 3).  A float32 magnitude could round up to
 // 2^15 on the 16-bit grid, so these groups get one bit of head-room.
 template <int T>
 struct XChunkRawF {
@@ -379,7 +386,8 @@ __device__ __forceinline__ void x_chunk_load_f(const float* __restrict__ xrow, i
         if (j < 2 * T && 4 * j < gs && k0 < k) {
             float a[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {1.f, 1.f, 1.f, 1.f};
             if (vec_ok && k0 + 3 < k) {
-                const float4 va = __ldg(reinterpret_cast<const float4*>(xrow + k0));
+                // mode 3 reads the normalised row the CTA prepared in shared memory: no read-only global path there
+                const float4 va = XMODE == 3 ? *reinterpret_cast<const float4*>(xrow + k0) : __ldg(reinterpret_cast<const float4*>(xrow + k0));
                 a[0] = va.x; a[1] = va.y; a[2] = va.z; a[3] = va.w;
                 if constexpr (XMODE == 2) {
                     const float4 vu = __ldg(reinterpret_cast<const float4*>(xrow + k + k0));
@@ -389,7 +397,7 @@ __device__ __forceinline__ void x_chunk_load_f(const float* __restrict__ xrow, i
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
                     if (4 * j + i < gs && k0 + i < k) {
-                        a[i] = __ldg(xrow + k0 + i);
+                        a[i] = XMODE == 3 ? xrow[k0 + i] : __ldg(xrow + k0 + i);
                         if constexpr (XMODE == 2) u[i] = __ldg(xrow + k + k0 + i);
                     }
             }
@@ -600,7 +608,40 @@ __device__ __forceinline__ void gemv1_bl_body(const GemvArgsB& a, const NintDevB
     XChunkRawF<T> rawf;
     // float32 rows: [rows, k], or the pair's gate|up products [pairs, 2k]
     const float* xrow_f = nullptr;
-    if constexpr (XMODE != 0) {
+    if constexpr (XMODE == 3) {
+        // residual add + RMSNorm of the row, once per CTA, into shared memory behind the rings (k is a multiple of 4)
+        __shared__ float norm_red[32];
+        float* xs = reinterpret_cast<float*>(anch + (size_t)a.rb_per_cta * 16 + (size_t)nwarps * S * REC);
+        const float4* h4 = reinterpret_cast<const float4*>(a.x);
+        const float4* d4 = reinterpret_cast<const float4*>(a.norm_delta);
+        const float4* g4 = reinterpret_cast<const float4*>(a.norm_gamma);
+        float4* o4 = (blockIdx.x == 0 && a.norm_h_out != nullptr) ? reinterpret_cast<float4*>(a.norm_h_out) : nullptr;
+        float ss = 0.f;
+        for (int i = tid; i < (w.k >> 2); i += blockDim.x) {
+            float4 v = h4[i];
+            if (d4 != nullptr) {
+                const float4 dv = d4[i];
+                v.x += dv.x; v.y += dv.y; v.z += dv.z; v.w += dv.w;
+            }
+            reinterpret_cast<float4*>(xs)[i] = v;
+            if (o4 != nullptr) o4[i] = v;
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) norm_red[warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+        for (int i = 0; i < nwarps; ++i) tot += norm_red[i];
+        const float inv = rsqrtf(tot / (float)w.k + a.norm_eps);
+        for (int i = tid; i < (w.k >> 2); i += blockDim.x) {
+            float4 v = reinterpret_cast<float4*>(xs)[i];
+            const float4 gv = __ldg(g4 + i);
+            v.x *= inv * gv.x; v.y *= inv * gv.y; v.z *= inv * gv.z; v.w *= inv * gv.w;
+            reinterpret_cast<float4*>(xs)[i] = v;
+        }
+        __syncthreads();
+        xrow_f = xs;
+    } else if constexpr (XMODE != 0) {
         const size_t xr = routed ? (size_t)(a.x_per_pair ? blockIdx.y : blockIdx.y / a.routes) : 0;
         xrow_f = reinterpret_cast<const float*>(a.x) + xr * (XMODE == 2 ? 2 : 1) * w.k;
     }
@@ -750,6 +791,13 @@ template <class C>
 __global__ void __launch_bounds__(C::MIN_CTAS >= 3 ? 384 : 256, C::MIN_CTAS >= 3 ? 2 : C::MIN_CTAS) gemv1_bl_kernel(const GemvArgsB a) {
     extern __shared__ __align__(16) unsigned char smem[];
     gemv1_bl_body<C, 0, true, true>(a, a.w, smem);
+}
+
+// Residual add + RMSNorm fused into the product (x_mode 3; the gated epilogue may follow).
+template <class C>
+__global__ void __launch_bounds__(C::MIN_CTAS >= 3 ? 384 : 256, C::MIN_CTAS >= 3 ? 2 : C::MIN_CTAS) gemv1_bl_norm_kernel(const GemvArgsB a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    gemv1_bl_body<C, 3, true, false>(a, a.w, smem);
 }
 
 // One CTA per row-block (launched when the grid equals the number of row-blocks).

@@ -11,7 +11,7 @@ struct GemvPlanB {
     int grid = 1, grid_y = 1, threads = 256;
     const GemvMultiTable* multi = nullptr;   // the weights of a multi-weight launch (passes == -1)
     int* occupancy_out = nullptr;            // set: nothing is launched, the kernel's resident CTAs per SM for (threads, smem) are stored here
-    int passes = 0;      // 0: single-row kernel; 1, 2, 4: batched kernel with that many two-row passes; -1: multi-weight single-row launch; -2: single-row kernel on a float32 gate|up row; -3: single-row kernel over (token, route) pairs of one cohort; 108, 116: f16 batched kernel for up to 8 or 16 rows
+    int passes = 0;      // 0: single-row kernel; 1, 2, 4: batched kernel with that many two-row passes; -1: multi-weight single-row launch; -2: single-row kernel on a float32 gate|up row; -3: single-row kernel over (token, route) pairs of one cohort; -4: single-row kernel with the fused residual add + RMSNorm; 108, 116: f16 batched kernel for up to 8 or 16 rows
     size_t smem = 0;
 };
 
@@ -75,6 +75,7 @@ static cudaError_t launch_kernel_pdl(Kernel kernel, const GemvArgsB& a, const Ge
 template <class C>
 static cudaError_t launch_gemv_codec(const GemvArgsB& a, const GemvPlanB& p, cudaStream_t stream) {
     switch (p.passes) {
+        case -4: return launch_kernel_pdl(gemv1_bl_norm_kernel<C>, a, p, stream);
         case -3: return launch_kernel_pdl(gemv1_bl_routed_kernel<C>, a, p, stream);
         case -2: return launch_kernel_pdl(gemv1_bl_swiglu_kernel<C>, a, p, stream);
         case -1: return p.multi ? launch_kernel_pdl(gemv1_bl_multi_kernel<C>, a, p, stream, *p.multi) : cudaErrorInvalidValue;

@@ -237,6 +237,8 @@ void launch_bl_gemv(const NintDevB& w, const void* x, int m, void* y, int y_dtyp
 bool nint_bl_supported(int bits, int gs);
 size_t gemvs_fix_bytes(int device);
 void launch_swiglu(const void* gate_up, int in_dtype, int rows, int f, void* hidden, cudaStream_t s);
+void launch_bl_gemv_norm(const NintDevB& w, const float* h, const float* delta, const float* gamma, float eps, float* h_out, void* y, int y_dtype,
+                         bool glu, int device, cudaStream_t s);
 bool nint_bl_gemvh_supported(const NintDevB& w, int rows_per_launch);
 int g_moe_f16_from_x2 = 4;   // see mfqb_tune
 int g_gemm_plan_choice = 0;   // see mfqb_tune
@@ -445,6 +447,18 @@ int mfqb_mul_mat_swiglu(const mfqb_weight* w, const void* gate_up, int m, void* 
         launch_swiglu(gate_up, MFQB_F32, m, (int)w->info.k, act, stream);
         const int rc = mfqb_mul_mat(w, act, m, y, y_dtype, stream);
         if (rc != MFQB_OK) throw Error(rc, mfqb_last_error());
+    });
+}
+
+int mfqb_mul_mat_rmsnorm(const mfqb_weight* w, const float* h, const float* delta, const float* gamma, float eps, float* h_out, void* y,
+                         int y_dtype, int gated, mfqb_stream_t stream) {
+    return guarded([&] {
+        if (!w || !h || !gamma || !y) fail(MFQB_ERR_ARG, "mfqb_mul_mat_rmsnorm: null argument");
+        if (y_dtype != MFQB_F32 && y_dtype != MFQB_BF16) fail(MFQB_ERR_ARG, "mfqb_mul_mat_rmsnorm: bad output dtype");
+        if (h_out == h) fail(MFQB_ERR_ARG, "mfqb_mul_mat_rmsnorm: h_out must not be h (other CTAs still read h)");
+        if (w->family != MFQB_FAMILY_NINT || w->nint.table) fail(MFQB_ERR_UNSUPPORTED, "mfqb_mul_mat_rmsnorm: scalar-quantised (NINT) weights only");
+        DeviceGuard guard(w->device);
+        launch_bl_gemv_norm(w->nint, h, delta, gamma, eps, h_out, y, y_dtype, gated != 0, w->device, stream);
     });
 }
 

@@ -80,6 +80,19 @@ class QuantWeight:
                                F32 if tdt == torch.float32 else BF16, _stream_ptr(self.device)))
         return y[0] if squeeze else y
 
+    def matmul_rmsnorm(self, h, gamma, delta=None, eps: float = 1e-5, gated: bool = False, out_dtype=None, return_residual: bool = False):
+        """One float32 residual row ``h`` [k]: ``W @ ((h + delta) / rms(h + delta) * gamma)`` (or its gated form) in one
+        launch; with ``return_residual`` also ``h + delta``."""
+        torch = _torch()
+        h1 = h.reshape(-1).contiguous()
+        tdt = out_dtype or torch.bfloat16
+        y = torch.empty((self.n // 2 if gated else self.n,), dtype=tdt, device=h1.device)
+        h_out = torch.empty_like(h1) if return_residual else None
+        check(lib.mfqb_mul_mat_rmsnorm(self._h, h1.data_ptr(), None if delta is None else delta.contiguous().data_ptr(), gamma.contiguous().data_ptr(),
+                                       eps, None if h_out is None else h_out.data_ptr(), y.data_ptr(),
+                                       F32 if tdt == torch.float32 else BF16, int(gated), _stream_ptr(self.device)))
+        return (y, h_out) if return_residual else y
+
     def matmul_glu(self, x, out_dtype=None):
         """Gated product for a weight whose 16-row blocks alternate gate and up rows:
         ``up * silu(gate)`` of ``x @ W.T``, shape [m, n / 2]."""
