@@ -74,12 +74,19 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.perf_counter(), line.strip()))
 
-    def stop(self) -> dict:
+    def mark(self) -> float:
+        """A point in time to pass to stop(since=...): only samples that arrived after it are used."""
+        return time.perf_counter()
+
+    def samples_since(self, since: float) -> int:
+        return sum(1 for t, _ in list(self.lines) if t >= since)
+
+    def stop(self, since: float = 0.0) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=2)
@@ -87,7 +94,7 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        for _, line in [tl for tl in list(self.lines) if tl[0] >= since]:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 6:
                 continue
@@ -305,11 +312,12 @@ def main() -> None:
         torch.cuda.synchronize(dev)
 
     with torch.cuda.stream(stream):
+        sampler = ClockSampler(dev)
+        sampler.start()   # before the warm-up: the sampling process is then up when the timed region starts
         for _ in range(warmup):
             run_step()
         barrier()
-        sampler = ClockSampler(dev)
-        sampler.start()
+        region_start = sampler.mark()
         # one event per step boundary: the total (first to last) is the timed region, the gaps give the spread
         marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
         marks[0].record(stream)
@@ -317,7 +325,18 @@ def main() -> None:
             run_step()
             marks[i + 1].record(stream)
         barrier()
-        clocks = sampler.stop()
+        clock_note = None
+        if sampler.samples_since(region_start) < 3:
+            # a timed region shorter than a few sampling periods: keep the same load running (untimed) until there are samples
+            clock_note = "timed region shorter than the sampling period: sampled under the same load right after it"
+            t_load = time.perf_counter()
+            while sampler.proc is not None and sampler.samples_since(region_start) < 3 and time.perf_counter() - t_load < 1.0:
+                for _ in range(20):
+                    run_step()
+                torch.cuda.synchronize(dev)
+        clocks = sampler.stop(since=region_start)
+        if clock_note:
+            clocks["note"] = clock_note
         ms = marks[0].elapsed_time(marks[-1])
         per_step = sorted(marks[i].elapsed_time(marks[i + 1]) for i in range(steps))
         step_p50, step_p95 = per_step[len(per_step) // 2], per_step[min(len(per_step) - 1, int(0.95 * len(per_step)))]
