@@ -163,3 +163,15 @@ def test_header_sizes_are_checked_before_anything_is_allocated_for_them():
     with pytest.raises(MfqbError) as e:
         T.MfqFile(image=image)
     assert e.value.code == _capi.ERR_FORMAT and "record count" in str(e.value)
+
+
+def test_tune_switch_checks_key_and_range():
+    """Execution-plan switches need no device; an unknown key or a value outside the key's range is an
+    argument error and leaves the plan as it was."""
+    assert lib.mfqb_tune(b"gemv1_kernel", 0) == 0
+    assert lib.mfqb_tune(b"gemm_plan", 0) == 0
+    assert lib.mfqb_tune(b"moe_f16_tiles_from_x2", 4) == 0
+    for key, value in ((b"gemv1_kernel", 3), (b"gemm_plan", -1), (b"moe_f16_tiles_from_x2", 1), (b"no_such_key", 0)):
+        assert lib.mfqb_tune(key, value) == _capi.ERR_ARG
+        assert b"mfqb_tune" in lib.mfqb_last_error()
+    assert lib.mfqb_tune(None, 0) == _capi.ERR_ARG
